@@ -1,0 +1,592 @@
+// ExecutionEngine for B200: graph file -> one device arena -> node list -> (CUDA Graph) replay.
+//
+// Counterpart of the reference runtime core, with LibTorch removed:
+//   ExecutionEngine  csrc/runtime/execution_engine.cpp:12-43
+//   MemoryManager    csrc/runtime/memory_manager.cpp:30-123   (arena, registry, alias binding)
+//   RuntimeGraph     csrc/runtime/runtime_graph.cpp:8-24      (NoOp dropped, kernel resolved once)
+//   RuntimeNode      csrc/runtime/runtime_node.cpp:8-45       (ids/params copied out of the file)
+//
+// Memory: ONE cudaMalloc per engine, laid out as
+//   [ activations at the planner's offsets | constants | static input slots | per-node
+//     persistent memory | shared scratch | status word ]
+// every region 256-byte aligned.  The reference gives each FeedForward/MHA node its own
+// torch::empty intermediates (csrc/runtime/cache.cpp:28-73); nodes execute strictly one after
+// another, so a single scratch region sized for the hungriest node serves all of them.
+//
+// Inputs live in static slots (the caller's buffers are copied in on the run's stream), which
+// keeps every pointer inside a captured CUDA Graph stable and also makes an Alias/Output of an
+// Input see the data of the current run.
+#include <algorithm>
+#include <cstring>
+#include <fstream>
+#include <sstream>
+
+#include "fbs_reader.hpp"
+#include "runtime.hpp"
+
+namespace fxf {
+
+// ---- error plumbing -------------------------------------------------------------------
+static thread_local std::string g_last_error;
+void set_last_error(const std::string& msg) { g_last_error = msg; }
+const std::string& last_error() { return g_last_error; }
+
+int decode_build_mask(const int64_t* tokens, uint8_t* mask, int B, int T, int cur, int64_t pad, ExecCtx& ctx);
+int decode_argmax_scatter(const float* logits, int64_t* tokens, int B, int T, int64_t V, int cur, ExecCtx& ctx);
+
+namespace {
+
+enum Kind { kInput = 0, kConstant = 1, kActivation = 2, kAlias = 3, kOutput = 4 };
+constexpr size_t kAlign = 256;
+
+struct Node {
+    int op = 0;
+    TensorIds in, out;
+    Params params;
+    std::unique_ptr<NodePlan> plan;
+    KernelFn fn = nullptr;
+    int launches = 0;
+};
+
+}  // namespace
+}  // namespace fxf
+
+using namespace fxf;
+
+struct fxf_engine {
+    int device = 0;
+    std::string name;
+    FxfEngineOptions opts{};
+    Registry reg;
+    std::vector<Node> nodes;
+    std::vector<uint32_t> input_ids, output_ids;
+    std::vector<size_t> input_off;
+    uint8_t* base = nullptr;
+    size_t total_bytes = 0, arena_bytes = 0, const_bytes = 0, input_bytes = 0, persist_bytes = 0, scratch_bytes = 0;
+    size_t scratch_off = 0, status_off = 0;
+    ExecCtx ctx;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t graph_exec = nullptr;
+    cudaStream_t capture_stream = nullptr;
+    int launches_per_run = 0;
+
+    ~fxf_engine() {
+        if (graph_exec) cudaGraphExecDestroy(graph_exec);
+        if (graph) cudaGraphDestroy(graph);
+        if (capture_stream) cudaStreamDestroy(capture_stream);
+        if (base) cudaFree(base);
+    }
+};
+
+namespace fxf {
+namespace {
+
+int run_nodes(fxf_engine* e, cudaStream_t stream) {
+    e->ctx.stream = stream;
+    for (auto& n : e->nodes) {
+        int before = e->ctx.launches;
+        if (n.fn(e->reg, n.in, n.out, n.params, n.plan.get(), e->ctx)) return 1;
+        n.launches = e->ctx.launches - before;
+    }
+    return 0;
+}
+
+int ensure_device(const fxf_engine* e) {
+    int cur = -1;
+    FXF_CUDA(cudaGetDevice(&cur));
+    if (cur != e->device) FXF_CUDA(cudaSetDevice(e->device));
+    return 0;
+}
+
+int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
+    fbs::Buffer buf{bytes, nbytes};
+    FXF_CHECK(nbytes >= 8, "graph file is too small to hold a graph (%zu bytes)", nbytes);
+    fbs::Table g = fbs::root(&buf);
+    e->name = g.str(fbs::GraphF::name);
+    uint64_t arena = g.scalar<uint64_t>(fbs::GraphF::arena_size, 0);
+    FXF_CHECK(arena <= (uint64_t(1) << 40), "Arena size is implausible: %llu bytes", (unsigned long long)arena);
+    e->arena_bytes = size_t(arena);
+    uint32_t n_tensors = g.table_vec_size(fbs::GraphF::tensors);
+    uint32_t n_nodes = g.table_vec_size(fbs::GraphF::nodes);
+    FXF_CHECK(n_tensors > 0, "Execution graph is not loaded: the file holds no tensors");
+
+    struct Meta {
+        int kind = 0;
+        int64_t offset = -1;
+        int alias_of = -1;
+        const uint8_t* data = nullptr;
+        size_t data_len = 0;
+        size_t region_off = 0;
+        bool seen = false;
+    };
+    std::vector<Meta> meta(n_tensors);
+    std::vector<uint32_t> order;  // registry ids in file order
+    e->reg.assign(n_tensors, FxfTensor{});
+
+    size_t const_cursor = round_up(e->arena_bytes, kAlign);
+    const size_t const_begin = const_cursor;
+    for (uint32_t i = 0; i < n_tensors; i++) {
+        fbs::Table t = g.table_at(fbs::GraphF::tensors, i);
+        uint32_t id = t.scalar<uint32_t>(fbs::TensorF::id, 0);
+        FXF_CHECK(id < n_tensors, "tensor id %u exceeds the tensor table size %u", id, n_tensors);
+        FXF_CHECK(!meta[id].seen, "tensor id %u appears twice", id);
+        Meta& m = meta[id];
+        m.seen = true;
+        m.kind = t.scalar<int8_t>(fbs::TensorF::kind, 0);
+        m.offset = t.scalar<int64_t>(fbs::TensorF::offset, -1);
+        m.alias_of = t.scalar<int32_t>(fbs::TensorF::alias_of, -1);
+        FxfTensor& r = e->reg[id];
+        r.dtype = t.scalar<int8_t>(fbs::TensorF::dtype, 0);
+        FXF_CHECK(dtype_size(r.dtype) > 0, "Unsupported DType in FlatBuffer (tensor %u, dtype %d)", id, r.dtype);
+        auto shape = t.vec<int64_t>(fbs::TensorF::shape);
+        FXF_CHECK(shape.size() <= FXF_MAX_DIMS, "tensor %u has rank %u; at most %d dims are supported", id, shape.size(), FXF_MAX_DIMS);
+        r.rank = int(shape.size());
+        for (int k = 0; k < r.rank; k++) {
+            r.shape[k] = shape[k];
+            FXF_CHECK(r.shape[k] >= 0, "tensor %u has a negative extent", id);
+        }
+        set_contiguous(r);
+        r.nbytes = numel(r) * dtype_size(r.dtype);
+        auto data = t.vec<uint8_t>(fbs::TensorF::data);
+        m.data = data.base;
+        m.data_len = data.size();
+        FXF_CHECK(m.kind >= kInput && m.kind <= kOutput, "Unsupported TensorKind in FlatBuffer (tensor %u, kind %d)", id, m.kind);
+        if (m.kind == kConstant) {
+            FXF_CHECK(m.data != nullptr, "Constant tensor missing data (tensor %u)", id);
+            FXF_CHECK(m.data_len >= size_t(r.nbytes), "Constant tensor %u carries %zu bytes but its shape needs %lld", id, m.data_len, (long long)r.nbytes);
+            m.region_off = const_cursor;
+            const_cursor = round_up(const_cursor + size_t(r.nbytes), kAlign);
+        }
+        order.push_back(id);
+    }
+    e->const_bytes = const_cursor - const_begin;
+    size_t cursor = const_cursor;
+    for (uint32_t id : order) {
+        if (meta[id].kind != kInput) continue;
+        e->input_ids.push_back(id);
+        meta[id].region_off = cursor;
+        e->input_off.push_back(cursor);
+        cursor = round_up(cursor + size_t(e->reg[id].nbytes), kAlign);
+    }
+    e->input_bytes = cursor - const_cursor;
+
+    // ---- nodes: ids and params are copied out; the file buffer is not needed after build ----
+    for (uint32_t i = 0; i < n_nodes; i++) {
+        fbs::Table nt = g.table_at(fbs::GraphF::nodes, i);
+        int op = nt.scalar<int8_t>(fbs::NodeF::op_code, 0);
+        if (op == FXF_OP_NOOP) continue;
+        FXF_CHECK(op > 0 && op < FXF_OP_COUNT, "Unsupported OpCode: %d", op);
+        const OpEntry& entry = op_entry(op);
+        FXF_CHECK(entry.kernel != nullptr, "Unregistered OpCode: %d", op);
+        Node n;
+        n.op = op;
+        n.fn = entry.kernel;
+        auto in = nt.vec<uint32_t>(fbs::NodeF::input_ids);
+        auto out = nt.vec<uint32_t>(fbs::NodeF::output_ids);
+        auto ints = nt.vec<int64_t>(fbs::NodeF::int_params);
+        auto floats = nt.vec<float>(fbs::NodeF::float_params);
+        for (uint32_t k = 0; k < in.size(); k++) n.in.push_back(in[k]);
+        for (uint32_t k = 0; k < out.size(); k++) n.out.push_back(out[k]);
+        for (uint32_t k = 0; k < ints.size(); k++) n.params.ints.push_back(ints[k]);
+        for (uint32_t k = 0; k < floats.size(); k++) n.params.floats.push_back(floats[k]);
+        for (auto id : n.in) FXF_CHECK(id < n_tensors, "node %u (%s) reads tensor id %u which does not exist", i, entry.name, id);
+        for (auto id : n.out) FXF_CHECK(id < n_tensors, "node %u (%s) writes tensor id %u which does not exist", i, entry.name, id);
+        FXF_CHECK(!n.out.empty(), "node %u (%s) has no output", i, entry.name);
+        n.plan = entry.plan(e->reg, n.in, n.out, n.params, e->opts.gemm_mode);
+        e->scratch_bytes = std::max(e->scratch_bytes, n.plan->scratch_bytes);
+        e->persist_bytes += round_up(n.plan->persist_bytes, kAlign);
+        e->nodes.push_back(std::move(n));
+    }
+    size_t persist_off = cursor;
+    cursor += e->persist_bytes;
+    e->scratch_off = cursor;
+    cursor = round_up(cursor + e->scratch_bytes, kAlign);
+    e->status_off = cursor;
+    cursor += kAlign;
+    e->total_bytes = cursor;
+
+    // ---- the one device allocation -----------------------------------------------------------
+    FXF_CUDA(cudaSetDevice(e->device));
+    cudaDeviceProp prop;
+    FXF_CUDA(cudaGetDeviceProperties(&prop, e->device));
+    FXF_CHECK(prop.major == 10, "this library is built for sm_100a only (B200); device %d is sm_%d%d", e->device, prop.major, prop.minor);
+    e->ctx.sm_count = prop.multiProcessorCount;
+    e->ctx.gemm_mode = e->opts.gemm_mode;
+    void* p = nullptr;
+    cudaError_t err = cudaMalloc(&p, e->total_bytes);
+    if (err != cudaSuccess) FXF_FAIL("Arena tensor is not allocated: cudaMalloc(%zu bytes) failed: %s", e->total_bytes, cudaGetErrorString(err));
+    e->base = static_cast<uint8_t*>(p);
+    FXF_CUDA(cudaMemset(e->base, 0, e->arena_bytes));
+    FXF_CUDA(cudaMemset(e->base + e->status_off, 0, kAlign));
+    e->ctx.scratch = e->base + e->scratch_off;
+    e->ctx.scratch_bytes = e->scratch_bytes;
+    e->ctx.status = reinterpret_cast<int*>(e->base + e->status_off);
+
+    // ---- registry binding, in file order (an alias binds to an already-built source) --------
+    std::vector<bool> bound(n_tensors, false);
+    for (uint32_t id : order) {
+        Meta& m = meta[id];
+        FxfTensor& r = e->reg[id];
+        switch (m.kind) {
+            case kConstant:
+                r.ptr = e->base + m.region_off;
+                if (r.nbytes) FXF_CUDA(cudaMemcpy(r.ptr, m.data, size_t(r.nbytes), cudaMemcpyHostToDevice));
+                break;
+            case kInput:
+                r.ptr = e->base + m.region_off;
+                if (r.nbytes) FXF_CUDA(cudaMemset(r.ptr, 0, size_t(r.nbytes)));
+                break;
+            case kActivation:
+                FXF_CHECK(m.offset >= 0, "Arena-backed tensor has invalid offset (tensor %u)", id);
+                FXF_CHECK(size_t(m.offset) + size_t(r.nbytes) <= e->arena_bytes, "tensor %u [%lld, +%lld) lies outside the arena of %zu bytes", id,
+                          (long long)m.offset, (long long)r.nbytes, e->arena_bytes);
+                r.ptr = e->base + m.offset;
+                break;
+            case kAlias:
+            case kOutput:
+                if (m.offset >= 0) {
+                    FXF_CHECK(size_t(m.offset) + size_t(r.nbytes) <= e->arena_bytes, "tensor %u [%lld, +%lld) lies outside the arena of %zu bytes", id,
+                              (long long)m.offset, (long long)r.nbytes, e->arena_bytes);
+                    r.ptr = e->base + m.offset;
+                } else {
+                    int src = m.alias_of;
+                    FXF_CHECK(src >= 0 && uint32_t(src) < n_tensors, "Invalid alias source ID (tensor %u aliases %d)", id, src);
+                    FXF_CHECK(bound[src], "Alias source tensor is not defined (tensor %u aliases %d)", id, src);
+                    FXF_CHECK(numel(e->reg[src]) == numel(r),
+                              "Alias numel mismatch for tensor id %u — runtime-shape-changing ops must not be marked as Alias kind", id);
+                    r.ptr = e->reg[src].ptr;
+                }
+                if (m.kind == kOutput) e->output_ids.push_back(id);
+                break;
+        }
+        bound[id] = true;
+    }
+
+    // ---- per-node persistent memory + one-off preparation -----------------------------------
+    size_t pcur = persist_off;
+    for (auto& n : e->nodes) {
+        if (n.plan->persist_bytes) {
+            n.plan->persist = e->base + pcur;
+            pcur += round_up(n.plan->persist_bytes, kAlign);
+        }
+        if (n.plan->prepare(e->reg, n.in, n.out, n.params, e->ctx)) return 1;
+    }
+    FXF_CUDA(cudaDeviceSynchronize());
+
+    // ---- warm-up run (validates every node's arguments), then capture ------------------------
+    FXF_CUDA(cudaStreamCreateWithFlags(&e->capture_stream, cudaStreamNonBlocking));
+    e->ctx.launches = 0;
+    if (run_nodes(e, e->capture_stream)) return 1;
+    e->launches_per_run = e->ctx.launches;
+    FXF_CUDA(cudaStreamSynchronize(e->capture_stream));
+    if (e->opts.use_cuda_graph && !e->nodes.empty()) {
+        FXF_CUDA(cudaStreamBeginCapture(e->capture_stream, cudaStreamCaptureModeThreadLocal));
+        int rc = run_nodes(e, e->capture_stream);
+        cudaError_t ce = cudaStreamEndCapture(e->capture_stream, &e->graph);
+        if (rc) return 1;
+        if (ce != cudaSuccess) FXF_FAIL("CUDA Graph capture failed: %s", cudaGetErrorString(ce));
+        FXF_CUDA(cudaGraphInstantiate(&e->graph_exec, e->graph, 0));
+    }
+    // the warm-up ran on zeroed inputs; leave the arena clean
+    FXF_CUDA(cudaMemset(e->base, 0, e->arena_bytes));
+    FXF_CUDA(cudaMemset(e->base + e->status_off, 0, kAlign));
+    FXF_CUDA(cudaDeviceSynchronize());
+    return 0;
+}
+
+int create_from_bytes(const uint8_t* bytes, size_t nbytes, int device, const FxfEngineOptions* opts, fxf_engine** out) {
+    FXF_CHECK(out != nullptr, "fxf_engine_create: out_engine is NULL");
+    *out = nullptr;
+    auto e = std::make_unique<fxf_engine>();
+    e->device = device;
+    e->opts.struct_size = sizeof(FxfEngineOptions);
+    e->opts.use_cuda_graph = 1;
+    e->opts.gemm_mode = FXF_GEMM_AUTO;
+    e->opts.tp_size = 1;
+    if (opts) {
+        size_t n = std::min<size_t>(sizeof(FxfEngineOptions), opts->struct_size > 0 ? size_t(opts->struct_size) : sizeof(FxfEngineOptions));
+        std::memcpy(&e->opts, opts, n);
+        if (e->opts.tp_size < 1) e->opts.tp_size = 1;
+    }
+    FXF_CHECK(e->opts.tp_size == 1, "tensor-parallel engines are not available in this build");
+    int count = 0;
+    FXF_CUDA(cudaGetDeviceCount(&count));
+    FXF_CHECK(device >= 0 && device < count, "device ordinal %d is out of range (%d CUDA devices)", device, count);
+    try {
+        if (build(e.get(), bytes, nbytes)) return 1;
+    } catch (const std::exception& ex) {
+        FXF_FAIL("%s", ex.what());
+    }
+    *out = e.release();
+    return 0;
+}
+
+}  // namespace
+}  // namespace fxf
+
+// =============================================================================================
+// C ABI
+// =============================================================================================
+extern "C" {
+
+const char* fxf_last_error(void) { return fxf::last_error().c_str(); }
+
+const char* fxf_version(void) { return "fxf_b200 19 ops sm_100a"; }
+
+int fxf_engine_create(const char* graph_path, int device_ordinal, const FxfEngineOptions* opts, fxf_engine** out_engine) {
+    FXF_CHECK(graph_path != nullptr, "fxf_engine_create: graph_path is NULL");
+    std::ifstream f(graph_path, std::ios::binary | std::ios::ate);
+    if (!f.is_open()) FXF_FAIL("ExecutionEngine failed to open: %s", graph_path);
+    std::streamsize size = f.tellg();
+    f.seekg(0, std::ios::beg);
+    std::vector<uint8_t> bytes(size > 0 ? size_t(size) : 0);
+    if (size > 0 && !f.read(reinterpret_cast<char*>(bytes.data()), size)) FXF_FAIL("ExecutionEngine failed to read: %s", graph_path);
+    return create_from_bytes(bytes.data(), bytes.size(), device_ordinal, opts, out_engine);
+}
+
+int fxf_engine_create_from_memory(const void* bytes, size_t nbytes, int device_ordinal, const FxfEngineOptions* opts, fxf_engine** out_engine) {
+    FXF_CHECK(bytes != nullptr, "fxf_engine_create_from_memory: bytes is NULL");
+    return create_from_bytes(static_cast<const uint8_t*>(bytes), nbytes, device_ordinal, opts, out_engine);
+}
+
+void fxf_engine_destroy(fxf_engine* e) {
+    if (!e) return;
+    int cur = -1;
+    cudaGetDevice(&cur);
+    if (cur != e->device) cudaSetDevice(e->device);
+    cudaDeviceSynchronize();
+    const int dev = e->device;
+    delete e;
+    if (cur >= 0 && cur != dev) cudaSetDevice(cur);
+}
+
+int fxf_engine_num_inputs(const fxf_engine* e) { return e ? int(e->input_ids.size()) : -1; }
+int fxf_engine_num_outputs(const fxf_engine* e) { return e ? int(e->output_ids.size()) : -1; }
+int fxf_engine_num_nodes(const fxf_engine* e) { return e ? int(e->nodes.size()) : -1; }
+int64_t fxf_engine_arena_bytes(const fxf_engine* e) { return e ? int64_t(e->arena_bytes) : -1; }
+int64_t fxf_engine_device_bytes(const fxf_engine* e) { return e ? int64_t(e->total_bytes) : -1; }
+int fxf_engine_launches_per_run(const fxf_engine* e) { return e ? e->launches_per_run : -1; }
+
+int fxf_engine_input_desc(const fxf_engine* e, int i, FxfTensor* out) {
+    FXF_CHECK(e && out, "fxf_engine_input_desc: NULL argument");
+    FXF_CHECK(i >= 0 && size_t(i) < e->input_ids.size(), "input index %d out of range", i);
+    *out = e->reg[e->input_ids[i]];
+    return 0;
+}
+int fxf_engine_output_desc(const fxf_engine* e, int i, FxfTensor* out) {
+    FXF_CHECK(e && out, "fxf_engine_output_desc: NULL argument");
+    FXF_CHECK(i >= 0 && size_t(i) < e->output_ids.size(), "output index %d out of range", i);
+    *out = e->reg[e->output_ids[i]];
+    return 0;
+}
+
+static int launch_forward(fxf_engine* e, cudaStream_t s) {
+    if (e->graph_exec) {
+        FXF_CUDA(cudaGraphLaunch(e->graph_exec, s));
+        return 0;
+    }
+    return run_nodes(e, s);
+}
+
+int fxf_engine_run(fxf_engine* e, const void* const* device_inputs, int n_inputs, void* stream) {
+    FXF_CHECK(e != nullptr, "fxf_engine_run: engine is NULL");
+    FXF_CHECK(size_t(n_inputs) == e->input_ids.size(), "Input count mismatch: the graph has %zu inputs, %d were given", e->input_ids.size(), n_inputs);
+    if (ensure_device(e)) return 1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    for (int i = 0; i < n_inputs; i++) {
+        FxfTensor& slot = e->reg[e->input_ids[i]];
+        FXF_CHECK(device_inputs && device_inputs[i], "input %d is NULL", i);
+        if (device_inputs[i] != slot.ptr && slot.nbytes)
+            FXF_CUDA(cudaMemcpyAsync(slot.ptr, device_inputs[i], size_t(slot.nbytes), cudaMemcpyDeviceToDevice, s));
+    }
+    return launch_forward(e, s);
+}
+
+int fxf_engine_run_host(fxf_engine* e, const void* const* host_inputs, int n_inputs, void* const* host_outputs, int n_outputs, void* stream) {
+    FXF_CHECK(e != nullptr, "fxf_engine_run_host: engine is NULL");
+    FXF_CHECK(size_t(n_inputs) == e->input_ids.size(), "Input count mismatch: the graph has %zu inputs, %d were given", e->input_ids.size(), n_inputs);
+    if (ensure_device(e)) return 1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    for (int i = 0; i < n_inputs; i++) {
+        FxfTensor& slot = e->reg[e->input_ids[i]];
+        FXF_CHECK(host_inputs && host_inputs[i], "input %d is NULL", i);
+        if (slot.nbytes) FXF_CUDA(cudaMemcpyAsync(slot.ptr, host_inputs[i], size_t(slot.nbytes), cudaMemcpyHostToDevice, s));
+    }
+    if (launch_forward(e, s)) return 1;
+    if (host_outputs) {
+        FXF_CHECK(size_t(n_outputs) == e->output_ids.size(), "Output count mismatch: the graph has %zu outputs, %d buffers were given", e->output_ids.size(), n_outputs);
+        for (int i = 0; i < n_outputs; i++) {
+            const FxfTensor& o = e->reg[e->output_ids[i]];
+            if (host_outputs[i] && o.nbytes) FXF_CUDA(cudaMemcpyAsync(host_outputs[i], o.ptr, size_t(o.nbytes), cudaMemcpyDeviceToHost, s));
+        }
+        FXF_CUDA(cudaStreamSynchronize(s));
+    }
+    return 0;
+}
+
+int fxf_engine_device_status(fxf_engine* e, void* stream, int* status_out) {
+    FXF_CHECK(e && status_out, "fxf_engine_device_status: NULL argument");
+    if (ensure_device(e)) return 1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    FXF_CUDA(cudaMemcpyAsync(status_out, e->ctx.status, sizeof(int), cudaMemcpyDeviceToHost, s));
+    FXF_CUDA(cudaStreamSynchronize(s));
+    return 0;
+}
+
+int fxf_engine_describe(const fxf_engine* e, char* out, size_t out_bytes) {
+    FXF_CHECK(e && out && out_bytes > 0, "fxf_engine_describe: NULL argument");
+    std::ostringstream os;
+    os << "graph '" << e->name << "' device " << e->device << " nodes " << e->nodes.size() << " tensors " << e->reg.size() << "\n";
+    os << "device allocation " << e->total_bytes << " B = arena " << e->arena_bytes << " + constants " << e->const_bytes << " + input slots " << e->input_bytes
+       << " + persistent " << e->persist_bytes << " + scratch " << e->scratch_bytes << " + status 256\n";
+    os << "cuda_graph " << (e->graph_exec ? "yes" : "no") << " launches/run " << e->launches_per_run << "\n";
+    for (size_t i = 0; i < e->nodes.size(); i++) {
+        const Node& n = e->nodes[i];
+        os << i << " " << op_entry(n.op).name << " in[";
+        for (auto id : n.in) os << id << " ";
+        os << "] out[";
+        for (auto id : n.out) os << id << "@" << (static_cast<uint8_t*>(e->reg[id].ptr) - e->base) << " ";
+        os << "] launches " << n.launches << " variant " << n.plan->variant << " scratch " << n.plan->scratch_bytes << "\n";
+    }
+    std::string s = os.str();
+    size_t n = std::min(out_bytes - 1, s.size());
+    std::memcpy(out, s.data(), n);
+    out[n] = 0;
+    return 0;
+}
+
+int fxf_engine_node_info(const fxf_engine* e, int node, int* op_code, double* flops, double* bytes, char* variant, size_t variant_bytes) {
+    FXF_CHECK(e != nullptr, "fxf_engine_node_info: engine is NULL");
+    FXF_CHECK(node >= 0 && size_t(node) < e->nodes.size(), "node index %d out of range", node);
+    const Node& n = e->nodes[node];
+    if (op_code) *op_code = n.op;
+    if (flops) *flops = n.plan->flops;
+    if (bytes) *bytes = n.plan->bytes;
+    if (variant && variant_bytes) {
+        size_t k = std::min(variant_bytes - 1, n.plan->variant.size());
+        std::memcpy(variant, n.plan->variant.data(), k);
+        variant[k] = 0;
+    }
+    return 0;
+}
+
+int fxf_engine_time_nodes(fxf_engine* e, float* ms_out, int n, void* stream) {
+    FXF_CHECK(e && ms_out, "fxf_engine_time_nodes: NULL argument");
+    FXF_CHECK(size_t(n) >= e->nodes.size(), "fxf_engine_time_nodes: buffer holds %d values, %zu needed", n, e->nodes.size());
+    if (ensure_device(e)) return 1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    std::vector<cudaEvent_t> ev(e->nodes.size() + 1);
+    for (auto& x : ev) FXF_CUDA(cudaEventCreate(&x));
+    e->ctx.stream = s;
+    FXF_CUDA(cudaEventRecord(ev[0], s));
+    int rc = 0;
+    for (size_t i = 0; i < e->nodes.size() && !rc; i++) {
+        Node& nd = e->nodes[i];
+        rc = nd.fn(e->reg, nd.in, nd.out, nd.params, nd.plan.get(), e->ctx);
+        cudaEventRecord(ev[i + 1], s);
+    }
+    cudaStreamSynchronize(s);
+    if (!rc)
+        for (size_t i = 0; i < e->nodes.size(); i++) cudaEventElapsedTime(&ms_out[i], ev[i], ev[i + 1]);
+    for (auto& x : ev) cudaEventDestroy(x);
+    return rc;
+}
+
+// ---- single kernels -----------------------------------------------------------------------------
+static int make_call(int op_code, const FxfTensor* reg, int n_reg, const uint32_t* in_ids, int n_in, const uint32_t* out_ids, int n_out,
+                     const int64_t* ints, int n_ints, const float* floats, int n_floats, Registry* r, TensorIds* in, TensorIds* out, Params* p) {
+    FXF_CHECK(op_code > 0 && op_code < FXF_OP_COUNT, "Unsupported OpCode: %d", op_code);
+    FXF_CHECK(reg != nullptr && n_reg > 0, "kernel call: empty registry");
+    r->assign(reg, reg + n_reg);
+    for (int i = 0; i < n_in; i++) {
+        FXF_CHECK(in_ids[i] < uint32_t(n_reg), "kernel call: input id %u out of range", in_ids[i]);
+        in->push_back(in_ids[i]);
+    }
+    for (int i = 0; i < n_out; i++) {
+        FXF_CHECK(out_ids[i] < uint32_t(n_reg), "kernel call: output id %u out of range", out_ids[i]);
+        out->push_back(out_ids[i]);
+    }
+    FXF_CHECK(!out->empty(), "kernel call: no output id");
+    if (n_ints > 0) p->ints.assign(ints, ints + n_ints);
+    if (n_floats > 0) p->floats.assign(floats, floats + n_floats);
+    for (auto& t : *r) FXF_CHECK(t.rank >= 0 && t.rank <= FXF_MAX_DIMS, "kernel call: tensor rank out of range");
+    return 0;
+}
+
+int64_t fxf_kernel_scratch_bytes(int op_code, const FxfTensor* reg, int n_reg, const uint32_t* in_ids, int n_in, const uint32_t* out_ids, int n_out,
+                                 const int64_t* ints, int n_ints, const float* floats, int n_floats, int gemm_mode) {
+    Registry r;
+    TensorIds in, out;
+    Params p;
+    if (make_call(op_code, reg, n_reg, in_ids, n_in, out_ids, n_out, ints, n_ints, floats, n_floats, &r, &in, &out, &p)) return -1;
+    auto plan = op_entry(op_code).plan(r, in, out, p, gemm_mode);
+    return int64_t(plan->scratch_bytes);
+}
+
+int fxf_kernel_invoke(int op_code, const FxfTensor* reg, int n_reg, const uint32_t* in_ids, int n_in, const uint32_t* out_ids, int n_out,
+                      const int64_t* ints, int n_ints, const float* floats, int n_floats, void* scratch, int64_t scratch_bytes, int gemm_mode,
+                      void* stream) {
+    Registry r;
+    TensorIds in, out;
+    Params p;
+    if (make_call(op_code, reg, n_reg, in_ids, n_in, out_ids, n_out, ints, n_ints, floats, n_floats, &r, &in, &out, &p)) return 1;
+    const OpEntry& entry = op_entry(op_code);
+    auto plan = entry.plan(r, in, out, p, gemm_mode);
+    FXF_CHECK(plan->persist_bytes == 0, "kernel call: op needs persistent memory; use an engine");
+    ExecCtx ctx;
+    ctx.stream = static_cast<cudaStream_t>(stream);
+    ctx.scratch = scratch;
+    ctx.scratch_bytes = scratch_bytes > 0 ? size_t(scratch_bytes) : 0;
+    ctx.gemm_mode = gemm_mode;
+    int dev = 0;
+    FXF_CUDA(cudaGetDevice(&dev));
+    int sms = 0;
+    FXF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    ctx.sm_count = sms;
+    return entry.kernel(r, in, out, p, plan.get(), ctx);
+}
+
+// ---- greedy static decode ---------------------------------------------------------------------
+int fxf_decode_build_mask(const int64_t* tokens, uint8_t* mask, int B, int T, int current_len, int64_t pad_idx, void* stream) {
+    FXF_CHECK(tokens && mask, "fxf_decode_build_mask: NULL argument");
+    ExecCtx ctx;
+    ctx.stream = static_cast<cudaStream_t>(stream);
+    return decode_build_mask(tokens, mask, B, T, current_len, pad_idx, ctx);
+}
+
+int fxf_decode_argmax_scatter(const float* logits, int64_t* tokens, int B, int T, int64_t V, int current_len, void* stream) {
+    FXF_CHECK(logits && tokens, "fxf_decode_argmax_scatter: NULL argument");
+    ExecCtx ctx;
+    ctx.stream = static_cast<cudaStream_t>(stream);
+    return decode_argmax_scatter(logits, tokens, B, T, V, current_len, ctx);
+}
+
+int fxf_decode_static(fxf_engine* e, int64_t* tokens_io, int initial_len, int64_t pad_idx, void* stream) {
+    FXF_CHECK(e && tokens_io, "fxf_decode_static: NULL argument");
+    FXF_CHECK(e->input_ids.size() == 2 && e->output_ids.size() >= 1, "fxf_decode_static: the graph must take (tokens, mask) and return logits");
+    if (ensure_device(e)) return 1;
+    FxfTensor& tok = e->reg[e->input_ids[0]];
+    FxfTensor& mask = e->reg[e->input_ids[1]];
+    const FxfTensor& logits = e->reg[e->output_ids[0]];
+    FXF_CHECK(tok.dtype == FXF_I64 && tok.rank == 2, "fxf_decode_static: input 0 must be int64 [B,T]");
+    int B = int(tok.shape[0]), T = int(tok.shape[1]);
+    FXF_CHECK(mask.dtype == FXF_BOOL && mask.rank == 4 && mask.shape[0] == B && mask.shape[1] == 1 && mask.shape[2] == T && mask.shape[3] == T,
+              "fxf_decode_static: input 1 must be bool [B,1,T,T]");
+    FXF_CHECK(logits.dtype == FXF_F32 && logits.rank == 3 && logits.shape[0] == B && logits.shape[1] == T, "fxf_decode_static: output 0 must be float32 [B,T,V]");
+    FXF_CHECK(initial_len >= 1 && initial_len <= T, "fxf_decode_static: initial_len %d must be in [1, %d]", initial_len, T);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int64_t* slot = static_cast<int64_t*>(tok.ptr);
+    if (tokens_io != slot) FXF_CUDA(cudaMemcpyAsync(slot, tokens_io, size_t(tok.nbytes), cudaMemcpyDeviceToDevice, s));
+    ExecCtx ctx;
+    ctx.stream = s;
+    ctx.sm_count = e->ctx.sm_count;
+    for (int cur = initial_len; cur < T; cur++) {
+        if (decode_build_mask(slot, static_cast<uint8_t*>(mask.ptr), B, T, cur, pad_idx, ctx)) return 1;
+        if (launch_forward(e, s)) return 1;
+        if (decode_argmax_scatter(static_cast<const float*>(logits.ptr), slot, B, T, logits.shape[2], cur, ctx)) return 1;
+    }
+    if (tokens_io != slot) FXF_CUDA(cudaMemcpyAsync(tokens_io, slot, size_t(tok.nbytes), cudaMemcpyDeviceToDevice, s));
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,313 @@
+// Conv2d / Conv2dRelu (BatchNorm already folded into weight and bias by the compile side) and
+// the window-pooling ops, on NCHW float32 tensors as the graph contract stores them.
+//
+// Reference semantics (LibTorch calls):
+//   conv2d / conv2d_relu  csrc/kernels/cpu/conv2d.cpp:5-17, conv2d_relu.cpp:5-17
+//       ints = [sh, sw, ph, pw, dh, dw, groups, <6 unused launch placeholders>]
+//   max_pool2d            csrc/kernels/cpu/max_pool2d.cpp:5-16
+//       ints = [kh, kw, sh, sw, ph, pw, dh, dw, ceil_mode, ...]; padding counts as -inf, NaN wins
+//   avg_pool2d            csrc/kernels/cpu/avg_pool2d.cpp:5-15
+//       ints = [kh, kw, sh, sw, ph, pw, ceil_mode, ...]; count_include_pad = true, the divisor is
+//       the window clipped to the padded extent
+//   adaptive_avg_pool2d   csrc/kernels/cpu/adaptive_avg_pool2d.cpp:5-12
+//       ints = [oh, ow, ...]; window i = [floor(i*H/oh), ceil((i+1)*H/oh))
+//
+// The convolution is an implicit GEMM (rows = output pixels n*Ho*Wo, columns = output
+// channels, depth = Cin/groups*Kh*Kw) on fp32 FFMA tiles of 64x64x16: the im2col gather happens
+// while the A tile is staged into shared memory, consecutive threads walk consecutive output
+// pixels so both the gather and the NCHW store are coalesced along W.
+#include <cfloat>
+#include <cmath>
+
+#include "../runtime.hpp"
+
+namespace fxf {
+namespace {
+
+struct ConvDesc {
+    int N, C, H, W, O, KH, KW, HO, WO;
+    int sh, sw, ph, pw, dh, dw, groups;
+    int cg, og;   // channels / outputs per group
+    int relu;
+};
+
+constexpr int CBM = 64, CBN = 64, CBK = 16;
+
+__global__ void __launch_bounds__(256) conv2d_igemm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                                                           float* __restrict__ out, ConvDesc d) {
+    __shared__ __align__(16) float As[CBK][CBM + 4];
+    __shared__ __align__(16) float Bs[CBK][CBN + 4];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;  // tx -> pixels, ty -> channels
+    const int g = blockIdx.z;
+    const int64_t pix0 = int64_t(blockIdx.x) * CBM;
+    const int oc0 = blockIdx.y * CBN;  // within group
+    const int64_t n_pix = int64_t(d.N) * d.HO * d.WO;
+    const int Kdepth = d.cg * d.KH * d.KW;
+
+    // A staging: thread loads 4 (pixel, k) pairs: pixel = tid % 64, k = tid / 64 + 4*i
+    const int a_pix = tid & 63, a_k0 = tid >> 6;
+    int64_t gp = pix0 + a_pix;
+    int pn = 0, py = 0, px = 0;
+    bool pvalid = gp < n_pix;
+    if (pvalid) {
+        px = int(gp % d.WO);
+        int64_t t = gp / d.WO;
+        py = int(t % d.HO);
+        pn = int(t / d.HO);
+    }
+    // B staging: weight row (oc) x 16 k-values; thread loads 4: oc = tid / 4, k = (tid % 4) * 4 + i
+    const int b_oc = tid >> 2, b_k0 = (tid & 3) * 4;
+
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+
+    for (int k0 = 0; k0 < Kdepth; k0 += CBK) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int k = k0 + a_k0 + 4 * i;
+            float v = 0.f;
+            if (pvalid && k < Kdepth) {
+                int kw = k % d.KW;
+                int t = k / d.KW;
+                int kh = t % d.KH;
+                int c = t / d.KH;
+                int iy = py * d.sh - d.ph + kh * d.dh, ix = px * d.sw - d.pw + kw * d.dw;
+                if (iy >= 0 && iy < d.H && ix >= 0 && ix < d.W)
+                    v = x[((int64_t(pn) * d.C + g * d.cg + c) * d.H + iy) * d.W + ix];
+            }
+            As[a_k0 + 4 * i][a_pix] = v;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int k = k0 + b_k0 + i, oc = oc0 + b_oc;
+            float v = 0.f;
+            if (oc < d.og && k < Kdepth) v = w[(int64_t(g) * d.og + oc) * Kdepth + k];
+            Bs[b_k0 + i][b_oc] = v;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < CBK; k++) {
+            float4 av = *reinterpret_cast<const float4*>(&As[k][tx * 4]);
+            float4 bv = *reinterpret_cast<const float4*>(&Bs[k][ty * 4]);
+            float a[4] = {av.x, av.y, av.z, av.w}, b[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int64_t p = pix0 + tx * 4 + i;
+        if (p >= n_pix) continue;
+        int ox = int(p % d.WO);
+        int64_t t = p / d.WO;
+        int oy = int(t % d.HO), n = int(t / d.HO);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            int oc = oc0 + ty * 4 + j;
+            if (oc >= d.og) continue;
+            int o = g * d.og + oc;
+            float v = acc[i][j] + bias[o];
+            if (d.relu) v = v > 0.f ? v : (v != v ? v : 0.f);
+            out[((int64_t(n) * d.O + o) * d.HO + oy) * d.WO + ox] = v;
+        }
+    }
+}
+
+struct PoolDesc {
+    int64_t NC;
+    int H, W, HO, WO, kh, kw, sh, sw, ph, pw, dh, dw;
+};
+
+__global__ void __launch_bounds__(256) max_pool2d_kernel(const float* __restrict__ x, float* __restrict__ out, PoolDesc d) {
+    int64_t total = d.NC * d.HO * d.WO, stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        int ox = int(i % d.WO);
+        int64_t t = i / d.WO;
+        int oy = int(t % d.HO);
+        int64_t nc = t / d.HO;
+        const float* src = x + nc * d.H * d.W;
+        float m = -INFINITY;
+        for (int a = 0; a < d.kh; a++) {
+            int iy = oy * d.sh - d.ph + a * d.dh;
+            if (iy < 0 || iy >= d.H) continue;
+            for (int b = 0; b < d.kw; b++) {
+                int ix = ox * d.sw - d.pw + b * d.dw;
+                if (ix < 0 || ix >= d.W) continue;
+                float v = src[int64_t(iy) * d.W + ix];
+                if (v > m || v != v) m = v;
+            }
+        }
+        out[i] = m;
+    }
+}
+
+__global__ void __launch_bounds__(256) avg_pool2d_kernel(const float* __restrict__ x, float* __restrict__ out, PoolDesc d) {
+    int64_t total = d.NC * d.HO * d.WO, stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        int ox = int(i % d.WO);
+        int64_t t = i / d.WO;
+        int oy = int(t % d.HO);
+        int64_t nc = t / d.HO;
+        const float* src = x + nc * d.H * d.W;
+        int hs = oy * d.sh - d.ph, ws = ox * d.sw - d.pw;
+        int he = min(hs + d.kh, d.H + d.ph), we = min(ws + d.kw, d.W + d.pw);
+        int pool = (he - hs) * (we - ws);  // count_include_pad
+        int hs2 = max(hs, 0), ws2 = max(ws, 0), he2 = min(he, d.H), we2 = min(we, d.W);
+        float s = 0.f;
+        for (int iy = hs2; iy < he2; iy++)
+            for (int ix = ws2; ix < we2; ix++) s += src[int64_t(iy) * d.W + ix];
+        out[i] = s / float(pool);
+    }
+}
+
+__global__ void __launch_bounds__(256) adaptive_avg_pool2d_kernel(const float* __restrict__ x, float* __restrict__ out, PoolDesc d) {
+    int64_t total = d.NC * d.HO * d.WO, stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        int ox = int(i % d.WO);
+        int64_t t = i / d.WO;
+        int oy = int(t % d.HO);
+        int64_t nc = t / d.HO;
+        const float* src = x + nc * d.H * d.W;
+        int hs = int((int64_t(oy) * d.H) / d.HO), he = int((int64_t(oy + 1) * d.H + d.HO - 1) / d.HO);
+        int ws = int((int64_t(ox) * d.W) / d.WO), we = int((int64_t(ox + 1) * d.W + d.WO - 1) / d.WO);
+        float s = 0.f;
+        for (int iy = hs; iy < he; iy++)
+            for (int ix = ws; ix < we; ix++) s += src[int64_t(iy) * d.W + ix];
+        out[i] = s / float((he - hs) * (we - ws));
+    }
+}
+
+// Global average (output 1x1): one warp per (n,c) plane, coalesced reads, shuffle reduction.
+__global__ void __launch_bounds__(256) global_avg_pool_kernel(const float* __restrict__ x, float* __restrict__ out, int64_t NC, int HW) {
+    int lane = threadIdx.x & 31;
+    int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5, nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+    for (int64_t p = warp; p < NC; p += nwarps) {
+        const float* src = x + p * HW;
+        float s = 0.f;
+        for (int i = lane; i < HW; i += 32) s += src[i];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) out[p] = s / float(HW);
+    }
+}
+
+int run_conv(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, bool relu, ExecCtx& ctx, const char* who) {
+    FXF_CHECK(in.size() >= 3 && out.size() >= 1 && p.ints.size() >= 7, "%s: expects [x, weight, bias] and 7 int params", who);
+    const FxfTensor &x = reg[in[0]], &w = reg[in[1]], &b = reg[in[2]], &o = reg[out[0]];
+    FXF_CHECK(x.dtype == FXF_F32 && w.dtype == FXF_F32 && o.dtype == FXF_F32, "%s: only float32 is supported", who);
+    FXF_CHECK(x.rank == 4 && w.rank == 4 && o.rank == 4, "%s: x, weight and output must be 4-D (NCHW / OIHW)", who);
+    ConvDesc d;
+    d.N = int(x.shape[0]); d.C = int(x.shape[1]); d.H = int(x.shape[2]); d.W = int(x.shape[3]);
+    d.O = int(w.shape[0]); d.KH = int(w.shape[2]); d.KW = int(w.shape[3]);
+    d.sh = int(p.ints[0]); d.sw = int(p.ints[1]); d.ph = int(p.ints[2]); d.pw = int(p.ints[3]);
+    d.dh = int(p.ints[4]); d.dw = int(p.ints[5]); d.groups = int(p.ints[6]);
+    FXF_CHECK(d.groups >= 1 && d.C % d.groups == 0 && d.O % d.groups == 0, "%s: channels are not divisible by groups", who);
+    d.cg = d.C / d.groups; d.og = d.O / d.groups;
+    FXF_CHECK(w.shape[1] == d.cg, "%s: weight input channels do not match x", who);
+    FXF_CHECK(numel(b) == d.O, "%s: bias size mismatch", who);
+    FXF_CHECK(d.sh > 0 && d.sw > 0 && d.dh > 0 && d.dw > 0, "%s: stride and dilation must be positive", who);
+    d.HO = (d.H + 2 * d.ph - d.dh * (d.KH - 1) - 1) / d.sh + 1;
+    d.WO = (d.W + 2 * d.pw - d.dw * (d.KW - 1) - 1) / d.sw + 1;
+    FXF_CHECK(o.shape[0] == d.N && o.shape[1] == d.O && o.shape[2] == d.HO && o.shape[3] == d.WO, "%s: output shape does not match the convolution geometry", who);
+    d.relu = relu ? 1 : 0;
+    int64_t n_pix = int64_t(d.N) * d.HO * d.WO;
+    if (n_pix == 0 || d.O == 0) return 0;
+    dim3 grid(unsigned((n_pix + CBM - 1) / CBM), unsigned((d.og + CBN - 1) / CBN), unsigned(d.groups));
+    conv2d_igemm_kernel<<<grid, 256, 0, ctx.stream>>>(static_cast<const float*>(x.ptr), static_cast<const float*>(w.ptr), static_cast<const float*>(b.ptr),
+                                                      static_cast<float*>(o.ptr), d);
+    FXF_LAUNCHED(ctx);
+    return 0;
+}
+
+int pool_desc(const FxfTensor& x, const FxfTensor& o, PoolDesc* d, const char* who) {
+    FXF_CHECK(x.dtype == FXF_F32 && o.dtype == FXF_F32, "%s: only float32 is supported", who);
+    FXF_CHECK(x.rank >= 3 && o.rank == x.rank, "%s: input must be [N,C,H,W] or [C,H,W]", who);
+    d->H = int(x.shape[x.rank - 2]); d->W = int(x.shape[x.rank - 1]);
+    d->HO = int(o.shape[o.rank - 2]); d->WO = int(o.shape[o.rank - 1]);
+    d->NC = 1;
+    for (int k = 0; k < x.rank - 2; k++) d->NC *= x.shape[k];
+    FXF_CHECK(numel(o) == d->NC * d->HO * d->WO, "%s: output size mismatch", who);
+    return 0;
+}
+
+inline int pool_grid(int64_t total, const ExecCtx& ctx) {
+    int64_t blocks = (total + 255) / 256, cap = int64_t(ctx.sm_count) * 8;
+    return int(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
+}
+
+struct ConvPlan : NodePlan {};
+
+}  // namespace
+
+int k_conv2d(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const NodePlan*, ExecCtx& ctx) {
+    return run_conv(reg, in, out, p, false, ctx, "conv2d");
+}
+int k_conv2d_relu(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const NodePlan*, ExecCtx& ctx) {
+    return run_conv(reg, in, out, p, true, ctx, "conv2d_relu");
+}
+
+int k_max_pool2d(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const NodePlan*, ExecCtx& ctx) {
+    FXF_CHECK(in.size() >= 1 && out.size() >= 1 && p.ints.size() >= 9, "max_pool2d: expects 9 int params");
+    PoolDesc d;
+    if (pool_desc(reg[in[0]], reg[out[0]], &d, "max_pool2d")) return 1;
+    d.kh = int(p.ints[0]); d.kw = int(p.ints[1]); d.sh = int(p.ints[2]); d.sw = int(p.ints[3]);
+    d.ph = int(p.ints[4]); d.pw = int(p.ints[5]); d.dh = int(p.ints[6]); d.dw = int(p.ints[7]);
+    FXF_CHECK(d.sh > 0 && d.sw > 0, "max_pool2d: stride must be positive");
+    int64_t total = d.NC * d.HO * d.WO;
+    if (total == 0) return 0;
+    max_pool2d_kernel<<<pool_grid(total, ctx), 256, 0, ctx.stream>>>(static_cast<const float*>(reg[in[0]].ptr), static_cast<float*>(reg[out[0]].ptr), d);
+    FXF_LAUNCHED(ctx);
+    return 0;
+}
+
+int k_avg_pool2d(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const NodePlan*, ExecCtx& ctx) {
+    FXF_CHECK(in.size() >= 1 && out.size() >= 1 && p.ints.size() >= 7, "avg_pool2d: expects 7 int params");
+    PoolDesc d;
+    if (pool_desc(reg[in[0]], reg[out[0]], &d, "avg_pool2d")) return 1;
+    d.kh = int(p.ints[0]); d.kw = int(p.ints[1]); d.sh = int(p.ints[2]); d.sw = int(p.ints[3]);
+    d.ph = int(p.ints[4]); d.pw = int(p.ints[5]); d.dh = 1; d.dw = 1;
+    FXF_CHECK(d.sh > 0 && d.sw > 0, "avg_pool2d: stride must be positive");
+    int64_t total = d.NC * d.HO * d.WO;
+    if (total == 0) return 0;
+    avg_pool2d_kernel<<<pool_grid(total, ctx), 256, 0, ctx.stream>>>(static_cast<const float*>(reg[in[0]].ptr), static_cast<float*>(reg[out[0]].ptr), d);
+    FXF_LAUNCHED(ctx);
+    return 0;
+}
+
+int k_adaptive_avg_pool2d(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const NodePlan*, ExecCtx& ctx) {
+    FXF_CHECK(in.size() >= 1 && out.size() >= 1 && p.ints.size() >= 2, "adaptive_avg_pool2d: expects [oh, ow]");
+    PoolDesc d;
+    if (pool_desc(reg[in[0]], reg[out[0]], &d, "adaptive_avg_pool2d")) return 1;
+    FXF_CHECK(d.HO == p.ints[0] && d.WO == p.ints[1], "adaptive_avg_pool2d: output shape does not match output_size");
+    d.kh = d.kw = d.sh = d.sw = d.dh = d.dw = 1; d.ph = d.pw = 0;
+    int64_t total = d.NC * d.HO * d.WO;
+    if (total == 0) return 0;
+    if (d.HO == 1 && d.WO == 1) {
+        int64_t blocks = (d.NC * 32 + 255) / 256, cap = int64_t(ctx.sm_count) * 8;
+        global_avg_pool_kernel<<<int(blocks < cap ? blocks : cap), 256, 0, ctx.stream>>>(static_cast<const float*>(reg[in[0]].ptr), static_cast<float*>(reg[out[0]].ptr), d.NC, d.H * d.W);
+    } else {
+        adaptive_avg_pool2d_kernel<<<pool_grid(total, ctx), 256, 0, ctx.stream>>>(static_cast<const float*>(reg[in[0]].ptr), static_cast<float*>(reg[out[0]].ptr), d);
+    }
+    FXF_LAUNCHED(ctx);
+    return 0;
+}
+
+std::unique_ptr<NodePlan> plan_conv(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, int) {
+    auto pl = std::make_unique<ConvPlan>();
+    if (in.size() >= 3 && out.size() >= 1 && reg[in[1]].rank == 4 && reg[out[0]].rank == 4) {
+        const FxfTensor &w = reg[in[1]], &o = reg[out[0]];
+        pl->flops = 2.0 * double(numel(o)) * double(w.shape[1]) * double(w.shape[2]) * double(w.shape[3]);
+        pl->bytes = double(reg[in[0]].nbytes) + double(w.nbytes) + double(reg[in[2]].nbytes) + double(o.nbytes);
+        pl->variant = "igemm-simt64x64";
+    }
+    (void)p;
+    return pl;
+}
+
+}  // namespace fxf

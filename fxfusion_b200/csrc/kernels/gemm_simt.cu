@@ -1,0 +1,224 @@
+// fp32 FFMA GEMM with fused bias (+ReLU) epilogue:  out[M,N] = act(x[M,K] · w[N,K]^T + bias[N]).
+//
+// This is the exact-fp32 contraction behind Linear / LinearRelu / FeedForward / the MHA
+// projections (reference: torch::linear, csrc/kernels/cpu/linear.cpp:11, linear_relu.cpp:11,
+// feedforward.cpp:13, mha.cpp:22,51) for shapes the tensor-core path does not take: small or
+// ragged problems (M, N, K not multiples of the tcgen05 tile) and FXF_GEMM_FP32_SIMT mode.
+//
+// Both operands are K-major, so tiles are fetched with 128-bit loads along K and stored
+// transposed in shared memory ([k][row]); every thread then accumulates a TM x TN register
+// tile split into 4-wide chunks so that shared-memory reads are conflict-free float4s.
+// Global->register prefetch of the next K-slab overlaps the FFMA loop (double buffering).
+// Roofline: fp32 FFMA, 148 SMs x 128 lanes x 2 flop.
+#include "../runtime.hpp"
+
+namespace fxf {
+namespace {
+
+template <int BM, int BN, int BK, int TM, int TN, bool RELU>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+gemm_tn_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias, float* __restrict__ out,
+               int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldo, int vec_in, int vec_out) {
+    constexpr int T = (BM / TM) * (BN / TN);
+    constexpr int VM = TM >= 4 ? 4 : TM, VN = TN >= 4 ? 4 : TN;  // chunk widths
+    constexpr int CM = TM / VM, CN = TN / VN;                    // chunks per thread
+    constexpr int PAD = 4;
+    constexpr int A_F4 = BM * BK / 4, B_F4 = BN * BK / 4;        // float4s per tile
+    constexpr int A_PER = (A_F4 + T - 1) / T, B_PER = (B_F4 + T - 1) / T;
+    constexpr int KQ = BK / 4;
+
+    __shared__ __align__(16) float As[2][BK][BM + PAD];
+    __shared__ __align__(16) float Bs[2][BK][BN + PAD];
+
+    const int tid = threadIdx.x;
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+    const int64_t row0 = int64_t(blockIdx.y) * BM, col0 = int64_t(blockIdx.x) * BN;
+
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; i++)
+#pragma unroll
+        for (int j = 0; j < TN; j++) acc[i][j] = 0.f;
+
+    float4 ra[A_PER], rb[B_PER];
+
+    auto load_global = [&](int64_t k0) {
+#pragma unroll
+        for (int i = 0; i < A_PER; i++) {
+            int f = tid + i * T;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (f < A_F4) {
+                int r = f / KQ, kq = f % KQ;
+                int64_t gr = row0 + r, gk = k0 + kq * 4;
+                if (gr < M) {
+                    const float* p = x + gr * ldx + gk;
+                    if (vec_in && gk + 3 < K) {
+                        v = *reinterpret_cast<const float4*>(p);
+                    } else {
+                        if (gk < K) v.x = p[0];
+                        if (gk + 1 < K) v.y = p[1];
+                        if (gk + 2 < K) v.z = p[2];
+                        if (gk + 3 < K) v.w = p[3];
+                    }
+                }
+            }
+            ra[i] = v;
+        }
+#pragma unroll
+        for (int i = 0; i < B_PER; i++) {
+            int f = tid + i * T;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (f < B_F4) {
+                int r = f / KQ, kq = f % KQ;
+                int64_t gr = col0 + r, gk = k0 + kq * 4;
+                if (gr < N) {
+                    const float* p = w + gr * ldw + gk;
+                    if (vec_in && gk + 3 < K) {
+                        v = *reinterpret_cast<const float4*>(p);
+                    } else {
+                        if (gk < K) v.x = p[0];
+                        if (gk + 1 < K) v.y = p[1];
+                        if (gk + 2 < K) v.z = p[2];
+                        if (gk + 3 < K) v.w = p[3];
+                    }
+                }
+            }
+            rb[i] = v;
+        }
+    };
+    auto store_shared = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < A_PER; i++) {
+            int f = tid + i * T;
+            if (f < A_F4) {
+                int r = f / KQ, kq = f % KQ;
+                As[buf][kq * 4 + 0][r] = ra[i].x;
+                As[buf][kq * 4 + 1][r] = ra[i].y;
+                As[buf][kq * 4 + 2][r] = ra[i].z;
+                As[buf][kq * 4 + 3][r] = ra[i].w;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < B_PER; i++) {
+            int f = tid + i * T;
+            if (f < B_F4) {
+                int r = f / KQ, kq = f % KQ;
+                Bs[buf][kq * 4 + 0][r] = rb[i].x;
+                Bs[buf][kq * 4 + 1][r] = rb[i].y;
+                Bs[buf][kq * 4 + 2][r] = rb[i].z;
+                Bs[buf][kq * 4 + 3][r] = rb[i].w;
+            }
+        }
+    };
+
+    const int64_t n_slabs = (K + BK - 1) / BK;
+    load_global(0);
+    store_shared(0);
+    __syncthreads();
+
+    for (int64_t s = 0; s < n_slabs; s++) {
+        int buf = int(s & 1);
+        if (s + 1 < n_slabs) load_global((s + 1) * BK);
+#pragma unroll
+        for (int k = 0; k < BK; k++) {
+            float a[TM], b[TN];
+#pragma unroll
+            for (int c = 0; c < CM; c++) {
+                const float* p = &As[buf][k][c * (BM / CM) + ty * VM];
+                if (VM == 4) {
+                    float4 v = *reinterpret_cast<const float4*>(p);
+                    a[c * VM + 0] = v.x; a[c * VM + 1] = v.y; a[c * VM + 2] = v.z; a[c * VM + 3] = v.w;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < VM; i++) a[c * VM + i] = p[i];
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < CN; c++) {
+                const float* p = &Bs[buf][k][c * (BN / CN) + tx * VN];
+                if (VN == 4) {
+                    float4 v = *reinterpret_cast<const float4*>(p);
+                    b[c * VN + 0] = v.x; b[c * VN + 1] = v.y; b[c * VN + 2] = v.z; b[c * VN + 3] = v.w;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < VN; i++) b[c * VN + i] = p[i];
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < TM; i++)
+#pragma unroll
+                for (int j = 0; j < TN; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        if (s + 1 < n_slabs) {
+            store_shared(buf ^ 1);
+            __syncthreads();
+        }
+    }
+
+    // epilogue: bias, activation, store
+#pragma unroll
+    for (int cm = 0; cm < CM; cm++) {
+#pragma unroll
+        for (int i = 0; i < VM; i++) {
+            int64_t gr = row0 + cm * (BM / CM) + ty * VM + i;
+            if (gr >= M) continue;
+#pragma unroll
+            for (int cn = 0; cn < CN; cn++) {
+                int64_t gc = col0 + cn * (BN / CN) + tx * VN;
+                float v[VN];
+#pragma unroll
+                for (int j = 0; j < VN; j++) {
+                    float t = acc[cm * VM + i][cn * VN + j];
+                    if (bias != nullptr && gc + j < N) t += bias[gc + j];
+                    if (RELU) t = t > 0.f ? t : (t != t ? t : 0.f);
+                    v[j] = t;
+                }
+                float* p = out + gr * ldo + gc;
+                if (VN == 4 && vec_out && gc + 3 < N) {
+                    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < VN; j++)
+                        if (gc + j < N) p[j] = v[j];
+                }
+            }
+        }
+    }
+}
+
+template <int BM, int BN, int BK, int TM, int TN>
+int launch_cfg(const GemmArgs& a, ExecCtx& ctx) {
+    dim3 grid(unsigned((a.N + BN - 1) / BN), unsigned((a.M + BM - 1) / BM));
+    dim3 block((BM / TM) * (BN / TN));
+    int vec_in = (a.ldx % 4 == 0 && a.ldw % 4 == 0 && aligned16(a.x) && aligned16(a.w)) ? 1 : 0;
+    int vec_out = (a.ldo % 4 == 0 && aligned16(a.out)) ? 1 : 0;
+    if (a.relu)
+        gemm_tn_kernel<BM, BN, BK, TM, TN, true><<<grid, block, 0, ctx.stream>>>(a.x, a.w, a.bias, a.out, a.M, a.N, a.K, a.ldx, a.ldw, a.ldo, vec_in, vec_out);
+    else
+        gemm_tn_kernel<BM, BN, BK, TM, TN, false><<<grid, block, 0, ctx.stream>>>(a.x, a.w, a.bias, a.out, a.M, a.N, a.K, a.ldx, a.ldw, a.ldo, vec_in, vec_out);
+    FXF_LAUNCHED(ctx);
+    return 0;
+}
+
+}  // namespace
+
+// 0 = 128x128, 1 = 64x64, 2 = 32x32
+int simt_tile_choice(int64_t M, int64_t N, int sm_count) {
+    int64_t big = ((M + 127) / 128) * ((N + 127) / 128);
+    int64_t mid = ((M + 63) / 64) * ((N + 63) / 64);
+    if (big >= sm_count) return 0;
+    if (mid >= sm_count / 2) return 1;
+    return 2;
+}
+
+int launch_gemm_simt(const GemmArgs& a, ExecCtx& ctx) {
+    if (a.M == 0 || a.N == 0) return 0;
+    FXF_CHECK(a.M > 0 && a.N > 0 && a.K >= 0, "gemm: negative dimension");
+    switch (simt_tile_choice(a.M, a.N, ctx.sm_count)) {
+        case 0: return launch_cfg<128, 128, 16, 8, 8>(a, ctx);
+        case 1: return launch_cfg<64, 64, 16, 4, 4>(a, ctx);
+        default: return launch_cfg<32, 32, 32, 2, 2>(a, ctx);
+    }
+}
+
+}  // namespace fxf

@@ -1,0 +1,170 @@
+// Runtime contracts of the B200 backend: registry, params, per-node plan and the KernelFn
+// function-pointer type.  They keep the shape of the reference's contracts
+// (csrc/include/runtime/tensor_registry.hpp:8-26) with LibTorch removed:
+//   TensorRegistry  vector<torch::Tensor>      -> vector<FxfTensor> (raw device pointers)
+//   Cache           per-node torch::empty bufs -> NodePlan: launch geometry computed once at
+//                                                 build + byte counts of the shared scratch /
+//                                                 persistent memory the node wants
+//   KernelFn        void(*)(reg,in,out,params,cache) -> int(*)(reg,in,out,params,plan,ctx)
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/fxf_b200.h"
+
+namespace fxf {
+
+using Registry = std::vector<FxfTensor>;
+using TensorIds = std::vector<uint32_t>;
+
+struct Params {
+    std::vector<int64_t> ints;
+    std::vector<float> floats;
+};
+
+// Everything a launch needs besides the registry.
+struct ExecCtx {
+    cudaStream_t stream = nullptr;
+    void* scratch = nullptr;       // shared by all nodes of an engine; nodes run one at a time
+    size_t scratch_bytes = 0;
+    int* status = nullptr;         // sticky device status word (0 = ok)
+    int sm_count = 148;
+    int gemm_mode = FXF_GEMM_AUTO;
+    int launches = 0;              // incremented by every kernel launch (host-side count)
+};
+
+struct NodePlan {
+    virtual ~NodePlan() = default;
+    size_t scratch_bytes = 0;   // shared scratch wanted at execute time
+    size_t persist_bytes = 0;   // memory that must survive across runs (e.g. re-laid-out weights)
+    void* persist = nullptr;    // assigned by the engine before prepare()
+    double flops = 0, bytes = 0;  // algorithmic work of the node
+    std::string variant;        // which kernel variant was chosen (for describe / profiling)
+    // Called once after device memory exists (constants uploaded).  May launch kernels.
+    virtual int prepare(Registry&, const TensorIds&, const TensorIds&, const Params&, ExecCtx&) { return 0; }
+};
+
+using KernelFn = int (*)(Registry&, const TensorIds&, const TensorIds&, const Params&, const NodePlan*, ExecCtx&);
+using PlanFn = std::unique_ptr<NodePlan> (*)(const Registry&, const TensorIds&, const TensorIds&, const Params&, int gemm_mode);
+
+struct OpEntry {
+    const char* name = nullptr;
+    KernelFn kernel = nullptr;
+    PlanFn plan = nullptr;
+};
+
+// OpCode -> {kernel, plan builder}.  Counterpart of OpRegistry (csrc/runtime/op_registry.cpp:16-106);
+// there is one kernel set only — CUDA — and no CPU fallback.
+const OpEntry& op_entry(int op_code);
+
+// ---- error plumbing -------------------------------------------------------------------
+void set_last_error(const std::string& msg);
+const std::string& last_error();
+
+inline std::string strfmt(const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    return std::string(buf);
+}
+
+#define FXF_FAIL(...)                                   \
+    do {                                                \
+        ::fxf::set_last_error(::fxf::strfmt(__VA_ARGS__)); \
+        return 1;                                       \
+    } while (0)
+
+#define FXF_CHECK(cond, ...)          \
+    do {                              \
+        if (!(cond)) FXF_FAIL(__VA_ARGS__); \
+    } while (0)
+
+#define FXF_CUDA(expr)                                                                       \
+    do {                                                                                     \
+        cudaError_t _e = (expr);                                                             \
+        if (_e != cudaSuccess) FXF_FAIL("CUDA error %s at %s:%d (%s)", cudaGetErrorString(_e), __FILE__, __LINE__, #expr); \
+    } while (0)
+
+// Checks the launch that has just been issued and counts it.
+#define FXF_LAUNCHED(ctx)                                                                     \
+    do {                                                                                      \
+        cudaError_t _e = cudaPeekAtLastError();                                               \
+        if (_e != cudaSuccess) FXF_FAIL("kernel launch failed: %s at %s:%d", cudaGetErrorString(_e), __FILE__, __LINE__); \
+        (ctx).launches++;                                                                     \
+    } while (0)
+
+// ---- tensor helpers ---------------------------------------------------------------------
+inline int64_t numel(const FxfTensor& t) {
+    int64_t n = 1;
+    for (int i = 0; i < t.rank; i++) n *= t.shape[i];
+    return n;
+}
+inline int dtype_size(int dt) {
+    switch (dt) {
+        case FXF_F32: return 4;
+        case FXF_F16: return 2;
+        case FXF_I32: return 4;
+        case FXF_I64: return 8;
+        case FXF_BOOL: return 1;
+        default: return 0;
+    }
+}
+inline void set_contiguous(FxfTensor& t) {
+    int64_t s = 1;
+    for (int i = t.rank - 1; i >= 0; i--) {
+        t.stride[i] = s;
+        s *= t.shape[i];
+    }
+}
+inline bool is_contiguous(const FxfTensor& t) {
+    int64_t s = 1;
+    for (int i = t.rank - 1; i >= 0; i--) {
+        if (t.shape[i] != 1 && t.stride[i] != s) return false;
+        s *= t.shape[i];
+    }
+    return true;
+}
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ---- kernels shared between ops (defined in the .cu files) -------------------------------
+// out[M,N] = act(x[M,K] · w[N,K]^T + bias[N]); row strides in elements (ldx, ldw, ldo).
+// `tc_w_lo`: optional pre-split low part of w for the tensor-core path (may be null).
+struct GemmArgs {
+    const float* x = nullptr;
+    const float* w = nullptr;
+    const float* bias = nullptr;
+    float* out = nullptr;
+    int64_t M = 0, N = 0, K = 0;
+    int64_t ldx = 0, ldw = 0, ldo = 0;
+    bool relu = false;
+};
+int launch_gemm(const GemmArgs& a, ExecCtx& ctx);
+int launch_gemm_simt(const GemmArgs& a, ExecCtx& ctx);
+int simt_tile_choice(int64_t M, int64_t N, int sm_count);
+std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count);
+
+// Attention core on packed qkv [B,T,3D] (Q | K | V thirds, head h at columns h*hd) -> ctx [B,T,D].
+struct AttnArgs {
+    const float* qkv = nullptr;
+    const uint8_t* mask = nullptr;
+    float* ctx = nullptr;
+    int B = 0, T = 0, H = 0, hd = 0;
+    int64_t ld_qkv = 0;   // row stride of qkv (= 3*D of the full model, or of the local shard)
+    int64_t q_off = 0, k_off = 0, v_off = 0;  // column offsets of the Q/K/V blocks inside a row
+    int64_t ld_ctx = 0;
+    int64_t mask_sb = 0, mask_sh = 0, mask_sq = 0, mask_sk = 0;  // mask strides (bytes): batch, head, query, key
+    float scale_divisor = 1.f;
+};
+int launch_attention(const AttnArgs& a, ExecCtx& ctx);
+
+}  // namespace fxf

@@ -1,0 +1,158 @@
+/*
+ * fxf_b200.h — C ABI of the B200 (sm_100a) CUDA backend for the FXFusion runtime.
+ *
+ * Everything here is plain C: pointers, sizes and status codes.  No LibTorch type crosses
+ * this boundary.  Each entry point names the reference interface it stands in for
+ * (paths relative to the reference project).
+ *
+ * Status convention: 0 = success, non-zero = failure; fxf_last_error() returns the
+ * thread-local message of the most recent failure (the reference throws c10::Error /
+ * std::runtime_error at the same points, e.g. csrc/runtime/memory_manager.cpp:14,87-90,103,114).
+ */
+#ifndef FXF_B200_H_
+#define FXF_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define FXF_API __attribute__((visibility("default")))
+#else
+#define FXF_API
+#endif
+
+#define FXF_MAX_DIMS 8
+
+/* DType values of the graph file (schema/graph.fbs:11-17). */
+enum { FXF_F32 = 0, FXF_F16 = 1, FXF_I32 = 2, FXF_I64 = 3, FXF_BOOL = 4 };
+
+/* OpCode values of the graph file (schema/graph.fbs:19-40). */
+enum {
+    FXF_OP_NOOP = 0, FXF_OP_CONV2D = 1, FXF_OP_CONV2D_RELU = 2, FXF_OP_LINEAR = 3,
+    FXF_OP_LINEAR_RELU = 4, FXF_OP_ADD = 5, FXF_OP_ADD_RELU = 6, FXF_OP_RELU = 7,
+    FXF_OP_MUL = 8, FXF_OP_MAX_POOL2D = 9, FXF_OP_AVG_POOL2D = 10,
+    FXF_OP_ADAPTIVE_AVG_POOL2D = 11, FXF_OP_TRANSPOSE = 12, FXF_OP_SIZE = 13,
+    FXF_OP_NARROW = 14, FXF_OP_EMBEDDING = 15, FXF_OP_LAYER_NORM = 16,
+    FXF_OP_ADD_LAYER_NORM = 17, FXF_OP_MHA = 18, FXF_OP_FEEDFORWARD = 19, FXF_OP_COUNT = 20
+};
+
+/* One registry slot.  Replaces the torch::Tensor elements of the reference TensorRegistry
+ * (csrc/include/runtime/tensor_registry.hpp:8).  Strides are in elements. */
+typedef struct FxfTensor {
+    void*   ptr;
+    int32_t dtype;
+    int32_t rank;
+    int64_t shape[FXF_MAX_DIMS];
+    int64_t stride[FXF_MAX_DIMS];
+    int64_t nbytes;
+} FxfTensor;
+
+/* GEMM arithmetic used by Linear / LinearRelu / FeedForward / MHA projections. */
+enum {
+    FXF_GEMM_AUTO = 0,      /* tensor-core 3xTF32 where the shape allows it, else fp32 SIMT */
+    FXF_GEMM_FP32_SIMT = 1, /* fp32 FFMA tiles only */
+    FXF_GEMM_TF32X3 = 2     /* tcgen05 kind::tf32 with hi/lo operand split (fp32-grade result) */
+};
+
+typedef struct FxfEngineOptions {
+    int32_t struct_size;     /* sizeof(FxfEngineOptions), for forward compatibility */
+    int32_t use_cuda_graph;  /* 1: capture one CUDA Graph per forward and replay it */
+    int32_t gemm_mode;       /* FXF_GEMM_* */
+    int32_t tp_rank;         /* tensor-parallel rank of this engine (0 when tp_size == 1) */
+    int32_t tp_size;         /* number of tensor-parallel ranks (1 = none) */
+    int32_t reserved[11];
+} FxfEngineOptions;
+
+typedef struct fxf_engine fxf_engine;
+
+/* Message of the last failure on the calling thread ("" if none). */
+FXF_API const char* fxf_last_error(void);
+
+/* Library build id: "fxf_b200 <n kernels> sm_100a". */
+FXF_API const char* fxf_version(void);
+
+/* ExecutionEngine(graph_path, device) — csrc/runtime/execution_engine.cpp:12-29.
+ * Reads the graph file, places every tensor in ONE cudaMalloc'd device arena (activations at
+ * the planner's offsets, then constants, input slots and shared scratch), binds aliases the
+ * way csrc/runtime/memory_manager.cpp:30-111 does and resolves one kernel per node
+ * (csrc/runtime/runtime_graph.cpp:8-18).  `opts` may be NULL. */
+FXF_API int fxf_engine_create(const char* graph_path, int device_ordinal, const FxfEngineOptions* opts,
+                      fxf_engine** out_engine);
+/* Same, from bytes already in memory (the engine copies what it needs). */
+FXF_API int fxf_engine_create_from_memory(const void* bytes, size_t nbytes, int device_ordinal,
+                                  const FxfEngineOptions* opts, fxf_engine** out_engine);
+FXF_API void fxf_engine_destroy(fxf_engine* e);
+
+/* Counts and descriptors of graph inputs / outputs (memory_manager.cpp:92-111).  Input
+ * descriptors point at the engine's static input slots; output descriptors at arena memory
+ * that stays valid (and is overwritten) across runs, like the views execution_engine.cpp:42
+ * returns. */
+FXF_API int fxf_engine_num_inputs(const fxf_engine* e);
+FXF_API int fxf_engine_num_outputs(const fxf_engine* e);
+FXF_API int fxf_engine_input_desc(const fxf_engine* e, int i, FxfTensor* out);
+FXF_API int fxf_engine_output_desc(const fxf_engine* e, int i, FxfTensor* out);
+FXF_API int fxf_engine_num_nodes(const fxf_engine* e);
+FXF_API int64_t fxf_engine_arena_bytes(const fxf_engine* e);    /* planner arena_size */
+FXF_API int64_t fxf_engine_device_bytes(const fxf_engine* e);   /* whole device allocation */
+/* Number of kernel launches one forward issues (graph replay or not). */
+FXF_API int fxf_engine_launches_per_run(const fxf_engine* e);
+
+/* ExecutionEngine::run — execution_engine.cpp:31-43, inputs resident on the device.
+ * `device_inputs[i]` is a contiguous device buffer of the i-th input's dtype/shape; it is
+ * copied into the static slot on `stream` (a cudaStream_t, may be NULL = legacy stream), then
+ * the forward is enqueued on the same stream.  Asynchronous: no host sync inside. */
+FXF_API int fxf_engine_run(fxf_engine* e, const void* const* device_inputs, int n_inputs, void* stream);
+/* Same with HOST buffers: host->device copies of the inputs on `stream`, forward, and (if
+ * host_outputs != NULL) device->host copies of every output followed by a stream sync. */
+FXF_API int fxf_engine_run_host(fxf_engine* e, const void* const* host_inputs, int n_inputs,
+                        void* const* host_outputs, int n_outputs, void* stream);
+/* Reads the sticky device status word (0 = no kernel reported a problem); syncs `stream`. */
+FXF_API int fxf_engine_device_status(fxf_engine* e, void* stream, int* status_out);
+/* Human-readable dump of nodes, offsets, scratch and the kernel variant chosen per node. */
+FXF_API int fxf_engine_describe(const fxf_engine* e, char* buf, size_t buf_bytes);
+/* Per-node CUDA-event timing of one forward (graph replay disabled for the measurement).
+ * ms_out receives fxf_engine_num_nodes() values. */
+FXF_API int fxf_engine_time_nodes(fxf_engine* e, float* ms_out, int n, void* stream);
+FXF_API int fxf_engine_node_info(const fxf_engine* e, int node, int* op_code, double* flops, double* bytes,
+                         char* variant, size_t variant_bytes);
+
+/* One kernel, outside any engine: the KernelFn contract of
+ * csrc/include/runtime/tensor_registry.hpp:20-26 (registry, input ids, output ids, Params)
+ * with the per-node Cache (csrc/runtime/cache.cpp:5-73) replaced by caller-provided scratch.
+ * `reg` holds device pointers.  fxf_kernel_scratch_bytes tells how much scratch the op needs. */
+FXF_API int64_t fxf_kernel_scratch_bytes(int op_code, const FxfTensor* reg, int n_reg,
+                                 const uint32_t* in_ids, int n_in, const uint32_t* out_ids, int n_out,
+                                 const int64_t* ints, int n_ints, const float* floats, int n_floats,
+                                 int gemm_mode);
+FXF_API int fxf_kernel_invoke(int op_code, const FxfTensor* reg, int n_reg,
+                      const uint32_t* in_ids, int n_in, const uint32_t* out_ids, int n_out,
+                      const int64_t* ints, int n_ints, const float* floats, int n_floats,
+                      void* scratch, int64_t scratch_bytes, int gemm_mode, void* stream);
+
+/* Greedy static decode on the device — the loop of
+ * py/fxfusion/models/transformer/inference.py:28-45 with the mask rule of
+ * py/fxfusion/models/transformer/layers/masks.py:141-154.
+ *
+ * fxf_decode_build_mask: mask[b,0,q,k] = (k < current_len) && (tokens[b,k] != pad) && (k <= q),
+ *   tokens int64 [B,T], mask bool [B,1,T,T].
+ * fxf_decode_argmax_scatter: tokens[b, current_len] = argmax_v logits[b, current_len-1, v]
+ *   (first maximum wins, NaN counts as maximum, like torch.argmax); logits fp32 [B,T,V].
+ * fxf_decode_static: whole loop for an engine whose inputs are (tokens int64 [B,T],
+ *   mask bool [B,1,T,T]) and whose output 0 is logits [B,T,V]: tokens_io (device, [B,T], prompt
+ *   in columns < initial_len, pad elsewhere) is completed in place up to column T-1.  No host
+ *   synchronisation is performed. */
+FXF_API int fxf_decode_build_mask(const int64_t* tokens, uint8_t* mask, int B, int T, int current_len,
+                          int64_t pad_idx, void* stream);
+FXF_API int fxf_decode_argmax_scatter(const float* logits, int64_t* tokens, int B, int T, int64_t V,
+                              int current_len, void* stream);
+FXF_API int fxf_decode_static(fxf_engine* e, int64_t* tokens_io, int initial_len, int64_t pad_idx,
+                      void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FXF_B200_H_ */

@@ -1,0 +1,56 @@
+"""The C-ABI library: loads, exports every declared symbol, reports errors — no GPU needed."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+from conftest import REPO
+
+
+def declared_symbols():
+    text = (REPO / "include" / "fxf_b200.h").read_text()
+    return re.findall(r"FXF_API\s+[\w\s\*]+?\b(fxf_\w+)\s*\(", text)
+
+
+def test_header_declares_the_expected_surface():
+    names = declared_symbols()
+    assert len(names) == len(set(names)) >= 24
+    for must in ("fxf_engine_create", "fxf_engine_run", "fxf_engine_run_host", "fxf_kernel_invoke", "fxf_decode_static", "fxf_last_error"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    from fxfusion_b200 import _lib
+    for name in declared_symbols():
+        assert hasattr(built_lib, name), f"{name} is declared in include/fxf_b200.h but not exported"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes prototype"
+    assert set(_lib.SIGNATURES) == set(declared_symbols())
+
+
+def test_struct_layout_matches_header(built_lib):
+    from fxfusion_b200._lib import FxfEngineOptions, FxfTensor
+    assert C.sizeof(FxfTensor) == 8 + 4 + 4 + 8 * 8 + 8 * 8 + 8
+    assert C.sizeof(FxfEngineOptions) == 16 * 4
+    assert built_lib.fxf_version().decode().endswith("sm_100a")
+
+
+def test_missing_file_reports_the_reference_error(built_lib):
+    h = C.c_void_p()
+    rc = built_lib.fxf_engine_create(b"/nonexistent/graph.bin", 0, None, C.byref(h))
+    assert rc != 0 and not h.value
+    assert "ExecutionEngine failed to open: /nonexistent/graph.bin" in built_lib.fxf_last_error().decode()
+
+
+def test_cpu_device_is_refused_by_the_wrapper():
+    from fxfusion_b200.engine import ExecutionEngine
+    with pytest.raises(RuntimeError, match="CUDA devices only"):
+        ExecutionEngine("whatever.bin", "cpu")
+
+
+def test_product_never_imports_the_oracle():
+    for path in (REPO / "fxfusion_b200").rglob("*"):
+        if path.suffix in (".py", ".cpp", ".cu", ".hpp", ".h") and "build" not in path.parts[len(REPO.parts):-1]:
+            text = path.read_text(errors="ignore")
+            assert not re.search(r"^\s*(from|import)\s+oracle\b", text, re.M), path
+            assert "oracle/" not in text, path
