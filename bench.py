@@ -1,0 +1,335 @@
+"""Benchmark of the hot path: GPT-2-small-shape greedy static decode on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE.json config 3): 12 layers, d_model 768, 12 heads, d_ff 3072, vocab 50257, fp32,
+batch 32, static length 256 = 128 prompt tokens + 128 generated; weights ~N(0, 0.02) and prompt ids
+uniform in [1, vocab) from a fixed seed (synthetic stand-ins: no dataset is involved).  Decode is the
+reference's full-recompute loop (no KV cache): one STEP = rebuild the [B,1,T,T] mask, run the whole
+graph on the [B,256] token buffer, argmax of one logits row, write the next token — 32 tokens per
+step and per GPU.  K defaults to 128 steps (one complete decode), W to 3.
+
+`value`   tokens/s with everything resident in HBM: mask kernel + captured CUDA Graph + argmax kernel
+          per step, no host synchronisation inside the timed region (CUDA events, max over ranks).
+`e2e`     the reference-shaped call with HOST buffers: every step builds the mask on the host, copies
+          tokens + mask host->device from pinned memory through fxf_engine_run_host, runs the
+          forward and the argmax, and reads the token buffer back device->host.
+Inputs exceed L2 (weights 0.65 GB + 1.65 GB of logits written per step), so no explicit L2 flush.
+N > 1: every rank runs an independent batch-32 replica (sequences are independent; no collective).
+`--impl reference` times the reference's CPU backend arithmetic (its own compiled CPU kernels when
+`oracle/_ref` is built, else the restated oracle) on the host cores, on a reduced batch per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+
+B, T, PROMPT = 32, 256, 128
+METRIC = "gpt2_small_greedy_decode_tokens_per_s"
+CPU_BUDGET_S = 150.0  # wall-clock budget of a CPU arm; the per-step batch is sized to fit it
+
+
+def measured_peaks():
+    p = REPO / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int) -> None:
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_graph_file(batch: int, tmpdir: str) -> str:
+    from fxfusion_b200 import lowering, wire
+    cfg = lowering.GPT2_SMALL
+    g = lowering.gpt_graph(cfg, lowering.gpt_params(cfg, 0), batch=batch, seq=T, name=f"gpt2_small_b{batch}")
+    path = os.path.join(tmpdir, f"{g.name}.bin")
+    wire.dump(g, path)
+    return path
+
+
+def pick_cpu_batch(steps: int, warmup: int) -> int:
+    """Largest power-of-two batch <= 32 whose (steps + warmup) decode steps fit CPU_BUDGET_S, from a
+    one-step calibration at batch 2 (bigger batches cost ~2.2x more per sequence: the 1.65 GB logits
+    tensor falls out of cache)."""
+    _, s_per_step, _, _ = cpu_decode_steps(2, 1, 1)
+    per_seq = s_per_step / 2 * 2.2
+    b = 32
+    while b > 1 and (steps + warmup) * per_seq * b > CPU_BUDGET_S:
+        b //= 2
+    return b
+
+
+def cpu_decode_steps(batch: int, steps: int, warmup: int):
+    """Reference CPU backend: graph walked node by node through the reference's CPU kernels."""
+    import torch
+    from fxfusion_b200 import lowering, wire
+    from oracle.graph_oracle import KERNELS, GraphOracle, make_static_buffer, static_decoder_mask
+    from oracle.ref_cpu.build import load as load_ref
+    cfg = lowering.GPT2_SMALL
+    graph = lowering.gpt_graph(cfg, lowering.gpt_params(cfg, 0), batch=batch, seq=T, name="cpu")
+    ref = load_ref()
+    kernels, kind = None, "port"
+    if ref is not None:
+        def bind(op):
+            def fn(reg, i, o, ints, floats):
+                ref.call(op, [t if t is not None else torch.empty(0) for t in reg], list(i), list(o), list(ints), list(floats))
+            return fn
+        kernels, kind = {op: bind(op) for op in KERNELS}, "reference"
+    orc = GraphOracle(graph, kernels=kernels)
+    tokens = torch.from_numpy(lowering.decode_prompt(batch, PROMPT, cfg.vocab))
+    buf = make_static_buffer(tokens, T)
+    cur = PROMPT
+
+    def step():
+        nonlocal cur
+        logits = orc.run([buf, static_decoder_mask(buf, cur)])[0]
+        buf[:, cur] = logits[:, cur - 1, :].argmax(-1)
+        cur = cur + 1 if cur + 1 < T else PROMPT
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = time.perf_counter() - t0
+    return batch * steps / dt, dt / steps, kind, torch.get_num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    batch = pick_cpu_batch(args.steps, args.warmup)
+    tps, s_per_step, kind, cores = cpu_decode_steps(batch, args.steps, args.warmup)
+    sample = f"{args.steps} full-recompute decode steps of the same model at batch {batch} (of {B}), seq {T}"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": s_per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "GPT-2-small-shape greedy static decode, batch 32, 128 prompt + 128 generated, fp32, full recompute",
+                   "cpu_step_batch": batch},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+
+    from fxfusion_b200 import _lib, lowering
+    from fxfusion_b200.engine import ExecutionEngine
+    import ctypes as C
+
+    K, W = args.steps, max(args.warmup, 3)
+    cfg = lowering.GPT2_SMALL
+    tmp = tempfile.TemporaryDirectory()
+    eng = ExecutionEngine(build_graph_file(B, tmp.name), f"cuda:{local}", precision=args.precision)
+    lib = _lib.lib()
+    prompt = torch.from_numpy(lowering.decode_prompt(B, PROMPT, cfg.vocab, seed=rank))
+    start_buf = torch.zeros((B, T), dtype=torch.int64)
+    start_buf[:, :PROMPT] = prompt
+    tok_slot, mask_slot = eng.input_slots()
+    logits = eng.outputs()[0]
+    V = logits.shape[-1]
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    h = eng.handle
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- value: device-resident loop ----------------------------------------------------------
+    state = {"cur": PROMPT}
+
+    def device_step():
+        cur = state["cur"]
+        _lib.check(lib.fxf_decode_build_mask(C.c_void_p(tok_slot.data_ptr()), C.c_void_p(mask_slot.data_ptr()), B, T, cur, 0, stream))
+        _lib.check(lib.fxf_engine_run(h, (C.c_void_p * 2)(tok_slot.data_ptr(), mask_slot.data_ptr()), 2, stream))
+        _lib.check(lib.fxf_decode_argmax_scatter(C.c_void_p(logits.data_ptr()), C.c_void_p(tok_slot.data_ptr()), B, T, V, cur, stream))
+        state["cur"] = cur + 1 if cur + 1 < T else PROMPT
+
+    tok_slot.copy_(start_buf)
+    for _ in range(W):
+        device_step()
+    tok_slot.copy_(start_buf)
+    state["cur"] = PROMPT
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(K):
+        device_step()
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if rank == 0 else None
+    status = eng.device_status()
+    generated = tok_slot.cpu()
+
+    # ---- e2e: host buffers every step -------------------------------------------------------
+    Ke = min(K, 32)
+    host_tok = torch.zeros((B, T), dtype=torch.int64).pin_memory()
+    host_mask = torch.zeros((B, 1, T, T), dtype=torch.bool).pin_memory()
+    causal = torch.tril(torch.ones((T, T), dtype=torch.bool))
+    ar = torch.arange(T)
+
+    def host_step(cur):
+        # the reference's mask rule, on the host (layers/masks.py:141-154)
+        torch.logical_and(((ar < cur).view(1, 1, 1, T) & (host_tok != 0).view(B, 1, 1, T)), causal, out=host_mask)
+        eng.run_host([host_tok.numpy(), host_mask.numpy().view(np.uint8)])
+        _lib.check(lib.fxf_decode_argmax_scatter(C.c_void_p(logits.data_ptr()), C.c_void_p(tok_slot.data_ptr()), B, T, V, cur, stream))
+        host_tok.copy_(tok_slot, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    host_tok.copy_(start_buf)
+    for i in range(3):
+        host_step(PROMPT + i)
+    host_tok.copy_(start_buf)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for i in range(Ke):
+        host_step(PROMPT + i)
+    e1.record()
+    barrier()
+    e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3 if world == 1 else 0.0)
+    e2e_match = bool(torch.equal(host_tok[:, :PROMPT + Ke], generated[:, :PROMPT + Ke])) if K >= Ke else None
+
+    # ---- max over ranks ----------------------------------------------------------------------
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t[0].item(), t[1].item()
+
+    if rank == 0:
+        # ---- roofline of the dominant kernel: one traced forward (an event after every launch) -----
+        tok_slot.copy_(start_buf)
+        eng.profile_launches()
+        trace = eng.profile_launches()
+        by = {}
+        for r in trace:
+            a = by.setdefault(r["kernel"], {"ms": 0.0, "flops": 0.0, "bytes": 0.0, "n": 0})
+            a["ms"] += r["ms"]; a["flops"] += r["flops"]; a["bytes"] += r["bytes"]; a["n"] += 1
+        total_ms = sum(a["ms"] for a in by.values())
+        top_name, top = max(by.items(), key=lambda kv: kv[1]["ms"])
+        peaks = measured_peaks()
+        achieved = top["flops"] / (top["ms"] * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": top_name, "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": None, "peak_source": peaks["source"] + " cuBLAS bf16, sustained",
+                    "launches_per_step": top["n"], "share_of_step": top["ms"] / total_ms,
+                    "note": "achieved = logical fp32 flops (2MNK, counted once) of all launches of this kernel in one forward / their summed device time"}
+        kernels = {k: {"launches": v["n"], "ms": round(v["ms"], 4), "share": round(v["ms"] / total_ms, 4),
+                       "tflops": round(v["flops"] / (v["ms"] * 1e-3) / 1e12, 3) if v["ms"] > 0 else None,
+                       "gbs": round(v["bytes"] / (v["ms"] * 1e-3) / 1e9, 1) if v["ms"] > 0 else None} for k, v in sorted(by.items(), key=lambda kv: -kv[1]["ms"])}
+        # ---- CPU baseline on a bounded sample -------------------------------------------------------
+        cpu = None
+        if not args.no_cpu_baseline:
+            cb = pick_cpu_batch(2, 1)
+            tps, s_per_step, kind, cores = cpu_decode_steps(cb, 2, 1)
+            cpu = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": kind,
+                   "sample": f"2 full-recompute decode steps of the same model at batch {cb} (of {B}), seq {T}; {s_per_step:.2f} s/step"}
+        tokens_per_step = B * world
+        line = {
+            "metric": METRIC, "value": tokens_per_step * K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "GPT-2-small-shape greedy static decode, batch 32 per GPU, 128 prompt + 128 generated, fp32, full recompute",
+                       "layers": 12, "d_model": 768, "heads": 12, "d_ff": 3072, "vocab": 50257, "batch_per_gpu": B, "seq": T,
+                       "parallelism": f"{world} independent replica(s), no collective", "gemm": args.precision,
+                       "l2": "inputs larger than L2 (0.65 GB weights read, 1.65 GB logits written per step)"},
+            "e2e": {"value": tokens_per_step * Ke / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * T * 8 + B * T * T,
+                    "d2h_bytes_per_step": B * T * 8, "steps": Ke, "tokens_equal_device_loop": e2e_match},
+            "gpu_launches": K * (eng.launches_per_run + 2),
+            "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu, "kernels": kernels,
+            "device_status": status, "device_bytes": eng.device_bytes,
+        }
+        print(json.dumps(line), flush=True)
+    eng.close()
+    tmp.cleanup()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--precision", default="auto", choices=["auto", "fp32_simt", "fp32_3xtf32"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

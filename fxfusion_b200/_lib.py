@@ -22,6 +22,10 @@ class FxfEngineOptions(C.Structure):
                 ("tp_rank", C.c_int32), ("tp_size", C.c_int32), ("reserved", C.c_int32 * 11)]
 
 
+class FxfLaunchInfo(C.Structure):
+    _fields_ = [("kernel", C.c_char * 48), ("node", C.c_int32), ("ms", C.c_float), ("flops", C.c_double), ("bytes", C.c_double)]
+
+
 GEMM_AUTO, GEMM_FP32_SIMT, GEMM_TF32X3 = 0, 1, 2
 GEMM_MODES = {"auto": GEMM_AUTO, "fp32_simt": GEMM_FP32_SIMT, "fp32_3xtf32": GEMM_TF32X3}
 
@@ -48,6 +52,7 @@ SIGNATURES = {
     "fxf_engine_describe": (C.c_int, [C.c_void_p, C.c_char_p, C.c_size_t]),
     "fxf_engine_time_nodes": (C.c_int, [C.c_void_p, _f32p, C.c_int, C.c_void_p]),
     "fxf_engine_node_info": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_double), C.POINTER(C.c_double), C.c_char_p, C.c_size_t]),
+    "fxf_engine_profile_launches": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(FxfLaunchInfo), C.c_int, C.POINTER(C.c_int)]),
     "fxf_kernel_scratch_bytes": (C.c_int64, _kernel_args + [C.c_int]),
     "fxf_kernel_invoke": (C.c_int, _kernel_args + [C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
     "fxf_decode_build_mask": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_void_p]),

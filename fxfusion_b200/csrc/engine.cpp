@@ -34,6 +34,14 @@ const std::string& last_error() { return g_last_error; }
 int decode_build_mask(const int64_t* tokens, uint8_t* mask, int B, int T, int cur, int64_t pad, ExecCtx& ctx);
 int decode_argmax_scatter(const float* logits, int64_t* tokens, int B, int T, int64_t V, int cur, ExecCtx& ctx);
 
+int trace_after_launch(ExecCtx& ctx) {
+    LaunchRecord r{ctx.tag_name, ctx.cur_node, ctx.tag_flops, ctx.tag_bytes, nullptr};
+    FXF_CUDA(cudaEventCreate(&r.done));
+    FXF_CUDA(cudaEventRecord(r.done, ctx.stream));
+    ctx.trace->push_back(r);
+    return 0;
+}
+
 namespace {
 
 enum Kind { kInput = 0, kConstant = 1, kActivation = 2, kAlias = 3, kOutput = 4 };
@@ -83,8 +91,11 @@ namespace {
 
 int run_nodes(fxf_engine* e, cudaStream_t stream) {
     e->ctx.stream = stream;
+    int index = 0;
     for (auto& n : e->nodes) {
         int before = e->ctx.launches;
+        e->ctx.cur_node = index++;
+        tag_launch(e->ctx, op_entry(n.op).name, n.plan->flops, n.plan->bytes);
         if (n.fn(e->reg, n.in, n.out, n.params, n.plan.get(), e->ctx)) return 1;
         n.launches = e->ctx.launches - before;
     }
@@ -489,6 +500,42 @@ int fxf_engine_time_nodes(fxf_engine* e, float* ms_out, int n, void* stream) {
     if (!rc)
         for (size_t i = 0; i < e->nodes.size(); i++) cudaEventElapsedTime(&ms_out[i], ev[i], ev[i + 1]);
     for (auto& x : ev) cudaEventDestroy(x);
+    return rc;
+}
+
+int fxf_engine_profile_launches(fxf_engine* e, void* stream, FxfLaunchInfo* out, int capacity, int* n_out) {
+    FXF_CHECK(e && out && n_out, "fxf_engine_profile_launches: NULL argument");
+    if (ensure_device(e)) return 1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    std::vector<LaunchRecord> trace;
+    trace.reserve(size_t(e->launches_per_run) + 8);
+    cudaEvent_t start;
+    FXF_CUDA(cudaEventCreate(&start));
+    e->ctx.trace = &trace;
+    FXF_CUDA(cudaEventRecord(start, s));
+    int rc = run_nodes(e, s);
+    e->ctx.trace = nullptr;
+    cudaStreamSynchronize(s);
+    int n = 0;
+    cudaEvent_t prev = start;
+    for (auto& r : trace) {
+        if (!rc && n < capacity) {
+            FxfLaunchInfo& o = out[n];
+            std::memset(&o, 0, sizeof(o));
+            std::strncpy(o.kernel, r.name, sizeof(o.kernel) - 1);
+            o.node = r.node;
+            o.flops = r.flops;
+            o.bytes = r.bytes;
+            cudaEventElapsedTime(&o.ms, prev, r.done);
+            n++;
+        }
+        if (prev != start) cudaEventDestroy(prev);
+        prev = r.done;
+    }
+    if (prev != start) cudaEventDestroy(prev);
+    cudaEventDestroy(start);
+    *n_out = n;
+    FXF_CHECK(rc || size_t(n) == trace.size(), "fxf_engine_profile_launches: %zu launches but capacity %d", trace.size(), capacity);
     return rc;
 }
 

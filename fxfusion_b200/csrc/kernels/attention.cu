@@ -199,6 +199,8 @@ int launch_hd(const AttnArgs& a, ExecCtx& ctx) {
 int launch_attention(const AttnArgs& a, ExecCtx& ctx) {
     if (a.B == 0 || a.T == 0 || a.H == 0) return 0;
     FXF_CHECK(a.hd >= 1 && a.hd <= 128, "mha: head_dim %d is outside the supported range 1..128", a.hd);
+    tag_launch(ctx, "attention_fp32_flash", 4.0 * double(a.B) * a.H * double(a.T) * a.T * a.hd,
+               4.0 * 4.0 * double(a.B) * a.T * double(a.H) * a.hd + double(a.B) * a.T * a.T);
     if (a.hd <= 16) return launch_hd<16>(a, ctx);
     if (a.hd <= 32) return launch_hd<32>(a, ctx);
     if (a.hd <= 64) return launch_hd<64>(a, ctx);

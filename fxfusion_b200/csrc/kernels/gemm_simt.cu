@@ -214,6 +214,9 @@ int simt_tile_choice(int64_t M, int64_t N, int sm_count) {
 int launch_gemm_simt(const GemmArgs& a, ExecCtx& ctx) {
     if (a.M == 0 || a.N == 0) return 0;
     FXF_CHECK(a.M > 0 && a.N > 0 && a.K >= 0, "gemm: negative dimension");
+    static const char* names[] = {"gemm_fp32_simt128x128", "gemm_fp32_simt64x64", "gemm_fp32_simt32x32"};
+    tag_launch(ctx, names[simt_tile_choice(a.M, a.N, ctx.sm_count)], 2.0 * double(a.M) * double(a.N) * double(a.K),
+               4.0 * (double(a.M) * a.K + double(a.N) * a.K + double(a.N) + double(a.M) * a.N));
     switch (simt_tile_choice(a.M, a.N, ctx.sm_count)) {
         case 0: return launch_cfg<128, 128, 16, 8, 8>(a, ctx);
         case 1: return launch_cfg<64, 64, 16, 4, 4>(a, ctx);

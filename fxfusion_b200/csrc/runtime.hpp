@@ -29,6 +29,14 @@ struct Params {
     std::vector<float> floats;
 };
 
+// One traced kernel launch (profiling mode only).
+struct LaunchRecord {
+    const char* name;      // kernel family, e.g. "gemm_simt128x128", "attention_fp32"
+    int node;              // index of the graph node that issued it
+    double flops, bytes;   // algorithmic work of this launch
+    cudaEvent_t done;      // recorded right after the launch
+};
+
 // Everything a launch needs besides the registry.
 struct ExecCtx {
     cudaStream_t stream = nullptr;
@@ -38,7 +46,18 @@ struct ExecCtx {
     int sm_count = 148;
     int gemm_mode = FXF_GEMM_AUTO;
     int launches = 0;              // incremented by every kernel launch (host-side count)
+    // profiling: when `trace` is set every launch appends a record carrying the current tag
+    std::vector<LaunchRecord>* trace = nullptr;
+    int cur_node = -1;
+    const char* tag_name = "kernel";
+    double tag_flops = 0, tag_bytes = 0;
 };
+inline void tag_launch(ExecCtx& c, const char* name, double flops, double bytes) {
+    c.tag_name = name;
+    c.tag_flops = flops;
+    c.tag_bytes = bytes;
+}
+int trace_after_launch(ExecCtx& ctx);
 
 struct NodePlan {
     virtual ~NodePlan() = default;
@@ -100,6 +119,7 @@ inline std::string strfmt(const char* fmt, ...) {
         cudaError_t _e = cudaPeekAtLastError();                                               \
         if (_e != cudaSuccess) FXF_FAIL("kernel launch failed: %s at %s:%d", cudaGetErrorString(_e), __FILE__, __LINE__); \
         (ctx).launches++;                                                                     \
+        if ((ctx).trace && ::fxf::trace_after_launch(ctx)) return 1;                          \
     } while (0)
 
 // ---- tensor helpers ---------------------------------------------------------------------

@@ -130,6 +130,15 @@ class ExecutionEngine:
         _lib.check(self._lib.fxf_engine_time_nodes(self._h, ms, n, self._stream()))
         return list(ms)
 
+    def profile_launches(self):
+        """One traced forward: [{kernel, node, ms, flops, bytes}] per kernel launch."""
+        cap = self.launches_per_run + 16
+        buf = (_lib.FxfLaunchInfo * cap)()
+        n = C.c_int()
+        _lib.check(self._lib.fxf_engine_profile_launches(self._h, self._stream(), buf, cap, C.byref(n)))
+        return [{"kernel": buf[i].kernel.decode(), "node": buf[i].node, "ms": buf[i].ms, "flops": buf[i].flops,
+                 "bytes": buf[i].bytes} for i in range(n.value)]
+
     def device_status(self) -> int:
         st = C.c_int()
         _lib.check(self._lib.fxf_engine_device_status(self._h, self._stream(), C.byref(st)))

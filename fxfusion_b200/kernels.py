@@ -1,0 +1,59 @@
+"""Call one CUDA kernel of the backend outside any engine (fxf_kernel_invoke).
+
+The argument contract is the reference's KernelFn (csrc/include/runtime/tensor_registry.hpp:20-26):
+a registry of tensors, input ids, output ids, int and float params.  Tensors are torch CUDA
+tensors; scratch memory, where an op needs it, is allocated here as a torch buffer.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Sequence
+
+from . import _lib, wire
+from ._lib import FxfTensor
+
+_DT = None
+
+
+def _dtype_code(t) -> int:
+    global _DT
+    import torch
+    if _DT is None:
+        _DT = {torch.float32: wire.DT_F32, torch.float16: wire.DT_F16, torch.int32: wire.DT_I32,
+               torch.int64: wire.DT_I64, torch.bool: wire.DT_BOOL}
+    return _DT[t.dtype]
+
+
+def describe(t) -> FxfTensor:
+    d = FxfTensor()
+    d.ptr = t.data_ptr()
+    d.dtype = _dtype_code(t)
+    d.rank = t.dim()
+    for i in range(t.dim()):
+        d.shape[i] = t.shape[i]
+        d.stride[i] = t.stride(i)
+    d.nbytes = t.numel() * t.element_size()
+    return d
+
+
+def invoke(op: str, registry: Sequence, in_ids: Sequence[int], out_ids: Sequence[int], ints: Sequence[int] = (),
+           floats: Sequence[float] = (), precision: str = "auto") -> None:
+    """Runs opcode `op` (name from wire.OPCODES) on the current CUDA stream; writes registry[out_ids[0]]."""
+    import torch
+    lib = _lib.lib()
+    n = len(registry)
+    reg = (FxfTensor * n)(*[describe(t) for t in registry])
+    ii = (C.c_uint32 * max(1, len(in_ids)))(*in_ids)
+    oo = (C.c_uint32 * max(1, len(out_ids)))(*out_ids)
+    ip = (C.c_int64 * max(1, len(ints)))(*[int(v) for v in ints])
+    fp = (C.c_float * max(1, len(floats)))(*[float(v) for v in floats])
+    mode = _lib.GEMM_MODES[precision]
+    head = (wire.OP[op], reg, n, ii, len(in_ids), oo, len(out_ids), ip, len(ints), fp, len(floats))
+    need = lib.fxf_kernel_scratch_bytes(*head, mode)
+    if need < 0:
+        raise RuntimeError(lib.fxf_last_error().decode())
+    dev = registry[out_ids[0]].device
+    scratch = torch.empty(max(int(need), 16), dtype=torch.uint8, device=dev)
+    stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check(lib.fxf_kernel_invoke(*head, C.c_void_p(scratch.data_ptr()), need, mode, stream))
+    scratch.record_stream(torch.cuda.current_stream(dev))

@@ -120,6 +120,18 @@ FXF_API int fxf_engine_time_nodes(fxf_engine* e, float* ms_out, int n, void* str
 FXF_API int fxf_engine_node_info(const fxf_engine* e, int node, int* op_code, double* flops, double* bytes,
                          char* variant, size_t variant_bytes);
 
+/* One forward with a CUDA event after every kernel launch (graph replay disabled): per launch the
+ * kernel family, the graph node that issued it, its device time (gap to the previous launch's
+ * end on the same stream) and its algorithmic flops / bytes.  Synchronises `stream`. */
+typedef struct FxfLaunchInfo {
+    char    kernel[48];
+    int32_t node;
+    float   ms;
+    double  flops;
+    double  bytes;
+} FxfLaunchInfo;
+FXF_API int fxf_engine_profile_launches(fxf_engine* e, void* stream, FxfLaunchInfo* out, int capacity, int* n_out);
+
 /* One kernel, outside any engine: the KernelFn contract of
  * csrc/include/runtime/tensor_registry.hpp:20-26 (registry, input ids, output ids, Params)
  * with the per-node Cache (csrc/runtime/cache.cpp:5-73) replaced by caller-provided scratch.

@@ -1,0 +1,209 @@
+"""Per-kernel parity through fxf_kernel_invoke: each CUDA kernel against the CPU oracle's restatement
+of the reference kernel on the same seeded inputs, including ragged, empty and odd-sized cases."""
+import math
+
+import pytest
+import torch
+
+from helpers import compare_outputs
+from fxfusion_b200 import wire
+from oracle.graph_oracle import KERNELS
+
+pytestmark = pytest.mark.gpu
+ATOL, RTOL = 1e-4, 1e-3
+
+
+def both(op, reg, in_ids, out_ids, ints=(), floats=(), exact=False, precision="auto", atol=ATOL, rtol=RTOL):
+    from fxfusion_b200.kernels import invoke
+    cpu = [t.clone() for t in reg]
+    KERNELS[wire.OP[op]](cpu, list(in_ids), list(out_ids), list(ints), list(floats))
+    gpu = [t.cuda() for t in reg]
+    invoke(op, gpu, in_ids, out_ids, ints, floats, precision=precision)
+    torch.cuda.synchronize()
+    got, want = gpu[out_ids[0]].cpu(), cpu[out_ids[0]]
+    if exact:
+        assert torch.equal(got, want), f"{op}: not bit-exact"
+    else:
+        ok, info = compare_outputs(got, want, atol=atol, rtol=rtol)
+        assert ok, f"{op}: {info}"
+    return got
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return torch.randn(*shape, generator=g) * scale
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (7, 13, 5), (32, 512, 512), (33, 65, 17), (128, 128, 64), (300, 700, 260),
+                                   (512, 1000, 256), (1024, 768, 768), (5, 2304, 768), (0, 8, 4), (3, 4, 0)])
+@pytest.mark.parametrize("relu", [False, True])
+def test_linear(built_lib, M, N, K, relu):
+    x, w, b = rnd(M, K), rnd(N, K, seed=1, scale=1 / math.sqrt(max(K, 1))), rnd(N, seed=2)
+    both("LinearRelu" if relu else "Linear", [x, w, b, torch.zeros(M, N)], [0, 1, 2], [3], precision="fp32_simt")
+
+
+def test_linear_keeps_leading_dims(built_lib):
+    both("Linear", [rnd(2, 3, 5, 16), rnd(24, 16, seed=1), rnd(24, seed=2), torch.zeros(2, 3, 5, 24)], [0, 1, 2], [3])
+
+
+@pytest.mark.parametrize("M,D,F,P", [(20, 64, 256, 64), (32, 512, 512, 10), (130, 96, 200, 50)])
+def test_feedforward(built_lib, M, D, F, P):
+    reg = [rnd(M, D), rnd(F, D, seed=1, scale=0.1), rnd(F, seed=2), rnd(P, F, seed=3, scale=0.1), rnd(P, seed=4), torch.zeros(M, P)]
+    both("FeedForward", reg, [0, 1, 2, 3, 4], [5])
+
+
+def _mha_reg(B, T, H, hd, mask):
+    D = H * hd
+    return [rnd(B, T, D), mask, rnd(3 * D, D, seed=1, scale=1 / math.sqrt(D)), rnd(3 * D, seed=2, scale=0.1),
+            rnd(D, D, seed=3, scale=1 / math.sqrt(D)), rnd(D, seed=4, scale=0.1), torch.zeros(B, T, D)]
+
+
+@pytest.mark.parametrize("B,T,H,hd", [(2, 6, 4, 8), (1, 5, 2, 16), (2, 64, 4, 64), (1, 65, 2, 64), (3, 130, 3, 32), (1, 8, 1, 128), (2, 33, 2, 20)])
+def test_mha_causal(built_lib, B, T, H, hd):
+    mask = torch.tril(torch.ones(T, T, dtype=torch.bool)).view(1, 1, T, T).expand(B, 1, T, T).contiguous()
+    both("MHA", _mha_reg(B, T, H, hd, mask), [0, 1, 2, 3, 4, 5], [6], ints=[H, hd, H * hd, 3 * H * hd], floats=[math.sqrt(hd)])
+
+
+@pytest.mark.parametrize("shape", ["b11t", "11tt", "bhtt", "random"])
+def test_mha_mask_broadcast_shapes(built_lib, shape):
+    B, T, H, hd = 2, 40, 3, 16
+    g = torch.Generator().manual_seed(5)
+    if shape == "b11t":
+        mask = torch.ones(B, 1, 1, T, dtype=torch.bool)
+        mask[1, 0, 0, 25:] = False
+    elif shape == "11tt":
+        mask = torch.tril(torch.ones(T, T, dtype=torch.bool)).view(1, 1, T, T)
+    elif shape == "bhtt":
+        mask = torch.rand(B, H, T, T, generator=g) < 0.7
+        mask[..., 0] = True
+    else:
+        mask = torch.rand(B, 1, T, T, generator=g) < 0.5
+        mask[..., 0] = True
+    both("MHA", _mha_reg(B, T, H, hd, mask), [0, 1, 2, 3, 4, 5], [6], ints=[H, hd, H * hd, 3 * H * hd], floats=[math.sqrt(hd)])
+
+
+def test_mha_fully_masked_rows_and_nan_values(built_lib):
+    """A fully masked query row is NaN; a NaN in the input poisons exactly what torch's matmul poisons."""
+    B, T, H, hd = 2, 12, 2, 8
+    mask = torch.ones(B, 1, T, T, dtype=torch.bool)
+    mask[0, 0, 3, :] = False
+    reg = _mha_reg(B, T, H, hd, mask)
+    got = both("MHA", reg, [0, 1, 2, 3, 4, 5], [6], ints=[H, hd, H * hd, 3 * H * hd], floats=[math.sqrt(hd)])
+    assert torch.isnan(got[0, 3]).all() and not torch.isnan(got[1]).any()
+    reg = _mha_reg(B, T, H, hd, torch.tril(torch.ones(T, T, dtype=torch.bool)).view(1, 1, T, T).expand(B, 1, T, T).contiguous())
+    reg[0][1, 9, :] = float("nan")  # a NaN token late in the sequence: masked for earlier queries, weight 0 * NaN
+    both("MHA", reg, [0, 1, 2, 3, 4, 5], [6], ints=[H, hd, H * hd, 3 * H * hd], floats=[math.sqrt(hd)])
+
+
+@pytest.mark.parametrize("M,N", [(1, 1), (3, 5), (20, 64), (8192, 768), (7, 1024), (5, 1028), (4, 4096), (9, 130), (0, 16)])
+def test_layer_norm_and_add_layer_norm(built_lib, M, N):
+    x, z, w, b = rnd(M, N, scale=3.0) + 0.5, rnd(M, N, seed=1), rnd(N, seed=2), rnd(N, seed=3)
+    both("LayerNorm", [x, w, b, torch.zeros(M, N)], [0, 1, 2], [3], ints=[1, N], floats=[1e-5])
+    both("AddLayerNorm", [x, z, w, b, torch.zeros(M, N)], [0, 1, 2, 3], [4], ints=[1, N], floats=[1e-5])
+
+
+def test_layer_norm_two_normalized_dims(built_lib):
+    x, w, b = rnd(3, 6, 10), rnd(6, 10, seed=1), rnd(6, 10, seed=2)
+    both("LayerNorm", [x, w, b, torch.zeros(3, 6, 10)], [0, 1, 2], [3], ints=[2, 6, 10], floats=[1e-5])
+
+
+@pytest.mark.parametrize("sa,sb", [((2, 8, 6, 6), (2, 8, 6, 6)), ((32, 256, 768), (1, 256, 768)), ((4, 10, 64), (64,)),
+                                   ((3, 5, 7), (3, 1, 7)), ((1, 5, 7), (3, 5, 7)), ((5,), (5,)), ((2, 3), (1,)), ((0, 4), (0, 4))])
+def test_add_family_broadcasting(built_lib, sa, sb):
+    a, b = rnd(*sa), rnd(*sb, seed=1)
+    out = torch.zeros(torch.broadcast_shapes(sa, sb))
+    both("Add", [a, b, out], [0, 1], [2], exact=True)
+    both("AddRelu", [a, b, out], [0, 1], [2], exact=True)
+    both("Mul", [a, b, out], [0, 1], [2], ints=[0], exact=True)
+
+
+def test_relu_and_scalar_mul_including_nan(built_lib):
+    x = rnd(5, 33)
+    x[0, 0], x[1, 1], x[2, 2] = float("nan"), float("inf"), -float("inf")
+    both("Relu", [x, torch.zeros(5, 33)], [0], [1], exact=True)
+    for mode, s in ((1, 2.5), (2, 3.0), (3, 0.0)):
+        both("Mul", [x, torch.zeros(5, 33)], [0], [1], ints=[mode], floats=[s], exact=True)
+    both("Relu", [rnd(16, 64), torch.zeros(16, 64)], [0], [1], exact=True)
+
+
+def test_relu_in_place_alias(built_lib):
+    """The planner may alias Relu's output onto its input (reference passes/memory_plan.py:72-75)."""
+    from fxfusion_b200.kernels import invoke
+    x = rnd(7, 64).cuda()
+    want = torch.relu(x.cpu())
+    invoke("Relu", [x, x], [0], [1])
+    assert torch.equal(x.cpu(), want)
+
+
+def test_size_writes_int64_scalar(built_lib):
+    both("Size", [rnd(6, 10, 64), torch.zeros((), dtype=torch.int64)], [0], [1], ints=[1], exact=True)
+    both("Size", [rnd(6, 10, 64), torch.zeros((), dtype=torch.int64)], [0], [1], ints=[-1], exact=True)
+
+
+@pytest.mark.parametrize("shape,dim,start,length", [((2, 10, 64), 1, 0, 5), ((2, 5, 13), 2, 3, 7), ((1, 5000, 32), 1, 0, 8),
+                                                    ((6, 64), 0, 2, 3), ((4, 3, 5), 1, 1, 1), ((3, 7), 1, 0, 0)])
+def test_narrow_is_bit_exact(built_lib, shape, dim, start, length):
+    x = rnd(*shape)
+    out_shape = list(shape)
+    out_shape[dim] = length
+    both("Narrow", [x, torch.zeros(out_shape)], [0], [1], ints=[dim, start, length], exact=True)
+    # dynamic form: length -1, taken from a scalar tensor in the reference and from the output shape here
+    both("Narrow", [x, torch.tensor(length, dtype=torch.int64), torch.zeros(out_shape)], [0, 1], [2], ints=[dim, start, -1], exact=True)
+
+
+def test_narrow_other_dtypes(built_lib):
+    x = torch.arange(2 * 9 * 5, dtype=torch.int64).view(2, 9, 5)
+    both("Narrow", [x, torch.zeros(2, 4, 5, dtype=torch.int64)], [0], [1], ints=[1, 2, 4], exact=True)
+    m = torch.rand(3, 11, generator=torch.Generator().manual_seed(0)) < 0.5
+    both("Narrow", [m, torch.zeros(3, 5, dtype=torch.bool)], [0], [1], ints=[1, 3, 5], exact=True)
+
+
+@pytest.mark.parametrize("V,D,shape", [(1000, 64, (2, 10)), (50, 7, (3,)), (128, 768, (32, 256)), (10, 4, (0,))])
+def test_embedding_is_bit_exact(built_lib, V, D, shape):
+    idx = torch.randint(0, V, shape, generator=torch.Generator().manual_seed(0))
+    both("Embedding", [idx, rnd(V, D), torch.zeros(*shape, D)], [0, 1], [2], exact=True)
+
+
+@pytest.mark.parametrize("shape,d0,d1", [((2, 5, 7, 3), 0, 2), ((6, 16), 0, 1), ((3, 37, 41), -2, -1), ((2, 8, 4, 16), 1, 2),
+                                         ((2, 3, 4, 5, 2, 3, 2, 2), 1, 6), ((5, 1), 0, 1), ((4, 6), 1, 1)])
+def test_transpose_is_bit_exact(built_lib, shape, d0, d1):
+    x = rnd(*shape)
+    want_shape = list(torch.transpose(x, d0, d1).shape)
+    both("Transpose", [x, torch.zeros(want_shape)], [0], [1], ints=[d0 % len(shape), d1 % len(shape)], exact=True)
+
+
+@pytest.mark.parametrize("N,C,H,W,O,k,s,p,d,g,relu", [
+    (1, 3, 20, 20, 16, 3, 1, 1, 1, 1, False), (2, 3, 21, 19, 16, 3, 2, 1, 1, 1, True), (2, 8, 30, 30, 24, 7, 2, 3, 1, 1, True),
+    (1, 16, 14, 14, 24, 1, 2, 0, 1, 1, False), (2, 8, 12, 12, 8, 3, 1, 2, 2, 1, False), (1, 12, 9, 9, 18, 3, 1, 1, 1, 3, True),
+    (3, 64, 7, 7, 130, 1, 1, 0, 1, 1, True)])
+def test_conv2d(built_lib, N, C, H, W, O, k, s, p, d, g, relu):
+    x, w, b = rnd(N, C, H, W), rnd(O, C // g, k, k, seed=1, scale=1 / math.sqrt(C // g * k * k)), rnd(O, seed=2)
+    ho = (H + 2 * p - d * (k - 1) - 1) // s + 1
+    wo = (W + 2 * p - d * (k - 1) - 1) // s + 1
+    both("Conv2dRelu" if relu else "Conv2d", [x, w, b, torch.zeros(N, O, ho, wo)], [0, 1, 2], [3],
+         ints=[s, s, p, p, d, d, g, 1, 1, 1, 256, 1, 1])
+
+
+def test_pools(built_lib):
+    x = rnd(2, 8, 28, 28)
+    both("MaxPool2d", [x, torch.zeros(2, 8, 14, 14)], [0], [1], ints=[3, 3, 2, 2, 1, 1, 1, 1, 0] + [1, 1, 1, 256, 1, 1], exact=True)
+    y = rnd(1, 4, 14, 15)
+    both("MaxPool2d", [y, torch.zeros(1, 4, 7, 7)], [0], [1], ints=[3, 3, 2, 2, 0, 0, 1, 1, 1] + [1, 1, 1, 256, 1, 1], exact=True)
+    both("AvgPool2d", [x, torch.zeros(2, 8, 14, 14)], [0], [1], ints=[3, 3, 2, 2, 1, 1, 0] + [1, 1, 1, 256, 1, 1])
+    both("AvgPool2d", [y, torch.zeros(1, 4, 7, 8)], [0], [1], ints=[2, 2, 2, 2, 0, 0, 1] + [1, 1, 1, 256, 1, 1])
+    both("AdaptiveAvgPool2d", [rnd(2, 32, 7, 7), torch.zeros(2, 32, 1, 1)], [0], [1], ints=[1, 1] + [1, 1, 1, 256, 1, 1])
+    both("AdaptiveAvgPool2d", [rnd(1, 5, 10, 7), torch.zeros(1, 5, 3, 2)], [0], [1], ints=[3, 2] + [1, 1, 1, 256, 1, 1])
+    z = rnd(1, 2, 6, 6)
+    z[0, 0, 2, 2] = float("nan")
+    both("MaxPool2d", [z, torch.zeros(1, 2, 3, 3)], [0], [1], ints=[2, 2, 2, 2, 0, 0, 1, 1, 0] + [1, 1, 1, 256, 1, 1])
+
+
+def test_argument_errors_are_reported_not_executed(built_lib):
+    from fxfusion_b200.kernels import invoke
+    x, w, b, o = rnd(4, 8).cuda(), rnd(6, 9).cuda(), rnd(6).cuda(), torch.zeros(4, 6).cuda()
+    with pytest.raises(RuntimeError, match="does not match weight"):
+        invoke("Linear", [x, w, b, o], [0, 1, 2], [3])
+    with pytest.raises(RuntimeError, match="unknown mul_mode"):
+        invoke("Mul", [x, torch.zeros(4, 8).cuda()], [0], [1], ints=[7], floats=[1.0])
+    with pytest.raises(RuntimeError, match="slice exceeds"):
+        invoke("Narrow", [x, torch.zeros(4, 9).cuda()], [0], [1], ints=[1, 0, 9])
