@@ -52,7 +52,8 @@ int linear_dims(const FxfTensor& x, const FxfTensor& w, const FxfTensor& b, cons
     FXF_CHECK(numel(b) == w.shape[0], "%s: bias size does not match weight rows", who);
     d->K = K;
     d->N = w.shape[0];
-    d->M = K ? numel(x) / K : 0;
+    d->M = 1;
+    for (int k = 0; k + 1 < x.rank; k++) d->M *= x.shape[k];
     FXF_CHECK(numel(o) == d->M * d->N, "%s: output size mismatch", who);
     return 0;
 }
@@ -109,7 +110,8 @@ int k_feedforward(Registry& reg, const TensorIds& in, const TensorIds& out, cons
     FXF_CHECK(w1.shape[1] == K && w2.shape[1] == F, "feedforward: weight shapes do not chain (x[..,%lld], w1[%lld,%lld], w2[%lld,%lld])",
               (long long)K, (long long)w1.shape[0], (long long)w1.shape[1], (long long)w2.shape[0], (long long)w2.shape[1]);
     FXF_CHECK(numel(b1) == F && numel(b2) == P, "feedforward: bias sizes do not match");
-    int64_t M = K ? numel(x) / K : 0;
+    int64_t M = 1;
+    for (int k = 0; k + 1 < x.rank; k++) M *= x.shape[k];
     FXF_CHECK(numel(o) == M * P, "feedforward: output size mismatch");
     size_t need = size_t(M) * size_t(F) * sizeof(float);
     FXF_CHECK(ctx.scratch_bytes >= need && (need == 0 || ctx.scratch != nullptr), "feedforward: scratch too small (%zu < %zu bytes)", ctx.scratch_bytes, need);

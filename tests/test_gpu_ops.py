@@ -22,7 +22,11 @@ def both(op, reg, in_ids, out_ids, ints=(), floats=(), exact=False, precision="a
     torch.cuda.synchronize()
     got, want = gpu[out_ids[0]].cpu(), cpu[out_ids[0]]
     if exact:
-        assert torch.equal(got, want), f"{op}: not bit-exact"
+        if got.dtype.is_floating_point:  # NaN != NaN, so compare NaN positions and the remaining bits separately
+            assert torch.equal(torch.isnan(got), torch.isnan(want)), f"{op}: NaN positions differ"
+            assert torch.equal(torch.nan_to_num(got, nan=0.0), torch.nan_to_num(want, nan=0.0)), f"{op}: not bit-exact"
+        else:
+            assert torch.equal(got, want), f"{op}: not bit-exact"
     else:
         ok, info = compare_outputs(got, want, atol=atol, rtol=rtol)
         assert ok, f"{op}: {info}"
