@@ -567,7 +567,7 @@ int64_t fxf_kernel_scratch_bytes(int op_code, const FxfTensor* reg, int n_reg, c
     Params p;
     if (make_call(op_code, reg, n_reg, in_ids, n_in, out_ids, n_out, ints, n_ints, floats, n_floats, &r, &in, &out, &p)) return -1;
     auto plan = op_entry(op_code).plan(r, in, out, p, gemm_mode);
-    return int64_t(plan->scratch_bytes);
+    return int64_t(round_up(plan->scratch_bytes, 256) + plan->persist_bytes);
 }
 
 int fxf_kernel_invoke(int op_code, const FxfTensor* reg, int n_reg, const uint32_t* in_ids, int n_in, const uint32_t* out_ids, int n_out,
@@ -579,17 +579,21 @@ int fxf_kernel_invoke(int op_code, const FxfTensor* reg, int n_reg, const uint32
     if (make_call(op_code, reg, n_reg, in_ids, n_in, out_ids, n_out, ints, n_ints, floats, n_floats, &r, &in, &out, &p)) return 1;
     const OpEntry& entry = op_entry(op_code);
     auto plan = entry.plan(r, in, out, p, gemm_mode);
-    FXF_CHECK(plan->persist_bytes == 0, "kernel call: op needs persistent memory; use an engine");
+    size_t need = round_up(plan->scratch_bytes, 256) + plan->persist_bytes;
+    FXF_CHECK(need == 0 || (scratch != nullptr && scratch_bytes >= int64_t(need)), "kernel call: scratch too small (%lld < %zu bytes)", (long long)scratch_bytes, need);
+    FXF_CHECK(need == 0 || (reinterpret_cast<uintptr_t>(scratch) & 255) == 0, "kernel call: scratch must be 256-byte aligned");
     ExecCtx ctx;
     ctx.stream = static_cast<cudaStream_t>(stream);
     ctx.scratch = scratch;
-    ctx.scratch_bytes = scratch_bytes > 0 ? size_t(scratch_bytes) : 0;
+    ctx.scratch_bytes = plan->scratch_bytes;
     ctx.gemm_mode = gemm_mode;
+    if (plan->persist_bytes) plan->persist = static_cast<char*>(scratch) + round_up(plan->scratch_bytes, 256);
     int dev = 0;
     FXF_CUDA(cudaGetDevice(&dev));
     int sms = 0;
     FXF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     ctx.sm_count = sms;
+    if (plan->prepare(r, in, out, p, ctx)) return 1;
     return entry.kernel(r, in, out, p, plan.get(), ctx);
 }
 

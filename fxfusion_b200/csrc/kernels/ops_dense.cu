@@ -14,9 +14,6 @@
 
 namespace fxf {
 
-int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx);       // gemm_tc.cu
-bool gemm_tc_supported(const GemmArgs& a);                  // gemm_tc.cu
-
 static bool use_tc(const GemmArgs& a, int gemm_mode) {
     if (gemm_mode == FXF_GEMM_FP32_SIMT) return false;
     return gemm_tc_supported(a);
@@ -31,14 +28,51 @@ int launch_gemm(const GemmArgs& a, ExecCtx& ctx) {
 }
 
 std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count) {
-    if (use_tc(a, gemm_mode)) return "tcgen05-tf32x3";
+    if (gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(a.M, a.N, a.K)) return a.N > 128 ? "tcgen05-tf32x3-128x256" : "tcgen05-tf32x3-128x128";
     static const char* names[] = {"simt128x128", "simt64x64", "simt32x32"};
     return names[simt_tile_choice(a.M, a.N, sm_count)];
 }
 
 namespace {
 
-struct DensePlan : NodePlan {};
+// Holds up to two weights pre-split into TF32 hi/lo halves inside the node's persistent memory.
+struct DensePlan : NodePlan {
+    struct Split {
+        int input = -1;      // position in input_ids of the weight
+        int64_t n = 0;       // elements
+        size_t offset = 0;   // byte offset of the hi half inside `persist`; lo follows
+    };
+    Split splits[2];
+    int n_splits = 0;
+    void want_split(int input, int64_t N, int64_t K, int64_t M, int gemm_mode) {
+        if (gemm_mode == FXF_GEMM_FP32_SIMT || !gemm_tc_shape_ok(M, N, K)) return;
+        Split& sp = splits[n_splits++];
+        sp.input = input;
+        sp.n = N * K;
+        sp.offset = persist_bytes;
+        persist_bytes += round_up(size_t(2) * size_t(sp.n) * sizeof(float), 256);
+    }
+    const float* hi(int input) const {
+        for (int i = 0; i < n_splits; i++)
+            if (splits[i].input == input && persist) return reinterpret_cast<const float*>(static_cast<const char*>(persist) + splits[i].offset);
+        return nullptr;
+    }
+    const float* lo(int input) const {
+        for (int i = 0; i < n_splits; i++)
+            if (splits[i].input == input && persist) return hi(input) + splits[i].n;
+        return nullptr;
+    }
+    int prepare(Registry& reg, const TensorIds& in, const TensorIds&, const Params&, ExecCtx& ctx) override {
+        for (int i = 0; i < n_splits; i++) {
+            const FxfTensor& w = reg[in[splits[i].input]];
+            FXF_CHECK(persist != nullptr && numel(w) == splits[i].n, "dense plan: persistent memory was not assigned");
+            float* h = reinterpret_cast<float*>(static_cast<char*>(persist) + splits[i].offset);
+            if (launch_split_tf32(static_cast<const float*>(w.ptr), h, h + splits[i].n, splits[i].n, ctx)) return 1;
+        }
+        return 0;
+    }
+};
+inline const DensePlan* dense(const NodePlan* p) { return static_cast<const DensePlan*>(p); }
 
 struct LinearDims {
     int64_t M, N, K;
@@ -58,7 +92,7 @@ int linear_dims(const FxfTensor& x, const FxfTensor& w, const FxfTensor& b, cons
     return 0;
 }
 
-int run_linear(Registry& reg, const TensorIds& in, const TensorIds& out, bool relu, ExecCtx& ctx, const char* who) {
+int run_linear(Registry& reg, const TensorIds& in, const TensorIds& out, bool relu, const NodePlan* plan, ExecCtx& ctx, const char* who) {
     FXF_CHECK(in.size() >= 3 && out.size() >= 1, "%s: expects [x, weight, bias]", who);
     const FxfTensor &x = reg[in[0]], &w = reg[in[1]], &b = reg[in[2]], &o = reg[out[0]];
     LinearDims d;
@@ -66,6 +100,7 @@ int run_linear(Registry& reg, const TensorIds& in, const TensorIds& out, bool re
     GemmArgs g;
     g.x = static_cast<const float*>(x.ptr);
     g.w = static_cast<const float*>(w.ptr);
+    if (plan) { g.w_hi = dense(plan)->hi(1); g.w_lo = dense(plan)->lo(1); }
     g.bias = static_cast<const float*>(b.ptr);
     g.out = static_cast<float*>(o.ptr);
     g.M = d.M; g.N = d.N; g.K = d.K;
@@ -76,11 +111,11 @@ int run_linear(Registry& reg, const TensorIds& in, const TensorIds& out, bool re
 
 }  // namespace
 
-int k_linear(Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const NodePlan*, ExecCtx& ctx) {
-    return run_linear(reg, in, out, false, ctx, "linear");
+int k_linear(Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const NodePlan* plan, ExecCtx& ctx) {
+    return run_linear(reg, in, out, false, plan, ctx, "linear");
 }
-int k_linear_relu(Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const NodePlan*, ExecCtx& ctx) {
-    return run_linear(reg, in, out, true, ctx, "linear_relu");
+int k_linear_relu(Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const NodePlan* plan, ExecCtx& ctx) {
+    return run_linear(reg, in, out, true, plan, ctx, "linear_relu");
 }
 
 std::unique_ptr<NodePlan> plan_linear(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, int gemm_mode) {
@@ -95,13 +130,14 @@ std::unique_ptr<NodePlan> plan_linear(const Registry& reg, const TensorIds& in, 
             p->flops = 2.0 * double(g.M) * double(g.N) * double(g.K);
             p->bytes = 4.0 * (double(g.M) * g.K + double(g.N) * g.K + double(g.N) + double(g.M) * g.N);
             p->variant = gemm_variant_name(g, gemm_mode, 148);
+            p->want_split(1, g.N, g.K, g.M, gemm_mode);
         }
     }
     return p;
 }
 
 // ---- FeedForward ------------------------------------------------------------------------------
-int k_feedforward(Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const NodePlan*, ExecCtx& ctx) {
+int k_feedforward(Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const NodePlan* plan, ExecCtx& ctx) {
     FXF_CHECK(in.size() >= 5 && out.size() >= 1, "feedforward: expects [x, w1, b1, w2, b2]");
     const FxfTensor &x = reg[in[0]], &w1 = reg[in[1]], &b1 = reg[in[2]], &w2 = reg[in[3]], &b2 = reg[in[4]], &o = reg[out[0]];
     FXF_CHECK(x.dtype == FXF_F32 && o.dtype == FXF_F32, "feedforward: only float32 is supported");
@@ -119,10 +155,12 @@ int k_feedforward(Registry& reg, const TensorIds& in, const TensorIds& out, cons
     GemmArgs g1;
     g1.x = static_cast<const float*>(x.ptr); g1.w = static_cast<const float*>(w1.ptr); g1.bias = static_cast<const float*>(b1.ptr);
     g1.out = hidden; g1.M = M; g1.N = F; g1.K = K; g1.ldx = K; g1.ldw = K; g1.ldo = F; g1.relu = true;
+    if (plan) { g1.w_hi = dense(plan)->hi(1); g1.w_lo = dense(plan)->lo(1); }
     if (launch_gemm(g1, ctx)) return 1;
     GemmArgs g2;
     g2.x = hidden; g2.w = static_cast<const float*>(w2.ptr); g2.bias = static_cast<const float*>(b2.ptr);
     g2.out = static_cast<float*>(o.ptr); g2.M = M; g2.N = P; g2.K = F; g2.ldx = F; g2.ldw = F; g2.ldo = P; g2.relu = false;
+    if (plan) { g2.w_hi = dense(plan)->hi(3); g2.w_lo = dense(plan)->lo(3); }
     return launch_gemm(g2, ctx);
 }
 
@@ -138,6 +176,8 @@ std::unique_ptr<NodePlan> plan_feedforward(const Registry& reg, const TensorIds&
             GemmArgs g1; g1.M = M; g1.N = F; g1.K = K; g1.ldx = K; g1.ldw = K; g1.ldo = F;
             GemmArgs g2; g2.M = M; g2.N = P; g2.K = F; g2.ldx = F; g2.ldw = F; g2.ldo = P;
             p->variant = gemm_variant_name(g1, gemm_mode, 148) + "+" + gemm_variant_name(g2, gemm_mode, 148);
+            p->want_split(1, F, K, M, gemm_mode);
+            p->want_split(3, P, F, M, gemm_mode);
         }
     }
     return p;
@@ -166,7 +206,7 @@ int mha_dims(const Registry& reg, const TensorIds& in, const TensorIds& out, con
 }
 }  // namespace
 
-int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const NodePlan*, ExecCtx& ctx) {
+int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const NodePlan* plan, ExecCtx& ctx) {
     MhaDims d;
     if (mha_dims(reg, in, out, p, &d)) return 1;
     const FxfTensor &x = reg[in[0]], &mask = reg[in[1]], &wq = reg[in[2]], &bq = reg[in[3]], &wo = reg[in[4]], &bo = reg[in[5]], &o = reg[out[0]];
@@ -188,6 +228,7 @@ int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params
     GemmArgs g;
     g.x = static_cast<const float*>(x.ptr); g.w = static_cast<const float*>(wq.ptr); g.bias = static_cast<const float*>(bq.ptr);
     g.out = qkv; g.M = d.M; g.N = d.QKV; g.K = d.D; g.ldx = d.D; g.ldw = d.D; g.ldo = d.QKV;
+    if (plan) { g.w_hi = dense(plan)->hi(2); g.w_lo = dense(plan)->lo(2); }
     if (launch_gemm(g, ctx)) return 1;
 
     AttnArgs a;
@@ -201,6 +242,7 @@ int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params
     GemmArgs g2;
     g2.x = cx; g2.w = static_cast<const float*>(wo.ptr); g2.bias = static_cast<const float*>(bo.ptr);
     g2.out = static_cast<float*>(o.ptr); g2.M = d.M; g2.N = d.D; g2.K = d.D; g2.ldx = d.D; g2.ldw = d.D; g2.ldo = d.D;
+    if (plan) { g2.w_hi = dense(plan)->hi(4); g2.w_lo = dense(plan)->lo(4); }
     return launch_gemm(g2, ctx);
 }
 
@@ -215,6 +257,8 @@ std::unique_ptr<NodePlan> plan_mha(const Registry& reg, const TensorIds& in, con
         GemmArgs g1; g1.M = M; g1.N = QKV; g1.K = D; g1.ldx = D; g1.ldw = D; g1.ldo = QKV;
         GemmArgs g2; g2.M = M; g2.N = D; g2.K = D; g2.ldx = D; g2.ldw = D; g2.ldo = D;
         pl->variant = gemm_variant_name(g1, gemm_mode, 148) + "+flash-fp32+" + gemm_variant_name(g2, gemm_mode, 148);
+        pl->want_split(2, QKV, D, M, gemm_mode);
+        pl->want_split(4, D, D, M, gemm_mode);
     }
     return pl;
 }

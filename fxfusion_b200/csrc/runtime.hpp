@@ -158,10 +158,13 @@ inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // ---- kernels shared between ops (defined in the .cu files) -------------------------------
 // out[M,N] = act(x[M,K] · w[N,K]^T + bias[N]); row strides in elements (ldx, ldw, ldo).
-// `tc_w_lo`: optional pre-split low part of w for the tensor-core path (may be null).
+// `w_hi` / `w_lo`: the weight pre-split into TF32 high and low parts for the tensor-core path
+// (both null when no split exists; the fp32 SIMT kernel is used then).
 struct GemmArgs {
     const float* x = nullptr;
     const float* w = nullptr;
+    const float* w_hi = nullptr;
+    const float* w_lo = nullptr;
     const float* bias = nullptr;
     float* out = nullptr;
     int64_t M = 0, N = 0, K = 0;
@@ -170,6 +173,10 @@ struct GemmArgs {
 };
 int launch_gemm(const GemmArgs& a, ExecCtx& ctx);
 int launch_gemm_simt(const GemmArgs& a, ExecCtx& ctx);
+int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx);
+bool gemm_tc_supported(const GemmArgs& a);
+bool gemm_tc_shape_ok(int64_t M, int64_t N, int64_t K);
+int launch_split_tf32(const float* w, float* hi, float* lo, int64_t n, ExecCtx& ctx);
 int simt_tile_choice(int64_t M, int64_t N, int sm_count);
 std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count);
 
