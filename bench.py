@@ -316,8 +316,57 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_micro(args):
+    """One op, outside any engine, through fxf_kernel_invoke — used to profile a single kernel on a
+    small case (inputs larger than L2, a few hundred MB on the device)."""
+    import math
+    import torch
+    from fxfusion_b200.kernels import invoke
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(0)
+    M, N, K = args.m, args.n, args.k
+    if args.micro == "linear":
+        reg = [torch.randn(M, K, generator=g).cuda(), (torch.randn(N, K, generator=g) / math.sqrt(K)).cuda(), torch.randn(N, generator=g).cuda(),
+               torch.empty(M, N, device="cuda")]
+        call = lambda: invoke("Linear", reg, [0, 1, 2], [3], precision=args.precision)
+        flops, nbytes = 2.0 * M * N * K, 4.0 * (M * K + N * K + N + M * N)
+    elif args.micro == "layernorm":
+        reg = [torch.randn(M, N, generator=g).cuda(), torch.ones(N).cuda(), torch.zeros(N).cuda(), torch.empty(M, N, device="cuda")]
+        call = lambda: invoke("LayerNorm", reg, [0, 1, 2], [3], ints=[1, N], floats=[1e-5])
+        flops, nbytes = 8.0 * M * N, 4.0 * (2 * M * N + 2 * N)
+    elif args.micro == "add":
+        reg = [torch.randn(M, N, generator=g).cuda(), torch.randn(M, N, generator=g).cuda(), torch.empty(M, N, device="cuda")]
+        call = lambda: invoke("Add", reg, [0, 1], [2])
+        flops, nbytes = 1.0 * M * N, 12.0 * M * N
+    else:  # mha: B = m, T = n, D = k, 64-wide heads
+        Bm, Tm, D = M, N, K
+        H = D // 64
+        mask = torch.tril(torch.ones(Tm, Tm, dtype=torch.bool)).view(1, 1, Tm, Tm).expand(Bm, 1, Tm, Tm).contiguous().cuda()
+        reg = [torch.randn(Bm, Tm, D, generator=g).cuda(), mask, (torch.randn(3 * D, D, generator=g) * 0.02).cuda(), torch.zeros(3 * D).cuda(),
+               (torch.randn(D, D, generator=g) * 0.02).cuda(), torch.zeros(D).cuda(), torch.empty(Bm, Tm, D, device="cuda")]
+        call = lambda: invoke("MHA", reg, [0, 1, 2, 3, 4, 5], [6], ints=[H, 64, D, 3 * D], floats=[8.0], precision=args.precision)
+        flops = 2.0 * Bm * Tm * 3 * D * D + 4.0 * Bm * H * Tm * Tm * 64 + 2.0 * Bm * Tm * D * D
+        nbytes = 4.0 * (2 * Bm * Tm * D + 4 * D * D) + Bm * Tm * Tm
+    for _ in range(max(args.warmup, 1)):
+        call()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"micro": args.micro, "m": M, "n": N, "k": K, "precision": args.precision, "ms_per_call": ms,
+                      "tflops": flops / ms / 1e9, "gbs": nbytes / ms / 1e6, "note": "includes the per-call weight split of the tensor-core path"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--micro", default=None, choices=["linear", "layernorm", "add", "mha"], help="profile one op instead of the decode workload")
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=3072)
+    ap.add_argument("--k", type=int, default=768)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
@@ -325,6 +374,8 @@ def main():
     ap.add_argument("--precision", default="auto", choices=["auto", "fp32_simt", "fp32_3xtf32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.micro:
+        return run_micro(args)
     if args.impl == "reference":
         run_reference(args)
     else:
