@@ -9,7 +9,7 @@ only this package can create workloads:
     order with `id == index` (reference passes/memory_plan.py:204, serializer.py:37), kinds
     input / const / activation / alias / output (memory_plan.py:87-102), NoOp nodes for
     placeholders, constants, eval-mode Dropout and `output` (serializer.py:116-133).
-  * `plan_memory` is the reference's static planner restated: liveness by last use, first-fit
+  * `GraphBuilder.finish` (with `_Arena`) is the reference's static planner restated: liveness by last use, first-fit
     free list with coalescing and top-of-arena shrink, sizes rounded up to the alignment, a
     buffer released right after its last user has been allocated
     (passes/memory_plan.py:147-213, passes/memory_manager.py:34-91).
