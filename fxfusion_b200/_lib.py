@@ -55,6 +55,8 @@ SIGNATURES = {
     "fxf_engine_profile_launches": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(FxfLaunchInfo), C.c_int, C.POINTER(C.c_int)]),
     "fxf_kernel_scratch_bytes": (C.c_int64, _kernel_args + [C.c_int]),
     "fxf_kernel_invoke": (C.c_int, _kernel_args + [C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
+    "fxf_feedforward_static_max_bytes": (C.c_int64, []),
+    "fxf_feedforward_static": (C.c_int, [C.c_void_p] * 6 + [C.c_int64] * 4 + [C.c_void_p]),
     "fxf_decode_build_mask": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_void_p]),
     "fxf_decode_argmax_scatter": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_int, C.c_void_p]),
     "fxf_decode_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_void_p]),

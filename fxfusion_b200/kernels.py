@@ -57,3 +57,17 @@ def invoke(op: str, registry: Sequence, in_ids: Sequence[int], out_ids: Sequence
     stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
     _lib.check(lib.fxf_kernel_invoke(*head, C.c_void_p(scratch.data_ptr()), need, mode, stream))
     scratch.record_stream(torch.cuda.current_stream(dev))
+
+
+def feedforward_static(x, w1, b1, w2, b2, out) -> None:
+    """out = relu(x @ w1.T + b1) @ w2.T + b2 through fxf_feedforward_static: nothing is allocated, the hidden
+    activation lives in the library's fixed scratch array (see include/fxf_b200.h for the limits).
+    All arguments are contiguous float32 CUDA tensors on the current device."""
+    import torch
+    lib = _lib.lib()
+    D = x.shape[-1]
+    M = x.numel() // D if D else 0
+    F, P = w1.shape[0], w2.shape[0]
+    stream = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(lib.fxf_feedforward_static(x.data_ptr(), w1.data_ptr(), b1.data_ptr(), w2.data_ptr(), b2.data_ptr(), out.data_ptr(),
+                                          M, D, F, P, stream))

@@ -164,6 +164,20 @@ FXF_API int fxf_decode_argmax_scatter(const float* logits, int64_t* tokens, int 
 FXF_API int fxf_decode_static(fxf_engine* e, int64_t* tokens_io, int initial_len, int64_t pad_idx,
                       void* stream);
 
+/* FeedForward without any allocation (no counterpart in the reference: its CUDA feedforward takes
+ * its hidden buffer from a per-node torch::empty).  For callers that cannot call cudaMalloc — the device
+ * is owned by their own pool, or an allocation's implicit synchronisation is not acceptable.  The
+ * [M,F] hidden activation is kept in a fixed array inside the library (fxf_feedforward_static_max_bytes()
+ * bytes, 8 MiB, held on every GPU that loads the library until the process exits); M*F*4 beyond that is
+ * refused with an error.  out[M,P] = relu(x[M,D]·w1[F,D]^T + b1)·w2[P,F]^T + b2, fp32 FFMA kernels; all
+ * pointers are device pointers, row-major, dense.  All calls on a GPU share the array: calls that can
+ * overlap on the GPU race and must be serialised by the caller.  The first call on a device resolves the
+ * array's address; make it before any stream capture. */
+FXF_API int64_t fxf_feedforward_static_max_bytes(void);
+FXF_API int fxf_feedforward_static(const float* x, const float* w1, const float* b1, const float* w2,
+                                   const float* b2, float* out, int64_t M, int64_t D, int64_t F, int64_t P,
+                                   void* stream);
+
 #ifdef __cplusplus
 }
 #endif
