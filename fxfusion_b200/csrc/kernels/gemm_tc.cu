@@ -8,26 +8,30 @@
 // Arithmetic.  x = x_hi + x_lo with x_hi = tf32(x) (round to nearest, 10-bit mantissa) and
 // x_lo = tf32(x - x_hi); same for w.  x·w ~= x_lo·w_hi + x_hi·w_lo + x_hi·w_hi, accumulated in
 // fp32; the dropped x_lo·w_lo term is ~2^-22 relative.  Weights are constants: they are split
-// once when an engine is built (split_tf32) and kept as two arrays.  Activations are split inside the
-// kernel, in shared memory, while the tensor core works on the previous stage.
+// once when an engine is built (split_tf32_kernel) and kept as two arrays.  Activations are split
+// inside the kernel, in shared memory, while the tensor core works on earlier stages.
 //
-// Structure (one CTA = one 128 x BN output tile, 192 threads):
-//   warp 0    TMA producer: per K-slab of 32 floats (one 128-byte swizzle row) three
-//             cp.async.bulk.tensor loads — x tile [128,32], w_hi and w_lo tiles [BN,32] — land in a
-//             STAGES-deep ring of shared-memory stages, completion counted on an mbarrier.
-//   warps 2-5 split the x tile in place (hi) and into a twin buffer (lo); being element-wise the
-//             128-byte swizzle pattern TMA wrote is preserved.  fence.proxy.async, then arrive.
-//   warp 1    one thread issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8): 4 K-steps x 3 products
-//             per stage, accumulating in TMEM; tcgen05.commit releases the stage to the producer.
-//   warps 2-5 epilogue: tcgen05.ld the accumulator (each warp its 32 TMEM lanes), add bias, ReLU,
-//             store.
-// Every mbarrier wait is bounded by a wall-clock budget; on expiry the CTA records an error in
-// the status word, stops issuing work, frees its TMEM and returns.
+// Structure: a PERSISTENT kernel, one CTA per SM, each CTA walking a strided list of 128 x BN output
+// tiles.  320 threads in four roles that only meet on mbarriers:
+//   warps 0-3  epilogue: tcgen05.ld of a finished accumulator (each warp its 32 TMEM lanes), staged
+//              through shared memory so that global stores are row-contiguous, bias + ReLU fused.
+//              TMEM holds TWO accumulators, so the epilogue of tile i runs under the main loop of
+//              tile i+1.
+//   warp 4     TMA producer: per K-slab three cp.async.bulk.tensor loads — x tile [128,BK], w_hi and
+//              w_lo tiles [BN,BK] — into a STAGES-deep ring, completion counted on an mbarrier.
+//   warp 5     one thread issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8), 3 products per K-step,
+//              accumulating in TMEM; tcgen05.commit hands the stage back to the producer and, after
+//              the last slab of a tile, the accumulator to the epilogue.
+//   warps 6-9  split the x tile in place (hi) and into a twin buffer (lo); being element-wise the
+//              swizzle pattern TMA wrote is preserved.  fence.proxy.async, then arrive.
+// Every mbarrier wait is bounded by a wall-clock budget; on expiry the CTA records an error in the
+// status word, all roles stop issuing work, the CTA frees its TMEM and returns.
 //
 // Bound: tensor pipe (TF32 rate / 3).  Shared-memory bandwidth is the practical limiter for an
 // SS-operand MMA with cta_group::1 (operand reads + TMA fills + the split pass share 128 B/clk).
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "../runtime.hpp"
@@ -36,11 +40,11 @@ namespace fxf {
 namespace {
 
 constexpr int BM = 128;
-constexpr int BK = 32;             // floats per K-slab = 128 bytes = one swizzle row
-constexpr int kThreads = 192;      // warp0 TMA, warp1 MMA, warps 2..5 split + epilogue
+constexpr int kThreads = 320;
+constexpr int kEpiWarp0 = 0, kTmaWarp = 4, kMmaWarp = 5, kSplitWarp0 = 6;
 constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s per wait
 
-enum : int { kErrWaitTma = 101, kErrWaitSplit = 102, kErrWaitEmpty = 103, kErrWaitAcc = 104 };
+enum : int { kErrWaitTma = 101, kErrWaitSplit = 102, kErrWaitEmpty = 103, kErrWaitAcc = 104, kErrWaitAccEmpty = 105 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -81,6 +85,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         }
     }
 }
+// Records why a role gave up (first reason wins) and tells the other roles to stop.
+__device__ __forceinline__ void give_up(volatile int* abort_flag, int* status, int code) {
+    if (!*abort_flag) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, code);
+    }
+}
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -88,14 +99,18 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
                  : "memory");
 }
 
-// K-major operand tile with 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart.
-__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
+// K-major operand tile whose rows are one swizzle span wide (BK floats = 128 or 64 bytes):
+// rows `row_bytes` apart, 8-row groups 8*row_bytes apart.
+template <int BK>
+__device__ __forceinline__ uint64_t umma_desc_k_major(uint32_t smem_addr) {
+    constexpr uint32_t row_bytes = BK * 4;
+    constexpr uint64_t layout = row_bytes == 128 ? 2 : 4;  // SWIZZLE_128B : SWIZZLE_64B
     uint64_t d = 0;
-    d |= uint64_t((smem_addr & 0x3FFFF) >> 4);   // start address, 16-byte units
-    d |= uint64_t(1) << 16;                      // leading byte offset (unused for swizzled K-major)
-    d |= uint64_t(1024 >> 4) << 32;              // stride byte offset between 8-row groups
-    d |= uint64_t(1) << 46;                      // descriptor version for sm_100
-    d |= uint64_t(2) << 61;                      // layout type: SWIZZLE_128B
+    d |= uint64_t((smem_addr & 0x3FFFF) >> 4);    // start address, 16-byte units
+    d |= uint64_t(1) << 16;                       // leading byte offset (unused for swizzled K-major)
+    d |= uint64_t((8 * row_bytes) >> 4) << 32;    // stride byte offset between 8-row groups
+    d |= uint64_t(1) << 46;                       // descriptor version for sm_100
+    d |= layout << 61;
     return d;
 }
 // kind::tf32, fp32 accumulate, A and B K-major, M x N tile.
@@ -135,16 +150,20 @@ __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
     lo = __uint_as_float(to_tf32(x - hi));
 }
 
-template <int BN, int STAGES>
+constexpr int kStagePad = 36;  // floats per staged epilogue row: 32 + 4 keeps float4 rows conflict-free
+
+template <int BN, int BK, int STAGES>
 struct alignas(1024) TcSmem {
     float a_hi[STAGES][BM * BK];
     float a_lo[STAGES][BM * BK];
     float b_hi[STAGES][BN * BK];
     float b_lo[STAGES][BN * BK];
+    float stage_out[4][32 * kStagePad];   // one 32 x 32 block per epilogue warp
     uint64_t full_tma[STAGES];
     uint64_t full_split[STAGES];
     uint64_t empty[STAGES];
-    uint64_t acc_full;
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -155,22 +174,35 @@ struct TcParams {
     int64_t M, N, K, ldo;
     int relu;
     int vec_out;
+    int tiles_m, tiles_n, m_fastest;
     int* status;
 };
 
-template <int BN, int STAGES>
+__device__ __forceinline__ void tile_coords(const TcParams& p, int tile, int& tm, int& tn) {
+    if (p.m_fastest) {
+        tm = tile % p.tiles_m;
+        tn = tile / p.tiles_m;
+    } else {
+        tn = tile % p.tiles_n;
+        tm = tile / p.tiles_n;
+    }
+}
+
+template <int BN, int BK, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_whi,
                    const __grid_constant__ CUtensorMap map_wlo, TcParams p) {
     extern __shared__ unsigned char smem_raw[];
     // dynamic shared memory is only guaranteed 16-byte aligned; swizzled tiles need 1024
-    TcSmem<BN, STAGES>& s = *reinterpret_cast<TcSmem<BN, STAGES>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    using Smem = TcSmem<BN, BK, STAGES>;
+    Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_n = blockIdx.x, tile_m = blockIdx.y;
     const int num_k = int((p.K + BK - 1) / BK);
+    const int num_tiles = p.tiles_m * p.tiles_n;
     constexpr uint32_t kStageBytes = uint32_t(BM * BK + 2 * BN * BK) * 4u;
     constexpr uint32_t kIdesc = umma_idesc_tf32(BM, BN);
+    constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators
     volatile int* abort_flag = &s.abort_flag;
 
     if (threadIdx.x == 0) {
@@ -179,143 +211,185 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             mbar_init(&s.full_split[i], 4);   // one arrival per split warp
             mbar_init(&s.empty[i], 1);
         }
-        mbar_init(&s.acc_full, 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&s.acc_full[i], 1);
+            mbar_init(&s.acc_empty[i], 4);    // one arrival per epilogue warp
+        }
         s.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // TMEM allocation is a warp-wide operation
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s.tmem_base)), "r"(uint32_t(BN)) : "memory");
+    if (warp == kMmaWarp) {  // TMEM allocation is a warp-wide operation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s.tmem_base)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_acc = s.tmem_base;
+    const uint32_t tmem_base = s.tmem_base;
 
-    if (warp == 0) {
+    if (warp == kTmaWarp) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            for (int k = 0; k < num_k; k++) {
-                int st = k % STAGES;
-                if (k >= STAGES && !mbar_wait(&s.empty[st], uint32_t((k / STAGES - 1) & 1), abort_flag)) {
-                    if (!*abort_flag) { *abort_flag = 1; if (p.status) atomicCAS(p.status, 0, kErrWaitEmpty); }
-                    break;
+            uint32_t it = 0;  // slab counter over all tiles of this CTA
+            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+                int tm, tn;
+                tile_coords(p, tile, tm, tn);
+                for (int k = 0; k < num_k; k++, it++) {
+                    int st = it % STAGES;
+                    if (it >= uint32_t(STAGES) && !mbar_wait(&s.empty[st], ((it / STAGES) - 1) & 1, abort_flag)) {
+                        give_up(abort_flag, p.status, kErrWaitEmpty);
+                        goto producer_done;
+                    }
+                    mbar_expect_tx(&s.full_tma[st], kStageBytes);
+                    tma_load_2d(s.a_hi[st], &map_x, k * BK, tm * BM, &s.full_tma[st]);
+                    tma_load_2d(s.b_hi[st], &map_whi, k * BK, tn * BN, &s.full_tma[st]);
+                    tma_load_2d(s.b_lo[st], &map_wlo, k * BK, tn * BN, &s.full_tma[st]);
                 }
-                mbar_expect_tx(&s.full_tma[st], kStageBytes);
-                tma_load_2d(s.a_hi[st], &map_x, k * BK, tile_m * BM, &s.full_tma[st]);
-                tma_load_2d(s.b_hi[st], &map_whi, k * BK, tile_n * BN, &s.full_tma[st]);
-                tma_load_2d(s.b_lo[st], &map_wlo, k * BK, tile_n * BN, &s.full_tma[st]);
             }
+        producer_done:;
         }
-    } else if (warp == 1) {
+    } else if (warp == kMmaWarp) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            bool ok = true;
-            for (int k = 0; k < num_k && ok; k++) {
-                int st = k % STAGES;
-                uint32_t par = uint32_t((k / STAGES) & 1);
-                if (!mbar_wait(&s.full_tma[st], par, abort_flag)) {
-                    if (!*abort_flag) { *abort_flag = 1; if (p.status) atomicCAS(p.status, 0, kErrWaitTma); }
-                    ok = false;
-                    break;
-                }
-                if (!mbar_wait(&s.full_split[st], par, abort_flag)) {
-                    if (!*abort_flag) { *abort_flag = 1; if (p.status) atomicCAS(p.status, 0, kErrWaitSplit); }
-                    ok = false;
-                    break;
+            uint32_t it = 0, tcount = 0;
+            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tcount++) {
+                const uint32_t buf = tcount & 1;
+                if (tcount >= 2 && !mbar_wait(&s.acc_empty[buf], ((tcount >> 1) - 1) & 1, abort_flag)) {
+                    give_up(abort_flag, p.status, kErrWaitAccEmpty);
+                    goto mma_done;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                uint64_t a_hi = umma_desc_k_sw128(smem_u32(s.a_hi[st])), a_lo = umma_desc_k_sw128(smem_u32(s.a_lo[st]));
-                uint64_t b_hi = umma_desc_k_sw128(smem_u32(s.b_hi[st])), b_lo = umma_desc_k_sw128(smem_u32(s.b_lo[st]));
+                const uint32_t tmem_acc = tmem_base + buf * uint32_t(BN);
+                for (int k = 0; k < num_k; k++, it++) {
+                    int st = it % STAGES;
+                    uint32_t par = (it / STAGES) & 1;
+                    if (!mbar_wait(&s.full_tma[st], par, abort_flag)) {
+                        give_up(abort_flag, p.status, kErrWaitTma);
+                        goto mma_done;
+                    }
+                    if (!mbar_wait(&s.full_split[st], par, abort_flag)) {
+                        give_up(abort_flag, p.status, kErrWaitSplit);
+                        goto mma_done;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    uint64_t a_hi = umma_desc_k_major<BK>(smem_u32(s.a_hi[st])), a_lo = umma_desc_k_major<BK>(smem_u32(s.a_lo[st]));
+                    uint64_t b_hi = umma_desc_k_major<BK>(smem_u32(s.b_hi[st])), b_lo = umma_desc_k_major<BK>(smem_u32(s.b_lo[st]));
 #pragma unroll
-                for (int kk = 0; kk < BK / 8; kk++) {
-                    uint64_t adv = uint64_t((kk * 8 * 4) >> 4);  // 32 bytes per K-step inside the swizzle row
-                    umma_tf32(tmem_acc, a_lo + adv, b_hi + adv, kIdesc, (k > 0 || kk > 0) ? 1u : 0u);
-                    umma_tf32(tmem_acc, a_hi + adv, b_lo + adv, kIdesc, 1u);
-                    umma_tf32(tmem_acc, a_hi + adv, b_hi + adv, kIdesc, 1u);
+                    for (int kk = 0; kk < BK / 8; kk++) {
+                        uint64_t adv = uint64_t((kk * 8 * 4) >> 4);  // 32 bytes per K-step inside the swizzle row
+                        umma_tf32(tmem_acc, a_lo + adv, b_hi + adv, kIdesc, (k > 0 || kk > 0) ? 1u : 0u);
+                        umma_tf32(tmem_acc, a_hi + adv, b_lo + adv, kIdesc, 1u);
+                        umma_tf32(tmem_acc, a_hi + adv, b_hi + adv, kIdesc, 1u);
+                    }
+                    umma_commit(&s.empty[st]);  // arrives once the MMAs above have consumed the stage
                 }
-                umma_commit(&s.empty[st]);  // arrives once the MMAs above have consumed the stage
+                umma_commit(&s.acc_full[buf]);
             }
-            if (ok) umma_commit(&s.acc_full);
+        mma_done:;
         }
-    } else {
+    } else if (warp >= kSplitWarp0) {
         // ---------------- activation split (hi in place, lo into the twin buffer) ----------------
-        const int t = threadIdx.x - 64;  // 0..127
-        bool ok = true;
-        for (int k = 0; k < num_k; k++) {
-            int st = k % STAGES;
-            if (!mbar_wait(&s.full_tma[st], uint32_t((k / STAGES) & 1), abort_flag)) {
-                if (!*abort_flag) { *abort_flag = 1; if (p.status) atomicCAS(p.status, 0, kErrWaitTma); }
-                ok = false;
+        const int t = threadIdx.x - kSplitWarp0 * 32;  // 0..127
+        uint32_t it = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            for (int k = 0; k < num_k; k++, it++) {
+                int st = it % STAGES;
+                if (!mbar_wait(&s.full_tma[st], (it / STAGES) & 1, abort_flag)) {
+                    give_up(abort_flag, p.status, kErrWaitTma);
+                    goto split_done;
+                }
+                float4* hi = reinterpret_cast<float4*>(s.a_hi[st]);
+                float4* lo = reinterpret_cast<float4*>(s.a_lo[st]);
+#pragma unroll
+                for (int i = 0; i < (BM * BK / 4) / 128; i++) {
+                    float4 v = hi[t + i * 128], h, l;
+                    split_tf32(v.x, h.x, l.x);
+                    split_tf32(v.y, h.y, l.y);
+                    split_tf32(v.z, h.z, l.z);
+                    split_tf32(v.w, h.w, l.w);
+                    hi[t + i * 128] = h;
+                    lo[t + i * 128] = l;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA (async proxy)
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.full_split[st]);
+            }
+        }
+    split_done:;
+    } else {
+        // ---------------- epilogue (warps 0..3; warp w owns TMEM lanes 32w .. 32w+31) ----------------
+        const int q = warp - kEpiWarp0;
+        float* stage = s.stage_out[q];
+        uint32_t tcount = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tcount++) {
+            const uint32_t buf = tcount & 1;
+            int tm, tn;
+            tile_coords(p, tile, tm, tn);
+            if (!mbar_wait(&s.acc_full[buf], (tcount >> 1) & 1, abort_flag)) {
+                give_up(abort_flag, p.status, kErrWaitAcc);
                 break;
             }
-            float4* hi = reinterpret_cast<float4*>(s.a_hi[st]);
-            float4* lo = reinterpret_cast<float4*>(s.a_lo[st]);
-#pragma unroll
-            for (int i = 0; i < (BM * BK / 4) / 128; i++) {
-                float4 v = hi[t + i * 128], h, l;
-                split_tf32(v.x, h.x, l.x);
-                split_tf32(v.y, h.y, l.y);
-                split_tf32(v.z, h.z, l.z);
-                split_tf32(v.w, h.w, l.w);
-                hi[t + i * 128] = h;
-                lo[t + i * 128] = l;
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA (async proxy)
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s.full_split[st]);
-        }
-        // ---------------- epilogue ----------------
-        if (ok && num_k > 0) {
-            if (!mbar_wait(&s.acc_full, 0, abort_flag)) {
-                if (!*abort_flag) { *abort_flag = 1; if (p.status) atomicCAS(p.status, 0, kErrWaitAcc); }
-                ok = false;
-            }
-        }
-        if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int quarter = warp & 3;  // a warp may only touch TMEM lanes 32*(warp%4) .. +31
-            const int64_t row = int64_t(tile_m) * BM + quarter * 32 + lane;
-            const int64_t col0 = int64_t(tile_n) * BN;
+            const int64_t row0 = int64_t(tm) * BM + q * 32;
+            const int64_t col0 = int64_t(tn) * BN;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; c++) {
                 uint32_t r[32];
-                if (num_k > 0) {
-                    tmem_ld32(tmem_acc + (uint32_t(quarter * 32) << 16) + uint32_t(c * 32), r);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                tmem_ld32(tmem_base + buf * uint32_t(BN) + (uint32_t(q * 32) << 16) + uint32_t(c * 32), r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (c == BN / 32 - 1) {
+                    // the accumulator is in registers: hand the TMEM buffer back before storing
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
+                }
+                const int64_t col = col0 + c * 32;
+                if (col >= p.N) continue;  // warp-uniform
+                // thread `lane` holds row (row0 + lane), 32 consecutive columns: stage it row-major
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4*>(stage + lane * kStagePad + j) =
+                        make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                __syncwarp();
+                if (p.vec_out && col + 31 < p.N) {
+                    // 8 lanes cover one 128-byte row segment, 4 rows per instruction
+                    const int cq = (lane & 7) * 4, rsub = lane >> 3;
+                    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (p.bias) b4 = *reinterpret_cast<const float4*>(p.bias + col + cq);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        int rr = i * 4 + rsub;
+                        float4 v = *reinterpret_cast<const float4*>(stage + rr * kStagePad + cq);
+                        v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
+                        if (p.relu) {
+                            v.x = v.x > 0.f ? v.x : (v.x != v.x ? v.x : 0.f);
+                            v.y = v.y > 0.f ? v.y : (v.y != v.y ? v.y : 0.f);
+                            v.z = v.z > 0.f ? v.z : (v.z != v.z ? v.z : 0.f);
+                            v.w = v.w > 0.f ? v.w : (v.w != v.w ? v.w : 0.f);
+                        }
+                        if (row0 + rr < p.M) *reinterpret_cast<float4*>(p.out + (row0 + rr) * p.ldo + col + cq) = v;
+                    }
                 } else {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) r[j] = 0u;
-                }
-                int64_t col = col0 + c * 32;
-                if (row < p.M && col < p.N) {
-                    float v[32];
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        float x = __uint_as_float(r[j]);
-                        if (p.bias != nullptr && col + j < p.N) x += __ldg(p.bias + col + j);
-                        if (p.relu) x = x > 0.f ? x : (x != x ? x : 0.f);
-                        v[j] = x;
-                    }
-                    float* dst = p.out + row * p.ldo + col;
-                    if (p.vec_out && col + 31 < p.N) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (col + j < p.N) dst[j] = v[j];
+                    // one row per instruction, lanes on consecutive columns
+                    const bool col_ok = col + lane < p.N;
+                    const float b = (p.bias && col_ok) ? __ldg(p.bias + col + lane) : 0.f;
+#pragma unroll 4
+                    for (int rr = 0; rr < 32; rr++) {
+                        float v = stage[rr * kStagePad + lane] + b;
+                        if (p.relu) v = v > 0.f ? v : (v != v ? v : 0.f);
+                        if (col_ok && row0 + rr < p.M) p.out[(row0 + rr) * p.ldo + col + lane] = v;
                     }
                 }
+                __syncwarp();
             }
         }
     }
     // ---------------- teardown (every thread arrives here, whatever happened above) ----------------
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 1) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(uint32_t(BN)) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
 }
 
@@ -346,43 +420,49 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// 2-D fp32 row-major [rows, cols] with row pitch `ld` floats; box = [box_rows, 32 floats], 128-byte swizzle.
-int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+// 2-D fp32 row-major [rows, cols] with row pitch `ld` floats; box = [box_rows, bk floats], rows one swizzle span wide.
+int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, int bk) {
     EncodeTiledFn fn = encode_tiled_fn();
     FXF_CHECK(fn != nullptr, "cuTensorMapEncodeTiled is not available from the CUDA driver");
     cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
     cuuint64_t strides[1] = {cuuint64_t(ld) * sizeof(float)};
-    cuuint32_t box[2] = {cuuint32_t(BK), cuuint32_t(box_rows)};
+    cuuint32_t box[2] = {cuuint32_t(bk), cuuint32_t(box_rows)};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     FXF_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d (rows %lld cols %lld ld %lld)", int(r), (long long)rows, (long long)cols, (long long)ld);
     return 0;
 }
 
-template <int BN, int STAGES>
+template <int BN, int BK, int STAGES>
 int launch_tc(const GemmArgs& a, ExecCtx& ctx) {
     CUtensorMap mx, mhi, mlo;
-    if (make_map(&mx, a.x, a.M, a.K, a.ldx, BM)) return 1;
-    if (make_map(&mhi, a.w_hi, a.N, a.K, a.K, BN)) return 1;
-    if (make_map(&mlo, a.w_lo, a.N, a.K, a.K, BN)) return 1;
+    if (make_map(&mx, a.x, a.M, a.K, a.ldx, BM, BK)) return 1;
+    if (make_map(&mhi, a.w_hi, a.N, a.K, a.K, BN, BK)) return 1;
+    if (make_map(&mlo, a.w_lo, a.N, a.K, a.K, BN, BK)) return 1;
     TcParams p;
     p.bias = a.bias; p.out = a.out; p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo;
     p.relu = a.relu ? 1 : 0;
-    p.vec_out = (a.ldo % 4 == 0 && aligned16(a.out)) ? 1 : 0;
+    p.vec_out = (a.ldo % 4 == 0 && aligned16(a.out) && (a.bias == nullptr || aligned16(a.bias))) ? 1 : 0;
+    p.tiles_m = int((a.M + BM - 1) / BM);
+    p.tiles_n = int((a.N + BN - 1) / BN);
+    // walk tiles so that the operand that does not fit in L2 is the one reused by concurrent CTAs
+    p.m_fastest = a.N > a.M ? 1 : 0;
     p.status = ctx.status;
-    size_t smem = sizeof(TcSmem<BN, STAGES>) + 1024;
+    size_t smem = sizeof(TcSmem<BN, BK, STAGES>) + 1024;
     static bool configured[64] = {};
     int dev = 0;
     FXF_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        FXF_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        FXF_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, BK, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    dim3 grid(unsigned((a.N + BN - 1) / BN), unsigned((a.M + BM - 1) / BM));
+    int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
+    int grid = int(tiles < ctx.sm_count ? tiles : ctx.sm_count);
     tag_launch(ctx, BN == 256 ? "gemm_tf32x3_tcgen05_128x256" : "gemm_tf32x3_tcgen05_128x128", 2.0 * double(a.M) * double(a.N) * double(a.K),
                4.0 * (double(a.M) * a.K + double(a.N) * a.K + double(a.N) + double(a.M) * a.N));
-    gemm_tf32x3_kernel<BN, STAGES><<<grid, kThreads, smem, ctx.stream>>>(mx, mhi, mlo, p);
+    gemm_tf32x3_kernel<BN, BK, STAGES><<<grid, kThreads, smem, ctx.stream>>>(mx, mhi, mlo, p);
     FXF_LAUNCHED(ctx);
     return 0;
 }
@@ -406,8 +486,14 @@ bool gemm_tc_shape_ok(int64_t M, int64_t N, int64_t K) {
 
 int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx) {
     FXF_CHECK(gemm_tc_supported(a), "tensor-core GEMM called with an unsupported problem");
-    if (a.N > 128) return launch_tc<256, 2>(a, ctx);
-    return launch_tc<128, 3>(a, ctx);
+    // Debug override of the ring geometry for wide tiles: FXF_TC_RING=0 -> 2 slabs of 32 floats,
+    // FXF_TC_RING=1 (default) -> 4 slabs of 16 floats.  Same shared-memory footprint.
+    static const int ring = [] {
+        const char* e = std::getenv("FXF_TC_RING");
+        return e ? std::atoi(e) : 1;
+    }();
+    if (a.N > 128) return ring == 0 ? launch_tc<256, 32, 2>(a, ctx) : launch_tc<256, 16, 4>(a, ctx);
+    return launch_tc<128, 32, 3>(a, ctx);
 }
 
 int launch_split_tf32(const float* w, float* hi, float* lo, int64_t n, ExecCtx& ctx) {
