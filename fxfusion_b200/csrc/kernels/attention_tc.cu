@@ -1,0 +1,455 @@
+// Tensor-core attention core for head_dim 64 on sm_100a:
+//     ctx = softmax(mask_fill(Q·K^T / scale_divisor)) · V        per (batch, head)
+// with both contractions on tcgen05 (kind::tf32, three products per logical product, fp32-grade).
+// Same semantics as attention.cu (reference csrc/kernels/cpu/mha.cpp:38-49): division by the scale,
+// -inf where mask == 0, fully masked rows give NaN, masked keys still enter P·V with weight 0, no key
+// tile is skipped.
+//
+// Two kernels:
+//   attn_vt_kernel   transposes the V third of the packed projection qkv[B*T, 3D] into V^T [B*H, 64, T]
+//                    (keys contiguous) so that the B operand of P·V is K-major.
+//   attn_tc_kernel   one CTA per (128 queries, b, h), 384 threads.  TMEM columns:
+//                    S [128x128] | P_hi [128x128] | P_lo [128x128] | O [128x64].
+//       warp 0, lane 0  TMA loads (Q and K tiles straight out of qkv through a 3-D tensor map, V^T
+//                       tiles from the transposed copy; zero fill beyond T) and all MMAs:
+//                       S = Q·K_blk^T with both operands in shared memory, O_blk = P·V_blk with P read
+//                       from TMEM.
+//       warps 4-11      (a) split every landed tile into TF32 hi (in place) and lo (twin buffer);
+//                       (b) softmax, two threads per query row, each owning 64 of the block's 128 keys
+//                       and 32 of the 64 output columns: tcgen05.ld of S, scale, mask (staged through
+//                       shared memory so the global reads are coalesced), online softmax in the log2
+//                       domain (running max m, running sum l), P split into hi/lo and stored to TMEM;
+//                       after the P·V MMA the block's O is folded into registers (o = o*alpha + O_blk).
+// Waits are bounded; on expiry the CTA records an error code in the status word and leaves.
+#include <cmath>
+
+#include "../runtime.hpp"
+#include "sm100.cuh"
+
+namespace fxf {
+namespace {
+
+using namespace sm100;
+
+constexpr int HD = 64, BQ = 128, BKEY = 128;
+constexpr int kAttnThreads = 384;
+constexpr int kSoftWarp0 = 4;            // warps 4..11: TMEM lane quarter = warp % 4, key half = (warp - 4) / 4
+constexpr int kMaskPitch = 144;          // bytes per staged mask row (128 + 16): 16-byte reads stay conflict-free
+constexpr float kLog2e = 1.4426950408889634f;
+enum : int { kErrAttnQ = 111, kErrAttnK = 112, kErrAttnV = 113, kErrAttnS = 114, kErrAttnP = 115, kErrAttnO = 116, kErrAttnSplit = 117 };
+
+// 2^x on the special-function unit: 2^-inf = 0, NaN stays NaN (the row-poisoning rules rely on both).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// Barrier among the 256 softmax threads only (id 1; id 0 is __syncthreads).
+__device__ __forceinline__ void soft_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// ---- V transpose -------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) attn_vt_kernel(const float* __restrict__ qkv, int64_t ld, int64_t v_off, int T, int H, float* __restrict__ vt) {
+    __shared__ float tile[HD][33];
+    const int bh = blockIdx.y, b = bh / H, h = bh % H, t0 = blockIdx.x * 32, tid = threadIdx.x;
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        int f = tid + i * 256, r = f >> 4, c4 = (f & 15) * 4, t = t0 + r;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t < T) v = *reinterpret_cast<const float4*>(qkv + (int64_t(b) * T + t) * ld + v_off + int64_t(h) * HD + c4);
+        tile[c4 + 0][r] = v.x; tile[c4 + 1][r] = v.y; tile[c4 + 2][r] = v.z; tile[c4 + 3][r] = v.w;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < HD * 32; idx += 256) {
+        int d = idx >> 5, tt = idx & 31, t = t0 + tt;
+        if (t < T) vt[(int64_t(bh) * HD + d) * T + t] = tile[d][tt];
+    }
+}
+
+// ---- main kernel -------------------------------------------------------------------------------------
+struct alignas(1024) AttnTcSmem {
+    float q_hi[2][BQ * 32], q_lo[2][BQ * 32];      // two 32-wide slabs of head_dim
+    float k_hi[2][BKEY * 32], k_lo[2][BKEY * 32];
+    float v_hi[4][HD * 32], v_lo[4][HD * 32];      // four 32-key slabs of V^T [64 x 32]
+    unsigned char mask_rows[BQ * kMaskPitch];      // this block's mask bytes, one padded row per query
+    float exch[2][BQ];                             // row statistics exchanged between the two threads of a row
+    uint64_t bar_q, bar_k, bar_v, bar_qs, bar_ks, bar_vs, bar_s, bar_p, bar_o;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+struct AttnTcParams {
+    const uint8_t* mask;
+    float* ctx;
+    int B, T, H;
+    int q_col, k_col;     // first column of the Q / K thirds inside a qkv row
+    int64_t ld_ctx;
+    int64_t mask_sb, mask_sh, mask_sq, mask_sk;
+    float scale_divisor;
+    float inv_scale;      // 1 / scale_divisor, used only when that is exact
+    int scale_is_pow2;
+    int mask_vec16;       // mask rows may be fetched as aligned 16-byte words
+    int* status;
+};
+
+// hi in place, lo into the twin buffer, for `n4` float4s, by the 256 softmax threads
+__device__ __forceinline__ void split_tile(float* hi_buf, float* lo_buf, int n4, int t) {
+    float4* hi = reinterpret_cast<float4*>(hi_buf);
+    float4* lo = reinterpret_cast<float4*>(lo_buf);
+    for (int i = t; i < n4; i += 256) {
+        float4 v = hi[i], h, l;
+        split_tf32(v.x, h.x, l.x);
+        split_tf32(v.y, h.y, l.y);
+        split_tf32(v.z, h.z, l.z);
+        split_tf32(v.w, h.w, l.w);
+        hi[i] = h;
+        lo[i] = l;
+    }
+}
+
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_vt,
+               AttnTcParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    AttnTcSmem& s = *reinterpret_cast<AttnTcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H, q0 = blockIdx.x * BQ, T = p.T;
+    const int nblk = (T + BKEY - 1) / BKEY;
+    volatile int* abort_flag = &s.abort_flag;
+    constexpr uint32_t kQBytes = BQ * HD * 4, kKBytes = BKEY * HD * 4, kVBytes = HD * BKEY * 4;
+    constexpr uint32_t kColS = 0, kColPhi = 128, kColPlo = 256, kColO = 384;
+    constexpr uint32_t kIdescS = umma_idesc_tf32(BQ, BKEY), kIdescO = umma_idesc_tf32(BQ, HD);
+
+    if (threadIdx.x == 0) {
+        mbar_init(&s.bar_q, 1);
+        mbar_init(&s.bar_k, 1);
+        mbar_init(&s.bar_v, 1);
+        mbar_init(&s.bar_qs, 8);    // one arrival per softmax warp
+        mbar_init(&s.bar_ks, 8);
+        mbar_init(&s.bar_vs, 8);
+        mbar_init(&s.bar_s, 1);
+        mbar_init(&s.bar_p, 8);
+        mbar_init(&s.bar_o, 1);
+        s.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s.tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s.tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            auto load_k = [&](int blk) {
+                mbar_expect_tx(&s.bar_k, kKBytes);
+                for (int sl = 0; sl < 2; sl++) tma_load_3d(s.k_hi[sl], &map_k, p.k_col + h * HD + sl * 32, blk * BKEY, b, &s.bar_k);
+            };
+            auto load_v = [&](int blk) {
+                mbar_expect_tx(&s.bar_v, kVBytes);
+                for (int ks = 0; ks < 4; ks++) tma_load_3d(s.v_hi[ks], &map_vt, blk * BKEY + ks * 32, 0, bh, &s.bar_v);
+            };
+            mbar_expect_tx(&s.bar_q, kQBytes);
+            for (int sl = 0; sl < 2; sl++) tma_load_3d(s.q_hi[sl], &map_qkv, p.q_col + h * HD + sl * 32, q0, b, &s.bar_q);
+            load_k(0);
+            load_v(0);
+            if (!mbar_wait(&s.bar_qs, 0, abort_flag)) {
+                give_up(abort_flag, p.status, kErrAttnQ);
+            } else {
+                for (int blk = 0; blk < nblk; blk++) {
+                    const uint32_t par = blk & 1;
+                    if (!mbar_wait(&s.bar_ks, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnK); break; }
+                    tc_fence_after();
+                    // S = Q · K_blk^T
+#pragma unroll
+                    for (int sl = 0; sl < 2; sl++) {
+                        uint64_t qh = umma_desc_k_major<32>(smem_u32(s.q_hi[sl])), ql = umma_desc_k_major<32>(smem_u32(s.q_lo[sl]));
+                        uint64_t kh = umma_desc_k_major<32>(smem_u32(s.k_hi[sl])), kl = umma_desc_k_major<32>(smem_u32(s.k_lo[sl]));
+#pragma unroll
+                        for (int kk = 0; kk < 4; kk++) {
+                            uint64_t adv = uint64_t((kk * 32) >> 4);
+                            umma_tf32(tmem + kColS, ql + adv, kh + adv, kIdescS, (sl > 0 || kk > 0) ? 1u : 0u);
+                            umma_tf32(tmem + kColS, qh + adv, kl + adv, kIdescS, 1u);
+                            umma_tf32(tmem + kColS, qh + adv, kh + adv, kIdescS, 1u);
+                        }
+                    }
+                    umma_commit(&s.bar_s);
+                    if (blk + 1 < nblk) {  // K buffer is free once the S MMAs have completed
+                        if (!mbar_wait(&s.bar_s, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnS); break; }
+                        load_k(blk + 1);
+                    }
+                    if (!mbar_wait(&s.bar_vs, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnV); break; }
+                    if (!mbar_wait(&s.bar_p, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnP); break; }
+                    tc_fence_after();
+                    // O_blk = P · V_blk   (A = P from TMEM, B = V^T slabs, K-major over keys)
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) {
+                        uint64_t vh = umma_desc_k_major<32>(smem_u32(s.v_hi[ks])), vl = umma_desc_k_major<32>(smem_u32(s.v_lo[ks]));
+#pragma unroll
+                        for (int kk = 0; kk < 4; kk++) {
+                            uint64_t adv = uint64_t((kk * 32) >> 4);
+                            uint32_t pc = uint32_t(ks * 32 + kk * 8);
+                            umma_tf32_ts(tmem + kColO, tmem + kColPlo + pc, vh + adv, kIdescO, (ks > 0 || kk > 0) ? 1u : 0u);
+                            umma_tf32_ts(tmem + kColO, tmem + kColPhi + pc, vl + adv, kIdescO, 1u);
+                            umma_tf32_ts(tmem + kColO, tmem + kColPhi + pc, vh + adv, kIdescO, 1u);
+                        }
+                    }
+                    umma_commit(&s.bar_o);
+                    if (blk + 1 < nblk) {  // V buffer is free once the P·V MMAs have completed
+                        if (!mbar_wait(&s.bar_o, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnO); break; }
+                        load_v(blk + 1);
+                    }
+                }
+            }
+        }
+    } else if (warp >= kSoftWarp0) {
+        // ---------------- split + softmax: two threads per query row ----------------
+        const int sw = warp - kSoftWarp0;          // 0..7
+        const int quarter = sw & 3, half = sw >> 2;
+        const int st = threadIdx.x - kSoftWarp0 * 32;  // 0..255
+        const int row = quarter * 32 + lane, qi = q0 + row;
+        const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+        const bool row_ok = qi < T;
+        const uint8_t* mhead = p.mask + int64_t(b) * p.mask_sb + int64_t(h) * p.mask_sh;
+        float o[32];
+#pragma unroll
+        for (int j = 0; j < 32; j++) o[j] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool alive = true;   // a thread that gave up keeps walking the loop so that soft_sync() stays matched
+
+        // Q split (once)
+        if (alive && !mbar_wait(&s.bar_q, 0, abort_flag)) { give_up(abort_flag, p.status, kErrAttnQ); alive = false; }
+        if (alive) {
+            split_tile(s.q_hi[0], s.q_lo[0], 2 * BQ * 32 / 4, st);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s.bar_qs);
+        }
+        for (int blk = 0; blk < nblk; blk++) {
+            const uint32_t par = blk & 1;
+            // ---- split K and V of this block as they land ----
+            if (alive && !mbar_wait(&s.bar_k, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnK); alive = false; }
+            if (alive) {
+                split_tile(s.k_hi[0], s.k_lo[0], 2 * BKEY * 32 / 4, st);
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.bar_ks);
+            }
+            if (alive && !mbar_wait(&s.bar_v, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnV); alive = false; }
+            if (alive) {
+                split_tile(s.v_hi[0], s.v_lo[0], 4 * HD * 32 / 4, st);
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.bar_vs);
+            }
+            // ---- stage this warp's share of the mask: rows of its quarter, the 64 keys of its half ----
+            const int key0 = blk * BKEY + half * 64;
+            if (p.mask_vec16) {
+#pragma unroll
+                for (int it = 0; it < 4; it++) {
+                    int rr = quarter * 32 + it * 8 + (lane >> 2), kq = key0 + (lane & 3) * 16, qq = q0 + rr;
+                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                    if (qq < T && kq < T) v = *reinterpret_cast<const uint4*>(mhead + int64_t(qq) * p.mask_sq + kq);
+                    *reinterpret_cast<uint4*>(s.mask_rows + rr * kMaskPitch + half * 64 + (lane & 3) * 16) = v;
+                }
+            } else {
+                for (int idx = lane; idx < 32 * 64; idx += 32) {
+                    int rr = quarter * 32 + (idx >> 6), kc = key0 + (idx & 63), qq = q0 + rr;
+                    unsigned char v = 0;
+                    if (qq < T && kc < T) v = mhead[int64_t(qq) * p.mask_sq + int64_t(kc) * p.mask_sk];
+                    s.mask_rows[rr * kMaskPitch + half * 64 + (idx & 63)] = v;
+                }
+            }
+            __syncwarp();
+            uint32_t keep[2];
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                uint32_t bits = 0;
+                const uint4* mp = reinterpret_cast<const uint4*>(s.mask_rows + row * kMaskPitch + half * 64 + c * 32);
+#pragma unroll
+                for (int w = 0; w < 2; w++) {
+                    uint4 m16 = mp[w];
+                    uint32_t words[4] = {m16.x, m16.y, m16.z, m16.w};
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        // 0x01 per non-zero byte, gathered into 4 bits by one multiply
+                        uint32_t nz = __vcmpne4(words[k], 0u) & 0x01010101u;
+                        bits |= ((nz * 0x01020408u) >> 24 & 0xFu) << (16 * w + 4 * k);
+                    }
+                }
+                keep[c] = bits;
+            }
+            __syncwarp();
+            // ---- pass 1: scale, mask, log2 domain, partial row maximum; processed scores go back to TMEM ----
+            if (alive && !mbar_wait(&s.bar_s, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnS); alive = false; }
+            float tmax = -INFINITY;
+            if (alive) {
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    uint32_t r[32];
+                    const uint32_t col = uint32_t(half * 64 + c * 32);
+                    tmem_ld32(tmem + kColS + lane_base + col, r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        float v = __uint_as_float(r[j]);
+                        v = p.scale_is_pow2 ? v * p.inv_scale : v / p.scale_divisor;   // identical rounding for a power of two
+                        v = ((keep[c] >> j) & 1u) ? v * kLog2e : -INFINITY;
+                        tmax = fmaxf(tmax, v);  // NaN scores do not move the max; they reach the sum below
+                        r[j] = __float_as_uint(v);
+                    }
+                    tmem_st32(tmem + kColS + lane_base + col, r);
+                }
+                tmem_wait_st();
+            }
+            s.exch[half][row] = tmax;
+            soft_sync();
+            const float m_new = fmaxf(m_run, fmaxf(tmax, s.exch[half ^ 1][row]));
+            const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+            const float alpha = fast_exp2(m_run - m_safe);
+            // ---- pass 2: probabilities, their partial sum, hi/lo halves into TMEM ----
+            float psum = 0.f;
+            if (alive) {
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    uint32_t r[32], lo[32];
+                    const uint32_t col = uint32_t(half * 64 + c * 32);
+                    tmem_ld32(tmem + kColS + lane_base + col, r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        float pv = fast_exp2(__uint_as_float(r[j]) - m_safe);
+                        psum += pv;
+                        float ph, pl;
+                        split_tf32(pv, ph, pl);
+                        r[j] = __float_as_uint(ph);
+                        lo[j] = __float_as_uint(pl);
+                    }
+                    tmem_st32(tmem + kColPhi + lane_base + col, r);
+                    tmem_st32(tmem + kColPlo + lane_base + col, lo);
+                }
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.bar_p);
+            }
+            l_run = l_run * alpha + psum;   // this thread's share of the row sum; the two shares are added at the end
+            m_run = m_new;
+#pragma unroll
+            for (int j = 0; j < 32; j++) o[j] *= alpha;
+            if (alive && !mbar_wait(&s.bar_o, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnO); alive = false; }
+            if (alive) {
+                tc_fence_after();
+                uint32_t r[32];
+                tmem_ld32(tmem + kColO + lane_base + uint32_t(half * 32), r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; j++) o[j] += __uint_as_float(r[j]);
+                tc_fence_before();
+            }
+            soft_sync();   // exch[] is reused by the next block (and by the final sum exchange)
+        }
+        s.exch[half][row] = l_run;
+        soft_sync();
+        const float l_tot = s.exch[0][row] + s.exch[1][row];
+        if (alive && row_ok) {
+            // 0/0 = NaN for a fully masked row, as the reference softmax gives
+            float* dst = p.ctx + (int64_t(b) * T + qi) * p.ld_ctx + int64_t(h) * HD + half * 32;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(dst + j) = make_float4(o[j] / l_tot, o[j + 1] / l_tot, o[j + 2] / l_tot, o[j + 3] / l_tot);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            return reinterpret_cast<EncodeTiledFn>(p);
+        return EncodeTiledFn(nullptr);
+    }();
+    return fn;
+}
+// fp32 tensor seen as [n2, n1, n0] with n0 contiguous and byte strides s1 (dim 1), s2 (dim 2);
+// box [1, box1, 32 floats], 128-byte swizzle, zero fill outside.
+int make_map3(CUtensorMap* map, const float* base, int64_t n0, int64_t n1, int64_t n2, int64_t s1, int64_t s2, int box1) {
+    EncodeTiledFn fn = encode_fn();
+    FXF_CHECK(fn != nullptr, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+    cuuint64_t dims[3] = {cuuint64_t(n0), cuuint64_t(n1), cuuint64_t(n2)};
+    cuuint64_t strides[2] = {cuuint64_t(s1), cuuint64_t(s2)};
+    cuuint32_t box[3] = {32, cuuint32_t(box1), 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    FXF_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (attention) failed with code %d", int(r));
+    return 0;
+}
+
+}  // namespace
+
+bool attention_tc_supported(const AttnArgs& a, int gemm_mode) {
+    if (gemm_mode == FXF_GEMM_FP32_SIMT) return false;
+    if (a.hd != HD || a.T % 4 != 0 || a.T < 16) return false;
+    if (a.ld_qkv % 4 != 0 || a.ld_ctx % 4 != 0 || (a.q_off | a.k_off | a.v_off) % 4 != 0) return false;
+    if (!aligned16(a.qkv) || !aligned16(a.ctx)) return false;
+    return true;
+}
+
+size_t attention_tc_scratch_bytes(int64_t B, int64_t T, int64_t H) { return size_t(B) * size_t(T) * size_t(H) * HD * sizeof(float); }
+
+int launch_attention_tc(const AttnArgs& a, float* vt_scratch, ExecCtx& ctx) {
+    FXF_CHECK(vt_scratch != nullptr && aligned16(vt_scratch), "attention: tensor-core path needs its V^T buffer");
+    const int64_t BH = int64_t(a.B) * a.H;
+    dim3 pgrid(unsigned((a.T + 31) / 32), unsigned(BH));
+    tag_launch(ctx, "attention_v_transpose", 0, 8.0 * double(BH) * a.T * HD);
+    attn_vt_kernel<<<pgrid, 256, 0, ctx.stream>>>(a.qkv, a.ld_qkv, a.v_off, a.T, a.H, vt_scratch);
+    FXF_LAUNCHED(ctx);
+
+    CUtensorMap mq, mk, mv;
+    // Q and K tiles come straight out of the packed projection: [B, T, ld] with the row pitch of qkv
+    if (make_map3(&mq, a.qkv, a.ld_qkv, a.T, a.B, a.ld_qkv * 4, int64_t(a.T) * a.ld_qkv * 4, BQ)) return 1;
+    if (make_map3(&mk, a.qkv, a.ld_qkv, a.T, a.B, a.ld_qkv * 4, int64_t(a.T) * a.ld_qkv * 4, BKEY)) return 1;
+    if (make_map3(&mv, vt_scratch, a.T, HD, BH, int64_t(a.T) * 4, int64_t(a.T) * HD * 4, HD)) return 1;
+    AttnTcParams p;
+    p.mask = a.mask; p.ctx = a.ctx; p.B = a.B; p.T = a.T; p.H = a.H; p.ld_ctx = a.ld_ctx;
+    p.q_col = int(a.q_off); p.k_col = int(a.k_off);
+    p.mask_sb = a.mask_sb; p.mask_sh = a.mask_sh; p.mask_sq = a.mask_sq; p.mask_sk = a.mask_sk;
+    p.scale_divisor = a.scale_divisor;
+    {
+        int e = 0;
+        float m = std::frexp(a.scale_divisor, &e);
+        p.scale_is_pow2 = (m == 0.5f && a.scale_divisor > 0.f && std::isfinite(a.scale_divisor)) ? 1 : 0;
+        p.inv_scale = p.scale_is_pow2 ? 1.0f / a.scale_divisor : 0.f;
+    }
+    p.mask_vec16 = (a.mask_sk == 1 && a.T % 16 == 0 && a.mask_sb % 16 == 0 && a.mask_sh % 16 == 0 && a.mask_sq % 16 == 0 && aligned16(a.mask)) ? 1 : 0;
+    p.status = ctx.status;
+    size_t smem = sizeof(AttnTcSmem) + 1024;
+    static bool configured[64] = {};
+    int dev = 0;
+    FXF_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        FXF_CUDA(cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    dim3 grid(unsigned((a.T + BQ - 1) / BQ), unsigned(BH));
+    tag_launch(ctx, "attention_tf32x3_tcgen05", 4.0 * double(a.B) * a.H * double(a.T) * a.T * a.hd,
+               4.0 * 4.0 * double(a.B) * a.T * double(a.H) * a.hd + double(a.B) * a.T * a.T);
+    attn_tc_kernel<<<grid, kAttnThreads, smem, ctx.stream>>>(mq, mk, mv, p);
+    FXF_LAUNCHED(ctx);
+    return 0;
+}
+
+}  // namespace fxf

@@ -35,120 +35,18 @@
 #include <mutex>
 
 #include "../runtime.hpp"
+#include "sm100.cuh"
 
 namespace fxf {
 namespace {
 
+using namespace sm100;
+
 constexpr int BM = 128;
 constexpr int kThreads = 320;
 constexpr int kEpiWarp0 = 0, kTmaWarp = 4, kMmaWarp = 5, kSplitWarp0 = 6;
-constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s per wait
 
 enum : int { kErrWaitTma = 101, kErrWaitSplit = 102, kErrWaitEmpty = 103, kErrWaitAcc = 104, kErrWaitAccEmpty = 105 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait.  Returns false when the budget ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
-    unsigned long long t0 = global_ns();
-    for (uint32_t spin = 1;; spin++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 255u) == 0) {
-            if (*abort_flag) return false;
-            if (global_ns() - t0 > kWaitBudgetNs) return false;
-        }
-    }
-}
-// Records why a role gave up (first reason wins) and tells the other roles to stop.
-__device__ __forceinline__ void give_up(volatile int* abort_flag, int* status, int code) {
-    if (!*abort_flag) {
-        *abort_flag = 1;
-        if (status) atomicCAS(status, 0, code);
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
-                 : "memory");
-}
-
-// K-major operand tile whose rows are one swizzle span wide (BK floats = 128 or 64 bytes):
-// rows `row_bytes` apart, 8-row groups 8*row_bytes apart.
-template <int BK>
-__device__ __forceinline__ uint64_t umma_desc_k_major(uint32_t smem_addr) {
-    constexpr uint32_t row_bytes = BK * 4;
-    constexpr uint64_t layout = row_bytes == 128 ? 2 : 4;  // SWIZZLE_128B : SWIZZLE_64B
-    uint64_t d = 0;
-    d |= uint64_t((smem_addr & 0x3FFFF) >> 4);    // start address, 16-byte units
-    d |= uint64_t(1) << 16;                       // leading byte offset (unused for swizzled K-major)
-    d |= uint64_t((8 * row_bytes) >> 4) << 32;    // stride byte offset between 8-row groups
-    d |= uint64_t(1) << 46;                       // descriptor version for sm_100
-    d |= layout << 61;
-    return d;
-}
-// kind::tf32, fp32 accumulate, A and B K-major, M x N tile.
-__host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n) {
-    return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
-}
-__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-}
-
-__device__ __forceinline__ uint32_t to_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return r;
-}
-__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
-    hi = __uint_as_float(to_tf32(x));
-    lo = __uint_as_float(to_tf32(x - hi));
-}
 
 constexpr int kStagePad = 36;  // floats per staged epilogue row: 32 + 4 keeps float4 rows conflict-free
 

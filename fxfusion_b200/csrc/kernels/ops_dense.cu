@@ -224,6 +224,8 @@ int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params
     FXF_CHECK(ctx.scratch_bytes >= need && (need == 0 || ctx.scratch != nullptr), "mha: scratch too small (%zu < %zu bytes)", ctx.scratch_bytes, need);
     float* qkv = static_cast<float*>(ctx.scratch);
     float* cx = qkv + d.M * d.QKV;
+    float* split = cx + d.M * d.D;  // only present when the plan reserved it
+    const bool have_split = ctx.scratch_bytes >= need + attention_tc_scratch_bytes(d.B, d.T, d.H);
 
     GemmArgs g;
     g.x = static_cast<const float*>(x.ptr); g.w = static_cast<const float*>(wq.ptr); g.bias = static_cast<const float*>(bq.ptr);
@@ -237,7 +239,11 @@ int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params
     a.ld_qkv = d.QKV; a.q_off = 0; a.k_off = d.D; a.v_off = 2 * d.D; a.ld_ctx = d.D;
     a.mask_sb = ms[0]; a.mask_sh = ms[1]; a.mask_sq = ms[2]; a.mask_sk = ms[3];
     a.scale_divisor = p.floats[0];
-    if (launch_attention(a, ctx)) return 1;
+    if (have_split && attention_tc_supported(a, ctx.gemm_mode)) {
+        if (launch_attention_tc(a, split, ctx)) return 1;
+    } else {
+        if (launch_attention(a, ctx)) return 1;
+    }
 
     GemmArgs g2;
     g2.x = cx; g2.w = static_cast<const float*>(wo.ptr); g2.bias = static_cast<const float*>(bo.ptr);
@@ -252,11 +258,13 @@ std::unique_ptr<NodePlan> plan_mha(const Registry& reg, const TensorIds& in, con
         const FxfTensor& x = reg[in[0]];
         int64_t B = x.shape[0], T = x.shape[1], H = p.ints[0], hd = p.ints[1], D = p.ints[2], QKV = p.ints[3], M = B * T;
         pl->scratch_bytes = size_t(M) * size_t(QKV + D) * sizeof(float);
+        const bool tc_attn = gemm_mode != FXF_GEMM_FP32_SIMT && hd == 64 && T % 4 == 0 && T >= 16 && D % 4 == 0;
+        if (tc_attn) pl->scratch_bytes += attention_tc_scratch_bytes(B, T, H);
         pl->flops = 2.0 * M * double(QKV) * D + 4.0 * double(B) * H * double(T) * T * hd + 2.0 * double(M) * D * D;
         pl->bytes = 4.0 * (2.0 * double(M) * D + double(QKV) * D + QKV + double(D) * D + D) + double(reg[in[1]].nbytes);
         GemmArgs g1; g1.M = M; g1.N = QKV; g1.K = D; g1.ldx = D; g1.ldw = D; g1.ldo = QKV;
         GemmArgs g2; g2.M = M; g2.N = D; g2.K = D; g2.ldx = D; g2.ldw = D; g2.ldo = D;
-        pl->variant = gemm_variant_name(g1, gemm_mode, 148) + "+flash-fp32+" + gemm_variant_name(g2, gemm_mode, 148);
+        pl->variant = gemm_variant_name(g1, gemm_mode, 148) + (tc_attn ? "+attn-tcgen05-tf32x3+" : "+flash-fp32+") + gemm_variant_name(g2, gemm_mode, 148);
         pl->want_split(2, QKV, D, M, gemm_mode);
         pl->want_split(4, D, D, M, gemm_mode);
     }

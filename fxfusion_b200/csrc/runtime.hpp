@@ -193,5 +193,9 @@ struct AttnArgs {
     float scale_divisor = 1.f;
 };
 int launch_attention(const AttnArgs& a, ExecCtx& ctx);
+// tcgen05 path (head_dim 64): needs 6*B*T*H*64 floats of scratch for the split, per-head operand copies
+bool attention_tc_supported(const AttnArgs& a, int gemm_mode);
+size_t attention_tc_scratch_bytes(int64_t B, int64_t T, int64_t H);
+int launch_attention_tc(const AttnArgs& a, float* split_scratch, ExecCtx& ctx);
 
 }  // namespace fxf

@@ -62,15 +62,19 @@ def _mha_reg(B, T, H, hd, mask):
             rnd(D, D, seed=3, scale=1 / math.sqrt(D)), rnd(D, seed=4, scale=0.1), torch.zeros(B, T, D)]
 
 
-@pytest.mark.parametrize("B,T,H,hd", [(2, 6, 4, 8), (1, 5, 2, 16), (2, 64, 4, 64), (1, 65, 2, 64), (3, 130, 3, 32), (1, 8, 1, 128), (2, 33, 2, 20)])
-def test_mha_causal(built_lib, B, T, H, hd):
+@pytest.mark.parametrize("precision", ["auto", "fp32_simt"])
+@pytest.mark.parametrize("B,T,H,hd", [(2, 6, 4, 8), (1, 5, 2, 16), (2, 64, 4, 64), (1, 65, 2, 64), (3, 130, 3, 32), (1, 8, 1, 128), (2, 33, 2, 20),
+                                      (1, 128, 1, 64), (1, 256, 2, 64), (2, 72, 2, 64), (1, 200, 3, 64), (3, 16, 1, 64), (2, 384, 2, 64)])
+def test_mha_causal(built_lib, B, T, H, hd, precision):
+    """head_dim 64 with T % 4 == 0 takes the tcgen05 attention kernel in "auto" mode, everything else the fp32 one."""
     mask = torch.tril(torch.ones(T, T, dtype=torch.bool)).view(1, 1, T, T).expand(B, 1, T, T).contiguous()
-    both("MHA", _mha_reg(B, T, H, hd, mask), [0, 1, 2, 3, 4, 5], [6], ints=[H, hd, H * hd, 3 * H * hd], floats=[math.sqrt(hd)])
+    both("MHA", _mha_reg(B, T, H, hd, mask), [0, 1, 2, 3, 4, 5], [6], ints=[H, hd, H * hd, 3 * H * hd], floats=[math.sqrt(hd)], precision=precision)
 
 
+@pytest.mark.parametrize("hd", [16, 64])
 @pytest.mark.parametrize("shape", ["b11t", "11tt", "bhtt", "random"])
-def test_mha_mask_broadcast_shapes(built_lib, shape):
-    B, T, H, hd = 2, 40, 3, 16
+def test_mha_mask_broadcast_shapes(built_lib, shape, hd):
+    B, T, H = 2, 40 if hd == 16 else 136, 3
     g = torch.Generator().manual_seed(5)
     if shape == "b11t":
         mask = torch.ones(B, 1, 1, T, dtype=torch.bool)
@@ -88,7 +92,11 @@ def test_mha_mask_broadcast_shapes(built_lib, shape):
 
 def test_mha_fully_masked_rows_and_nan_values(built_lib):
     """A fully masked query row is NaN; a NaN in the input poisons exactly what torch's matmul poisons."""
-    B, T, H, hd = 2, 12, 2, 8
+    _masked_rows_and_nan(2, 12, 2, 8)
+    _masked_rows_and_nan(2, 132, 2, 64)   # the tcgen05 attention kernel, two key blocks
+
+
+def _masked_rows_and_nan(B, T, H, hd):
     mask = torch.ones(B, 1, T, T, dtype=torch.bool)
     mask[0, 0, 3, :] = False
     reg = _mha_reg(B, T, H, hd, mask)
