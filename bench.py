@@ -37,6 +37,9 @@ sys.path.insert(0, str(REPO))
 
 B, T, PROMPT = 32, 256, 128
 METRIC = "gpt2_small_greedy_decode_tokens_per_s"
+# DRAM bytes (read + written) of the dominant kernel's launches in ONE forward, from an ncu capture of
+# this workload (profiles/decode_step_gpt2_small_b32_launch_list.md); bench.py cannot run ncu itself.
+NCU_DRAM_BYTES_PER_FORWARD = {"gemm_tf32x3_tcgen05_128x256": (5906021376, 49)}
 CPU_BUDGET_S = 150.0  # wall-clock budget of a CPU arm; the per-step batch is sized to fit it
 
 
@@ -281,8 +284,10 @@ def run_ours(args):
         top_name, top = max(by.items(), key=lambda kv: kv[1]["ms"])
         peaks = measured_peaks()
         achieved = top["flops"] / (top["ms"] * 1e-3) / 1e12
+        traffic = NCU_DRAM_BYTES_PER_FORWARD.get(top_name)
         roofline = {"bound": "tensor", "kernel": top_name, "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                    "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": None, "peak_source": peaks["source"] + " cuBLAS bf16, sustained",
+                    "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": (traffic[0] / traffic[1]) if traffic and traffic[1] == top["n"] else None,
+                    "algorithmic_bytes": top["bytes"] / top["n"], "peak_source": peaks["source"] + " cuBLAS bf16, sustained",
                     "launches_per_step": top["n"], "share_of_step": top["ms"] / total_ms,
                     "note": "achieved = logical fp32 flops (2MNK, counted once) of all launches of this kernel in one forward / their summed device time"}
         kernels = {k: {"launches": v["n"], "ms": round(v["ms"], 4), "share": round(v["ms"] / total_ms, 4),
