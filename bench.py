@@ -188,9 +188,20 @@ def run_ours(args):
     K, W = args.steps, max(args.warmup, 3)
     cfg = lowering.GPT2_SMALL
     tmp = tempfile.TemporaryDirectory()
-    eng = ExecutionEngine(build_graph_file(B, tmp.name), f"cuda:{local}", precision=args.precision)
+    # layout: independent replicas (default), or tensor-parallel groups of 2 / 4 GPUs (12 heads do not divide by 8)
+    tp_size, comm = 1, None
+    if args.parallel == "tp" and world > 1:
+        from fxfusion_b200.tp import Communicator
+        tp_size = 4 if world % 4 == 0 else 2 if world % 2 == 0 else 1
+        groups = [list(range(g * tp_size, (g + 1) * tp_size)) for g in range(world // tp_size)]
+        handles = [dist.new_group(ranks=r) for r in groups]
+        mine = rank // tp_size
+        comm = Communicator.from_process_group(local, ranks=groups[mine], group=handles[mine]) if tp_size > 1 else None
+    dp_size = world // tp_size
+    dp_rank = rank // tp_size
+    eng = ExecutionEngine(build_graph_file(B, tmp.name), f"cuda:{local}", precision=args.precision, comm=comm, shard_output=comm is not None)
     lib = _lib.lib()
-    prompt = torch.from_numpy(lowering.decode_prompt(B, PROMPT, cfg.vocab, seed=rank))
+    prompt = torch.from_numpy(lowering.decode_prompt(B, PROMPT, cfg.vocab, seed=dp_rank))
     start_buf = torch.zeros((B, T), dtype=torch.int64)
     start_buf[:, :PROMPT] = prompt
     tok_slot, mask_slot = eng.input_slots()
@@ -212,7 +223,7 @@ def run_ours(args):
         cur = state["cur"]
         _lib.check(lib.fxf_decode_build_mask(C.c_void_p(tok_slot.data_ptr()), C.c_void_p(mask_slot.data_ptr()), B, T, cur, 0, stream))
         _lib.check(lib.fxf_engine_run(h, (C.c_void_p * 2)(tok_slot.data_ptr(), mask_slot.data_ptr()), 2, stream))
-        _lib.check(lib.fxf_decode_argmax_scatter(C.c_void_p(logits.data_ptr()), C.c_void_p(tok_slot.data_ptr()), B, T, V, cur, stream))
+        _lib.check(lib.fxf_engine_argmax_scatter(h, C.c_void_p(tok_slot.data_ptr()), cur, stream))
         state["cur"] = cur + 1 if cur + 1 < T else PROMPT
 
     tok_slot.copy_(start_buf)
@@ -246,7 +257,7 @@ def run_ours(args):
         # the reference's mask rule, on the host (layers/masks.py:141-154)
         torch.logical_and(((ar < cur).view(1, 1, 1, T) & (host_tok != 0).view(B, 1, 1, T)), causal, out=host_mask)
         eng.run_host([host_tok.numpy(), host_mask.numpy().view(np.uint8)])
-        _lib.check(lib.fxf_decode_argmax_scatter(C.c_void_p(logits.data_ptr()), C.c_void_p(tok_slot.data_ptr()), B, T, V, cur, stream))
+        _lib.check(lib.fxf_engine_argmax_scatter(h, C.c_void_p(tok_slot.data_ptr()), cur, stream))
         host_tok.copy_(tok_slot, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
@@ -271,11 +282,15 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = t[0].item(), t[1].item()
 
-    if rank == 0:
-        # ---- roofline of the dominant kernel: one traced forward (an event after every launch) -----
+    # one traced forward (an event after every launch).  With tensor parallelism a forward contains
+    # collectives, so every rank of the group has to run it, not only the rank that reports.
+    trace = None
+    if rank == 0 or comm is not None:
         tok_slot.copy_(start_buf)
         eng.profile_launches()
         trace = eng.profile_launches()
+    if rank == 0:
+        # ---- roofline of the dominant kernel -----
         by = {}
         for r in trace:
             a = by.setdefault(r["kernel"], {"ms": 0.0, "flops": 0.0, "bytes": 0.0, "n": 0})
@@ -300,13 +315,15 @@ def run_ours(args):
             tps, s_per_step, kind, cores = cpu_decode_steps(cb, 2, 1)
             cpu = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": kind,
                    "sample": f"2 full-recompute decode steps of the same model at batch {cb} (of {B}), seq {T}; {s_per_step:.2f} s/step"}
-        tokens_per_step = B * world
+        tokens_per_step = B * dp_size
         line = {
             "metric": METRIC, "value": tokens_per_step * K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "GPT-2-small-shape greedy static decode, batch 32 per GPU, 128 prompt + 128 generated, fp32, full recompute",
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak" if tp_size == 1 else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "GPT-2-small-shape greedy static decode, batch 32 per replica, 128 prompt + 128 generated, fp32, full recompute",
                        "layers": 12, "d_model": 768, "heads": 12, "d_ff": 3072, "vocab": 50257, "batch_per_gpu": B, "seq": T,
-                       "parallelism": f"{world} independent replica(s), no collective", "gemm": args.precision,
+                       "parallelism": (f"{world} independent replica(s), no collective" if tp_size == 1 else
+                                       f"tp{tp_size} x dp{dp_size}: heads, FeedForward hidden units and vocabulary sharded over {tp_size} GPUs, "
+                                       f"2 NCCL all-reduces per layer, {dp_size} replica group(s) of batch {B}"), "gemm": args.precision,
                        "l2": "inputs larger than L2 (0.65 GB weights read, 1.65 GB logits written per step)"},
             "e2e": {"value": tokens_per_step * Ke / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * T * 8 + B * T * T,
                     "d2h_bytes_per_step": B * T * 8, "steps": Ke, "tokens_equal_device_loop": e2e_match},
@@ -316,6 +333,8 @@ def run_ours(args):
         }
         print(json.dumps(line), flush=True)
     eng.close()
+    if comm is not None:
+        comm.close()
     tmp.cleanup()
     if world > 1:
         dist.destroy_process_group()
@@ -378,6 +397,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--precision", default="auto", choices=["auto", "fp32_simt", "fp32_3xtf32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallel", default="replicas", choices=["replicas", "tp"],
+                    help="N > 1: independent batch replicas (default) or tensor-parallel groups (head-sharded MHA, split FeedForward, NCCL all-reduce)")
     args = ap.parse_args()
     if args.micro:
         return run_micro(args)

@@ -19,7 +19,7 @@ class FxfTensor(C.Structure):
 
 class FxfEngineOptions(C.Structure):
     _fields_ = [("struct_size", C.c_int32), ("use_cuda_graph", C.c_int32), ("gemm_mode", C.c_int32),
-                ("tp_rank", C.c_int32), ("tp_size", C.c_int32), ("reserved", C.c_int32 * 11)]
+                ("tp_rank", C.c_int32), ("tp_size", C.c_int32), ("tp_shard_output", C.c_int32), ("reserved", C.c_int32 * 10)]
 
 
 class FxfLaunchInfo(C.Structure):
@@ -36,6 +36,13 @@ SIGNATURES = {
     "fxf_last_error": (C.c_char_p, []),
     "fxf_version": (C.c_char_p, []),
     "fxf_engine_create": (C.c_int, [C.c_char_p, C.c_int, C.POINTER(FxfEngineOptions), C.POINTER(C.c_void_p)]),
+    "fxf_comm_unique_id": (C.c_int, [C.c_void_p]),
+    "fxf_comm_create": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
+    "fxf_comm_destroy": (None, [C.c_void_p]),
+    "fxf_comm_rank": (C.c_int, [C.c_void_p]),
+    "fxf_comm_size": (C.c_int, [C.c_void_p]),
+    "fxf_engine_create_tp": (C.c_int, [C.c_char_p, C.c_int, C.POINTER(FxfEngineOptions), C.c_void_p, C.POINTER(C.c_void_p)]),
+    "fxf_engine_argmax_scatter": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "fxf_engine_create_from_memory": (C.c_int, [C.c_void_p, C.c_size_t, C.c_int, C.POINTER(FxfEngineOptions), C.POINTER(C.c_void_p)]),
     "fxf_engine_destroy": (None, [C.c_void_p]),
     "fxf_engine_num_inputs": (C.c_int, [C.c_void_p]),

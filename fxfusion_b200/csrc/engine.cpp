@@ -33,6 +33,8 @@ const std::string& last_error() { return g_last_error; }
 
 int decode_build_mask(const int64_t* tokens, uint8_t* mask, int B, int T, int cur, int64_t pad, ExecCtx& ctx);
 int decode_argmax_scatter(const float* logits, int64_t* tokens, int B, int T, int64_t V, int cur, ExecCtx& ctx);
+int decode_argmax_scatter_sharded(const float* logits, int64_t* tokens, int B, int T, int64_t V, int cur, int64_t col0, int64_t ncols,
+                                  void* cand_local, void* cand_all, ExecCtx& ctx);
 
 int trace_after_launch(ExecCtx& ctx) {
     LaunchRecord r{ctx.tag_name, ctx.cur_node, ctx.tag_flops, ctx.tag_bytes, nullptr};
@@ -61,6 +63,10 @@ struct Node {
 
 using namespace fxf;
 
+struct fxf_comm;
+extern "C" int fxf_comm_rank(const fxf_comm*);
+extern "C" int fxf_comm_size(const fxf_comm*);
+
 struct fxf_engine {
     int device = 0;
     std::string name;
@@ -77,6 +83,11 @@ struct fxf_engine {
     cudaGraphExec_t graph_exec = nullptr;
     cudaStream_t capture_stream = nullptr;
     int launches_per_run = 0;
+    // tensor parallelism
+    fxf_comm* comm = nullptr;          // borrowed; must outlive the engine
+    bool head_sharded = false;         // the final Linear writes only this rank's column block of the logits
+    int64_t head_col0 = 0, head_ncols = 0;
+    size_t cand_off = 0, cand_bytes = 0;  // argmax candidates: [local | all ranks]
 
     ~fxf_engine() {
         if (graph_exec) cudaGraphExecDestroy(graph_exec);
@@ -182,6 +193,16 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
     e->input_bytes = cursor - const_cursor;
 
     // ---- nodes: ids and params are copied out; the file buffer is not needed after build ----
+    std::vector<bool> feeds_output(n_tensors, false);
+    for (uint32_t id : order)
+        if (meta[id].kind == kOutput) {
+            feeds_output[id] = true;
+            if (meta[id].alias_of >= 0 && uint32_t(meta[id].alias_of) < n_tensors) feeds_output[meta[id].alias_of] = true;
+        }
+    PlanEnv env;
+    env.gemm_mode = e->opts.gemm_mode;
+    env.tp_rank = e->opts.tp_rank;
+    env.tp_size = e->opts.tp_size;
     for (uint32_t i = 0; i < n_nodes; i++) {
         fbs::Table nt = g.table_at(fbs::GraphF::nodes, i);
         int op = nt.scalar<int8_t>(fbs::NodeF::op_code, 0);
@@ -203,7 +224,16 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
         for (auto id : n.in) FXF_CHECK(id < n_tensors, "node %u (%s) reads tensor id %u which does not exist", i, entry.name, id);
         for (auto id : n.out) FXF_CHECK(id < n_tensors, "node %u (%s) writes tensor id %u which does not exist", i, entry.name, id);
         FXF_CHECK(!n.out.empty(), "node %u (%s) has no output", i, entry.name);
-        n.plan = entry.plan(e->reg, n.in, n.out, n.params, e->opts.gemm_mode);
+        env.shard_output_cols = false;
+        if (e->opts.tp_size > 1 && e->opts.tp_shard_output && op == FXF_OP_LINEAR && feeds_output[n.out[0]] && n.in.size() >= 2 &&
+            e->reg[n.in[1]].rank == 2 && !e->head_sharded) {
+            env.shard_output_cols = true;
+            e->head_sharded = true;
+            int64_t N = e->reg[n.in[1]].shape[0], c = (N + e->opts.tp_size - 1) / e->opts.tp_size;
+            e->head_col0 = std::min<int64_t>(N, c * e->opts.tp_rank);
+            e->head_ncols = std::min<int64_t>(N, e->head_col0 + c) - e->head_col0;
+        }
+        n.plan = entry.plan(e->reg, n.in, n.out, n.params, env);
         e->scratch_bytes = std::max(e->scratch_bytes, n.plan->scratch_bytes);
         e->persist_bytes += round_up(n.plan->persist_bytes, kAlign);
         e->nodes.push_back(std::move(n));
@@ -214,6 +244,11 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
     cursor = round_up(cursor + e->scratch_bytes, kAlign);
     e->status_off = cursor;
     cursor += kAlign;
+    if (e->head_sharded && !e->input_ids.empty() && e->reg[e->input_ids[0]].rank >= 1) {
+        e->cand_off = cursor;
+        e->cand_bytes = round_up(size_t(e->opts.tp_size + 1) * size_t(e->reg[e->input_ids[0]].shape[0]) * 16, kAlign);
+        cursor += e->cand_bytes;
+    }
     e->total_bytes = cursor;
 
     // ---- the one device allocation -----------------------------------------------------------
@@ -223,6 +258,9 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
     FXF_CHECK(prop.major == 10, "this library is built for sm_100a only (B200); device %d is sm_%d%d", e->device, prop.major, prop.minor);
     e->ctx.sm_count = prop.multiProcessorCount;
     e->ctx.gemm_mode = e->opts.gemm_mode;
+    e->ctx.tp_rank = e->opts.tp_rank;
+    e->ctx.tp_size = e->opts.tp_size;
+    e->ctx.comm = e->comm;
     void* p = nullptr;
     cudaError_t err = cudaMalloc(&p, e->total_bytes);
     if (err != cudaSuccess) FXF_FAIL("Arena tensor is not allocated: cudaMalloc(%zu bytes) failed: %s", e->total_bytes, cudaGetErrorString(err));
@@ -305,7 +343,7 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
     return 0;
 }
 
-int create_from_bytes(const uint8_t* bytes, size_t nbytes, int device, const FxfEngineOptions* opts, fxf_engine** out) {
+int create_from_bytes(const uint8_t* bytes, size_t nbytes, int device, const FxfEngineOptions* opts, fxf_comm* comm, fxf_engine** out) {
     FXF_CHECK(out != nullptr, "fxf_engine_create: out_engine is NULL");
     *out = nullptr;
     auto e = std::make_unique<fxf_engine>();
@@ -319,7 +357,14 @@ int create_from_bytes(const uint8_t* bytes, size_t nbytes, int device, const Fxf
         std::memcpy(&e->opts, opts, n);
         if (e->opts.tp_size < 1) e->opts.tp_size = 1;
     }
-    FXF_CHECK(e->opts.tp_size == 1, "tensor-parallel engines are not available in this build");
+    if (comm != nullptr) {
+        e->comm = comm;
+        e->opts.tp_rank = fxf_comm_rank(comm);
+        e->opts.tp_size = fxf_comm_size(comm);
+    } else {
+        FXF_CHECK(e->opts.tp_size == 1, "a tensor-parallel engine (tp_size %d) needs a communicator: use fxf_engine_create_tp", e->opts.tp_size);
+        e->opts.tp_rank = 0;
+    }
     int count = 0;
     FXF_CUDA(cudaGetDeviceCount(&count));
     FXF_CHECK(device >= 0 && device < count, "device ordinal %d is out of range (%d CUDA devices)", device, count);
@@ -344,7 +389,7 @@ const char* fxf_last_error(void) { return fxf::last_error().c_str(); }
 
 const char* fxf_version(void) { return "fxf_b200 19 ops sm_100a"; }
 
-int fxf_engine_create(const char* graph_path, int device_ordinal, const FxfEngineOptions* opts, fxf_engine** out_engine) {
+int fxf_engine_create_tp(const char* graph_path, int device_ordinal, const FxfEngineOptions* opts, fxf_comm* comm, fxf_engine** out_engine) {
     FXF_CHECK(graph_path != nullptr, "fxf_engine_create: graph_path is NULL");
     std::ifstream f(graph_path, std::ios::binary | std::ios::ate);
     if (!f.is_open()) FXF_FAIL("ExecutionEngine failed to open: %s", graph_path);
@@ -352,12 +397,16 @@ int fxf_engine_create(const char* graph_path, int device_ordinal, const FxfEngin
     f.seekg(0, std::ios::beg);
     std::vector<uint8_t> bytes(size > 0 ? size_t(size) : 0);
     if (size > 0 && !f.read(reinterpret_cast<char*>(bytes.data()), size)) FXF_FAIL("ExecutionEngine failed to read: %s", graph_path);
-    return create_from_bytes(bytes.data(), bytes.size(), device_ordinal, opts, out_engine);
+    return create_from_bytes(bytes.data(), bytes.size(), device_ordinal, opts, comm, out_engine);
+}
+
+int fxf_engine_create(const char* graph_path, int device_ordinal, const FxfEngineOptions* opts, fxf_engine** out_engine) {
+    return fxf_engine_create_tp(graph_path, device_ordinal, opts, nullptr, out_engine);
 }
 
 int fxf_engine_create_from_memory(const void* bytes, size_t nbytes, int device_ordinal, const FxfEngineOptions* opts, fxf_engine** out_engine) {
     FXF_CHECK(bytes != nullptr, "fxf_engine_create_from_memory: bytes is NULL");
-    return create_from_bytes(static_cast<const uint8_t*>(bytes), nbytes, device_ordinal, opts, out_engine);
+    return create_from_bytes(static_cast<const uint8_t*>(bytes), nbytes, device_ordinal, opts, nullptr, out_engine);
 }
 
 void fxf_engine_destroy(fxf_engine* e) {
@@ -566,7 +615,9 @@ int64_t fxf_kernel_scratch_bytes(int op_code, const FxfTensor* reg, int n_reg, c
     TensorIds in, out;
     Params p;
     if (make_call(op_code, reg, n_reg, in_ids, n_in, out_ids, n_out, ints, n_ints, floats, n_floats, &r, &in, &out, &p)) return -1;
-    auto plan = op_entry(op_code).plan(r, in, out, p, gemm_mode);
+    PlanEnv env;
+    env.gemm_mode = gemm_mode;
+    auto plan = op_entry(op_code).plan(r, in, out, p, env);
     return int64_t(round_up(plan->scratch_bytes, 256) + plan->persist_bytes);
 }
 
@@ -578,7 +629,9 @@ int fxf_kernel_invoke(int op_code, const FxfTensor* reg, int n_reg, const uint32
     Params p;
     if (make_call(op_code, reg, n_reg, in_ids, n_in, out_ids, n_out, ints, n_ints, floats, n_floats, &r, &in, &out, &p)) return 1;
     const OpEntry& entry = op_entry(op_code);
-    auto plan = entry.plan(r, in, out, p, gemm_mode);
+    PlanEnv env;
+    env.gemm_mode = gemm_mode;
+    auto plan = entry.plan(r, in, out, p, env);
     size_t need = round_up(plan->scratch_bytes, 256) + plan->persist_bytes;
     FXF_CHECK(need == 0 || (scratch != nullptr && scratch_bytes >= int64_t(need)), "kernel call: scratch too small (%lld < %zu bytes)", (long long)scratch_bytes, need);
     FXF_CHECK(need == 0 || (reinterpret_cast<uintptr_t>(scratch) & 255) == 0, "kernel call: scratch must be 256-byte aligned");
@@ -612,6 +665,26 @@ int fxf_decode_argmax_scatter(const float* logits, int64_t* tokens, int B, int T
     return decode_argmax_scatter(logits, tokens, B, T, V, current_len, ctx);
 }
 
+int fxf_engine_argmax_scatter(fxf_engine* e, int64_t* tokens, int current_len, void* stream) {
+    FXF_CHECK(e && tokens, "fxf_engine_argmax_scatter: NULL argument");
+    FXF_CHECK(!e->output_ids.empty(), "fxf_engine_argmax_scatter: the graph has no output");
+    const FxfTensor& logits = e->reg[e->output_ids[0]];
+    FXF_CHECK(logits.dtype == FXF_F32 && logits.rank == 3, "fxf_engine_argmax_scatter: output 0 must be float32 [B,T,V]");
+    if (ensure_device(e)) return 1;
+    const int B = int(logits.shape[0]), T = int(logits.shape[1]);
+    ExecCtx ctx;
+    ctx.stream = static_cast<cudaStream_t>(stream);
+    ctx.sm_count = e->ctx.sm_count;
+    ctx.tp_rank = e->ctx.tp_rank;
+    ctx.tp_size = e->ctx.tp_size;
+    ctx.comm = e->ctx.comm;
+    if (!e->head_sharded) return decode_argmax_scatter(static_cast<const float*>(logits.ptr), tokens, B, T, logits.shape[2], current_len, ctx);
+    FXF_CHECK(e->cand_bytes >= size_t(e->ctx.tp_size + 1) * size_t(B) * 16, "fxf_engine_argmax_scatter: candidate buffer too small");
+    char* cand = reinterpret_cast<char*>(e->base + e->cand_off);
+    return decode_argmax_scatter_sharded(static_cast<const float*>(logits.ptr), tokens, B, T, logits.shape[2], current_len, e->head_col0,
+                                         e->head_ncols, cand, cand + size_t(B) * 16, ctx);
+}
+
 int fxf_decode_static(fxf_engine* e, int64_t* tokens_io, int initial_len, int64_t pad_idx, void* stream) {
     FXF_CHECK(e && tokens_io, "fxf_decode_static: NULL argument");
     FXF_CHECK(e->input_ids.size() == 2 && e->output_ids.size() >= 1, "fxf_decode_static: the graph must take (tokens, mask) and return logits");
@@ -631,10 +704,13 @@ int fxf_decode_static(fxf_engine* e, int64_t* tokens_io, int initial_len, int64_
     ExecCtx ctx;
     ctx.stream = s;
     ctx.sm_count = e->ctx.sm_count;
+    ctx.tp_rank = e->ctx.tp_rank;
+    ctx.tp_size = e->ctx.tp_size;
+    ctx.comm = e->ctx.comm;
     for (int cur = initial_len; cur < T; cur++) {
         if (decode_build_mask(slot, static_cast<uint8_t*>(mask.ptr), B, T, cur, pad_idx, ctx)) return 1;
         if (launch_forward(e, s)) return 1;
-        if (decode_argmax_scatter(static_cast<const float*>(logits.ptr), slot, B, T, logits.shape[2], cur, ctx)) return 1;
+        if (fxf_engine_argmax_scatter(e, slot, cur, stream)) return 1;
     }
     if (tokens_io != slot) FXF_CUDA(cudaMemcpyAsync(tokens_io, slot, size_t(tok.nbytes), cudaMemcpyDeviceToDevice, s));
     return 0;

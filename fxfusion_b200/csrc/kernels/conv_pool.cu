@@ -298,7 +298,7 @@ int k_adaptive_avg_pool2d(Registry& reg, const TensorIds& in, const TensorIds& o
     return 0;
 }
 
-std::unique_ptr<NodePlan> plan_conv(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, int) {
+std::unique_ptr<NodePlan> plan_conv(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv&) {
     auto pl = std::make_unique<ConvPlan>();
     if (in.size() >= 3 && out.size() >= 1 && reg[in[1]].rank == 4 && reg[out[0]].rank == 4) {
         const FxfTensor &w = reg[in[1]], &o = reg[out[0]];

@@ -95,7 +95,74 @@ __global__ void __launch_bounds__(1024) argmax_scatter_kernel(const float* __res
     }
 }
 
+// Vocabulary-sharded variant: every rank scans only its own column block and publishes one candidate per
+// sequence; after the all-gather each rank picks the same winner (the comparator prefers the lower index
+// on ties, so the result equals an argmax over the whole row).
+struct alignas(16) Candidate {
+    float v;
+    int pad;
+    int64_t i;
+};
+
+__global__ void __launch_bounds__(1024) argmax_partial_kernel(const float* __restrict__ logits, Candidate* __restrict__ cand, int T, int64_t V, int cur,
+                                                              int64_t col0, int64_t ncols) {
+    __shared__ Best red[32];
+    int b = blockIdx.x;
+    const float* row = logits + (int64_t(b) * T + (cur - 1)) * V;
+    Best best{0.f, -1};
+    for (int64_t i = col0 + threadIdx.x; i < col0 + ncols; i += blockDim.x) {
+        Best c{row[i], i};
+        if (better(c, best)) best = c;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best c;
+        c.v = __shfl_xor_sync(0xffffffffu, best.v, o);
+        c.i = __shfl_xor_sync(0xffffffffu, best.i, o);
+        if (better(c, best)) best = c;
+    }
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) red[warp] = best;
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < (blockDim.x >> 5) ? red[lane] : Best{0.f, -1};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            Best c;
+            c.v = __shfl_xor_sync(0xffffffffu, best.v, o);
+            c.i = __shfl_xor_sync(0xffffffffu, best.i, o);
+            if (better(c, best)) best = c;
+        }
+        if (lane == 0) cand[b] = Candidate{best.v, 0, best.i};
+    }
+}
+
+__global__ void argmax_combine_scatter_kernel(const Candidate* __restrict__ all, int64_t* __restrict__ tokens, int B, int T, int cur, int n_ranks) {
+    int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    Best best{0.f, -1};
+    for (int r = 0; r < n_ranks; r++) {
+        Candidate c = all[int64_t(r) * B + b];
+        Best cb{c.v, c.i};
+        if (better(cb, best)) best = cb;
+    }
+    tokens[int64_t(b) * T + cur] = best.i < 0 ? 0 : best.i;
+}
+
 }  // namespace
+
+// cand_local: B candidates; cand_all: n_ranks * B candidates (16 bytes each)
+int decode_argmax_scatter_sharded(const float* logits, int64_t* tokens, int B, int T, int64_t V, int cur, int64_t col0, int64_t ncols,
+                                  void* cand_local, void* cand_all, ExecCtx& ctx) {
+    FXF_CHECK(cur >= 1 && cur < T, "decode: current_len %d must be in [1, %d)", cur, T);
+    if (B == 0) return 0;
+    argmax_partial_kernel<<<B, 1024, 0, ctx.stream>>>(logits, static_cast<Candidate*>(cand_local), T, V, cur, col0, ncols);
+    FXF_LAUNCHED(ctx);
+    if (tp_all_gather(cand_local, cand_all, int64_t(B) * int64_t(sizeof(Candidate)), ctx)) return 1;
+    argmax_combine_scatter_kernel<<<(B + 127) / 128, 128, 0, ctx.stream>>>(static_cast<const Candidate*>(cand_all), tokens, B, T, cur, ctx.tp_size);
+    FXF_LAUNCHED(ctx);
+    return 0;
+}
 
 int decode_build_mask(const int64_t* tokens, uint8_t* mask, int B, int T, int cur, int64_t pad, ExecCtx& ctx) {
     FXF_CHECK(B >= 0 && T >= 0 && cur >= 0 && cur <= T, "decode: current_len %d exceeds static length %d", cur, T);

@@ -283,7 +283,7 @@ int run_transpose_typed(const FxfTensor& x, const FxfTensor& out, int d0, int d1
 
 struct SimplePlan : NodePlan {};
 
-std::unique_ptr<NodePlan> plan_elementwise(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, int) {
+std::unique_ptr<NodePlan> plan_elementwise(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const PlanEnv&) {
     auto p = std::make_unique<SimplePlan>();
     double b = 0;
     for (auto id : in) b += double(reg[id].nbytes);
@@ -408,11 +408,11 @@ int k_transpose(Registry& reg, const TensorIds& in, const TensorIds& out, const 
     FXF_FAIL("transpose: unsupported dtype");
 }
 
-std::unique_ptr<NodePlan> plan_bandwidth(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, int m) {
+std::unique_ptr<NodePlan> plan_bandwidth(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& m) {
     return plan_elementwise(reg, in, out, p, m);
 }
 // Narrow and Embedding touch only the slice / the gathered rows, not their whole first input.
-std::unique_ptr<NodePlan> plan_gather(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, int) {
+std::unique_ptr<NodePlan> plan_gather(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const PlanEnv&) {
     auto p = std::make_unique<SimplePlan>();
     double ob = out.empty() ? 0 : double(reg[out[0]].nbytes);
     p->bytes = 2 * ob;

@@ -187,7 +187,7 @@ int k_add_layer_norm(Registry& reg, const TensorIds& in, const TensorIds& out, c
                                static_cast<const float*>(b.ptr), static_cast<float*>(o.ptr), M, N, p.floats[0], ctx);
 }
 
-std::unique_ptr<NodePlan> plan_layernorm(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, int) {
+std::unique_ptr<NodePlan> plan_layernorm(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const PlanEnv&) {
     auto p = std::make_unique<LayerNormPlan>();
     double b = 0;
     for (auto id : in) b += double(reg[id].nbytes);

@@ -1,4 +1,4 @@
-// Dense-contraction ops: Linear, LinearRelu, FeedForward, MHA.
+// Dense-contraction ops: Linear, LinearRelu, FeedForward, MHA — single GPU and tensor-parallel.
 //
 // Reference semantics (LibTorch-delegating CPU kernels):
 //   linear       out = x · w^T + b                          csrc/kernels/cpu/linear.cpp:5-12
@@ -10,6 +10,19 @@
 // FeedForward [M,F]; MHA qkv [B,T,3D], scores [B,H,T,T], ctx [B,T,D]).  Here every node
 // borrows the engine's single shared scratch region for the duration of its launches, and the
 // score matrix is never materialised.
+//
+// Tensor parallelism (the reference has none).  With tp_size = n ranks, each holding the whole graph file:
+//   MHA          heads are sharded: rank r keeps heads [r·H/n, (r+1)·H/n): the matching rows of each of the
+//                Q, K, V thirds of the packed weight and bias, and the matching COLUMNS of the output
+//                projection.  Its out-projection yields a partial [M,D]; bias only on rank 0; all-reduce.
+//   FeedForward  w1 rows / b1 entries [r·F/n, (r+1)·F/n) (column-parallel), ReLU local, the matching
+//                columns of w2 (row-parallel) -> partial [M,P]; b2 only on rank 0; all-reduce.
+//   final Linear (optional) its rows (vocabulary) are sharded; each rank writes only its column block of
+//                the logits, and the decode argmax combines the ranks' candidates.
+// Everything else is replicated.  The slices are gathered once, at engine build, into the node's
+// persistent memory (and split into TF32 hi/lo there), so a forward never touches the unsharded weights.
+#include <algorithm>
+
 #include "../runtime.hpp"
 
 namespace fxf {
@@ -35,77 +48,111 @@ std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count) {
 
 namespace {
 
-// Holds up to two weights pre-split into TF32 hi/lo halves inside the node's persistent memory.
+// A dense fp32 matrix [rows, cols] (a vector when cols == 1), assembled from up to three row
+// ranges and one column range of a graph tensor.  `whole` slices use the tensor in place.
+struct Slice {
+    int input = -1;                 // position of the source tensor in the node's input_ids
+    int n_ranges = 0;
+    int64_t row0[3] = {0, 0, 0}, nrow[3] = {0, 0, 0};
+    int64_t col0 = 0, ncol = 0;     // column window
+    int64_t src_ld = 0;             // row pitch of the source (elements)
+    bool whole = true;              // the slice is the entire tensor: no copy
+    bool split = false;             // TF32 hi/lo copies wanted (tensor-core GEMM operand)
+    bool drop = false;              // replaced by "no bias" (rank != 0 of a row-parallel product)
+    size_t off_copy = 0, off_split = 0;  // byte offsets inside the plan's persistent memory
+    const float *ptr = nullptr, *hi = nullptr, *lo = nullptr;  // resolved by prepare()
+    int64_t rows() const { return nrow[0] + nrow[1] + nrow[2]; }
+    int64_t elems() const { return rows() * ncol; }
+};
+
 struct DensePlan : NodePlan {
-    struct Split {
-        int input = -1;      // position in input_ids of the weight
-        int64_t n = 0;       // elements
-        size_t offset = 0;   // byte offset of the hi half inside `persist`; lo follows
-    };
-    Split splits[2];
-    int n_splits = 0;
-    void want_split(int input, int64_t N, int64_t K, int64_t M, int gemm_mode) {
-        if (gemm_mode == FXF_GEMM_FP32_SIMT || !gemm_tc_shape_ok(M, N, K)) return;
-        Split& sp = splits[n_splits++];
-        sp.input = input;
-        sp.n = N * K;
-        sp.offset = persist_bytes;
-        persist_bytes += round_up(size_t(2) * size_t(sp.n) * sizeof(float), 256);
+    Slice s[4];  // meaning depends on the op (see the plan builders)
+    int n = 0;
+    // dims the kernels need again
+    int64_t M = 0, heads_local = 0, head0 = 0, n_local = 0, col_off = 0;
+
+    Slice& add(int input, int64_t rows, int64_t cols) {
+        Slice& x = s[n++];
+        x.input = input;
+        x.n_ranges = 1;
+        x.row0[0] = 0; x.nrow[0] = rows;
+        x.col0 = 0; x.ncol = cols; x.src_ld = cols;
+        return x;
     }
-    const float* hi(int input) const {
-        for (int i = 0; i < n_splits; i++)
-            if (splits[i].input == input && persist) return reinterpret_cast<const float*>(static_cast<const char*>(persist) + splits[i].offset);
-        return nullptr;
-    }
-    const float* lo(int input) const {
-        for (int i = 0; i < n_splits; i++)
-            if (splits[i].input == input && persist) return hi(input) + splits[i].n;
-        return nullptr;
+    void reserve(Slice& x, bool want_split) {
+        if (x.drop) return;
+        if (!x.whole) {
+            x.off_copy = persist_bytes;
+            persist_bytes += round_up(size_t(x.elems()) * sizeof(float), 256);
+        }
+        if (want_split) {
+            x.split = true;
+            x.off_split = persist_bytes;
+            persist_bytes += round_up(size_t(2) * size_t(x.elems()) * sizeof(float), 256);
+        }
     }
     int prepare(Registry& reg, const TensorIds& in, const TensorIds&, const Params&, ExecCtx& ctx) override {
-        for (int i = 0; i < n_splits; i++) {
-            const FxfTensor& w = reg[in[splits[i].input]];
-            FXF_CHECK(persist != nullptr && numel(w) == splits[i].n, "dense plan: persistent memory was not assigned");
-            float* h = reinterpret_cast<float*>(static_cast<char*>(persist) + splits[i].offset);
-            if (launch_split_tf32(static_cast<const float*>(w.ptr), h, h + splits[i].n, splits[i].n, ctx)) return 1;
+        for (int i = 0; i < n; i++) {
+            Slice& x = s[i];
+            if (x.drop) continue;
+            const float* src = static_cast<const float*>(reg[in[x.input]].ptr);
+            if (x.whole) {
+                x.ptr = src;
+            } else {
+                FXF_CHECK(persist != nullptr, "dense plan: persistent memory was not assigned");
+                float* dst = reinterpret_cast<float*>(static_cast<char*>(persist) + x.off_copy);
+                int64_t done = 0;
+                for (int r = 0; r < x.n_ranges; r++) {
+                    if (x.nrow[r] == 0) continue;
+                    FXF_CUDA(cudaMemcpy2DAsync(dst + done * x.ncol, size_t(x.ncol) * 4, src + x.row0[r] * x.src_ld + x.col0, size_t(x.src_ld) * 4,
+                                               size_t(x.ncol) * 4, size_t(x.nrow[r]), cudaMemcpyDeviceToDevice, ctx.stream));
+                    done += x.nrow[r];
+                }
+                x.ptr = dst;
+            }
+            if (x.split) {
+                FXF_CHECK(persist != nullptr, "dense plan: persistent memory was not assigned");
+                float* h = reinterpret_cast<float*>(static_cast<char*>(persist) + x.off_split);
+                if (launch_split_tf32(x.ptr, h, h + x.elems(), x.elems(), ctx)) return 1;
+                x.hi = h;
+                x.lo = h + x.elems();
+            }
         }
         return 0;
     }
 };
 inline const DensePlan* dense(const NodePlan* p) { return static_cast<const DensePlan*>(p); }
 
-struct LinearDims {
-    int64_t M, N, K;
-};
+bool want_tc(const PlanEnv& env, int64_t M, int64_t N, int64_t K) { return env.gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(M, N, K); }
 
-int linear_dims(const FxfTensor& x, const FxfTensor& w, const FxfTensor& b, const FxfTensor& o, LinearDims* d, const char* who) {
-    FXF_CHECK(x.dtype == FXF_F32 && w.dtype == FXF_F32 && b.dtype == FXF_F32 && o.dtype == FXF_F32, "%s: only float32 is supported", who);
-    FXF_CHECK(w.rank == 2 && x.rank >= 1, "%s: weight must be [N,K] and x at least 1-D", who);
-    int64_t K = x.shape[x.rank - 1];
-    FXF_CHECK(w.shape[1] == K, "%s: x inner size %lld does not match weight K %lld", who, (long long)K, (long long)w.shape[1]);
-    FXF_CHECK(numel(b) == w.shape[0], "%s: bias size does not match weight rows", who);
-    d->K = K;
-    d->N = w.shape[0];
-    d->M = 1;
-    for (int k = 0; k + 1 < x.rank; k++) d->M *= x.shape[k];
-    FXF_CHECK(numel(o) == d->M * d->N, "%s: output size mismatch", who);
-    return 0;
+void fill_gemm(GemmArgs& g, const float* x, const Slice& w, const Slice* bias, float* out, int64_t M, int64_t ldx, int64_t ldo, bool relu) {
+    g.x = x; g.w = w.ptr; g.w_hi = w.hi; g.w_lo = w.lo;
+    g.bias = (bias && !bias->drop) ? bias->ptr : nullptr;
+    g.out = out; g.M = M; g.N = w.rows(); g.K = w.ncol;
+    g.ldx = ldx; g.ldw = w.ncol; g.ldo = ldo; g.relu = relu;
 }
 
+int64_t leading_rows(const FxfTensor& x) {
+    int64_t m = 1;
+    for (int k = 0; k + 1 < x.rank; k++) m *= x.shape[k];
+    return m;
+}
+
+// ---- Linear / LinearRelu ------------------------------------------------------------------------------
+// slices: s[0] = weight rows kept by this rank, s[1] = matching bias entries
 int run_linear(Registry& reg, const TensorIds& in, const TensorIds& out, bool relu, const NodePlan* plan, ExecCtx& ctx, const char* who) {
     FXF_CHECK(in.size() >= 3 && out.size() >= 1, "%s: expects [x, weight, bias]", who);
     const FxfTensor &x = reg[in[0]], &w = reg[in[1]], &b = reg[in[2]], &o = reg[out[0]];
-    LinearDims d;
-    if (linear_dims(x, w, b, o, &d, who)) return 1;
+    FXF_CHECK(x.dtype == FXF_F32 && w.dtype == FXF_F32 && b.dtype == FXF_F32 && o.dtype == FXF_F32, "%s: only float32 is supported", who);
+    FXF_CHECK(w.rank == 2 && x.rank >= 1, "%s: weight must be [N,K] and x at least 1-D", who);
+    const int64_t K = x.shape[x.rank - 1], N = w.shape[0], M = leading_rows(x);
+    FXF_CHECK(w.shape[1] == K, "%s: x inner size %lld does not match weight K %lld", who, (long long)K, (long long)w.shape[1]);
+    FXF_CHECK(numel(b) == N, "%s: bias size does not match weight rows", who);
+    FXF_CHECK(numel(o) == M * N, "%s: output size mismatch", who);
+    const DensePlan* pl = dense(plan);
+    FXF_CHECK(pl != nullptr && pl->n == 2 && pl->s[0].ptr != nullptr, "%s: the node was not prepared", who);
     GemmArgs g;
-    g.x = static_cast<const float*>(x.ptr);
-    g.w = static_cast<const float*>(w.ptr);
-    if (plan) { g.w_hi = dense(plan)->hi(1); g.w_lo = dense(plan)->lo(1); }
-    g.bias = static_cast<const float*>(b.ptr);
-    g.out = static_cast<float*>(o.ptr);
-    g.M = d.M; g.N = d.N; g.K = d.K;
-    g.ldx = d.K; g.ldw = d.K; g.ldo = d.N;
-    g.relu = relu;
+    fill_gemm(g, static_cast<const float*>(x.ptr), pl->s[0], &pl->s[1], static_cast<float*>(o.ptr) + pl->col_off, M, K, N, relu);
     return launch_gemm(g, ctx);
 }
 
@@ -118,156 +165,194 @@ int k_linear_relu(Registry& reg, const TensorIds& in, const TensorIds& out, cons
     return run_linear(reg, in, out, true, plan, ctx, "linear_relu");
 }
 
-std::unique_ptr<NodePlan> plan_linear(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, int gemm_mode) {
+std::unique_ptr<NodePlan> plan_linear(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const PlanEnv& env) {
     auto p = std::make_unique<DensePlan>();
-    if (in.size() >= 3 && out.size() >= 1) {
-        const FxfTensor &x = reg[in[0]], &w = reg[in[1]];
-        if (w.rank == 2 && x.rank >= 1 && x.shape[x.rank - 1] > 0) {
-            GemmArgs g;
-            g.K = x.shape[x.rank - 1]; g.N = w.shape[0]; g.M = numel(x) / g.K;
-            g.ldx = g.K; g.ldw = g.K; g.ldo = g.N;
-            g.x = static_cast<const float*>(x.ptr); g.w = static_cast<const float*>(w.ptr); g.out = static_cast<float*>(reg[out[0]].ptr);
-            p->flops = 2.0 * double(g.M) * double(g.N) * double(g.K);
-            p->bytes = 4.0 * (double(g.M) * g.K + double(g.N) * g.K + double(g.N) + double(g.M) * g.N);
-            p->variant = gemm_variant_name(g, gemm_mode, 148);
-            p->want_split(1, g.N, g.K, g.M, gemm_mode);
-        }
+    if (in.size() < 3 || out.size() < 1) return p;
+    const FxfTensor &x = reg[in[0]], &w = reg[in[1]];
+    if (w.rank != 2 || x.rank < 1) return p;
+    const int64_t K = x.shape[x.rank - 1], N = w.shape[0], M = leading_rows(x);
+    Slice& ws = p->add(1, N, K);
+    Slice& bs = p->add(2, N, 1);
+    p->n_local = N;
+    if (env.shard_output_cols && env.tp_size > 1) {
+        // vocabulary-parallel head: rank r owns rows [r*c, min(N, (r+1)*c)) with c = ceil(N / n)
+        int64_t c = (N + env.tp_size - 1) / env.tp_size, r0 = std::min<int64_t>(N, c * env.tp_rank), r1 = std::min<int64_t>(N, r0 + c);
+        ws.row0[0] = r0; ws.nrow[0] = r1 - r0; ws.whole = false;
+        bs.row0[0] = r0; bs.nrow[0] = r1 - r0; bs.whole = false;
+        p->col_off = r0;
+        p->n_local = r1 - r0;
     }
+    p->reserve(ws, want_tc(env, M, p->n_local, K));
+    p->reserve(bs, false);
+    p->M = M;
+    p->flops = 2.0 * double(M) * double(p->n_local) * double(K);
+    p->bytes = 4.0 * (double(M) * K + double(p->n_local) * K + double(p->n_local) + double(M) * p->n_local);
+    GemmArgs g;
+    g.M = M; g.N = p->n_local; g.K = K;
+    p->variant = gemm_variant_name(g, env.gemm_mode, 148);
     return p;
 }
 
 // ---- FeedForward ------------------------------------------------------------------------------
+// slices: s[0] = w1 rows of this rank [Fl, D], s[1] = b1 entries [Fl], s[2] = w2 columns of this rank [P, Fl], s[3] = b2
 int k_feedforward(Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const NodePlan* plan, ExecCtx& ctx) {
     FXF_CHECK(in.size() >= 5 && out.size() >= 1, "feedforward: expects [x, w1, b1, w2, b2]");
     const FxfTensor &x = reg[in[0]], &w1 = reg[in[1]], &b1 = reg[in[2]], &w2 = reg[in[3]], &b2 = reg[in[4]], &o = reg[out[0]];
     FXF_CHECK(x.dtype == FXF_F32 && o.dtype == FXF_F32, "feedforward: only float32 is supported");
     FXF_CHECK(w1.rank == 2 && w2.rank == 2 && x.rank >= 1, "feedforward: weights must be 2-D");
-    int64_t K = x.shape[x.rank - 1], F = w1.shape[0], P = w2.shape[0];
+    const int64_t K = x.shape[x.rank - 1], F = w1.shape[0], P = w2.shape[0], M = leading_rows(x);
     FXF_CHECK(w1.shape[1] == K && w2.shape[1] == F, "feedforward: weight shapes do not chain (x[..,%lld], w1[%lld,%lld], w2[%lld,%lld])",
               (long long)K, (long long)w1.shape[0], (long long)w1.shape[1], (long long)w2.shape[0], (long long)w2.shape[1]);
     FXF_CHECK(numel(b1) == F && numel(b2) == P, "feedforward: bias sizes do not match");
-    int64_t M = 1;
-    for (int k = 0; k + 1 < x.rank; k++) M *= x.shape[k];
     FXF_CHECK(numel(o) == M * P, "feedforward: output size mismatch");
-    size_t need = size_t(M) * size_t(F) * sizeof(float);
+    const DensePlan* pl = dense(plan);
+    FXF_CHECK(pl != nullptr && pl->n == 4 && pl->s[0].ptr != nullptr, "feedforward: the node was not prepared");
+    const int64_t Fl = pl->s[0].rows();
+    size_t need = size_t(M) * size_t(Fl) * sizeof(float);
     FXF_CHECK(ctx.scratch_bytes >= need && (need == 0 || ctx.scratch != nullptr), "feedforward: scratch too small (%zu < %zu bytes)", ctx.scratch_bytes, need);
     float* hidden = static_cast<float*>(ctx.scratch);
-    GemmArgs g1;
-    g1.x = static_cast<const float*>(x.ptr); g1.w = static_cast<const float*>(w1.ptr); g1.bias = static_cast<const float*>(b1.ptr);
-    g1.out = hidden; g1.M = M; g1.N = F; g1.K = K; g1.ldx = K; g1.ldw = K; g1.ldo = F; g1.relu = true;
-    if (plan) { g1.w_hi = dense(plan)->hi(1); g1.w_lo = dense(plan)->lo(1); }
+    GemmArgs g1, g2;
+    fill_gemm(g1, static_cast<const float*>(x.ptr), pl->s[0], &pl->s[1], hidden, M, K, Fl, true);
     if (launch_gemm(g1, ctx)) return 1;
-    GemmArgs g2;
-    g2.x = hidden; g2.w = static_cast<const float*>(w2.ptr); g2.bias = static_cast<const float*>(b2.ptr);
-    g2.out = static_cast<float*>(o.ptr); g2.M = M; g2.N = P; g2.K = F; g2.ldx = F; g2.ldw = F; g2.ldo = P; g2.relu = false;
-    if (plan) { g2.w_hi = dense(plan)->hi(3); g2.w_lo = dense(plan)->lo(3); }
-    return launch_gemm(g2, ctx);
+    fill_gemm(g2, hidden, pl->s[2], &pl->s[3], static_cast<float*>(o.ptr), M, Fl, P, false);
+    if (launch_gemm(g2, ctx)) return 1;
+    return tp_all_reduce_sum(static_cast<float*>(o.ptr), M * P, ctx);
 }
 
-std::unique_ptr<NodePlan> plan_feedforward(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, int gemm_mode) {
+std::unique_ptr<NodePlan> plan_feedforward(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const PlanEnv& env) {
     auto p = std::make_unique<DensePlan>();
-    if (in.size() >= 5 && out.size() >= 1) {
-        const FxfTensor &x = reg[in[0]], &w1 = reg[in[1]], &w2 = reg[in[3]];
-        if (w1.rank == 2 && w2.rank == 2 && x.rank >= 1 && x.shape[x.rank - 1] > 0) {
-            int64_t K = x.shape[x.rank - 1], F = w1.shape[0], P = w2.shape[0], M = numel(x) / K;
-            p->scratch_bytes = size_t(M) * size_t(F) * sizeof(float);
-            p->flops = 2.0 * double(M) * double(F) * double(K) + 2.0 * double(M) * double(P) * double(F);
-            p->bytes = 4.0 * (double(M) * K + double(F) * K + F + double(P) * F + P + double(M) * P);
-            GemmArgs g1; g1.M = M; g1.N = F; g1.K = K; g1.ldx = K; g1.ldw = K; g1.ldo = F;
-            GemmArgs g2; g2.M = M; g2.N = P; g2.K = F; g2.ldx = F; g2.ldw = F; g2.ldo = P;
-            p->variant = gemm_variant_name(g1, gemm_mode, 148) + "+" + gemm_variant_name(g2, gemm_mode, 148);
-            p->want_split(1, F, K, M, gemm_mode);
-            p->want_split(3, P, F, M, gemm_mode);
-        }
+    if (in.size() < 5 || out.size() < 1) return p;
+    const FxfTensor &x = reg[in[0]], &w1 = reg[in[1]], &w2 = reg[in[3]];
+    if (w1.rank != 2 || w2.rank != 2 || x.rank < 1) return p;
+    const int64_t K = x.shape[x.rank - 1], F = w1.shape[0], P = w2.shape[0], M = leading_rows(x);
+    const int n = env.tp_size > 1 && F % env.tp_size == 0 ? env.tp_size : 1;  // hidden width must divide evenly, else replicate
+    const int64_t Fl = F / n, f0 = (n > 1 ? env.tp_rank : 0) * Fl;
+    Slice& s_w1 = p->add(1, F, K);
+    Slice& s_b1 = p->add(2, F, 1);
+    Slice& s_w2 = p->add(3, P, F);
+    Slice& s_b2 = p->add(4, P, 1);
+    if (n > 1) {
+        s_w1.row0[0] = f0; s_w1.nrow[0] = Fl; s_w1.whole = false;
+        s_b1.row0[0] = f0; s_b1.nrow[0] = Fl; s_b1.whole = false;
+        s_w2.col0 = f0; s_w2.ncol = Fl; s_w2.whole = false;
+        s_b2.drop = env.tp_rank != 0;
+    } else if (env.tp_size > 1) {
+        p->variant = "replicated ";
     }
+    p->reserve(s_w1, want_tc(env, M, Fl, K));
+    p->reserve(s_b1, false);
+    p->reserve(s_w2, want_tc(env, M, P, Fl));
+    p->reserve(s_b2, false);
+    p->M = M;
+    p->scratch_bytes = size_t(M) * size_t(Fl) * sizeof(float);
+    p->flops = 2.0 * double(M) * double(Fl) * double(K) + 2.0 * double(M) * double(P) * double(Fl);
+    p->bytes = 4.0 * (double(M) * K + double(Fl) * K + Fl + double(P) * Fl + P + double(M) * P);
+    GemmArgs g1, g2;
+    g1.M = M; g1.N = Fl; g1.K = K;
+    g2.M = M; g2.N = P; g2.K = Fl;
+    p->variant += gemm_variant_name(g1, env.gemm_mode, 148) + "+" + gemm_variant_name(g2, env.gemm_mode, 148);
     return p;
 }
 
 // ---- MHA ----------------------------------------------------------------------------------------
-namespace {
-struct MhaDims {
-    int64_t B, T, H, hd, D, QKV, M;
-};
-int mha_dims(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, MhaDims* d) {
+// slices: s[0] = packed QKV rows of the local heads [3*Dl, D], s[1] = their bias [3*Dl],
+//         s[2] = output-projection columns of the local heads [D, Dl], s[3] = output bias [D]
+int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const NodePlan* plan, ExecCtx& ctx) {
     FXF_CHECK(in.size() >= 6 && out.size() >= 1, "mha: expects [x, mask, qkv_weight, qkv_bias, out_weight, out_bias]");
     FXF_CHECK(p.ints.size() >= 4 && p.floats.size() >= 1, "mha: expects ints [H, head_dim, d_model, qkv_dim] and floats [scale_divisor]");
-    const FxfTensor& x = reg[in[0]];
-    FXF_CHECK(x.rank == 3, "mha: x must be [B,T,D]");
-    d->B = x.shape[0]; d->T = x.shape[1];
-    d->H = p.ints[0]; d->hd = p.ints[1]; d->D = p.ints[2]; d->QKV = p.ints[3];
-    d->M = d->B * d->T;
-    FXF_CHECK(d->H > 0 && d->hd > 0 && d->H * d->hd == d->D && d->QKV == 3 * d->D, "mha: inconsistent head parameters");
-    FXF_CHECK(x.shape[2] == d->D, "mha: x inner size does not match d_model");
-    const FxfTensor &wq = reg[in[2]], &bq = reg[in[3]], &wo = reg[in[4]], &bo = reg[in[5]];
-    FXF_CHECK(wq.rank == 2 && wq.shape[0] == d->QKV && wq.shape[1] == d->D && numel(bq) == d->QKV, "mha: packed QKV weight/bias shape mismatch");
-    FXF_CHECK(wo.rank == 2 && wo.shape[0] == d->D && wo.shape[1] == d->D && numel(bo) == d->D, "mha: output projection shape mismatch");
-    FXF_CHECK(numel(reg[out[0]]) == d->M * d->D, "mha: output size mismatch");
-    return 0;
-}
-}  // namespace
-
-int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const NodePlan* plan, ExecCtx& ctx) {
-    MhaDims d;
-    if (mha_dims(reg, in, out, p, &d)) return 1;
     const FxfTensor &x = reg[in[0]], &mask = reg[in[1]], &wq = reg[in[2]], &bq = reg[in[3]], &wo = reg[in[4]], &bo = reg[in[5]], &o = reg[out[0]];
+    FXF_CHECK(x.rank == 3, "mha: x must be [B,T,D]");
+    const int64_t B = x.shape[0], T = x.shape[1], H = p.ints[0], hd = p.ints[1], D = p.ints[2], QKV = p.ints[3], M = B * T;
+    FXF_CHECK(H > 0 && hd > 0 && H * hd == D && QKV == 3 * D, "mha: inconsistent head parameters");
+    FXF_CHECK(x.shape[2] == D, "mha: x inner size does not match d_model");
+    FXF_CHECK(wq.rank == 2 && wq.shape[0] == QKV && wq.shape[1] == D && numel(bq) == QKV, "mha: packed QKV weight/bias shape mismatch");
+    FXF_CHECK(wo.rank == 2 && wo.shape[0] == D && wo.shape[1] == D && numel(bo) == D, "mha: output projection shape mismatch");
+    FXF_CHECK(numel(o) == M * D, "mha: output size mismatch");
     FXF_CHECK(x.dtype == FXF_F32 && o.dtype == FXF_F32, "mha: only float32 activations are supported");
     FXF_CHECK(mask.dtype == FXF_BOOL, "mha: mask must be a bool tensor");
     FXF_CHECK(mask.rank <= 4, "mha: mask rank must be <= 4");
     // broadcast the mask to [B,H,T,T]: right-align its dims, stride 0 where its extent is 1
-    int64_t want[4] = {d.B, d.H, d.T, d.T}, ms[4] = {0, 0, 0, 0};
+    int64_t want[4] = {B, H, T, T}, ms[4] = {0, 0, 0, 0};
     for (int k = 0; k < mask.rank; k++) {
         int tgt = 4 - mask.rank + k;
         FXF_CHECK(mask.shape[k] == want[tgt] || mask.shape[k] == 1, "mha: mask shape is not broadcastable to [B,H,T,T]");
         ms[tgt] = mask.shape[k] == 1 ? 0 : mask.stride[k];
     }
-    size_t need = size_t(d.M) * size_t(d.QKV + d.D) * sizeof(float);
+    const DensePlan* pl = dense(plan);
+    FXF_CHECK(pl != nullptr && pl->n == 4 && pl->s[0].ptr != nullptr, "mha: the node was not prepared");
+    const int64_t Hl = pl->heads_local, Dl = Hl * hd, QKVl = 3 * Dl;
+    size_t need = size_t(M) * size_t(QKVl + Dl) * sizeof(float);
     FXF_CHECK(ctx.scratch_bytes >= need && (need == 0 || ctx.scratch != nullptr), "mha: scratch too small (%zu < %zu bytes)", ctx.scratch_bytes, need);
     float* qkv = static_cast<float*>(ctx.scratch);
-    float* cx = qkv + d.M * d.QKV;
-    float* split = cx + d.M * d.D;  // only present when the plan reserved it
-    const bool have_split = ctx.scratch_bytes >= need + attention_tc_scratch_bytes(d.B, d.T, d.H);
+    float* cx = qkv + M * QKVl;
+    float* vt = cx + M * Dl;  // only present when the plan reserved it
+    const bool have_vt = ctx.scratch_bytes >= need + attention_tc_scratch_bytes(B, T, Hl);
 
     GemmArgs g;
-    g.x = static_cast<const float*>(x.ptr); g.w = static_cast<const float*>(wq.ptr); g.bias = static_cast<const float*>(bq.ptr);
-    g.out = qkv; g.M = d.M; g.N = d.QKV; g.K = d.D; g.ldx = d.D; g.ldw = d.D; g.ldo = d.QKV;
-    if (plan) { g.w_hi = dense(plan)->hi(2); g.w_lo = dense(plan)->lo(2); }
+    fill_gemm(g, static_cast<const float*>(x.ptr), pl->s[0], &pl->s[1], qkv, M, D, QKVl, false);
     if (launch_gemm(g, ctx)) return 1;
 
     AttnArgs a;
-    a.qkv = qkv; a.mask = static_cast<const uint8_t*>(mask.ptr); a.ctx = cx;
-    a.B = int(d.B); a.T = int(d.T); a.H = int(d.H); a.hd = int(d.hd);
-    a.ld_qkv = d.QKV; a.q_off = 0; a.k_off = d.D; a.v_off = 2 * d.D; a.ld_ctx = d.D;
+    a.qkv = qkv; a.ctx = cx;
+    a.mask = static_cast<const uint8_t*>(mask.ptr) + pl->head0 * ms[1];  // local head 0 is global head `head0`
+    a.B = int(B); a.T = int(T); a.H = int(Hl); a.hd = int(hd);
+    a.ld_qkv = QKVl; a.q_off = 0; a.k_off = Dl; a.v_off = 2 * Dl; a.ld_ctx = Dl;
     a.mask_sb = ms[0]; a.mask_sh = ms[1]; a.mask_sq = ms[2]; a.mask_sk = ms[3];
     a.scale_divisor = p.floats[0];
-    if (have_split && attention_tc_supported(a, ctx.gemm_mode)) {
-        if (launch_attention_tc(a, split, ctx)) return 1;
+    if (have_vt && attention_tc_supported(a, ctx.gemm_mode)) {
+        if (launch_attention_tc(a, vt, ctx)) return 1;
     } else {
         if (launch_attention(a, ctx)) return 1;
     }
 
     GemmArgs g2;
-    g2.x = cx; g2.w = static_cast<const float*>(wo.ptr); g2.bias = static_cast<const float*>(bo.ptr);
-    g2.out = static_cast<float*>(o.ptr); g2.M = d.M; g2.N = d.D; g2.K = d.D; g2.ldx = d.D; g2.ldw = d.D; g2.ldo = d.D;
-    if (plan) { g2.w_hi = dense(plan)->hi(4); g2.w_lo = dense(plan)->lo(4); }
-    return launch_gemm(g2, ctx);
+    fill_gemm(g2, cx, pl->s[2], &pl->s[3], static_cast<float*>(o.ptr), M, Dl, D, false);
+    if (launch_gemm(g2, ctx)) return 1;
+    return tp_all_reduce_sum(static_cast<float*>(o.ptr), M * D, ctx);
 }
 
-std::unique_ptr<NodePlan> plan_mha(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, int gemm_mode) {
+std::unique_ptr<NodePlan> plan_mha(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& env) {
     auto pl = std::make_unique<DensePlan>();
-    if (in.size() >= 6 && out.size() >= 1 && p.ints.size() >= 4 && reg[in[0]].rank == 3) {
-        const FxfTensor& x = reg[in[0]];
-        int64_t B = x.shape[0], T = x.shape[1], H = p.ints[0], hd = p.ints[1], D = p.ints[2], QKV = p.ints[3], M = B * T;
-        pl->scratch_bytes = size_t(M) * size_t(QKV + D) * sizeof(float);
-        const bool tc_attn = gemm_mode != FXF_GEMM_FP32_SIMT && hd == 64 && T % 4 == 0 && T >= 16 && D % 4 == 0;
-        if (tc_attn) pl->scratch_bytes += attention_tc_scratch_bytes(B, T, H);
-        pl->flops = 2.0 * M * double(QKV) * D + 4.0 * double(B) * H * double(T) * T * hd + 2.0 * double(M) * D * D;
-        pl->bytes = 4.0 * (2.0 * double(M) * D + double(QKV) * D + QKV + double(D) * D + D) + double(reg[in[1]].nbytes);
-        GemmArgs g1; g1.M = M; g1.N = QKV; g1.K = D; g1.ldx = D; g1.ldw = D; g1.ldo = QKV;
-        GemmArgs g2; g2.M = M; g2.N = D; g2.K = D; g2.ldx = D; g2.ldw = D; g2.ldo = D;
-        pl->variant = gemm_variant_name(g1, gemm_mode, 148) + (tc_attn ? "+attn-tcgen05-tf32x3+" : "+flash-fp32+") + gemm_variant_name(g2, gemm_mode, 148);
-        pl->want_split(2, QKV, D, M, gemm_mode);
-        pl->want_split(4, D, D, M, gemm_mode);
+    if (in.size() < 6 || out.size() < 1 || p.ints.size() < 4 || reg[in[0]].rank != 3) return pl;
+    const FxfTensor& x = reg[in[0]];
+    const int64_t B = x.shape[0], T = x.shape[1], H = p.ints[0], hd = p.ints[1], D = p.ints[2], QKV = p.ints[3], M = B * T;
+    if (H <= 0 || hd <= 0) return pl;
+    const int n = env.tp_size > 1 && H % env.tp_size == 0 ? env.tp_size : 1;  // heads must divide evenly, else replicate
+    const int64_t Hl = H / n, h0 = (n > 1 ? env.tp_rank : 0) * Hl, Dl = Hl * hd;
+    pl->heads_local = Hl;
+    pl->head0 = h0;
+    Slice& s_wq = pl->add(2, QKV, D);
+    Slice& s_bq = pl->add(3, QKV, 1);
+    Slice& s_wo = pl->add(4, D, D);
+    Slice& s_bo = pl->add(5, D, 1);
+    if (n > 1) {
+        for (Slice* s : {&s_wq, &s_bq}) {
+            s->n_ranges = 3;
+            for (int third = 0; third < 3; third++) {
+                s->row0[third] = third * D + h0 * hd;
+                s->nrow[third] = Dl;
+            }
+            s->whole = false;
+        }
+        s_wo.col0 = h0 * hd; s_wo.ncol = Dl; s_wo.whole = false;
+        s_bo.drop = env.tp_rank != 0;
+    } else if (env.tp_size > 1) {
+        pl->variant = "replicated ";
     }
+    pl->reserve(s_wq, want_tc(env, M, 3 * Dl, D));
+    pl->reserve(s_bq, false);
+    pl->reserve(s_wo, want_tc(env, M, D, Dl));
+    pl->reserve(s_bo, false);
+    pl->M = M;
+    pl->scratch_bytes = size_t(M) * size_t(3 * Dl + Dl) * sizeof(float);
+    const bool tc_attn = env.gemm_mode != FXF_GEMM_FP32_SIMT && hd == 64 && T % 4 == 0 && T >= 16 && Dl % 4 == 0;
+    if (tc_attn) pl->scratch_bytes += attention_tc_scratch_bytes(B, T, Hl);
+    pl->flops = 2.0 * M * double(3 * Dl) * D + 4.0 * double(B) * Hl * double(T) * T * hd + 2.0 * double(M) * D * Dl;
+    pl->bytes = 4.0 * (2.0 * double(M) * D + double(3 * Dl) * D + 3 * Dl + double(D) * Dl + D) + double(reg[in[1]].nbytes);
+    GemmArgs g1, g2;
+    g1.M = M; g1.N = 3 * Dl; g1.K = D;
+    g2.M = M; g2.N = D; g2.K = Dl;
+    pl->variant += gemm_variant_name(g1, env.gemm_mode, 148) + (tc_attn ? "+attn-tcgen05-tf32x3+" : "+flash-fp32+") + gemm_variant_name(g2, env.gemm_mode, 148);
     return pl;
 }
 

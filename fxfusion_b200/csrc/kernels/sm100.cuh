@@ -1,6 +1,6 @@
 // Thin inline-PTX wrappers for the sm_100a features the tensor-core kernels use: mbarriers with
 // bounded waits, TMA tile loads (cp.async.bulk.tensor), UMMA shared-memory / instruction descriptors,
-// tcgen05.mma / commit / ld / st, and the TF32 hi/lo split.  No load here uses cluster multicast.
+// tcgen05.mma / commit / ld / st, and the TF32 hi/lo split.  Every CTA issues its own plain tile loads.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>

@@ -7,7 +7,7 @@
 namespace fxf {
 
 #define FXF_DECL_KERNEL(name) int name(Registry&, const TensorIds&, const TensorIds&, const Params&, const NodePlan*, ExecCtx&)
-#define FXF_DECL_PLAN(name) std::unique_ptr<NodePlan> name(const Registry&, const TensorIds&, const TensorIds&, const Params&, int)
+#define FXF_DECL_PLAN(name) std::unique_ptr<NodePlan> name(const Registry&, const TensorIds&, const TensorIds&, const Params&, const PlanEnv&)
 
 FXF_DECL_KERNEL(k_conv2d);
 FXF_DECL_KERNEL(k_conv2d_relu);

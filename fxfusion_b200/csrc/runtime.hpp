@@ -46,6 +46,8 @@ struct ExecCtx {
     int sm_count = 148;
     int gemm_mode = FXF_GEMM_AUTO;
     int launches = 0;              // incremented by every kernel launch (host-side count)
+    int tp_rank = 0, tp_size = 1;  // tensor-parallel position; tp_size > 1 needs `comm`
+    void* comm = nullptr;          // fxf_comm* (NCCL communicator wrapper), owned by the caller
     // profiling: when `trace` is set every launch appends a record carrying the current tag
     std::vector<LaunchRecord>* trace = nullptr;
     int cur_node = -1;
@@ -70,8 +72,15 @@ struct NodePlan {
     virtual int prepare(Registry&, const TensorIds&, const TensorIds&, const Params&, ExecCtx&) { return 0; }
 };
 
+// What a plan builder needs to know about the engine it plans for.
+struct PlanEnv {
+    int gemm_mode = FXF_GEMM_AUTO;
+    int tp_rank = 0, tp_size = 1;     // tensor-parallel position of this engine
+    bool shard_output_cols = false;   // this node is the graph's final Linear and its columns are sharded over the ranks
+};
+
 using KernelFn = int (*)(Registry&, const TensorIds&, const TensorIds&, const Params&, const NodePlan*, ExecCtx&);
-using PlanFn = std::unique_ptr<NodePlan> (*)(const Registry&, const TensorIds&, const TensorIds&, const Params&, int gemm_mode);
+using PlanFn = std::unique_ptr<NodePlan> (*)(const Registry&, const TensorIds&, const TensorIds&, const Params&, const PlanEnv&);
 
 struct OpEntry {
     const char* name = nullptr;
@@ -193,6 +202,10 @@ struct AttnArgs {
     float scale_divisor = 1.f;
 };
 int launch_attention(const AttnArgs& a, ExecCtx& ctx);
+// Sum `n` floats in place over the tensor-parallel ranks (NCCL all-reduce on ctx.stream); no-op for tp_size 1.
+int tp_all_reduce_sum(float* buf, int64_t n, ExecCtx& ctx);
+// Gather `bytes` from every rank into recv[rank * bytes ...] (NCCL all-gather on ctx.stream).
+int tp_all_gather(const void* send, void* recv, int64_t bytes, ExecCtx& ctx);
 // tcgen05 path (head_dim 64): needs 6*B*T*H*64 floats of scratch for the split, per-head operand copies
 bool attention_tc_supported(const AttnArgs& a, int gemm_mode);
 size_t attention_tc_scratch_bytes(int64_t B, int64_t T, int64_t H);

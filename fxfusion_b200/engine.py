@@ -63,7 +63,11 @@ class ExecutionEngine:
     """Loads a graph file onto one GPU and runs it.  Not re-entrant (one run at a time)."""
 
     def __init__(self, graph_path: str, device: str = "cuda:0", *, use_cuda_graph: bool = True,
-                 precision: str = "auto") -> None:
+                 precision: str = "auto", comm=None, shard_output: bool = False) -> None:
+        """`comm`: a fxfusion_b200.tp.Communicator makes this a tensor-parallel engine (heads and FeedForward
+        hidden units sharded over its ranks; construction is collective).  `shard_output` additionally shards
+        the vocabulary of the final Linear: `outputs()` then holds only this rank's column block and
+        `argmax_scatter` / `decode_static` combine the ranks."""
         self._h = C.c_void_p()
         lib = _lib.lib()
         if precision not in _lib.GEMM_MODES:
@@ -72,10 +76,13 @@ class ExecutionEngine:
         opts.struct_size = C.sizeof(FxfEngineOptions)
         opts.use_cuda_graph = 1 if use_cuda_graph else 0
         opts.gemm_mode = _lib.GEMM_MODES[precision]
-        opts.tp_rank, opts.tp_size = 0, 1
+        opts.tp_rank, opts.tp_size = (comm.rank, comm.size) if comm is not None else (0, 1)
+        opts.tp_shard_output = 1 if (shard_output and comm is not None) else 0
+        self.comm = comm  # keeps the communicator alive as long as the engine
         self.device_index = _device_index(device)
         self.device = f"cuda:{self.device_index}"
-        _lib.check(lib.fxf_engine_create(str(graph_path).encode(), self.device_index, C.byref(opts), C.byref(self._h)))
+        _lib.check(lib.fxf_engine_create_tp(str(graph_path).encode(), self.device_index, C.byref(opts),
+                                            comm.handle if comm is not None else None, C.byref(self._h)))
         self._lib = lib
         self.num_inputs = lib.fxf_engine_num_inputs(self._h)
         self.num_outputs = lib.fxf_engine_num_outputs(self._h)
@@ -207,6 +214,11 @@ class ExecutionEngine:
         for i, a in enumerate(outputs):
             optrs[i] = a.ctypes.data if a is not None else None
         _lib.check(self._lib.fxf_engine_run_host(self._h, ptrs, self.num_inputs, optrs, self.num_outputs, self._stream()))
+
+    def argmax_scatter(self, tokens, current_len: int) -> None:
+        """tokens[:, current_len] = argmax of output 0 at position current_len - 1 (combined over the ranks when
+        the vocabulary is sharded)."""
+        _lib.check(self._lib.fxf_engine_argmax_scatter(self._h, C.c_void_p(tokens.data_ptr()), int(current_len), self._stream()))
 
     def decode_static(self, tokens, initial_len: int, pad_idx: int = 0):
         """Complete `tokens` (int64 CUDA tensor [B,T], prompt in the first `initial_len` columns) in

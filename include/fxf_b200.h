@@ -63,8 +63,10 @@ typedef struct FxfEngineOptions {
     int32_t use_cuda_graph;  /* 1: capture one CUDA Graph per forward and replay it */
     int32_t gemm_mode;       /* FXF_GEMM_* */
     int32_t tp_rank;         /* tensor-parallel rank of this engine (0 when tp_size == 1) */
-    int32_t tp_size;         /* number of tensor-parallel ranks (1 = none) */
-    int32_t reserved[11];
+    int32_t tp_size;         /* number of tensor-parallel ranks (1 = none); both are taken from the communicator */
+    int32_t tp_shard_output; /* 1: also shard the rows (vocabulary) of the final Linear over the ranks; each rank then
+                                writes only its column block of the output and fxf_engine_argmax_scatter combines them */
+    int32_t reserved[10];
 } FxfEngineOptions;
 
 typedef struct fxf_engine fxf_engine;
@@ -82,6 +84,21 @@ FXF_API const char* fxf_version(void);
  * (csrc/runtime/runtime_graph.cpp:8-18).  `opts` may be NULL. */
 FXF_API int fxf_engine_create(const char* graph_path, int device_ordinal, const FxfEngineOptions* opts,
                       fxf_engine** out_engine);
+/* Tensor-parallel engine (no counterpart in the reference, which is single-device).  Every rank loads the
+ * same graph file; MHA nodes keep H/n heads, FeedForward nodes F/n hidden units, their partial outputs are
+ * summed with one NCCL all-reduce each (on the run's stream, captured into the CUDA Graph); all other nodes
+ * are replicated.  `comm` must outlive the engine.  Creation is collective: all ranks call it together. */
+typedef struct fxf_comm fxf_comm;
+FXF_API int fxf_comm_unique_id(void* out_128_bytes);           /* rank 0; ship the 128 bytes to the others */
+FXF_API int fxf_comm_create(const void* unique_id_128_bytes, int rank, int size, int device_ordinal, fxf_comm** out);
+FXF_API void fxf_comm_destroy(fxf_comm* c);
+FXF_API int fxf_comm_rank(const fxf_comm* c);
+FXF_API int fxf_comm_size(const fxf_comm* c);
+FXF_API int fxf_engine_create_tp(const char* graph_path, int device_ordinal, const FxfEngineOptions* opts, fxf_comm* comm,
+                                 fxf_engine** out_engine);
+/* tokens[b, current_len] = argmax_v output0[b, current_len-1, v] for this engine, whether the vocabulary is
+ * sharded (candidates of all ranks are gathered and every rank writes the same token) or not. */
+FXF_API int fxf_engine_argmax_scatter(fxf_engine* e, int64_t* tokens, int current_len, void* stream);
 /* Same, from bytes already in memory (the engine copies what it needs). */
 FXF_API int fxf_engine_create_from_memory(const void* bytes, size_t nbytes, int device_ordinal,
                                   const FxfEngineOptions* opts, fxf_engine** out_engine);

@@ -1,0 +1,121 @@
+"""Worker for the tensor-parallel tests; launched with torch.distributed.run (one process per rank).
+
+    mode "cpu":  gloo ranks on the CPU check the sharding rule of fxfusion_b200.tp against the unsharded oracle
+                 kernels (an MHA node, a FeedForward node, a vocabulary-sharded argmax).
+    mode "gpu":  one GPU per rank; a tensor-parallel engine is compared with the CPU oracle (forward, greedy
+                 decode with the vocabulary sharded) and with the single-GPU engine on rank 0.
+"""
+import math
+import os
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from fxfusion_b200 import lowering, tp, wire
+from oracle.graph_oracle import KERNELS, GraphOracle, decode_static, make_static_buffer, static_decoder_mask
+
+
+def cpu_checks(rank, size):
+    g = torch.Generator().manual_seed(0)
+    B, T, H, hd, Fh = 2, 12, 4, 8, 64
+    D = H * hd
+    x = torch.randn(B, T, D, generator=g)
+    mask = torch.tril(torch.ones(T, T, dtype=torch.bool)).view(1, 1, T, T).expand(B, 1, T, T).contiguous()
+    wqkv, bqkv = torch.randn(3 * D, D, generator=g) / math.sqrt(D), torch.randn(3 * D, generator=g) * 0.1
+    wo, bo = torch.randn(D, D, generator=g) / math.sqrt(D), torch.randn(D, generator=g) * 0.1
+    # --- MHA: local heads only, partial output, all-reduce ---
+    sh = tp.shard_mha(wqkv.numpy(), bqkv.numpy(), wo.numpy(), bo.numpy(), H, rank, size)
+    Hl, Dl = sh["heads"], sh["heads"] * hd
+    qkv = F.linear(x, torch.from_numpy(sh["wqkv"]), torch.from_numpy(sh["bqkv"]))
+    q, k, v = (qkv[:, :, i * Dl:(i + 1) * Dl].view(B, T, Hl, hd).transpose(1, 2) for i in range(3))
+    s = (q @ k.transpose(-2, -1)) / math.sqrt(hd)
+    s = s.masked_fill(mask == 0, -math.inf)
+    ctx = (torch.softmax(s, -1) @ v).transpose(1, 2).contiguous().view(B, T, Dl)
+    part = F.linear(ctx, torch.from_numpy(np.ascontiguousarray(sh["wo"])), torch.from_numpy(sh["bo"]))
+    dist.all_reduce(part)
+    want = torch.zeros(B, T, D)
+    KERNELS[wire.OP["MHA"]]([x, mask, wqkv, bqkv, wo, bo, want], [0, 1, 2, 3, 4, 5], [6], [H, hd, D, 3 * D], [math.sqrt(hd)])
+    assert torch.allclose(part, want, atol=1e-5, rtol=1e-5), (part - want).abs().max()
+    # --- FeedForward: column-parallel then row-parallel ---
+    w1, b1 = torch.randn(Fh, D, generator=g) / math.sqrt(D), torch.randn(Fh, generator=g) * 0.1
+    w2, b2 = torch.randn(D, Fh, generator=g) / math.sqrt(Fh), torch.randn(D, generator=g) * 0.1
+    sf = tp.shard_feedforward(w1.numpy(), b1.numpy(), w2.numpy(), b2.numpy(), rank, size)
+    part = F.linear(torch.relu(F.linear(x, torch.from_numpy(sf["w1"]), torch.from_numpy(sf["b1"]))),
+                    torch.from_numpy(np.ascontiguousarray(sf["w2"])), torch.from_numpy(sf["b2"]))
+    dist.all_reduce(part)
+    want = torch.zeros(B, T, D)
+    KERNELS[wire.OP["FeedForward"]]([x, w1, b1, w2, b2, want], [0, 1, 2, 3, 4], [5], [], [])
+    assert torch.allclose(part, want, atol=1e-5, rtol=1e-5)
+    # --- vocabulary-sharded argmax: local candidates, gather, first maximum wins ---
+    V = 101
+    logits = torch.randn(B, V, generator=g)
+    logits[0, 7] = logits[0, 90] = 9.0  # a tie across shards: the lower index must win
+    v0, v1 = tp.vocab_range(V, rank, size)
+    local = logits[:, v0:v1]
+    cand = torch.stack([local.max(-1).values, (local.argmax(-1) + v0).float()], -1)
+    gathered = [torch.zeros_like(cand) for _ in range(size)]
+    dist.all_gather(gathered, cand)
+    allc = torch.stack(gathered)  # [size, B, 2]
+    best = allc[..., 0].max(0).values
+    idx = torch.where(allc[..., 0] == best, allc[..., 1], torch.full_like(best, float(V))).min(0).values.long()
+    assert torch.equal(idx, logits.argmax(-1)), (idx, logits.argmax(-1))
+    covered = sum(r1 - r0 for r0, r1 in (tp.vocab_range(V, r, size) for r in range(size)))
+    assert covered == V
+    # --- non-divisible head counts are replicated, not sharded ---
+    assert tp.head_range(12, rank, 8) == (0, 12) and tp.head_range(12, 1, 4) == (3, 6)
+
+
+def gpu_checks(rank, size, tmp):
+    from fxfusion_b200.engine import ExecutionEngine
+    torch.cuda.set_device(rank)
+    comm = tp.Communicator.from_process_group(rank)
+    cfg = lowering.GPTConfig(256, 4, 1000, 4, 2)  # 4 heads of 64: divides over 2 and 4 ranks
+    B, T, L0 = 4, 64, 40
+    graph = lowering.gpt_graph(cfg, lowering.gpt_params(cfg, 0), batch=B, seq=T, name="tp_gpt")
+    path = os.path.join(tmp, f"tp_gpt_{rank}.bin")
+    wire.dump(graph, path)
+    tokens = torch.from_numpy(lowering.decode_prompt(B, L0, cfg.vocab))
+    buf = make_static_buffer(tokens, T)
+    mask = static_decoder_mask(buf, L0)
+    oracle = GraphOracle(graph)
+    want = oracle.run([buf, mask])[0]
+    for precision in ("auto", "fp32_simt"):
+        eng = ExecutionEngine(path, f"cuda:{rank}", comm=comm, precision=precision)
+        got = eng.run([buf.cuda(), mask.cuda()])[0].cpu()
+        err = (got - want).abs().max().item()
+        assert err < 1e-4, f"rank {rank} {precision}: TP forward differs from the oracle by {err}"
+        assert eng.device_status() == 0
+        eng.close()
+    # greedy decode with the vocabulary sharded as well: tokens must equal the oracle's on every rank
+    eng = ExecutionEngine(path, f"cuda:{rank}", comm=comm, shard_output=True)
+    dev = buf.cuda()
+    eng.decode_static(dev, L0)
+    torch.cuda.synchronize()
+    want_tokens = decode_static(lambda b, m: oracle.run([b, m])[0], tokens, T)
+    assert torch.equal(dev.cpu(), want_tokens), f"rank {rank}: TP greedy tokens differ from the oracle"
+    eng.close()
+    comm.close()
+
+
+def main():
+    mode = sys.argv[1]
+    dist.init_process_group("gloo" if mode == "cpu" else "nccl")
+    rank, size = dist.get_rank(), dist.get_world_size()
+    if mode == "cpu":
+        cpu_checks(rank, size)
+    else:
+        gpu_checks(rank, size, sys.argv[2])
+    dist.barrier()
+    if rank == 0:
+        print(f"tp_worker {mode} ok on {size} ranks")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
