@@ -100,7 +100,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     const int num_tiles = p.tiles_m * p.tiles_n;
     constexpr uint32_t kStageBytes = uint32_t(BM * BK + 2 * BN * BK) * 4u;
     constexpr uint32_t kIdesc = umma_idesc_tf32(BM, BN);
-    constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators
+    constexpr uint32_t kTmemCols = 2 * BN <= 256 ? 256 : 512;  // two accumulators; allocations are powers of two
     volatile int* abort_flag = &s.abort_flag;
 
     if (threadIdx.x == 0) {
@@ -358,7 +358,7 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx) {
     }
     int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
     int grid = int(tiles < ctx.sm_count ? tiles : ctx.sm_count);
-    tag_launch(ctx, BN == 256 ? "gemm_tf32x3_tcgen05_128x256" : "gemm_tf32x3_tcgen05_128x128", 2.0 * double(a.M) * double(a.N) * double(a.K),
+    tag_launch(ctx, "gemm_tf32x3_tcgen05", 2.0 * double(a.M) * double(a.N) * double(a.K),
                4.0 * (double(a.M) * a.K + double(a.N) * a.K + double(a.N) + double(a.M) * a.N));
     gemm_tf32x3_kernel<BN, BK, STAGES><<<grid, kThreads, smem, ctx.stream>>>(mx, mhi, mlo, p);
     FXF_LAUNCHED(ctx);
@@ -382,16 +382,42 @@ bool gemm_tc_shape_ok(int64_t M, int64_t N, int64_t K) {
     return M >= 64 && N >= 64 && K >= 32 && K % 4 == 0 && M < (int64_t(1) << 31) && N < (int64_t(1) << 31) && K < (int64_t(1) << 31);
 }
 
+// Tile width.  A persistent CTA runs ceil(tiles / SMs) tiles back to back, so the launch time is that count
+// times the tile time (proportional to BN, with a small penalty for narrower tiles whose operand traffic per
+// flop is higher).  E.g. M = 8192 on 148 SMs: N = 768 gives 192 tiles of 256 (2 rounds) but 256 tiles of 192
+// (also 2 rounds, each 25 % shorter); N = 2304 is best at 256.
+int gemm_tc_pick_bn(int64_t M, int64_t N, int sm_count) {
+    if (N <= 128) return 128;
+    const int64_t tiles_m = (M + BM - 1) / BM;
+    const int cand[3] = {256, 192, 128};
+    const double penalty[3] = {1.0, 1.05, 1.25};
+    int best = 256;
+    double best_cost = 0;
+    for (int i = 0; i < 3; i++) {
+        int64_t tiles = tiles_m * ((N + cand[i] - 1) / cand[i]);
+        double cost = double((tiles + sm_count - 1) / sm_count) * cand[i] * penalty[i];
+        if (i == 0 || cost < best_cost * 0.9) {
+            best = cand[i];
+            best_cost = cost;
+        }
+    }
+    return best;
+}
+
 int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx) {
     FXF_CHECK(gemm_tc_supported(a), "tensor-core GEMM called with an unsupported problem");
-    // Debug override of the ring geometry for wide tiles: FXF_TC_RING=0 -> 2 slabs of 32 floats,
-    // FXF_TC_RING=1 (default) -> 4 slabs of 16 floats.  Same shared-memory footprint.
-    static const int ring = [] {
-        const char* e = std::getenv("FXF_TC_RING");
-        return e ? std::atoi(e) : 1;
+    // Debug override: FXF_TC_BN=256|192|128 forces the tile width.
+    static const int forced = [] {
+        const char* e = std::getenv("FXF_TC_BN");
+        return e ? std::atoi(e) : 0;
     }();
-    if (a.N > 128) return ring == 0 ? launch_tc<256, 32, 2>(a, ctx) : launch_tc<256, 16, 4>(a, ctx);
-    return launch_tc<128, 32, 3>(a, ctx);
+    int bn = forced ? forced : gemm_tc_pick_bn(a.M, a.N, ctx.sm_count);
+    if (a.N <= 128) bn = 128;
+    switch (bn) {
+        case 256: return launch_tc<256, 16, 4>(a, ctx);
+        case 192: return launch_tc<192, 16, 5>(a, ctx);
+        default: return launch_tc<128, 32, 3>(a, ctx);
+    }
 }
 
 int launch_split_tf32(const float* w, float* hi, float* lo, int64_t n, ExecCtx& ctx) {

@@ -41,7 +41,7 @@ int launch_gemm(const GemmArgs& a, ExecCtx& ctx) {
 }
 
 std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count) {
-    if (gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(a.M, a.N, a.K)) return a.N > 128 ? "tcgen05-tf32x3-128x256" : "tcgen05-tf32x3-128x128";
+    if (gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(a.M, a.N, a.K)) return "tcgen05-tf32x3-128x" + std::to_string(gemm_tc_pick_bn(a.M, a.N, sm_count));
     static const char* names[] = {"simt128x128", "simt64x64", "simt32x32"};
     return names[simt_tile_choice(a.M, a.N, sm_count)];
 }

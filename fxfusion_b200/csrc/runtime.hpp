@@ -185,6 +185,7 @@ int launch_gemm_simt(const GemmArgs& a, ExecCtx& ctx);
 int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx);
 bool gemm_tc_supported(const GemmArgs& a);
 bool gemm_tc_shape_ok(int64_t M, int64_t N, int64_t K);
+int gemm_tc_pick_bn(int64_t M, int64_t N, int sm_count);
 int launch_split_tf32(const float* w, float* hi, float* lo, int64_t n, ExecCtx& ctx);
 int simt_tile_choice(int64_t M, int64_t N, int sm_count);
 std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count);
