@@ -139,7 +139,7 @@ class ExecutionEngine:
 
     def profile_launches(self):
         """One traced forward: [{kernel, node, ms, flops, bytes}] per kernel launch."""
-        cap = self.launches_per_run + 16
+        cap = self.launches_per_run + 2 * self.num_nodes + 16  # collectives are traced too
         buf = (_lib.FxfLaunchInfo * cap)()
         n = C.c_int()
         _lib.check(self._lib.fxf_engine_profile_launches(self._h, self._stream(), buf, cap, C.byref(n)))
