@@ -385,8 +385,55 @@ def run_micro(args):
                       "tflops": flops / ms / 1e9, "gbs": nbytes / ms / 1e6, "note": "includes the per-call weight split of the tensor-core path"}), flush=True)
 
 
+def run_latency(args):
+    """Forward latency of the two small configurations (secondary metrics): c1 = MLP, 16 layers of width 512,
+    batch 32; c2 = GPT 4 layers d_model 256, batch 8 x seq 64.  CUDA-Graph replay, device-resident inputs."""
+    import torch
+    from fxfusion_b200 import lowering, wire
+    from fxfusion_b200.engine import ExecutionEngine
+    torch.cuda.set_device(0)
+    tmp = tempfile.TemporaryDirectory()
+    if args.workload == "c5":
+        nb = args.m if args.m != 8192 else 256
+        g = lowering.resnet50_graph(lowering.resnet50_params(0), batch=nb, name="c5_resnet50")
+        inputs = [torch.randn(nb, 3, 224, 224, generator=torch.Generator().manual_seed(0)).cuda()]
+        flops = sum(2.0 * float(np_.size) for np_ in ()) or 8.2e9 * nb
+        weight_bytes = 4.0 * sum(int(v.size) for v in lowering.resnet50_params(0).values())
+    elif args.workload == "c1":
+        g = lowering.mlp_graph(lowering.mlp_params(16, 512, 10, seed=0), batch=32, name="c1_mlp")
+        inputs = [torch.randn(32, 512, generator=torch.Generator().manual_seed(0)).cuda()]
+        flops, weight_bytes = 2.0 * 32 * 512 * (512 * 15 + 10), 4.0 * (512 * 512 * 15 + 512 * 10)
+    else:
+        cfg = lowering.GPT_C2
+        g = lowering.gpt_graph(cfg, lowering.gpt_params(cfg, 0), batch=8, seq=64, name="c2_gpt")
+        ids = torch.from_numpy(lowering.decode_prompt(8, 64, cfg.vocab))
+        inputs = [ids.cuda(), torch.tril(torch.ones(64, 64, dtype=torch.bool)).view(1, 1, 64, 64).expand(8, 1, 64, 64).contiguous().cuda()]
+        flops, weight_bytes = 3.62e9, 4.0 * sum(int(np_.size) for np_ in lowering.gpt_params(cfg, 0).values())
+    path = os.path.join(tmp.name, g.name + ".bin")
+    wire.dump(g, path)
+    eng = ExecutionEngine(path, "cuda:0", precision=args.precision)
+    for _ in range(max(args.warmup, 3)):
+        eng.run(inputs)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = max(args.steps, 1)
+    e0.record()
+    for _ in range(n):
+        eng.run(inputs)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / n
+    trace = eng.profile_launches()
+    print(json.dumps({"workload": args.workload, "forward_us": us, "items_per_s": (inputs[0].shape[0] / us * 1e6), "nodes": eng.num_nodes, "launches": eng.launches_per_run,
+                      "gflops_per_forward": flops / 1e9, "tflops": flops / us / 1e6, "weight_mb": weight_bytes / 1e6,
+                      "kernels_us": {r["kernel"]: round(sum(x["ms"] for x in trace if x["kernel"] == r["kernel"]) * 1e3, 2) for r in trace}}), flush=True)
+    eng.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="c3", choices=["c3", "c1", "c2", "c5"],
+                    help="c3 = the decode benchmark (default); c1 / c2 = forward latency of the small configs; c5 = ResNet-50 forward (batch --m, default 256)")
     ap.add_argument("--micro", default=None, choices=["linear", "layernorm", "add", "mha"], help="profile one op instead of the decode workload")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=3072)
@@ -402,6 +449,8 @@ def main():
     args = ap.parse_args()
     if args.micro:
         return run_micro(args)
+    if args.workload != "c3":
+        return run_latency(args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -186,6 +186,102 @@ gemm_tn_kernel(const float* __restrict__ x, const float* __restrict__ w, const f
     }
 }
 
+// Few-row problems (M <= 64: batch-sized MLP layers).  A 32x32 tile would leave all but a handful of SMs
+// idle and make each of them walk the whole K; here a CTA owns 32 rows x 8 columns, so N/8 CTAs stream
+// disjoint 8-row slices of the weight while the small activation block is re-read from L2.  One output per
+// thread, K staged through shared memory in slabs of 128 with register prefetch of the next slab.
+constexpr int SK_BM = 32, SK_BN = 8, SK_BK = 128, SK_PAD = 4;
+
+template <bool RELU>
+__global__ void __launch_bounds__(256) gemm_skinny_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                                                          float* __restrict__ out, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldo,
+                                                          int vec_in) {
+    __shared__ __align__(16) float xs[SK_BM][SK_BK + SK_PAD];
+    __shared__ __align__(16) float ws[SK_BN][SK_BK + SK_PAD];
+    const int tid = threadIdx.x, tm = tid >> 3, tn = tid & 7;
+    const int64_t row0 = int64_t(blockIdx.y) * SK_BM, col0 = int64_t(blockIdx.x) * SK_BN;
+    float4 rx[4], rw;
+    auto fetch = [&](int64_t k0) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int f = tid + i * 256, r = f >> 5, c = (f & 31) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            int64_t gr = row0 + r, gk = k0 + c;
+            if (gr < M) {
+                const float* p = x + gr * ldx + gk;
+                if (vec_in && gk + 3 < K) v = *reinterpret_cast<const float4*>(p);
+                else {
+                    if (gk < K) v.x = p[0];
+                    if (gk + 1 < K) v.y = p[1];
+                    if (gk + 2 < K) v.z = p[2];
+                    if (gk + 3 < K) v.w = p[3];
+                }
+            }
+            rx[i] = v;
+        }
+        {
+            int r = tid >> 5, c = (tid & 31) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            int64_t gr = col0 + r, gk = k0 + c;
+            if (gr < N) {
+                const float* p = w + gr * ldw + gk;
+                if (vec_in && gk + 3 < K) v = *reinterpret_cast<const float4*>(p);
+                else {
+                    if (gk < K) v.x = p[0];
+                    if (gk + 1 < K) v.y = p[1];
+                    if (gk + 2 < K) v.z = p[2];
+                    if (gk + 3 < K) v.w = p[3];
+                }
+            }
+            rw = v;
+        }
+    };
+    auto stash = [&]() {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int f = tid + i * 256, r = f >> 5, c = (f & 31) * 4;
+            *reinterpret_cast<float4*>(&xs[r][c]) = rx[i];
+        }
+        *reinterpret_cast<float4*>(&ws[tid >> 5][(tid & 31) * 4]) = rw;
+    };
+    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+    const int64_t slabs = (K + SK_BK - 1) / SK_BK;
+    if (slabs > 0) fetch(0);
+    for (int64_t s = 0; s < slabs; s++) {
+        __syncthreads();
+        stash();
+        __syncthreads();
+        if (s + 1 < slabs) fetch((s + 1) * SK_BK);
+#pragma unroll 8
+        for (int k = 0; k < SK_BK; k += 4) {
+            float4 a = *reinterpret_cast<const float4*>(&xs[tm][k]);
+            float4 b = *reinterpret_cast<const float4*>(&ws[tn][k]);
+            acc0 = fmaf(a.x, b.x, acc0);
+            acc1 = fmaf(a.y, b.y, acc1);
+            acc2 = fmaf(a.z, b.z, acc2);
+            acc3 = fmaf(a.w, b.w, acc3);
+        }
+    }
+    int64_t gr = row0 + tm, gc = col0 + tn;
+    if (gr < M && gc < N) {
+        float v = (acc0 + acc1) + (acc2 + acc3);
+        if (bias != nullptr) v += bias[gc];
+        if (RELU) v = v > 0.f ? v : (v != v ? v : 0.f);
+        out[gr * ldo + gc] = v;
+    }
+}
+
+int launch_skinny(const GemmArgs& a, ExecCtx& ctx) {
+    dim3 grid(unsigned((a.N + SK_BN - 1) / SK_BN), unsigned((a.M + SK_BM - 1) / SK_BM));
+    int vec_in = (a.ldx % 4 == 0 && a.ldw % 4 == 0 && aligned16(a.x) && aligned16(a.w)) ? 1 : 0;
+    if (a.relu)
+        gemm_skinny_kernel<true><<<grid, 256, 0, ctx.stream>>>(a.x, a.w, a.bias, a.out, a.M, a.N, a.K, a.ldx, a.ldw, a.ldo, vec_in);
+    else
+        gemm_skinny_kernel<false><<<grid, 256, 0, ctx.stream>>>(a.x, a.w, a.bias, a.out, a.M, a.N, a.K, a.ldx, a.ldw, a.ldo, vec_in);
+    FXF_LAUNCHED(ctx);
+    return 0;
+}
+
 template <int BM, int BN, int BK, int TM, int TN>
 int launch_cfg(const GemmArgs& a, ExecCtx& ctx) {
     dim3 grid(unsigned((a.N + BN - 1) / BN), unsigned((a.M + BM - 1) / BM));
@@ -202,8 +298,9 @@ int launch_cfg(const GemmArgs& a, ExecCtx& ctx) {
 
 }  // namespace
 
-// 0 = 128x128, 1 = 64x64, 2 = 32x32
+// 0 = 128x128, 1 = 64x64, 2 = 32x32, 3 = skinny 32x8
 int simt_tile_choice(int64_t M, int64_t N, int sm_count) {
+    if (M <= 64) return 3;
     int64_t big = ((M + 127) / 128) * ((N + 127) / 128);
     int64_t mid = ((M + 63) / 64) * ((N + 63) / 64);
     if (big >= sm_count) return 0;
@@ -214,10 +311,11 @@ int simt_tile_choice(int64_t M, int64_t N, int sm_count) {
 int launch_gemm_simt(const GemmArgs& a, ExecCtx& ctx) {
     if (a.M == 0 || a.N == 0) return 0;
     FXF_CHECK(a.M > 0 && a.N > 0 && a.K >= 0, "gemm: negative dimension");
-    static const char* names[] = {"gemm_fp32_simt128x128", "gemm_fp32_simt64x64", "gemm_fp32_simt32x32"};
+    static const char* names[] = {"gemm_fp32_simt128x128", "gemm_fp32_simt64x64", "gemm_fp32_simt32x32", "gemm_fp32_skinny32x8"};
     tag_launch(ctx, names[simt_tile_choice(a.M, a.N, ctx.sm_count)], 2.0 * double(a.M) * double(a.N) * double(a.K),
                4.0 * (double(a.M) * a.K + double(a.N) * a.K + double(a.N) + double(a.M) * a.N));
     switch (simt_tile_choice(a.M, a.N, ctx.sm_count)) {
+        case 3: return launch_skinny(a, ctx);
         case 0: return launch_cfg<128, 128, 16, 8, 8>(a, ctx);
         case 1: return launch_cfg<64, 64, 16, 4, 4>(a, ctx);
         default: return launch_cfg<32, 32, 32, 2, 2>(a, ctx);

@@ -42,7 +42,7 @@ int launch_gemm(const GemmArgs& a, ExecCtx& ctx) {
 
 std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count) {
     if (gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(a.M, a.N, a.K)) return "tcgen05-tf32x3-128x" + std::to_string(gemm_tc_pick_bn(a.M, a.N, sm_count));
-    static const char* names[] = {"simt128x128", "simt64x64", "simt32x32"};
+    static const char* names[] = {"simt128x128", "simt64x64", "simt32x32", "skinny32x8"};
     return names[simt_tile_choice(a.M, a.N, sm_count)];
 }
 
@@ -70,6 +70,7 @@ struct DensePlan : NodePlan {
     int n = 0;
     // dims the kernels need again
     int64_t M = 0, heads_local = 0, head0 = 0, n_local = 0, col_off = 0;
+    bool prepared = false;
 
     Slice& add(int input, int64_t rows, int64_t cols) {
         Slice& x = s[n++];
@@ -118,6 +119,7 @@ struct DensePlan : NodePlan {
                 x.lo = h + x.elems();
             }
         }
+        prepared = true;
         return 0;
     }
 };
@@ -150,7 +152,7 @@ int run_linear(Registry& reg, const TensorIds& in, const TensorIds& out, bool re
     FXF_CHECK(numel(b) == N, "%s: bias size does not match weight rows", who);
     FXF_CHECK(numel(o) == M * N, "%s: output size mismatch", who);
     const DensePlan* pl = dense(plan);
-    FXF_CHECK(pl != nullptr && pl->n == 2 && pl->s[0].ptr != nullptr, "%s: the node was not prepared", who);
+    FXF_CHECK(pl != nullptr && pl->n == 2 && pl->prepared, "%s: the node was not prepared", who);
     GemmArgs g;
     fill_gemm(g, static_cast<const float*>(x.ptr), pl->s[0], &pl->s[1], static_cast<float*>(o.ptr) + pl->col_off, M, K, N, relu);
     return launch_gemm(g, ctx);
@@ -206,7 +208,7 @@ int k_feedforward(Registry& reg, const TensorIds& in, const TensorIds& out, cons
     FXF_CHECK(numel(b1) == F && numel(b2) == P, "feedforward: bias sizes do not match");
     FXF_CHECK(numel(o) == M * P, "feedforward: output size mismatch");
     const DensePlan* pl = dense(plan);
-    FXF_CHECK(pl != nullptr && pl->n == 4 && pl->s[0].ptr != nullptr, "feedforward: the node was not prepared");
+    FXF_CHECK(pl != nullptr && pl->n == 4 && pl->prepared, "feedforward: the node was not prepared");
     const int64_t Fl = pl->s[0].rows();
     size_t need = size_t(M) * size_t(Fl) * sizeof(float);
     FXF_CHECK(ctx.scratch_bytes >= need && (need == 0 || ctx.scratch != nullptr), "feedforward: scratch too small (%zu < %zu bytes)", ctx.scratch_bytes, need);
@@ -279,7 +281,7 @@ int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params
         ms[tgt] = mask.shape[k] == 1 ? 0 : mask.stride[k];
     }
     const DensePlan* pl = dense(plan);
-    FXF_CHECK(pl != nullptr && pl->n == 4 && pl->s[0].ptr != nullptr, "mha: the node was not prepared");
+    FXF_CHECK(pl != nullptr && pl->n == 4 && pl->prepared, "mha: the node was not prepared");
     const int64_t Hl = pl->heads_local, Dl = Hl * hd, QKVl = 3 * Dl;
     size_t need = size_t(M) * size_t(QKVl + Dl) * sizeof(float);
     FXF_CHECK(ctx.scratch_bytes >= need && (need == 0 || ctx.scratch != nullptr), "mha: scratch too small (%zu < %zu bytes)", ctx.scratch_bytes, need);

@@ -313,3 +313,79 @@ def decode_prompt(batch: int, prompt_len: int, vocab: int, seed: int = 0) -> np.
     (reference py/tests/test_ops.py:423, layers/masks.py:52-55)."""
     rng = np.random.default_rng(seed + 1)
     return rng.integers(1, vocab, size=(batch, prompt_len), dtype=np.int64)
+
+
+# --------------------------------------------------------------------------------------
+# ResNet-50 (Conv+BN folded, NCHW) — reference lowering: 33 Conv2dRelu, 20 Conv2d, 16 AddRelu, MaxPool2d,
+# AdaptiveAvgPool2d, flatten (alias), Linear.  BatchNorm is folded into the convolution the way the
+# reference fusion pass does it (passes/fusion/matchers.py:125-174): w' = w * g / sqrt(var + eps) per output
+# channel, b' = beta - mean * g / sqrt(var + eps).
+# --------------------------------------------------------------------------------------
+_GRID_BLOCK = [1, 1, 1, 256, 1, 1]  # unused launch placeholders the reference serializer appends (serializer.py:188-203)
+RESNET50_LAYERS = ((64, 3, 1), (128, 4, 2), (256, 6, 2), (512, 3, 2))  # (width, blocks, stride of the first block)
+
+
+def _folded_conv(rng: np.random.Generator, c_out: int, c_in: int, k: int, eps: float = 1e-5) -> Tuple[np.ndarray, np.ndarray]:
+    w = _normal(rng, (c_out, c_in, k, k), math.sqrt(2.0 / (c_out * k * k)))          # Kaiming normal, fan_out
+    gamma, beta = 1.0 + _normal(rng, (c_out,), 0.1), _normal(rng, (c_out,), 0.1)
+    mean, var = _normal(rng, (c_out,), 0.1), rng.uniform(0.5, 1.5, size=(c_out,)).astype(np.float32)
+    scale = (gamma / np.sqrt(var + np.float32(eps))).astype(np.float32)
+    return (w * scale[:, None, None, None]).astype(np.float32), (beta - mean * scale).astype(np.float32)
+
+
+def resnet50_params(seed: int = 0, num_classes: int = 1000) -> Dict[str, np.ndarray]:
+    rng = np.random.default_rng(seed)
+    p: Dict[str, np.ndarray] = {}
+    p["stem.w"], p["stem.b"] = _folded_conv(rng, 64, 3, 7)
+    c_in = 64
+    for li, (width, blocks, _) in enumerate(RESNET50_LAYERS):
+        for bi in range(blocks):
+            pre = f"l{li}.b{bi}."
+            p[pre + "c1.w"], p[pre + "c1.b"] = _folded_conv(rng, width, c_in, 1)
+            p[pre + "c2.w"], p[pre + "c2.b"] = _folded_conv(rng, width, width, 3)
+            p[pre + "c3.w"], p[pre + "c3.b"] = _folded_conv(rng, width * 4, width, 1)
+            if bi == 0:
+                p[pre + "down.w"], p[pre + "down.b"] = _folded_conv(rng, width * 4, c_in, 1)
+            c_in = width * 4
+    bound = 1.0 / math.sqrt(c_in)
+    p["fc.w"], p["fc.b"] = _uniform(rng, (num_classes, c_in), bound), _uniform(rng, (num_classes,), bound)
+    return p
+
+
+def resnet50_graph(params: Dict[str, np.ndarray], batch: int, image: int = 224, name: str = "resnet50", alignment: int = 64) -> GraphRec:
+    b = GraphBuilder(name, alignment)
+
+    def conv(x, shape, w, bias, stride, pad, relu):
+        n, _, h, wd = shape
+        o, _, k, _ = w.shape
+        ho, wo = (h + 2 * pad - k) // stride + 1, (wd + 2 * pad - k) // stride + 1
+        wi, bi = b.const(w), b.const(bias)
+        out_shape = (n, o, ho, wo)
+        y = b.op("Conv2dRelu" if relu else "Conv2d", [x, wi, bi], out_shape, ints=[stride, stride, pad, pad, 1, 1, 1] + _GRID_BLOCK)
+        return y, out_shape
+
+    shape = (batch, 3, image, image)
+    x = b.input(shape, wire.DT_F32)
+    x, shape = conv(x, shape, params["stem.w"], params["stem.b"], 2, 3, True)
+    n, c, h, w = shape
+    shape = (n, c, (h + 2 - 3) // 2 + 1, (w + 2 - 3) // 2 + 1)
+    x = b.op("MaxPool2d", [x], shape, ints=[3, 3, 2, 2, 1, 1, 1, 1, 0] + _GRID_BLOCK)
+    for li, (width, blocks, stride) in enumerate(RESNET50_LAYERS):
+        for bi in range(blocks):
+            pre = f"l{li}.b{bi}."
+            s = stride if bi == 0 else 1
+            y, ys = conv(x, shape, params[pre + "c1.w"], params[pre + "c1.b"], 1, 0, True)
+            y, ys = conv(y, ys, params[pre + "c2.w"], params[pre + "c2.b"], s, 1, True)
+            y, ys = conv(y, ys, params[pre + "c3.w"], params[pre + "c3.b"], 1, 0, False)
+            identity = x
+            if bi == 0:
+                identity, _ = conv(x, shape, params[pre + "down.w"], params[pre + "down.b"], s, 0, False)
+            x = b.op("AddRelu", [y, identity], ys)
+            shape = ys
+    n, c, _, _ = shape
+    x = b.op("AdaptiveAvgPool2d", [x], (n, c, 1, 1), ints=[1, 1] + _GRID_BLOCK)
+    x = b.alias(x, (n, c))  # torch.flatten(x, 1)
+    wi, bi_ = b.const(params["fc.w"]), b.const(params["fc.b"])
+    x = b.op("Linear", [x, wi, bi_], (n, params["fc.w"].shape[0]))
+    b.output(x)
+    return b.finish()

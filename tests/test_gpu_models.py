@@ -164,3 +164,17 @@ def test_c3_decode_host_loop_equals_device_loop(built_lib, c3):
     assert torch.equal(dev, host)
     assert torch.equal(dev[:, :248].cpu(), tokens)
     assert (dev[:, 248:] >= 0).all() and (dev[:, 248:] < cfg.vocab).all()
+
+
+def test_c5_resnet50_matches_oracle_on_reduced_batch(built_lib, tmp_path):
+    """ResNet-50 (BatchNorm folded into 53 convolutions, NCHW) at batch 2: 72 nodes against the CPU oracle."""
+    g = lowering.resnet50_graph(lowering.resnet50_params(0), batch=2, name="c5_resnet50_b2")
+    x = torch.randn(2, 3, 224, 224, generator=torch.Generator().manual_seed(0))
+    eng = _engine(g, tmp_path)
+    got = eng.run([x.cuda()])[0].cpu()
+    want = GraphOracle(g).run([x])[0]
+    ok, info = compare_outputs(got, want, atol=ATOL, rtol=RTOL)
+    assert ok, info
+    assert eng.num_nodes == 72 and eng.arena_bytes == 27295744
+    assert torch.equal(got.argmax(-1), want.argmax(-1))
+    eng.close()

@@ -134,3 +134,17 @@ def test_mlp_builder_equals_reference_passes(reference_py):
             mods.append(nn.ReLU())
     _, ref = compile_with_reference(nn.Sequential(*mods).eval(), [torch.randn(4, 32)], model_name="mlp")
     _same_graph(ref, lowering.mlp_graph(layers, 4))
+
+
+def test_resnet50_builder_equals_reference_passes(reference_py):
+    """torchvision's ResNet-50 lowered by the reference passes == the direct builder: op sequence, params, tensor
+    table, offsets and arena size (27 295 744 bytes at batch 2)."""
+    torch = pytest.importorskip("torch")
+    tv = pytest.importorskip("torchvision")
+    from fxfusion_b200.compile_ref import compile_with_reference
+    _, ref = compile_with_reference(tv.models.resnet50(weights=None).eval(), [torch.randn(2, 3, 224, 224)], model_name="r50")
+    mine = lowering.resnet50_graph(lowering.resnet50_params(0), 2)
+    assert ref.arena_size == mine.arena_size == 27295744
+    assert [(n.op_code, n.input_ids, n.output_ids, n.int_params) for n in ref.nodes] == [(n.op_code, n.input_ids, n.output_ids, n.int_params) for n in mine.nodes]
+    for a, b in zip(ref.tensors, mine.tensors):
+        assert (a.id, a.kind, a.offset, a.size_bytes, tuple(a.shape), a.dtype, a.alias_of) == (b.id, b.kind, b.offset, b.size_bytes, tuple(b.shape), b.dtype, b.alias_of)
