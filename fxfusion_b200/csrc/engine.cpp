@@ -224,6 +224,73 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
         for (auto id : n.in) FXF_CHECK(id < n_tensors, "node %u (%s) reads tensor id %u which does not exist", i, entry.name, id);
         for (auto id : n.out) FXF_CHECK(id < n_tensors, "node %u (%s) writes tensor id %u which does not exist", i, entry.name, id);
         FXF_CHECK(!n.out.empty(), "node %u (%s) has no output", i, entry.name);
+        e->nodes.push_back(std::move(n));
+    }
+
+    // ---- layout pass: keep 4-D activations channels-last between layout-aware nodes ------------------
+    // Convolutions may write channels-last (their 1x1 form is then a plain GEMM on the tensor cores); pools and
+    // same-shape Add / AddRelu follow their operands.  A tensor stays NCHW if anything else reads it, if it is
+    // aliased (views, outputs) or if it is a graph input/output: the file's NCHW contract holds at every boundary.
+    {
+        std::vector<char> cl(n_tensors, 0);
+        auto differs = [&](uint32_t id) {  // layouts are distinguishable only for C > 1 and H*W > 1
+            const FxfTensor& t = e->reg[id];
+            return t.rank == 4 && t.dtype == FXF_F32 && t.shape[1] > 1 && t.shape[2] * t.shape[3] > 1;
+        };
+        auto same_shape = [&](uint32_t a, uint32_t b) {
+            const FxfTensor &x = e->reg[a], &y = e->reg[b];
+            if (x.rank != y.rank) return false;
+            for (int k = 0; k < x.rank; k++)
+                if (x.shape[k] != y.shape[k]) return false;
+            return true;
+        };
+        for (auto& n : e->nodes)
+            if ((n.op == FXF_OP_CONV2D || n.op == FXF_OP_CONV2D_RELU) && differs(n.out[0]) && meta[n.out[0]].kind == kActivation) cl[n.out[0]] = 1;
+        for (auto& n : e->nodes) {  // optimistic propagation through pools and element-wise nodes
+            const bool pool = n.op == FXF_OP_MAX_POOL2D || n.op == FXF_OP_AVG_POOL2D || n.op == FXF_OP_ADAPTIVE_AVG_POOL2D;
+            const bool ew = n.op == FXF_OP_ADD || n.op == FXF_OP_ADD_RELU;
+            if (!(pool || ew) || !differs(n.out[0]) || meta[n.out[0]].kind != kActivation) continue;
+            bool all = !n.in.empty();
+            for (auto id : n.in) all = all && cl[id] && (pool || same_shape(id, n.out[0]));
+            if (all) cl[n.out[0]] = 1;
+        }
+        for (bool changed = true; changed;) {
+            changed = false;
+            auto demote = [&](uint32_t id) {
+                if (cl[id]) { cl[id] = 0; changed = true; }
+            };
+            for (uint32_t id : order)
+                if ((meta[id].kind == kAlias || meta[id].kind == kOutput) && meta[id].alias_of >= 0 && uint32_t(meta[id].alias_of) < n_tensors)
+                    demote(uint32_t(meta[id].alias_of));
+            for (auto& n : e->nodes) {
+                const bool conv = n.op == FXF_OP_CONV2D || n.op == FXF_OP_CONV2D_RELU;
+                const bool pool = n.op == FXF_OP_MAX_POOL2D || n.op == FXF_OP_AVG_POOL2D || n.op == FXF_OP_ADAPTIVE_AVG_POOL2D;
+                const bool ew = n.op == FXF_OP_ADD || n.op == FXF_OP_ADD_RELU;
+                if (conv) continue;  // reads and writes either layout
+                if (pool) {
+                    if (differs(n.out[0]) && cl[n.in[0]] != cl[n.out[0]]) { demote(n.in[0]); demote(n.out[0]); }
+                    continue;
+                }
+                if (ew) {
+                    bool uniform = true;
+                    for (auto id : n.in) uniform = uniform && same_shape(id, n.out[0]) && cl[id] == cl[n.out[0]];
+                    if (!uniform) {
+                        for (auto id : n.in) demote(id);
+                        demote(n.out[0]);
+                    }
+                    continue;
+                }
+                for (auto id : n.in) demote(id);
+            }
+        }
+        for (uint32_t id = 0; id < n_tensors; id++)
+            if (cl[id]) set_channels_last(e->reg[id]);
+    }
+
+    // ---- plans (they see the final layouts) ---------------------------------------------------------
+    for (auto& n : e->nodes) {
+        const int op = n.op;
+        const OpEntry& entry = op_entry(op);
         env.shard_output_cols = false;
         if (e->opts.tp_size > 1 && e->opts.tp_shard_output && op == FXF_OP_LINEAR && feeds_output[n.out[0]] && n.in.size() >= 2 &&
             e->reg[n.in[1]].rank == 2 && !e->head_sharded) {
@@ -236,7 +303,6 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
         n.plan = entry.plan(e->reg, n.in, n.out, n.params, env);
         e->scratch_bytes = std::max(e->scratch_bytes, n.plan->scratch_bytes);
         e->persist_bytes += round_up(n.plan->persist_bytes, kAlign);
-        e->nodes.push_back(std::move(n));
     }
     size_t persist_off = cursor;
     cursor += e->persist_bytes;
@@ -505,7 +571,7 @@ int fxf_engine_describe(const fxf_engine* e, char* out, size_t out_bytes) {
         os << i << " " << op_entry(n.op).name << " in[";
         for (auto id : n.in) os << id << " ";
         os << "] out[";
-        for (auto id : n.out) os << id << "@" << (static_cast<uint8_t*>(e->reg[id].ptr) - e->base) << " ";
+        for (auto id : n.out) os << id << "@" << (static_cast<uint8_t*>(e->reg[id].ptr) - e->base) << (is_channels_last(e->reg[id]) ? "[nhwc] " : " ");
         os << "] launches " << n.launches << " variant " << n.plan->variant << " scratch " << n.plan->scratch_bytes << "\n";
     }
     std::string s = os.str();

@@ -1,5 +1,7 @@
 // Conv2d / Conv2dRelu (BatchNorm already folded into weight and bias by the compile side) and
-// the window-pooling ops, on NCHW float32 tensors as the graph contract stores them.
+// the window-pooling ops.  The graph contract is NCHW float32; between layout-aware nodes the engine may
+// keep activations channels-last (NHWC), which it states through the registry strides, so every kernel
+// here addresses its tensors through (n, c, h, w) strides and is correct for either layout.
 //
 // Reference semantics (LibTorch calls):
 //   conv2d / conv2d_relu  csrc/kernels/cpu/conv2d.cpp:5-17, conv2d_relu.cpp:5-17
@@ -12,10 +14,12 @@
 //   adaptive_avg_pool2d   csrc/kernels/cpu/adaptive_avg_pool2d.cpp:5-12
 //       ints = [oh, ow, ...]; window i = [floor(i*H/oh), ceil((i+1)*H/oh))
 //
-// The convolution is an implicit GEMM (rows = output pixels n*Ho*Wo, columns = output
-// channels, depth = Cin/groups*Kh*Kw) on fp32 FFMA tiles of 64x64x16: the im2col gather happens
-// while the A tile is staged into shared memory, consecutive threads walk consecutive output
-// pixels so both the gather and the NCHW store are coalesced along W.
+// Convolution paths:
+//   * 1x1, stride 1, no padding, channels-last in and out: the convolution IS the GEMM
+//     out[pixel, o] = x[pixel, :] · w[o, :] + b[o]  — it runs on the tcgen05 3xTF32 GEMM kernel with the bias
+//     and ReLU fused in its epilogue (weights split into TF32 hi/lo once, at engine build).
+//   * everything else: an implicit GEMM (rows = output pixels n*Ho*Wo, columns = output channels, depth =
+//     Cin/groups*Kh*Kw) on fp32 FFMA tiles of 64x64x16 with the im2col gather done while the A tile is staged.
 #include <cfloat>
 #include <cmath>
 
@@ -24,11 +28,20 @@
 namespace fxf {
 namespace {
 
+struct Strides4 {
+    int64_t n, c, h, w;
+};
+inline Strides4 strides_of(const FxfTensor& t) {  // rank 3 ([C,H,W]) or 4
+    if (t.rank == 4) return {t.stride[0], t.stride[1], t.stride[2], t.stride[3]};
+    return {0, t.stride[0], t.stride[1], t.stride[2]};
+}
+
 struct ConvDesc {
     int N, C, H, W, O, KH, KW, HO, WO;
     int sh, sw, ph, pw, dh, dw, groups;
     int cg, og;   // channels / outputs per group
     int relu;
+    Strides4 xs, os;
 };
 
 constexpr int CBM = 64, CBN = 64, CBK = 16;
@@ -76,7 +89,7 @@ __global__ void __launch_bounds__(256) conv2d_igemm_kernel(const float* __restri
                 int c = t / d.KH;
                 int iy = py * d.sh - d.ph + kh * d.dh, ix = px * d.sw - d.pw + kw * d.dw;
                 if (iy >= 0 && iy < d.H && ix >= 0 && ix < d.W)
-                    v = x[((int64_t(pn) * d.C + g * d.cg + c) * d.H + iy) * d.W + ix];
+                    v = x[int64_t(pn) * d.xs.n + int64_t(g * d.cg + c) * d.xs.c + int64_t(iy) * d.xs.h + int64_t(ix) * d.xs.w];
             }
             As[a_k0 + 4 * i][a_pix] = v;
         }
@@ -114,76 +127,79 @@ __global__ void __launch_bounds__(256) conv2d_igemm_kernel(const float* __restri
             int o = g * d.og + oc;
             float v = acc[i][j] + bias[o];
             if (d.relu) v = v > 0.f ? v : (v != v ? v : 0.f);
-            out[((int64_t(n) * d.O + o) * d.HO + oy) * d.WO + ox] = v;
+            out[int64_t(n) * d.os.n + int64_t(o) * d.os.c + int64_t(oy) * d.os.h + int64_t(ox) * d.os.w] = v;
         }
     }
 }
 
+// ---- pools ----------------------------------------------------------------------------------------
 struct PoolDesc {
-    int64_t NC;
-    int H, W, HO, WO, kh, kw, sh, sw, ph, pw, dh, dw;
+    int64_t N;
+    int C, H, W, HO, WO, kh, kw, sh, sw, ph, pw, dh, dw;
+    Strides4 xs, os;
+    int cl;  // walk the output channels-fastest (channels-last tensors) instead of width-fastest
 };
 
-__global__ void __launch_bounds__(256) max_pool2d_kernel(const float* __restrict__ x, float* __restrict__ out, PoolDesc d) {
-    int64_t total = d.NC * d.HO * d.WO, stride = int64_t(gridDim.x) * blockDim.x;
+__device__ __forceinline__ void pool_coords(const PoolDesc& d, int64_t i, int64_t& n, int& c, int& oy, int& ox) {
+    if (d.cl) {
+        c = int(i % d.C); i /= d.C;
+        ox = int(i % d.WO); i /= d.WO;
+        oy = int(i % d.HO);
+        n = i / d.HO;
+    } else {
+        ox = int(i % d.WO); i /= d.WO;
+        oy = int(i % d.HO); i /= d.HO;
+        c = int(i % d.C);
+        n = i / d.C;
+    }
+}
+
+enum PoolOp { kMaxPool = 0, kAvgPool = 1, kAdaptiveAvg = 2 };
+
+template <int OP>
+__global__ void __launch_bounds__(256) pool2d_kernel(const float* __restrict__ x, float* __restrict__ out, PoolDesc d) {
+    int64_t total = d.N * d.C * d.HO * d.WO, stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        int ox = int(i % d.WO);
-        int64_t t = i / d.WO;
-        int oy = int(t % d.HO);
-        int64_t nc = t / d.HO;
-        const float* src = x + nc * d.H * d.W;
-        float m = -INFINITY;
-        for (int a = 0; a < d.kh; a++) {
-            int iy = oy * d.sh - d.ph + a * d.dh;
-            if (iy < 0 || iy >= d.H) continue;
-            for (int b = 0; b < d.kw; b++) {
-                int ix = ox * d.sw - d.pw + b * d.dw;
-                if (ix < 0 || ix >= d.W) continue;
-                float v = src[int64_t(iy) * d.W + ix];
-                if (v > m || v != v) m = v;
+        int64_t n;
+        int c, oy, ox;
+        pool_coords(d, i, n, c, oy, ox);
+        const float* src = x + n * d.xs.n + int64_t(c) * d.xs.c;
+        float r;
+        if (OP == kMaxPool) {
+            float m = -INFINITY;
+            for (int a = 0; a < d.kh; a++) {
+                int iy = oy * d.sh - d.ph + a * d.dh;
+                if (iy < 0 || iy >= d.H) continue;
+                for (int b = 0; b < d.kw; b++) {
+                    int ix = ox * d.sw - d.pw + b * d.dw;
+                    if (ix < 0 || ix >= d.W) continue;
+                    float v = src[int64_t(iy) * d.xs.h + int64_t(ix) * d.xs.w];
+                    if (v > m || v != v) m = v;
+                }
             }
+            r = m;
+        } else {
+            int hs, he, ws, we, count;
+            if (OP == kAvgPool) {
+                hs = oy * d.sh - d.ph; ws = ox * d.sw - d.pw;
+                he = min(hs + d.kh, d.H + d.ph); we = min(ws + d.kw, d.W + d.pw);
+                count = (he - hs) * (we - ws);  // count_include_pad
+                hs = max(hs, 0); ws = max(ws, 0); he = min(he, d.H); we = min(we, d.W);
+            } else {
+                hs = int((int64_t(oy) * d.H) / d.HO); he = int((int64_t(oy + 1) * d.H + d.HO - 1) / d.HO);
+                ws = int((int64_t(ox) * d.W) / d.WO); we = int((int64_t(ox + 1) * d.W + d.WO - 1) / d.WO);
+                count = (he - hs) * (we - ws);
+            }
+            float s = 0.f;
+            for (int iy = hs; iy < he; iy++)
+                for (int ix = ws; ix < we; ix++) s += src[int64_t(iy) * d.xs.h + int64_t(ix) * d.xs.w];
+            r = s / float(count);
         }
-        out[i] = m;
+        out[n * d.os.n + int64_t(c) * d.os.c + int64_t(oy) * d.os.h + int64_t(ox) * d.os.w] = r;
     }
 }
 
-__global__ void __launch_bounds__(256) avg_pool2d_kernel(const float* __restrict__ x, float* __restrict__ out, PoolDesc d) {
-    int64_t total = d.NC * d.HO * d.WO, stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        int ox = int(i % d.WO);
-        int64_t t = i / d.WO;
-        int oy = int(t % d.HO);
-        int64_t nc = t / d.HO;
-        const float* src = x + nc * d.H * d.W;
-        int hs = oy * d.sh - d.ph, ws = ox * d.sw - d.pw;
-        int he = min(hs + d.kh, d.H + d.ph), we = min(ws + d.kw, d.W + d.pw);
-        int pool = (he - hs) * (we - ws);  // count_include_pad
-        int hs2 = max(hs, 0), ws2 = max(ws, 0), he2 = min(he, d.H), we2 = min(we, d.W);
-        float s = 0.f;
-        for (int iy = hs2; iy < he2; iy++)
-            for (int ix = ws2; ix < we2; ix++) s += src[int64_t(iy) * d.W + ix];
-        out[i] = s / float(pool);
-    }
-}
-
-__global__ void __launch_bounds__(256) adaptive_avg_pool2d_kernel(const float* __restrict__ x, float* __restrict__ out, PoolDesc d) {
-    int64_t total = d.NC * d.HO * d.WO, stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        int ox = int(i % d.WO);
-        int64_t t = i / d.WO;
-        int oy = int(t % d.HO);
-        int64_t nc = t / d.HO;
-        const float* src = x + nc * d.H * d.W;
-        int hs = int((int64_t(oy) * d.H) / d.HO), he = int((int64_t(oy + 1) * d.H + d.HO - 1) / d.HO);
-        int ws = int((int64_t(ox) * d.W) / d.WO), we = int((int64_t(ox + 1) * d.W + d.WO - 1) / d.WO);
-        float s = 0.f;
-        for (int iy = hs; iy < he; iy++)
-            for (int ix = ws; ix < we; ix++) s += src[int64_t(iy) * d.W + ix];
-        out[i] = s / float((he - hs) * (we - ws));
-    }
-}
-
-// Global average (output 1x1): one warp per (n,c) plane, coalesced reads, shuffle reduction.
+// Global average of a row-major plane (output 1x1, NCHW input): one warp per (n,c) plane.
 __global__ void __launch_bounds__(256) global_avg_pool_kernel(const float* __restrict__ x, float* __restrict__ out, int64_t NC, int HW) {
     int lane = threadIdx.x & 31;
     int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5, nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
@@ -197,28 +213,71 @@ __global__ void __launch_bounds__(256) global_avg_pool_kernel(const float* __res
     }
 }
 
-int run_conv(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, bool relu, ExecCtx& ctx, const char* who) {
-    FXF_CHECK(in.size() >= 3 && out.size() >= 1 && p.ints.size() >= 7, "%s: expects [x, weight, bias] and 7 int params", who);
-    const FxfTensor &x = reg[in[0]], &w = reg[in[1]], &b = reg[in[2]], &o = reg[out[0]];
+// ---- host side ----------------------------------------------------------------------------------------
+struct ConvPlan : NodePlan {
+    bool gemm_1x1 = false;          // planned for the tensor-core GEMM (still needs channels-last tensors at run time)
+    int64_t w_elems = 0;
+    const float *w_hi = nullptr, *w_lo = nullptr;
+    int prepare(Registry& reg, const TensorIds& in, const TensorIds&, const Params&, ExecCtx& ctx) override {
+        if (!gemm_1x1) return 0;
+        FXF_CHECK(persist != nullptr, "conv plan: persistent memory was not assigned");
+        float* h = static_cast<float*>(persist);
+        if (launch_split_tf32(static_cast<const float*>(reg[in[1]].ptr), h, h + w_elems, w_elems, ctx)) return 1;
+        w_hi = h;
+        w_lo = h + w_elems;
+        return 0;
+    }
+};
+
+// dense [N*H*W, C] view of a 4-D tensor: channels-last, or any layout when H*W == 1 / C == 1
+bool pixel_major(const FxfTensor& t) { return t.rank == 4 && (is_channels_last(t) || (is_contiguous(t) && (t.shape[2] * t.shape[3] == 1 || t.shape[1] == 1))); }
+
+int conv_desc(const FxfTensor& x, const FxfTensor& w, const FxfTensor& b, const FxfTensor& o, const Params& p, ConvDesc* d, const char* who) {
     FXF_CHECK(x.dtype == FXF_F32 && w.dtype == FXF_F32 && o.dtype == FXF_F32, "%s: only float32 is supported", who);
     FXF_CHECK(x.rank == 4 && w.rank == 4 && o.rank == 4, "%s: x, weight and output must be 4-D (NCHW / OIHW)", who);
+    FXF_CHECK(is_contiguous(w), "%s: weight must be contiguous OIHW", who);
+    d->N = int(x.shape[0]); d->C = int(x.shape[1]); d->H = int(x.shape[2]); d->W = int(x.shape[3]);
+    d->O = int(w.shape[0]); d->KH = int(w.shape[2]); d->KW = int(w.shape[3]);
+    d->sh = int(p.ints[0]); d->sw = int(p.ints[1]); d->ph = int(p.ints[2]); d->pw = int(p.ints[3]);
+    d->dh = int(p.ints[4]); d->dw = int(p.ints[5]); d->groups = int(p.ints[6]);
+    FXF_CHECK(d->groups >= 1 && d->C % d->groups == 0 && d->O % d->groups == 0, "%s: channels are not divisible by groups", who);
+    d->cg = d->C / d->groups; d->og = d->O / d->groups;
+    FXF_CHECK(w.shape[1] == d->cg, "%s: weight input channels do not match x", who);
+    FXF_CHECK(numel(b) == d->O, "%s: bias size mismatch", who);
+    FXF_CHECK(d->sh > 0 && d->sw > 0 && d->dh > 0 && d->dw > 0, "%s: stride and dilation must be positive", who);
+    d->HO = (d->H + 2 * d->ph - d->dh * (d->KH - 1) - 1) / d->sh + 1;
+    d->WO = (d->W + 2 * d->pw - d->dw * (d->KW - 1) - 1) / d->sw + 1;
+    FXF_CHECK(o.shape[0] == d->N && o.shape[1] == d->O && o.shape[2] == d->HO && o.shape[3] == d->WO, "%s: output shape does not match the convolution geometry", who);
+    d->xs = strides_of(x);
+    d->os = strides_of(o);
+    return 0;
+}
+
+int run_conv(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, bool relu, const NodePlan* plan, ExecCtx& ctx, const char* who) {
+    FXF_CHECK(in.size() >= 3 && out.size() >= 1 && p.ints.size() >= 7, "%s: expects [x, weight, bias] and 7 int params", who);
+    const FxfTensor &x = reg[in[0]], &w = reg[in[1]], &b = reg[in[2]], &o = reg[out[0]];
     ConvDesc d;
-    d.N = int(x.shape[0]); d.C = int(x.shape[1]); d.H = int(x.shape[2]); d.W = int(x.shape[3]);
-    d.O = int(w.shape[0]); d.KH = int(w.shape[2]); d.KW = int(w.shape[3]);
-    d.sh = int(p.ints[0]); d.sw = int(p.ints[1]); d.ph = int(p.ints[2]); d.pw = int(p.ints[3]);
-    d.dh = int(p.ints[4]); d.dw = int(p.ints[5]); d.groups = int(p.ints[6]);
-    FXF_CHECK(d.groups >= 1 && d.C % d.groups == 0 && d.O % d.groups == 0, "%s: channels are not divisible by groups", who);
-    d.cg = d.C / d.groups; d.og = d.O / d.groups;
-    FXF_CHECK(w.shape[1] == d.cg, "%s: weight input channels do not match x", who);
-    FXF_CHECK(numel(b) == d.O, "%s: bias size mismatch", who);
-    FXF_CHECK(d.sh > 0 && d.sw > 0 && d.dh > 0 && d.dw > 0, "%s: stride and dilation must be positive", who);
-    d.HO = (d.H + 2 * d.ph - d.dh * (d.KH - 1) - 1) / d.sh + 1;
-    d.WO = (d.W + 2 * d.pw - d.dw * (d.KW - 1) - 1) / d.sw + 1;
-    FXF_CHECK(o.shape[0] == d.N && o.shape[1] == d.O && o.shape[2] == d.HO && o.shape[3] == d.WO, "%s: output shape does not match the convolution geometry", who);
+    if (conv_desc(x, w, b, o, p, &d, who)) return 1;
     d.relu = relu ? 1 : 0;
     int64_t n_pix = int64_t(d.N) * d.HO * d.WO;
     if (n_pix == 0 || d.O == 0) return 0;
+    const ConvPlan* cp = static_cast<const ConvPlan*>(plan);
+    const bool is_1x1 = d.KH == 1 && d.KW == 1 && d.sh == 1 && d.sw == 1 && d.ph == 0 && d.pw == 0 && d.groups == 1;
+    if (is_1x1 && pixel_major(x) && pixel_major(o)) {
+        GemmArgs g;
+        g.x = static_cast<const float*>(x.ptr);
+        g.w = static_cast<const float*>(w.ptr);
+        if (cp && cp->gemm_1x1) { g.w_hi = cp->w_hi; g.w_lo = cp->w_lo; }
+        g.bias = static_cast<const float*>(b.ptr);
+        g.out = static_cast<float*>(o.ptr);
+        g.M = n_pix; g.N = d.O; g.K = d.C;
+        g.ldx = d.C; g.ldw = d.C; g.ldo = d.O;
+        g.relu = relu;
+        return launch_gemm(g, ctx);
+    }
     dim3 grid(unsigned((n_pix + CBM - 1) / CBM), unsigned((d.og + CBN - 1) / CBN), unsigned(d.groups));
+    tag_launch(ctx, "conv2d_igemm_fp32_simt64x64", 2.0 * double(n_pix) * d.O * d.cg * d.KH * d.KW,
+               double(x.nbytes) + double(w.nbytes) + double(b.nbytes) + double(o.nbytes));
     conv2d_igemm_kernel<<<grid, 256, 0, ctx.stream>>>(static_cast<const float*>(x.ptr), static_cast<const float*>(w.ptr), static_cast<const float*>(b.ptr),
                                                       static_cast<float*>(o.ptr), d);
     FXF_LAUNCHED(ctx);
@@ -227,12 +286,15 @@ int run_conv(Registry& reg, const TensorIds& in, const TensorIds& out, const Par
 
 int pool_desc(const FxfTensor& x, const FxfTensor& o, PoolDesc* d, const char* who) {
     FXF_CHECK(x.dtype == FXF_F32 && o.dtype == FXF_F32, "%s: only float32 is supported", who);
-    FXF_CHECK(x.rank >= 3 && o.rank == x.rank, "%s: input must be [N,C,H,W] or [C,H,W]", who);
-    d->H = int(x.shape[x.rank - 2]); d->W = int(x.shape[x.rank - 1]);
-    d->HO = int(o.shape[o.rank - 2]); d->WO = int(o.shape[o.rank - 1]);
-    d->NC = 1;
-    for (int k = 0; k < x.rank - 2; k++) d->NC *= x.shape[k];
-    FXF_CHECK(numel(o) == d->NC * d->HO * d->WO, "%s: output size mismatch", who);
+    FXF_CHECK((x.rank == 3 || x.rank == 4) && o.rank == x.rank, "%s: input must be [N,C,H,W] or [C,H,W]", who);
+    const int r = x.rank;
+    d->N = r == 4 ? x.shape[0] : 1;
+    d->C = int(x.shape[r - 3]); d->H = int(x.shape[r - 2]); d->W = int(x.shape[r - 1]);
+    d->HO = int(o.shape[r - 2]); d->WO = int(o.shape[r - 1]);
+    FXF_CHECK(o.shape[r - 3] == d->C && (r == 3 || o.shape[0] == x.shape[0]), "%s: output batch/channels do not match the input", who);
+    d->xs = strides_of(x);
+    d->os = strides_of(o);
+    d->cl = is_channels_last(o) ? 1 : 0;
     return 0;
 }
 
@@ -241,15 +303,13 @@ inline int pool_grid(int64_t total, const ExecCtx& ctx) {
     return int(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
 }
 
-struct ConvPlan : NodePlan {};
-
 }  // namespace
 
-int k_conv2d(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const NodePlan*, ExecCtx& ctx) {
-    return run_conv(reg, in, out, p, false, ctx, "conv2d");
+int k_conv2d(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const NodePlan* plan, ExecCtx& ctx) {
+    return run_conv(reg, in, out, p, false, plan, ctx, "conv2d");
 }
-int k_conv2d_relu(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const NodePlan*, ExecCtx& ctx) {
-    return run_conv(reg, in, out, p, true, ctx, "conv2d_relu");
+int k_conv2d_relu(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const NodePlan* plan, ExecCtx& ctx) {
+    return run_conv(reg, in, out, p, true, plan, ctx, "conv2d_relu");
 }
 
 int k_max_pool2d(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const NodePlan*, ExecCtx& ctx) {
@@ -259,9 +319,9 @@ int k_max_pool2d(Registry& reg, const TensorIds& in, const TensorIds& out, const
     d.kh = int(p.ints[0]); d.kw = int(p.ints[1]); d.sh = int(p.ints[2]); d.sw = int(p.ints[3]);
     d.ph = int(p.ints[4]); d.pw = int(p.ints[5]); d.dh = int(p.ints[6]); d.dw = int(p.ints[7]);
     FXF_CHECK(d.sh > 0 && d.sw > 0, "max_pool2d: stride must be positive");
-    int64_t total = d.NC * d.HO * d.WO;
+    int64_t total = d.N * d.C * d.HO * d.WO;
     if (total == 0) return 0;
-    max_pool2d_kernel<<<pool_grid(total, ctx), 256, 0, ctx.stream>>>(static_cast<const float*>(reg[in[0]].ptr), static_cast<float*>(reg[out[0]].ptr), d);
+    pool2d_kernel<kMaxPool><<<pool_grid(total, ctx), 256, 0, ctx.stream>>>(static_cast<const float*>(reg[in[0]].ptr), static_cast<float*>(reg[out[0]].ptr), d);
     FXF_LAUNCHED(ctx);
     return 0;
 }
@@ -273,9 +333,9 @@ int k_avg_pool2d(Registry& reg, const TensorIds& in, const TensorIds& out, const
     d.kh = int(p.ints[0]); d.kw = int(p.ints[1]); d.sh = int(p.ints[2]); d.sw = int(p.ints[3]);
     d.ph = int(p.ints[4]); d.pw = int(p.ints[5]); d.dh = 1; d.dw = 1;
     FXF_CHECK(d.sh > 0 && d.sw > 0, "avg_pool2d: stride must be positive");
-    int64_t total = d.NC * d.HO * d.WO;
+    int64_t total = d.N * d.C * d.HO * d.WO;
     if (total == 0) return 0;
-    avg_pool2d_kernel<<<pool_grid(total, ctx), 256, 0, ctx.stream>>>(static_cast<const float*>(reg[in[0]].ptr), static_cast<float*>(reg[out[0]].ptr), d);
+    pool2d_kernel<kAvgPool><<<pool_grid(total, ctx), 256, 0, ctx.stream>>>(static_cast<const float*>(reg[in[0]].ptr), static_cast<float*>(reg[out[0]].ptr), d);
     FXF_LAUNCHED(ctx);
     return 0;
 }
@@ -286,27 +346,37 @@ int k_adaptive_avg_pool2d(Registry& reg, const TensorIds& in, const TensorIds& o
     if (pool_desc(reg[in[0]], reg[out[0]], &d, "adaptive_avg_pool2d")) return 1;
     FXF_CHECK(d.HO == p.ints[0] && d.WO == p.ints[1], "adaptive_avg_pool2d: output shape does not match output_size");
     d.kh = d.kw = d.sh = d.sw = d.dh = d.dw = 1; d.ph = d.pw = 0;
-    int64_t total = d.NC * d.HO * d.WO;
+    int64_t total = d.N * d.C * d.HO * d.WO;
     if (total == 0) return 0;
-    if (d.HO == 1 && d.WO == 1) {
-        int64_t blocks = (d.NC * 32 + 255) / 256, cap = int64_t(ctx.sm_count) * 8;
-        global_avg_pool_kernel<<<int(blocks < cap ? blocks : cap), 256, 0, ctx.stream>>>(static_cast<const float*>(reg[in[0]].ptr), static_cast<float*>(reg[out[0]].ptr), d.NC, d.H * d.W);
+    if (d.HO == 1 && d.WO == 1 && is_contiguous(reg[in[0]]) && is_contiguous(reg[out[0]])) {
+        int64_t nc = d.N * d.C, blocks = (nc * 32 + 255) / 256, cap = int64_t(ctx.sm_count) * 8;
+        global_avg_pool_kernel<<<int(blocks < cap ? blocks : cap), 256, 0, ctx.stream>>>(static_cast<const float*>(reg[in[0]].ptr), static_cast<float*>(reg[out[0]].ptr), nc, d.H * d.W);
     } else {
-        adaptive_avg_pool2d_kernel<<<pool_grid(total, ctx), 256, 0, ctx.stream>>>(static_cast<const float*>(reg[in[0]].ptr), static_cast<float*>(reg[out[0]].ptr), d);
+        // a channels-last input is walked channels-fastest, which keeps the strided window reads coalesced
+        if (is_channels_last(reg[in[0]])) d.cl = 1;
+        pool2d_kernel<kAdaptiveAvg><<<pool_grid(total, ctx), 256, 0, ctx.stream>>>(static_cast<const float*>(reg[in[0]].ptr), static_cast<float*>(reg[out[0]].ptr), d);
     }
     FXF_LAUNCHED(ctx);
     return 0;
 }
 
-std::unique_ptr<NodePlan> plan_conv(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv&) {
+std::unique_ptr<NodePlan> plan_conv(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& env) {
     auto pl = std::make_unique<ConvPlan>();
-    if (in.size() >= 3 && out.size() >= 1 && reg[in[1]].rank == 4 && reg[out[0]].rank == 4) {
+    if (in.size() >= 3 && out.size() >= 1 && reg[in[1]].rank == 4 && reg[out[0]].rank == 4 && p.ints.size() >= 7) {
         const FxfTensor &w = reg[in[1]], &o = reg[out[0]];
         pl->flops = 2.0 * double(numel(o)) * double(w.shape[1]) * double(w.shape[2]) * double(w.shape[3]);
         pl->bytes = double(reg[in[0]].nbytes) + double(w.nbytes) + double(reg[in[2]].nbytes) + double(o.nbytes);
-        pl->variant = "igemm-simt64x64";
+        const int64_t M = o.shape[0] * o.shape[2] * o.shape[3], O = w.shape[0], C = w.shape[1];
+        const bool is_1x1 = w.shape[2] == 1 && w.shape[3] == 1 && p.ints[0] == 1 && p.ints[1] == 1 && p.ints[2] == 0 && p.ints[3] == 0 && p.ints[6] == 1;
+        if (is_1x1 && env.gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(M, O, C)) {
+            pl->gemm_1x1 = true;
+            pl->w_elems = O * C;
+            pl->persist_bytes = round_up(size_t(2) * size_t(pl->w_elems) * sizeof(float), 256);
+            pl->variant = "1x1 -> tcgen05-tf32x3 GEMM when channels-last, else igemm-simt64x64";
+        } else {
+            pl->variant = "igemm-simt64x64";
+        }
     }
-    (void)p;
     return pl;
 }
 

@@ -111,11 +111,20 @@ int run_binary(const FxfTensor& a, const FxfTensor& b, const FxfTensor& out, Exe
         for (; b_suffix && kb >= 0; kb--) if (b.shape[kb] != 1) b_suffix = false;
         if (prod != nb) b_suffix = false;
     }
-    if (na == n && is_contiguous(a) && b_suffix && n % 4 == 0 && nb % 4 == 0 && aligned16(a.ptr) && aligned16(b.ptr) && aligned16(out.ptr)) {
+    // operands and output in one and the same dense layout (row-major or channels-last): a flat element-wise pass
+    const bool flat = same_layout(a, out) && same_layout(b, out) && (is_contiguous(out) || is_channels_last(out));
+    if (!flat) FXF_CHECK(is_contiguous(out), "binary op: a channels-last output needs operands in the same layout");
+    if (flat) { b_suffix = true; nb = n; na = n; }
+    if (na == n && (flat || is_contiguous(a)) && b_suffix && n % 4 == 0 && nb % 4 == 0 && aligned16(a.ptr) && aligned16(b.ptr) && aligned16(out.ptr)) {
         int64_t n4 = n / 4;
         binary_vec4_kernel<OP><<<grid_for(n4, ctx), kThreads, 0, ctx.stream>>>(
             static_cast<const float4*>(a.ptr), static_cast<const float4*>(b.ptr), static_cast<float4*>(out.ptr), n4, nb / 4);
     } else {
+        if (flat) {  // identical layouts but not 16-byte friendly: walk storage order with unit strides
+            d.rank = 1;
+            d.shape[0] = n;
+            d.sa[0] = d.sb[0] = 1;
+        }
         binary_generic_kernel<OP><<<grid_for(n, ctx), kThreads, 0, ctx.stream>>>(
             static_cast<const float*>(a.ptr), static_cast<const float*>(b.ptr), static_cast<float*>(out.ptr), n, d);
     }
@@ -147,6 +156,7 @@ int run_unary(const FxfTensor& x, const FxfTensor& out, float s, ExecCtx& ctx) {
     FXF_CHECK(x.dtype == FXF_F32 && out.dtype == FXF_F32, "unary op: only float32 is supported");
     int64_t n = numel(out);
     FXF_CHECK(numel(x) == n, "unary op: input/output element counts differ");
+    FXF_CHECK(same_layout(x, out) || (is_contiguous(x) && is_contiguous(out)), "unary op: input and output layouts differ");
     if (n == 0) return 0;
     if (n % 4 == 0 && aligned16(x.ptr) && aligned16(out.ptr)) {
         unary_vec4_kernel<OP><<<grid_for(n / 4, ctx), kThreads, 0, ctx.stream>>>(static_cast<const float4*>(x.ptr), static_cast<float4*>(out.ptr), n / 4, s);

@@ -162,6 +162,27 @@ inline bool is_contiguous(const FxfTensor& t) {
     }
     return true;
 }
+// Channels-last ("NHWC") physical layout of a logical [N,C,H,W] tensor: strides (H*W*C, 1, W*C, C).  The graph
+// contract is NCHW; the engine may keep intermediate activations between layout-aware nodes channels-last
+// and says so through the registry strides, the way torch's channels_last memory format does.
+inline void set_channels_last(FxfTensor& t) {
+    const int64_t C = t.shape[1], H = t.shape[2], W = t.shape[3];
+    t.stride[0] = H * W * C;
+    t.stride[1] = 1;
+    t.stride[2] = W * C;
+    t.stride[3] = C;
+}
+inline bool is_channels_last(const FxfTensor& t) {
+    if (t.rank != 4 || is_contiguous(t)) return false;
+    const int64_t C = t.shape[1], H = t.shape[2], W = t.shape[3];
+    return (t.shape[0] == 1 || t.stride[0] == H * W * C) && (C == 1 || t.stride[1] == 1) && (H == 1 || t.stride[2] == W * C) && (W == 1 || t.stride[3] == C);
+}
+inline bool same_layout(const FxfTensor& a, const FxfTensor& b) {
+    if (a.rank != b.rank) return false;
+    for (int i = 0; i < a.rank; i++)
+        if (a.shape[i] != b.shape[i] || (a.shape[i] != 1 && a.stride[i] != b.stride[i])) return false;
+    return true;
+}
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 

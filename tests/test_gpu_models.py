@@ -166,14 +166,25 @@ def test_c3_decode_host_loop_equals_device_loop(built_lib, c3):
     assert (dev[:, 248:] >= 0).all() and (dev[:, 248:] < cfg.vocab).all()
 
 
-def test_c5_resnet50_matches_oracle_on_reduced_batch(built_lib, tmp_path):
-    """ResNet-50 (BatchNorm folded into 53 convolutions, NCHW) at batch 2: 72 nodes against the CPU oracle."""
+@pytest.mark.parametrize("precision", ["fp32_simt", "auto"])
+def test_c5_resnet50_matches_oracle_on_reduced_batch(built_lib, tmp_path, precision):
+    """ResNet-50 (BatchNorm folded into 53 convolutions) at batch 2: 72 nodes against the CPU oracle.  The engine
+    keeps the activations channels-last internally; input and output stay NCHW.  With random weights and no
+    normalisation the logits have a standard deviation near 100, so the tensor-core path (whose fp32 accumulator
+    truncates, error ~4e-8 * K per product chain, compounding over 36 1x1 convolutions) is held to 1e-4 of the
+    output SCALE plus the element-wise rule at rel 1e-2; the fp32 FFMA path meets the element-wise 1e-4 / 1e-3 rule."""
     g = lowering.resnet50_graph(lowering.resnet50_params(0), batch=2, name="c5_resnet50_b2")
     x = torch.randn(2, 3, 224, 224, generator=torch.Generator().manual_seed(0))
-    eng = _engine(g, tmp_path)
+    eng = _engine(g, tmp_path, precision=precision)
+    assert "[nhwc]" in eng.describe()
     got = eng.run([x.cuda()])[0].cpu()
     want = GraphOracle(g).run([x])[0]
-    ok, info = compare_outputs(got, want, atol=ATOL, rtol=RTOL)
+    if precision == "fp32_simt":
+        ok, info = compare_outputs(got, want, atol=ATOL, rtol=RTOL)
+    else:
+        scale = want.abs().max().item()
+        assert (got - want).abs().max().item() <= 1e-4 * scale, ((got - want).abs().max().item(), scale)
+        ok, info = compare_outputs(got, want, atol=1e-4 * scale, rtol=1e-2)
     assert ok, info
     assert eng.num_nodes == 72 and eng.arena_bytes == 27295744
     assert torch.equal(got.argmax(-1), want.argmax(-1))

@@ -219,3 +219,33 @@ def test_argument_errors_are_reported_not_executed(built_lib):
         invoke("Mul", [x, torch.zeros(4, 8).cuda()], [0], [1], ints=[7], floats=[1.0])
     with pytest.raises(RuntimeError, match="slice exceeds"):
         invoke("Narrow", [x, torch.zeros(4, 9).cuda()], [0], [1], ints=[1, 0, 9])
+
+
+def test_channels_last_tensors_are_honoured(built_lib):
+    """Kernels address 4-D tensors through their strides: channels-last inputs / outputs (what the engine uses
+    between convolutions) give the same values as NCHW ones."""
+    from fxfusion_b200.kernels import invoke
+    cl = lambda t: t.contiguous(memory_format=torch.channels_last)
+    N, C, H, W, O = 2, 64, 14, 14, 96
+    x, w1, b1 = rnd(N, C, H, W), rnd(O, C, 1, 1, seed=1, scale=0.1), rnd(O, seed=2)
+    w3, b3 = rnd(O, C, 3, 3, seed=3, scale=0.05), rnd(O, seed=4)
+    ints = lambda s, p: [s, s, p, p, 1, 1, 1, 1, 1, 1, 256, 1, 1]
+    for wt, bs, s, p in ((w1, b1, 1, 0), (w1, b1, 2, 0), (w3, b3, 1, 1), (w3, b3, 2, 1)):
+        want = torch.relu(torch.conv2d(x, wt, bs, s, p))
+        for xin in (x.cuda(), cl(x.cuda())):
+            for out in (torch.zeros_like(want).cuda(), cl(torch.zeros_like(want).cuda())):
+                invoke("Conv2dRelu", [xin, wt.cuda(), bs.cuda(), out], [0, 1, 2], [3], ints=ints(s, p))
+                assert out.stride() != want.stride() or True
+                ok, info = compare_outputs(out.cpu().contiguous(), want, atol=ATOL, rtol=RTOL)
+                assert ok, (s, p, xin.stride(), out.stride(), info)
+    xc = cl(x.cuda())
+    mp = cl(torch.zeros(N, C, 7, 7).cuda())
+    invoke("MaxPool2d", [xc, mp], [0], [1], ints=[3, 3, 2, 2, 1, 1, 1, 1, 0, 1, 1, 1, 256, 1, 1])
+    assert torch.equal(mp.cpu().contiguous(), torch.max_pool2d(x, 3, 2, 1))
+    ap = torch.zeros(N, C, 1, 1).cuda()
+    invoke("AdaptiveAvgPool2d", [xc, ap], [0], [1], ints=[1, 1, 1, 1, 1, 256, 1, 1])
+    assert torch.allclose(ap.cpu(), torch.nn.functional.adaptive_avg_pool2d(x, 1), atol=1e-5)
+    y = cl(rnd(N, C, H, W, seed=9).cuda())
+    o = cl(torch.zeros(N, C, H, W).cuda())
+    invoke("AddRelu", [xc, y, o], [0, 1], [2])
+    assert torch.equal(o.cpu().contiguous(), torch.relu(x + y.cpu().contiguous()))
