@@ -216,13 +216,17 @@ __global__ void __launch_bounds__(256) global_avg_pool_kernel(const float* __res
 // ---- host side ----------------------------------------------------------------------------------------
 struct ConvPlan : NodePlan {
     bool gemm_1x1 = false;          // planned for the tensor-core GEMM (still needs channels-last tensors at run time)
+    bool igemm_tc = false;          // k x k or strided 1x1, stride <= 2: planned for the tensor-core implicit GEMM (same run-time condition)
     int64_t w_elems = 0;
     const float *w_hi = nullptr, *w_lo = nullptr;
     int prepare(Registry& reg, const TensorIds& in, const TensorIds&, const Params&, ExecCtx& ctx) override {
-        if (!gemm_1x1) return 0;
+        if (!gemm_1x1 && !igemm_tc) return 0;
         FXF_CHECK(persist != nullptr, "conv plan: persistent memory was not assigned");
         float* h = static_cast<float*>(persist);
-        if (launch_split_tf32(static_cast<const float*>(reg[in[1]].ptr), h, h + w_elems, w_elems, ctx)) return 1;
+        const FxfTensor& w = reg[in[1]];
+        if (igemm_tc) {
+            if (launch_conv_weight_split(static_cast<const float*>(w.ptr), h, h + w_elems, int(w.shape[0]), int(w.shape[1]), int(w.shape[2]), int(w.shape[3]), ctx)) return 1;
+        } else if (launch_split_tf32(static_cast<const float*>(w.ptr), h, h + w_elems, w_elems, ctx)) return 1;
         w_hi = h;
         w_lo = h + w_elems;
         return 0;
@@ -274,6 +278,17 @@ int run_conv(Registry& reg, const TensorIds& in, const TensorIds& out, const Par
         g.ldx = d.C; g.ldw = d.C; g.ldo = d.O;
         g.relu = relu;
         return launch_gemm(g, ctx);
+    }
+    if (cp && cp->igemm_tc && cp->w_hi && is_channels_last(x) && is_channels_last(o) && aligned16(x.ptr)) {
+        ConvTcArgs c;
+        c.x = static_cast<const float*>(x.ptr);
+        c.w_hi = cp->w_hi; c.w_lo = cp->w_lo;
+        c.bias = static_cast<const float*>(b.ptr);
+        c.out = static_cast<float*>(o.ptr);
+        c.N = d.N; c.C = d.C; c.H = d.H; c.W = d.W; c.O = d.O; c.KH = d.KH; c.KW = d.KW; c.HO = d.HO; c.WO = d.WO;
+        c.pad_h = d.ph; c.pad_w = d.pw; c.dil_h = d.dh; c.dil_w = d.dw; c.str_h = d.sh; c.str_w = d.sw;
+        c.relu = relu;
+        return launch_conv_tc(c, ctx);
     }
     dim3 grid(unsigned((n_pix + CBM - 1) / CBM), unsigned((d.og + CBN - 1) / CBN), unsigned(d.groups));
     tag_launch(ctx, "conv2d_igemm_fp32_simt64x64", 2.0 * double(n_pix) * d.O * d.cg * d.KH * d.KW,
@@ -373,6 +388,12 @@ std::unique_ptr<NodePlan> plan_conv(const Registry& reg, const TensorIds& in, co
             pl->w_elems = O * C;
             pl->persist_bytes = round_up(size_t(2) * size_t(pl->w_elems) * sizeof(float), 256);
             pl->variant = "1x1 -> tcgen05-tf32x3 GEMM when channels-last, else igemm-simt64x64";
+        } else if (!is_1x1 && p.ints[0] >= 1 && p.ints[0] <= 2 && p.ints[1] >= 1 && p.ints[1] <= 2 && p.ints[6] == 1 && env.gemm_mode != FXF_GEMM_FP32_SIMT && conv_tc_shape_ok(M, int(C), int(O)) &&
+                   reg[in[0]].rank == 4 && reg[in[0]].shape[1] == C) {
+            pl->igemm_tc = true;
+            pl->w_elems = O * C * w.shape[2] * w.shape[3];
+            pl->persist_bytes = round_up(size_t(2) * size_t(pl->w_elems) * sizeof(float), 256);
+            pl->variant = "tcgen05-tf32x3 implicit GEMM when channels-last, else igemm-simt64x64";
         } else {
             pl->variant = "igemm-simt64x64";
         }

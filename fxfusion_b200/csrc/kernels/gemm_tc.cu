@@ -31,6 +31,7 @@
 // SS-operand MMA with cta_group::1 (operand reads + TMA fills + the split pass share 128 B/clk).
 #include <cuda.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <mutex>
 
@@ -66,7 +67,21 @@ struct alignas(1024) TcSmem {
     int abort_flag;
 };
 
+// Implicit-GEMM geometry of a convolution over a channels-last activation.  A tile's 128 rows are a box of
+// output pixels (BW x BH x BNI <= 128; rows beyond the box are ignored); K-slab k is input-channel slab
+// (k % c_slabs) of filter tap (k / c_slabs), fetched by one 4-D TMA load whose W/H coordinates are shifted by
+// the tap (out-of-range pixels = zero padding).  A strided convolution uses the tensor map's traversal stride:
+// the box spans BW*stride input pixels and every stride-th one is fetched.
+struct ConvGeom {
+    int enabled;
+    int c_slabs, KW, WO, HO, N;
+    int pad_h, pad_w, dil_h, dil_w, str_h, str_w;
+    int BW, BH, BNI, tiles_w, tiles_h;
+    uint32_t a_bytes;
+};
+
 struct TcParams {
+    ConvGeom cv;
     const float* bias;
     float* out;
     int64_t M, N, K, ldo;
@@ -84,6 +99,28 @@ __device__ __forceinline__ void tile_coords(const TcParams& p, int tile, int& tm
         tn = tile % p.tiles_n;
         tm = tile / p.tiles_n;
     }
+}
+
+// origin (ox0, oy0, n0) of the pixel box of M-tile `tm`
+__device__ __forceinline__ void conv_tile_origin(const ConvGeom& c, int tm, int& ox0, int& oy0, int& n0) {
+    ox0 = (tm % c.tiles_w) * c.BW;
+    oy0 = ((tm / c.tiles_w) % c.tiles_h) * c.BH;
+    n0 = (tm / (c.tiles_w * c.tiles_h)) * c.BNI;
+}
+// element offset of output row `r` (0..127) of M-tile `tm`, and whether that row exists
+__device__ __forceinline__ int64_t out_row_offset(const TcParams& p, int tm, int r, bool& ok) {
+    if (!p.cv.enabled) {
+        int64_t row = int64_t(tm) * BM + r;
+        ok = row < p.M;
+        return row * p.ldo;
+    }
+    const ConvGeom& c = p.cv;
+    int ox0, oy0, n0;
+    conv_tile_origin(c, tm, ox0, oy0, n0);
+    int w = r % c.BW, h = (r / c.BW) % c.BH, ni = r / (c.BW * c.BH);
+    int ox = ox0 + w, oy = oy0 + h, n = n0 + ni;
+    ok = ni < c.BNI && ox < c.WO && oy < c.HO && n < c.N;
+    return ((int64_t(n) * c.HO + oy) * c.WO + ox) * p.ldo;
 }
 
 template <int BN, int BK, int STAGES>
@@ -138,8 +175,17 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         give_up(abort_flag, p.status, kErrWaitEmpty);
                         goto producer_done;
                     }
-                    mbar_expect_tx(&s.full_tma[st], kStageBytes);
-                    tma_load_2d(s.a_hi[st], &map_x, k * BK, tm * BM, &s.full_tma[st]);
+                    if (p.cv.enabled) {
+                        int ox0, oy0, n0;
+                        conv_tile_origin(p.cv, tm, ox0, oy0, n0);
+                        const int tap = k / p.cv.c_slabs, cs = k - tap * p.cv.c_slabs, kh = tap / p.cv.KW, kw = tap - kh * p.cv.KW;
+                        mbar_expect_tx(&s.full_tma[st], p.cv.a_bytes + uint32_t(2 * BN * BK) * 4u);
+                        tma_load_4d(s.a_hi[st], &map_x, cs * BK, ox0 * p.cv.str_w - p.cv.pad_w + kw * p.cv.dil_w,
+                                    oy0 * p.cv.str_h - p.cv.pad_h + kh * p.cv.dil_h, n0, &s.full_tma[st]);
+                    } else {
+                        mbar_expect_tx(&s.full_tma[st], kStageBytes);
+                        tma_load_2d(s.a_hi[st], &map_x, k * BK, tm * BM, &s.full_tma[st]);
+                    }
                     tma_load_2d(s.b_hi[st], &map_whi, k * BK, tn * BN, &s.full_tma[st]);
                     tma_load_2d(s.b_lo[st], &map_wlo, k * BK, tn * BN, &s.full_tma[st]);
                 }
@@ -228,7 +274,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int64_t row0 = int64_t(tm) * BM + q * 32;
+            const int row0 = q * 32;  // first row of this warp inside the tile
             const int64_t col0 = int64_t(tn) * BN;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; c++) {
@@ -265,7 +311,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                             v.z = v.z > 0.f ? v.z : (v.z != v.z ? v.z : 0.f);
                             v.w = v.w > 0.f ? v.w : (v.w != v.w ? v.w : 0.f);
                         }
-                        if (row0 + rr < p.M) *reinterpret_cast<float4*>(p.out + (row0 + rr) * p.ldo + col + cq) = v;
+                        bool row_ok;
+                        int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
+                        if (row_ok) *reinterpret_cast<float4*>(p.out + off + col + cq) = v;
                     }
                 } else {
                     // one row per instruction, lanes on consecutive columns
@@ -275,7 +323,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     for (int rr = 0; rr < 32; rr++) {
                         float v = stage[rr * kStagePad + lane] + b;
                         if (p.relu) v = v > 0.f ? v : (v != v ? v : 0.f);
-                        if (col_ok && row0 + rr < p.M) p.out[(row0 + rr) * p.ldo + col + lane] = v;
+                        bool row_ok;
+                        int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
+                        if (col_ok && row_ok) p.out[off + col + lane] = v;
                     }
                 }
                 __syncwarp();
@@ -333,13 +383,37 @@ int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, in
     return 0;
 }
 
+// channels-last activation [N,H,W,C] as a 4-D map; box = [BNI, BH, BW, bk channels], 64-byte swizzle (bk = 16).
+// With a traversal stride s the box extent is given in input pixels (BW * s) and ceil(extent / s) = BW are loaded.
+int make_map_nhwc(CUtensorMap* map, const float* base, int N, int H, int W, int C, int bni, int bh, int bw, int bk, int sh, int sw) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    FXF_CHECK(fn != nullptr, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+    cuuint64_t dims[4] = {cuuint64_t(C), cuuint64_t(W), cuuint64_t(H), cuuint64_t(N)};
+    cuuint64_t strides[3] = {cuuint64_t(C) * 4, cuuint64_t(W) * C * 4, cuuint64_t(H) * W * C * 4};
+    cuuint32_t box[4] = {cuuint32_t(bk), cuuint32_t(bw * sw), cuuint32_t(bh * sh), cuuint32_t(bni)};
+    cuuint32_t estr[4] = {1, cuuint32_t(sw), cuuint32_t(sh), 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    FXF_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (conv) failed with code %d", int(r));
+    return 0;
+}
+
 template <int BN, int BK, int STAGES>
-int launch_tc(const GemmArgs& a, ExecCtx& ctx) {
+int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, const ConvGeom* geom = nullptr) {
     CUtensorMap mx, mhi, mlo;
-    if (make_map(&mx, a.x, a.M, a.K, a.ldx, BM, BK)) return 1;
+    if (cv) {
+        if (make_map_nhwc(&mx, cv->x, cv->N, cv->H, cv->W, cv->C, geom->BNI, geom->BH, geom->BW, BK, geom->str_h, geom->str_w)) return 1;
+    } else if (make_map(&mx, a.x, a.M, a.K, a.ldx, BM, BK)) return 1;
     if (make_map(&mhi, a.w_hi, a.N, a.K, a.K, BN, BK)) return 1;
     if (make_map(&mlo, a.w_lo, a.N, a.K, a.K, BN, BK)) return 1;
-    TcParams p;
+    TcParams p{};
+    if (geom) {
+        p.cv = *geom;
+        p.cv.enabled = 1;
+        p.cv.c_slabs = cv->C / BK;
+        p.cv.a_bytes = uint32_t(geom->BW * geom->BH * geom->BNI * BK) * 4u;
+    }
     p.bias = a.bias; p.out = a.out; p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo;
     p.relu = a.relu ? 1 : 0;
     p.vec_out = (a.ldo % 4 == 0 && aligned16(a.out) && (a.bias == nullptr || aligned16(a.bias))) ? 1 : 0;
@@ -358,8 +432,14 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx) {
     }
     int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
     int grid = int(tiles < ctx.sm_count ? tiles : ctx.sm_count);
-    tag_launch(ctx, "gemm_tf32x3_tcgen05", 2.0 * double(a.M) * double(a.N) * double(a.K),
-               4.0 * (double(a.M) * a.K + double(a.N) * a.K + double(a.N) + double(a.M) * a.N));
+    if (cv) {
+        const double pix = double(cv->N) * cv->HO * cv->WO;
+        tag_launch(ctx, "conv2d_igemm_tf32x3_tcgen05", 2.0 * pix * double(a.N) * double(a.K),
+                   4.0 * (double(cv->N) * cv->H * cv->W * cv->C + double(a.N) * a.K + double(a.N) + pix * a.N));
+    } else {
+        tag_launch(ctx, "gemm_tf32x3_tcgen05", 2.0 * double(a.M) * double(a.N) * double(a.K),
+                   4.0 * (double(a.M) * a.K + double(a.N) * a.K + double(a.N) + double(a.M) * a.N));
+    }
     gemm_tf32x3_kernel<BN, BK, STAGES><<<grid, kThreads, smem, ctx.stream>>>(mx, mhi, mlo, p);
     FXF_LAUNCHED(ctx);
     return 0;
@@ -417,6 +497,79 @@ int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx) {
         case 256: return launch_tc<256, 16, 4>(a, ctx);
         case 192: return launch_tc<192, 16, 5>(a, ctx);
         default: return launch_tc<128, 32, 3>(a, ctx);
+    }
+}
+
+// ---- convolution as implicit GEMM ---------------------------------------------------------------------
+bool conv_tc_shape_ok(int64_t n_pix, int C, int O) { return C >= 16 && C % 16 == 0 && O >= 64 && n_pix >= 64; }
+
+namespace {
+// Pixel box (BW x BH x BNI <= 128) that wastes the fewest rows: ragged tiles at the right/bottom edge and
+// rows of the 128-row MMA tile beyond the box both count as waste.
+void pick_pixel_box(int N, int HO, int WO, ConvGeom* g) {
+    double best = -1;
+    for (int bw = 1; bw <= std::min(WO, 128); bw++)
+        for (int bh = 1; bh <= std::min(HO, 128 / bw); bh++) {
+            int bni = (bw == WO && bh == HO) ? std::max(1, std::min(N, 128 / (bw * bh))) : 1;
+            int64_t tiles = int64_t((WO + bw - 1) / bw) * ((HO + bh - 1) / bh) * ((N + bni - 1) / bni);
+            double eff = double(WO) * HO * N / (double(tiles) * 128.0);
+            if (eff > best + 1e-9) {
+                best = eff;
+                g->BW = bw; g->BH = bh; g->BNI = bni;
+            }
+        }
+    g->tiles_w = (WO + g->BW - 1) / g->BW;
+    g->tiles_h = (HO + g->BH - 1) / g->BH;
+}
+
+__global__ void __launch_bounds__(256) conv_weight_split_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo, int O, int C, int KH, int KW) {
+    int64_t total = int64_t(O) * C * KH * KW, stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        int c = int(i % C);
+        int64_t t = i / C;
+        int kw = int(t % KW); t /= KW;
+        int kh = int(t % KH);
+        int o = int(t / KH);
+        float h, l;
+        split_tf32(w[((int64_t(o) * C + c) * KH + kh) * KW + kw], h, l);
+        hi[i] = h;
+        lo[i] = l;
+    }
+}
+}  // namespace
+
+int launch_conv_weight_split(const float* w_oihw, float* hi, float* lo, int O, int C, int KH, int KW, ExecCtx& ctx) {
+    int64_t total = int64_t(O) * C * KH * KW;
+    if (total == 0) return 0;
+    int64_t blocks = (total + 255) / 256, cap = int64_t(ctx.sm_count) * 8;
+    tag_launch(ctx, "conv_weight_split_tf32", 0, 12.0 * double(total));
+    conv_weight_split_kernel<<<int(blocks < cap ? blocks : cap), 256, 0, ctx.stream>>>(w_oihw, hi, lo, O, C, KH, KW);
+    FXF_LAUNCHED(ctx);
+    return 0;
+}
+
+int launch_conv_tc(const ConvTcArgs& c, ExecCtx& ctx) {
+    FXF_CHECK(c.x && c.w_hi && c.w_lo && c.out, "conv (tensor core): NULL operand");
+    FXF_CHECK(c.str_h >= 1 && c.str_h <= 2 && c.str_w >= 1 && c.str_w <= 2, "conv (tensor core): stride must be 1 or 2");
+    FXF_CHECK(conv_tc_shape_ok(int64_t(c.N) * c.HO * c.WO, c.C, c.O) && aligned16(c.x) && aligned16(c.w_hi) && aligned16(c.w_lo),
+              "conv (tensor core): unsupported problem");
+    ConvGeom g{};
+    g.KW = c.KW; g.WO = c.WO; g.HO = c.HO; g.N = c.N;
+    g.pad_h = c.pad_h; g.pad_w = c.pad_w; g.dil_h = c.dil_h; g.dil_w = c.dil_w; g.str_h = c.str_h; g.str_w = c.str_w;
+    pick_pixel_box(c.N, c.HO, c.WO, &g);
+    const int64_t tiles_m = int64_t(g.tiles_w) * g.tiles_h * ((c.N + g.BNI - 1) / g.BNI);
+    GemmArgs a;
+    a.w_hi = c.w_hi; a.w_lo = c.w_lo; a.bias = c.bias; a.out = c.out;
+    a.M = tiles_m * BM;  // rows the kernel schedules; rows outside the image are masked at the store
+    a.N = c.O;
+    a.K = int64_t(c.KH) * c.KW * c.C;
+    a.ldo = c.O;
+    a.relu = c.relu;
+    int bn = a.N <= 128 ? 128 : gemm_tc_pick_bn(a.M, a.N, ctx.sm_count);
+    switch (bn) {  // the pixel-box loads use 16-channel slabs, so every width runs the 16-float ring
+        case 256: return launch_tc<256, 16, 4>(a, ctx, &c, &g);
+        case 192: return launch_tc<192, 16, 5>(a, ctx, &c, &g);
+        default: return launch_tc<128, 16, 6>(a, ctx, &c, &g);
     }
 }
 

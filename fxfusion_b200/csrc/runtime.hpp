@@ -211,6 +211,22 @@ int launch_split_tf32(const float* w, float* hi, float* lo, int64_t n, ExecCtx& 
 int simt_tile_choice(int64_t M, int64_t N, int sm_count);
 std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count);
 
+// Convolution (stride 1 or 2) as an implicit GEMM on the tensor cores: channels-last activation x [N,H,W,C], weights
+// repacked to [O, KH*KW*C] (tap-major, channel-minor) and split into TF32 hi/lo, channels-last output [N,HO,WO,O].
+struct ConvTcArgs {
+    const float* x = nullptr;
+    const float *w_hi = nullptr, *w_lo = nullptr;
+    const float* bias = nullptr;
+    float* out = nullptr;
+    int N = 0, C = 0, H = 0, W = 0, O = 0, KH = 0, KW = 0, HO = 0, WO = 0;
+    int pad_h = 0, pad_w = 0, dil_h = 1, dil_w = 1, str_h = 1, str_w = 1;
+    bool relu = false;
+};
+bool conv_tc_shape_ok(int64_t n_pix, int C, int O);
+int launch_conv_tc(const ConvTcArgs& a, ExecCtx& ctx);
+// w_oihw [O,C,KH,KW] -> TF32 hi/lo halves laid out [O,KH,KW,C]
+int launch_conv_weight_split(const float* w_oihw, float* hi, float* lo, int O, int C, int KH, int KW, ExecCtx& ctx);
+
 // Attention core on packed qkv [B,T,3D] (Q | K | V thirds, head h at columns h*hd) -> ctx [B,T,D].
 struct AttnArgs {
     const float* qkv = nullptr;

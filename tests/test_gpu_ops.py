@@ -249,3 +249,35 @@ def test_channels_last_tensors_are_honoured(built_lib):
     o = cl(torch.zeros(N, C, H, W).cuda())
     invoke("AddRelu", [xc, y, o], [0, 1], [2])
     assert torch.equal(o.cpu().contiguous(), torch.relu(x + y.cpu().contiguous()))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("N,C,H,W,O,kh,kw,ph,pw,dh,dw,st", [
+    (2, 64, 14, 14, 96, 3, 3, 1, 1, 1, 1, 1),     # ResNet-style 3x3, two images per 128-pixel box is impossible (196 > 128)
+    (5, 32, 7, 7, 64, 3, 3, 1, 1, 1, 1, 1),       # whole images per box (49 pixels -> two images per tile, ragged batch)
+    (1, 16, 56, 56, 64, 3, 3, 1, 1, 1, 1, 1),     # one 16-channel slab per tap
+    (3, 48, 9, 20, 130, 5, 3, 2, 0, 1, 1, 1),     # asymmetric filter and padding, output channels not a tile multiple
+    (2, 64, 17, 17, 64, 3, 3, 2, 2, 2, 2, 1),     # dilation 2
+    (1, 128, 28, 28, 256, 3, 3, 0, 0, 1, 1, 1),   # no padding: output smaller than input
+    (4, 64, 12, 12, 64, 1, 7, 0, 3, 1, 1, 1),     # 1 x 7
+    (2, 128, 56, 56, 128, 3, 3, 1, 1, 1, 1, 2),   # ResNet stage transition: 3x3 stride 2
+    (3, 256, 56, 56, 512, 1, 1, 0, 0, 1, 1, 2),   # ResNet downsample branch: 1x1 stride 2
+    (5, 32, 15, 13, 64, 3, 3, 1, 1, 1, 1, 2),     # odd extents with stride 2 (whole images per box)
+    (2, 16, 30, 30, 64, 5, 5, 2, 2, 1, 1, 2),     # 5x5 stride 2
+])
+def test_conv_implicit_gemm_tensor_core(built_lib, N, C, H, W, O, kh, kw, ph, pw, dh, dw, st):
+    """Convolution (stride 1 or 2) over channels-last tensors runs as an implicit GEMM on the tensor cores
+    (3xTF32); NCHW tensors and the fp32 mode take the SIMT kernel.  Both match torch.conv2d
+    (reference semantics: csrc/kernels/cpu/conv2d.cpp:6-22, conv2d_relu.cpp)."""
+    from fxfusion_b200.kernels import invoke
+    cl = lambda t: t.contiguous(memory_format=torch.channels_last)
+    x, w, b = rnd(N, C, H, W, seed=11), rnd(O, C, kh, kw, seed=12, scale=0.05), rnd(O, seed=13)
+    ints = [st, st, ph, pw, dh, dw, 1]
+    for relu in (False, True):
+        want = torch.conv2d(x, w, b, st, (ph, pw), (dh, dw))
+        want = torch.relu(want) if relu else want
+        for precision in ("auto", "fp32_simt"):
+            out = cl(torch.full_like(want, float("nan")).cuda())
+            invoke("Conv2dRelu" if relu else "Conv2d", [cl(x.cuda()), w.cuda(), b.cuda(), out], [0, 1, 2], [3], ints=ints, precision=precision)
+            ok, info = compare_outputs(out.cpu().contiguous(), want, atol=ATOL, rtol=RTOL)
+            assert ok, (precision, relu, info)
