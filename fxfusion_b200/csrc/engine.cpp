@@ -35,6 +35,9 @@ int decode_build_mask(const int64_t* tokens, uint8_t* mask, int B, int T, int cu
 int decode_argmax_scatter(const float* logits, int64_t* tokens, int B, int T, int64_t V, int cur, ExecCtx& ctx);
 int decode_argmax_scatter_sharded(const float* logits, int64_t* tokens, int B, int T, int64_t V, int cur, int64_t col0, int64_t ncols,
                                   void* cand_local, void* cand_all, ExecCtx& ctx);
+int decode_argmax_scatter_rows(const float* logits, int64_t row_stride, int64_t row_off, int64_t* tokens, int B, int T, int64_t V, int cur, ExecCtx& ctx);
+int decode_argmax_scatter_sharded_rows(const float* logits, int64_t row_stride, int64_t row_off, int64_t* tokens, int B, int T, int64_t V, int cur,
+                                       int64_t col0, int64_t ncols, void* cand_local, void* cand_all, ExecCtx& ctx);
 
 int trace_after_launch(ExecCtx& ctx) {
     LaunchRecord r{ctx.tag_name, ctx.cur_node, ctx.tag_flops, ctx.tag_bytes, nullptr};
@@ -88,10 +91,17 @@ struct fxf_engine {
     bool head_sharded = false;         // the final Linear writes only this rank's column block of the logits
     int64_t head_col0 = 0, head_ncols = 0;
     size_t cand_off = 0, cand_bytes = 0;  // argmax candidates: [local | all ranks]
+    // decode that evaluates the final Linear only at the position whose logits are read
+    int tail_node = -1;                // index of that Linear (the last node), -1 when the graph does not end in one
+    size_t lastrow_off = 0, lastrow_bytes = 0;  // its [B,V] output
+    cudaGraph_t body_graph = nullptr;  // all nodes before tail_node
+    cudaGraphExec_t body_exec = nullptr;
 
     ~fxf_engine() {
         if (graph_exec) cudaGraphExecDestroy(graph_exec);
         if (graph) cudaGraphDestroy(graph);
+        if (body_exec) cudaGraphExecDestroy(body_exec);
+        if (body_graph) cudaGraphDestroy(body_graph);
         if (capture_stream) cudaStreamDestroy(capture_stream);
         if (base) cudaFree(base);
     }
@@ -100,10 +110,11 @@ struct fxf_engine {
 namespace fxf {
 namespace {
 
-int run_nodes(fxf_engine* e, cudaStream_t stream) {
+int run_nodes(fxf_engine* e, cudaStream_t stream, int count = -1) {
     e->ctx.stream = stream;
     int index = 0;
     for (auto& n : e->nodes) {
+        if (count >= 0 && index >= count) break;
         int before = e->ctx.launches;
         e->ctx.cur_node = index++;
         tag_launch(e->ctx, op_entry(n.op).name, n.plan->flops, n.plan->bytes);
@@ -315,6 +326,25 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
         e->cand_bytes = round_up(size_t(e->opts.tp_size + 1) * size_t(e->reg[e->input_ids[0]].shape[0]) * 16, kAlign);
         cursor += e->cand_bytes;
     }
+    // a graph that ends in Linear([B,T,D]) -> output 0 can decode with that Linear evaluated on one position only
+    uint32_t first_output = n_tensors;  // output 0 = the first output tensor in file order (as the binding below numbers them)
+    for (uint32_t id : order)
+        if (meta[id].kind == kOutput) { first_output = id; break; }
+    if (!e->nodes.empty() && first_output < n_tensors) {
+        int last = int(e->nodes.size()) - 1;
+        while (last > 0 && e->nodes[size_t(last)].op == 0) last--;  // trailing no-op (output / constant) nodes launch nothing
+        const Node& t = e->nodes[size_t(last)];
+        if (t.op == FXF_OP_LINEAR && t.in.size() >= 3 && t.out.size() == 1 &&
+            (t.out[0] == first_output || (meta[first_output].alias_of >= 0 && uint32_t(meta[first_output].alias_of) == t.out[0]))) {
+            const FxfTensor &x = e->reg[t.in[0]], &w = e->reg[t.in[1]], &o = e->reg[t.out[0]];
+            if (x.rank == 3 && o.rank == 3 && w.rank == 2 && x.dtype == FXF_F32 && w.dtype == FXF_F32 && x.shape[2] == w.shape[1] && o.shape[2] == w.shape[0]) {
+                e->tail_node = last;
+                e->lastrow_off = cursor;
+                e->lastrow_bytes = round_up(size_t(o.shape[0]) * size_t(o.shape[2]) * sizeof(float), kAlign);
+                cursor += e->lastrow_bytes;
+            }
+        }
+    }
     e->total_bytes = cursor;
 
     // ---- the one device allocation -----------------------------------------------------------
@@ -401,6 +431,14 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
         if (rc) return 1;
         if (ce != cudaSuccess) FXF_FAIL("CUDA Graph capture failed: %s", cudaGetErrorString(ce));
         FXF_CUDA(cudaGraphInstantiate(&e->graph_exec, e->graph, 0));
+        if (e->tail_node > 0) {
+            FXF_CUDA(cudaStreamBeginCapture(e->capture_stream, cudaStreamCaptureModeThreadLocal));
+            rc = run_nodes(e, e->capture_stream, e->tail_node);
+            ce = cudaStreamEndCapture(e->capture_stream, &e->body_graph);
+            if (rc) return 1;
+            if (ce != cudaSuccess) FXF_FAIL("CUDA Graph capture (decode body) failed: %s", cudaGetErrorString(ce));
+            FXF_CUDA(cudaGraphInstantiate(&e->body_exec, e->body_graph, 0));
+        }
     }
     // the warm-up ran on zeroed inputs; leave the arena clean
     FXF_CUDA(cudaMemset(e->base, 0, e->arena_bytes));
@@ -751,7 +789,37 @@ int fxf_engine_argmax_scatter(fxf_engine* e, int64_t* tokens, int current_len, v
                                          e->head_ncols, cand, cand + size_t(B) * 16, ctx);
 }
 
+static int decode_loop(fxf_engine* e, int64_t* tokens_io, int initial_len, int64_t pad_idx, void* stream, bool last_row);
+
 int fxf_decode_static(fxf_engine* e, int64_t* tokens_io, int initial_len, int64_t pad_idx, void* stream) {
+    return decode_loop(e, tokens_io, initial_len, pad_idx, stream, false);
+}
+
+int fxf_decode_static_last_row(fxf_engine* e, int64_t* tokens_io, int initial_len, int64_t pad_idx, void* stream) {
+    FXF_CHECK(e, "fxf_decode_static_last_row: NULL argument");
+    FXF_CHECK(e->tail_node >= 0, "fxf_decode_static_last_row: the graph does not end in a Linear node that produces output 0");
+    return decode_loop(e, tokens_io, initial_len, pad_idx, stream, true);
+}
+
+int fxf_engine_supports_last_row(const fxf_engine* e) { return e && e->tail_node >= 0 ? 1 : 0; }
+
+// The final Linear on row (current_len - 1) of every sequence -> [B,V] buffer, then argmax + token scatter.
+static int last_row_head(fxf_engine* e, int64_t* tokens, int cur, ExecCtx& ctx) {
+    const Node& t = e->nodes[size_t(e->tail_node)];
+    const FxfTensor &x = e->reg[t.in[0]], &w = e->reg[t.in[1]];
+    const int B = int(x.shape[0]), T = int(x.shape[1]);
+    const int64_t D = x.shape[2], V = w.shape[0];
+    const int64_t col0 = e->head_sharded ? e->head_col0 : 0, ncols = e->head_sharded ? e->head_ncols : V;
+    float* rows = reinterpret_cast<float*>(e->base + e->lastrow_off);
+    ctx.gemm_mode = e->ctx.gemm_mode;
+    ctx.status = e->ctx.status;
+    if (linear_on_rows(t.plan.get(), static_cast<const float*>(x.ptr) + int64_t(cur - 1) * D, B, int64_t(T) * D, rows, V, ctx)) return 1;
+    if (!e->head_sharded) return decode_argmax_scatter_rows(rows, V, 0, tokens, B, T, V, cur, ctx);
+    char* cand = reinterpret_cast<char*>(e->base + e->cand_off);
+    return decode_argmax_scatter_sharded_rows(rows, V, 0, tokens, B, T, V, cur, col0, ncols, cand, cand + size_t(B) * 16, ctx);
+}
+
+static int decode_loop(fxf_engine* e, int64_t* tokens_io, int initial_len, int64_t pad_idx, void* stream, bool last_row) {
     FXF_CHECK(e && tokens_io, "fxf_decode_static: NULL argument");
     FXF_CHECK(e->input_ids.size() == 2 && e->output_ids.size() >= 1, "fxf_decode_static: the graph must take (tokens, mask) and return logits");
     if (ensure_device(e)) return 1;
@@ -775,8 +843,15 @@ int fxf_decode_static(fxf_engine* e, int64_t* tokens_io, int initial_len, int64_
     ctx.comm = e->ctx.comm;
     for (int cur = initial_len; cur < T; cur++) {
         if (decode_build_mask(slot, static_cast<uint8_t*>(mask.ptr), B, T, cur, pad_idx, ctx)) return 1;
-        if (launch_forward(e, s)) return 1;
-        if (fxf_engine_argmax_scatter(e, slot, cur, stream)) return 1;
+        if (last_row) {
+            if (e->body_exec) {
+                FXF_CUDA(cudaGraphLaunch(e->body_exec, s));
+            } else if (run_nodes(e, s, e->tail_node)) return 1;
+            if (last_row_head(e, slot, cur, ctx)) return 1;
+        } else {
+            if (launch_forward(e, s)) return 1;
+            if (fxf_engine_argmax_scatter(e, slot, cur, stream)) return 1;
+        }
     }
     if (tokens_io != slot) FXF_CUDA(cudaMemcpyAsync(tokens_io, slot, size_t(tok.nbytes), cudaMemcpyDeviceToDevice, s));
     return 0;

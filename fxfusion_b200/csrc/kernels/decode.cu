@@ -63,10 +63,10 @@ __device__ __forceinline__ bool better(const Best& a, const Best& b) {
     return a.i < b.i;
 }
 
-__global__ void __launch_bounds__(1024) argmax_scatter_kernel(const float* __restrict__ logits, int64_t* __restrict__ tokens, int T, int64_t V, int cur) {
+__global__ void __launch_bounds__(1024) argmax_scatter_kernel(const float* __restrict__ logits, int64_t row_stride, int64_t row_off, int64_t* __restrict__ tokens, int T, int64_t V, int cur) {
     __shared__ Best red[32];
     int b = blockIdx.x;
-    const float* row = logits + (int64_t(b) * T + (cur - 1)) * V;
+    const float* row = logits + int64_t(b) * row_stride + row_off;
     Best best{0.f, -1};
     for (int64_t i = threadIdx.x; i < V; i += blockDim.x) {
         Best c{row[i], i};
@@ -104,11 +104,11 @@ struct alignas(16) Candidate {
     int64_t i;
 };
 
-__global__ void __launch_bounds__(1024) argmax_partial_kernel(const float* __restrict__ logits, Candidate* __restrict__ cand, int T, int64_t V, int cur,
+__global__ void __launch_bounds__(1024) argmax_partial_kernel(const float* __restrict__ logits, int64_t row_stride, int64_t row_off, Candidate* __restrict__ cand,
                                                               int64_t col0, int64_t ncols) {
     __shared__ Best red[32];
     int b = blockIdx.x;
-    const float* row = logits + (int64_t(b) * T + (cur - 1)) * V;
+    const float* row = logits + int64_t(b) * row_stride + row_off;
     Best best{0.f, -1};
     for (int64_t i = col0 + threadIdx.x; i < col0 + ncols; i += blockDim.x) {
         Best c{row[i], i};
@@ -151,12 +151,23 @@ __global__ void argmax_combine_scatter_kernel(const Candidate* __restrict__ all,
 
 }  // namespace
 
+int decode_argmax_scatter_rows(const float* logits, int64_t row_stride, int64_t row_off, int64_t* tokens, int B, int T, int64_t V, int cur, ExecCtx& ctx);
+int decode_argmax_scatter_sharded_rows(const float* logits, int64_t row_stride, int64_t row_off, int64_t* tokens, int B, int T, int64_t V, int cur,
+                                       int64_t col0, int64_t ncols, void* cand_local, void* cand_all, ExecCtx& ctx);
+
 // cand_local: B candidates; cand_all: n_ranks * B candidates (16 bytes each)
 int decode_argmax_scatter_sharded(const float* logits, int64_t* tokens, int B, int T, int64_t V, int cur, int64_t col0, int64_t ncols,
                                   void* cand_local, void* cand_all, ExecCtx& ctx) {
+    return decode_argmax_scatter_sharded_rows(logits, int64_t(T) * V, int64_t(cur - 1) * V, tokens, B, T, V, cur, col0, ncols, cand_local, cand_all, ctx);
+}
+
+// Row b of the logits starts at logits + b * row_stride + row_off; the token goes to tokens[b, cur].
+int decode_argmax_scatter_sharded_rows(const float* logits, int64_t row_stride, int64_t row_off, int64_t* tokens, int B, int T, int64_t V, int cur,
+                                       int64_t col0, int64_t ncols, void* cand_local, void* cand_all, ExecCtx& ctx) {
     FXF_CHECK(cur >= 1 && cur < T, "decode: current_len %d must be in [1, %d)", cur, T);
     if (B == 0) return 0;
-    argmax_partial_kernel<<<B, 1024, 0, ctx.stream>>>(logits, static_cast<Candidate*>(cand_local), T, V, cur, col0, ncols);
+    (void)V;
+    argmax_partial_kernel<<<B, 1024, 0, ctx.stream>>>(logits, row_stride, row_off, static_cast<Candidate*>(cand_local), col0, ncols);
     FXF_LAUNCHED(ctx);
     if (tp_all_gather(cand_local, cand_all, int64_t(B) * int64_t(sizeof(Candidate)), ctx)) return 1;
     argmax_combine_scatter_kernel<<<(B + 127) / 128, 128, 0, ctx.stream>>>(static_cast<const Candidate*>(cand_all), tokens, B, T, cur, ctx.tp_size);
@@ -180,10 +191,14 @@ int decode_build_mask(const int64_t* tokens, uint8_t* mask, int B, int T, int cu
 }
 
 int decode_argmax_scatter(const float* logits, int64_t* tokens, int B, int T, int64_t V, int cur, ExecCtx& ctx) {
+    return decode_argmax_scatter_rows(logits, int64_t(T) * V, int64_t(cur - 1) * V, tokens, B, T, V, cur, ctx);
+}
+
+int decode_argmax_scatter_rows(const float* logits, int64_t row_stride, int64_t row_off, int64_t* tokens, int B, int T, int64_t V, int cur, ExecCtx& ctx) {
     FXF_CHECK(cur >= 1 && cur < T, "decode: current_len %d must be in [1, %d)", cur, T);
     FXF_CHECK(V >= 1, "decode: empty vocabulary");
     if (B == 0) return 0;
-    argmax_scatter_kernel<<<B, 1024, 0, ctx.stream>>>(logits, tokens, T, V, cur);
+    argmax_scatter_kernel<<<B, 1024, 0, ctx.stream>>>(logits, row_stride, row_off, tokens, T, V, cur);
     FXF_LAUNCHED(ctx);
     return 0;
 }

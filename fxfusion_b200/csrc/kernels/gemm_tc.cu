@@ -450,9 +450,9 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
 // The tensor-core path needs: pre-split weights, 16-byte aligned bases, row pitches that are
 // multiples of 4 floats (TMA strides are multiples of 16 bytes), K a multiple of 4 and a problem
 // large enough that 128-row tiles are not mostly padding.
-bool gemm_tc_supported(const GemmArgs& a) {
+bool gemm_tc_supported(const GemmArgs& a, bool allow_few_rows) {
     if (a.w_hi == nullptr || a.w_lo == nullptr) return false;
-    if (!gemm_tc_shape_ok(a.M, a.N, a.K)) return false;
+    if (!gemm_tc_shape_ok(allow_few_rows && a.M >= 1 ? std::max<int64_t>(a.M, 64) : a.M, a.N, a.K)) return false;
     if (a.ldx % 4 != 0 || a.ldx < a.K) return false;
     if (!aligned16(a.x) || !aligned16(a.w_hi) || !aligned16(a.w_lo)) return false;
     return true;
@@ -484,8 +484,8 @@ int gemm_tc_pick_bn(int64_t M, int64_t N, int sm_count) {
     return best;
 }
 
-int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx) {
-    FXF_CHECK(gemm_tc_supported(a), "tensor-core GEMM called with an unsupported problem");
+int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows) {
+    FXF_CHECK(gemm_tc_supported(a, allow_few_rows), "tensor-core GEMM called with an unsupported problem");
     // Debug override: FXF_TC_BN=256|192|128 forces the tile width.
     static const int forced = [] {
         const char* e = std::getenv("FXF_TC_BN");

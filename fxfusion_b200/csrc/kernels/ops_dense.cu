@@ -163,6 +163,17 @@ int run_linear(Registry& reg, const TensorIds& in, const TensorIds& out, bool re
 int k_linear(Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const NodePlan* plan, ExecCtx& ctx) {
     return run_linear(reg, in, out, false, plan, ctx, "linear");
 }
+
+int linear_on_rows(const NodePlan* plan, const float* x_rows, int64_t M, int64_t ldx, float* out, int64_t ldo, ExecCtx& ctx) {
+    const DensePlan* pl = dense(plan);
+    FXF_CHECK(pl != nullptr && pl->n == 2 && pl->prepared, "linear (rows): the node was not prepared");
+    if (M == 0 || pl->s[0].rows() == 0) return 0;
+    GemmArgs g;
+    fill_gemm(g, x_rows, pl->s[0], &pl->s[1], out + pl->col_off, M, ldx, ldo, false);
+    // few rows against a large weight: the tensor-core kernel streams the pre-split weight once; rows beyond M are zero fill
+    if (ctx.gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_supported(g, true)) return launch_gemm_tc(g, ctx, true);
+    return launch_gemm_simt(g, ctx);
+}
 int k_linear_relu(Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const NodePlan* plan, ExecCtx& ctx) {
     return run_linear(reg, in, out, true, plan, ctx, "linear_relu");
 }

@@ -203,8 +203,9 @@ struct GemmArgs {
 };
 int launch_gemm(const GemmArgs& a, ExecCtx& ctx);
 int launch_gemm_simt(const GemmArgs& a, ExecCtx& ctx);
-int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx);
-bool gemm_tc_supported(const GemmArgs& a);
+int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows = false);
+// allow_few_rows: accept M < 64 (a weight-streaming problem: most rows of the 128-row tile are padding, the time is the weight read)
+bool gemm_tc_supported(const GemmArgs& a, bool allow_few_rows = false);
 bool gemm_tc_shape_ok(int64_t M, int64_t N, int64_t K);
 int gemm_tc_pick_bn(int64_t M, int64_t N, int sm_count);
 int launch_split_tf32(const float* w, float* hi, float* lo, int64_t n, ExecCtx& ctx);
@@ -223,6 +224,9 @@ struct ConvTcArgs {
     bool relu = false;
 };
 bool conv_tc_shape_ok(int64_t n_pix, int C, int O);
+// The Linear of a planned node applied to M rows that start at x_rows and lie ldx floats apart; row m of the result
+// goes to out + m * ldo (+ the column offset of this rank's block when the node's output columns are sharded).
+int linear_on_rows(const NodePlan* plan, const float* x_rows, int64_t M, int64_t ldx, float* out, int64_t ldo, ExecCtx& ctx);
 int launch_conv_tc(const ConvTcArgs& a, ExecCtx& ctx);
 // w_oihw [O,C,KH,KW] -> TF32 hi/lo halves laid out [O,KH,KW,C]
 int launch_conv_weight_split(const float* w_oihw, float* hi, float* lo, int O, int C, int KH, int KW, ExecCtx& ctx);

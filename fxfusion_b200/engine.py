@@ -220,13 +220,23 @@ class ExecutionEngine:
         the vocabulary is sharded)."""
         _lib.check(self._lib.fxf_engine_argmax_scatter(self._h, C.c_void_p(tokens.data_ptr()), int(current_len), self._stream()))
 
-    def decode_static(self, tokens, initial_len: int, pad_idx: int = 0):
+    @property
+    def supports_last_row(self) -> bool:
+        """True when the graph ends in the Linear that produces output 0, so decode_static(last_row_only=True) applies."""
+        return bool(self._lib.fxf_engine_supports_last_row(self._h))
+
+    def decode_static(self, tokens, initial_len: int, pad_idx: int = 0, last_row_only: bool = False):
         """Complete `tokens` (int64 CUDA tensor [B,T], prompt in the first `initial_len` columns) in
-        place by greedy decoding on the device; returns it.  No host synchronisation."""
+        place by greedy decoding on the device; returns it.  No host synchronisation.
+
+        last_row_only=True evaluates the final vocabulary projection only at the position the loop reads
+        (row current_len - 1 of each sequence) instead of at all T positions: the same tokens, about 30 % fewer
+        flops per step at GPT-2-small shape; the engine's output 0 (full logits) is then not updated."""
         torch = _torch()
         if not (isinstance(tokens, torch.Tensor) and tokens.is_cuda and tokens.dtype == torch.int64 and tokens.is_contiguous()):
             raise RuntimeError("decode_static: tokens must be a contiguous int64 CUDA tensor")
-        _lib.check(self._lib.fxf_decode_static(self._h, C.c_void_p(tokens.data_ptr()), int(initial_len), int(pad_idx), self._stream()))
+        fn = self._lib.fxf_decode_static_last_row if last_row_only else self._lib.fxf_decode_static
+        _lib.check(fn(self._h, C.c_void_p(tokens.data_ptr()), int(initial_len), int(pad_idx), self._stream()))
         return tokens
 
     def close(self) -> None:

@@ -180,6 +180,15 @@ FXF_API int fxf_decode_argmax_scatter(const float* logits, int64_t* tokens, int 
                               int current_len, void* stream);
 FXF_API int fxf_decode_static(fxf_engine* e, int64_t* tokens_io, int initial_len, int64_t pad_idx,
                       void* stream);
+/* The same loop and the same tokens, for a graph whose last node is the Linear that produces output 0
+ * ([B,T,D] -> [B,T,V], the vocabulary projection): each step runs every node but that one, then evaluates
+ * the projection only on row current_len-1 of each sequence — the only row the loop reads
+ * (inference.py:38-40, `logits[:, current_len - 1, :]`) — into a [B,V] buffer inside the engine, in fp32
+ * FFMA arithmetic.  Output 0 of the engine is NOT updated by this call; no counterpart in the reference,
+ * whose loop always runs the whole graph.  fxf_engine_supports_last_row tells whether the graph qualifies. */
+FXF_API int fxf_engine_supports_last_row(const fxf_engine* e);
+FXF_API int fxf_decode_static_last_row(fxf_engine* e, int64_t* tokens_io, int initial_len, int64_t pad_idx,
+                               void* stream);
 
 /* FeedForward without any allocation (no counterpart in the reference: its CUDA feedforward takes
  * its hidden buffer from a per-node torch::empty).  For callers that cannot call cudaMalloc — the device

@@ -164,6 +164,12 @@ def test_c3_decode_host_loop_equals_device_loop(built_lib, c3):
     assert torch.equal(dev, host)
     assert torch.equal(dev[:, :248].cpu(), tokens)
     assert (dev[:, 248:] >= 0).all() and (dev[:, 248:] < cfg.vocab).all()
+    # the loop that evaluates the vocabulary projection only on the row it reads yields the same tokens
+    assert eng.supports_last_row
+    short = buf.cuda()
+    eng.decode_static(short, 248, last_row_only=True)
+    assert torch.equal(short, dev)
+    assert eng.device_status() == 0
 
 
 @pytest.mark.parametrize("precision", ["fp32_simt", "auto"])

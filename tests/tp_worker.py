@@ -99,6 +99,10 @@ def gpu_checks(rank, size, tmp):
     torch.cuda.synchronize()
     want_tokens = decode_static(lambda b, m: oracle.run([b, m])[0], tokens, T)
     assert torch.equal(dev.cpu(), want_tokens), f"rank {rank}: TP greedy tokens differ from the oracle"
+    dev = buf.cuda()
+    eng.decode_static(dev, L0, last_row_only=True)
+    torch.cuda.synchronize()
+    assert torch.equal(dev.cpu(), want_tokens), f"rank {rank}: TP greedy tokens (last-row projection) differ from the oracle"
     eng.close()
     comm.close()
 
