@@ -383,6 +383,13 @@ def run_micro(args):
         reg = [torch.randn(M, N, generator=g).cuda(), torch.randn(M, N, generator=g).cuda(), torch.empty(M, N, device="cuda")]
         call = lambda: invoke("Add", reg, [0, 1], [2])
         flops, nbytes = 1.0 * M * N, 12.0 * M * N
+    elif args.micro == "conv":  # 3x3, stride 1, pad 1, channels-last: batch = m, channels in = out = n, height = width = k
+        cl = lambda t: t.contiguous(memory_format=torch.channels_last)
+        reg = [cl(torch.randn(M, N, K, K, generator=g).cuda()), (torch.randn(N, N, 3, 3, generator=g) * 0.05).cuda(), torch.zeros(N).cuda(),
+               cl(torch.empty(M, N, K, K, device="cuda"))]
+        call = lambda: invoke("Conv2dRelu", reg, [0, 1, 2], [3], ints=[1, 1, 1, 1, 1, 1, 1], precision=args.precision)
+        flops = 2.0 * M * K * K * N * N * 9
+        nbytes = 4.0 * (2 * M * N * K * K + 9 * N * N + N)
     else:  # mha: B = m, T = n, D = k, 64-wide heads
         Bm, Tm, D = M, N, K
         H = D // 64
@@ -455,7 +462,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="c3", choices=["c3", "c1", "c2", "c5"],
                     help="c3 = the decode benchmark (default); c1 / c2 = forward latency of the small configs; c5 = ResNet-50 forward (batch --m, default 256)")
-    ap.add_argument("--micro", default=None, choices=["linear", "layernorm", "add", "mha"], help="profile one op instead of the decode workload")
+    ap.add_argument("--micro", default=None, choices=["linear", "layernorm", "add", "mha", "conv"], help="profile one op instead of the decode workload")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=3072)
     ap.add_argument("--k", type=int, default=768)
