@@ -81,6 +81,7 @@ struct fxf_engine {
     uint8_t* base = nullptr;
     size_t total_bytes = 0, arena_bytes = 0, const_bytes = 0, input_bytes = 0, persist_bytes = 0, scratch_bytes = 0;
     size_t scratch_off = 0, status_off = 0;
+    size_t gemm_ws_off = 0, gemm_ws_bytes = 0, gemm_flags_off = 0, gemm_flags_bytes = 0;
     ExecCtx ctx;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
@@ -321,6 +322,17 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
     cursor = round_up(cursor + e->scratch_bytes, kAlign);
     e->status_off = cursor;
     cursor += kAlign;
+    if (e->opts.gemm_mode != FXF_GEMM_FP32_SIMT) {
+        // K-split workspace of the tensor-core GEMM: one 128 x 256 partial tile and four flags per SM
+        int sms = 148;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, e->device);
+        e->gemm_ws_off = cursor;
+        e->gemm_ws_bytes = round_up(size_t(sms) * 128 * 256 * sizeof(float), kAlign);
+        cursor += e->gemm_ws_bytes;
+        e->gemm_flags_off = cursor;
+        e->gemm_flags_bytes = round_up(size_t(sms) * 4 * sizeof(int), kAlign);
+        cursor += e->gemm_flags_bytes;
+    }
     if (e->head_sharded && !e->input_ids.empty() && e->reg[e->input_ids[0]].rank >= 1) {
         e->cand_off = cursor;
         e->cand_bytes = round_up(size_t(e->opts.tp_size + 1) * size_t(e->reg[e->input_ids[0]].shape[0]) * 16, kAlign);
@@ -366,6 +378,13 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
     e->ctx.scratch = e->base + e->scratch_off;
     e->ctx.scratch_bytes = e->scratch_bytes;
     e->ctx.status = reinterpret_cast<int*>(e->base + e->status_off);
+    if (e->gemm_ws_bytes) {
+        e->ctx.gemm_ws = reinterpret_cast<float*>(e->base + e->gemm_ws_off);
+        e->ctx.gemm_ws_bytes = e->gemm_ws_bytes;
+        e->ctx.gemm_flags = reinterpret_cast<int*>(e->base + e->gemm_flags_off);
+        e->ctx.gemm_flag_count = int(e->gemm_flags_bytes / sizeof(int));
+        FXF_CUDA(cudaMemset(e->ctx.gemm_flags, 0, e->gemm_flags_bytes));
+    }
 
     // ---- registry binding, in file order (an alias binds to an already-built source) --------
     std::vector<bool> bound(n_tensors, false);
@@ -713,6 +732,13 @@ static int make_call(int op_code, const FxfTensor* reg, int n_reg, const uint32_
     return 0;
 }
 
+// A single kernel call that may reach the tensor-core GEMM (its plan keeps split weights) also carries that kernel's
+// K-split workspace behind its scratch: partial tiles for up to kCallWsSms SMs, then the flags.
+constexpr size_t kCallWsSms = 160, kCallWsTile = size_t(128) * 256 * sizeof(float), kCallFlagBytes = 4096;
+static size_t call_ws_bytes(const NodePlan& plan, int gemm_mode) {
+    return (gemm_mode != FXF_GEMM_FP32_SIMT && plan.persist_bytes > 0) ? kCallWsSms * kCallWsTile + kCallFlagBytes : 0;
+}
+
 int64_t fxf_kernel_scratch_bytes(int op_code, const FxfTensor* reg, int n_reg, const uint32_t* in_ids, int n_in, const uint32_t* out_ids, int n_out,
                                  const int64_t* ints, int n_ints, const float* floats, int n_floats, int gemm_mode) {
     Registry r;
@@ -722,7 +748,7 @@ int64_t fxf_kernel_scratch_bytes(int op_code, const FxfTensor* reg, int n_reg, c
     PlanEnv env;
     env.gemm_mode = gemm_mode;
     auto plan = op_entry(op_code).plan(r, in, out, p, env);
-    return int64_t(round_up(plan->scratch_bytes, 256) + plan->persist_bytes);
+    return int64_t(round_up(plan->scratch_bytes, 256) + round_up(plan->persist_bytes, 256) + call_ws_bytes(*plan, gemm_mode));
 }
 
 int fxf_kernel_invoke(int op_code, const FxfTensor* reg, int n_reg, const uint32_t* in_ids, int n_in, const uint32_t* out_ids, int n_out,
@@ -736,7 +762,8 @@ int fxf_kernel_invoke(int op_code, const FxfTensor* reg, int n_reg, const uint32
     PlanEnv env;
     env.gemm_mode = gemm_mode;
     auto plan = entry.plan(r, in, out, p, env);
-    size_t need = round_up(plan->scratch_bytes, 256) + plan->persist_bytes;
+    const size_t ws_bytes = call_ws_bytes(*plan, gemm_mode);
+    size_t need = round_up(plan->scratch_bytes, 256) + round_up(plan->persist_bytes, 256) + ws_bytes;
     FXF_CHECK(need == 0 || (scratch != nullptr && scratch_bytes >= int64_t(need)), "kernel call: scratch too small (%lld < %zu bytes)", (long long)scratch_bytes, need);
     FXF_CHECK(need == 0 || (reinterpret_cast<uintptr_t>(scratch) & 255) == 0, "kernel call: scratch must be 256-byte aligned");
     ExecCtx ctx;
@@ -745,6 +772,14 @@ int fxf_kernel_invoke(int op_code, const FxfTensor* reg, int n_reg, const uint32
     ctx.scratch_bytes = plan->scratch_bytes;
     ctx.gemm_mode = gemm_mode;
     if (plan->persist_bytes) plan->persist = static_cast<char*>(scratch) + round_up(plan->scratch_bytes, 256);
+    if (ws_bytes) {
+        char* ws = static_cast<char*>(scratch) + round_up(plan->scratch_bytes, 256) + round_up(plan->persist_bytes, 256);
+        ctx.gemm_ws = reinterpret_cast<float*>(ws);
+        ctx.gemm_ws_bytes = kCallWsSms * kCallWsTile;
+        ctx.gemm_flags = reinterpret_cast<int*>(ws + kCallWsSms * kCallWsTile);
+        ctx.gemm_flag_count = int(kCallFlagBytes / sizeof(int));
+        FXF_CUDA(cudaMemsetAsync(ctx.gemm_flags, 0, kCallFlagBytes, ctx.stream));
+    }
     int dev = 0;
     FXF_CUDA(cudaGetDevice(&dev));
     int sms = 0;
@@ -813,6 +848,8 @@ static int last_row_head(fxf_engine* e, int64_t* tokens, int cur, ExecCtx& ctx) 
     float* rows = reinterpret_cast<float*>(e->base + e->lastrow_off);
     ctx.gemm_mode = e->ctx.gemm_mode;
     ctx.status = e->ctx.status;
+    ctx.gemm_ws = e->ctx.gemm_ws; ctx.gemm_ws_bytes = e->ctx.gemm_ws_bytes;
+    ctx.gemm_flags = e->ctx.gemm_flags; ctx.gemm_flag_count = e->ctx.gemm_flag_count;
     if (linear_on_rows(t.plan.get(), static_cast<const float*>(x.ptr) + int64_t(cur - 1) * D, B, int64_t(T) * D, rows, V, ctx)) return 1;
     if (!e->head_sharded) return decode_argmax_scatter_rows(rows, V, 0, tokens, B, T, V, cur, ctx);
     char* cand = reinterpret_cast<char*>(e->base + e->cand_off);

@@ -9,26 +9,33 @@
 // x_lo = tf32(x - x_hi); same for w.  x·w ~= x_lo·w_hi + x_hi·w_lo + x_hi·w_hi, accumulated in
 // fp32; the dropped x_lo·w_lo term is ~2^-22 relative.  Weights are constants: they are split
 // once when an engine is built (split_tf32_kernel) and kept as two arrays.  Activations are split
-// inside the kernel, in shared memory, while the tensor core works on earlier stages.
+// inside the kernel, on their way from shared memory to TENSOR MEMORY, while the tensor core works on
+// earlier stages: the MMAs take their A operand (x_hi, x_lo) from TMEM and only B (w_hi, w_lo) from
+// shared memory.
+//
+// Why A lives in TMEM.  With both operands in shared memory a 128 x 256 x 8 tf32 MMA reads 12 KB in its
+// 136 clocks (90 B/clk of the SM's 128 B/clk); adding the split pass (read x, write x_hi and x_lo)
+// the kernel sat at the shared-memory limit with the tensor pipe 77 % busy.  From TMEM the MMA
+// reads 8 KB per instruction and the split writes nothing to shared memory: about 70 B/clk.
 //
 // Structure: a PERSISTENT kernel, one CTA per SM, each CTA walking a strided list of 128 x BN output
 // tiles.  320 threads in four roles that only meet on mbarriers:
 //   warps 0-3  epilogue: tcgen05.ld of a finished accumulator (each warp its 32 TMEM lanes), staged
 //              through shared memory so that global stores are row-contiguous, bias + ReLU fused.
-//              TMEM holds TWO accumulators, so the epilogue of tile i runs under the main loop of
-//              tile i+1.
+//              With ACC = 2 TMEM holds two accumulators, so the epilogue of tile i runs under the
+//              main loop of tile i+1 (BN <= 192); BN = 256 has one accumulator.
 //   warp 4     TMA producer: per K-slab three cp.async.bulk.tensor loads — x tile [128,BK], w_hi and
 //              w_lo tiles [BN,BK] — into a STAGES-deep ring, completion counted on an mbarrier.
 //   warp 5     one thread issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8), 3 products per K-step,
 //              accumulating in TMEM; tcgen05.commit hands the stage back to the producer and, after
 //              the last slab of a tile, the accumulator to the epilogue.
-//   warps 6-9  split the x tile in place (hi) and into a twin buffer (lo); being element-wise the
-//              swizzle pattern TMA wrote is preserved.  fence.proxy.async, then arrive.
+//   warps 6-9  one thread per tile row: reads its BK floats of x from the (swizzled) stage, splits them
+//              and stores x_hi / x_lo with tcgen05.st into the stage's 2*BK TMEM columns, then arrives.
+// TMEM columns: [0, ACC*BN) accumulators, then STAGES x (BK hi + BK lo) columns of A.
 // Every mbarrier wait is bounded by a wall-clock budget; on expiry the CTA records an error in the
 // status word, all roles stop issuing work, the CTA frees its TMEM and returns.
 //
-// Bound: tensor pipe (TF32 rate / 3).  Shared-memory bandwidth is the practical limiter for an
-// SS-operand MMA with cta_group::1 (operand reads + TMA fills + the split pass share 128 B/clk).
+// Bound: tensor pipe (TF32 rate / 3).
 #include <cuda.h>
 
 #include <algorithm>
@@ -47,14 +54,14 @@ constexpr int BM = 128;
 constexpr int kThreads = 320;
 constexpr int kEpiWarp0 = 0, kTmaWarp = 4, kMmaWarp = 5, kSplitWarp0 = 6;
 
-enum : int { kErrWaitTma = 101, kErrWaitSplit = 102, kErrWaitEmpty = 103, kErrWaitAcc = 104, kErrWaitAccEmpty = 105 };
+enum : int { kErrWaitTma = 101, kErrWaitSplit = 102, kErrWaitEmpty = 103, kErrWaitAcc = 104, kErrWaitAccEmpty = 105, kErrWaitPartial = 106 };
 
 constexpr int kStagePad = 36;  // floats per staged epilogue row: 32 + 4 keeps float4 rows conflict-free
 
-template <int BN, int BK, int STAGES>
+template <int BN, int BK, int STAGES, bool TS>
 struct alignas(1024) TcSmem {
-    float a_hi[STAGES][BM * BK];
-    float a_lo[STAGES][BM * BK];
+    float a[STAGES][BM * BK];             // x tile as TMA wrote it (fp32, swizzled rows of BK floats); x_hi in place when !TS
+    float a_lo[TS ? 1 : STAGES][TS ? 256 : BM * BK];  // x_lo twin buffers, only when the MMAs read A from shared memory
     float b_hi[STAGES][BN * BK];
     float b_lo[STAGES][BN * BK];
     float stage_out[4][32 * kStagePad];   // one 32 x 32 block per epilogue warp
@@ -88,8 +95,32 @@ struct TcParams {
     int relu;
     int vec_out;
     int tiles_m, tiles_n, m_fastest;
+    // Tail split: the first `full_tiles` tiles are computed whole; each of the remaining `tail_tiles` is cut along K
+    // into `tail_split` work units that run on different CTAs.  Parts 1.. write their partial accumulator to `ws`
+    // (unit-major, 128 x BN floats each) and raise flags[unit*4 + warp]; part 0 adds them in part order (deterministic).
+    int full_tiles, tail_tiles, tail_split;
+    float* ws;
+    int* flags;
     int* status;
 };
+
+struct Unit {
+    int tile, k0, k1, part, nparts, u;
+};
+__device__ __forceinline__ Unit get_unit(const TcParams& p, int unit, int num_k) {
+    Unit r;
+    if (unit < p.full_tiles) {
+        r.tile = unit; r.k0 = 0; r.k1 = num_k; r.part = 0; r.nparts = 1; r.u = 0;
+    } else {
+        r.u = unit - p.full_tiles;
+        r.nparts = p.tail_split;
+        r.tile = p.full_tiles + r.u / r.nparts;
+        r.part = r.u % r.nparts;
+        r.k0 = int(int64_t(num_k) * r.part / r.nparts);
+        r.k1 = int(int64_t(num_k) * (r.part + 1) / r.nparts);
+    }
+    return r;
+}
 
 __device__ __forceinline__ void tile_coords(const TcParams& p, int tile, int& tm, int& tn) {
     if (p.m_fastest) {
@@ -123,21 +154,24 @@ __device__ __forceinline__ int64_t out_row_offset(const TcParams& p, int tm, int
     return ((int64_t(n) * c.HO + oy) * c.WO + ox) * p.ldo;
 }
 
-template <int BN, int BK, int STAGES>
+template <int BN, int BK, int STAGES, int ACC, bool TS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_whi,
                    const __grid_constant__ CUtensorMap map_wlo, TcParams p) {
     extern __shared__ unsigned char smem_raw[];
     // dynamic shared memory is only guaranteed 16-byte aligned; swizzled tiles need 1024
-    using Smem = TcSmem<BN, BK, STAGES>;
+    using Smem = TcSmem<BN, BK, STAGES, TS>;
     Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_k = int((p.K + BK - 1) / BK);
-    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_units = p.full_tiles + p.tail_tiles * p.tail_split;
     constexpr uint32_t kStageBytes = uint32_t(BM * BK + 2 * BN * BK) * 4u;
     constexpr uint32_t kIdesc = umma_idesc_tf32(BM, BN);
-    constexpr uint32_t kTmemCols = 2 * BN <= 256 ? 256 : 512;  // two accumulators; allocations are powers of two
+    constexpr uint32_t kColA = uint32_t(ACC * BN);             // first TMEM column of the A stages
+    constexpr uint32_t kColsUsed = kColA + (TS ? uint32_t(STAGES * 2 * BK) : 0u);
+    static_assert(kColsUsed <= 512, "accumulators and A stages exceed the 512 TMEM columns");
+    constexpr uint32_t kTmemCols = kColsUsed <= 256 ? 256 : 512;  // allocations are powers of two
     volatile int* abort_flag = &s.abort_flag;
 
     if (threadIdx.x == 0) {
@@ -146,7 +180,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             mbar_init(&s.full_split[i], 4);   // one arrival per split warp
             mbar_init(&s.empty[i], 1);
         }
-        for (int i = 0; i < 2; i++) {
+        for (int i = 0; i < ACC; i++) {
             mbar_init(&s.acc_full[i], 1);
             mbar_init(&s.acc_empty[i], 4);    // one arrival per epilogue warp
         }
@@ -166,10 +200,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             uint32_t it = 0;  // slab counter over all tiles of this CTA
-            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+                const Unit un = get_unit(p, unit, num_k);
                 int tm, tn;
-                tile_coords(p, tile, tm, tn);
-                for (int k = 0; k < num_k; k++, it++) {
+                tile_coords(p, un.tile, tm, tn);
+                for (int k = un.k0; k < un.k1; k++, it++) {
                     int st = it % STAGES;
                     if (it >= uint32_t(STAGES) && !mbar_wait(&s.empty[st], ((it / STAGES) - 1) & 1, abort_flag)) {
                         give_up(abort_flag, p.status, kErrWaitEmpty);
@@ -180,11 +215,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         conv_tile_origin(p.cv, tm, ox0, oy0, n0);
                         const int tap = k / p.cv.c_slabs, cs = k - tap * p.cv.c_slabs, kh = tap / p.cv.KW, kw = tap - kh * p.cv.KW;
                         mbar_expect_tx(&s.full_tma[st], p.cv.a_bytes + uint32_t(2 * BN * BK) * 4u);
-                        tma_load_4d(s.a_hi[st], &map_x, cs * BK, ox0 * p.cv.str_w - p.cv.pad_w + kw * p.cv.dil_w,
+                        tma_load_4d(s.a[st], &map_x, cs * BK, ox0 * p.cv.str_w - p.cv.pad_w + kw * p.cv.dil_w,
                                     oy0 * p.cv.str_h - p.cv.pad_h + kh * p.cv.dil_h, n0, &s.full_tma[st]);
                     } else {
                         mbar_expect_tx(&s.full_tma[st], kStageBytes);
-                        tma_load_2d(s.a_hi[st], &map_x, k * BK, tm * BM, &s.full_tma[st]);
+                        tma_load_2d(s.a[st], &map_x, k * BK, tm * BM, &s.full_tma[st]);
                     }
                     tma_load_2d(s.b_hi[st], &map_whi, k * BK, tn * BN, &s.full_tma[st]);
                     tma_load_2d(s.b_lo[st], &map_wlo, k * BK, tn * BN, &s.full_tma[st]);
@@ -196,15 +231,16 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             uint32_t it = 0, tcount = 0;
-            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tcount++) {
-                const uint32_t buf = tcount & 1;
-                if (tcount >= 2 && !mbar_wait(&s.acc_empty[buf], ((tcount >> 1) - 1) & 1, abort_flag)) {
+            for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, tcount++) {
+                const Unit un = get_unit(p, unit, num_k);
+                const uint32_t buf = tcount % ACC;
+                if (tcount >= uint32_t(ACC) && !mbar_wait(&s.acc_empty[buf], ((tcount / ACC) - 1) & 1, abort_flag)) {
                     give_up(abort_flag, p.status, kErrWaitAccEmpty);
                     goto mma_done;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_acc = tmem_base + buf * uint32_t(BN);
-                for (int k = 0; k < num_k; k++, it++) {
+                for (int k = un.k0; k < un.k1; k++, it++) {
                     int st = it % STAGES;
                     uint32_t par = (it / STAGES) & 1;
                     if (!mbar_wait(&s.full_tma[st], par, abort_flag)) {
@@ -216,14 +252,25 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         goto mma_done;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    uint64_t a_hi = umma_desc_k_major<BK>(smem_u32(s.a_hi[st])), a_lo = umma_desc_k_major<BK>(smem_u32(s.a_lo[st]));
                     uint64_t b_hi = umma_desc_k_major<BK>(smem_u32(s.b_hi[st])), b_lo = umma_desc_k_major<BK>(smem_u32(s.b_lo[st]));
+                    if (TS) {
+                        const uint32_t a_hi = tmem_base + kColA + uint32_t(st * 2 * BK), a_lo = a_hi + uint32_t(BK);  // 8 columns per K-step
 #pragma unroll
-                    for (int kk = 0; kk < BK / 8; kk++) {
-                        uint64_t adv = uint64_t((kk * 8 * 4) >> 4);  // 32 bytes per K-step inside the swizzle row
-                        umma_tf32(tmem_acc, a_lo + adv, b_hi + adv, kIdesc, (k > 0 || kk > 0) ? 1u : 0u);
-                        umma_tf32(tmem_acc, a_hi + adv, b_lo + adv, kIdesc, 1u);
-                        umma_tf32(tmem_acc, a_hi + adv, b_hi + adv, kIdesc, 1u);
+                        for (int kk = 0; kk < BK / 8; kk++) {
+                            uint64_t adv = uint64_t((kk * 8 * 4) >> 4);  // 32 bytes per K-step inside the swizzle row
+                            umma_tf32_ts(tmem_acc, a_lo + uint32_t(kk * 8), b_hi + adv, kIdesc, (k > un.k0 || kk > 0) ? 1u : 0u);
+                            umma_tf32_ts(tmem_acc, a_hi + uint32_t(kk * 8), b_lo + adv, kIdesc, 1u);
+                            umma_tf32_ts(tmem_acc, a_hi + uint32_t(kk * 8), b_hi + adv, kIdesc, 1u);
+                        }
+                    } else {
+                        uint64_t a_hi = umma_desc_k_major<BK>(smem_u32(s.a[st])), a_lo = umma_desc_k_major<BK>(smem_u32(s.a_lo[st]));
+#pragma unroll
+                        for (int kk = 0; kk < BK / 8; kk++) {
+                            uint64_t adv = uint64_t((kk * 8 * 4) >> 4);
+                            umma_tf32(tmem_acc, a_lo + adv, b_hi + adv, kIdesc, (k > un.k0 || kk > 0) ? 1u : 0u);
+                            umma_tf32(tmem_acc, a_hi + adv, b_lo + adv, kIdesc, 1u);
+                            umma_tf32(tmem_acc, a_hi + adv, b_hi + adv, kIdesc, 1u);
+                        }
                     }
                     umma_commit(&s.empty[st]);  // arrives once the MMAs above have consumed the stage
                 }
@@ -232,31 +279,69 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         mma_done:;
         }
     } else if (warp >= kSplitWarp0) {
-        // ---------------- activation split (hi in place, lo into the twin buffer) ----------------
-        const int t = threadIdx.x - kSplitWarp0 * 32;  // 0..127
         uint32_t it = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-            for (int k = 0; k < num_k; k++, it++) {
-                int st = it % STAGES;
-                if (!mbar_wait(&s.full_tma[st], (it / STAGES) & 1, abort_flag)) {
-                    give_up(abort_flag, p.status, kErrWaitTma);
-                    goto split_done;
-                }
-                float4* hi = reinterpret_cast<float4*>(s.a_hi[st]);
-                float4* lo = reinterpret_cast<float4*>(s.a_lo[st]);
+        if (TS) {
+            // ---------------- activation split: shared memory -> registers -> TMEM (hi | lo) ----------------
+            const int quarter = warp & 3;                 // TMEM lane quarter this warp may address
+            const int row = quarter * 32 + lane;          // tile row owned by this thread
+            const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+            // TMA swizzle: the 16-byte chunks of a row are permuted by the row index (64-byte rows: bits 1-2, 128-byte rows: bits 0-2)
+            const int sw = BK == 16 ? ((row >> 1) & 3) : (row & 7);
+            for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+                const Unit un = get_unit(p, unit, num_k);
+                for (int k = un.k0; k < un.k1; k++, it++) {
+                    int st = it % STAGES;
+                    if (!mbar_wait(&s.full_tma[st], (it / STAGES) & 1, abort_flag)) {
+                        give_up(abort_flag, p.status, kErrWaitTma);
+                        goto split_done;
+                    }
+                    const float4* src = reinterpret_cast<const float4*>(s.a[st]) + row * (BK / 4);
+                    uint32_t hi[BK], lo[BK];
 #pragma unroll
-                for (int i = 0; i < (BM * BK / 4) / 128; i++) {
-                    float4 v = hi[t + i * 128], h, l;
-                    split_tf32(v.x, h.x, l.x);
-                    split_tf32(v.y, h.y, l.y);
-                    split_tf32(v.z, h.z, l.z);
-                    split_tf32(v.w, h.w, l.w);
-                    hi[t + i * 128] = h;
-                    lo[t + i * 128] = l;
+                    for (int c = 0; c < BK / 4; c++) {
+                        float4 v = src[c ^ sw];
+                        float h, l;
+                        split_tf32(v.x, h, l); hi[4 * c + 0] = __float_as_uint(h); lo[4 * c + 0] = __float_as_uint(l);
+                        split_tf32(v.y, h, l); hi[4 * c + 1] = __float_as_uint(h); lo[4 * c + 1] = __float_as_uint(l);
+                        split_tf32(v.z, h, l); hi[4 * c + 2] = __float_as_uint(h); lo[4 * c + 2] = __float_as_uint(l);
+                        split_tf32(v.w, h, l); hi[4 * c + 3] = __float_as_uint(h); lo[4 * c + 3] = __float_as_uint(l);
+                    }
+                    const uint32_t a_col = tmem_base + lane_base + kColA + uint32_t(st * 2 * BK);
+                    tmem_st(a_col, hi);
+                    tmem_st(a_col + uint32_t(BK), lo);
+                    tmem_wait_st();
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&s.full_split[st]);
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA (async proxy)
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&s.full_split[st]);
+            }
+        } else {
+            // ---------------- activation split in shared memory (hi in place, lo into the twin buffer) ----------------
+            const int t = threadIdx.x - kSplitWarp0 * 32;  // 0..127
+            for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+                const Unit un = get_unit(p, unit, num_k);
+                for (int k = un.k0; k < un.k1; k++, it++) {
+                    int st = it % STAGES;
+                    if (!mbar_wait(&s.full_tma[st], (it / STAGES) & 1, abort_flag)) {
+                        give_up(abort_flag, p.status, kErrWaitTma);
+                        goto split_done;
+                    }
+                    float4* hi = reinterpret_cast<float4*>(s.a[st]);
+                    float4* lo = reinterpret_cast<float4*>(s.a_lo[st]);
+#pragma unroll
+                    for (int i = 0; i < (BM * BK / 4) / 128; i++) {
+                        float4 v = hi[t + i * 128], h, l;
+                        split_tf32(v.x, h.x, l.x);
+                        split_tf32(v.y, h.y, l.y);
+                        split_tf32(v.z, h.z, l.z);
+                        split_tf32(v.w, h.w, l.w);
+                        hi[t + i * 128] = h;
+                        lo[t + i * 128] = l;
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA (async proxy)
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&s.full_split[st]);
+                }
             }
         }
     split_done:;
@@ -265,11 +350,26 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         const int q = warp - kEpiWarp0;
         float* stage = s.stage_out[q];
         uint32_t tcount = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tcount++) {
-            const uint32_t buf = tcount & 1;
+        for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, tcount++) {
+            const Unit un = get_unit(p, unit, num_k);
+            const uint32_t buf = tcount % ACC;
             int tm, tn;
-            tile_coords(p, tile, tm, tn);
-            if (!mbar_wait(&s.acc_full[buf], (tcount >> 1) & 1, abort_flag)) {
+            tile_coords(p, un.tile, tm, tn);
+            const bool writes_partial = un.nparts > 1 && un.part > 0;
+            const bool adds_partials = un.nparts > 1 && un.part == 0;
+            float* ws_mine = p.ws + size_t(un.u) * size_t(BM * BN);
+            if (adds_partials) {
+                // the other K-parts of this tile run on other CTAs of this launch; wait for this warp's rows of each
+                int ok = 1;
+                if (lane == 0)
+                    for (int pp = 1; pp < un.nparts && ok; pp++) ok = flag_wait(p.flags + (un.u + pp) * 4 + q, abort_flag) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) {
+                    give_up(abort_flag, p.status, kErrWaitPartial);
+                    break;
+                }
+            }
+            if (!mbar_wait(&s.acc_full[buf], (tcount / ACC) & 1, abort_flag)) {
                 give_up(abort_flag, p.status, kErrWaitAcc);
                 break;
             }
@@ -295,27 +395,47 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     *reinterpret_cast<float4*>(stage + lane * kStagePad + j) =
                         make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
                 __syncwarp();
-                if (p.vec_out && col + 31 < p.N) {
-                    // 8 lanes cover one 128-byte row segment, 4 rows per instruction
-                    const int cq = (lane & 7) * 4, rsub = lane >> 3;
-                    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (p.bias) b4 = *reinterpret_cast<const float4*>(p.bias + col + cq);
+                const int cq = (lane & 7) * 4, rsub = lane >> 3;  // 8 lanes cover one 128-byte row segment, 4 rows per instruction
+                if (writes_partial) {
+                    // raw partial sums, 128 x BN row-major; bias and activation belong to part 0
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
                         int rr = i * 4 + rsub;
-                        float4 v = *reinterpret_cast<const float4*>(stage + rr * kStagePad + cq);
-                        v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
+                        *reinterpret_cast<float4*>(ws_mine + (row0 + rr) * BN + c * 32 + cq) = *reinterpret_cast<const float4*>(stage + rr * kStagePad + cq);
+                    }
+                } else if (p.vec_out && col + 31 < p.N) {
+                    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (p.bias) b4 = *reinterpret_cast<const float4*>(p.bias + col + cq);
+                    float4 v[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) v[i] = *reinterpret_cast<const float4*>(stage + (i * 4 + rsub) * kStagePad + cq);
+                    if (adds_partials) {
+                        // all eight loads of a part are issued before the first add: one L2 round trip per part and chunk
+                        for (int pp = 1; pp < un.nparts; pp++) {
+                            const float* src = ws_mine + size_t(pp) * size_t(BM * BN) + row0 * BN + c * 32 + cq;
+                            float4 w[8];
+#pragma unroll
+                            for (int i = 0; i < 8; i++) w[i] = __ldcg(reinterpret_cast<const float4*>(src + (i * 4 + rsub) * BN));
+#pragma unroll
+                            for (int i = 0; i < 8; i++) { v[i].x += w[i].x; v[i].y += w[i].y; v[i].z += w[i].z; v[i].w += w[i].w; }
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        int rr = i * 4 + rsub;
+                        float4 o = v[i];
+                        o.x += b4.x; o.y += b4.y; o.z += b4.z; o.w += b4.w;
                         if (p.relu) {
-                            v.x = v.x > 0.f ? v.x : (v.x != v.x ? v.x : 0.f);
-                            v.y = v.y > 0.f ? v.y : (v.y != v.y ? v.y : 0.f);
-                            v.z = v.z > 0.f ? v.z : (v.z != v.z ? v.z : 0.f);
-                            v.w = v.w > 0.f ? v.w : (v.w != v.w ? v.w : 0.f);
+                            o.x = o.x > 0.f ? o.x : (o.x != o.x ? o.x : 0.f);
+                            o.y = o.y > 0.f ? o.y : (o.y != o.y ? o.y : 0.f);
+                            o.z = o.z > 0.f ? o.z : (o.z != o.z ? o.z : 0.f);
+                            o.w = o.w > 0.f ? o.w : (o.w != o.w ? o.w : 0.f);
                         }
                         bool row_ok;
                         int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
-                        if (row_ok) *reinterpret_cast<float4*>(p.out + off + col + cq) = v;
+                        if (row_ok) *reinterpret_cast<float4*>(p.out + off + col + cq) = o;
                     }
-                } else {
+                } else if (!adds_partials) {
                     // one row per instruction, lanes on consecutive columns
                     const bool col_ok = col + lane < p.N;
                     const float b = (p.bias && col_ok) ? __ldg(p.bias + col + lane) : 0.f;
@@ -327,8 +447,29 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
                         if (col_ok && row_ok) p.out[off + col + lane] = v;
                     }
+                } else {
+                    const bool col_ok = col + lane < p.N;
+                    const float b = (p.bias && col_ok) ? __ldg(p.bias + col + lane) : 0.f;
+                    for (int rr = 0; rr < 32; rr++) {
+                        float v = stage[rr * kStagePad + lane];
+                        for (int pp = 1; pp < un.nparts; pp++) v += __ldcg(ws_mine + size_t(pp) * size_t(BM * BN) + (row0 + rr) * BN + c * 32 + lane);
+                        v += b;
+                        if (p.relu) v = v > 0.f ? v : (v != v ? v : 0.f);
+                        bool row_ok;
+                        int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
+                        if (col_ok && row_ok) p.out[off + col + lane] = v;
+                    }
                 }
                 __syncwarp();
+            }
+            if (writes_partial) {
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) flag_set(p.flags + un.u * 4 + q, 1);
+            } else if (adds_partials) {
+                __syncwarp();   // every lane has read its partials: lower the flags for the next launch
+                if (lane == 0)
+                    for (int pp = 1; pp < un.nparts; pp++) flag_set(p.flags + (un.u + pp) * 4 + q, 0);
             }
         }
     }
@@ -350,6 +491,34 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict
         hi[i] = h;
         lo[i] = l;
     }
+}
+
+// Work split of `tiles` tiles (128 x bn, depth K) over `sms` persistent CTAs: whole tiles first, then the remainder
+// R = tiles % sms cut along K into s parts each, so that the last round keeps R*s SMs busy for 1/s of a tile instead
+// of R SMs for a whole one.  s minimises  tile_time / s + reduce_time(s)  over 1 <= s <= min(sms / R, 4) with at least
+// 64 of K per part; the two times are in microseconds as measured on B200 (0.43 us per 128 x 256 x 16 slab of three
+// TF32 products; 3 us + 7 us per extra part for writing, fetching and adding the partial tiles).
+struct TailSplit { int64_t full, tail; int parts; double tail_us, tile_us; };
+TailSplit plan_tail(int64_t tiles, int64_t K, int bn, int sms, bool allowed) {
+    TailSplit t{tiles, 0, 1, 0.0, 0.0};
+    t.tile_us = double((K + 15) / 16) * 0.43 * double(bn) / 256.0;
+    t.tail_us = tiles % std::max(sms, 1) ? t.tile_us : 0.0;
+    static const bool disabled = [] {  // debug override: FXF_TC_SPLITK=0 computes every tile whole
+        const char* e = std::getenv("FXF_TC_SPLITK");
+        return e && e[0] == '0';
+    }();
+    if (!allowed || disabled || sms <= 1) return t;
+    const int64_t R = tiles % sms;
+    if (R == 0) return t;
+    const int64_t smax = std::min<int64_t>(std::min<int64_t>(sms / R, K / 64), 4);
+    for (int64_t s = 2; s <= smax; s++) {
+        const double us = t.tile_us / double(s) + 3.0 + 7.0 * double(s - 1);
+        if (us < t.tail_us) {
+            t.tail_us = us;
+            t.full = tiles - R; t.tail = R; t.parts = int(s);
+        }
+    }
+    return t;
 }
 
 // ---- host side -------------------------------------------------------------------------------------
@@ -399,7 +568,7 @@ int make_map_nhwc(CUtensorMap* map, const float* base, int N, int H, int W, int 
     return 0;
 }
 
-template <int BN, int BK, int STAGES>
+template <int BN, int BK, int STAGES, int ACC, bool TS>
 int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, const ConvGeom* geom = nullptr) {
     CUtensorMap mx, mhi, mlo;
     if (cv) {
@@ -422,16 +591,22 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
     // walk tiles so that the operand that does not fit in L2 is the one reused by concurrent CTAs
     p.m_fastest = a.N > a.M ? 1 : 0;
     p.status = ctx.status;
-    size_t smem = sizeof(TcSmem<BN, BK, STAGES>) + 1024;
+    size_t smem = sizeof(TcSmem<BN, BK, STAGES, TS>) + 1024;
     static bool configured[64] = {};
     int dev = 0;
     FXF_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        FXF_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, BK, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        FXF_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, BK, STAGES, ACC, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
-    int grid = int(tiles < ctx.sm_count ? tiles : ctx.sm_count);
+    const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
+    TailSplit ts = plan_tail(tiles, a.K, BN, ctx.sm_count, ctx.gemm_ws != nullptr && ctx.gemm_flags != nullptr);
+    if (ts.parts > 1 && (size_t(ts.tail) * ts.parts * size_t(BM * BN) * sizeof(float) > ctx.gemm_ws_bytes || ts.tail * ts.parts * 4 > ctx.gemm_flag_count))
+        ts = TailSplit{tiles, 0, 1, 0.0, 0.0};
+    p.full_tiles = int(ts.full); p.tail_tiles = int(ts.tail); p.tail_split = ts.parts;
+    p.ws = ctx.gemm_ws; p.flags = ctx.gemm_flags;
+    const int64_t units = ts.full + ts.tail * ts.parts;
+    int grid = int(units < ctx.sm_count ? units : ctx.sm_count);
     if (cv) {
         const double pix = double(cv->N) * cv->HO * cv->WO;
         tag_launch(ctx, "conv2d_igemm_tf32x3_tcgen05", 2.0 * pix * double(a.N) * double(a.K),
@@ -440,7 +615,7 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
         tag_launch(ctx, "gemm_tf32x3_tcgen05", 2.0 * double(a.M) * double(a.N) * double(a.K),
                    4.0 * (double(a.M) * a.K + double(a.N) * a.K + double(a.N) + double(a.M) * a.N));
     }
-    gemm_tf32x3_kernel<BN, BK, STAGES><<<grid, kThreads, smem, ctx.stream>>>(mx, mhi, mlo, p);
+    gemm_tf32x3_kernel<BN, BK, STAGES, ACC, TS><<<grid, kThreads, smem, ctx.stream>>>(mx, mhi, mlo, p);
     FXF_LAUNCHED(ctx);
     return 0;
 }
@@ -466,22 +641,36 @@ bool gemm_tc_shape_ok(int64_t M, int64_t N, int64_t K) {
 // times the tile time (proportional to BN, with a small penalty for narrower tiles whose operand traffic per
 // flop is higher).  E.g. M = 8192 on 148 SMs: N = 768 gives 192 tiles of 256 (2 rounds) but 256 tiles of 192
 // (also 2 rounds, each 25 % shorter); N = 2304 is best at 256.
-int gemm_tc_pick_bn(int64_t M, int64_t N, int sm_count) {
+int gemm_tc_pick_bn(int64_t M, int64_t N, int sm_count, int64_t K) {
     if (N <= 128) return 128;
     const int64_t tiles_m = (M + BM - 1) / BM;
     const int cand[3] = {256, 192, 128};
-    const double penalty[3] = {1.0, 1.05, 1.25};
+    const double penalty[3] = {1.0, 1.08, 1.25};   // time per flop relative to the 256-wide tile (measured on the GPT-2 shapes)
     int best = 256;
     double best_cost = 0;
     for (int i = 0; i < 3; i++) {
-        int64_t tiles = tiles_m * ((N + cand[i] - 1) / cand[i]);
-        double cost = double((tiles + sm_count - 1) / sm_count) * cand[i] * penalty[i];
-        if (i == 0 || cost < best_cost * 0.9) {
+        const int64_t tiles = tiles_m * ((N + cand[i] - 1) / cand[i]);
+        const TailSplit t = plan_tail(tiles, K > 0 ? K : 768, cand[i], sm_count, K > 0);
+        // rounds of whole tiles, plus the (possibly K-split) last round
+        const double cost = (double(t.full / sm_count) * t.tile_us + t.tail_us) * penalty[i];
+        if (i == 0 || cost < best_cost * 0.95) {
             best = cand[i];
             best_cost = cost;
         }
     }
     return best;
+}
+
+// Where the MMAs take A from.  Measured on B200: with 256- and 192-wide tiles the shared-memory variant (two
+// accumulators in TMEM) is faster — TMEM has no room for two 256-column accumulators plus A stages — while
+// 128-wide tiles, whose shared-memory traffic per flop is 1.5x higher, gain 40 % from A in tensor memory.
+// Debug override: FXF_TC_A=smem | tmem forces one variant for every width.
+static bool a_from_smem(int bn) {
+    static const int mode = [] {
+        const char* e = std::getenv("FXF_TC_A");
+        return !e ? 0 : (e[0] == 's' ? 1 : (e[0] == 't' ? 2 : 0));
+    }();
+    return mode == 1 || (mode == 0 && bn > 128);
 }
 
 int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows) {
@@ -491,12 +680,19 @@ int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows) {
         const char* e = std::getenv("FXF_TC_BN");
         return e ? std::atoi(e) : 0;
     }();
-    int bn = forced ? forced : gemm_tc_pick_bn(a.M, a.N, ctx.sm_count);
+    int bn = forced ? forced : gemm_tc_pick_bn(a.M, a.N, ctx.sm_count, ctx.gemm_ws ? a.K : 0);
     if (a.N <= 128) bn = 128;
+    if (a_from_smem(bn)) {
+        switch (bn) {
+            case 256: return launch_tc<256, 16, 4, 2, false>(a, ctx);
+            case 192: return launch_tc<192, 16, 5, 2, false>(a, ctx);
+            default: return launch_tc<128, 32, 3, 2, false>(a, ctx);
+        }
+    }
     switch (bn) {
-        case 256: return launch_tc<256, 16, 4>(a, ctx);
-        case 192: return launch_tc<192, 16, 5>(a, ctx);
-        default: return launch_tc<128, 32, 3>(a, ctx);
+        case 256: return launch_tc<256, 16, 5, 1, true>(a, ctx);
+        case 192: return launch_tc<192, 16, 4, 2, true>(a, ctx);
+        default: return launch_tc<128, 32, 4, 2, true>(a, ctx);
     }
 }
 
@@ -565,11 +761,18 @@ int launch_conv_tc(const ConvTcArgs& c, ExecCtx& ctx) {
     a.K = int64_t(c.KH) * c.KW * c.C;
     a.ldo = c.O;
     a.relu = c.relu;
-    int bn = a.N <= 128 ? 128 : gemm_tc_pick_bn(a.M, a.N, ctx.sm_count);
-    switch (bn) {  // the pixel-box loads use 16-channel slabs, so every width runs the 16-float ring
-        case 256: return launch_tc<256, 16, 4>(a, ctx, &c, &g);
-        case 192: return launch_tc<192, 16, 5>(a, ctx, &c, &g);
-        default: return launch_tc<128, 16, 6>(a, ctx, &c, &g);
+    int bn = a.N <= 128 ? 128 : gemm_tc_pick_bn(a.M, a.N, ctx.sm_count, ctx.gemm_ws ? a.K : 0);
+    if (a_from_smem(bn)) {
+        switch (bn) {
+            case 256: return launch_tc<256, 16, 4, 2, false>(a, ctx, &c, &g);
+            case 192: return launch_tc<192, 16, 5, 2, false>(a, ctx, &c, &g);
+            default: return launch_tc<128, 16, 6, 2, false>(a, ctx, &c, &g);
+        }
+    }
+    switch (bn) {
+        case 256: return launch_tc<256, 16, 5, 1, true>(a, ctx, &c, &g);
+        case 192: return launch_tc<192, 16, 4, 2, true>(a, ctx, &c, &g);
+        default: return c.C % 32 == 0 ? launch_tc<128, 32, 4, 2, true>(a, ctx, &c, &g) : launch_tc<128, 16, 8, 2, true>(a, ctx, &c, &g);
     }
 }
 

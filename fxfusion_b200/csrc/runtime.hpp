@@ -48,6 +48,12 @@ struct ExecCtx {
     int launches = 0;              // incremented by every kernel launch (host-side count)
     int tp_rank = 0, tp_size = 1;  // tensor-parallel position; tp_size > 1 needs `comm`
     void* comm = nullptr;          // fxf_comm* (NCCL communicator wrapper), owned by the caller
+    // workspace of the tensor-core GEMM's K-split last round: partial tiles and their ready flags (zero between
+    // launches).  Without it every tile is computed whole.
+    float* gemm_ws = nullptr;
+    size_t gemm_ws_bytes = 0;
+    int* gemm_flags = nullptr;
+    int gemm_flag_count = 0;
     // profiling: when `trace` is set every launch appends a record carrying the current tag
     std::vector<LaunchRecord>* trace = nullptr;
     int cur_node = -1;
@@ -207,7 +213,8 @@ int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows = false)
 // allow_few_rows: accept M < 64 (a weight-streaming problem: most rows of the 128-row tile are padding, the time is the weight read)
 bool gemm_tc_supported(const GemmArgs& a, bool allow_few_rows = false);
 bool gemm_tc_shape_ok(int64_t M, int64_t N, int64_t K);
-int gemm_tc_pick_bn(int64_t M, int64_t N, int sm_count);
+// K > 0: the launch may cut the tiles of its last round along K (needs the context's GEMM workspace)
+int gemm_tc_pick_bn(int64_t M, int64_t N, int sm_count, int64_t K = 0);
 int launch_split_tf32(const float* w, float* hi, float* lo, int64_t n, ExecCtx& ctx);
 int simt_tile_choice(int64_t M, int64_t N, int sm_count);
 std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count);
