@@ -2,8 +2,11 @@
 //     ctx = softmax(mask_fill(Q·K^T / scale_divisor)) · V        per (batch, head)
 // with both contractions on tcgen05 (kind::tf32, three products per logical product, fp32-grade).
 // Same semantics as attention.cu (reference csrc/kernels/cpu/mha.cpp:38-49): division by the scale,
-// -inf where mask == 0, fully masked rows give NaN, masked keys still enter P·V with weight 0, no key
-// tile is skipped.
+// -inf where mask == 0, fully masked rows give NaN, masked keys still enter P·V with weight 0 (so a
+// non-finite V row poisons the output as 0 * inf does in the reference).  A block of 128 keys is skipped
+// only when that cannot change a bit of the result: every mask byte of the block is 0 for all 128 query
+// rows of the CTA (its probabilities are exactly 0) and the block's V rows are all finite (0 * V = 0).
+// With a causal mask that drops the upper-triangle blocks.
 //
 // Two kernels:
 //   attn_vt_kernel   transposes the V third of the packed projection qkv[B*T, 3D] into V^T [B*H, 64, T]
@@ -48,17 +51,23 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __device__ __forceinline__ void soft_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // ---- V transpose -------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) attn_vt_kernel(const float* __restrict__ qkv, int64_t ld, int64_t v_off, int T, int H, float* __restrict__ vt) {
+// Also records, per (batch*head, 32-key slab), whether any V element is NaN or infinite: vflags[bh * n32 + slab].
+__global__ void __launch_bounds__(256) attn_vt_kernel(const float* __restrict__ qkv, int64_t ld, int64_t v_off, int T, int H, float* __restrict__ vt,
+                                                      unsigned char* __restrict__ vflags) {
     __shared__ float tile[HD][33];
     const int bh = blockIdx.y, b = bh / H, h = bh % H, t0 = blockIdx.x * 32, tid = threadIdx.x;
+    int bad = 0;
 #pragma unroll
     for (int i = 0; i < 2; i++) {
         int f = tid + i * 256, r = f >> 4, c4 = (f & 15) * 4, t = t0 + r;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (t < T) v = *reinterpret_cast<const float4*>(qkv + (int64_t(b) * T + t) * ld + v_off + int64_t(h) * HD + c4);
+        // x - x is 0 for finite x and NaN for NaN / infinity
+        bad |= ((v.x - v.x) != 0.f) | ((v.y - v.y) != 0.f) | ((v.z - v.z) != 0.f) | ((v.w - v.w) != 0.f);
         tile[c4 + 0][r] = v.x; tile[c4 + 1][r] = v.y; tile[c4 + 2][r] = v.z; tile[c4 + 3][r] = v.w;
     }
-    __syncthreads();
+    bad = __syncthreads_or(bad);
+    if (tid == 0) vflags[int64_t(bh) * gridDim.x + blockIdx.x] = bad ? 1 : 0;
     for (int idx = tid; idx < HD * 32; idx += 256) {
         int d = idx >> 5, tt = idx & 31, t = t0 + tt;
         if (t < T) vt[(int64_t(bh) * HD + d) * T + t] = tile[d][tt];
@@ -75,9 +84,12 @@ struct alignas(1024) AttnTcSmem {
     uint64_t bar_q, bar_k, bar_v, bar_qs, bar_ks, bar_vs, bar_s, bar_p, bar_o;
     uint32_t tmem_base;
     int abort_flag;
+    unsigned int need_blocks;   // bit blk set: key block blk has to be processed
 };
 
 struct AttnTcParams {
+    const unsigned char* vflags;   // per (batch*head, 32-key slab): V has a non-finite element
+    int n32;                       // slabs per (batch*head)
     const uint8_t* mask;
     float* ctx;
     int B, T, H;
@@ -130,6 +142,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
         mbar_init(&s.bar_p, 8);
         mbar_init(&s.bar_o, 1);
         s.abort_flag = 0;
+        s.need_blocks = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -141,6 +154,30 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
     tc_fence_after();
     const uint32_t tmem = s.tmem_base;
 
+    // ---- which key blocks matter to this CTA's 128 query rows ----
+    const unsigned int all_blocks = nblk >= 32 ? 0xffffffffu : ((1u << nblk) - 1u);
+    if (p.mask_vec16 && nblk <= 32) {
+        unsigned int mine = 0;
+        const uint8_t* mh = p.mask + int64_t(b) * p.mask_sb + int64_t(h) * p.mask_sh;
+        const int vec_per_row = T / 16, rows = min(BQ, T - q0);
+        for (int idx = threadIdx.x; idx < rows * vec_per_row; idx += kAttnThreads) {
+            const int rr = idx / vec_per_row, vv = idx - rr * vec_per_row;
+            const uint4 m16 = *reinterpret_cast<const uint4*>(mh + int64_t(q0 + rr) * p.mask_sq + vv * 16);
+            if (m16.x | m16.y | m16.z | m16.w) mine |= 1u << (vv / (BKEY / 16));
+        }
+        // a block whose V rows hold NaN or infinity is kept: 0 * inf has to reach the output
+        for (int sl = threadIdx.x; sl < p.n32; sl += kAttnThreads)
+            if (p.vflags[int64_t(bh) * p.n32 + sl]) mine |= 1u << (sl / (BKEY / 32));
+        mine = __reduce_or_sync(0xffffffffu, mine);
+        if (lane == 0 && mine) atomicOr(&s.need_blocks, mine);
+        __syncthreads();
+    } else {
+        if (threadIdx.x == 0) s.need_blocks = all_blocks;
+        __syncthreads();
+    }
+    const unsigned int need = s.need_blocks & all_blocks;
+    const int n_act = __popc(need);
+
     if (warp == 0) {
         if (lane == 0) {
             auto load_k = [&](int blk) {
@@ -151,15 +188,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
                 mbar_expect_tx(&s.bar_v, kVBytes);
                 for (int ks = 0; ks < 4; ks++) tma_load_3d(s.v_hi[ks], &map_vt, blk * BKEY + ks * 32, 0, bh, &s.bar_v);
             };
-            mbar_expect_tx(&s.bar_q, kQBytes);
-            for (int sl = 0; sl < 2; sl++) tma_load_3d(s.q_hi[sl], &map_qkv, p.q_col + h * HD + sl * 32, q0, b, &s.bar_q);
-            load_k(0);
-            load_v(0);
-            if (!mbar_wait(&s.bar_qs, 0, abort_flag)) {
+            unsigned int rem = need;
+            if (n_act > 0) {
+                mbar_expect_tx(&s.bar_q, kQBytes);
+                for (int sl = 0; sl < 2; sl++) tma_load_3d(s.q_hi[sl], &map_qkv, p.q_col + h * HD + sl * 32, q0, b, &s.bar_q);
+                load_k(__ffs(rem) - 1);
+                load_v(__ffs(rem) - 1);
+            }
+            if (n_act > 0 && !mbar_wait(&s.bar_qs, 0, abort_flag)) {
                 give_up(abort_flag, p.status, kErrAttnQ);
             } else {
-                for (int blk = 0; blk < nblk; blk++) {
-                    const uint32_t par = blk & 1;
+                for (int i = 0; i < n_act; i++) {
+                    rem &= rem - 1;                                   // `rem` now holds the blocks after this one
+                    const int next_blk = rem ? __ffs(rem) - 1 : -1;
+                    const uint32_t par = i & 1;
                     if (!mbar_wait(&s.bar_ks, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnK); break; }
                     tc_fence_after();
                     // S = Q · K_blk^T
@@ -176,9 +218,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
                         }
                     }
                     umma_commit(&s.bar_s);
-                    if (blk + 1 < nblk) {  // K buffer is free once the S MMAs have completed
+                    if (next_blk >= 0) {  // K buffer is free once the S MMAs have completed
                         if (!mbar_wait(&s.bar_s, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnS); break; }
-                        load_k(blk + 1);
+                        load_k(next_blk);
                     }
                     if (!mbar_wait(&s.bar_vs, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnV); break; }
                     if (!mbar_wait(&s.bar_p, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnP); break; }
@@ -197,9 +239,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
                         }
                     }
                     umma_commit(&s.bar_o);
-                    if (blk + 1 < nblk) {  // V buffer is free once the P·V MMAs have completed
+                    if (next_blk >= 0) {  // V buffer is free once the P·V MMAs have completed
                         if (!mbar_wait(&s.bar_o, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnO); break; }
-                        load_v(blk + 1);
+                        load_v(next_blk);
                     }
                 }
             }
@@ -220,15 +262,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
         bool alive = true;   // a thread that gave up keeps walking the loop so that soft_sync() stays matched
 
         // Q split (once)
-        if (alive && !mbar_wait(&s.bar_q, 0, abort_flag)) { give_up(abort_flag, p.status, kErrAttnQ); alive = false; }
-        if (alive) {
+        if (n_act > 0 && alive && !mbar_wait(&s.bar_q, 0, abort_flag)) { give_up(abort_flag, p.status, kErrAttnQ); alive = false; }
+        if (n_act > 0 && alive) {
             split_tile(s.q_hi[0], s.q_lo[0], 2 * BQ * 32 / 4, st);
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(&s.bar_qs);
         }
-        for (int blk = 0; blk < nblk; blk++) {
-            const uint32_t par = blk & 1;
+        unsigned int rem = need;
+        for (int i = 0; i < n_act; i++) {
+            const int blk = __ffs(rem) - 1;
+            rem &= rem - 1;
+            const uint32_t par = i & 1;
             // ---- split K and V of this block as they land ----
             if (alive && !mbar_wait(&s.bar_k, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnK); alive = false; }
             if (alive) {
@@ -408,14 +453,18 @@ bool attention_tc_supported(const AttnArgs& a, int gemm_mode) {
     return true;
 }
 
-size_t attention_tc_scratch_bytes(int64_t B, int64_t T, int64_t H) { return size_t(B) * size_t(T) * size_t(H) * HD * sizeof(float); }
+// V^T [B*H, 64, T] followed by one "non-finite" byte per (batch*head, 32-key slab)
+size_t attention_tc_scratch_bytes(int64_t B, int64_t T, int64_t H) {
+    return size_t(B) * size_t(T) * size_t(H) * HD * sizeof(float) + round_up(size_t(B) * size_t(H) * size_t((T + 31) / 32), 256);
+}
 
 int launch_attention_tc(const AttnArgs& a, float* vt_scratch, ExecCtx& ctx) {
     FXF_CHECK(vt_scratch != nullptr && aligned16(vt_scratch), "attention: tensor-core path needs its V^T buffer");
     const int64_t BH = int64_t(a.B) * a.H;
     dim3 pgrid(unsigned((a.T + 31) / 32), unsigned(BH));
     tag_launch(ctx, "attention_v_transpose", 0, 8.0 * double(BH) * a.T * HD);
-    attn_vt_kernel<<<pgrid, 256, 0, ctx.stream>>>(a.qkv, a.ld_qkv, a.v_off, a.T, a.H, vt_scratch);
+    unsigned char* vflags = reinterpret_cast<unsigned char*>(vt_scratch + size_t(BH) * size_t(a.T) * HD);
+    attn_vt_kernel<<<pgrid, 256, 0, ctx.stream>>>(a.qkv, a.ld_qkv, a.v_off, a.T, a.H, vt_scratch, vflags);
     FXF_LAUNCHED(ctx);
 
     CUtensorMap mq, mk, mv;
@@ -424,6 +473,7 @@ int launch_attention_tc(const AttnArgs& a, float* vt_scratch, ExecCtx& ctx) {
     if (make_map3(&mk, a.qkv, a.ld_qkv, a.T, a.B, a.ld_qkv * 4, int64_t(a.T) * a.ld_qkv * 4, BKEY)) return 1;
     if (make_map3(&mv, vt_scratch, a.T, HD, BH, int64_t(a.T) * 4, int64_t(a.T) * HD * 4, HD)) return 1;
     AttnTcParams p;
+    p.vflags = vflags; p.n32 = int((a.T + 31) / 32);
     p.mask = a.mask; p.ctx = a.ctx; p.B = a.B; p.T = a.T; p.H = a.H; p.ld_ctx = a.ld_ctx;
     p.q_col = int(a.q_off); p.k_col = int(a.k_off);
     p.mask_sb = a.mask_sb; p.mask_sh = a.mask_sh; p.mask_sq = a.mask_sq; p.mask_sk = a.mask_sk;

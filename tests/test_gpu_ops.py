@@ -94,16 +94,36 @@ def test_mha_fully_masked_rows_and_nan_values(built_lib):
     """A fully masked query row is NaN; a NaN in the input poisons exactly what torch's matmul poisons."""
     _masked_rows_and_nan(2, 12, 2, 8)
     _masked_rows_and_nan(2, 132, 2, 64)   # the tcgen05 attention kernel, two key blocks
+    # three key blocks, causal: the kernel may skip a block whose mask bytes are all zero, but not one whose V rows
+    # hold a NaN (position 300 is masked for the first 300 queries and still poisons them, as 0 * NaN does in torch)
+    _masked_rows_and_nan(2, 384, 2, 64, nan_pos=300)
 
 
-def _masked_rows_and_nan(B, T, H, hd):
+def test_mha_block_sparse_masks(built_lib):
+    """Masks with whole 128-key blocks of zeros (skipped by the tcgen05 kernel) next to fully masked rows and a CTA
+    whose every block is masked."""
+    B, T, H, hd = 2, 512, 2, 64
+    mask = torch.ones(B, 1, T, T, dtype=torch.bool)
+    mask[:, :, :, 128:256] = False            # one key block is dead for every query
+    mask[0, :, 256:384, :] = False            # batch 0: a whole query tile sees nothing -> NaN rows
+    mask[1, :, 5, :] = False                  # batch 1: one fully masked row
+    mask[1, :, 384:, :384] = False            # batch 1: the last query tile sees only the last key block
+    got = both("MHA", _mha_reg(B, T, H, hd, mask), [0, 1, 2, 3, 4, 5], [6], ints=[H, hd, H * hd, 3 * H * hd], floats=[math.sqrt(hd)])
+    assert torch.isnan(got[0, 256:384]).all() and torch.isnan(got[1, 5]).all() and not torch.isnan(got[1, 384:]).any()
+    # an infinite V element inside the dead block still reaches every row (0 * inf = NaN in the reference)
+    reg = _mha_reg(B, T, H, hd, mask)
+    reg[0][1, 200, :] = float("inf")
+    both("MHA", reg, [0, 1, 2, 3, 4, 5], [6], ints=[H, hd, H * hd, 3 * H * hd], floats=[math.sqrt(hd)])
+
+
+def _masked_rows_and_nan(B, T, H, hd, nan_pos=9):
     mask = torch.ones(B, 1, T, T, dtype=torch.bool)
     mask[0, 0, 3, :] = False
     reg = _mha_reg(B, T, H, hd, mask)
     got = both("MHA", reg, [0, 1, 2, 3, 4, 5], [6], ints=[H, hd, H * hd, 3 * H * hd], floats=[math.sqrt(hd)])
     assert torch.isnan(got[0, 3]).all() and not torch.isnan(got[1]).any()
     reg = _mha_reg(B, T, H, hd, torch.tril(torch.ones(T, T, dtype=torch.bool)).view(1, 1, T, T).expand(B, 1, T, T).contiguous())
-    reg[0][1, 9, :] = float("nan")  # a NaN token late in the sequence: masked for earlier queries, weight 0 * NaN
+    reg[0][1, nan_pos, :] = float("nan")  # a NaN token late in the sequence: masked for earlier queries, weight 0 * NaN
     both("MHA", reg, [0, 1, 2, 3, 4, 5], [6], ints=[H, hd, H * hd, 3 * H * hd], floats=[math.sqrt(hd)])
 
 
