@@ -278,7 +278,7 @@ def run_ours(args):
 
     # ---- opt-in loop: vocabulary projection only on the row the loop reads (whole 128-step decode) -----
     lr_ms, lr_match = None, None
-    if eng.supports_last_row:
+    if eng.supports_last_row and not args.no_extras:
         lr_buf = start_buf.cuda()
         warm = start_buf.cuda()
         eng.decode_static(warm, T - 3, last_row_only=True)
@@ -472,6 +472,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--precision", default="auto", choices=["auto", "fp32_simt", "fp32_3xtf32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the opt-in last-row-projection decode measurement (keeps profiler captures short)")
     ap.add_argument("--parallel", default="replicas", choices=["replicas", "tp"],
                     help="N > 1: independent batch replicas (default) or tensor-parallel groups (head-sharded MHA, split FeedForward, NCCL all-reduce)")
     args = ap.parse_args()

@@ -103,17 +103,22 @@ struct AttnTcParams {
     int* status;
 };
 
-// hi in place, lo into the twin buffer, for `n4` float4s, by the 256 softmax threads
-__device__ __forceinline__ void split_tile(float* hi_buf, float* lo_buf, int n4, int t) {
-    float4* hi = reinterpret_cast<float4*>(hi_buf);
+// x - (x with its 13 low mantissa bits cleared), rounded to TF32: the part of x a TF32 MMA does not see
+__device__ __forceinline__ float lo_of_truncated(float x) {
+    const float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+    return __uint_as_float(to_tf32(x - hi));
+}
+// The MMA reads only the upper 19 bits of an fp32 operand in shared memory, so the tile TMA wrote already is the
+// "hi" operand (x truncated to TF32); the 256 softmax threads write only the "lo" twin, for `n4` float4s.
+__device__ __forceinline__ void split_tile(const float* hi_buf, float* lo_buf, int n4, int t) {
+    const float4* hi = reinterpret_cast<const float4*>(hi_buf);
     float4* lo = reinterpret_cast<float4*>(lo_buf);
     for (int i = t; i < n4; i += 256) {
-        float4 v = hi[i], h, l;
-        split_tf32(v.x, h.x, l.x);
-        split_tf32(v.y, h.y, l.y);
-        split_tf32(v.z, h.z, l.z);
-        split_tf32(v.w, h.w, l.w);
-        hi[i] = h;
+        float4 v = hi[i], l;
+        l.x = lo_of_truncated(v.x);
+        l.y = lo_of_truncated(v.y);
+        l.z = lo_of_truncated(v.z);
+        l.w = lo_of_truncated(v.w);
         lo[i] = l;
     }
 }

@@ -5,18 +5,21 @@
 // torch::linear, csrc/kernels/cpu/linear.cpp:11, feedforward.cpp:13, mha.cpp:22,51; the
 // reference CUDA kernel is a 32x32 SIMT tile, csrc/kernels/cuda/linear.cu:5-41).
 //
-// Arithmetic.  x = x_hi + x_lo with x_hi = tf32(x) (round to nearest, 10-bit mantissa) and
-// x_lo = tf32(x - x_hi); same for w.  x·w ~= x_lo·w_hi + x_hi·w_lo + x_hi·w_hi, accumulated in
-// fp32; the dropped x_lo·w_lo term is ~2^-22 relative.  Weights are constants: they are split
-// once when an engine is built (split_tf32_kernel) and kept as two arrays.  Activations are split
-// inside the kernel, on their way from shared memory to TENSOR MEMORY, while the tensor core works on
-// earlier stages: the MMAs take their A operand (x_hi, x_lo) from TMEM and only B (w_hi, w_lo) from
-// shared memory.
+// Arithmetic.  x = x_hi + x_lo with x_hi the TF32 the tensor core sees and x_lo = tf32(x - x_hi); same
+// for w.  x·w ~= x_lo·w_hi + x_hi·w_lo + x_hi·w_hi, accumulated in fp32; the dropped x_lo·w_lo term is
+// ~2^-21 relative.  Weights are constants: they are split once when an engine is built
+// (split_tf32_kernel, x_hi rounded to nearest) and kept as two arrays.  Activations are split inside
+// the kernel while the tensor core works on earlier stages, in one of two ways:
+//   A in shared memory (256-wide tiles): a TF32 MMA ignores the 13 low mantissa bits of an fp32 operand,
+//     so the tile TMA wrote already is x_hi (x truncated); four warps write only x_lo into a twin buffer.
+//   A in tensor memory (192- and 128-wide tiles): one thread per tile row reads its BK floats, splits
+//     them (x_hi rounded to nearest) and stores x_hi / x_lo with tcgen05.st; the MMAs take A from TMEM
+//     and only B (w_hi, w_lo) from shared memory.
 //
-// Why A lives in TMEM.  With both operands in shared memory a 128 x 256 x 8 tf32 MMA reads 12 KB in its
-// 136 clocks (90 B/clk of the SM's 128 B/clk); adding the split pass (read x, write x_hi and x_lo)
-// the kernel sat at the shared-memory limit with the tensor pipe 77 % busy.  From TMEM the MMA
-// reads 8 KB per instruction and the split writes nothing to shared memory: about 70 B/clk.
+// Why two ways.  The kernel is bound by the shared-memory data pipe before the tensor pipe: with both
+// operands in shared memory, operand reads and the split pass each took ~46 % of its wavefronts.
+// Writing only x_lo removes a third of the split traffic; A in TMEM removes the split stores and the
+// A operand reads, but TMEM (512 columns) cannot hold two 256-column accumulators plus A stages.
 //
 // Structure: a PERSISTENT kernel, one CTA per SM, each CTA walking a strided list of 128 x BN output
 // tiles.  320 threads in four roles that only meet on mbarriers:
@@ -29,8 +32,7 @@
 //   warp 5     one thread issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8), 3 products per K-step,
 //              accumulating in TMEM; tcgen05.commit hands the stage back to the producer and, after
 //              the last slab of a tile, the accumulator to the epilogue.
-//   warps 6-9  one thread per tile row: reads its BK floats of x from the (swizzled) stage, splits them
-//              and stores x_hi / x_lo with tcgen05.st into the stage's 2*BK TMEM columns, then arrives.
+//   warps 6-9  the activation split of a landed stage (either way above), then arrive.
 // TMEM columns: [0, ACC*BN) accumulators, then STAGES x (BK hi + BK lo) columns of A.
 // Every mbarrier wait is bounded by a wall-clock budget; on expiry the CTA records an error in the
 // status word, all roles stop issuing work, the CTA frees its TMEM and returns.
@@ -103,6 +105,12 @@ struct TcParams {
     int* flags;
     int* status;
 };
+
+// x - (x with its 13 low mantissa bits cleared), rounded to TF32: the part of x a TF32 MMA does not see
+__device__ __forceinline__ float lo_of_truncated(float x) {
+    const float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+    return __uint_as_float(to_tf32(x - hi));
+}
 
 struct Unit {
     int tile, k0, k1, part, nparts, u;
@@ -326,16 +334,17 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         give_up(abort_flag, p.status, kErrWaitTma);
                         goto split_done;
                     }
-                    float4* hi = reinterpret_cast<float4*>(s.a[st]);
+                    // The MMA reads only the upper 19 bits of an fp32 operand, so the tile TMA wrote already IS x_hi
+                    // (x truncated to TF32); only x_lo = tf32(x - trunc(x)) has to be written.
+                    const float4* hi = reinterpret_cast<const float4*>(s.a[st]);
                     float4* lo = reinterpret_cast<float4*>(s.a_lo[st]);
 #pragma unroll
                     for (int i = 0; i < (BM * BK / 4) / 128; i++) {
-                        float4 v = hi[t + i * 128], h, l;
-                        split_tf32(v.x, h.x, l.x);
-                        split_tf32(v.y, h.y, l.y);
-                        split_tf32(v.z, h.z, l.z);
-                        split_tf32(v.w, h.w, l.w);
-                        hi[t + i * 128] = h;
+                        float4 v = hi[t + i * 128], l;
+                        l.x = lo_of_truncated(v.x);
+                        l.y = lo_of_truncated(v.y);
+                        l.z = lo_of_truncated(v.z);
+                        l.w = lo_of_truncated(v.w);
                         lo[t + i * 128] = l;
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA (async proxy)
@@ -645,7 +654,7 @@ int gemm_tc_pick_bn(int64_t M, int64_t N, int sm_count, int64_t K) {
     if (N <= 128) return 128;
     const int64_t tiles_m = (M + BM - 1) / BM;
     const int cand[3] = {256, 192, 128};
-    const double penalty[3] = {1.0, 1.08, 1.25};   // time per flop relative to the 256-wide tile (measured on the GPT-2 shapes)
+    const double penalty[3] = {1.0, 1.10, 1.25};   // time per flop relative to the 256-wide tile (measured on the GPT-2 shapes)
     int best = 256;
     double best_cost = 0;
     for (int i = 0; i < 3; i++) {
@@ -661,16 +670,18 @@ int gemm_tc_pick_bn(int64_t M, int64_t N, int sm_count, int64_t K) {
     return best;
 }
 
-// Where the MMAs take A from.  Measured on B200: with 256- and 192-wide tiles the shared-memory variant (two
-// accumulators in TMEM) is faster — TMEM has no room for two 256-column accumulators plus A stages — while
-// 128-wide tiles, whose shared-memory traffic per flop is 1.5x higher, gain 40 % from A in tensor memory.
+// Where the MMAs take A from.  With A in shared memory the kernel saturates the shared-memory data pipe (192-wide
+// tiles: operand reads 48 % + split loads/stores 48 % of its wavefronts, tensor pipe 62 %); from tensor memory the
+// split writes nothing to shared memory and the MMA reads only B there.  Measured on B200: 128-wide tiles gain 40 %,
+// 192-wide 5-7 %.  256-wide tiles keep A in shared memory: TMEM has no room for two 256-column accumulators plus
+// A stages, and one accumulator (no epilogue overlap) costs more than the shared-memory pressure.
 // Debug override: FXF_TC_A=smem | tmem forces one variant for every width.
 static bool a_from_smem(int bn) {
     static const int mode = [] {
         const char* e = std::getenv("FXF_TC_A");
         return !e ? 0 : (e[0] == 's' ? 1 : (e[0] == 't' ? 2 : 0));
     }();
-    return mode == 1 || (mode == 0 && bn > 128);
+    return mode == 1 || (mode == 0 && bn > 192);
 }
 
 int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows) {
