@@ -46,18 +46,21 @@ __global__ void __launch_bounds__(256) attention_kernel(AttnArgs a) {
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
     const int q0 = blockIdx.x * kBQ;
-    const int T = a.T, hd = a.hd;
-    const bool vec = (hd % 4 == 0) && (a.ld_qkv % 4 == 0) && ((a.q_off | a.k_off | a.v_off) % 4 == 0);
+    const int T = a.T, hd = a.hd;                      // T = number of queries per batch
+    const int Tk = a.kv ? a.Tk : a.T;                   // number of keys per batch
+    const float* kvp = a.kv ? a.kv : a.qkv;
+    const int64_t ldk = a.kv ? a.ld_kv : a.ld_qkv;
+    const bool vec = (hd % 4 == 0) && (a.ld_qkv % 4 == 0) && (ldk % 4 == 0) && ((a.q_off | a.k_off | a.v_off) % 4 == 0);
 
     const float* qbase = a.qkv + int64_t(b) * T * a.ld_qkv + a.q_off + int64_t(h) * hd;
-    const float* kbase = a.qkv + int64_t(b) * T * a.ld_qkv + a.k_off + int64_t(h) * hd;
-    const float* vbase = a.qkv + int64_t(b) * T * a.ld_qkv + a.v_off + int64_t(h) * hd;
+    const float* kbase = kvp + int64_t(b) * Tk * ldk + a.k_off + int64_t(h) * hd;
+    const float* vbase = kvp + int64_t(b) * Tk * ldk + a.v_off + int64_t(h) * hd;
 
-    auto load_row4 = [&](const float* base, int row, int d4) -> float4 {
+    auto load_row4 = [&](const float* base, int64_t ld, int rows, int row, int d4) -> float4 {
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         int d = d4 * 4;
-        if (row < T && d < hd) {
-            const float* p = base + int64_t(row) * a.ld_qkv + d;
+        if (row < rows && d < hd) {
+            const float* p = base + int64_t(row) * ld + d;
             if (vec) {
                 v = *reinterpret_cast<const float4*>(p);
             } else {
@@ -73,7 +76,7 @@ __global__ void __launch_bounds__(256) attention_kernel(AttnArgs a) {
     // Q tile (zero-padded beyond T rows / hd columns)
     for (int f = tid; f < kBQ * DQ; f += 256) {
         int r = f / DQ, d4 = f % DQ;
-        float4 v = load_row4(qbase, q0 + r, d4);
+        float4 v = load_row4(qbase, a.ld_qkv, T, q0 + r, d4);
         s.q[d4 * 4 + 0][r] = v.x; s.q[d4 * 4 + 1][r] = v.y; s.q[d4 * 4 + 2][r] = v.z; s.q[d4 * 4 + 3][r] = v.w;
     }
 
@@ -89,13 +92,13 @@ __global__ void __launch_bounds__(256) attention_kernel(AttnArgs a) {
 
     const uint8_t* mbase = a.mask + int64_t(b) * a.mask_sb + int64_t(h) * a.mask_sh;
 
-    for (int k0 = 0; k0 < T; k0 += kBK) {
+    for (int k0 = 0; k0 < Tk; k0 += kBK) {
         __syncthreads();  // previous tile fully consumed (also orders the Q stores on the first pass)
         for (int f = tid; f < kBK * DQ; f += 256) {
             int r = f / DQ, d4 = f % DQ;
-            float4 kv = load_row4(kbase, k0 + r, d4);
+            float4 kv = load_row4(kbase, ldk, Tk, k0 + r, d4);
             s.k[d4 * 4 + 0][r] = kv.x; s.k[d4 * 4 + 1][r] = kv.y; s.k[d4 * 4 + 2][r] = kv.z; s.k[d4 * 4 + 3][r] = kv.w;
-            float4 vv = load_row4(vbase, k0 + r, d4);
+            float4 vv = load_row4(vbase, ldk, Tk, k0 + r, d4);
             *reinterpret_cast<float4*>(&s.v[r][d4 * 4]) = vv;
         }
         __syncthreads();
@@ -127,7 +130,7 @@ __global__ void __launch_bounds__(256) attention_kernel(AttnArgs a) {
                 int kc = k0 + tx * 4 + j;
                 float v = sc[i][j] / a.scale_divisor;
                 bool keep = false;
-                if (kc < T && qr < T) keep = mbase[int64_t(qr) * a.mask_sq + int64_t(kc) * a.mask_sk] != 0;
+                if (kc < Tk && qr < T) keep = mbase[int64_t(qr) * a.mask_sq + int64_t(kc) * a.mask_sk] != 0;
                 v = keep ? v : -INFINITY;
                 sc[i][j] = v;
                 tmax = fmaxf(tmax, v);  // NaN scores do not move the max; they reach the sum below
@@ -199,8 +202,9 @@ int launch_hd(const AttnArgs& a, ExecCtx& ctx) {
 int launch_attention(const AttnArgs& a, ExecCtx& ctx) {
     if (a.B == 0 || a.T == 0 || a.H == 0) return 0;
     FXF_CHECK(a.hd >= 1 && a.hd <= 128, "mha: head_dim %d is outside the supported range 1..128", a.hd);
-    tag_launch(ctx, "attention_fp32_flash", 4.0 * double(a.B) * a.H * double(a.T) * a.T * a.hd,
-               4.0 * 4.0 * double(a.B) * a.T * double(a.H) * a.hd + double(a.B) * a.T * a.T);
+    const double tk = a.kv ? a.Tk : a.T;
+    tag_launch(ctx, "attention_fp32_flash", 4.0 * double(a.B) * a.H * double(a.T) * tk * a.hd,
+               4.0 * 2.0 * double(a.B) * (double(a.T) + tk) * double(a.H) * a.hd + double(a.B) * a.T * tk);
     if (a.hd <= 16) return launch_hd<16>(a, ctx);
     if (a.hd <= 32) return launch_hd<32>(a, ctx);
     if (a.hd <= 64) return launch_hd<64>(a, ctx);

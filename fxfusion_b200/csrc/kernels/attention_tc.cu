@@ -92,8 +92,8 @@ struct AttnTcParams {
     int n32;                       // slabs per (batch*head)
     const uint8_t* mask;
     float* ctx;
-    int B, T, H;
-    int q_col, k_col;     // first column of the Q / K thirds inside a qkv row
+    int B, T, Tk, H;      // T queries and Tk keys per batch
+    int q_col, k_col;     // first column of the Q block inside a query row / of the K block inside a key row
     int64_t ld_ctx;
     int64_t mask_sb, mask_sh, mask_sq, mask_sk;
     float scale_divisor;
@@ -129,8 +129,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
     extern __shared__ unsigned char smem_raw[];
     AttnTcSmem& s = *reinterpret_cast<AttnTcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H, q0 = blockIdx.x * BQ, T = p.T;
-    const int nblk = (T + BKEY - 1) / BKEY;
+    const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H, q0 = blockIdx.x * BQ, T = p.T, Tk = p.Tk;
+    const int nblk = (Tk + BKEY - 1) / BKEY;
     volatile int* abort_flag = &s.abort_flag;
     constexpr uint32_t kQBytes = BQ * HD * 4, kKBytes = BKEY * HD * 4, kVBytes = HD * BKEY * 4;
     constexpr uint32_t kColS = 0, kColPhi = 128, kColPlo = 256, kColO = 384;
@@ -164,7 +164,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
     if (p.mask_vec16 && nblk <= 32) {
         unsigned int mine = 0;
         const uint8_t* mh = p.mask + int64_t(b) * p.mask_sb + int64_t(h) * p.mask_sh;
-        const int vec_per_row = T / 16, rows = min(BQ, T - q0);
+        const int vec_per_row = Tk / 16, rows = min(BQ, T - q0);
         for (int idx = threadIdx.x; idx < rows * vec_per_row; idx += kAttnThreads) {
             const int rr = idx / vec_per_row, vv = idx - rr * vec_per_row;
             const uint4 m16 = *reinterpret_cast<const uint4*>(mh + int64_t(q0 + rr) * p.mask_sq + vv * 16);
@@ -301,14 +301,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
                 for (int it = 0; it < 4; it++) {
                     int rr = quarter * 32 + it * 8 + (lane >> 2), kq = key0 + (lane & 3) * 16, qq = q0 + rr;
                     uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                    if (qq < T && kq < T) v = *reinterpret_cast<const uint4*>(mhead + int64_t(qq) * p.mask_sq + kq);
+                    if (qq < T && kq < Tk) v = *reinterpret_cast<const uint4*>(mhead + int64_t(qq) * p.mask_sq + kq);
                     *reinterpret_cast<uint4*>(s.mask_rows + rr * kMaskPitch + half * 64 + (lane & 3) * 16) = v;
                 }
             } else {
                 for (int idx = lane; idx < 32 * 64; idx += 32) {
                     int rr = quarter * 32 + (idx >> 6), kc = key0 + (idx & 63), qq = q0 + rr;
                     unsigned char v = 0;
-                    if (qq < T && kc < T) v = mhead[int64_t(qq) * p.mask_sq + int64_t(kc) * p.mask_sk];
+                    if (qq < T && kc < Tk) v = mhead[int64_t(qq) * p.mask_sq + int64_t(kc) * p.mask_sk];
                     s.mask_rows[rr * kMaskPitch + half * 64 + (idx & 63)] = v;
                 }
             }
@@ -452,8 +452,10 @@ int make_map3(CUtensorMap* map, const float* base, int64_t n0, int64_t n1, int64
 
 bool attention_tc_supported(const AttnArgs& a, int gemm_mode) {
     if (gemm_mode == FXF_GEMM_FP32_SIMT) return false;
-    if (a.hd != HD || a.T % 4 != 0 || a.T < 16) return false;
+    const int Tk = a.kv ? a.Tk : a.T;
+    if (a.hd != HD || Tk % 4 != 0 || Tk < 16 || a.T < 1) return false;   // V^T rows (Tk floats) must be 16-byte multiples
     if (a.ld_qkv % 4 != 0 || a.ld_ctx % 4 != 0 || (a.q_off | a.k_off | a.v_off) % 4 != 0) return false;
+    if (a.kv && (a.ld_kv % 4 != 0 || !aligned16(a.kv))) return false;
     if (!aligned16(a.qkv) || !aligned16(a.ctx)) return false;
     return true;
 }
@@ -466,20 +468,23 @@ size_t attention_tc_scratch_bytes(int64_t B, int64_t T, int64_t H) {
 int launch_attention_tc(const AttnArgs& a, float* vt_scratch, ExecCtx& ctx) {
     FXF_CHECK(vt_scratch != nullptr && aligned16(vt_scratch), "attention: tensor-core path needs its V^T buffer");
     const int64_t BH = int64_t(a.B) * a.H;
-    dim3 pgrid(unsigned((a.T + 31) / 32), unsigned(BH));
-    tag_launch(ctx, "attention_v_transpose", 0, 8.0 * double(BH) * a.T * HD);
-    unsigned char* vflags = reinterpret_cast<unsigned char*>(vt_scratch + size_t(BH) * size_t(a.T) * HD);
-    attn_vt_kernel<<<pgrid, 256, 0, ctx.stream>>>(a.qkv, a.ld_qkv, a.v_off, a.T, a.H, vt_scratch, vflags);
+    const int Tk = a.kv ? a.Tk : a.T;                     // keys per batch
+    const float* kvp = a.kv ? a.kv : a.qkv;               // where K and V live
+    const int64_t ldk = a.kv ? a.ld_kv : a.ld_qkv;
+    dim3 pgrid(unsigned((Tk + 31) / 32), unsigned(BH));
+    tag_launch(ctx, "attention_v_transpose", 0, 8.0 * double(BH) * Tk * HD);
+    unsigned char* vflags = reinterpret_cast<unsigned char*>(vt_scratch + size_t(BH) * size_t(Tk) * HD);
+    attn_vt_kernel<<<pgrid, 256, 0, ctx.stream>>>(kvp, ldk, a.v_off, Tk, a.H, vt_scratch, vflags);
     FXF_LAUNCHED(ctx);
 
     CUtensorMap mq, mk, mv;
     // Q and K tiles come straight out of the packed projection: [B, T, ld] with the row pitch of qkv
     if (make_map3(&mq, a.qkv, a.ld_qkv, a.T, a.B, a.ld_qkv * 4, int64_t(a.T) * a.ld_qkv * 4, BQ)) return 1;
-    if (make_map3(&mk, a.qkv, a.ld_qkv, a.T, a.B, a.ld_qkv * 4, int64_t(a.T) * a.ld_qkv * 4, BKEY)) return 1;
-    if (make_map3(&mv, vt_scratch, a.T, HD, BH, int64_t(a.T) * 4, int64_t(a.T) * HD * 4, HD)) return 1;
+    if (make_map3(&mk, kvp, ldk, Tk, a.B, ldk * 4, int64_t(Tk) * ldk * 4, BKEY)) return 1;
+    if (make_map3(&mv, vt_scratch, Tk, HD, BH, int64_t(Tk) * 4, int64_t(Tk) * HD * 4, HD)) return 1;
     AttnTcParams p;
-    p.vflags = vflags; p.n32 = int((a.T + 31) / 32);
-    p.mask = a.mask; p.ctx = a.ctx; p.B = a.B; p.T = a.T; p.H = a.H; p.ld_ctx = a.ld_ctx;
+    p.vflags = vflags; p.n32 = int((Tk + 31) / 32);
+    p.mask = a.mask; p.ctx = a.ctx; p.B = a.B; p.T = a.T; p.Tk = Tk; p.H = a.H; p.ld_ctx = a.ld_ctx;
     p.q_col = int(a.q_off); p.k_col = int(a.k_off);
     p.mask_sb = a.mask_sb; p.mask_sh = a.mask_sh; p.mask_sq = a.mask_sq; p.mask_sk = a.mask_sk;
     p.scale_divisor = a.scale_divisor;
@@ -489,7 +494,7 @@ int launch_attention_tc(const AttnArgs& a, float* vt_scratch, ExecCtx& ctx) {
         p.scale_is_pow2 = (m == 0.5f && a.scale_divisor > 0.f && std::isfinite(a.scale_divisor)) ? 1 : 0;
         p.inv_scale = p.scale_is_pow2 ? 1.0f / a.scale_divisor : 0.f;
     }
-    p.mask_vec16 = (a.mask_sk == 1 && a.T % 16 == 0 && a.mask_sb % 16 == 0 && a.mask_sh % 16 == 0 && a.mask_sq % 16 == 0 && aligned16(a.mask)) ? 1 : 0;
+    p.mask_vec16 = (a.mask_sk == 1 && Tk % 16 == 0 && a.mask_sb % 16 == 0 && a.mask_sh % 16 == 0 && a.mask_sq % 16 == 0 && aligned16(a.mask)) ? 1 : 0;
     p.status = ctx.status;
     size_t smem = sizeof(AttnTcSmem) + 1024;
     static bool configured[64] = {};
@@ -500,8 +505,8 @@ int launch_attention_tc(const AttnArgs& a, float* vt_scratch, ExecCtx& ctx) {
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     dim3 grid(unsigned((a.T + BQ - 1) / BQ), unsigned(BH));
-    tag_launch(ctx, "attention_tf32x3_tcgen05", 4.0 * double(a.B) * a.H * double(a.T) * a.T * a.hd,
-               4.0 * 4.0 * double(a.B) * a.T * double(a.H) * a.hd + double(a.B) * a.T * a.T);
+    tag_launch(ctx, "attention_tf32x3_tcgen05", 4.0 * double(a.B) * a.H * double(a.T) * Tk * a.hd,
+               4.0 * 2.0 * double(a.B) * (double(a.T) + Tk) * double(a.H) * a.hd + double(a.B) * a.T * Tk);
     attn_tc_kernel<<<grid, kAttnThreads, smem, ctx.stream>>>(mq, mk, mv, p);
     FXF_LAUNCHED(ctx);
     return 0;

@@ -241,6 +241,11 @@ int launch_conv_weight_split(const float* w_oihw, float* hi, float* lo, int O, i
 // Attention core on packed qkv [B,T,3D] (Q | K | V thirds, head h at columns h*hd) -> ctx [B,T,D].
 struct AttnArgs {
     const float* qkv = nullptr;
+    // Cross-attention: keys and values come from `kv` (rows of ld_kv floats, Tk rows per batch) while the queries
+    // stay in `qkv`; self-attention leaves kv NULL and K/V are read from `qkv` with T rows.
+    const float* kv = nullptr;
+    int64_t ld_kv = 0;
+    int Tk = 0;
     const uint8_t* mask = nullptr;
     float* ctx = nullptr;
     int B = 0, T = 0, H = 0, hd = 0;
