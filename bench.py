@@ -427,6 +427,21 @@ def run_latency(args):
         inputs = [torch.randn(nb, 3, 224, 224, generator=torch.Generator().manual_seed(0)).cuda()]
         flops = sum(2.0 * float(np_.size) for np_ in ()) or 8.2e9 * nb
         weight_bytes = 4.0 * sum(int(v.size) for v in lowering.resnet50_params(0).values())
+    elif args.workload == "c4":
+        cfg = lowering.TRANSFORMER_C4
+        nb = args.m if args.m != 8192 else 64
+        L = 256
+        g = lowering.transformer_graph(cfg, lowering.transformer_params(cfg, 0), batch=nb, src_len=L, tgt_len=L, name="c4_encdec")
+        gen = torch.Generator().manual_seed(0)
+        inputs = [torch.randint(1, cfg.vocab, (nb, L), generator=gen).cuda(), torch.randint(1, cfg.vocab, (nb, L), generator=gen).cuda(),
+                  torch.ones(nb, 1, 1, L, dtype=torch.bool).cuda(),
+                  torch.tril(torch.ones(L, L, dtype=torch.bool)).view(1, 1, L, L).expand(nb, 1, L, L).contiguous().cuda()]
+        M, D, F, V, H = nb * L, cfg.d_model, cfg.d_ff, cfg.vocab, cfg.heads
+        attn = 4.0 * nb * H * L * L * (D // H)
+        enc = cfg.enc_layers * (2.0 * M * 3 * D * D + attn + 2.0 * M * D * D + 4.0 * M * D * F)
+        dec = cfg.dec_layers * (2.0 * M * 3 * D * D + attn + 2.0 * M * D * D + (2.0 * M * D * D + 2.0 * M * 2 * D * D + attn + 2.0 * M * D * D) + 4.0 * M * D * F)
+        flops = enc + dec + 2.0 * M * D * V
+        weight_bytes = 4.0 * sum(int(v.size) for k, v in lowering.transformer_params(cfg, 0).items() if not k.endswith(".pe"))
     elif args.workload == "c1":
         g = lowering.mlp_graph(lowering.mlp_params(16, 512, 10, seed=0), batch=32, name="c1_mlp")
         inputs = [torch.randn(32, 512, generator=torch.Generator().manual_seed(0)).cuda()]
@@ -460,8 +475,9 @@ def run_latency(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="c3", choices=["c3", "c1", "c2", "c5"],
-                    help="c3 = the decode benchmark (default); c1 / c2 = forward latency of the small configs; c5 = ResNet-50 forward (batch --m, default 256)")
+    ap.add_argument("--workload", default="c3", choices=["c3", "c1", "c2", "c4", "c5"],
+                    help="c3 = the decode benchmark (default); c1 / c2 = forward latency of the small configs; c4 = encoder-decoder forward "
+                         "(batch --m, default 64; 256 source + 256 target positions); c5 = ResNet-50 forward (batch --m, default 256)")
     ap.add_argument("--micro", default=None, choices=["linear", "layernorm", "add", "mha", "conv"], help="profile one op instead of the decode workload")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=3072)

@@ -66,7 +66,7 @@ struct Slice {
 };
 
 struct DensePlan : NodePlan {
-    Slice s[4];  // meaning depends on the op (see the plan builders)
+    Slice s[6];  // meaning depends on the op (see the plan builders)
     int n = 0;
     // dims the kernels need again
     int64_t M = 0, heads_local = 0, head0 = 0, n_local = 0, col_off = 0;
@@ -366,6 +366,137 @@ std::unique_ptr<NodePlan> plan_mha(const Registry& reg, const TensorIds& in, con
     g1.M = M; g1.N = 3 * Dl; g1.K = D;
     g2.M = M; g2.N = D; g2.K = Dl;
     pl->variant += gemm_variant_name(g1, env.gemm_mode, 148) + (tc_attn ? "+attn-tcgen05-tf32x3+" : "+flash-fp32+") + gemm_variant_name(g2, env.gemm_mode, 148);
+    return pl;
+}
+
+// ---- CrossMHA (no counterpart in the reference runtime) --------------------------------------------------
+// Attention whose queries come from one sequence and whose keys / values from another — the decoder's second
+// attention of an encoder-decoder Transformer (reference model: layers/attention.py:19-33 called as
+// cross_attn(norm2(x), encoder_output, encoder_output, src_mask), blocks/decoder_block.py:22).  The reference's QKV
+// packing needs three Linear siblings on ONE input (matchers.py:615-621), so its compile passes cannot lower this
+// call; this opcode is an extension with the same arithmetic as MHA:
+//     q = x·Wq^T + bq   [B,Tq,D];   k | v = memory·Wkv^T + bkv   [B,Tk,2D]  (K rows 0..D, V rows D..2D of Wkv)
+//     out = softmax(mask_fill(q·k^T / scale_divisor)) · v, heads re-interleaved, then ·Wo^T + bo.
+// inputs [x, memory, mask, Wq[D,D], bq[D], Wkv[2D,D], bkv[2D], Wo[D,D], bo[D]]; ints [H, head_dim, D, 2D]; floats [scale_divisor].
+// slices: s[0] = Wq rows of the local heads, s[1] = their bias, s[2] = Wkv rows of the local heads (K block, V block),
+//         s[3] = their bias, s[4] = Wo columns of the local heads, s[5] = bo
+int k_cross_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const NodePlan* plan, ExecCtx& ctx) {
+    FXF_CHECK(in.size() >= 9 && out.size() >= 1, "cross_mha: expects [x, memory, mask, q_weight, q_bias, kv_weight, kv_bias, out_weight, out_bias]");
+    FXF_CHECK(p.ints.size() >= 4 && p.floats.size() >= 1, "cross_mha: expects ints [H, head_dim, d_model, kv_dim] and floats [scale_divisor]");
+    const FxfTensor &x = reg[in[0]], &mem = reg[in[1]], &mask = reg[in[2]], &wq = reg[in[3]], &bq = reg[in[4]], &wkv = reg[in[5]], &bkv = reg[in[6]],
+                    &wo = reg[in[7]], &bo = reg[in[8]], &o = reg[out[0]];
+    FXF_CHECK(x.rank == 3 && mem.rank == 3, "cross_mha: x must be [B,Tq,D] and memory [B,Tk,D]");
+    const int64_t B = x.shape[0], Tq = x.shape[1], Tk = mem.shape[1], H = p.ints[0], hd = p.ints[1], D = p.ints[2], KV = p.ints[3];
+    const int64_t Mq = B * Tq, Mk = B * Tk;
+    FXF_CHECK(H > 0 && hd > 0 && H * hd == D && KV == 2 * D, "cross_mha: inconsistent head parameters");
+    FXF_CHECK(x.shape[2] == D && mem.shape[2] == D && mem.shape[0] == B, "cross_mha: x / memory shapes do not match d_model or each other");
+    FXF_CHECK(wq.rank == 2 && wq.shape[0] == D && wq.shape[1] == D && numel(bq) == D, "cross_mha: query projection shape mismatch");
+    FXF_CHECK(wkv.rank == 2 && wkv.shape[0] == KV && wkv.shape[1] == D && numel(bkv) == KV, "cross_mha: packed KV weight/bias shape mismatch");
+    FXF_CHECK(wo.rank == 2 && wo.shape[0] == D && wo.shape[1] == D && numel(bo) == D, "cross_mha: output projection shape mismatch");
+    FXF_CHECK(numel(o) == Mq * D, "cross_mha: output size mismatch");
+    FXF_CHECK(x.dtype == FXF_F32 && mem.dtype == FXF_F32 && o.dtype == FXF_F32, "cross_mha: only float32 activations are supported");
+    FXF_CHECK(mask.dtype == FXF_BOOL && mask.rank <= 4, "cross_mha: mask must be a bool tensor of rank <= 4");
+    int64_t want[4] = {B, H, Tq, Tk}, ms[4] = {0, 0, 0, 0};
+    for (int k = 0; k < mask.rank; k++) {
+        int tgt = 4 - mask.rank + k;
+        FXF_CHECK(mask.shape[k] == want[tgt] || mask.shape[k] == 1, "cross_mha: mask shape is not broadcastable to [B,H,Tq,Tk]");
+        ms[tgt] = mask.shape[k] == 1 ? 0 : mask.stride[k];
+    }
+    const DensePlan* pl = dense(plan);
+    FXF_CHECK(pl != nullptr && pl->n == 6 && pl->prepared, "cross_mha: the node was not prepared");
+    const int64_t Hl = pl->heads_local, Dl = Hl * hd;
+    size_t need = (size_t(Mq) * size_t(2 * Dl) + size_t(Mk) * size_t(2 * Dl)) * sizeof(float);
+    FXF_CHECK(ctx.scratch_bytes >= need && (need == 0 || ctx.scratch != nullptr), "cross_mha: scratch too small (%zu < %zu bytes)", ctx.scratch_bytes, need);
+    float* q = static_cast<float*>(ctx.scratch);   // [Mq, Dl]
+    float* kv = q + Mq * Dl;                        // [Mk, 2*Dl]
+    float* cx = kv + Mk * 2 * Dl;                   // [Mq, Dl]
+    float* vt = cx + Mq * Dl;                       // only present when the plan reserved it
+    const bool have_vt = ctx.scratch_bytes >= need + attention_tc_scratch_bytes(B, Tk, Hl);
+
+    GemmArgs g;
+    fill_gemm(g, static_cast<const float*>(x.ptr), pl->s[0], &pl->s[1], q, Mq, D, Dl, false);
+    if (launch_gemm(g, ctx)) return 1;
+    GemmArgs gk;
+    fill_gemm(gk, static_cast<const float*>(mem.ptr), pl->s[2], &pl->s[3], kv, Mk, D, 2 * Dl, false);
+    if (launch_gemm(gk, ctx)) return 1;
+
+    if (Tk == 0) {  // softmax over no keys: the context is an empty sum
+        if (Mq * Dl > 0) FXF_CUDA(cudaMemsetAsync(cx, 0, size_t(Mq) * size_t(Dl) * sizeof(float), ctx.stream));
+    } else {
+        AttnArgs a;
+        a.qkv = q; a.ld_qkv = Dl; a.q_off = 0;
+        a.kv = kv; a.ld_kv = 2 * Dl; a.k_off = 0; a.v_off = Dl; a.Tk = int(Tk);
+        a.ctx = cx; a.ld_ctx = Dl;
+        a.mask = static_cast<const uint8_t*>(mask.ptr) + pl->head0 * ms[1];
+        a.B = int(B); a.T = int(Tq); a.H = int(Hl); a.hd = int(hd);
+        a.mask_sb = ms[0]; a.mask_sh = ms[1]; a.mask_sq = ms[2]; a.mask_sk = ms[3];
+        a.scale_divisor = p.floats[0];
+        if (have_vt && attention_tc_supported(a, ctx.gemm_mode)) {
+            if (launch_attention_tc(a, vt, ctx)) return 1;
+        } else {
+            if (launch_attention(a, ctx)) return 1;
+        }
+    }
+
+    GemmArgs g2;
+    fill_gemm(g2, cx, pl->s[4], &pl->s[5], static_cast<float*>(o.ptr), Mq, Dl, D, false);
+    if (launch_gemm(g2, ctx)) return 1;
+    return tp_all_reduce_sum(static_cast<float*>(o.ptr), Mq * D, ctx);
+}
+
+std::unique_ptr<NodePlan> plan_cross_mha(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& env) {
+    auto pl = std::make_unique<DensePlan>();
+    if (in.size() < 9 || out.size() < 1 || p.ints.size() < 4 || reg[in[0]].rank != 3 || reg[in[1]].rank != 3) return pl;
+    const FxfTensor &x = reg[in[0]], &mem = reg[in[1]];
+    const int64_t B = x.shape[0], Tq = x.shape[1], Tk = mem.shape[1], H = p.ints[0], hd = p.ints[1], D = p.ints[2], KV = p.ints[3];
+    const int64_t Mq = B * Tq, Mk = B * Tk;
+    if (H <= 0 || hd <= 0) return pl;
+    const int n = env.tp_size > 1 && H % env.tp_size == 0 ? env.tp_size : 1;
+    const int64_t Hl = H / n, h0 = (n > 1 ? env.tp_rank : 0) * Hl, Dl = Hl * hd;
+    pl->heads_local = Hl;
+    pl->head0 = h0;
+    Slice& s_wq = pl->add(3, D, D);
+    Slice& s_bq = pl->add(4, D, 1);
+    Slice& s_wkv = pl->add(5, KV, D);
+    Slice& s_bkv = pl->add(6, KV, 1);
+    Slice& s_wo = pl->add(7, D, D);
+    Slice& s_bo = pl->add(8, D, 1);
+    if (n > 1) {
+        for (Slice* s : {&s_wq, &s_bq}) {
+            s->row0[0] = h0 * hd; s->nrow[0] = Dl;
+            s->whole = false;
+        }
+        for (Slice* s : {&s_wkv, &s_bkv}) {
+            s->n_ranges = 2;
+            for (int half = 0; half < 2; half++) {
+                s->row0[half] = half * D + h0 * hd;
+                s->nrow[half] = Dl;
+            }
+            s->whole = false;
+        }
+        s_wo.col0 = h0 * hd; s_wo.ncol = Dl; s_wo.whole = false;
+        s_bo.drop = env.tp_rank != 0;
+    } else if (env.tp_size > 1) {
+        pl->variant = "replicated ";
+    }
+    pl->reserve(s_wq, want_tc(env, Mq, Dl, D));
+    pl->reserve(s_bq, false);
+    pl->reserve(s_wkv, want_tc(env, Mk, 2 * Dl, D));
+    pl->reserve(s_bkv, false);
+    pl->reserve(s_wo, want_tc(env, Mq, D, Dl));
+    pl->reserve(s_bo, false);
+    pl->M = Mq;
+    pl->scratch_bytes = (size_t(Mq) * size_t(2 * Dl) + size_t(Mk) * size_t(2 * Dl)) * sizeof(float);
+    const bool tc_attn = env.gemm_mode != FXF_GEMM_FP32_SIMT && hd == 64 && Tk % 4 == 0 && Tk >= 16 && Dl % 4 == 0;
+    if (tc_attn) pl->scratch_bytes += attention_tc_scratch_bytes(B, Tk, Hl);
+    pl->flops = 2.0 * double(Mq) * Dl * D + 2.0 * double(Mk) * 2 * Dl * D + 4.0 * double(B) * Hl * double(Tq) * Tk * hd + 2.0 * double(Mq) * D * Dl;
+    pl->bytes = 4.0 * (2.0 * double(Mq) * D + double(Mk) * D + 2.0 * double(Dl) * D + 2.0 * double(Dl) * D + 3 * Dl + D) + double(reg[in[2]].nbytes);
+    GemmArgs g1, g2, g3;
+    g1.M = Mq; g1.N = Dl; g1.K = D;
+    g2.M = Mk; g2.N = 2 * Dl; g2.K = D;
+    g3.M = Mq; g3.N = D; g3.K = Dl;
+    pl->variant += gemm_variant_name(g1, env.gemm_mode, 148) + "+" + gemm_variant_name(g2, env.gemm_mode, 148) +
+                   (tc_attn ? "+attn-tcgen05-tf32x3+" : "+flash-fp32+") + gemm_variant_name(g3, env.gemm_mode, 148);
     return pl;
 }
 

@@ -308,6 +308,110 @@ def gpt_graph(cfg: GPTConfig, params: Dict[str, np.ndarray], batch: int, seq: in
     return b.finish()
 
 
+# --------------------------------------------------------------------------------------
+# Encoder-decoder Transformer (reference model: models/transformer.py:7-18, models/encoder.py, models/decoder.py,
+# blocks/encoder_block.py, blocks/decoder_block.py).  The reference's compile passes cannot lower it: the decoder's
+# second attention takes its queries from one tensor and its keys/values from another, the QKV packing wants three
+# Linear siblings on one input (passes/fusion/matchers.py:615-621) and the unfused matmul / softmax nodes are not
+# serializable (serializer.py:157,169).  This builder lowers everything the way the reference lowers a GPT stack and
+# expresses that attention with the CrossMHA opcode (an extension of this library: Wq alone, Wk and Wv packed).
+# --------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class TransformerConfig:
+    d_model: int
+    heads: int
+    vocab: int
+    expansion: int
+    enc_layers: int
+    dec_layers: int
+    pe_len: int = 5000
+
+    @property
+    def d_ff(self) -> int:
+        return self.d_model * self.expansion
+
+
+TRANSFORMER_C4 = TransformerConfig(512, 8, 32000, 4, 6, 6)   # 6 + 6 layers, d_model 512, 8 heads, d_ff 2048
+
+
+def transformer_params(cfg: TransformerConfig, seed: int = 0, std: float = 0.02) -> Dict[str, np.ndarray]:
+    """Weights ~ N(0, std), biases 0, LayerNorm gamma 1 / beta 0.  Self-attention projections are packed as
+    cat([Wq, Wk, Wv], 0); the decoder's cross-attention keeps Wq apart and packs cat([Wk, Wv], 0)."""
+    rng = np.random.default_rng(seed)
+    D, F, V = cfg.d_model, cfg.d_ff, cfg.vocab
+    p: Dict[str, np.ndarray] = {}
+    pe = sinusoidal_pe(cfg.pe_len, D)
+
+    def ln(key):
+        p[key + ".w"], p[key + ".b"] = np.ones(D, np.float32), np.zeros(D, np.float32)
+
+    def lin(key, n_out, n_in):
+        p[key + ".w"], p[key + ".b"] = _normal(rng, (n_out, n_in), std), np.zeros(n_out, np.float32)
+
+    for side, layers in (("enc", cfg.enc_layers), ("dec", cfg.dec_layers)):
+        p[f"{side}.emb"] = _normal(rng, (V, D), std)
+        p[f"{side}.pe"] = pe
+        for l in range(layers):
+            pre = f"{side}.l{l}."
+            ln(pre + "ln1"); lin(pre + "qkv", 3 * D, D); lin(pre + "wo", D, D)
+            if side == "dec":
+                ln(pre + "ln2"); lin(pre + "cq", D, D); lin(pre + "ckv", 2 * D, D); lin(pre + "co", D, D)
+            ln(pre + "lnf"); lin(pre + "ff1", F, D); lin(pre + "ff2", D, F)
+        ln(f"{side}.ln_out")
+    lin("head", V, D)
+    return p
+
+
+def transformer_graph(cfg: TransformerConfig, params: Dict[str, np.ndarray], batch: int, src_len: int, tgt_len: int,
+                      name: str = "transformer", alignment: int = 64, eps: float = 1e-5) -> GraphRec:
+    """Inputs in the order of Transformer.forward: src ids int64 [B,S], tgt ids int64 [B,T], src mask bool [B,1,1,S],
+    tgt mask bool [B,1,T,T]; output logits [B,T,vocab]."""
+    B, S, T, D, H = batch, src_len, tgt_len, cfg.d_model, cfg.heads
+    hd = D // H
+    b = GraphBuilder(name, alignment)
+    src = b.input((B, S), wire.DT_I64)
+    tgt = b.input((B, T), wire.DT_I64)
+    src_mask = b.input((B, 1, 1, S), wire.DT_BOOL)
+    tgt_mask = b.input((B, 1, T, T), wire.DT_BOOL)
+    ln_ints = [1, D]
+
+    def c(key):
+        return b.const(params[key])
+
+    def embed(ids, side, L):
+        emb = b.op("Embedding", [ids, c(f"{side}.emb")], (B, L, D))
+        mul = b.op("Mul", [emb], (B, L, D), ints=[1], floats=[math.sqrt(D)])
+        size = b.op("Size", [mul], (), wire.DT_I64, ints=[1])
+        nar = b.op("Narrow", [c(f"{side}.pe"), size], (1, L, D), ints=[1, 0, -1])
+        return b.alias(b.op("Add", [mul, nar], (B, L, D)))  # positional-encoding dropout (eval mode)
+
+    def stack(h, side, layers, L, self_mask, memory=None):
+        for l in range(layers):
+            pre = f"{side}.l{l}."
+            n1 = b.op("LayerNorm", [h, c(pre + "ln1.w"), c(pre + "ln1.b")], (B, L, D), ints=ln_ints, floats=[eps])
+            att = b.op("MHA", [n1, self_mask, c(pre + "qkv.w"), c(pre + "qkv.b"), c(pre + "wo.w"), c(pre + "wo.b")], (B, L, D),
+                       ints=[H, hd, D, 3 * D], floats=[math.sqrt(hd)])
+            h = b.op("Add", [h, b.alias(att)], (B, L, D))
+            if memory is not None:
+                n2 = b.op("LayerNorm", [h, c(pre + "ln2.w"), c(pre + "ln2.b")], (B, L, D), ints=ln_ints, floats=[eps])
+                cross = b.op("CrossMHA", [n2, memory, src_mask, c(pre + "cq.w"), c(pre + "cq.b"), c(pre + "ckv.w"), c(pre + "ckv.b"),
+                                          c(pre + "co.w"), c(pre + "co.b")], (B, L, D), ints=[H, hd, D, 2 * D], floats=[math.sqrt(hd)])
+                h = b.op("Add", [h, b.alias(cross)], (B, L, D))
+            nf = b.op("LayerNorm", [h, c(pre + "lnf.w"), c(pre + "lnf.b")], (B, L, D), ints=ln_ints, floats=[eps])
+            ff = b.op("FeedForward", [nf, c(pre + "ff1.w"), c(pre + "ff1.b"), c(pre + "ff2.w"), c(pre + "ff2.b")], (B, L, D))
+            if l < layers - 1:
+                h = b.op("Add", [h, b.alias(ff)], (B, L, D))
+            else:  # the last residual add fuses with the stack's output LayerNorm
+                h = b.op("AddLayerNorm", [h, b.alias(ff), c(f"{side}.ln_out.w"), c(f"{side}.ln_out.b")], (B, L, D), ints=ln_ints, floats=[eps])
+        return h
+
+    memory = stack(embed(src, "enc", S), "enc", cfg.enc_layers, S, src_mask)
+    dec = stack(embed(tgt, "dec", T), "dec", cfg.dec_layers, T, tgt_mask, memory)
+    logits = b.op("Linear", [dec, c("head.w"), c("head.b")], (B, T, cfg.vocab))
+    b.output(logits)
+    return b.finish()
+
+
 def decode_prompt(batch: int, prompt_len: int, vocab: int, seed: int = 0) -> np.ndarray:
     """Prompt ids uniform in [1, vocab): id 0 is the pad id that the decode mask blocks
     (reference py/tests/test_ops.py:423, layers/masks.py:52-55)."""

@@ -30,14 +30,17 @@ extern "C" {
 /* DType values of the graph file (schema/graph.fbs:11-17). */
 enum { FXF_F32 = 0, FXF_F16 = 1, FXF_I32 = 2, FXF_I64 = 3, FXF_BOOL = 4 };
 
-/* OpCode values of the graph file (schema/graph.fbs:19-40). */
+/* OpCode values of the graph file (schema/graph.fbs:19-40).  Values above 19 do not exist in the reference schema:
+ * FXF_OP_CROSS_MHA is attention with queries from one sequence and keys/values from another (the decoder's second
+ * attention of an encoder-decoder model), which the reference's QKV packing cannot lower.
+ * inputs [x, memory, mask, Wq[D,D], bq[D], Wkv[2D,D], bkv[2D], Wo[D,D], bo[D]], ints [H, head_dim, D, 2D], floats [scale_divisor]. */
 enum {
     FXF_OP_NOOP = 0, FXF_OP_CONV2D = 1, FXF_OP_CONV2D_RELU = 2, FXF_OP_LINEAR = 3,
     FXF_OP_LINEAR_RELU = 4, FXF_OP_ADD = 5, FXF_OP_ADD_RELU = 6, FXF_OP_RELU = 7,
     FXF_OP_MUL = 8, FXF_OP_MAX_POOL2D = 9, FXF_OP_AVG_POOL2D = 10,
     FXF_OP_ADAPTIVE_AVG_POOL2D = 11, FXF_OP_TRANSPOSE = 12, FXF_OP_SIZE = 13,
     FXF_OP_NARROW = 14, FXF_OP_EMBEDDING = 15, FXF_OP_LAYER_NORM = 16,
-    FXF_OP_ADD_LAYER_NORM = 17, FXF_OP_MHA = 18, FXF_OP_FEEDFORWARD = 19, FXF_OP_COUNT = 20
+    FXF_OP_ADD_LAYER_NORM = 17, FXF_OP_MHA = 18, FXF_OP_FEEDFORWARD = 19, FXF_OP_CROSS_MHA = 20, FXF_OP_COUNT = 21
 };
 
 /* One registry slot.  Replaces the torch::Tensor elements of the reference TensorRegistry

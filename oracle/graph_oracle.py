@@ -91,6 +91,25 @@ def _mha(reg, i, o, ints, floats):
     reg[o[0]].copy_(F.linear(ctx, wo, bo))
 
 
+def _cross_mha(reg, i, o, ints, floats):
+    """Attention with queries from x and keys/values from `memory`: the arithmetic of the reference's eager
+    MultiHeadAttention.forward(q, k, v, mask) (py/fxfusion/models/transformer/layers/attention.py:19-33) called as the decoder
+    block calls it (blocks/decoder_block.py:22), with Wk and Wv packed into one weight."""
+    x, mem, mask, wq, bq, wkv, bkv, wo, bo = (reg[k] for k in i[:9])
+    H, hd, D, KV = ints[:4]
+    scale = float(np.float32(floats[0]))
+    B, Tq, Tk = x.size(0), x.size(1), mem.size(1)
+    q = F.linear(x, wq, bq).view(B, Tq, H, hd).transpose(1, 2)
+    kv = F.linear(mem, wkv, bkv)
+    k = kv[:, :, 0:D].view(B, Tk, H, hd).transpose(1, 2)
+    v = kv[:, :, D:KV].view(B, Tk, H, hd).transpose(1, 2)
+    scores = torch.matmul(q, k.transpose(-2, -1)) / scale
+    scores = scores.masked_fill(mask == 0, -math.inf)
+    attn = torch.softmax(scores, -1)
+    ctx = torch.matmul(attn, v).transpose(1, 2).contiguous().view(B, Tq, D)
+    reg[o[0]].copy_(F.linear(ctx, wo, bo))
+
+
 KERNELS: Dict[int, KernelFn] = {
     wire.OP["Conv2d"]: lambda r, i, o, a, f: _conv(r, i, o, a, f, False),
     wire.OP["Conv2dRelu"]: lambda r, i, o, a, f: _conv(r, i, o, a, f, True),
@@ -112,6 +131,7 @@ KERNELS: Dict[int, KernelFn] = {
     wire.OP["LayerNorm"]: _layer_norm,
     wire.OP["AddLayerNorm"]: _add_layer_norm,
     wire.OP["MHA"]: _mha,
+    wire.OP["CrossMHA"]: _cross_mha,
     wire.OP["FeedForward"]: lambda r, i, o, a, f: r[o[0]].copy_(
         F.linear(torch.relu(F.linear(r[i[0]], r[i[1]], r[i[2]])), r[i[3]], r[i[4]])),
 }

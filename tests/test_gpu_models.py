@@ -196,3 +196,24 @@ def test_c5_resnet50_matches_oracle_on_reduced_batch(built_lib, tmp_path, precis
     assert eng.num_nodes == 72 and eng.arena_bytes == 27295744
     assert torch.equal(got.argmax(-1), want.argmax(-1))
     eng.close()
+
+
+@pytest.mark.parametrize("precision", ["auto", "fp32_simt"])
+def test_c4_encoder_decoder_matches_oracle_on_reduced_batch(built_lib, tmp_path, precision):
+    """Encoder-decoder Transformer of configuration 4 (6 + 6 layers, d_model 512, 8 heads, vocab 32000) at batch 2 and
+    64 source / 48 target positions: 117 launching nodes, 6 of them the CrossMHA extension, against the CPU oracle (which
+    the committed encdec_* fixtures pin to the reference's eager model)."""
+    cfg = lowering.TRANSFORMER_C4
+    g = lowering.transformer_graph(cfg, lowering.transformer_params(cfg, 0), batch=2, src_len=64, tgt_len=48, name="c4_b2")
+    gen = torch.Generator().manual_seed(0)
+    src, tgt = torch.randint(1, cfg.vocab, (2, 64), generator=gen), torch.randint(1, cfg.vocab, (2, 48), generator=gen)
+    src_mask = torch.ones(2, 1, 1, 64, dtype=torch.bool)
+    src_mask[1, 0, 0, 50:] = False
+    tgt_mask = torch.tril(torch.ones(48, 48, dtype=torch.bool)).view(1, 1, 48, 48).expand(2, 1, 48, 48).contiguous()
+    eng = _engine(g, tmp_path, precision=precision)
+    got = eng.run([src.cuda(), tgt.cuda(), src_mask.cuda(), tgt_mask.cuda()])[0].cpu()
+    want = GraphOracle(g).run([src, tgt, src_mask, tgt_mask])[0]
+    ok, info = compare_outputs(got, want, atol=ATOL, rtol=RTOL)
+    assert ok, info
+    assert eng.device_status() == 0
+    assert "CrossMHA" in eng.describe()

@@ -90,6 +90,40 @@ def test_mha_mask_broadcast_shapes(built_lib, shape, hd):
     both("MHA", _mha_reg(B, T, H, hd, mask), [0, 1, 2, 3, 4, 5], [6], ints=[H, hd, H * hd, 3 * H * hd], floats=[math.sqrt(hd)])
 
 
+@pytest.mark.parametrize("precision", ["auto", "fp32_simt"])
+@pytest.mark.parametrize("B,Tq,Tk,H,hd,mask_kind", [(2, 6, 9, 4, 8, "b11k"), (1, 40, 72, 2, 64, "b11k"), (2, 130, 64, 3, 64, "bqk"), (2, 24, 256, 2, 64, "causal-ish"),
+                                                   (1, 5, 33, 2, 20, "bqk"), (2, 128, 384, 2, 64, "b11k"), (1, 7, 16, 1, 64, "11qk")])
+def test_cross_mha(built_lib, B, Tq, Tk, H, hd, mask_kind, precision):
+    """Attention with queries from one sequence and keys/values from another (extension opcode CrossMHA): head_dim 64
+    with Tk % 4 == 0 takes the tcgen05 kernel in "auto" mode.  Oracle = the reference's eager MultiHeadAttention math."""
+    D = H * hd
+    g = torch.Generator().manual_seed(3)
+    if mask_kind == "b11k":
+        mask = torch.ones(B, 1, 1, Tk, dtype=torch.bool)
+        mask[-1, 0, 0, Tk - Tk // 3:] = False
+    elif mask_kind == "bqk":
+        mask = torch.rand(B, 1, Tq, Tk, generator=g) < 0.6
+        mask[..., 0] = True
+    elif mask_kind == "11qk":
+        mask = torch.rand(1, 1, Tq, Tk, generator=g) < 0.5
+        mask[..., 1] = True
+    else:  # a band: query q sees keys <= 10 q  (whole key blocks are masked for the early queries)
+        mask = (torch.arange(Tk).view(1, 1, 1, Tk) <= 10 * torch.arange(Tq).view(1, 1, Tq, 1)).expand(B, 1, Tq, Tk).contiguous()
+    reg = [rnd(B, Tq, D), rnd(B, Tk, D, seed=9), mask, rnd(D, D, seed=1, scale=1 / math.sqrt(D)), rnd(D, seed=2, scale=0.1),
+           rnd(2 * D, D, seed=3, scale=1 / math.sqrt(D)), rnd(2 * D, seed=4, scale=0.1), rnd(D, D, seed=5, scale=1 / math.sqrt(D)), rnd(D, seed=6, scale=0.1),
+           torch.zeros(B, Tq, D)]
+    both("CrossMHA", reg, [0, 1, 2, 3, 4, 5, 6, 7, 8], [9], ints=[H, hd, D, 2 * D], floats=[math.sqrt(hd)], precision=precision)
+
+
+def test_cross_mha_rejects_inconsistent_operands(built_lib):
+    from fxfusion_b200.kernels import invoke
+    D = 32
+    reg = [rnd(2, 4, D).cuda(), rnd(3, 5, D).cuda(), torch.ones(2, 1, 1, 5, dtype=torch.bool).cuda(), rnd(D, D).cuda(), rnd(D).cuda(),
+           rnd(2 * D, D).cuda(), rnd(2 * D).cuda(), rnd(D, D).cuda(), rnd(D).cuda(), torch.zeros(2, 4, D).cuda()]
+    with pytest.raises(RuntimeError, match="cross_mha"):   # memory batch differs from x batch
+        invoke("CrossMHA", reg, [0, 1, 2, 3, 4, 5, 6, 7, 8], [9], ints=[4, 8, D, 2 * D], floats=[math.sqrt(8)])
+
+
 def test_mha_fully_masked_rows_and_nan_values(built_lib):
     """A fully masked query row is NaN; a NaN in the input poisons exactly what torch's matmul poisons."""
     _masked_rows_and_nan(2, 12, 2, 8)

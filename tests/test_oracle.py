@@ -56,7 +56,8 @@ def test_restatement_is_bit_identical_to_reference_kernels(name):
 
     _, ins, _ = _case(name)
     a = GraphOracle(str(GOLDEN / f"{name}.bin")).run(ins)
-    b = GraphOracle(str(GOLDEN / f"{name}.bin"), kernels={op: bind(op) for op in KERNELS}).run(ins)
+    # opcodes above 19 are this library's extensions: the reference has no kernel for them, the restatement stays
+    b = GraphOracle(str(GOLDEN / f"{name}.bin"), kernels={op: (bind(op) if op <= 19 else KERNELS[op]) for op in KERNELS}).run(ins)
     for x, y in zip(a, b):
         assert torch.equal(torch.isnan(x), torch.isnan(y))
         assert torch.equal(torch.nan_to_num(x), torch.nan_to_num(y))
