@@ -82,6 +82,20 @@ def shard_mha(wqkv: np.ndarray, bqkv: np.ndarray, wo: np.ndarray, bo: np.ndarray
             "bo": bo if (rank == 0 or not sharded) else np.zeros_like(bo), "heads": h1 - h0, "head0": h0, "sharded": sharded}
 
 
+def shard_cross_mha(wq: np.ndarray, bq: np.ndarray, wkv: np.ndarray, bkv: np.ndarray, wo: np.ndarray, bo: np.ndarray,
+                    num_heads: int, rank: int, size: int) -> Dict[str, np.ndarray]:
+    """Local operands of a head-sharded CrossMHA: rows of Wq, of the K half and of the V half of the packed Wkv for the
+    local heads, the matching columns of the output projection, the output bias on rank 0 only."""
+    D = wo.shape[0]
+    hd = D // num_heads
+    h0, h1 = head_range(num_heads, rank, size)
+    q_rows = np.arange(h0 * hd, h1 * hd)
+    kv_rows = np.concatenate([np.arange(t * D + h0 * hd, t * D + h1 * hd) for t in range(2)])
+    sharded = (h1 - h0) != num_heads
+    return {"wq": wq[q_rows], "bq": bq[q_rows], "wkv": wkv[kv_rows], "bkv": bkv[kv_rows], "wo": wo[:, h0 * hd:h1 * hd],
+            "bo": bo if (rank == 0 or not sharded) else np.zeros_like(bo), "heads": h1 - h0, "head0": h0, "sharded": sharded}
+
+
 def shard_feedforward(w1: np.ndarray, b1: np.ndarray, w2: np.ndarray, b2: np.ndarray, rank: int, size: int) -> Dict[str, np.ndarray]:
     f0, f1 = hidden_range(w1.shape[0], rank, size)
     sharded = (f1 - f0) != w1.shape[0]

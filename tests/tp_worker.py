@@ -42,6 +42,25 @@ def cpu_checks(rank, size):
     want = torch.zeros(B, T, D)
     KERNELS[wire.OP["MHA"]]([x, mask, wqkv, bqkv, wo, bo, want], [0, 1, 2, 3, 4, 5], [6], [H, hd, D, 3 * D], [math.sqrt(hd)])
     assert torch.allclose(part, want, atol=1e-5, rtol=1e-5), (part - want).abs().max()
+    # --- CrossMHA: queries from x, keys/values from a longer memory, local heads only ---
+    Tk = 17
+    mem = torch.randn(B, Tk, D, generator=g)
+    cmask = torch.ones(B, 1, 1, Tk, dtype=torch.bool)
+    cmask[1, 0, 0, 11:] = False
+    wq, bq = torch.randn(D, D, generator=g) / math.sqrt(D), torch.randn(D, generator=g) * 0.1
+    wkv, bkv = torch.randn(2 * D, D, generator=g) / math.sqrt(D), torch.randn(2 * D, generator=g) * 0.1
+    sc = tp.shard_cross_mha(wq.numpy(), bq.numpy(), wkv.numpy(), bkv.numpy(), wo.numpy(), bo.numpy(), H, rank, size)
+    Hl, Dl = sc["heads"], sc["heads"] * hd
+    q = F.linear(x, torch.from_numpy(sc["wq"]), torch.from_numpy(sc["bq"])).view(B, T, Hl, hd).transpose(1, 2)
+    kv = F.linear(mem, torch.from_numpy(sc["wkv"]), torch.from_numpy(sc["bkv"]))
+    k, v = (kv[:, :, i * Dl:(i + 1) * Dl].view(B, Tk, Hl, hd).transpose(1, 2) for i in range(2))
+    s = ((q @ k.transpose(-2, -1)) / math.sqrt(hd)).masked_fill(cmask == 0, -math.inf)
+    ctx = (torch.softmax(s, -1) @ v).transpose(1, 2).contiguous().view(B, T, Dl)
+    part = F.linear(ctx, torch.from_numpy(np.ascontiguousarray(sc["wo"])), torch.from_numpy(sc["bo"]))
+    dist.all_reduce(part)
+    want = torch.zeros(B, T, D)
+    KERNELS[wire.OP["CrossMHA"]]([x, mem, cmask, wq, bq, wkv, bkv, wo, bo, want], [0, 1, 2, 3, 4, 5, 6, 7, 8], [9], [H, hd, D, 2 * D], [math.sqrt(hd)])
+    assert torch.allclose(part, want, atol=1e-5, rtol=1e-5), (part - want).abs().max()
     # --- FeedForward: column-parallel then row-parallel ---
     w1, b1 = torch.randn(Fh, D, generator=g) / math.sqrt(D), torch.randn(Fh, generator=g) * 0.1
     w2, b2 = torch.randn(D, Fh, generator=g) / math.sqrt(Fh), torch.randn(D, generator=g) * 0.1
@@ -92,6 +111,23 @@ def gpu_checks(rank, size, tmp):
         assert err < 1e-4, f"rank {rank} {precision}: TP forward differs from the oracle by {err}"
         assert eng.device_status() == 0
         eng.close()
+    # encoder-decoder graph: CrossMHA nodes are head-sharded like MHA
+    ecfg = lowering.TransformerConfig(256, 4, 500, 2, 1, 2, pe_len=64)
+    eg = lowering.transformer_graph(ecfg, lowering.transformer_params(ecfg, 1), batch=2, src_len=48, tgt_len=32, name="tp_encdec")
+    epath = os.path.join(tmp, f"tp_encdec_{rank}.bin")
+    wire.dump(eg, epath)
+    gen = torch.Generator().manual_seed(3)
+    esrc, etgt = torch.randint(1, 500, (2, 48), generator=gen), torch.randint(1, 500, (2, 32), generator=gen)
+    esm = torch.ones(2, 1, 1, 48, dtype=torch.bool)
+    esm[1, 0, 0, 40:] = False
+    etm = torch.tril(torch.ones(32, 32, dtype=torch.bool)).view(1, 1, 32, 32).expand(2, 1, 32, 32).contiguous()
+    ewant = GraphOracle(eg).run([esrc, etgt, esm, etm])[0]
+    eng = ExecutionEngine(epath, f"cuda:{rank}", comm=comm)
+    egot = eng.run([esrc.cuda(), etgt.cuda(), esm.cuda(), etm.cuda()])[0].cpu()
+    err = (egot - ewant).abs().max().item()
+    assert err < 1e-4, f"rank {rank}: TP encoder-decoder forward differs from the oracle by {err}"
+    assert eng.device_status() == 0
+    eng.close()
     # greedy decode with the vocabulary sharded as well: tokens must equal the oracle's on every rank
     eng = ExecutionEngine(path, f"cuda:{rank}", comm=comm, shard_output=True)
     dev = buf.cuda()
