@@ -17,6 +17,7 @@
 // keeps every pointer inside a captured CUDA Graph stable and also makes an Alias/Output of an
 // Input see the data of the current run.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <fstream>
 #include <sstream>
@@ -92,6 +93,10 @@ struct fxf_engine {
     bool head_sharded = false;         // the final Linear writes only this rank's column block of the logits
     int64_t head_col0 = 0, head_ncols = 0;
     size_t cand_off = 0, cand_bytes = 0;  // argmax candidates: [local | all ranks]
+    // peer-memory all-reduce: flags + epoch inside this allocation (same offset on every rank), peers' allocations mapped
+    size_t p2p_off = 0;
+    PeerMap peers;
+    bool peers_mapped = false;
     // decode that evaluates the final Linear only at the position whose logits are read
     int tail_node = -1;                // index of that Linear (the last node), -1 when the graph does not end in one
     size_t lastrow_off = 0, lastrow_bytes = 0;  // its [B,V] output
@@ -104,6 +109,7 @@ struct fxf_engine {
         if (body_exec) cudaGraphExecDestroy(body_exec);
         if (body_graph) cudaGraphDestroy(body_graph);
         if (capture_stream) cudaStreamDestroy(capture_stream);
+        if (peers_mapped) tp_unmap_peers(comm, &peers);   // collective: every rank destroys its engine
         if (base) cudaFree(base);
     }
 };
@@ -316,6 +322,12 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
         e->scratch_bytes = std::max(e->scratch_bytes, n.plan->scratch_bytes);
         e->persist_bytes += round_up(n.plan->persist_bytes, kAlign);
     }
+    constexpr size_t kP2pRegion = 8192;  // [0, 4096): flags [rank][block]; [4096, ..): epoch, block counter
+    if (e->comm != nullptr && e->opts.tp_size > 1) {
+        // placed before everything whose size may differ between ranks, so that its offset is the same everywhere
+        e->p2p_off = cursor;
+        cursor += kP2pRegion;
+    }
     size_t persist_off = cursor;
     cursor += e->persist_bytes;
     e->scratch_off = cursor;
@@ -378,6 +390,28 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
     e->ctx.scratch = e->base + e->scratch_off;
     e->ctx.scratch_bytes = e->scratch_bytes;
     e->ctx.status = reinterpret_cast<int*>(e->base + e->status_off);
+    if (e->p2p_off) {
+        FXF_CUDA(cudaMemset(e->base + e->p2p_off, 0, kP2pRegion));
+        FXF_CUDA(cudaDeviceSynchronize());
+        // FXF_TP_ALLREDUCE=nccl keeps NCCL for the two all-reduces of a layer (debugging / comparison)
+        const char* mode = std::getenv("FXF_TP_ALLREDUCE");
+        if (!(mode && mode[0] == 'n')) {
+            if (tp_map_peers(e->comm, e->base, &e->peers) == 0) {
+                e->peers.shared_bytes = e->arena_bytes;
+                e->peers.flags_off = e->p2p_off;
+                e->peers.epoch_off = e->p2p_off + 4096;
+                e->peers.grid = 128;  // 8 ranks x 128 blocks x 4 bytes = 4 KB of flags
+                if (const char* g = std::getenv("FXF_P2P_GRID")) {  // debug override, 1..128
+                    int v = std::atoi(g);
+                    if (v >= 1 && v <= 128) e->peers.grid = v;
+                }
+                e->peers_mapped = true;
+                e->ctx.peers = &e->peers;
+            } else {
+                set_last_error("");   // not an error: the all-reduce stays with NCCL
+            }
+        }
+    }
     if (e->gemm_ws_bytes) {
         e->ctx.gemm_ws = reinterpret_cast<float*>(e->base + e->gemm_ws_off);
         e->ctx.gemm_ws_bytes = e->gemm_ws_bytes;

@@ -38,6 +38,16 @@ struct LaunchRecord {
 };
 
 // Everything a launch needs besides the registry.
+// The engine allocations of all tensor-parallel ranks of a node as mapped into this process (CUDA IPC).
+constexpr int kMaxTpRanks = 8;
+struct PeerMap {
+    char* base[kMaxTpRanks] = {};   // base[r]: rank r's allocation (own rank: the local pointer)
+    size_t shared_bytes = 0;        // offsets below this mean the same tensor on every rank (the planner's arena)
+    size_t flags_off = 0;           // barrier flags [peer][block] of the peer all-reduce, same offset on every rank
+    size_t epoch_off = 0;           // two ints: epoch, finished-block counter
+    int grid = 0;                   // blocks of the peer all-reduce kernel (fixes the flag layout)
+};
+
 struct ExecCtx {
     cudaStream_t stream = nullptr;
     void* scratch = nullptr;       // shared by all nodes of an engine; nodes run one at a time
@@ -48,6 +58,7 @@ struct ExecCtx {
     int launches = 0;              // incremented by every kernel launch (host-side count)
     int tp_rank = 0, tp_size = 1;  // tensor-parallel position; tp_size > 1 needs `comm`
     void* comm = nullptr;          // fxf_comm* (NCCL communicator wrapper), owned by the caller
+    const PeerMap* peers = nullptr;  // set when the ranks' allocations are mapped into each other: all-reduce over peer memory
     // workspace of the tensor-core GEMM's K-split last round: partial tiles and their ready flags (zero between
     // launches).  Without it every tile is computed whole.
     float* gemm_ws = nullptr;
@@ -258,6 +269,11 @@ struct AttnArgs {
 int launch_attention(const AttnArgs& a, ExecCtx& ctx);
 // Sum `n` floats in place over the tensor-parallel ranks (NCCL all-reduce on ctx.stream); no-op for tp_size 1.
 int tp_all_reduce_sum(float* buf, int64_t n, ExecCtx& ctx);
+// Peer-memory all-reduce (kernels/allreduce_p2p.cu) and the IPC exchange that sets it up (tp_comm.cpp).
+bool p2p_all_reduce_usable(const float* buf, int64_t n, const ExecCtx& ctx);
+int launch_p2p_all_reduce(float* buf, int64_t n, ExecCtx& ctx);
+int tp_map_peers(void* comm, void* base, PeerMap* out);     // collective: every rank passes its own allocation
+void tp_unmap_peers(void* comm, PeerMap* pm);               // collective as well
 // Gather `bytes` from every rank into recv[rank * bytes ...] (NCCL all-gather on ctx.stream).
 int tp_all_gather(const void* send, void* recv, int64_t bytes, ExecCtx& ctx);
 // tcgen05 path (head_dim 64): needs 6*B*T*H*64 floats of scratch for the split, per-head operand copies

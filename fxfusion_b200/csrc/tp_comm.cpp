@@ -8,6 +8,7 @@
 
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "runtime.hpp"
 
@@ -71,6 +72,7 @@ namespace fxf {
 
 int tp_all_reduce_sum(float* buf, int64_t n, ExecCtx& ctx) {
     if (ctx.tp_size <= 1 || n == 0) return 0;
+    if (p2p_all_reduce_usable(buf, n, ctx)) return launch_p2p_all_reduce(buf, n, ctx);
     auto* c = static_cast<fxf_comm*>(ctx.comm);
     FXF_CHECK(c != nullptr && c->nccl != nullptr, "tensor-parallel engine has no communicator");
     FXF_NCCL(api().AllReduce(buf, buf, size_t(n), kNcclFloat32, kNcclSum, c->nccl, ctx.stream));
@@ -79,6 +81,97 @@ int tp_all_reduce_sum(float* buf, int64_t n, ExecCtx& ctx) {
         if (trace_after_launch(ctx)) return 1;
     }
     return 0;
+}
+
+// Exchanges the CUDA IPC handles of the ranks' engine allocations (64 bytes each, gathered with NCCL through a small
+// device buffer) and maps every peer's allocation into this process.  Collective.  Returns non-zero, leaving `out`
+// unusable, when peer mapping is not possible (the caller then keeps NCCL for the all-reduce).
+int tp_map_peers(void* comm, void* base, PeerMap* out) {
+    auto* c = static_cast<fxf_comm*>(comm);
+    FXF_CHECK(c != nullptr && c->nccl != nullptr && c->size >= 2 && c->size <= kMaxTpRanks, "peer mapping needs a communicator of 2..%d ranks", kMaxTpRanks);
+    // slot layout: [ok flag (int) | 60 bytes padding | 64-byte handle] per rank, so that a failing rank is seen by all
+    constexpr size_t kSlot = 128;
+    char mine[kSlot] = {};
+    cudaIpcMemHandle_t h;
+    int ok = cudaIpcGetMemHandle(&h, base) == cudaSuccess ? 1 : 0;
+    if (!ok) cudaGetLastError();
+    std::memcpy(mine, &ok, sizeof(ok));
+    std::memcpy(mine + 64, &h, sizeof(h));
+    char* dev = nullptr;
+    FXF_CUDA(cudaMalloc(reinterpret_cast<void**>(&dev), kSlot * size_t(c->size + 1)));
+    std::vector<char> all(kSlot * size_t(c->size));
+    cudaStream_t s = nullptr;
+    FXF_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    int rc = 0;
+    do {
+        if (cudaMemcpyAsync(dev, mine, kSlot, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = 1; break; }
+        if (api().AllGather(dev, dev + kSlot, kSlot, kNcclInt8, c->nccl, s) != 0) { rc = 1; break; }
+        if (cudaMemcpyAsync(all.data(), dev + kSlot, all.size(), cudaMemcpyDeviceToHost, s) != cudaSuccess) { rc = 1; break; }
+        if (cudaStreamSynchronize(s) != cudaSuccess) { rc = 1; break; }
+    } while (false);
+    cudaStreamDestroy(s);
+    cudaFree(dev);
+    FXF_CHECK(rc == 0, "peer mapping: exchanging the IPC handles failed");
+    for (int r = 0; r < c->size; r++) {
+        int peer_ok = 0;
+        std::memcpy(&peer_ok, all.data() + kSlot * size_t(r), sizeof(peer_ok));
+        FXF_CHECK(peer_ok == 1, "peer mapping: rank %d could not export its allocation", r);
+    }
+    int opened = 1;
+    std::string why;
+    for (int r = 0; r < c->size && opened; r++) {
+        if (r == c->rank) {
+            out->base[r] = static_cast<char*>(base);
+            continue;
+        }
+        cudaIpcMemHandle_t ph;
+        std::memcpy(&ph, all.data() + kSlot * size_t(r) + 64, sizeof(ph));
+        void* p = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&p, ph, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            opened = 0;
+            why = std::string("cudaIpcOpenMemHandle for rank ") + std::to_string(r) + " failed: " + cudaGetErrorString(e);
+        } else {
+            out->base[r] = static_cast<char*>(p);
+        }
+    }
+    // every rank must take the same decision: count the ranks that mapped all their peers
+    float* agree = nullptr;
+    FXF_CUDA(cudaMalloc(reinterpret_cast<void**>(&agree), 256));
+    const float mine_ok = float(opened);
+    float total = 0.f;
+    int arc = 0;
+    if (cudaMemcpy(agree, &mine_ok, sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) arc = 1;
+    if (!arc && api().AllReduce(agree, agree, 1, kNcclFloat32, kNcclSum, c->nccl, nullptr) != 0) arc = 1;
+    if (!arc && cudaDeviceSynchronize() != cudaSuccess) arc = 1;
+    if (!arc && cudaMemcpy(&total, agree, sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) arc = 1;
+    cudaFree(agree);
+    if (arc || int(total + 0.5f) != c->size) {
+        for (int r = 0; r < c->size; r++)
+            if (r != c->rank && out->base[r]) cudaIpcCloseMemHandle(out->base[r]);
+        *out = PeerMap{};
+        FXF_FAIL("peer mapping is not available on every rank%s%s", why.empty() ? "" : ": ", why.c_str());
+    }
+    return 0;
+}
+
+// Unmaps the peers.  The tiny all-reduce afterwards keeps any rank from freeing its allocation while a peer still has
+// it mapped.
+void tp_unmap_peers(void* comm, PeerMap* pm) {
+    auto* c = static_cast<fxf_comm*>(comm);
+    if (c == nullptr || pm == nullptr) return;
+    cudaDeviceSynchronize();
+    for (int r = 0; r < c->size && r < kMaxTpRanks; r++)
+        if (r != c->rank && pm->base[r]) cudaIpcCloseMemHandle(pm->base[r]);
+    float* d = nullptr;
+    if (c->nccl && cudaMalloc(reinterpret_cast<void**>(&d), 256) == cudaSuccess) {
+        cudaMemset(d, 0, 256);
+        api().AllReduce(d, d, 1, kNcclFloat32, kNcclSum, c->nccl, nullptr);
+        cudaDeviceSynchronize();
+        cudaFree(d);
+    }
+    *pm = PeerMap{};
 }
 
 int tp_all_gather(const void* send, void* recv, int64_t bytes, ExecCtx& ctx) {
