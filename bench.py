@@ -335,7 +335,7 @@ def run_ours(args):
         tokens_per_step = B * dp_size
         line = {
             "metric": METRIC, "value": tokens_per_step * K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak" if tp_size == 1 else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak" if tp_size == 1 else "strong", "vs_baseline": None, "dtype": "bf16" if args.precision == "bf16" else "f32", "data": "synthetic",
             "config": {"workload": "GPT-2-small-shape greedy static decode, batch 32 per replica, 128 prompt + 128 generated, fp32, full recompute",
                        "layers": 12, "d_model": 768, "heads": 12, "d_ff": 3072, "vocab": 50257, "batch_per_gpu": B, "seq": T,
                        "parallelism": (f"{world} independent replica(s), no collective" if tp_size == 1 else
@@ -486,7 +486,8 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--precision", default="auto", choices=["auto", "fp32_simt", "fp32_3xtf32"])
+    ap.add_argument("--precision", default="auto", choices=["auto", "fp32_simt", "fp32_3xtf32", "bf16"],
+                    help="bf16 = optional reduced-precision mode (bf16 tensor-core products, fp32 accumulation); not the headline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the opt-in last-row-projection decode measurement (keeps profiler captures short)")
     ap.add_argument("--parallel", default="replicas", choices=["replicas", "tp"],

@@ -216,6 +216,7 @@ __global__ void __launch_bounds__(256) global_avg_pool_kernel(const float* __res
 // ---- host side ----------------------------------------------------------------------------------------
 struct ConvPlan : NodePlan {
     bool gemm_1x1 = false;          // planned for the tensor-core GEMM (still needs channels-last tensors at run time)
+    bool bf16 = false;              // bf16 mode: one bf16 copy of the weights instead of the TF32 hi/lo pair
     bool igemm_tc = false;          // k x k or strided 1x1, stride <= 2: planned for the tensor-core implicit GEMM (same run-time condition)
     int64_t w_elems = 0;
     const float *w_hi = nullptr, *w_lo = nullptr;
@@ -224,6 +225,14 @@ struct ConvPlan : NodePlan {
         FXF_CHECK(persist != nullptr, "conv plan: persistent memory was not assigned");
         float* h = static_cast<float*>(persist);
         const FxfTensor& w = reg[in[1]];
+        if (bf16) {
+            if (igemm_tc) {
+                if (launch_conv_weight_bf16(static_cast<const float*>(w.ptr), h, int(w.shape[0]), int(w.shape[1]), int(w.shape[2]), int(w.shape[3]), ctx)) return 1;
+            } else if (launch_convert_bf16(static_cast<const float*>(w.ptr), h, w_elems, ctx)) return 1;
+            w_hi = h;
+            w_lo = nullptr;
+            return 0;
+        }
         if (igemm_tc) {
             if (launch_conv_weight_split(static_cast<const float*>(w.ptr), h, h + w_elems, int(w.shape[0]), int(w.shape[1]), int(w.shape[2]), int(w.shape[3]), ctx)) return 1;
         } else if (launch_split_tf32(static_cast<const float*>(w.ptr), h, h + w_elems, w_elems, ctx)) return 1;
@@ -271,7 +280,7 @@ int run_conv(Registry& reg, const TensorIds& in, const TensorIds& out, const Par
         GemmArgs g;
         g.x = static_cast<const float*>(x.ptr);
         g.w = static_cast<const float*>(w.ptr);
-        if (cp && cp->gemm_1x1) { g.w_hi = cp->w_hi; g.w_lo = cp->w_lo; }
+        if (cp && cp->gemm_1x1) { g.w_hi = cp->w_hi; g.w_lo = cp->w_lo; g.w_is_bf16 = cp->bf16; }
         g.bias = static_cast<const float*>(b.ptr);
         g.out = static_cast<float*>(o.ptr);
         g.M = n_pix; g.N = d.O; g.K = d.C;
@@ -282,7 +291,7 @@ int run_conv(Registry& reg, const TensorIds& in, const TensorIds& out, const Par
     if (cp && cp->igemm_tc && cp->w_hi && is_channels_last(x) && is_channels_last(o) && aligned16(x.ptr)) {
         ConvTcArgs c;
         c.x = static_cast<const float*>(x.ptr);
-        c.w_hi = cp->w_hi; c.w_lo = cp->w_lo;
+        c.w_hi = cp->w_hi; c.w_lo = cp->w_lo; c.w_is_bf16 = cp->bf16;
         c.bias = static_cast<const float*>(b.ptr);
         c.out = static_cast<float*>(o.ptr);
         c.N = d.N; c.C = d.C; c.H = d.H; c.W = d.W; c.O = d.O; c.KH = d.KH; c.KW = d.KW; c.HO = d.HO; c.WO = d.WO;
@@ -386,14 +395,16 @@ std::unique_ptr<NodePlan> plan_conv(const Registry& reg, const TensorIds& in, co
         if (is_1x1 && env.gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(M, O, C)) {
             pl->gemm_1x1 = true;
             pl->w_elems = O * C;
+            pl->bf16 = env.gemm_mode == FXF_GEMM_BF16 && C % 8 == 0;
             pl->persist_bytes = round_up(size_t(2) * size_t(pl->w_elems) * sizeof(float), 256);
-            pl->variant = "1x1 -> tcgen05-tf32x3 GEMM when channels-last, else igemm-simt64x64";
+            pl->variant = pl->bf16 ? "1x1 -> tcgen05-bf16 GEMM when channels-last, else igemm-simt64x64" : "1x1 -> tcgen05-tf32x3 GEMM when channels-last, else igemm-simt64x64";
         } else if (!is_1x1 && p.ints[0] >= 1 && p.ints[0] <= 2 && p.ints[1] >= 1 && p.ints[1] <= 2 && p.ints[6] == 1 && env.gemm_mode != FXF_GEMM_FP32_SIMT && conv_tc_shape_ok(M, int(C), int(O)) &&
                    reg[in[0]].rank == 4 && reg[in[0]].shape[1] == C) {
             pl->igemm_tc = true;
             pl->w_elems = O * C * w.shape[2] * w.shape[3];
+            pl->bf16 = env.gemm_mode == FXF_GEMM_BF16 && C % 32 == 0;
             pl->persist_bytes = round_up(size_t(2) * size_t(pl->w_elems) * sizeof(float), 256);
-            pl->variant = "tcgen05-tf32x3 implicit GEMM when channels-last, else igemm-simt64x64";
+            pl->variant = pl->bf16 ? "tcgen05-bf16 implicit GEMM when channels-last, else igemm-simt64x64" : "tcgen05-tf32x3 implicit GEMM when channels-last, else igemm-simt64x64";
         } else {
             pl->variant = "igemm-simt64x64";
         }

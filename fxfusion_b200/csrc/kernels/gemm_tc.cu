@@ -21,6 +21,11 @@
 // Writing only x_lo removes a third of the split traffic; A in TMEM removes the split stores and the
 // A operand reads, but TMEM (512 columns) cannot hold two 256-column accumulators plus A stages.
 //
+// Optional bf16 mode (FXF_GEMM_BF16, template flag BF16): the same pipeline with ONE product per logical product —
+// weights converted to bf16 once per engine, the activation tile converted to packed bf16 pairs on its way into
+// tensor memory, tcgen05.mma.kind::f16 (K = 16 per instruction), fp32 accumulation and fp32 output.  Results are
+// bf16-grade (about 3e-3 of the output scale); it exists for throughput, not for the parity contract.
+//
 // Structure: a PERSISTENT kernel, one CTA per SM, each CTA walking a strided list of 128 x BN output
 // tiles.  320 threads in four roles that only meet on mbarriers:
 //   warps 0-3  epilogue: tcgen05.ld of a finished accumulator (each warp its 32 TMEM lanes), staged
@@ -60,12 +65,12 @@ enum : int { kErrWaitTma = 101, kErrWaitSplit = 102, kErrWaitEmpty = 103, kErrWa
 
 constexpr int kStagePad = 36;  // floats per staged epilogue row: 32 + 4 keeps float4 rows conflict-free
 
-template <int BN, int BK, int STAGES, bool TS>
+template <int BN, int BK, int STAGES, bool TS, bool BF16>
 struct alignas(1024) TcSmem {
     float a[STAGES][BM * BK];             // x tile as TMA wrote it (fp32, swizzled rows of BK floats); x_hi in place when !TS
     float a_lo[TS ? 1 : STAGES][TS ? 256 : BM * BK];  // x_lo twin buffers, only when the MMAs read A from shared memory
-    float b_hi[STAGES][BN * BK];
-    float b_lo[STAGES][BN * BK];
+    float b_hi[STAGES][BF16 ? BN * BK / 2 : BN * BK];   // w_hi tile (fp32), or the whole bf16 weight tile in bf16 mode
+    float b_lo[BF16 ? 1 : STAGES][BF16 ? 256 : BN * BK];
     float stage_out[4][32 * kStagePad];   // one 32 x 32 block per epilogue warp
     uint64_t full_tma[STAGES];
     uint64_t full_split[STAGES];
@@ -162,22 +167,26 @@ __device__ __forceinline__ int64_t out_row_offset(const TcParams& p, int tm, int
     return ((int64_t(n) * c.HO + oy) * c.WO + ox) * p.ldo;
 }
 
-template <int BN, int BK, int STAGES, int ACC, bool TS>
+template <int BN, int BK, int STAGES, int ACC, bool TS, bool BF16, bool HYB>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_whi,
                    const __grid_constant__ CUtensorMap map_wlo, TcParams p) {
     extern __shared__ unsigned char smem_raw[];
     // dynamic shared memory is only guaranteed 16-byte aligned; swizzled tiles need 1024
-    using Smem = TcSmem<BN, BK, STAGES, TS>;
+    static_assert(!BF16 || (TS && BK == 32), "the bf16 mode takes A from tensor memory with 32-float slabs");
+    static_assert(!HYB || (TS && !BF16), "hybrid: x_hi is the raw tile in shared memory, x_lo goes to tensor memory");
+    using Smem = TcSmem<BN, BK, STAGES, TS, BF16>;
     Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_k = int((p.K + BK - 1) / BK);
     const int num_units = p.full_tiles + p.tail_tiles * p.tail_split;
-    constexpr uint32_t kStageBytes = uint32_t(BM * BK + 2 * BN * BK) * 4u;
-    constexpr uint32_t kIdesc = umma_idesc_tf32(BM, BN);
+    constexpr uint32_t kBBytes = BF16 ? uint32_t(BN * BK) * 2u : uint32_t(2 * BN * BK) * 4u;   // weight bytes per stage
+    constexpr uint32_t kStageBytes = uint32_t(BM * BK) * 4u + kBBytes;
+    constexpr uint32_t kIdesc = BF16 ? umma_idesc_bf16(BM, BN) : umma_idesc_tf32(BM, BN);
+    constexpr int kACols = BF16 ? BK / 2 : (HYB ? BK : 2 * BK);   // TMEM columns of one A stage
     constexpr uint32_t kColA = uint32_t(ACC * BN);             // first TMEM column of the A stages
-    constexpr uint32_t kColsUsed = kColA + (TS ? uint32_t(STAGES * 2 * BK) : 0u);
+    constexpr uint32_t kColsUsed = kColA + (TS ? uint32_t(STAGES * kACols) : 0u);
     static_assert(kColsUsed <= 512, "accumulators and A stages exceed the 512 TMEM columns");
     constexpr uint32_t kTmemCols = kColsUsed <= 256 ? 256 : 512;  // allocations are powers of two
     volatile int* abort_flag = &s.abort_flag;
@@ -222,7 +231,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         int ox0, oy0, n0;
                         conv_tile_origin(p.cv, tm, ox0, oy0, n0);
                         const int tap = k / p.cv.c_slabs, cs = k - tap * p.cv.c_slabs, kh = tap / p.cv.KW, kw = tap - kh * p.cv.KW;
-                        mbar_expect_tx(&s.full_tma[st], p.cv.a_bytes + uint32_t(2 * BN * BK) * 4u);
+                        mbar_expect_tx(&s.full_tma[st], p.cv.a_bytes + kBBytes);
                         tma_load_4d(s.a[st], &map_x, cs * BK, ox0 * p.cv.str_w - p.cv.pad_w + kw * p.cv.dil_w,
                                     oy0 * p.cv.str_h - p.cv.pad_h + kh * p.cv.dil_h, n0, &s.full_tma[st]);
                     } else {
@@ -230,7 +239,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         tma_load_2d(s.a[st], &map_x, k * BK, tm * BM, &s.full_tma[st]);
                     }
                     tma_load_2d(s.b_hi[st], &map_whi, k * BK, tn * BN, &s.full_tma[st]);
-                    tma_load_2d(s.b_lo[st], &map_wlo, k * BK, tn * BN, &s.full_tma[st]);
+                    if (!BF16) tma_load_2d(s.b_lo[BF16 ? 0 : st], &map_wlo, k * BK, tn * BN, &s.full_tma[st]);
                 }
             }
         producer_done:;
@@ -260,9 +269,29 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         goto mma_done;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    uint64_t b_hi = umma_desc_k_major<BK>(smem_u32(s.b_hi[st])), b_lo = umma_desc_k_major<BK>(smem_u32(s.b_lo[st]));
-                    if (TS) {
-                        const uint32_t a_hi = tmem_base + kColA + uint32_t(st * 2 * BK), a_lo = a_hi + uint32_t(BK);  // 8 columns per K-step
+                    if (BF16) {
+                        const uint32_t a_bf = tmem_base + kColA + uint32_t(st * kACols);   // 8 columns (16 bf16) per K-step
+                        const uint64_t b_bf = umma_desc_k_major_bytes<BK * 2>(smem_u32(s.b_hi[st]));
+#pragma unroll
+                        for (int kk = 0; kk < BK / 16; kk++)
+                            umma_bf16_ts(tmem_acc, a_bf + uint32_t(kk * 8), b_bf + uint64_t((kk * 32) >> 4), kIdesc, (k > un.k0 || kk > 0) ? 1u : 0u);
+                        umma_commit(&s.empty[st]);
+                        continue;
+                    }
+                    uint64_t b_hi = umma_desc_k_major<BK>(smem_u32(s.b_hi[st])), b_lo = umma_desc_k_major<BK>(smem_u32(s.b_lo[BF16 ? 0 : st]));
+                    if (HYB) {
+                        // x_hi = the fp32 tile as it lies in shared memory (the MMA truncates it), x_lo from tensor memory
+                        const uint32_t a_lo = tmem_base + kColA + uint32_t(st * kACols);
+                        const uint64_t a_hi = umma_desc_k_major<BK>(smem_u32(s.a[st]));
+#pragma unroll
+                        for (int kk = 0; kk < BK / 8; kk++) {
+                            uint64_t adv = uint64_t((kk * 8 * 4) >> 4);
+                            umma_tf32_ts(tmem_acc, a_lo + uint32_t(kk * 8), b_hi + adv, kIdesc, (k > un.k0 || kk > 0) ? 1u : 0u);
+                            umma_tf32(tmem_acc, a_hi + adv, b_lo + adv, kIdesc, 1u);
+                            umma_tf32(tmem_acc, a_hi + adv, b_hi + adv, kIdesc, 1u);
+                        }
+                    } else if (TS) {
+                        const uint32_t a_hi = tmem_base + kColA + uint32_t(st * kACols), a_lo = a_hi + uint32_t(BK);  // 8 columns per K-step
 #pragma unroll
                         for (int kk = 0; kk < BK / 8; kk++) {
                             uint64_t adv = uint64_t((kk * 8 * 4) >> 4);  // 32 bytes per K-step inside the swizzle row
@@ -304,6 +333,39 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         goto split_done;
                     }
                     const float4* src = reinterpret_cast<const float4*>(s.a[st]) + row * (BK / 4);
+                    if (BF16) {
+                        // bf16 mode: the row's BK floats become BK/2 packed words (element k in the low half of word k/2)
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int c = 0; c < BK / 4 && c < 8; c++) {
+                            float4 v = src[c ^ sw];
+                            packed[2 * c + 0] = pack_bf16x2(v.x, v.y);
+                            packed[2 * c + 1] = pack_bf16x2(v.z, v.w);
+                        }
+                        tmem_st16(tmem_base + lane_base + kColA + uint32_t(st * kACols), packed);
+                        tmem_wait_st();
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&s.full_split[st]);
+                        continue;
+                    }
+                    if (HYB) {
+                        uint32_t lo_only[BK];
+#pragma unroll
+                        for (int c = 0; c < BK / 4; c++) {
+                            float4 v = src[c ^ sw];
+                            lo_only[4 * c + 0] = __float_as_uint(lo_of_truncated(v.x));
+                            lo_only[4 * c + 1] = __float_as_uint(lo_of_truncated(v.y));
+                            lo_only[4 * c + 2] = __float_as_uint(lo_of_truncated(v.z));
+                            lo_only[4 * c + 3] = __float_as_uint(lo_of_truncated(v.w));
+                        }
+                        tmem_st(tmem_base + lane_base + kColA + uint32_t(st * kACols), lo_only);
+                        tmem_wait_st();
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&s.full_split[st]);
+                        continue;
+                    }
                     uint32_t hi[BK], lo[BK];
 #pragma unroll
                     for (int c = 0; c < BK / 4; c++) {
@@ -314,7 +376,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         split_tf32(v.z, h, l); hi[4 * c + 2] = __float_as_uint(h); lo[4 * c + 2] = __float_as_uint(l);
                         split_tf32(v.w, h, l); hi[4 * c + 3] = __float_as_uint(h); lo[4 * c + 3] = __float_as_uint(l);
                     }
-                    const uint32_t a_col = tmem_base + lane_base + kColA + uint32_t(st * 2 * BK);
+                    const uint32_t a_col = tmem_base + lane_base + kColA + uint32_t(st * kACols);
                     tmem_st(a_col, hi);
                     tmem_st(a_col + uint32_t(BK), lo);
                     tmem_wait_st();
@@ -561,6 +623,21 @@ int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, in
     return 0;
 }
 
+// bf16 weight matrix [rows, cols] (row pitch `ld` elements): box [box_rows, bk], rows of bk * 2 bytes = one swizzle span
+int make_map_bf16(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, int bk) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    FXF_CHECK(fn != nullptr, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+    cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+    cuuint64_t strides[1] = {cuuint64_t(ld) * 2};
+    cuuint32_t box[2] = {cuuint32_t(bk), cuuint32_t(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    bk == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    FXF_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (bf16) failed with code %d (rows %lld cols %lld ld %lld)", int(r), (long long)rows, (long long)cols, (long long)ld);
+    return 0;
+}
+
 // channels-last activation [N,H,W,C] as a 4-D map; box = [BNI, BH, BW, bk channels], 64-byte swizzle (bk = 16).
 // With a traversal stride s the box extent is given in input pixels (BW * s) and ceil(extent / s) = BW are loaded.
 int make_map_nhwc(CUtensorMap* map, const float* base, int N, int H, int W, int C, int bni, int bh, int bw, int bk, int sh, int sw) {
@@ -577,14 +654,19 @@ int make_map_nhwc(CUtensorMap* map, const float* base, int N, int H, int W, int 
     return 0;
 }
 
-template <int BN, int BK, int STAGES, int ACC, bool TS>
+template <int BN, int BK, int STAGES, int ACC, bool TS, bool BF16 = false, bool HYB = false>
 int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, const ConvGeom* geom = nullptr) {
     CUtensorMap mx, mhi, mlo;
     if (cv) {
         if (make_map_nhwc(&mx, cv->x, cv->N, cv->H, cv->W, cv->C, geom->BNI, geom->BH, geom->BW, BK, geom->str_h, geom->str_w)) return 1;
     } else if (make_map(&mx, a.x, a.M, a.K, a.ldx, BM, BK)) return 1;
-    if (make_map(&mhi, a.w_hi, a.N, a.K, a.K, BN, BK)) return 1;
-    if (make_map(&mlo, a.w_lo, a.N, a.K, a.K, BN, BK)) return 1;
+    if (BF16) {
+        if (make_map_bf16(&mhi, a.w_hi, a.N, a.K, a.K, BN, BK)) return 1;
+        mlo = mhi;
+    } else {
+        if (make_map(&mhi, a.w_hi, a.N, a.K, a.K, BN, BK)) return 1;
+        if (make_map(&mlo, a.w_lo, a.N, a.K, a.K, BN, BK)) return 1;
+    }
     TcParams p{};
     if (geom) {
         p.cv = *geom;
@@ -600,12 +682,12 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
     // walk tiles so that the operand that does not fit in L2 is the one reused by concurrent CTAs
     p.m_fastest = a.N > a.M ? 1 : 0;
     p.status = ctx.status;
-    size_t smem = sizeof(TcSmem<BN, BK, STAGES, TS>) + 1024;
+    size_t smem = sizeof(TcSmem<BN, BK, STAGES, TS, BF16>) + 1024;
     static bool configured[64] = {};
     int dev = 0;
     FXF_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        FXF_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, BK, STAGES, ACC, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        FXF_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, BK, STAGES, ACC, TS, BF16, HYB>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
@@ -618,13 +700,13 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
     int grid = int(units < ctx.sm_count ? units : ctx.sm_count);
     if (cv) {
         const double pix = double(cv->N) * cv->HO * cv->WO;
-        tag_launch(ctx, "conv2d_igemm_tf32x3_tcgen05", 2.0 * pix * double(a.N) * double(a.K),
+        tag_launch(ctx, BF16 ? "conv2d_igemm_bf16_tcgen05" : "conv2d_igemm_tf32x3_tcgen05", 2.0 * pix * double(a.N) * double(a.K),
                    4.0 * (double(cv->N) * cv->H * cv->W * cv->C + double(a.N) * a.K + double(a.N) + pix * a.N));
     } else {
-        tag_launch(ctx, "gemm_tf32x3_tcgen05", 2.0 * double(a.M) * double(a.N) * double(a.K),
+        tag_launch(ctx, BF16 ? "gemm_bf16_tcgen05" : "gemm_tf32x3_tcgen05", 2.0 * double(a.M) * double(a.N) * double(a.K),
                    4.0 * (double(a.M) * a.K + double(a.N) * a.K + double(a.N) + double(a.M) * a.N));
     }
-    gemm_tf32x3_kernel<BN, BK, STAGES, ACC, TS><<<grid, kThreads, smem, ctx.stream>>>(mx, mhi, mlo, p);
+    gemm_tf32x3_kernel<BN, BK, STAGES, ACC, TS, BF16, HYB><<<grid, kThreads, smem, ctx.stream>>>(mx, mhi, mlo, p);
     FXF_LAUNCHED(ctx);
     return 0;
 }
@@ -635,10 +717,11 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
 // multiples of 4 floats (TMA strides are multiples of 16 bytes), K a multiple of 4 and a problem
 // large enough that 128-row tiles are not mostly padding.
 bool gemm_tc_supported(const GemmArgs& a, bool allow_few_rows) {
-    if (a.w_hi == nullptr || a.w_lo == nullptr) return false;
+    if (a.w_hi == nullptr || (!a.w_is_bf16 && a.w_lo == nullptr)) return false;
+    if (a.w_is_bf16 && a.K % 8 != 0) return false;   // bf16 rows must be 16-byte multiples for TMA
     if (!gemm_tc_shape_ok(allow_few_rows && a.M >= 1 ? std::max<int64_t>(a.M, 64) : a.M, a.N, a.K)) return false;
     if (a.ldx % 4 != 0 || a.ldx < a.K) return false;
-    if (!aligned16(a.x) || !aligned16(a.w_hi) || !aligned16(a.w_lo)) return false;
+    if (!aligned16(a.x) || !aligned16(a.w_hi) || (!a.w_is_bf16 && !aligned16(a.w_lo))) return false;
     return true;
 }
 
@@ -653,6 +736,11 @@ bool gemm_tc_shape_ok(int64_t M, int64_t N, int64_t K) {
 int gemm_tc_pick_bn(int64_t M, int64_t N, int sm_count, int64_t K) {
     if (N <= 128) return 128;
     const int64_t tiles_m = (M + BM - 1) / BM;
+    // Very large problems whose N wastes < 2 % of a 224-wide tiling take the hybrid variant (x_hi read from shared
+    // memory as delivered, x_lo from tensor memory; 224 = the widest tile that leaves TMEM room for x_lo stages):
+    // 6 % faster than 256-wide tiles on the 8192 x 50257 x 768 vocabulary projection, slower on mid-size shapes.
+    const int64_t n224 = (N + 223) / 224;
+    if (K > 0 && tiles_m * n224 >= int64_t(16) * sm_count && double(n224 * 224) <= 1.02 * double(N)) return 224;
     const int cand[3] = {256, 192, 128};
     const double penalty[3] = {1.0, 1.10, 1.25};   // time per flop relative to the 256-wide tile (measured on the GPT-2 shapes)
     int best = 256;
@@ -693,6 +781,11 @@ int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows) {
     }();
     int bn = forced ? forced : gemm_tc_pick_bn(a.M, a.N, ctx.sm_count, ctx.gemm_ws ? a.K : 0);
     if (a.N <= 128) bn = 128;
+    if (a.w_is_bf16) {  // bf16 mode: one product per logical product, A converted into tensor memory
+        if (bn >= 192 && a.N > 128) return launch_tc<192, 32, 6, 2, true, true>(a, ctx);
+        return launch_tc<128, 32, 8, 2, true, true>(a, ctx);
+    }
+    if (bn == 224) return launch_tc<224, 16, 4, 2, true, false, true>(a, ctx);
     if (a_from_smem(bn)) {
         switch (bn) {
             case 256: return launch_tc<256, 16, 4, 2, false>(a, ctx);
@@ -756,9 +849,9 @@ int launch_conv_weight_split(const float* w_oihw, float* hi, float* lo, int O, i
 }
 
 int launch_conv_tc(const ConvTcArgs& c, ExecCtx& ctx) {
-    FXF_CHECK(c.x && c.w_hi && c.w_lo && c.out, "conv (tensor core): NULL operand");
+    FXF_CHECK(c.x && c.w_hi && (c.w_lo || c.w_is_bf16) && c.out, "conv (tensor core): NULL operand");
     FXF_CHECK(c.str_h >= 1 && c.str_h <= 2 && c.str_w >= 1 && c.str_w <= 2, "conv (tensor core): stride must be 1 or 2");
-    FXF_CHECK(conv_tc_shape_ok(int64_t(c.N) * c.HO * c.WO, c.C, c.O) && aligned16(c.x) && aligned16(c.w_hi) && aligned16(c.w_lo),
+    FXF_CHECK(conv_tc_shape_ok(int64_t(c.N) * c.HO * c.WO, c.C, c.O) && aligned16(c.x) && aligned16(c.w_hi) && (c.w_is_bf16 || aligned16(c.w_lo)),
               "conv (tensor core): unsupported problem");
     ConvGeom g{};
     g.KW = c.KW; g.WO = c.WO; g.HO = c.HO; g.N = c.N;
@@ -773,6 +866,13 @@ int launch_conv_tc(const ConvTcArgs& c, ExecCtx& ctx) {
     a.ldo = c.O;
     a.relu = c.relu;
     int bn = a.N <= 128 ? 128 : gemm_tc_pick_bn(a.M, a.N, ctx.sm_count, ctx.gemm_ws ? a.K : 0);
+    if (c.w_is_bf16) {
+        a.w_is_bf16 = true;
+        FXF_CHECK(c.C % 32 == 0, "conv (tensor core, bf16): input channels must be a multiple of 32");
+        if (bn >= 192) return launch_tc<192, 32, 6, 2, true, true>(a, ctx, &c, &g);
+        return launch_tc<128, 32, 8, 2, true, true>(a, ctx, &c, &g);
+    }
+    if (bn == 224) return launch_tc<224, 16, 4, 2, true, false, true>(a, ctx, &c, &g);
     if (a_from_smem(bn)) {
         switch (bn) {
             case 256: return launch_tc<256, 16, 4, 2, false>(a, ctx, &c, &g);
@@ -785,6 +885,44 @@ int launch_conv_tc(const ConvTcArgs& c, ExecCtx& ctx) {
         case 192: return launch_tc<192, 16, 4, 2, true>(a, ctx, &c, &g);
         default: return c.C % 32 == 0 ? launch_tc<128, 32, 4, 2, true>(a, ctx, &c, &g) : launch_tc<128, 16, 8, 2, true>(a, ctx, &c, &g);
     }
+}
+
+// ---- bf16 mode: weights converted once per engine ---------------------------------------------------
+namespace {
+__global__ void __launch_bounds__(256) convert_bf16_kernel(const float* __restrict__ w, uint16_t* __restrict__ out, int64_t n) {
+    int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = uint16_t(pack_bf16x2(w[i], 0.f) & 0xffffu);
+}
+__global__ void __launch_bounds__(256) conv_weight_bf16_kernel(const float* __restrict__ w, uint16_t* __restrict__ out, int O, int C, int KH, int KW) {
+    int64_t total = int64_t(O) * C * KH * KW, stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        int c = int(i % C);
+        int64_t t = i / C;
+        int kw = int(t % KW); t /= KW;
+        int kh = int(t % KH);
+        int o = int(t / KH);
+        out[i] = uint16_t(pack_bf16x2(w[((int64_t(o) * C + c) * KH + kh) * KW + kw], 0.f) & 0xffffu);
+    }
+}
+}  // namespace
+
+int launch_convert_bf16(const float* w, void* out, int64_t n, ExecCtx& ctx) {
+    if (n == 0) return 0;
+    int64_t blocks = (n + 255) / 256, cap = int64_t(ctx.sm_count) * 8;
+    tag_launch(ctx, "convert_bf16", 0, 6.0 * double(n));
+    convert_bf16_kernel<<<int(blocks < cap ? blocks : cap), 256, 0, ctx.stream>>>(w, static_cast<uint16_t*>(out), n);
+    FXF_LAUNCHED(ctx);
+    return 0;
+}
+
+int launch_conv_weight_bf16(const float* w_oihw, void* out, int O, int C, int KH, int KW, ExecCtx& ctx) {
+    int64_t total = int64_t(O) * C * KH * KW;
+    if (total == 0) return 0;
+    int64_t blocks = (total + 255) / 256, cap = int64_t(ctx.sm_count) * 8;
+    tag_launch(ctx, "conv_weight_bf16", 0, 6.0 * double(total));
+    conv_weight_bf16_kernel<<<int(blocks < cap ? blocks : cap), 256, 0, ctx.stream>>>(w_oihw, static_cast<uint16_t*>(out), O, C, KH, KW);
+    FXF_LAUNCHED(ctx);
+    return 0;
 }
 
 int launch_split_tf32(const float* w, float* hi, float* lo, int64_t n, ExecCtx& ctx) {

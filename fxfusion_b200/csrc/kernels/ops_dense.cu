@@ -41,7 +41,8 @@ int launch_gemm(const GemmArgs& a, ExecCtx& ctx) {
 }
 
 std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count) {
-    if (gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(a.M, a.N, a.K)) return "tcgen05-tf32x3-128x" + std::to_string(gemm_tc_pick_bn(a.M, a.N, sm_count));
+    if (gemm_mode == FXF_GEMM_BF16 && gemm_tc_shape_ok(a.M, a.N, a.K) && a.K % 8 == 0) return std::string("tcgen05-bf16-128x") + (a.N > 128 ? "192" : "128");
+    if (gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(a.M, a.N, a.K)) return "tcgen05-tf32x3-128x" + std::to_string(gemm_tc_pick_bn(a.M, a.N, sm_count, a.K));
     static const char* names[] = {"simt128x128", "simt64x64", "simt32x32", "skinny32x8"};
     return names[simt_tile_choice(a.M, a.N, sm_count)];
 }
@@ -58,6 +59,7 @@ struct Slice {
     int64_t src_ld = 0;             // row pitch of the source (elements)
     bool whole = true;              // the slice is the entire tensor: no copy
     bool split = false;             // TF32 hi/lo copies wanted (tensor-core GEMM operand)
+    bool bf16 = false;              // bf16 mode: one bf16 copy instead (hi points to it, lo stays NULL)
     bool drop = false;              // replaced by "no bias" (rank != 0 of a row-parallel product)
     size_t off_copy = 0, off_split = 0;  // byte offsets inside the plan's persistent memory
     const float *ptr = nullptr, *hi = nullptr, *lo = nullptr;  // resolved by prepare()
@@ -71,6 +73,7 @@ struct DensePlan : NodePlan {
     // dims the kernels need again
     int64_t M = 0, heads_local = 0, head0 = 0, n_local = 0, col_off = 0;
     bool prepared = false;
+    bool bf16_mode = false;   // set by the plan builders from the engine's GEMM mode
 
     Slice& add(int input, int64_t rows, int64_t cols) {
         Slice& x = s[n++];
@@ -88,8 +91,9 @@ struct DensePlan : NodePlan {
         }
         if (want_split) {
             x.split = true;
+            x.bf16 = bf16_mode && x.ncol % 8 == 0;
             x.off_split = persist_bytes;
-            persist_bytes += round_up(size_t(2) * size_t(x.elems()) * sizeof(float), 256);
+            persist_bytes += round_up(x.bf16 ? size_t(x.elems()) * 2 : size_t(2) * size_t(x.elems()) * sizeof(float), 256);
         }
     }
     int prepare(Registry& reg, const TensorIds& in, const TensorIds&, const Params&, ExecCtx& ctx) override {
@@ -114,9 +118,15 @@ struct DensePlan : NodePlan {
             if (x.split) {
                 FXF_CHECK(persist != nullptr, "dense plan: persistent memory was not assigned");
                 float* h = reinterpret_cast<float*>(static_cast<char*>(persist) + x.off_split);
-                if (launch_split_tf32(x.ptr, h, h + x.elems(), x.elems(), ctx)) return 1;
-                x.hi = h;
-                x.lo = h + x.elems();
+                if (x.bf16) {
+                    if (launch_convert_bf16(x.ptr, h, x.elems(), ctx)) return 1;
+                    x.hi = h;
+                    x.lo = nullptr;
+                } else {
+                    if (launch_split_tf32(x.ptr, h, h + x.elems(), x.elems(), ctx)) return 1;
+                    x.hi = h;
+                    x.lo = h + x.elems();
+                }
             }
         }
         prepared = true;
@@ -128,7 +138,7 @@ inline const DensePlan* dense(const NodePlan* p) { return static_cast<const Dens
 bool want_tc(const PlanEnv& env, int64_t M, int64_t N, int64_t K) { return env.gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(M, N, K); }
 
 void fill_gemm(GemmArgs& g, const float* x, const Slice& w, const Slice* bias, float* out, int64_t M, int64_t ldx, int64_t ldo, bool relu) {
-    g.x = x; g.w = w.ptr; g.w_hi = w.hi; g.w_lo = w.lo;
+    g.x = x; g.w = w.ptr; g.w_hi = w.hi; g.w_lo = w.lo; g.w_is_bf16 = w.bf16;
     g.bias = (bias && !bias->drop) ? bias->ptr : nullptr;
     g.out = out; g.M = M; g.N = w.rows(); g.K = w.ncol;
     g.ldx = ldx; g.ldw = w.ncol; g.ldo = ldo; g.relu = relu;
@@ -180,6 +190,7 @@ int k_linear_relu(Registry& reg, const TensorIds& in, const TensorIds& out, cons
 
 std::unique_ptr<NodePlan> plan_linear(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const PlanEnv& env) {
     auto p = std::make_unique<DensePlan>();
+    p->bf16_mode = env.gemm_mode == FXF_GEMM_BF16;
     if (in.size() < 3 || out.size() < 1) return p;
     const FxfTensor &x = reg[in[0]], &w = reg[in[1]];
     if (w.rank != 2 || x.rank < 1) return p;
@@ -234,6 +245,7 @@ int k_feedforward(Registry& reg, const TensorIds& in, const TensorIds& out, cons
 
 std::unique_ptr<NodePlan> plan_feedforward(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const PlanEnv& env) {
     auto p = std::make_unique<DensePlan>();
+    p->bf16_mode = env.gemm_mode == FXF_GEMM_BF16;
     if (in.size() < 5 || out.size() < 1) return p;
     const FxfTensor &x = reg[in[0]], &w1 = reg[in[1]], &w2 = reg[in[3]];
     if (w1.rank != 2 || w2.rank != 2 || x.rank < 1) return p;
@@ -326,6 +338,7 @@ int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params
 
 std::unique_ptr<NodePlan> plan_mha(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& env) {
     auto pl = std::make_unique<DensePlan>();
+    pl->bf16_mode = env.gemm_mode == FXF_GEMM_BF16;
     if (in.size() < 6 || out.size() < 1 || p.ints.size() < 4 || reg[in[0]].rank != 3) return pl;
     const FxfTensor& x = reg[in[0]];
     const int64_t B = x.shape[0], T = x.shape[1], H = p.ints[0], hd = p.ints[1], D = p.ints[2], QKV = p.ints[3], M = B * T;
@@ -446,6 +459,7 @@ int k_cross_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const 
 
 std::unique_ptr<NodePlan> plan_cross_mha(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& env) {
     auto pl = std::make_unique<DensePlan>();
+    pl->bf16_mode = env.gemm_mode == FXF_GEMM_BF16;
     if (in.size() < 9 || out.size() < 1 || p.ints.size() < 4 || reg[in[0]].rank != 3 || reg[in[1]].rank != 3) return pl;
     const FxfTensor &x = reg[in[0]], &mem = reg[in[1]];
     const int64_t B = x.shape[0], Tq = x.shape[1], Tk = mem.shape[1], H = p.ints[0], hd = p.ints[1], D = p.ints[2], KV = p.ints[3];

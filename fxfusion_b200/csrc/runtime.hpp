@@ -212,6 +212,7 @@ struct GemmArgs {
     const float* w = nullptr;
     const float* w_hi = nullptr;
     const float* w_lo = nullptr;
+    bool w_is_bf16 = false;   // bf16 mode: w_hi points to the weight as bf16 [N,K] (w_lo unused)
     const float* bias = nullptr;
     float* out = nullptr;
     int64_t M = 0, N = 0, K = 0;
@@ -235,6 +236,7 @@ std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count);
 struct ConvTcArgs {
     const float* x = nullptr;
     const float *w_hi = nullptr, *w_lo = nullptr;
+    bool w_is_bf16 = false;   // bf16 mode: w_hi points to the repacked filters as bf16
     const float* bias = nullptr;
     float* out = nullptr;
     int N = 0, C = 0, H = 0, W = 0, O = 0, KH = 0, KW = 0, HO = 0, WO = 0;
@@ -247,6 +249,8 @@ bool conv_tc_shape_ok(int64_t n_pix, int C, int O);
 int linear_on_rows(const NodePlan* plan, const float* x_rows, int64_t M, int64_t ldx, float* out, int64_t ldo, ExecCtx& ctx);
 int launch_conv_tc(const ConvTcArgs& a, ExecCtx& ctx);
 // w_oihw [O,C,KH,KW] -> TF32 hi/lo halves laid out [O,KH,KW,C]
+int launch_convert_bf16(const float* w, void* out_bf16, int64_t n, ExecCtx& ctx);
+int launch_conv_weight_bf16(const float* w_oihw, void* out_bf16_ohwi, int O, int C, int KH, int KW, ExecCtx& ctx);
 int launch_conv_weight_split(const float* w_oihw, float* hi, float* lo, int O, int C, int KH, int KW, ExecCtx& ctx);
 
 // Attention core on packed qkv [B,T,3D] (Q | K | V thirds, head h at columns h*hd) -> ctx [B,T,D].

@@ -58,7 +58,10 @@ typedef struct FxfTensor {
 enum {
     FXF_GEMM_AUTO = 0,      /* tensor-core 3xTF32 where the shape allows it, else fp32 SIMT */
     FXF_GEMM_FP32_SIMT = 1, /* fp32 FFMA tiles only */
-    FXF_GEMM_TF32X3 = 2     /* tcgen05 kind::tf32 with hi/lo operand split (fp32-grade result) */
+    FXF_GEMM_TF32X3 = 2,    /* tcgen05 kind::tf32 with hi/lo operand split (fp32-grade result) */
+    FXF_GEMM_BF16 = 3       /* optional reduced-precision mode: weights and activations rounded to bf16 for the tensor-core
+                               products (one product per logical product), fp32 accumulation and fp32 tensors everywhere
+                               else; results within about 1e-2 relative of the fp32 path, decode tokens may differ */
 };
 
 typedef struct FxfEngineOptions {

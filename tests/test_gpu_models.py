@@ -217,3 +217,22 @@ def test_c4_encoder_decoder_matches_oracle_on_reduced_batch(built_lib, tmp_path,
     assert ok, info
     assert eng.device_status() == 0
     assert "CrossMHA" in eng.describe()
+
+
+def test_bf16_mode_gpt_forward_and_decode(built_lib, tmp_path):
+    """Optional bf16 mode on the 4-layer GPT of configuration 2: logits within 2e-2 of the oracle's scale, and the greedy
+    decode runs to completion (tokens may differ from the fp32 path where logits are nearly tied)."""
+    cfg = lowering.GPT_C2
+    g = lowering.gpt_graph(cfg, lowering.gpt_params(cfg, 0), batch=8, seq=64, name="c2_bf16")
+    tokens, buf, mask = _gpt_inputs(cfg, 8, 64, 40)
+    eng = _engine(g, tmp_path, precision="bf16")
+    assert "tcgen05-bf16" in eng.describe()
+    got = eng.run([buf.cuda(), mask.cuda()])[0].cpu()
+    want = GraphOracle(g).run([buf, mask])[0]
+    valid = ~torch.isnan(want)
+    rel = ((got - want)[valid].abs().max() / want[valid].abs().max()).item()
+    assert 1e-6 < rel < 2e-2, rel
+    dev = buf.cuda()
+    eng.decode_static(dev, 40)
+    assert torch.equal(dev[:, :40].cpu(), tokens) and (dev >= 0).all() and (dev < cfg.vocab).all()
+    assert eng.device_status() == 0

@@ -335,3 +335,49 @@ def test_conv_implicit_gemm_tensor_core(built_lib, N, C, H, W, O, kh, kw, ph, pw
             invoke("Conv2dRelu" if relu else "Conv2d", [cl(x.cuda()), w.cuda(), b.cuda(), out], [0, 1, 2], [3], ints=ints, precision=precision)
             ok, info = compare_outputs(out.cpu().contiguous(), want, atol=ATOL, rtol=RTOL)
             assert ok, (precision, relu, info)
+
+
+def _rel_to_scale(got, want):
+    return ((got - want).abs().max() / want.abs().max().clamp_min(1e-30)).item()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (300, 700, 264), (8192, 768, 768), (1000, 2304, 768), (64, 50, 32), (256, 192, 4096)])
+def test_bf16_mode_linear(built_lib, M, N, K):
+    """Optional bf16 mode: operands rounded to bf16 for the tensor-core products, fp32 accumulation and output.
+    Within 2e-2 of the output scale (measured about 3e-3); shapes the tensor-core kernel does not take fall back to fp32."""
+    from fxfusion_b200.kernels import invoke
+    x, w, b = rnd(M, K), rnd(N, K, seed=1, scale=1 / math.sqrt(K)), rnd(N, seed=2)
+    want = torch.relu(torch.nn.functional.linear(x, w, b))
+    out = torch.full((M, N), float("nan")).cuda()
+    invoke("LinearRelu", [x.cuda(), w.cuda(), b.cuda(), out], [0, 1, 2], [3], precision="bf16")
+    err = _rel_to_scale(out.cpu(), want)
+    assert err < 2e-2, err
+    # the rounding must actually be bf16-sized where the tensor-core kernel applies, and absent where it does not
+    if M >= 64 and N >= 64 and K >= 32 and K % 8 == 0:
+        assert err > 1e-5, "bf16 mode produced fp32-grade results: the bf16 kernel did not run"
+
+
+def test_bf16_mode_mha_feedforward_conv(built_lib):
+    from fxfusion_b200.kernels import invoke
+    B, T, H, hd = 2, 128, 4, 64
+    D = H * hd
+    mask = torch.tril(torch.ones(T, T, dtype=torch.bool)).view(1, 1, T, T).expand(B, 1, T, T).contiguous()
+    reg = _mha_reg(B, T, H, hd, mask)
+    cpu = [t.clone() for t in reg]
+    KERNELS[wire.OP["MHA"]](cpu, [0, 1, 2, 3, 4, 5], [6], [H, hd, D, 3 * D], [math.sqrt(hd)])
+    gpu = [t.cuda() for t in reg]
+    invoke("MHA", gpu, [0, 1, 2, 3, 4, 5], [6], ints=[H, hd, D, 3 * D], floats=[math.sqrt(hd)], precision="bf16")
+    assert _rel_to_scale(gpu[6].cpu(), cpu[6]) < 2e-2
+    x, w1, b1, w2, b2 = rnd(512, 256), rnd(1024, 256, seed=1, scale=1 / 16), rnd(1024, seed=2), rnd(256, 1024, seed=3, scale=1 / 32), rnd(256, seed=4)
+    want = torch.nn.functional.linear(torch.relu(torch.nn.functional.linear(x, w1, b1)), w2, b2)
+    out = torch.zeros(512, 256).cuda()
+    invoke("FeedForward", [x.cuda(), w1.cuda(), b1.cuda(), w2.cuda(), b2.cuda(), out], [0, 1, 2, 3, 4], [5], precision="bf16")
+    assert _rel_to_scale(out.cpu(), want) < 2e-2
+    cl = lambda t: t.contiguous(memory_format=torch.channels_last)
+    xi, wc, bc = rnd(2, 64, 28, 28, seed=5), rnd(128, 64, 3, 3, seed=6, scale=0.05), rnd(128, seed=7)
+    for stride in (1, 2):
+        want = torch.relu(torch.conv2d(xi, wc, bc, stride, 1))
+        out = cl(torch.zeros_like(want).cuda())
+        invoke("Conv2dRelu", [cl(xi.cuda()), wc.cuda(), bc.cuda(), out], [0, 1, 2], [3], ints=[stride, stride, 1, 1, 1, 1, 1], precision="bf16")
+        err = _rel_to_scale(out.cpu().contiguous(), want)
+        assert 1e-5 < err < 2e-2, err
