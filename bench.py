@@ -199,7 +199,8 @@ def run_ours(args):
         comm = Communicator.from_process_group(local, ranks=groups[mine], group=handles[mine]) if tp_size > 1 else None
     dp_size = world // tp_size
     dp_rank = rank // tp_size
-    eng = ExecutionEngine(build_graph_file(B, tmp.name), f"cuda:{local}", precision=args.precision, comm=comm, shard_output=comm is not None)
+    graph_path = build_graph_file(B, tmp.name)
+    eng = ExecutionEngine(graph_path, f"cuda:{local}", precision=args.precision, comm=comm, shard_output=comm is not None)
     lib = _lib.lib()
     prompt = torch.from_numpy(lowering.decode_prompt(B, PROMPT, cfg.vocab, seed=dp_rank))
     start_buf = torch.zeros((B, T), dtype=torch.int64)
@@ -292,6 +293,26 @@ def run_ours(args):
         n_cmp = PROMPT + min(K, T - PROMPT)
         lr_match = bool(torch.equal(lr_buf.cpu()[:, :n_cmp], generated[:, :n_cmp]))
 
+    # ---- optional bf16 mode (one GPU only): the same 128-step decode with bf16 tensor-core products --------------
+    bf16 = None
+    if world == 1 and not args.no_extras and args.precision != "bf16":
+        eng16 = ExecutionEngine(graph_path, f"cuda:{local}", precision="bf16")
+        b16 = start_buf.cuda()
+        eng16.decode_static(start_buf.cuda(), T - 3)
+        torch.cuda.synchronize()
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b0.record()
+        eng16.decode_static(b16, PROMPT)
+        b1.record()
+        torch.cuda.synchronize()
+        bms = b0.elapsed_time(b1)
+        n_cmp = min(K, T - PROMPT)
+        same = (b16.cpu()[:, PROMPT:PROMPT + n_cmp] == generated[:, PROMPT:PROMPT + n_cmp]).float().mean().item() if n_cmp else None
+        bf16 = {"value": B * (T - PROMPT) / (bms * 1e-3), "unit": "tokens/s", "ms_per_step": bms / (T - PROMPT), "steps": T - PROMPT,
+                "tokens_equal_fp32_loop_fraction": same, "device_status": eng16.device_status(),
+                "note": "optional FXF_GEMM_BF16 mode, full-contract loop; greedy tokens diverge from the fp32 path after the first near-tie, by design not the headline"}
+        eng16.close()
+
     # ---- max over ranks ----------------------------------------------------------------------
     if world > 1:
         t = torch.tensor([ms, e2e_ms, lr_ms or 0.0], device="cuda", dtype=torch.float64)
@@ -348,6 +369,7 @@ def run_ours(args):
                 "value": tokens_per_step * (T - PROMPT) / (lr_ms * 1e-3), "unit": "tokens/s", "ms_per_step": lr_ms / (T - PROMPT), "steps": T - PROMPT,
                 "tokens_equal_full_loop": lr_match,
                 "note": "opt-in fxf_decode_static_last_row: same tokens, the final Linear evaluated on 1 of 256 positions; not the headline (the graph contract's output is full logits)"},
+            "bf16_mode": bf16,
             "gpu_launches": K * (eng.launches_per_run + 2),
             "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu, "kernels": kernels,
             "device_status": status, "device_bytes": eng.device_bytes,
