@@ -70,6 +70,7 @@ SIGNATURES = {
     "fxf_decode_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_void_p]),
     "fxf_decode_static_last_row": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_void_p]),
     "fxf_engine_supports_last_row": (C.c_int, [C.c_void_p]),
+    "fxf_decode_cached": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
 }
 
 _lib = None

@@ -36,6 +36,7 @@ int decode_build_mask(const int64_t* tokens, uint8_t* mask, int B, int T, int cu
 int decode_argmax_scatter(const float* logits, int64_t* tokens, int B, int T, int64_t V, int cur, ExecCtx& ctx);
 int decode_argmax_scatter_sharded(const float* logits, int64_t* tokens, int B, int T, int64_t V, int cur, int64_t col0, int64_t ncols,
                                   void* cand_local, void* cand_all, ExecCtx& ctx);
+int decode_step_prepare(const int64_t* tokens, int64_t* ids, int64_t* pos, int B, int T, int p, ExecCtx& ctx);
 int decode_argmax_scatter_rows(const float* logits, int64_t row_stride, int64_t row_off, int64_t* tokens, int B, int T, int64_t V, int cur, ExecCtx& ctx);
 int decode_argmax_scatter_sharded_rows(const float* logits, int64_t row_stride, int64_t row_off, int64_t* tokens, int B, int T, int64_t V, int cur,
                                        int64_t col0, int64_t ncols, void* cand_local, void* cand_all, ExecCtx& ctx);
@@ -871,6 +872,36 @@ int fxf_decode_static_last_row(fxf_engine* e, int64_t* tokens_io, int initial_le
 }
 
 int fxf_engine_supports_last_row(const fxf_engine* e) { return e && e->tail_node >= 0 ? 1 : 0; }
+
+// Incremental greedy decode: `e` is a single-position step graph (inputs ids int64 [B,1], pos int64 [1], tokens int64 [B,T];
+// output logits [B,1,V]; its attention nodes are CachedMHA).  Position p = 0 .. T-2 is fed in order: the step reads
+// tokens[:, p], and from p + 1 >= initial_len on its argmax becomes tokens[:, p + 1].  No host synchronisation.
+int fxf_decode_cached(fxf_engine* e, int64_t* tokens_io, int initial_len, void* stream) {
+    FXF_CHECK(e && tokens_io, "fxf_decode_cached: NULL argument");
+    FXF_CHECK(e->input_ids.size() == 3 && e->output_ids.size() >= 1, "fxf_decode_cached: the graph must take (ids, pos, tokens) and return logits");
+    if (ensure_device(e)) return 1;
+    const FxfTensor &ids = e->reg[e->input_ids[0]], &pos = e->reg[e->input_ids[1]], &tok = e->reg[e->input_ids[2]], &logits = e->reg[e->output_ids[0]];
+    FXF_CHECK(tok.dtype == FXF_I64 && tok.rank == 2, "fxf_decode_cached: input 2 must be int64 [B,T]");
+    const int B = int(tok.shape[0]), T = int(tok.shape[1]);
+    FXF_CHECK(ids.dtype == FXF_I64 && numel(ids) == B, "fxf_decode_cached: input 0 must be int64 [B,1]");
+    FXF_CHECK(pos.dtype == FXF_I64 && numel(pos) == 1, "fxf_decode_cached: input 1 must be one int64");
+    FXF_CHECK(logits.dtype == FXF_F32 && logits.rank == 3 && logits.shape[0] == B && logits.shape[1] == 1, "fxf_decode_cached: output 0 must be float32 [B,1,V]");
+    FXF_CHECK(initial_len >= 1 && initial_len <= T, "fxf_decode_cached: initial_len %d must be in [1, %d]", initial_len, T);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int64_t* slot = static_cast<int64_t*>(tok.ptr);
+    if (tokens_io != slot) FXF_CUDA(cudaMemcpyAsync(slot, tokens_io, size_t(tok.nbytes), cudaMemcpyDeviceToDevice, s));
+    ExecCtx ctx;
+    ctx.stream = s;
+    ctx.sm_count = e->ctx.sm_count;
+    const int64_t V = logits.shape[2];
+    for (int p = 0; p + 1 < T; p++) {
+        if (decode_step_prepare(slot, static_cast<int64_t*>(ids.ptr), static_cast<int64_t*>(pos.ptr), B, T, p, ctx)) return 1;
+        if (launch_forward(e, s)) return 1;
+        if (p + 1 >= initial_len && decode_argmax_scatter_rows(static_cast<const float*>(logits.ptr), V, 0, slot, B, T, V, p + 1, ctx)) return 1;
+    }
+    if (tokens_io != slot) FXF_CUDA(cudaMemcpyAsync(tokens_io, slot, size_t(tok.nbytes), cudaMemcpyDeviceToDevice, s));
+    return 0;
+}
 
 // The final Linear on row (current_len - 1) of every sequence -> [B,V] buffer, then argmax + token scatter.
 static int last_row_head(fxf_engine* e, int64_t* tokens, int cur, ExecCtx& ctx) {

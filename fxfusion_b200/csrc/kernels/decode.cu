@@ -175,6 +175,22 @@ int decode_argmax_scatter_sharded_rows(const float* logits, int64_t row_stride, 
     return 0;
 }
 
+namespace {
+// ids[b] = tokens[b, p]; *pos = p  — the inputs of one incremental decode step
+__global__ void step_prepare_kernel(const int64_t* __restrict__ tokens, int64_t* __restrict__ ids, int64_t* __restrict__ pos, int B, int T, int p) {
+    int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < B) ids[b] = tokens[int64_t(b) * T + p];
+    if (b == 0) *pos = p;
+}
+}  // namespace
+
+int decode_step_prepare(const int64_t* tokens, int64_t* ids, int64_t* pos, int B, int T, int p, ExecCtx& ctx) {
+    FXF_CHECK(p >= 0 && p < T, "decode: position %d is outside the static length %d", p, T);
+    step_prepare_kernel<<<(B + 127) / 128 > 0 ? (B + 127) / 128 : 1, 128, 0, ctx.stream>>>(tokens, ids, pos, B, T, p);
+    FXF_LAUNCHED(ctx);
+    return 0;
+}
+
 int decode_build_mask(const int64_t* tokens, uint8_t* mask, int B, int T, int cur, int64_t pad, ExecCtx& ctx) {
     FXF_CHECK(B >= 0 && T >= 0 && cur >= 0 && cur <= T, "decode: current_len %d exceeds static length %d", cur, T);
     if (B == 0 || T == 0) return 0;

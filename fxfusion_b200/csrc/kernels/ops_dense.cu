@@ -31,10 +31,14 @@ static bool use_tc(const GemmArgs& a, int gemm_mode) {
     if (gemm_mode == FXF_GEMM_FP32_SIMT) return false;
     return gemm_tc_supported(a);
 }
+static bool use_tc_few_rows(const GemmArgs& a, int gemm_mode) {
+    return gemm_mode != FXF_GEMM_FP32_SIMT && a.M < 64 && a.N * a.K >= (int64_t(1) << 20) && gemm_tc_supported(a, true);
+}
 
 int launch_gemm(const GemmArgs& a, ExecCtx& ctx) {
     if (a.M == 0 || a.N == 0) return 0;
     if (use_tc(a, ctx.gemm_mode)) return launch_gemm_tc(a, ctx);
+    if (use_tc_few_rows(a, ctx.gemm_mode)) return launch_gemm_tc(a, ctx, true);
     FXF_CHECK(ctx.gemm_mode != FXF_GEMM_TF32X3, "gemm: FXF_GEMM_TF32X3 was requested but the shape M=%lld N=%lld K=%lld (or its alignment) is not supported by the tensor-core kernel",
               (long long)a.M, (long long)a.N, (long long)a.K);
     return launch_gemm_simt(a, ctx);
@@ -72,6 +76,7 @@ struct DensePlan : NodePlan {
     int n = 0;
     // dims the kernels need again
     int64_t M = 0, heads_local = 0, head0 = 0, n_local = 0, col_off = 0;
+    size_t cache_off = 0;   // CachedMHA: byte offset of the K/V cache inside the persistent memory
     bool prepared = false;
     bool bf16_mode = false;   // set by the plan builders from the engine's GEMM mode
 
@@ -135,7 +140,12 @@ struct DensePlan : NodePlan {
 };
 inline const DensePlan* dense(const NodePlan* p) { return static_cast<const DensePlan*>(p); }
 
-bool want_tc(const PlanEnv& env, int64_t M, int64_t N, int64_t K) { return env.gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(M, N, K); }
+// Few rows against a large weight (single-position decode steps): the time is the weight read, which the tensor-core
+// kernel streams once from its pre-split copy; small weights (the 512-wide MLP) stay on the FFMA weight-streaming kernel.
+bool few_rows_tc(int64_t M, int64_t N, int64_t K) { return M >= 1 && M < 64 && N * K >= (int64_t(1) << 20) && gemm_tc_shape_ok(64, N, K); }
+bool want_tc(const PlanEnv& env, int64_t M, int64_t N, int64_t K) {
+    return env.gemm_mode != FXF_GEMM_FP32_SIMT && (gemm_tc_shape_ok(M, N, K) || few_rows_tc(M, N, K));
+}
 
 void fill_gemm(GemmArgs& g, const float* x, const Slice& w, const Slice* bias, float* out, int64_t M, int64_t ldx, int64_t ldo, bool relu) {
     g.x = x; g.w = w.ptr; g.w_hi = w.hi; g.w_lo = w.lo; g.w_is_bf16 = w.bf16;
@@ -511,6 +521,153 @@ std::unique_ptr<NodePlan> plan_cross_mha(const Registry& reg, const TensorIds& i
     g3.M = Mq; g3.N = D; g3.K = Dl;
     pl->variant += gemm_variant_name(g1, env.gemm_mode, 148) + "+" + gemm_variant_name(g2, env.gemm_mode, 148) +
                    (tc_attn ? "+attn-tcgen05-tf32x3+" : "+flash-fp32+") + gemm_variant_name(g3, env.gemm_mode, 148);
+    return pl;
+}
+
+// ---- CachedMHA (no counterpart in the reference runtime) ---------------------------------------------------
+// Self-attention of ONE new position per sequence against keys / values kept from earlier positions — the building
+// block of incremental ("KV cache") greedy decoding, which the reference lists as future work (README.md:183) and
+// replaces by recomputing the whole static buffer every step (inference.py:27-45).  Arithmetic per position is that of
+// MHA (csrc/kernels/cpu/mha.cpp:5-52) restricted to query row `pos` under the static decoder mask
+// (layers/masks.py:141-154): key j takes part iff j <= pos and tokens[b, j] != pad.
+//   inputs [x [B,1,D], tokens int64 [B,T], pos int64 [1] (0-based position of x), Wqkv[3D,D], bqkv[3D], Wo[D,D], bo[D]]
+//   ints [H, head_dim, D, 3D, pad_idx]; floats [scale_divisor]; output [B,1,D].
+// State: the node's persistent memory holds K and V of every position seen so far, [B, T, 2D]; a call first stores
+// row `pos`, then attends over rows 0..pos.  Positions must be fed in order starting at 0.
+// slices: s[0] = Wqkv, s[1] = bqkv, s[2] = Wo, s[3] = bo   (replicated under tensor parallelism)
+namespace {
+
+constexpr int kCachedAttnThreads = 128;
+
+__global__ void __launch_bounds__(kCachedAttnThreads) cached_attn_kernel(const float* __restrict__ qkv, float* __restrict__ cache, const int64_t* __restrict__ tokens,
+                                                                         const int64_t* __restrict__ pos_ptr, float* __restrict__ ctxo, int T, int D, int hd,
+                                                                         float scale_divisor, int64_t pad, int* status) {
+    __shared__ float sm_m[4], sm_l[4], sm_o[4][128];
+    const int h = blockIdx.x, b = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t pos64 = *pos_ptr;
+    if (pos64 < 0 || pos64 >= T) {   // uniform: a position outside the cache is reported, nothing is written
+        if (threadIdx.x == 0 && status) atomicCAS(status, 0, 3);
+        return;
+    }
+    const int pos = int(pos64);
+    float* rows = cache + int64_t(b) * T * 2 * D;
+    const float* qrow = qkv + int64_t(b) * 3 * D;
+    for (int t = threadIdx.x; t < hd; t += kCachedAttnThreads) {
+        rows[int64_t(pos) * 2 * D + h * hd + t] = qrow[D + h * hd + t];
+        rows[int64_t(pos) * 2 * D + D + h * hd + t] = qrow[2 * D + h * hd + t];
+    }
+    __syncthreads();
+    float q[4], o[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int d = lane + 32 * i;
+        q[i] = d < hd ? qrow[h * hd + d] : 0.f;
+        o[i] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f;
+    for (int j = warp; j <= pos; j += 4) {
+        const float* kj = rows + int64_t(j) * 2 * D + h * hd;
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int d = lane + 32 * i;
+            if (d < hd) dot = fmaf(q[i], kj[d], dot);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+        const float s = tokens[int64_t(b) * T + j] != pad ? dot / scale_divisor : -INFINITY;
+        const float m_new = fmaxf(m, s);   // a NaN score does not move the maximum; it reaches the sum below
+        const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+        const float alpha = expf(m - m_safe), pj = expf(s - m_safe);
+        l = l * alpha + pj;
+        const float* vj = kj + D;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int d = lane + 32 * i;
+            if (d < hd) o[i] = o[i] * alpha + pj * vj[d];
+        }
+        m = m_new;
+    }
+    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < 4; i++) sm_o[warp][lane + 32 * i] = o[i];
+    __syncthreads();
+    if (warp == 0) {
+        float m_all = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+        const float m_safe = m_all == -INFINITY ? 0.f : m_all;
+        float l_all = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int w = 0; w < 4; w++) {
+            const float f = expf(sm_m[w] - m_safe);   // 0 for a warp that saw no unmasked key
+            l_all += sm_l[w] * f;
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[i] += sm_o[w][lane + 32 * i] * f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int d = lane + 32 * i;
+            if (d < hd) ctxo[int64_t(b) * D + h * hd + d] = acc[i] / l_all;   // 0/0 = NaN when every key is masked
+        }
+    }
+}
+
+}  // namespace
+
+int k_cached_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const NodePlan* plan, ExecCtx& ctx) {
+    FXF_CHECK(in.size() >= 7 && out.size() >= 1, "cached_mha: expects [x, tokens, pos, qkv_weight, qkv_bias, out_weight, out_bias]");
+    FXF_CHECK(p.ints.size() >= 5 && p.floats.size() >= 1, "cached_mha: expects ints [H, head_dim, d_model, qkv_dim, pad_idx] and floats [scale_divisor]");
+    const FxfTensor &x = reg[in[0]], &tok = reg[in[1]], &pos = reg[in[2]], &wq = reg[in[3]], &bq = reg[in[4]], &wo = reg[in[5]], &bo = reg[in[6]], &o = reg[out[0]];
+    FXF_CHECK(x.rank == 3 && x.shape[1] == 1, "cached_mha: x must be [B,1,D]");
+    FXF_CHECK(tok.rank == 2 && tok.dtype == FXF_I64 && tok.shape[0] == x.shape[0], "cached_mha: tokens must be int64 [B,T]");
+    FXF_CHECK(pos.dtype == FXF_I64 && numel(pos) == 1, "cached_mha: pos must be one int64");
+    const int64_t B = x.shape[0], T = tok.shape[1], H = p.ints[0], hd = p.ints[1], D = p.ints[2], QKV = p.ints[3];
+    FXF_CHECK(H > 0 && hd > 0 && hd <= 128 && H * hd == D && QKV == 3 * D && x.shape[2] == D, "cached_mha: inconsistent head parameters");
+    FXF_CHECK(wq.rank == 2 && wq.shape[0] == QKV && wq.shape[1] == D && numel(bq) == QKV, "cached_mha: packed QKV weight/bias shape mismatch");
+    FXF_CHECK(wo.rank == 2 && wo.shape[0] == D && wo.shape[1] == D && numel(bo) == D, "cached_mha: output projection shape mismatch");
+    FXF_CHECK(numel(o) == B * D && x.dtype == FXF_F32 && o.dtype == FXF_F32, "cached_mha: output must be float32 [B,1,D]");
+    const DensePlan* pl = dense(plan);
+    FXF_CHECK(pl != nullptr && pl->n == 4 && pl->prepared && pl->persist != nullptr, "cached_mha: the node was not prepared");
+    size_t need = size_t(B) * size_t(4 * D) * sizeof(float);
+    FXF_CHECK(ctx.scratch_bytes >= need && ctx.scratch != nullptr, "cached_mha: scratch too small (%zu < %zu bytes)", ctx.scratch_bytes, need);
+    float* qkv = static_cast<float*>(ctx.scratch);
+    float* cx = qkv + B * 3 * D;
+    float* cache = reinterpret_cast<float*>(static_cast<char*>(pl->persist) + pl->cache_off);
+    if (B == 0) return 0;
+    GemmArgs g;
+    fill_gemm(g, static_cast<const float*>(x.ptr), pl->s[0], &pl->s[1], qkv, B, D, QKV, false);
+    if (launch_gemm(g, ctx)) return 1;
+    tag_launch(ctx, "cached_attention_fp32", 4.0 * double(B) * H * double(T) * hd, 4.0 * 2.0 * double(B) * T * D);
+    cached_attn_kernel<<<dim3(unsigned(H), unsigned(B)), kCachedAttnThreads, 0, ctx.stream>>>(
+        qkv, cache, static_cast<const int64_t*>(tok.ptr), static_cast<const int64_t*>(pos.ptr), cx, int(T), int(D), int(hd), p.floats[0], p.ints[4], ctx.status);
+    FXF_LAUNCHED(ctx);
+    GemmArgs g2;
+    fill_gemm(g2, cx, pl->s[2], &pl->s[3], static_cast<float*>(o.ptr), B, D, D, false);
+    return launch_gemm(g2, ctx);
+}
+
+std::unique_ptr<NodePlan> plan_cached_mha(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& env) {
+    auto pl = std::make_unique<DensePlan>();
+    pl->bf16_mode = env.gemm_mode == FXF_GEMM_BF16;
+    if (in.size() < 7 || out.size() < 1 || p.ints.size() < 5 || reg[in[0]].rank != 3 || reg[in[1]].rank != 2) return pl;
+    const int64_t B = reg[in[0]].shape[0], T = reg[in[1]].shape[1], H = p.ints[0], hd = p.ints[1], D = p.ints[2], QKV = p.ints[3];
+    if (H <= 0 || hd <= 0) return pl;
+    pl->heads_local = H;
+    Slice& s_wq = pl->add(3, QKV, D);
+    Slice& s_bq = pl->add(4, QKV, 1);
+    Slice& s_wo = pl->add(5, D, D);
+    Slice& s_bo = pl->add(6, D, 1);
+    pl->reserve(s_wq, want_tc(env, B, QKV, D));
+    pl->reserve(s_bq, false);
+    pl->reserve(s_wo, want_tc(env, B, D, D));
+    pl->reserve(s_bo, false);
+    pl->cache_off = pl->persist_bytes;
+    pl->persist_bytes += round_up(size_t(B) * size_t(T) * size_t(2 * D) * sizeof(float), 256);
+    pl->M = B;
+    pl->scratch_bytes = size_t(B) * size_t(4 * D) * sizeof(float);
+    pl->flops = 2.0 * double(B) * QKV * D + 4.0 * double(B) * H * double(T) * hd + 2.0 * double(B) * D * D;
+    pl->bytes = 4.0 * (double(QKV) * D + double(D) * D + 2.0 * double(B) * T * D);
+    GemmArgs g1;
+    g1.M = B; g1.N = QKV; g1.K = D;
+    pl->variant = std::string(env.tp_size > 1 ? "replicated " : "") + gemm_variant_name(g1, env.gemm_mode, 148) + "+cached-attn-fp32";
     return pl;
 }
 

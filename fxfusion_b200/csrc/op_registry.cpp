@@ -29,6 +29,7 @@ FXF_DECL_KERNEL(k_add_layer_norm);
 FXF_DECL_KERNEL(k_mha);
 FXF_DECL_KERNEL(k_feedforward);
 FXF_DECL_KERNEL(k_cross_mha);
+FXF_DECL_KERNEL(k_cached_mha);
 
 FXF_DECL_PLAN(plan_bandwidth);
 FXF_DECL_PLAN(plan_gather);
@@ -38,6 +39,7 @@ FXF_DECL_PLAN(plan_feedforward);
 FXF_DECL_PLAN(plan_mha);
 FXF_DECL_PLAN(plan_conv);
 FXF_DECL_PLAN(plan_cross_mha);
+FXF_DECL_PLAN(plan_cached_mha);
 
 const OpEntry& op_entry(int op_code) {
     static const OpEntry table[FXF_OP_COUNT] = {
@@ -62,6 +64,7 @@ const OpEntry& op_entry(int op_code) {
         {"MHA", k_mha, plan_mha},
         {"FeedForward", k_feedforward, plan_feedforward},
         {"CrossMHA", k_cross_mha, plan_cross_mha},   // extension, not in the reference schema
+        {"CachedMHA", k_cached_mha, plan_cached_mha},   // extension: one new position against cached keys / values
     };
     static const OpEntry none{"?", nullptr, nullptr};
     if (op_code < 0 || op_code >= FXF_OP_COUNT) return none;

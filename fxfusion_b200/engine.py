@@ -239,6 +239,15 @@ class ExecutionEngine:
         _lib.check(fn(self._h, C.c_void_p(tokens.data_ptr()), int(initial_len), int(pad_idx), self._stream()))
         return tokens
 
+    def decode_cached(self, tokens, initial_len: int):
+        """Incremental greedy decode for an engine built from `lowering.gpt_step_graph` (one position per forward,
+        keys / values cached inside the engine): completes `tokens` (int64 CUDA tensor [B,T]) in place and returns it."""
+        torch = _torch()
+        if not (isinstance(tokens, torch.Tensor) and tokens.is_cuda and tokens.dtype == torch.int64 and tokens.is_contiguous()):
+            raise RuntimeError("decode_cached: tokens must be a contiguous int64 CUDA tensor")
+        _lib.check(self._lib.fxf_decode_cached(self._h, C.c_void_p(tokens.data_ptr()), int(initial_len), self._stream()))
+        return tokens
+
     def close(self) -> None:
         if getattr(self, "_h", None) is not None and self._h.value:
             self._outputs = None

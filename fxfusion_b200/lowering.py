@@ -308,6 +308,42 @@ def gpt_graph(cfg: GPTConfig, params: Dict[str, np.ndarray], batch: int, seq: in
     return b.finish()
 
 
+def gpt_step_graph(cfg: GPTConfig, params: Dict[str, np.ndarray], batch: int, max_len: int, name: str = "gpt_step",
+                   alignment: int = 64, eps: float = 1e-5, pad_idx: int = 0) -> GraphRec:
+    """One decode position of the GPT of `gpt_graph`, for incremental ("KV cache") decoding — the reference's stated
+    future work (README.md:183); no reference lowering exists.  Same weights and the same per-position arithmetic as
+    `gpt_graph`; the attention nodes are CachedMHA (extension opcode 21), the positional row is an Embedding gather of
+    the sinusoidal table at `pos`.  Inputs: ids int64 [B,1] (the tokens at `pos`), pos int64 [1], tokens int64
+    [B,max_len] (whole buffer: the pad mask of the cached keys is read from it).  Output: logits [B,1,vocab]."""
+    B, T, D, H = batch, max_len, cfg.d_model, cfg.heads
+    hd = D // H
+    b = GraphBuilder(name, alignment)
+    ids = b.input((B, 1), wire.DT_I64)
+    pos = b.input((1,), wire.DT_I64)
+    tokens = b.input((B, T), wire.DT_I64)
+    emb = b.op("Embedding", [ids, b.const(params["emb"])], (B, 1, D))
+    mul = b.op("Mul", [emb], (B, 1, D), ints=[1], floats=[math.sqrt(D)])
+    pe = b.const(np.ascontiguousarray(params["pe"].reshape(-1, D)[:max(T, 1)]))   # rows 0..T-1 of the [1,P,D] table
+    pe_row = b.op("Embedding", [pos, pe], (1, 1, D))
+    h = b.op("Add", [mul, pe_row], (B, 1, D))
+    ln_ints = [1, D]
+    for l in range(cfg.layers):
+        ln1 = b.op("LayerNorm", [h, b.const(params[f"l{l}.ln1.w"]), b.const(params[f"l{l}.ln1.b"])], (B, 1, D), ints=ln_ints, floats=[eps])
+        consts = [b.const(params[f"l{l}.qkv.w"]), b.const(params[f"l{l}.qkv.b"]), b.const(params[f"l{l}.wo.w"]), b.const(params[f"l{l}.wo.b"])]
+        att = b.op("CachedMHA", [ln1, tokens, pos] + consts, (B, 1, D), ints=[H, hd, D, 3 * D, pad_idx], floats=[math.sqrt(hd)])
+        a1 = b.op("Add", [h, att], (B, 1, D))
+        ln2 = b.op("LayerNorm", [a1, b.const(params[f"l{l}.ln2.w"]), b.const(params[f"l{l}.ln2.b"])], (B, 1, D), ints=ln_ints, floats=[eps])
+        consts = [b.const(params[f"l{l}.ff1.w"]), b.const(params[f"l{l}.ff1.b"]), b.const(params[f"l{l}.ff2.w"]), b.const(params[f"l{l}.ff2.b"])]
+        ff = b.op("FeedForward", [ln2] + consts, (B, 1, D))
+        if l < cfg.layers - 1:
+            h = b.op("Add", [a1, ff], (B, 1, D))
+        else:
+            h = b.op("AddLayerNorm", [a1, ff, b.const(params["ln_f.w"]), b.const(params["ln_f.b"])], (B, 1, D), ints=ln_ints, floats=[eps])
+    logits = b.op("Linear", [h, b.const(params["head.w"]), b.const(params["head.b"])], (B, 1, cfg.vocab))
+    b.output(logits)
+    return b.finish()
+
+
 # --------------------------------------------------------------------------------------
 # Encoder-decoder Transformer (reference model: models/transformer.py:7-18, models/encoder.py, models/decoder.py,
 # blocks/encoder_block.py, blocks/decoder_block.py).  The reference's compile passes cannot lower it: the decoder's

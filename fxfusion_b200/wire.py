@@ -34,7 +34,7 @@ NP_DTYPES = [np.float32, np.float16, np.int32, np.int64, np.bool_]
 
 OPCODES = ("NoOp Conv2d Conv2dRelu Linear LinearRelu Add AddRelu Relu Mul MaxPool2d AvgPool2d "
            "AdaptiveAvgPool2d Transpose Size Narrow Embedding LayerNorm AddLayerNorm MHA "
-           "FeedForward CrossMHA").split()  # CrossMHA (20) is this library's extension, not in schema/graph.fbs
+           "FeedForward CrossMHA CachedMHA").split()  # CrossMHA (20) and CachedMHA (21) are this library's extensions, not in schema/graph.fbs
 OP = {name: i for i, name in enumerate(OPCODES)}
 
 

@@ -33,14 +33,18 @@ enum { FXF_F32 = 0, FXF_F16 = 1, FXF_I32 = 2, FXF_I64 = 3, FXF_BOOL = 4 };
 /* OpCode values of the graph file (schema/graph.fbs:19-40).  Values above 19 do not exist in the reference schema:
  * FXF_OP_CROSS_MHA is attention with queries from one sequence and keys/values from another (the decoder's second
  * attention of an encoder-decoder model), which the reference's QKV packing cannot lower.
- * inputs [x, memory, mask, Wq[D,D], bq[D], Wkv[2D,D], bkv[2D], Wo[D,D], bo[D]], ints [H, head_dim, D, 2D], floats [scale_divisor]. */
+ * inputs [x, memory, mask, Wq[D,D], bq[D], Wkv[2D,D], bkv[2D], Wo[D,D], bo[D]], ints [H, head_dim, D, 2D], floats [scale_divisor].
+ * FXF_OP_CACHED_MHA is self-attention of one new position per sequence against the keys/values of the positions fed before
+ * (kept in the node's persistent memory): the step of an incremental greedy decode, see fxf_decode_cached.
+ * inputs [x [B,1,D], tokens int64 [B,T], pos int64 [1], Wqkv[3D,D], bqkv[3D], Wo[D,D], bo[D]], ints [H, head_dim, D, 3D, pad_idx],
+ * floats [scale_divisor]. */
 enum {
     FXF_OP_NOOP = 0, FXF_OP_CONV2D = 1, FXF_OP_CONV2D_RELU = 2, FXF_OP_LINEAR = 3,
     FXF_OP_LINEAR_RELU = 4, FXF_OP_ADD = 5, FXF_OP_ADD_RELU = 6, FXF_OP_RELU = 7,
     FXF_OP_MUL = 8, FXF_OP_MAX_POOL2D = 9, FXF_OP_AVG_POOL2D = 10,
     FXF_OP_ADAPTIVE_AVG_POOL2D = 11, FXF_OP_TRANSPOSE = 12, FXF_OP_SIZE = 13,
     FXF_OP_NARROW = 14, FXF_OP_EMBEDDING = 15, FXF_OP_LAYER_NORM = 16,
-    FXF_OP_ADD_LAYER_NORM = 17, FXF_OP_MHA = 18, FXF_OP_FEEDFORWARD = 19, FXF_OP_CROSS_MHA = 20, FXF_OP_COUNT = 21
+    FXF_OP_ADD_LAYER_NORM = 17, FXF_OP_MHA = 18, FXF_OP_FEEDFORWARD = 19, FXF_OP_CROSS_MHA = 20, FXF_OP_CACHED_MHA = 21, FXF_OP_COUNT = 22
 };
 
 /* One registry slot.  Replaces the torch::Tensor elements of the reference TensorRegistry
@@ -193,6 +197,13 @@ FXF_API int fxf_decode_static(fxf_engine* e, int64_t* tokens_io, int initial_len
  * FFMA arithmetic.  Output 0 of the engine is NOT updated by this call; no counterpart in the reference,
  * whose loop always runs the whole graph.  fxf_engine_supports_last_row tells whether the graph qualifies. */
 FXF_API int fxf_engine_supports_last_row(const fxf_engine* e);
+/* Incremental ("KV cache") greedy decode, which the reference names as future work (README.md:183).  `e` runs a
+ * single-position step graph — inputs ids int64 [B,1], pos int64 [1], tokens int64 [B,T]; output logits [B,1,V]; attention
+ * nodes of kind FXF_OP_CACHED_MHA (fxfusion_b200.lowering.gpt_step_graph builds it from the same weights).  Positions
+ * 0 .. T-2 are fed in order; prompt positions only fill the caches, from initial_len-1 on the argmax of a step becomes the
+ * next token.  tokens_io as for fxf_decode_static.  The arithmetic per position is that of the full-recompute loop, so the
+ * tokens agree with fxf_decode_static except where two logits are tied to within rounding. */
+FXF_API int fxf_decode_cached(fxf_engine* e, int64_t* tokens_io, int initial_len, void* stream);
 FXF_API int fxf_decode_static_last_row(fxf_engine* e, int64_t* tokens_io, int initial_len, int64_t pad_idx,
                                void* stream);
 

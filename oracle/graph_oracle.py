@@ -110,6 +110,30 @@ def _cross_mha(reg, i, o, ints, floats):
     reg[o[0]].copy_(F.linear(ctx, wo, bo))
 
 
+_KV_STATE: Dict[tuple, torch.Tensor] = {}
+
+
+def _cached_mha(reg, i, o, ints, floats):
+    """One new position against cached keys / values: MHA (csrc/kernels/cpu/mha.cpp:5-52) restricted to query row `pos`
+    under the static decoder mask (layers/masks.py:141-154: key j <= pos and tokens[b, j] != pad).  The cache is kept per
+    (registry, output tensor), i.e. per node of one GraphOracle."""
+    x, tokens, pos, wqkv, bqkv, wo, bo = (reg[k] for k in i[:7])
+    H, hd, D, QKV, pad = ints[:5]
+    scale = float(np.float32(floats[0]))
+    B, T, p = x.size(0), tokens.size(1), int(pos.item())
+    cache = _KV_STATE.setdefault((id(reg), o[0]), torch.zeros(B, T, 2 * D))
+    qkv = F.linear(x, wqkv, bqkv)                      # [B,1,3D]
+    cache[:, p, :] = qkv[:, 0, D:]
+    q = qkv[:, :, 0:D].view(B, 1, H, hd).transpose(1, 2)                    # [B,H,1,hd]
+    k = cache[:, :p + 1, 0:D].reshape(B, p + 1, H, hd).transpose(1, 2)       # [B,H,p+1,hd]
+    v = cache[:, :p + 1, D:].reshape(B, p + 1, H, hd).transpose(1, 2)
+    scores = torch.matmul(q, k.transpose(-2, -1)) / scale
+    keep = (tokens[:, :p + 1] != pad).view(B, 1, 1, p + 1)
+    scores = scores.masked_fill(keep == 0, -math.inf)
+    ctx = torch.matmul(torch.softmax(scores, -1), v).transpose(1, 2).contiguous().view(B, 1, D)
+    reg[o[0]].copy_(F.linear(ctx, wo, bo))
+
+
 KERNELS: Dict[int, KernelFn] = {
     wire.OP["Conv2d"]: lambda r, i, o, a, f: _conv(r, i, o, a, f, False),
     wire.OP["Conv2dRelu"]: lambda r, i, o, a, f: _conv(r, i, o, a, f, True),
@@ -132,6 +156,7 @@ KERNELS: Dict[int, KernelFn] = {
     wire.OP["AddLayerNorm"]: _add_layer_norm,
     wire.OP["MHA"]: _mha,
     wire.OP["CrossMHA"]: _cross_mha,
+    wire.OP["CachedMHA"]: _cached_mha,
     wire.OP["FeedForward"]: lambda r, i, o, a, f: r[o[0]].copy_(
         F.linear(torch.relu(F.linear(r[i[0]], r[i[1]], r[i[2]])), r[i[3]], r[i[4]])),
 }
@@ -234,3 +259,16 @@ def decode_static(run: Callable[[torch.Tensor, torch.Tensor], torch.Tensor], tok
         buf[:, cur] = row.argmax(dim=-1)
         cur += 1
     return buf[:, :cur]
+
+
+def decode_cached(run_step: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor], tokens: torch.Tensor, max_seq_len: int) -> torch.Tensor:
+    """Greedy incremental decode with a single-position step graph: `run_step(ids [B,1], pos [1], buffer [B,T])` returns
+    logits [B,1,V] for the tokens at `pos` (the step keeps keys / values of earlier positions itself).  Positions are fed
+    in order from 0; prompt positions only fill the caches."""
+    B, initial_len = tokens.shape
+    buf = make_static_buffer(tokens, max_seq_len)
+    for p in range(max_seq_len - 1):
+        logits = run_step(buf[:, p:p + 1].contiguous(), torch.tensor([p], dtype=torch.int64), buf)
+        if p + 1 >= initial_len:
+            buf[:, p + 1] = logits[:, 0, :].argmax(dim=-1)
+    return buf

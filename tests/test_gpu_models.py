@@ -236,3 +236,40 @@ def test_bf16_mode_gpt_forward_and_decode(built_lib, tmp_path):
     eng.decode_static(dev, 40)
     assert torch.equal(dev[:, :40].cpu(), tokens) and (dev >= 0).all() and (dev < cfg.vocab).all()
     assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("precision", ["auto", "fp32_simt"])
+def test_incremental_decode_on_gpu_matches_oracle_tokens(built_lib, tmp_path, precision):
+    """fxf_decode_cached with the step graph of configuration 2 (4 layers, d_model 256, 4 heads of 64): the tokens equal
+    those of the CPU oracle's full-recompute decode (the reference contract) — 8 sequences, 40-token prompts (one with a pad
+    token inside), 24 generated tokens — and those of this engine's own full-recompute loop."""
+    from oracle.graph_oracle import decode_static
+    cfg = lowering.GPT_C2
+    params = lowering.gpt_params(cfg, 0)
+    B, T, L0 = 8, 64, 40
+    tokens = torch.from_numpy(lowering.decode_prompt(B, L0, cfg.vocab))
+    tokens[2, 17] = 0
+    buf = make_static_buffer(tokens, T)
+    full_graph = lowering.gpt_graph(cfg, params, batch=B, seq=T, name="c2_full")
+    oracle = GraphOracle(full_graph)
+    margins = []
+    want = decode_static(lambda b, m: oracle.run([b, m])[0], tokens, T, margins=margins)
+    step = _engine(lowering.gpt_step_graph(cfg, params, batch=B, max_len=T, name="c2_step"), tmp_path, precision=precision)
+    assert "CachedMHA" in step.describe()
+    dev = buf.cuda()
+    step.decode_cached(dev, L0)
+    torch.cuda.synchronize()
+    assert step.device_status() == 0
+    assert torch.equal(dev[:, :L0].cpu(), tokens)
+    if min(m.min().item() for m in margins) > 1e-4:   # no near-tie among the oracle's decisions: tokens must be identical
+        assert torch.equal(dev.cpu(), want)
+    else:
+        assert (dev.cpu() == want).float().mean().item() > 0.95
+    full = _engine(full_graph, tmp_path, precision=precision)
+    dev2 = buf.cuda()
+    full.decode_static(dev2, L0)
+    assert torch.equal(dev2.cpu(), want)
+    # a second decode on the same engine starts from position 0 again and overwrites the caches
+    dev3 = buf.cuda()
+    step.decode_cached(dev3, L0)
+    assert torch.equal(dev3, dev)

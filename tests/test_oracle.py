@@ -71,3 +71,20 @@ def test_golden_files_are_complete():
         assert (GOLDEN / f"{n}.npz").exists()
         ops_seen |= {nd.op_code for nd in wire.load(GOLDEN / f"{n}.bin").nodes}
     assert ops_seen >= set(range(1, 20)), f"golden set misses opcodes {set(range(1, 20)) - ops_seen}"
+
+
+def test_incremental_decode_equals_full_recompute():
+    """The single-position step graph (CachedMHA, extension opcode 21) decodes the same tokens as the reference-shaped
+    full-recompute graph, including a pad token inside a prompt (masked as a key from then on)."""
+    from fxfusion_b200 import lowering
+    from oracle.graph_oracle import decode_cached
+    cfg = lowering.GPTConfig(64, 4, 200, 4, 2)
+    params = lowering.gpt_params(cfg, 0, std=0.2)
+    B, T, L0 = 3, 24, 6
+    tokens = torch.from_numpy(lowering.decode_prompt(B, L0, cfg.vocab))
+    tokens[1, 3] = 0
+    full = GraphOracle(lowering.gpt_graph(cfg, params, batch=B, seq=T))
+    step = GraphOracle(lowering.gpt_step_graph(cfg, params, batch=B, max_len=T))
+    want = decode_static(lambda b, m: full.run([b, m])[0], tokens, T)
+    got = decode_cached(lambda i, p, b: step.run([i, p, b])[0], tokens, T)
+    assert torch.equal(got, want)
