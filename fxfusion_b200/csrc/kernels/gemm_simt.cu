@@ -10,6 +10,8 @@
 // tile split into 4-wide chunks so that shared-memory reads are conflict-free float4s.
 // Global->register prefetch of the next K-slab overlaps the FFMA loop (double buffering).
 // Roofline: fp32 FFMA, 148 SMs x 128 lanes x 2 flop.
+#include <algorithm>
+
 #include "../runtime.hpp"
 
 namespace fxf {
@@ -271,6 +273,170 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const float* __restric
     }
 }
 
+// Few rows against a LARGE weight (single-position decode steps: M = batch, weights of megabytes).  The time is the
+// weight read, so the work is cut into many independent pieces that each put a whole [64 x 128] weight slab (32 KB) in
+// flight at once: CTA (n-tile, k-part, m-tile) owns 32 rows x 64 columns and a range of 128-wide K slabs.  With more than
+// one k-part the partial tiles go to the GEMM workspace and the LAST CTA to finish a tile (a counter per tile) adds them
+// in part order — the sum does not depend on which CTA that is — then applies bias and ReLU.  fp32 FFMA throughout.
+constexpr int FR_BM = 32, FR_BN = 64, FR_BK = 128, FR_LD = FR_BK + 4;
+
+__global__ void __launch_bounds__(256) gemm_fewrows_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                                                           float* __restrict__ out, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldo,
+                                                           int vec_in, int relu, int k_parts, int slabs_per_part, float* __restrict__ partial, int* __restrict__ counters) {
+    extern __shared__ __align__(16) float fr_smem[];
+    float (*xs)[FR_LD] = reinterpret_cast<float (*)[FR_LD]>(fr_smem);
+    float (*ws)[FR_LD] = reinterpret_cast<float (*)[FR_LD]>(fr_smem + FR_BM * FR_LD);
+    __shared__ int is_last;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;           // thread: rows 2*ty, 2*ty+1; columns tx, tx+16, tx+32, tx+48
+    const int64_t col0 = int64_t(blockIdx.x) * FR_BN, row0 = int64_t(blockIdx.z) * FR_BM;
+    const int part = blockIdx.y;
+    const int64_t total_slabs = (K + FR_BK - 1) / FR_BK;
+    const int64_t s0 = int64_t(part) * slabs_per_part, s1 = min(s0 + slabs_per_part, total_slabs);
+    float acc[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+    auto load4 = [&](const float* base, int64_t r, int64_t rows, int64_t ld, int64_t gk) -> float4 {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < rows) {
+            const float* p = base + r * ld + gk;
+            if (vec_in && gk + 3 < K) v = *reinterpret_cast<const float4*>(p);
+            else {
+                if (gk < K) v.x = p[0];
+                if (gk + 1 < K) v.y = p[1];
+                if (gk + 2 < K) v.z = p[2];
+                if (gk + 3 < K) v.w = p[3];
+            }
+        }
+        return v;
+    };
+    float4 rw[8], rx[4];
+    auto fetch = [&](int64_t sl) {
+        const int64_t k0 = sl * FR_BK;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {          // weight slab: 64 rows x 32 float4
+            int f = tid + i * 256, r = f >> 5, c = (f & 31) * 4;
+            rw[i] = load4(w, col0 + r, N, ldw, k0 + c);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {          // activation slab: 32 rows x 32 float4
+            int f = tid + i * 256, r = f >> 5, c = (f & 31) * 4;
+            rx[i] = load4(x, row0 + r, M, ldx, k0 + c);
+        }
+    };
+    if (s0 < s1) fetch(s0);
+    for (int64_t sl = s0; sl < s1; sl++) {
+        __syncthreads();                        // the previous slab has been consumed
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            int f = tid + i * 256;
+            *reinterpret_cast<float4*>(&ws[f >> 5][(f & 31) * 4]) = rw[i];
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int f = tid + i * 256;
+            *reinterpret_cast<float4*>(&xs[f >> 5][(f & 31) * 4]) = rx[i];
+        }
+        __syncthreads();
+        if (sl + 1 < s1) fetch(sl + 1);        // the next slab's loads fly while this one is multiplied
+#pragma unroll 4
+        for (int k = 0; k < FR_BK; k += 4) {
+            const float4 a0 = *reinterpret_cast<const float4*>(&xs[2 * ty][k]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&xs[2 * ty + 1][k]);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float4 b = *reinterpret_cast<const float4*>(&ws[tx + 16 * j][k]);
+                acc[0][j] = fmaf(a0.x, b.x, acc[0][j]); acc[0][j] = fmaf(a0.y, b.y, acc[0][j]);
+                acc[0][j] = fmaf(a0.z, b.z, acc[0][j]); acc[0][j] = fmaf(a0.w, b.w, acc[0][j]);
+                acc[1][j] = fmaf(a1.x, b.x, acc[1][j]); acc[1][j] = fmaf(a1.y, b.y, acc[1][j]);
+                acc[1][j] = fmaf(a1.z, b.z, acc[1][j]); acc[1][j] = fmaf(a1.w, b.w, acc[1][j]);
+            }
+        }
+    }
+    auto finish = [&](float v, int64_t gr, int64_t gc) {
+        if (gr < M && gc < N) {
+            if (bias != nullptr) v += bias[gc];
+            if (relu) v = v > 0.f ? v : (v != v ? v : 0.f);
+            out[gr * ldo + gc] = v;
+        }
+    };
+    if (k_parts == 1) {
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) finish(acc[i][j], row0 + 2 * ty + i, col0 + tx + 16 * j);
+        return;
+    }
+    // partial tile [part][32][64] of this (m-tile, n-tile), then the last arriver reduces in part order
+    const int64_t tile = int64_t(blockIdx.z) * gridDim.x + blockIdx.x;
+    float* mine = partial + (tile * k_parts + part) * (FR_BM * FR_BN);
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) mine[(2 * ty + i) * FR_BN + tx + 16 * j] = acc[i][j];
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int done = atomicAdd(counters + tile, 1);
+        is_last = done == k_parts - 1;
+        if (is_last) counters[tile] = 0;   // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const float* all = partial + tile * k_parts * (FR_BM * FR_BN);
+    float sum[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) sum[i][j] = 0.f;
+    for (int q = 0; q < k_parts; q++) {        // part order; the eight loads of a part are independent
+        float t[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) t[i][j] = __ldcg(all + q * (FR_BM * FR_BN) + (2 * ty + i) * FR_BN + tx + 16 * j);
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) sum[i][j] += t[i][j];
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) finish(sum[i][j], row0 + 2 * ty + i, col0 + tx + 16 * j);
+}
+
+// Few rows and a weight worth splitting: enough pieces to occupy the GPU twice over.
+bool fewrows_applies(const GemmArgs& a) { return a.M <= 64 && a.N >= 64 && a.N * a.K >= (int64_t(1) << 20); }
+
+int launch_fewrows(const GemmArgs& a, ExecCtx& ctx) {
+    const int64_t n_tiles = (a.N + FR_BN - 1) / FR_BN, m_tiles = (a.M + FR_BM - 1) / FR_BM, slabs = (a.K + FR_BK - 1) / FR_BK;
+    int64_t parts = 1;
+    if (ctx.gemm_ws != nullptr && ctx.gemm_flags != nullptr && n_tiles * m_tiles <= ctx.gemm_flag_count) {
+        const int64_t want = (2 * int64_t(ctx.sm_count) + n_tiles * m_tiles - 1) / (n_tiles * m_tiles);
+        parts = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(want, slabs), 8));
+        while (parts > 1 && size_t(n_tiles * m_tiles * parts) * FR_BM * FR_BN * sizeof(float) > ctx.gemm_ws_bytes) parts--;
+    }
+    const int64_t per = (slabs + parts - 1) / parts;
+    parts = (slabs + per - 1) / per;   // no empty part
+    const int vec_in = (a.ldx % 4 == 0 && a.ldw % 4 == 0 && aligned16(a.x) && aligned16(a.w)) ? 1 : 0;
+    const size_t smem = size_t(FR_BM + FR_BN) * FR_LD * sizeof(float);
+    static bool configured[64] = {};
+    int dev = 0;
+    FXF_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        FXF_CUDA(cudaFuncSetAttribute(gemm_fewrows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    const dim3 fr_grid{unsigned(n_tiles), unsigned(parts), unsigned(m_tiles)};
+    gemm_fewrows_kernel<<<fr_grid, 256, smem, ctx.stream>>>(a.x, a.w, a.bias, a.out, a.M, a.N, a.K, a.ldx, a.ldw, a.ldo, vec_in, a.relu ? 1 : 0, int(parts), int(per),
+                                                         ctx.gemm_ws, ctx.gemm_flags);
+    FXF_LAUNCHED(ctx);
+    return 0;
+}
+
 int launch_skinny(const GemmArgs& a, ExecCtx& ctx) {
     dim3 grid(unsigned((a.N + SK_BN - 1) / SK_BN), unsigned((a.M + SK_BM - 1) / SK_BM));
     int vec_in = (a.ldx % 4 == 0 && a.ldw % 4 == 0 && aligned16(a.x) && aligned16(a.w)) ? 1 : 0;
@@ -298,7 +464,7 @@ int launch_cfg(const GemmArgs& a, ExecCtx& ctx) {
 
 }  // namespace
 
-// 0 = 128x128, 1 = 64x64, 2 = 32x32, 3 = skinny 32x8
+// 0 = 128x128, 1 = 64x64, 2 = 32x32, 3 = skinny 32x8 (or, for large weights, the K-split few-rows kernel)
 int simt_tile_choice(int64_t M, int64_t N, int sm_count) {
     if (M <= 64) return 3;
     int64_t big = ((M + 127) / 128) * ((N + 127) / 128);
@@ -312,8 +478,10 @@ int launch_gemm_simt(const GemmArgs& a, ExecCtx& ctx) {
     if (a.M == 0 || a.N == 0) return 0;
     FXF_CHECK(a.M > 0 && a.N > 0 && a.K >= 0, "gemm: negative dimension");
     static const char* names[] = {"gemm_fp32_simt128x128", "gemm_fp32_simt64x64", "gemm_fp32_simt32x32", "gemm_fp32_skinny32x8"};
-    tag_launch(ctx, names[simt_tile_choice(a.M, a.N, ctx.sm_count)], 2.0 * double(a.M) * double(a.N) * double(a.K),
+    const bool fewrows = simt_tile_choice(a.M, a.N, ctx.sm_count) == 3 && fewrows_applies(a);
+    tag_launch(ctx, fewrows ? "gemm_fp32_fewrows32x64_ksplit" : names[simt_tile_choice(a.M, a.N, ctx.sm_count)], 2.0 * double(a.M) * double(a.N) * double(a.K),
                4.0 * (double(a.M) * a.K + double(a.N) * a.K + double(a.N) + double(a.M) * a.N));
+    if (fewrows) return launch_fewrows(a, ctx);
     switch (simt_tile_choice(a.M, a.N, ctx.sm_count)) {
         case 3: return launch_skinny(a, ctx);
         case 0: return launch_cfg<128, 128, 16, 8, 8>(a, ctx);

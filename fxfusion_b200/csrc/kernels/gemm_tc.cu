@@ -781,6 +781,7 @@ int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows) {
     }();
     int bn = forced ? forced : gemm_tc_pick_bn(a.M, a.N, ctx.sm_count, ctx.gemm_ws ? a.K : 0);
     if (a.N <= 128) bn = 128;
+    if (allow_few_rows && a.M < 64 && !forced) bn = 128;   // a weight-streaming problem: more, narrower tiles keep more SMs loading
     if (a.w_is_bf16) {  // bf16 mode: one product per logical product, A converted into tensor memory
         if (bn >= 192 && a.N > 128) return launch_tc<192, 32, 6, 2, true, true>(a, ctx);
         return launch_tc<128, 32, 8, 2, true, true>(a, ctx);

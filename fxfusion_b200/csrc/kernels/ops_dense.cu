@@ -31,14 +31,10 @@ static bool use_tc(const GemmArgs& a, int gemm_mode) {
     if (gemm_mode == FXF_GEMM_FP32_SIMT) return false;
     return gemm_tc_supported(a);
 }
-static bool use_tc_few_rows(const GemmArgs& a, int gemm_mode) {
-    return gemm_mode != FXF_GEMM_FP32_SIMT && a.M < 64 && a.N * a.K >= (int64_t(1) << 20) && gemm_tc_supported(a, true);
-}
 
 int launch_gemm(const GemmArgs& a, ExecCtx& ctx) {
     if (a.M == 0 || a.N == 0) return 0;
     if (use_tc(a, ctx.gemm_mode)) return launch_gemm_tc(a, ctx);
-    if (use_tc_few_rows(a, ctx.gemm_mode)) return launch_gemm_tc(a, ctx, true);
     FXF_CHECK(ctx.gemm_mode != FXF_GEMM_TF32X3, "gemm: FXF_GEMM_TF32X3 was requested but the shape M=%lld N=%lld K=%lld (or its alignment) is not supported by the tensor-core kernel",
               (long long)a.M, (long long)a.N, (long long)a.K);
     return launch_gemm_simt(a, ctx);
@@ -140,12 +136,9 @@ struct DensePlan : NodePlan {
 };
 inline const DensePlan* dense(const NodePlan* p) { return static_cast<const DensePlan*>(p); }
 
-// Few rows against a large weight (single-position decode steps): the time is the weight read, which the tensor-core
-// kernel streams once from its pre-split copy; small weights (the 512-wide MLP) stay on the FFMA weight-streaming kernel.
-bool few_rows_tc(int64_t M, int64_t N, int64_t K) { return M >= 1 && M < 64 && N * K >= (int64_t(1) << 20) && gemm_tc_shape_ok(64, N, K); }
-bool want_tc(const PlanEnv& env, int64_t M, int64_t N, int64_t K) {
-    return env.gemm_mode != FXF_GEMM_FP32_SIMT && (gemm_tc_shape_ok(M, N, K) || few_rows_tc(M, N, K));
-}
+// M < 64 (batch-sized layers, single-position decode steps) never takes the tensor-core path: those problems are weight
+// reads, served by the fp32 FFMA few-rows kernels from the fp32 weights (half the bytes of a hi/lo pair).
+bool want_tc(const PlanEnv& env, int64_t M, int64_t N, int64_t K) { return env.gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(M, N, K); }
 
 void fill_gemm(GemmArgs& g, const float* x, const Slice& w, const Slice* bias, float* out, int64_t M, int64_t ldx, int64_t ldo, bool relu) {
     g.x = x; g.w = w.ptr; g.w_hi = w.hi; g.w_lo = w.lo; g.w_is_bf16 = w.bf16;
@@ -537,76 +530,98 @@ std::unique_ptr<NodePlan> plan_cross_mha(const Registry& reg, const TensorIds& i
 // slices: s[0] = Wqkv, s[1] = bqkv, s[2] = Wo, s[3] = bo   (replicated under tensor parallelism)
 namespace {
 
-constexpr int kCachedAttnThreads = 128;
+constexpr int kCachedAttnThreads = 256;
 
+__device__ __forceinline__ float block_reduce(float v, float* red, bool is_max) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        float o = __shfl_xor_sync(0xffffffffu, v, off);
+        v = is_max ? fmaxf(v, o) : v + o;
+    }
+    __syncthreads();   // `red` may still be read from a previous reduction
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = red[0];
+    for (int w = 1; w < kCachedAttnThreads / 32; w++) r = is_max ? fmaxf(r, red[w]) : r + red[w];
+    return r;
+}
+
+// One block per (head, sequence).  Phase 1: one key per thread (independent 16-byte loads of whole key rows keep many
+// requests in flight), scores to shared memory; phase 2: probabilities; phase 3: threads = (output dim, key residue class),
+// value rows read coalesced.  Dynamic shared memory: T scores.
 __global__ void __launch_bounds__(kCachedAttnThreads) cached_attn_kernel(const float* __restrict__ qkv, float* __restrict__ cache, const int64_t* __restrict__ tokens,
                                                                          const int64_t* __restrict__ pos_ptr, float* __restrict__ ctxo, int T, int D, int hd,
                                                                          float scale_divisor, int64_t pad, int* status) {
-    __shared__ float sm_m[4], sm_l[4], sm_o[4][128];
-    const int h = blockIdx.x, b = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    extern __shared__ float scores[];
+    __shared__ float red[kCachedAttnThreads / 32], qs[128], part_o[kCachedAttnThreads];
+    const int h = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
     const int64_t pos64 = *pos_ptr;
     if (pos64 < 0 || pos64 >= T) {   // uniform: a position outside the cache is reported, nothing is written
-        if (threadIdx.x == 0 && status) atomicCAS(status, 0, 3);
+        if (t == 0 && status) atomicCAS(status, 0, 3);
         return;
     }
-    const int pos = int(pos64);
+    const int pos = int(pos64), n_keys = pos + 1;
     float* rows = cache + int64_t(b) * T * 2 * D;
     const float* qrow = qkv + int64_t(b) * 3 * D;
-    for (int t = threadIdx.x; t < hd; t += kCachedAttnThreads) {
+    if (t < hd) {
         rows[int64_t(pos) * 2 * D + h * hd + t] = qrow[D + h * hd + t];
         rows[int64_t(pos) * 2 * D + D + h * hd + t] = qrow[2 * D + h * hd + t];
+        qs[t] = qrow[h * hd + t];
     }
     __syncthreads();
-    float q[4], o[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        int d = lane + 32 * i;
-        q[i] = d < hd ? qrow[h * hd + d] : 0.f;
-        o[i] = 0.f;
-    }
-    float m = -INFINITY, l = 0.f;
-    for (int j = warp; j <= pos; j += 4) {
+    // ---- phase 1: scores ----
+    const bool vec = (hd % 4 == 0) && (D % 4 == 0);
+    float tmax = -INFINITY;
+    for (int j = t; j < n_keys; j += kCachedAttnThreads) {
         const float* kj = rows + int64_t(j) * 2 * D + h * hd;
         float dot = 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            int d = lane + 32 * i;
-            if (d < hd) dot = fmaf(q[i], kj[d], dot);
+        if (vec) {
+            for (int d = 0; d < hd; d += 4) {
+                const float4 kv = *reinterpret_cast<const float4*>(kj + d);
+                dot = fmaf(qs[d], kv.x, dot); dot = fmaf(qs[d + 1], kv.y, dot); dot = fmaf(qs[d + 2], kv.z, dot); dot = fmaf(qs[d + 3], kv.w, dot);
+            }
+        } else {
+            for (int d = 0; d < hd; d++) dot = fmaf(qs[d], kj[d], dot);
         }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-        const float s = tokens[int64_t(b) * T + j] != pad ? dot / scale_divisor : -INFINITY;
-        const float m_new = fmaxf(m, s);   // a NaN score does not move the maximum; it reaches the sum below
-        const float m_safe = m_new == -INFINITY ? 0.f : m_new;
-        const float alpha = expf(m - m_safe), pj = expf(s - m_safe);
-        l = l * alpha + pj;
-        const float* vj = kj + D;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            int d = lane + 32 * i;
-            if (d < hd) o[i] = o[i] * alpha + pj * vj[d];
-        }
-        m = m_new;
+        const float sc = tokens[int64_t(b) * T + j] != pad ? dot / scale_divisor : -INFINITY;
+        scores[j] = sc;
+        tmax = fmaxf(tmax, sc);   // a NaN score does not move the maximum; it reaches the sum below
     }
-    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
-#pragma unroll
-    for (int i = 0; i < 4; i++) sm_o[warp][lane + 32 * i] = o[i];
+    const float m_all = block_reduce(tmax, red, true);
+    const float m_safe = m_all == -INFINITY ? 0.f : m_all;
+    // ---- phase 2: probabilities and their sum ----
+    float tsum = 0.f;
+    for (int j = t; j < n_keys; j += kCachedAttnThreads) {
+        const float pj = expf(scores[j] - m_safe);
+        scores[j] = pj;
+        tsum += pj;
+    }
+    const float l_all = block_reduce(tsum, red, false);   // its barriers also publish the probabilities
+    // ---- phase 3: context = sum_j p_j * v_j ----
+    int hd_pad = 32;
+    while (hd_pad < hd) hd_pad <<= 1;
+    const int parts = kCachedAttnThreads / hd_pad, d = t % hd_pad, part = t / hd_pad;
+    float acc = 0.f;
+    if (d < hd) {
+        const float* vcol = rows + D + h * hd + d;
+        int j = part;
+        for (; j + 3 * parts < n_keys; j += 4 * parts) {   // four independent value loads in flight
+            const float v0 = vcol[int64_t(j) * 2 * D], v1 = vcol[int64_t(j + parts) * 2 * D], v2 = vcol[int64_t(j + 2 * parts) * 2 * D],
+                        v3 = vcol[int64_t(j + 3 * parts) * 2 * D];
+            acc = fmaf(scores[j], v0, acc);
+            acc = fmaf(scores[j + parts], v1, acc);
+            acc = fmaf(scores[j + 2 * parts], v2, acc);
+            acc = fmaf(scores[j + 3 * parts], v3, acc);
+        }
+        for (; j < n_keys; j += parts) acc = fmaf(scores[j], vcol[int64_t(j) * 2 * D], acc);
+    }
+    part_o[t] = acc;
     __syncthreads();
-    if (warp == 0) {
-        float m_all = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
-        const float m_safe = m_all == -INFINITY ? 0.f : m_all;
-        float l_all = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int w = 0; w < 4; w++) {
-            const float f = expf(sm_m[w] - m_safe);   // 0 for a warp that saw no unmasked key
-            l_all += sm_l[w] * f;
-#pragma unroll
-            for (int i = 0; i < 4; i++) acc[i] += sm_o[w][lane + 32 * i] * f;
-        }
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            int d = lane + 32 * i;
-            if (d < hd) ctxo[int64_t(b) * D + h * hd + d] = acc[i] / l_all;   // 0/0 = NaN when every key is masked
-        }
+    if (t < hd) {
+        float o = 0.f;
+        for (int q = 0; q < parts; q++) o += part_o[q * hd_pad + t];
+        ctxo[int64_t(b) * D + h * hd + t] = o / l_all;   // 0/0 = NaN when every key is masked
     }
 }
 
@@ -636,7 +651,9 @@ int k_cached_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const
     fill_gemm(g, static_cast<const float*>(x.ptr), pl->s[0], &pl->s[1], qkv, B, D, QKV, false);
     if (launch_gemm(g, ctx)) return 1;
     tag_launch(ctx, "cached_attention_fp32", 4.0 * double(B) * H * double(T) * hd, 4.0 * 2.0 * double(B) * T * D);
-    cached_attn_kernel<<<dim3(unsigned(H), unsigned(B)), kCachedAttnThreads, 0, ctx.stream>>>(
+    FXF_CHECK(T * sizeof(float) <= 160 * 1024, "cached_mha: static length %lld is too long for the score buffer", (long long)T);
+    if (size_t(T) * sizeof(float) > 40 * 1024) FXF_CUDA(cudaFuncSetAttribute(cached_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(T * sizeof(float))));
+    cached_attn_kernel<<<dim3(unsigned(H), unsigned(B)), kCachedAttnThreads, size_t(T) * sizeof(float), ctx.stream>>>(
         qkv, cache, static_cast<const int64_t*>(tok.ptr), static_cast<const int64_t*>(pos.ptr), cx, int(T), int(D), int(hd), p.floats[0], p.ints[4], ctx.status);
     FXF_LAUNCHED(ctx);
     GemmArgs g2;
