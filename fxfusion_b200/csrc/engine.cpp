@@ -61,6 +61,10 @@ struct Node {
     std::unique_ptr<NodePlan> plan;
     KernelFn fn = nullptr;
     int launches = 0;
+    // epilogue fusion: this contraction also performs the residual Add / AddRelu that follows it ...
+    int fuse_res = -1, fuse_out = -1;   // tensor ids of the residual operand and of the Add's output
+    bool fuse_relu = false;
+    bool folded = false;                // ... and this Add / AddRelu node launches nothing
 };
 
 }  // namespace
@@ -118,16 +122,37 @@ struct fxf_engine {
 namespace fxf {
 namespace {
 
+// One node, with the epilogue fusion decided at build time: a folded Add launches nothing, the contraction before it gets
+// the residual and the Add's output through the context.
+int run_node(fxf_engine* e, size_t i) {
+    Node& n = e->nodes[i];
+    const int before = e->ctx.launches;
+    e->ctx.cur_node = int(i);
+    if (n.folded) {
+        n.launches = 0;
+        return 0;
+    }
+    tag_launch(e->ctx, op_entry(n.op).name, n.plan->flops, n.plan->bytes);
+    e->ctx.fuse = EpilogueFusion{};
+    if (n.fuse_out >= 0) {
+        e->ctx.fuse.residual = static_cast<const float*>(e->reg[size_t(n.fuse_res)].ptr);
+        e->ctx.fuse.out = static_cast<float*>(e->reg[size_t(n.fuse_out)].ptr);
+        e->ctx.fuse.relu = n.fuse_relu;
+    }
+    if (n.fn(e->reg, n.in, n.out, n.params, n.plan.get(), e->ctx)) return 1;
+    if (n.fuse_out >= 0) {
+        FXF_CHECK(e->ctx.fuse.consumed, "node %zu (%s): the folded residual Add was not performed by the kernel", i, op_entry(n.op).name);
+        e->ctx.fuse = EpilogueFusion{};
+    }
+    n.launches = e->ctx.launches - before;
+    return 0;
+}
+
 int run_nodes(fxf_engine* e, cudaStream_t stream, int count = -1) {
     e->ctx.stream = stream;
-    int index = 0;
-    for (auto& n : e->nodes) {
-        if (count >= 0 && index >= count) break;
-        int before = e->ctx.launches;
-        e->ctx.cur_node = index++;
-        tag_launch(e->ctx, op_entry(n.op).name, n.plan->flops, n.plan->bytes);
-        if (n.fn(e->reg, n.in, n.out, n.params, n.plan.get(), e->ctx)) return 1;
-        n.launches = e->ctx.launches - before;
+    for (size_t i = 0; i < e->nodes.size(); i++) {
+        if (count >= 0 && int(i) >= count) break;
+        if (run_node(e, i)) return 1;
     }
     return 0;
 }
@@ -304,6 +329,82 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
         }
         for (uint32_t id = 0; id < n_tensors; id++)
             if (cl[id]) set_channels_last(e->reg[id]);
+    }
+
+    // ---- epilogue fusion: a residual Add / AddRelu right after a dense contraction is folded into that contraction ------
+    // The contraction writes act(acc + bias + residual) straight into the Add's output (bit-identical to the two nodes run
+    // separately: the same two fp32 additions in the same order).  Conditions: the two nodes are adjacent; the
+    // contraction's result (through aliases) is read by nothing else and is not a graph output; shapes, dtypes and layouts
+    // agree without broadcasting; the residual exists before the contraction runs; and the Add's output does not share
+    // arena bytes with any operand the writing GEMM still reads (the planner may have given it the slot of a tensor that
+    // dies at the contraction).  FXF_FUSE_ADD=0 turns the pass off.
+    {
+        const char* fenv = std::getenv("FXF_FUSE_ADD");
+        const bool enabled = !(fenv && fenv[0] == '0');
+        auto root = [&](uint32_t id) {
+            for (int guard = 0; guard < 64 && meta[id].alias_of >= 0 && uint32_t(meta[id].alias_of) < n_tensors; guard++) id = uint32_t(meta[id].alias_of);
+            return id;
+        };
+        auto same_shape = [&](uint32_t a, uint32_t b) {
+            const FxfTensor &x = e->reg[a], &y = e->reg[b];
+            if (x.rank != y.rank) return false;
+            for (int k = 0; k < x.rank; k++)
+                if (x.shape[k] != y.shape[k]) return false;
+            return true;
+        };
+        std::vector<int> producer(n_tensors, -1), n_readers(n_tensors, 0);
+        std::vector<char> escapes(n_tensors, 0);
+        for (size_t i = 0; i < e->nodes.size(); i++) {
+            for (auto id : e->nodes[i].out) producer[root(id)] = int(i);
+            for (auto id : e->nodes[i].in) n_readers[root(id)]++;
+        }
+        for (uint32_t id = 0; id < n_tensors; id++)
+            if (meta[id].kind == kOutput) escapes[root(id)] = 1;
+        auto arena_range = [&](uint32_t id, int64_t* lo, int64_t* hi) {   // false: not in the arena (constant, input)
+            const uint32_t r = root(id);
+            if (meta[r].kind == kConstant || meta[r].kind == kInput || meta[r].offset < 0) return false;
+            *lo = meta[r].offset;
+            *hi = meta[r].offset + int64_t(e->reg[r].nbytes);
+            return true;
+        };
+        for (size_t bi = 1; enabled && bi < e->nodes.size(); bi++) {
+            Node &A = e->nodes[bi - 1], &B = e->nodes[bi];
+            if ((B.op != FXF_OP_ADD && B.op != FXF_OP_ADD_RELU) || B.in.size() != 2 || B.out.size() != 1) continue;
+            // Convolutions are left alone: their layers are bandwidth-bound with short K loops, and the residual read in the
+            // GEMM epilogue (16 KB in flight per SM) is slower than the separate AddRelu kernel (measured on ResNet-50).
+            if (A.op != FXF_OP_LINEAR && A.op != FXF_OP_FEEDFORWARD && A.op != FXF_OP_MHA && A.op != FXF_OP_CROSS_MHA) continue;
+            if (A.fuse_out >= 0 || A.out.size() != 1) continue;
+            if (B.op == FXF_OP_ADD_RELU && e->opts.tp_size > 1) continue;   // the ReLU would have to follow the all-reduce
+            if (A.op == FXF_OP_LINEAR && e->opts.tp_size > 1 && e->opts.tp_shard_output) continue;
+            const uint32_t t = root(A.out[0]);
+            const int which = root(B.in[0]) == t ? 0 : (root(B.in[1]) == t ? 1 : -1);
+            if (which < 0) continue;
+            const uint32_t r = B.in[1 - which], o = B.out[0];
+            if (root(r) == t || n_readers[t] != 1 || escapes[t]) continue;
+            const FxfTensor &ta = e->reg[A.out[0]], &tr = e->reg[r], &to = e->reg[o];
+            if (ta.dtype != FXF_F32 || tr.dtype != FXF_F32 || to.dtype != FXF_F32) continue;
+            if (!same_shape(A.out[0], r) || !same_shape(A.out[0], o)) continue;
+            if (!same_layout(ta, tr) || !same_layout(ta, to)) continue;
+            const int pr = producer[root(r)];
+            if (pr >= int(bi) - 1) continue;   // the residual must exist before the contraction runs (inputs / constants: -1)
+            int64_t olo = 0, ohi = 0;
+            if (!arena_range(o, &olo, &ohi) || meta[o].alias_of >= 0) continue;
+            bool clash = false;
+            // MHA / CrossMHA / FeedForward read their activation inputs in their first GEMM; the final GEMM, which does the
+            // writing, reads only scratch and weights.  A plain Linear reads its input while it writes.
+            if (A.op == FXF_OP_LINEAR)
+                for (auto id : A.in) {
+                    int64_t lo = 0, hi = 0;
+                    if (arena_range(id, &lo, &hi) && lo < ohi && olo < hi) clash = true;
+                }
+            int64_t rlo = 0, rhi = 0;
+            if (arena_range(r, &rlo, &rhi) && rlo < ohi && olo < rhi) clash = true;
+            if (clash) continue;
+            A.fuse_res = int(r);
+            A.fuse_out = int(o);
+            A.fuse_relu = B.op == FXF_OP_ADD_RELU;
+            B.folded = true;
+        }
     }
 
     // ---- plans (they see the final layouts) ---------------------------------------------------------
@@ -664,7 +765,10 @@ int fxf_engine_describe(const fxf_engine* e, char* out, size_t out_bytes) {
         for (auto id : n.in) os << id << " ";
         os << "] out[";
         for (auto id : n.out) os << id << "@" << (static_cast<uint8_t*>(e->reg[id].ptr) - e->base) << (is_channels_last(e->reg[id]) ? "[nhwc] " : " ");
-        os << "] launches " << n.launches << " variant " << n.plan->variant << " scratch " << n.plan->scratch_bytes << "\n";
+        os << "] launches " << n.launches << " variant " << n.plan->variant << " scratch " << n.plan->scratch_bytes;
+        if (n.fuse_out >= 0) os << " +" << (n.fuse_relu ? "AddRelu" : "Add") << "(residual " << n.fuse_res << ") -> out " << n.fuse_out;
+        if (n.folded) os << " folded into the previous node's epilogue";
+        os << "\n";
     }
     std::string s = os.str();
     size_t n = std::min(out_bytes - 1, s.size());
@@ -699,8 +803,7 @@ int fxf_engine_time_nodes(fxf_engine* e, float* ms_out, int n, void* stream) {
     FXF_CUDA(cudaEventRecord(ev[0], s));
     int rc = 0;
     for (size_t i = 0; i < e->nodes.size() && !rc; i++) {
-        Node& nd = e->nodes[i];
-        rc = nd.fn(e->reg, nd.in, nd.out, nd.params, nd.plan.get(), e->ctx);
+        rc = run_node(e, i);
         cudaEventRecord(ev[i + 1], s);
     }
     cudaStreamSynchronize(s);

@@ -286,6 +286,7 @@ int run_conv(Registry& reg, const TensorIds& in, const TensorIds& out, const Par
         g.M = n_pix; g.N = d.O; g.K = d.C;
         g.ldx = d.C; g.ldw = d.C; g.ldo = d.O;
         g.relu = relu;
+        apply_fusion(ctx, g);
         return launch_gemm(g, ctx);
     }
     if (cp && cp->igemm_tc && cp->w_hi && is_channels_last(x) && is_channels_last(o) && aligned16(x.ptr)) {
@@ -297,14 +298,25 @@ int run_conv(Registry& reg, const TensorIds& in, const TensorIds& out, const Par
         c.N = d.N; c.C = d.C; c.H = d.H; c.W = d.W; c.O = d.O; c.KH = d.KH; c.KW = d.KW; c.HO = d.HO; c.WO = d.WO;
         c.pad_h = d.ph; c.pad_w = d.pw; c.dil_h = d.dh; c.dil_w = d.dw; c.str_h = d.sh; c.str_w = d.sw;
         c.relu = relu;
+        apply_fusion(ctx, c);
         return launch_conv_tc(c, ctx);
     }
     dim3 grid(unsigned((n_pix + CBM - 1) / CBM), unsigned((d.og + CBN - 1) / CBN), unsigned(d.groups));
     tag_launch(ctx, "conv2d_igemm_fp32_simt64x64", 2.0 * double(n_pix) * d.O * d.cg * d.KH * d.KW,
                double(x.nbytes) + double(w.nbytes) + double(b.nbytes) + double(o.nbytes));
-    conv2d_igemm_kernel<<<grid, 256, 0, ctx.stream>>>(static_cast<const float*>(x.ptr), static_cast<const float*>(w.ptr), static_cast<const float*>(b.ptr),
-                                                      static_cast<float*>(o.ptr), d);
+    // a folded residual Add: the FFMA kernel writes the plain convolution into the Add's output, then act(out + residual)
+    float* dst = static_cast<float*>(o.ptr);
+    const bool fused = ctx.fuse.out != nullptr;
+    if (fused) {
+        dst = ctx.fuse.out;
+        d.relu = 0;
+    }
+    conv2d_igemm_kernel<<<grid, 256, 0, ctx.stream>>>(static_cast<const float*>(x.ptr), static_cast<const float*>(w.ptr), static_cast<const float*>(b.ptr), dst, d);
     FXF_LAUNCHED(ctx);
+    if (fused) {
+        ctx.fuse.consumed = true;
+        return launch_residual_epilogue(dst, ctx.fuse.residual, numel(o), relu || ctx.fuse.relu, ctx);
+    }
     return 0;
 }
 

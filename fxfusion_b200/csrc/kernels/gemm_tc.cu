@@ -97,6 +97,7 @@ struct ConvGeom {
 struct TcParams {
     ConvGeom cv;
     const float* bias;
+    const float* residual;   // optional, addressed like `out`
     float* out;
     int64_t M, N, K, ldo;
     int relu;
@@ -491,20 +492,35 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                             for (int i = 0; i < 8; i++) { v[i].x += w[i].x; v[i].y += w[i].y; v[i].z += w[i].z; v[i].w += w[i].w; }
                         }
                     }
+                    // row offsets once; the residual (a folded Add) is fetched as eight independent loads before any store
+                    int64_t offs[8];
+                    bool oks[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) offs[i] = out_row_offset(p, tm, row0 + i * 4 + rsub, oks[i]);
+                    if (p.residual) {
+                        float4 r4[8];
+#pragma unroll
+                        for (int i = 0; i < 8; i++)
+                            r4[i] = oks[i] ? *reinterpret_cast<const float4*>(p.residual + offs[i] + col + cq) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {   // (acc + bias) + residual, the order of the two separate nodes
+                            v[i].x = (v[i].x + b4.x) + r4[i].x; v[i].y = (v[i].y + b4.y) + r4[i].y;
+                            v[i].z = (v[i].z + b4.z) + r4[i].z; v[i].w = (v[i].w + b4.w) + r4[i].w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; i++) { v[i].x += b4.x; v[i].y += b4.y; v[i].z += b4.z; v[i].w += b4.w; }
+                    }
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
-                        int rr = i * 4 + rsub;
                         float4 o = v[i];
-                        o.x += b4.x; o.y += b4.y; o.z += b4.z; o.w += b4.w;
                         if (p.relu) {
                             o.x = o.x > 0.f ? o.x : (o.x != o.x ? o.x : 0.f);
                             o.y = o.y > 0.f ? o.y : (o.y != o.y ? o.y : 0.f);
                             o.z = o.z > 0.f ? o.z : (o.z != o.z ? o.z : 0.f);
                             o.w = o.w > 0.f ? o.w : (o.w != o.w ? o.w : 0.f);
                         }
-                        bool row_ok;
-                        int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
-                        if (row_ok) *reinterpret_cast<float4*>(p.out + off + col + cq) = o;
+                        if (oks[i]) *reinterpret_cast<float4*>(p.out + offs[i] + col + cq) = o;
                     }
                 } else if (!adds_partials) {
                     // one row per instruction, lanes on consecutive columns
@@ -513,9 +529,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
 #pragma unroll 4
                     for (int rr = 0; rr < 32; rr++) {
                         float v = stage[rr * kStagePad + lane] + b;
-                        if (p.relu) v = v > 0.f ? v : (v != v ? v : 0.f);
                         bool row_ok;
                         int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
+                        if (p.residual && col_ok && row_ok) v += p.residual[off + col + lane];
+                        if (p.relu) v = v > 0.f ? v : (v != v ? v : 0.f);
                         if (col_ok && row_ok) p.out[off + col + lane] = v;
                     }
                 } else {
@@ -525,9 +542,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         float v = stage[rr * kStagePad + lane];
                         for (int pp = 1; pp < un.nparts; pp++) v += __ldcg(ws_mine + size_t(pp) * size_t(BM * BN) + (row0 + rr) * BN + c * 32 + lane);
                         v += b;
-                        if (p.relu) v = v > 0.f ? v : (v != v ? v : 0.f);
                         bool row_ok;
                         int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
+                        if (p.residual && col_ok && row_ok) v += p.residual[off + col + lane];
+                        if (p.relu) v = v > 0.f ? v : (v != v ? v : 0.f);
                         if (col_ok && row_ok) p.out[off + col + lane] = v;
                     }
                 }
@@ -674,9 +692,9 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
         p.cv.c_slabs = cv->C / BK;
         p.cv.a_bytes = uint32_t(geom->BW * geom->BH * geom->BNI * BK) * 4u;
     }
-    p.bias = a.bias; p.out = a.out; p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo;
+    p.bias = a.bias; p.residual = cv ? cv->residual : a.residual; p.out = a.out; p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo;
     p.relu = a.relu ? 1 : 0;
-    p.vec_out = (a.ldo % 4 == 0 && aligned16(a.out) && (a.bias == nullptr || aligned16(a.bias))) ? 1 : 0;
+    p.vec_out = (a.ldo % 4 == 0 && aligned16(a.out) && (a.bias == nullptr || aligned16(a.bias)) && (p.residual == nullptr || aligned16(p.residual))) ? 1 : 0;
     p.tiles_m = int((a.M + BM - 1) / BM);
     p.tiles_n = int((a.N + BN - 1) / BN);
     // walk tiles so that the operand that does not fit in L2 is the one reused by concurrent CTAs

@@ -32,9 +32,38 @@ static bool use_tc(const GemmArgs& a, int gemm_mode) {
     return gemm_tc_supported(a);
 }
 
+namespace {
+__global__ void __launch_bounds__(256) residual_epilogue_kernel(float* __restrict__ out, const float* __restrict__ res, int64_t n, int relu) {
+    int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float v = out[i] + res[i];
+        if (relu) v = v > 0.f ? v : (v != v ? v : 0.f);
+        out[i] = v;
+    }
+}
+}  // namespace
+
+int launch_residual_epilogue(float* out, const float* residual, int64_t n, bool relu, ExecCtx& ctx) {
+    if (n == 0) return 0;
+    int64_t blocks = (n + 255) / 256, cap = int64_t(ctx.sm_count) * 8;
+    tag_launch(ctx, "residual_epilogue", double(n), 12.0 * double(n));
+    residual_epilogue_kernel<<<int(blocks < cap ? blocks : cap), 256, 0, ctx.stream>>>(out, residual, n, relu ? 1 : 0);
+    FXF_LAUNCHED(ctx);
+    return 0;
+}
+
 int launch_gemm(const GemmArgs& a, ExecCtx& ctx) {
     if (a.M == 0 || a.N == 0) return 0;
     if (use_tc(a, ctx.gemm_mode)) return launch_gemm_tc(a, ctx);
+    if (a.residual != nullptr) {
+        // the FFMA kernels have no residual epilogue: plain GEMM, then act(out + residual) in place (dense rows only)
+        FXF_CHECK(a.ldo == a.N, "gemm: a fused residual needs a dense output on the fp32 FFMA path");
+        GemmArgs plain = a;
+        plain.residual = nullptr;
+        plain.relu = false;
+        if (launch_gemm(plain, ctx)) return 1;
+        return launch_residual_epilogue(a.out, a.residual, a.M * a.N, a.relu, ctx);
+    }
     FXF_CHECK(ctx.gemm_mode != FXF_GEMM_TF32X3, "gemm: FXF_GEMM_TF32X3 was requested but the shape M=%lld N=%lld K=%lld (or its alignment) is not supported by the tensor-core kernel",
               (long long)a.M, (long long)a.N, (long long)a.K);
     return launch_gemm_simt(a, ctx);
@@ -168,6 +197,7 @@ int run_linear(Registry& reg, const TensorIds& in, const TensorIds& out, bool re
     FXF_CHECK(pl != nullptr && pl->n == 2 && pl->prepared, "%s: the node was not prepared", who);
     GemmArgs g;
     fill_gemm(g, static_cast<const float*>(x.ptr), pl->s[0], &pl->s[1], static_cast<float*>(o.ptr) + pl->col_off, M, K, N, relu);
+    if (pl->col_off == 0 && pl->s[0].rows() == N) apply_fusion(ctx, g);   // never with a column-sharded output
     return launch_gemm(g, ctx);
 }
 
@@ -242,8 +272,9 @@ int k_feedforward(Registry& reg, const TensorIds& in, const TensorIds& out, cons
     fill_gemm(g1, static_cast<const float*>(x.ptr), pl->s[0], &pl->s[1], hidden, M, K, Fl, true);
     if (launch_gemm(g1, ctx)) return 1;
     fill_gemm(g2, hidden, pl->s[2], &pl->s[3], static_cast<float*>(o.ptr), M, Fl, P, false);
+    apply_fusion(ctx, g2);
     if (launch_gemm(g2, ctx)) return 1;
-    return tp_all_reduce_sum(static_cast<float*>(o.ptr), M * P, ctx);
+    return tp_all_reduce_sum(g2.out, M * P, ctx);
 }
 
 std::unique_ptr<NodePlan> plan_feedforward(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const PlanEnv& env) {
@@ -335,8 +366,9 @@ int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params
 
     GemmArgs g2;
     fill_gemm(g2, cx, pl->s[2], &pl->s[3], static_cast<float*>(o.ptr), M, Dl, D, false);
+    apply_fusion(ctx, g2);
     if (launch_gemm(g2, ctx)) return 1;
-    return tp_all_reduce_sum(static_cast<float*>(o.ptr), M * D, ctx);
+    return tp_all_reduce_sum(g2.out, M * D, ctx);
 }
 
 std::unique_ptr<NodePlan> plan_mha(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& env) {
@@ -456,8 +488,9 @@ int k_cross_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const 
 
     GemmArgs g2;
     fill_gemm(g2, cx, pl->s[4], &pl->s[5], static_cast<float*>(o.ptr), Mq, Dl, D, false);
+    apply_fusion(ctx, g2);
     if (launch_gemm(g2, ctx)) return 1;
-    return tp_all_reduce_sum(static_cast<float*>(o.ptr), Mq * D, ctx);
+    return tp_all_reduce_sum(g2.out, Mq * D, ctx);
 }
 
 std::unique_ptr<NodePlan> plan_cross_mha(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& env) {

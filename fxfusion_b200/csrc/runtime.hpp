@@ -48,6 +48,15 @@ struct PeerMap {
     int grid = 0;                   // blocks of the peer all-reduce kernel (fixes the flag layout)
 };
 
+// A residual Add / AddRelu node folded into the contraction that precedes it: the owner of that node's final GEMM writes
+// act(acc + bias + residual) straight into the Add's output tensor.
+struct EpilogueFusion {
+    const float* residual = nullptr;
+    float* out = nullptr;
+    bool relu = false;
+    bool consumed = false;
+};
+
 struct ExecCtx {
     cudaStream_t stream = nullptr;
     void* scratch = nullptr;       // shared by all nodes of an engine; nodes run one at a time
@@ -59,6 +68,7 @@ struct ExecCtx {
     int tp_rank = 0, tp_size = 1;  // tensor-parallel position; tp_size > 1 needs `comm`
     void* comm = nullptr;          // fxf_comm* (NCCL communicator wrapper), owned by the caller
     const PeerMap* peers = nullptr;  // set when the ranks' allocations are mapped into each other: all-reduce over peer memory
+    EpilogueFusion fuse;             // set by the engine around a node whose following Add was folded into it
     // workspace of the tensor-core GEMM's K-split last round: partial tiles and their ready flags (zero between
     // launches).  Without it every tile is computed whole.
     float* gemm_ws = nullptr;
@@ -77,6 +87,18 @@ inline void tag_launch(ExecCtx& c, const char* name, double flops, double bytes)
     c.tag_bytes = bytes;
 }
 int trace_after_launch(ExecCtx& ctx);
+// Called by the op that owns the final GEMM of a node: redirects the output and attaches the residual of a folded Add.
+// Under tensor parallelism the partial outputs are summed afterwards, so only rank 0 adds the residual (like the bias).
+template <class Args>
+inline void apply_fusion(ExecCtx& ctx, Args& g) {
+    if (ctx.fuse.out == nullptr) return;
+    g.out = ctx.fuse.out;
+    g.residual = (ctx.tp_size <= 1 || ctx.tp_rank == 0) ? ctx.fuse.residual : nullptr;
+    g.relu = g.relu || ctx.fuse.relu;
+    ctx.fuse.consumed = true;
+}
+// out = act(out + residual) over n contiguous floats: the fallback when a GEMM without a fused epilogue ran
+int launch_residual_epilogue(float* out, const float* residual, int64_t n, bool relu, ExecCtx& ctx);
 
 struct NodePlan {
     virtual ~NodePlan() = default;
@@ -214,6 +236,7 @@ struct GemmArgs {
     const float* w_lo = nullptr;
     bool w_is_bf16 = false;   // bf16 mode: w_hi points to the weight as bf16 [N,K] (w_lo unused)
     const float* bias = nullptr;
+    const float* residual = nullptr;   // optional [M,N] with the pitch of `out`, added after the bias and before the ReLU
     float* out = nullptr;
     int64_t M = 0, N = 0, K = 0;
     int64_t ldx = 0, ldw = 0, ldo = 0;
@@ -238,6 +261,7 @@ struct ConvTcArgs {
     const float *w_hi = nullptr, *w_lo = nullptr;
     bool w_is_bf16 = false;   // bf16 mode: w_hi points to the repacked filters as bf16
     const float* bias = nullptr;
+    const float* residual = nullptr;   // optional, laid out like `out`
     float* out = nullptr;
     int N = 0, C = 0, H = 0, W = 0, O = 0, KH = 0, KW = 0, HO = 0, WO = 0;
     int pad_h = 0, pad_w = 0, dil_h = 1, dil_w = 1, str_h = 1, str_w = 1;
