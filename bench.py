@@ -387,7 +387,7 @@ def run_ours(args):
                        "layers": 12, "d_model": 768, "heads": 12, "d_ff": 3072, "vocab": 50257, "batch_per_gpu": B, "seq": T,
                        "parallelism": (f"{world} independent replica(s), no collective" if tp_size == 1 else
                                        f"tp{tp_size} x dp{dp_size}: heads, FeedForward hidden units and vocabulary sharded over {tp_size} GPUs, "
-                                       f"2 NCCL all-reduces per layer, {dp_size} replica group(s) of batch {B}"), "gemm": args.precision,
+                                       f"2 all-reduces per layer (own peer-memory kernel over NVLink, NCCL as fallback), {dp_size} replica group(s) of batch {B}"), "gemm": args.precision,
                        "l2": "inputs larger than L2 (0.65 GB weights read, 1.65 GB logits written per step)"},
             "e2e": {"value": tokens_per_step * Ke / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * T * 8 + B * T * T,
                     "d2h_bytes_per_step": B * T * 8, "steps": Ke, "tokens_equal_device_loop": e2e_match},
