@@ -39,7 +39,7 @@ B, T, PROMPT = 32, 256, 128
 METRIC = "gpt2_small_greedy_decode_tokens_per_s"
 # DRAM bytes (read + written) of the dominant kernel's launches in ONE forward, from an ncu capture of
 # this workload (profiles/decode_step_gpt2_small_b32_launch_list.md); bench.py cannot run ncu itself.
-NCU_DRAM_BYTES_PER_FORWARD = {"gemm_tf32x3_tcgen05": (6009769472, 49)}
+NCU_DRAM_BYTES_PER_FORWARD = {"gemm_tf32x3_tcgen05": (6591865088, 49)}
 CPU_BUDGET_S = 150.0  # wall-clock budget of a CPU arm; the per-step batch is sized to fit it
 
 

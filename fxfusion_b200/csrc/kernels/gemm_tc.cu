@@ -492,48 +492,68 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                             for (int i = 0; i < 8; i++) { v[i].x += w[i].x; v[i].y += w[i].y; v[i].z += w[i].z; v[i].w += w[i].w; }
                         }
                     }
-                    // row offsets once; the residual (a folded Add) is fetched as eight independent loads before any store
-                    int64_t offs[8];
-                    bool oks[8];
+                    if (p.residual == nullptr) {
 #pragma unroll
-                    for (int i = 0; i < 8; i++) offs[i] = out_row_offset(p, tm, row0 + i * 4 + rsub, oks[i]);
-                    if (p.residual) {
-                        float4 r4[8];
-#pragma unroll
-                        for (int i = 0; i < 8; i++)
-                            r4[i] = oks[i] ? *reinterpret_cast<const float4*>(p.residual + offs[i] + col + cq) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                        for (int i = 0; i < 8; i++) {   // (acc + bias) + residual, the order of the two separate nodes
-                            v[i].x = (v[i].x + b4.x) + r4[i].x; v[i].y = (v[i].y + b4.y) + r4[i].y;
-                            v[i].z = (v[i].z + b4.z) + r4[i].z; v[i].w = (v[i].w + b4.w) + r4[i].w;
+                        for (int i = 0; i < 8; i++) {
+                            int rr = i * 4 + rsub;
+                            float4 o = v[i];
+                            o.x += b4.x; o.y += b4.y; o.z += b4.z; o.w += b4.w;
+                            if (p.relu) {
+                                o.x = o.x > 0.f ? o.x : (o.x != o.x ? o.x : 0.f);
+                                o.y = o.y > 0.f ? o.y : (o.y != o.y ? o.y : 0.f);
+                                o.z = o.z > 0.f ? o.z : (o.z != o.z ? o.z : 0.f);
+                                o.w = o.w > 0.f ? o.w : (o.w != o.w ? o.w : 0.f);
+                            }
+                            bool row_ok;
+                            int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
+                            if (row_ok) *reinterpret_cast<float4*>(p.out + off + col + cq) = o;
                         }
                     } else {
+                        // a folded residual Add: the eight residual loads are issued before any store, (acc + bias) + residual
+                        // is the order of the two separate nodes
+                        int64_t offs[8];
+                        bool oks[8];
+                        float4 r4[8];
 #pragma unroll
-                        for (int i = 0; i < 8; i++) { v[i].x += b4.x; v[i].y += b4.y; v[i].z += b4.z; v[i].w += b4.w; }
-                    }
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        float4 o = v[i];
-                        if (p.relu) {
-                            o.x = o.x > 0.f ? o.x : (o.x != o.x ? o.x : 0.f);
-                            o.y = o.y > 0.f ? o.y : (o.y != o.y ? o.y : 0.f);
-                            o.z = o.z > 0.f ? o.z : (o.z != o.z ? o.z : 0.f);
-                            o.w = o.w > 0.f ? o.w : (o.w != o.w ? o.w : 0.f);
+                        for (int i = 0; i < 8; i++) {
+                            offs[i] = out_row_offset(p, tm, row0 + i * 4 + rsub, oks[i]);
+                            r4[i] = oks[i] ? *reinterpret_cast<const float4*>(p.residual + offs[i] + col + cq) : make_float4(0.f, 0.f, 0.f, 0.f);
                         }
-                        if (oks[i]) *reinterpret_cast<float4*>(p.out + offs[i] + col + cq) = o;
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            float4 o = v[i];
+                            o.x = (o.x + b4.x) + r4[i].x; o.y = (o.y + b4.y) + r4[i].y; o.z = (o.z + b4.z) + r4[i].z; o.w = (o.w + b4.w) + r4[i].w;
+                            if (p.relu) {
+                                o.x = o.x > 0.f ? o.x : (o.x != o.x ? o.x : 0.f);
+                                o.y = o.y > 0.f ? o.y : (o.y != o.y ? o.y : 0.f);
+                                o.z = o.z > 0.f ? o.z : (o.z != o.z ? o.z : 0.f);
+                                o.w = o.w > 0.f ? o.w : (o.w != o.w ? o.w : 0.f);
+                            }
+                            if (oks[i]) *reinterpret_cast<float4*>(p.out + offs[i] + col + cq) = o;
+                        }
                     }
                 } else if (!adds_partials) {
                     // one row per instruction, lanes on consecutive columns
                     const bool col_ok = col + lane < p.N;
                     const float b = (p.bias && col_ok) ? __ldg(p.bias + col + lane) : 0.f;
+                    if (p.residual == nullptr) {   // kept free of loads: the stores of consecutive rows pipeline
 #pragma unroll 4
-                    for (int rr = 0; rr < 32; rr++) {
-                        float v = stage[rr * kStagePad + lane] + b;
-                        bool row_ok;
-                        int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
-                        if (p.residual && col_ok && row_ok) v += p.residual[off + col + lane];
-                        if (p.relu) v = v > 0.f ? v : (v != v ? v : 0.f);
-                        if (col_ok && row_ok) p.out[off + col + lane] = v;
+                        for (int rr = 0; rr < 32; rr++) {
+                            float v = stage[rr * kStagePad + lane] + b;
+                            if (p.relu) v = v > 0.f ? v : (v != v ? v : 0.f);
+                            bool row_ok;
+                            int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
+                            if (col_ok && row_ok) p.out[off + col + lane] = v;
+                        }
+                    } else {
+                        for (int rr = 0; rr < 32; rr++) {
+                            float v = stage[rr * kStagePad + lane] + b;
+                            bool row_ok;
+                            int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
+                            if (col_ok && row_ok) v += p.residual[off + col + lane];
+                            if (p.relu) v = v > 0.f ? v : (v != v ? v : 0.f);
+                            if (col_ok && row_ok) p.out[off + col + lane] = v;
+                        }
                     }
                 } else {
                     const bool col_ok = col + lane < p.N;
