@@ -213,18 +213,83 @@ __global__ void __launch_bounds__(256) global_avg_pool_kernel(const float* __res
     }
 }
 
+// ---- stem convolutions (few input channels, stride 2) as a stride-1 convolution over a space-to-depth copy ----------
+// A k x k stride-2 convolution over C <= 4 channels cannot feed the tensor-core path (16-channel K slabs).  Rearranging
+// the zero-padded input P into S[n, Y, X, (ry*2 + rx)*C + c] = P[n, c, 2Y + ry, 2X + rx] (16 channels, the unused ones
+// zero) turns it into a stride-1, unpadded ceil(k/2) x ceil(k/2) convolution over 16 channels with the filters
+// rearranged the same way (taps beyond k are zero): out[oy, ox] = sum_{qy,qx,ch} S[oy+qy, ox+qx, ch] * W'[o, qy, qx, ch].
+__global__ void __launch_bounds__(256) space_to_depth16_kernel(const float* __restrict__ x, float4* __restrict__ s, int64_t N, int C, int H, int W, int Hs, int Ws,
+                                                               int ph, int pw, Strides4 xs) {
+    const int64_t total = N * Hs * Ws * 4, stride = int64_t(gridDim.x) * blockDim.x;   // one float4 = 4 of the 16 channels
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int g = int(i & 3);
+        int64_t t = i >> 2;
+        const int X = int(t % Ws); t /= Ws;
+        const int Y = int(t % Hs);
+        const int64_t n = t / Hs;
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int ch = g * 4 + j, r = ch / C, c = ch - r * C;   // r = ry*2 + rx
+            float val = 0.f;
+            if (r < 4) {
+                const int iy = 2 * Y + (r >> 1) - ph, ix = 2 * X + (r & 1) - pw;
+                if (iy >= 0 && iy < H && ix >= 0 && ix < W) val = x[n * xs.n + int64_t(c) * xs.c + int64_t(iy) * xs.h + int64_t(ix) * xs.w];
+            }
+            v[j] = val;
+        }
+        s[i] = make_float4(v[0], v[1], v[2], v[3]);
+    }
+}
+
+// filters OIHW [O, C, KH, KW] -> [O, KH2, KW2, 16] in the space-to-depth channel order, split into TF32 hi / lo
+__global__ void __launch_bounds__(256) conv_weight_s2d_split_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo, int O, int C, int KH,
+                                                                    int KW, int KH2, int KW2) {
+    const int64_t total = int64_t(O) * KH2 * KW2 * 16, stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int ch = int(i & 15);
+        int64_t t = i >> 4;
+        const int qx = int(t % KW2); t /= KW2;
+        const int qy = int(t % KH2);
+        const int o = int(t / KH2);
+        const int r = ch / C, c = ch - r * C;
+        float val = 0.f;
+        if (r < 4) {
+            const int ky = 2 * qy + (r >> 1), kx = 2 * qx + (r & 1);
+            if (ky < KH && kx < KW) val = w[((int64_t(o) * C + c) * KH + ky) * KW + kx];
+        }
+        const float h = __uint_as_float(__float_as_uint(val) & 0xffffe000u);   // what a TF32 MMA sees of an fp32 operand
+        uint32_t lbits;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lbits) : "f"(val - h));
+        hi[i] = val;    // the MMA truncates it itself
+        lo[i] = __uint_as_float(lbits);
+    }
+}
+
 // ---- host side ----------------------------------------------------------------------------------------
 struct ConvPlan : NodePlan {
     bool gemm_1x1 = false;          // planned for the tensor-core GEMM (still needs channels-last tensors at run time)
     bool bf16 = false;              // bf16 mode: one bf16 copy of the weights instead of the TF32 hi/lo pair
     bool igemm_tc = false;          // k x k or strided 1x1, stride <= 2: planned for the tensor-core implicit GEMM (same run-time condition)
+    bool s2d_tc = false;            // <= 4 input channels, stride 2: space-to-depth copy, then a stride-1 tensor-core convolution
+    int Hs = 0, Ws = 0, KH2 = 0, KW2 = 0;
     int64_t w_elems = 0;
     const float *w_hi = nullptr, *w_lo = nullptr;
     int prepare(Registry& reg, const TensorIds& in, const TensorIds&, const Params&, ExecCtx& ctx) override {
-        if (!gemm_1x1 && !igemm_tc) return 0;
+        if (!gemm_1x1 && !igemm_tc && !s2d_tc) return 0;
         FXF_CHECK(persist != nullptr, "conv plan: persistent memory was not assigned");
         float* h = static_cast<float*>(persist);
         const FxfTensor& w = reg[in[1]];
+        if (s2d_tc) {
+            const int64_t blocks = (w_elems + 255) / 256, cap = int64_t(ctx.sm_count) * 8;
+            tag_launch(ctx, "conv_weight_s2d_split", 0, 12.0 * double(w_elems));
+            conv_weight_s2d_split_kernel<<<int(blocks < cap ? blocks : cap), 256, 0, ctx.stream>>>(static_cast<const float*>(w.ptr), h, h + w_elems, int(w.shape[0]),
+                                                                                                   int(w.shape[1]), int(w.shape[2]), int(w.shape[3]), KH2, KW2);
+            FXF_LAUNCHED(ctx);
+            w_hi = h;
+            w_lo = h + w_elems;
+            return 0;
+        }
         if (bf16) {
             if (igemm_tc) {
                 if (launch_conv_weight_bf16(static_cast<const float*>(w.ptr), h, int(w.shape[0]), int(w.shape[1]), int(w.shape[2]), int(w.shape[3]), ctx)) return 1;
@@ -266,6 +331,11 @@ int conv_desc(const FxfTensor& x, const FxfTensor& w, const FxfTensor& b, const 
     return 0;
 }
 
+inline int pool_grid(int64_t total, const ExecCtx& ctx) {
+    int64_t blocks = (total + 255) / 256, cap = int64_t(ctx.sm_count) * 8;
+    return int(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
+}
+
 int run_conv(Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, bool relu, const NodePlan* plan, ExecCtx& ctx, const char* who) {
     FXF_CHECK(in.size() >= 3 && out.size() >= 1 && p.ints.size() >= 7, "%s: expects [x, weight, bias] and 7 int params", who);
     const FxfTensor &x = reg[in[0]], &w = reg[in[1]], &b = reg[in[2]], &o = reg[out[0]];
@@ -288,6 +358,26 @@ int run_conv(Registry& reg, const TensorIds& in, const TensorIds& out, const Par
         g.relu = relu;
         apply_fusion(ctx, g);
         return launch_gemm(g, ctx);
+    }
+    if (cp && cp->s2d_tc && cp->w_hi && is_channels_last(o) && ctx.scratch != nullptr &&
+        ctx.scratch_bytes >= size_t(d.N) * size_t(cp->Hs) * size_t(cp->Ws) * 16 * sizeof(float)) {
+        float* sbuf = static_cast<float*>(ctx.scratch);
+        const int64_t total4 = int64_t(d.N) * cp->Hs * cp->Ws * 4;
+        tag_launch(ctx, "space_to_depth16", 0, double(x.nbytes) + 16.0 * double(total4));
+        space_to_depth16_kernel<<<pool_grid(total4, ctx), 256, 0, ctx.stream>>>(static_cast<const float*>(x.ptr), reinterpret_cast<float4*>(sbuf), d.N, d.C, d.H, d.W,
+                                                                                cp->Hs, cp->Ws, d.ph, d.pw, d.xs);
+        FXF_LAUNCHED(ctx);
+        ConvTcArgs c;
+        c.x = sbuf;
+        c.w_hi = cp->w_hi; c.w_lo = cp->w_lo;
+        c.bias = static_cast<const float*>(b.ptr);
+        c.out = static_cast<float*>(o.ptr);
+        c.N = d.N; c.C = 16; c.H = cp->Hs; c.W = cp->Ws; c.O = d.O; c.KH = cp->KH2; c.KW = cp->KW2; c.HO = d.HO; c.WO = d.WO;
+        c.pad_h = 0; c.pad_w = 0; c.dil_h = 1; c.dil_w = 1; c.str_h = 1; c.str_w = 1;
+        c.relu = relu;
+        apply_fusion(ctx, c);
+        tag_launch(ctx, "conv2d_s2d_igemm_tf32x3_tcgen05", 2.0 * double(n_pix) * d.O * d.C * d.KH * d.KW, double(x.nbytes) + double(w.nbytes) + double(o.nbytes));
+        return launch_conv_tc(c, ctx);
     }
     if (cp && cp->igemm_tc && cp->w_hi && is_channels_last(x) && is_channels_last(o) && aligned16(x.ptr)) {
         ConvTcArgs c;
@@ -334,10 +424,7 @@ int pool_desc(const FxfTensor& x, const FxfTensor& o, PoolDesc* d, const char* w
     return 0;
 }
 
-inline int pool_grid(int64_t total, const ExecCtx& ctx) {
-    int64_t blocks = (total + 255) / 256, cap = int64_t(ctx.sm_count) * 8;
-    return int(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
-}
+
 
 }  // namespace
 
@@ -417,6 +504,20 @@ std::unique_ptr<NodePlan> plan_conv(const Registry& reg, const TensorIds& in, co
             pl->bf16 = env.gemm_mode == FXF_GEMM_BF16 && C % 32 == 0;
             pl->persist_bytes = round_up(size_t(2) * size_t(pl->w_elems) * sizeof(float), 256);
             pl->variant = pl->bf16 ? "tcgen05-bf16 implicit GEMM when channels-last, else igemm-simt64x64" : "tcgen05-tf32x3 implicit GEMM when channels-last, else igemm-simt64x64";
+        } else if (!is_1x1 && p.ints[0] == 2 && p.ints[1] == 2 && p.ints[4] == 1 && p.ints[5] == 1 && p.ints[6] == 1 && C >= 1 && C <= 4 && O >= 64 &&
+                   env.gemm_mode != FXF_GEMM_FP32_SIMT && reg[in[0]].rank == 4 && reg[in[0]].shape[1] == C && M >= 64) {
+            // stem: space-to-depth copy (16 channels) in the shared scratch, then a stride-1 tensor-core convolution
+            const FxfTensor& x = reg[in[0]];
+            pl->s2d_tc = true;
+            pl->KH2 = int((w.shape[2] + 1) / 2);
+            pl->KW2 = int((w.shape[3] + 1) / 2);
+            pl->Hs = int(o.shape[2]) + pl->KH2 - 1;   // rows the unpadded stride-1 convolution reads
+            pl->Ws = int(o.shape[3]) + pl->KW2 - 1;
+            (void)x;
+            pl->w_elems = O * pl->KH2 * pl->KW2 * 16;
+            pl->persist_bytes = round_up(size_t(2) * size_t(pl->w_elems) * sizeof(float), 256);
+            pl->scratch_bytes = size_t(o.shape[0]) * size_t(pl->Hs) * size_t(pl->Ws) * 16 * sizeof(float);
+            pl->variant = "space-to-depth + tcgen05-tf32x3 implicit GEMM when the output is channels-last, else igemm-simt64x64";
         } else {
             pl->variant = "igemm-simt64x64";
         }

@@ -318,6 +318,9 @@ def test_channels_last_tensors_are_honoured(built_lib):
     (3, 256, 56, 56, 512, 1, 1, 0, 0, 1, 1, 2),   # ResNet downsample branch: 1x1 stride 2
     (5, 32, 15, 13, 64, 3, 3, 1, 1, 1, 1, 2),     # odd extents with stride 2 (whole images per box)
     (2, 16, 30, 30, 64, 5, 5, 2, 2, 1, 1, 2),     # 5x5 stride 2
+    (2, 3, 64, 64, 64, 7, 7, 3, 3, 1, 1, 2),      # ResNet stem: 3 channels, 7x7 stride 2 -> space-to-depth + stride-1 tensor-core convolution
+    (3, 4, 33, 29, 80, 3, 5, 1, 2, 1, 1, 2),      # 4 channels, odd extents, asymmetric filter
+    (2, 1, 40, 40, 64, 4, 4, 0, 0, 1, 1, 2),      # one channel, even filter, no padding
 ])
 def test_conv_implicit_gemm_tensor_core(built_lib, N, C, H, W, O, kh, kw, ph, pw, dh, dw, st):
     """Convolution (stride 1 or 2) over channels-last tensors runs as an implicit GEMM on the tensor cores
