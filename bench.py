@@ -368,6 +368,10 @@ def run_ours(args):
                     "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": (traffic[0] / traffic[1]) if traffic and traffic[1] == top["n"] else None,
                     "algorithmic_bytes": top["bytes"] / top["n"], "peak_source": peaks["source"] + " cuBLAS bf16, sustained",
                     "launches_per_step": top["n"], "share_of_step": top["ms"] / total_ms,
+                    # fp32 results from three TF32 products: TF32 runs at half the bf16 rate, so the ceiling of this arithmetic
+                    # on the measured scale is peak / 6 (bf16 mode: the peak itself)
+                    "fp32_emulation_ceiling": None if args.precision == "bf16" else peaks["bf16_tflops_sustained"] / 6.0,
+                    "frac_of_fp32_emulation_ceiling": None if args.precision == "bf16" else achieved / (peaks["bf16_tflops_sustained"] / 6.0),
                     "note": "achieved = logical fp32 flops (2MNK, counted once) of all launches of this kernel in one forward / their summed device time"}
         kernels = {k: {"launches": v["n"], "ms": round(v["ms"], 4), "share": round(v["ms"] / total_ms, 4),
                        "tflops": round(v["flops"] / (v["ms"] * 1e-3) / 1e12, 3) if v["ms"] > 0 else None,
