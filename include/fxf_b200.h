@@ -96,8 +96,12 @@ FXF_API int fxf_engine_create(const char* graph_path, int device_ordinal, const 
                       fxf_engine** out_engine);
 /* Tensor-parallel engine (no counterpart in the reference, which is single-device).  Every rank loads the
  * same graph file; MHA nodes keep H/n heads, FeedForward nodes F/n hidden units, their partial outputs are
- * summed with one NCCL all-reduce each (on the run's stream, captured into the CUDA Graph); all other nodes
- * are replicated.  `comm` must outlive the engine.  Creation is collective: all ranks call it together. */
+ * summed with one all-reduce each (on the run's stream, captured into the CUDA Graph); all other nodes
+ * are replicated.  `comm` must outlive the engine.  Creation is collective: all ranks call it together.
+ * The all-reduce is this library's own kernel over peer memory: at creation the ranks exchange CUDA IPC handles of their
+ * engine allocations and map each other's memory (GPUs of one node with peer access); where that is not possible, or with
+ * FXF_TP_ALLREDUCE=nccl in the environment, NCCL's all-reduce is used.  Device status 121 / 122 = a peer did not reach the
+ * all-reduce within its budget (20 s for the first barrier, which absorbs host-side skew; 2 s for the second). */
 typedef struct fxf_comm fxf_comm;
 FXF_API int fxf_comm_unique_id(void* out_128_bytes);           /* rank 0; ship the 128 bytes to the others */
 FXF_API int fxf_comm_create(const void* unique_id_128_bytes, int rank, int size, int device_ordinal, fxf_comm** out);
@@ -112,6 +116,9 @@ FXF_API int fxf_engine_argmax_scatter(fxf_engine* e, int64_t* tokens, int curren
 /* Same, from bytes already in memory (the engine copies what it needs). */
 FXF_API int fxf_engine_create_from_memory(const void* bytes, size_t nbytes, int device_ordinal,
                                   const FxfEngineOptions* opts, fxf_engine** out_engine);
+/* Frees the engine.  A tensor-parallel engine whose ranks mapped each other's memory (see fxf_engine_create_tp) must be
+ * destroyed on every rank, before the communicator: the call unmaps the peers and then meets the other ranks once, so
+ * that no rank frees memory a peer still has mapped. */
 FXF_API void fxf_engine_destroy(fxf_engine* e);
 
 /* Counts and descriptors of graph inputs / outputs (memory_manager.cpp:92-111).  Input
