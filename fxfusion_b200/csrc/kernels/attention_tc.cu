@@ -47,8 +47,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// Barrier among the 256 softmax threads only (id 1; id 0 is __syncthreads).
-__device__ __forceinline__ void soft_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// Barrier between the two softmax warps that share a quarter of the query rows (ids 1..4; id 0 is __syncthreads): the row
+// statistics they exchange concern only their own 32 rows, so the four pairs need not wait for one another.
+__device__ __forceinline__ void soft_sync(int quarter) { asm volatile("bar.sync %0, 64;" ::"r"(quarter + 1) : "memory"); }
 
 // ---- V transpose -------------------------------------------------------------------------------------
 // Also records, per (batch*head, 32-key slab), whether any V element is NaN or infinite: vflags[bh * n32 + slab].
@@ -356,7 +357,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
                 tmem_wait_st();
             }
             s.exch[half][row] = tmax;
-            soft_sync();
+            soft_sync(quarter);
             const float m_new = fmaxf(m_run, fmaxf(tmax, s.exch[half ^ 1][row]));
             const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
             const float alpha = fast_exp2(m_run - m_safe);
@@ -400,10 +401,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
                 for (int j = 0; j < 32; j++) o[j] += __uint_as_float(r[j]);
                 tc_fence_before();
             }
-            soft_sync();   // exch[] is reused by the next block (and by the final sum exchange)
+            soft_sync(quarter);   // exch[] is reused by the next block (and by the final sum exchange)
         }
         s.exch[half][row] = l_run;
-        soft_sync();
+        soft_sync(quarter);
         const float l_tot = s.exch[0][row] + s.exch[1][row];
         if (alive && row_ok) {
             // 0/0 = NaN for a fully masked row, as the reference softmax gives

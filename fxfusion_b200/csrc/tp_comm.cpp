@@ -3,7 +3,10 @@
 // PyTorch, shares that copy).  The reference has no communication layer at all; collectives exist here
 // only where the tensor-parallel path has a real exchange step: one all-reduce after the attention output
 // projection, one after the second FeedForward product, and a tiny all-gather of argmax candidates when the
-// vocabulary is sharded.  NCCL calls are made on the engine's stream and are captured into its CUDA Graph.
+// vocabulary is sharded.  The two all-reduces of a layer run as this library's own kernel over peer memory
+// (kernels/allreduce_p2p.cu) once the ranks have mapped each other's engine allocations (tp_map_peers below: CUDA IPC
+// handles exchanged through NCCL); NCCL's all-reduce remains the fallback and carries the small all-gather.  Everything is
+// issued on the engine's stream and captured into its CUDA Graph.
 #include <dlfcn.h>
 
 #include <cstring>
