@@ -810,6 +810,15 @@ static bool a_from_smem(int bn) {
     return mode == 1 || (mode == 0 && bn > 192);
 }
 
+// Debug override: FXF_TC_N64=0 keeps 128-wide tiles for N <= 64.
+static bool narrow_tiles() {
+    static const bool on = [] {
+        const char* e = std::getenv("FXF_TC_N64");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows) {
     FXF_CHECK(gemm_tc_supported(a, allow_few_rows), "tensor-core GEMM called with an unsupported problem");
     // Debug override: FXF_TC_BN=256|192|128 forces the tile width.
@@ -835,7 +844,10 @@ int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows) {
     switch (bn) {
         case 256: return launch_tc<256, 16, 5, 1, true>(a, ctx);
         case 192: return launch_tc<192, 16, 4, 2, true>(a, ctx);
-        default: return launch_tc<128, 32, 4, 2, true>(a, ctx);
+        default:
+            // N <= 64 (64-channel convolutions as GEMM, narrow heads): a 64-wide tile does not multiply 64 columns of padding
+            if (a.N <= 64 && narrow_tiles()) return launch_tc<64, 32, 4, 2, true>(a, ctx);
+            return launch_tc<128, 32, 4, 2, true>(a, ctx);
     }
 }
 
@@ -922,7 +934,9 @@ int launch_conv_tc(const ConvTcArgs& c, ExecCtx& ctx) {
     switch (bn) {
         case 256: return launch_tc<256, 16, 5, 1, true>(a, ctx, &c, &g);
         case 192: return launch_tc<192, 16, 4, 2, true>(a, ctx, &c, &g);
-        default: return c.C % 32 == 0 ? launch_tc<128, 32, 4, 2, true>(a, ctx, &c, &g) : launch_tc<128, 16, 8, 2, true>(a, ctx, &c, &g);
+        default:
+            if (a.N <= 64 && narrow_tiles()) return c.C % 32 == 0 ? launch_tc<64, 32, 4, 2, true>(a, ctx, &c, &g) : launch_tc<64, 16, 8, 2, true>(a, ctx, &c, &g);
+            return c.C % 32 == 0 ? launch_tc<128, 32, 4, 2, true>(a, ctx, &c, &g) : launch_tc<128, 16, 8, 2, true>(a, ctx, &c, &g);
     }
 }
 
