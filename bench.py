@@ -296,48 +296,54 @@ def run_ours(args):
     # ---- optional bf16 mode (one GPU only): the same 128-step decode with bf16 tensor-core products --------------
     bf16 = None
     if world == 1 and not args.no_extras and args.precision != "bf16":
-        eng16 = ExecutionEngine(graph_path, f"cuda:{local}", precision="bf16")
-        b16 = start_buf.cuda()
-        eng16.decode_static(start_buf.cuda(), T - 3)
-        torch.cuda.synchronize()
-        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        b0.record()
-        eng16.decode_static(b16, PROMPT)
-        b1.record()
-        torch.cuda.synchronize()
-        bms = b0.elapsed_time(b1)
-        n_cmp = min(K, T - PROMPT)
-        same = (b16.cpu()[:, PROMPT:PROMPT + n_cmp] == generated[:, PROMPT:PROMPT + n_cmp]).float().mean().item() if n_cmp else None
-        bf16 = {"value": B * (T - PROMPT) / (bms * 1e-3), "unit": "tokens/s", "ms_per_step": bms / (T - PROMPT), "steps": T - PROMPT,
-                "tokens_equal_fp32_loop_fraction": same, "device_status": eng16.device_status(),
-                "note": "optional FXF_GEMM_BF16 mode, full-contract loop; greedy tokens diverge from the fp32 path after the first near-tie, by design not the headline"}
-        eng16.close()
+        try:   # an extra must never cost the headline line
+            eng16 = ExecutionEngine(graph_path, f"cuda:{local}", precision="bf16")
+            b16 = start_buf.cuda()
+            eng16.decode_static(start_buf.cuda(), T - 3)
+            torch.cuda.synchronize()
+            b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            b0.record()
+            eng16.decode_static(b16, PROMPT)
+            b1.record()
+            torch.cuda.synchronize()
+            bms = b0.elapsed_time(b1)
+            n_cmp = min(K, T - PROMPT)
+            same = (b16.cpu()[:, PROMPT:PROMPT + n_cmp] == generated[:, PROMPT:PROMPT + n_cmp]).float().mean().item() if n_cmp else None
+            bf16 = {"value": B * (T - PROMPT) / (bms * 1e-3), "unit": "tokens/s", "ms_per_step": bms / (T - PROMPT), "steps": T - PROMPT,
+                    "tokens_equal_fp32_loop_fraction": same, "device_status": eng16.device_status(),
+                    "note": "optional FXF_GEMM_BF16 mode, full-contract loop; greedy tokens diverge from the fp32 path after the first near-tie, by design not the headline"}
+            eng16.close()
+        except Exception as exc:  # noqa: BLE001
+            bf16 = {"error": str(exc)[:300]}
 
     # ---- opt-in incremental decode (one GPU only): single-position step graph with cached keys / values -----------
     kv = None
     if world == 1 and not args.no_extras:
-        cfg3 = lowering.GPT2_SMALL
-        step_graph = lowering.gpt_step_graph(cfg3, lowering.gpt_params(cfg3, 0), batch=B, max_len=T, name="c3_step")
-        step_path = os.path.join(tmp.name, "c3_step.bin")
-        wire.dump(step_graph, step_path)
-        del step_graph
-        engs = ExecutionEngine(step_path, f"cuda:{local}", precision=args.precision)
-        engs.decode_cached(start_buf.cuda(), PROMPT)          # warm-up: one whole decode
-        kbuf = start_buf.cuda()
-        torch.cuda.synchronize()
-        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        k0.record()
-        engs.decode_cached(kbuf, PROMPT)
-        k1.record()
-        torch.cuda.synchronize()
-        kms = k0.elapsed_time(k1)
-        n_cmp = min(K, T - PROMPT)
-        same = (kbuf.cpu()[:, PROMPT:PROMPT + n_cmp] == generated[:, PROMPT:PROMPT + n_cmp]).float().mean().item() if n_cmp else None
-        kv = {"value": B * (T - PROMPT) / (kms * 1e-3), "unit": "tokens/s", "ms_total": kms, "positions_fed": T - 1, "ms_per_position": kms / (T - 1),
-              "tokens_equal_full_loop_fraction": same, "device_status": engs.device_status(), "launches_per_position": engs.launches_per_run + 2,
-              "note": "opt-in fxf_decode_cached (the reference's stated future work): 255 single-position forwards, prompt positions included in the time; "
-                      "not the headline, whose contract is full recompute"}
-        engs.close()
+        try:
+            cfg3 = lowering.GPT2_SMALL
+            step_graph = lowering.gpt_step_graph(cfg3, lowering.gpt_params(cfg3, 0), batch=B, max_len=T, name="c3_step")
+            step_path = os.path.join(tmp.name, "c3_step.bin")
+            wire.dump(step_graph, step_path)
+            del step_graph
+            engs = ExecutionEngine(step_path, f"cuda:{local}", precision=args.precision)
+            engs.decode_cached(start_buf.cuda(), PROMPT)          # warm-up: one whole decode
+            kbuf = start_buf.cuda()
+            torch.cuda.synchronize()
+            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            k0.record()
+            engs.decode_cached(kbuf, PROMPT)
+            k1.record()
+            torch.cuda.synchronize()
+            kms = k0.elapsed_time(k1)
+            n_cmp = min(K, T - PROMPT)
+            same = (kbuf.cpu()[:, PROMPT:PROMPT + n_cmp] == generated[:, PROMPT:PROMPT + n_cmp]).float().mean().item() if n_cmp else None
+            kv = {"value": B * (T - PROMPT) / (kms * 1e-3), "unit": "tokens/s", "ms_total": kms, "positions_fed": T - 1, "ms_per_position": kms / (T - 1),
+                  "tokens_equal_full_loop_fraction": same, "device_status": engs.device_status(), "launches_per_position": engs.launches_per_run + 2,
+                  "note": "opt-in fxf_decode_cached (the reference's stated future work): 255 single-position forwards, prompt positions included in the time; "
+                          "not the headline, whose contract is full recompute"}
+            engs.close()
+        except Exception as exc:  # noqa: BLE001
+            kv = {"error": str(exc)[:300]}
 
     # ---- max over ranks ----------------------------------------------------------------------
     if world > 1:
