@@ -17,8 +17,9 @@
 //                       tiles from the transposed copy; zero fill beyond T) and all MMAs:
 //                       S = Q·K_blk^T with both operands in shared memory, O_blk = P·V_blk with P read
 //                       from TMEM.
-//       warps 4-11      (a) split every landed tile into TF32 hi (in place) and lo (twin buffer);
-//                       (b) softmax, two threads per query row, each owning 64 of the block's 128 keys
+//       warps 1-3       write the TF32 "lo" twin of every landed Q / K / V tile (the tile itself serves as "hi": the MMA
+//                       ignores the 13 low mantissa bits), so the softmax threads never wait for operands;
+//       warps 4-11      softmax, two threads per query row, each owning 64 of the block's 128 keys
 //                       and 32 of the 64 output columns: tcgen05.ld of S, scale, mask (staged through
 //                       shared memory so the global reads are coalesced), online softmax in the log2
 //                       domain (running max m, running sum l), P split into hi/lo and stored to TMEM;
@@ -37,6 +38,7 @@ using namespace sm100;
 constexpr int HD = 64, BQ = 128, BKEY = 128;
 constexpr int kAttnThreads = 384;
 constexpr int kSoftWarp0 = 4;            // warps 4..11: TMEM lane quarter = warp % 4, key half = (warp - 4) / 4
+constexpr int kSplitWarp0 = 1, kSplitWarps = 3;   // warps 1..3 split the landed Q / K / V tiles (off the softmax threads' path)
 constexpr int kMaskPitch = 144;          // bytes per staged mask row (128 + 16): 16-byte reads stay conflict-free
 constexpr float kLog2e = 1.4426950408889634f;
 enum : int { kErrAttnQ = 111, kErrAttnK = 112, kErrAttnV = 113, kErrAttnS = 114, kErrAttnP = 115, kErrAttnO = 116, kErrAttnSplit = 117 };
@@ -110,11 +112,11 @@ __device__ __forceinline__ float lo_of_truncated(float x) {
     return __uint_as_float(to_tf32(x - hi));
 }
 // The MMA reads only the upper 19 bits of an fp32 operand in shared memory, so the tile TMA wrote already is the
-// "hi" operand (x truncated to TF32); the 256 softmax threads write only the "lo" twin, for `n4` float4s.
-__device__ __forceinline__ void split_tile(const float* hi_buf, float* lo_buf, int n4, int t) {
+// "hi" operand (x truncated to TF32); the splitting threads write only the "lo" twin, for `n4` float4s.
+__device__ __forceinline__ void split_tile(const float* hi_buf, float* lo_buf, int n4, int t, int n_threads) {
     const float4* hi = reinterpret_cast<const float4*>(hi_buf);
     float4* lo = reinterpret_cast<float4*>(lo_buf);
-    for (int i = t; i < n4; i += 256) {
+    for (int i = t; i < n4; i += n_threads) {
         float4 v = hi[i], l;
         l.x = lo_of_truncated(v.x);
         l.y = lo_of_truncated(v.y);
@@ -141,9 +143,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
         mbar_init(&s.bar_q, 1);
         mbar_init(&s.bar_k, 1);
         mbar_init(&s.bar_v, 1);
-        mbar_init(&s.bar_qs, 8);    // one arrival per softmax warp
-        mbar_init(&s.bar_ks, 8);
-        mbar_init(&s.bar_vs, 8);
+        mbar_init(&s.bar_qs, kSplitWarps);    // one arrival per split warp
+        mbar_init(&s.bar_ks, kSplitWarps);
+        mbar_init(&s.bar_vs, kSplitWarps);
         mbar_init(&s.bar_s, 1);
         mbar_init(&s.bar_p, 8);
         mbar_init(&s.bar_o, 1);
@@ -252,11 +254,34 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
                 }
             }
         }
+    } else if (warp >= kSplitWarp0 && warp < kSplitWarp0 + kSplitWarps) {
+        // ---------------- operand split: the "lo" twins of Q (once) and of every landed K / V block ----------------
+        const int t = threadIdx.x - kSplitWarp0 * 32, nt = kSplitWarps * 32;
+        bool ok = n_act > 0;
+        if (ok && !mbar_wait(&s.bar_q, 0, abort_flag)) { give_up(abort_flag, p.status, kErrAttnQ); ok = false; }
+        if (ok) {
+            split_tile(s.q_hi[0], s.q_lo[0], 2 * BQ * 32 / 4, t, nt);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s.bar_qs);
+        }
+        for (int i = 0; ok && i < n_act; i++) {
+            const uint32_t par = i & 1;
+            if (!mbar_wait(&s.bar_k, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnK); break; }
+            split_tile(s.k_hi[0], s.k_lo[0], 2 * BKEY * 32 / 4, t, nt);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s.bar_ks);
+            if (!mbar_wait(&s.bar_v, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnV); break; }
+            split_tile(s.v_hi[0], s.v_lo[0], 4 * HD * 32 / 4, t, nt);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s.bar_vs);
+        }
     } else if (warp >= kSoftWarp0) {
-        // ---------------- split + softmax: two threads per query row ----------------
+        // ---------------- softmax: two threads per query row ----------------
         const int sw = warp - kSoftWarp0;          // 0..7
         const int quarter = sw & 3, half = sw >> 2;
-        const int st = threadIdx.x - kSoftWarp0 * 32;  // 0..255
         const int row = quarter * 32 + lane, qi = q0 + row;
         const uint32_t lane_base = uint32_t(quarter * 32) << 16;
         const bool row_ok = qi < T;
@@ -267,34 +292,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
         float m_run = -INFINITY, l_run = 0.f;
         bool alive = true;   // a thread that gave up keeps walking the loop so that soft_sync() stays matched
 
-        // Q split (once)
-        if (n_act > 0 && alive && !mbar_wait(&s.bar_q, 0, abort_flag)) { give_up(abort_flag, p.status, kErrAttnQ); alive = false; }
-        if (n_act > 0 && alive) {
-            split_tile(s.q_hi[0], s.q_lo[0], 2 * BQ * 32 / 4, st);
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s.bar_qs);
-        }
         unsigned int rem = need;
         for (int i = 0; i < n_act; i++) {
             const int blk = __ffs(rem) - 1;
             rem &= rem - 1;
             const uint32_t par = i & 1;
-            // ---- split K and V of this block as they land ----
-            if (alive && !mbar_wait(&s.bar_k, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnK); alive = false; }
-            if (alive) {
-                split_tile(s.k_hi[0], s.k_lo[0], 2 * BKEY * 32 / 4, st);
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&s.bar_ks);
-            }
-            if (alive && !mbar_wait(&s.bar_v, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnV); alive = false; }
-            if (alive) {
-                split_tile(s.v_hi[0], s.v_lo[0], 4 * HD * 32 / 4, st);
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&s.bar_vs);
-            }
             // ---- stage this warp's share of the mask: rows of its quarter, the 64 keys of its half ----
             const int key0 = blk * BKEY + half * 64;
             if (p.mask_vec16) {
