@@ -106,11 +106,10 @@ struct AttnTcParams {
     int* status;
 };
 
-// x - (x with its 13 low mantissa bits cleared), rounded to TF32: the part of x a TF32 MMA does not see
-__device__ __forceinline__ float lo_of_truncated(float x) {
-    const float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
-    return __uint_as_float(to_tf32(x - hi));
-}
+// x - (x with its 13 low mantissa bits cleared): the part of x a TF32 MMA does not see.  The difference is exact in fp32 and
+// is handed to the MMA as it is (which again reads its upper 19 bits: what is dropped is below 2^-20 of x), so the split
+// needs no conversion instruction.
+__device__ __forceinline__ float lo_of_truncated(float x) { return x - __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
 // The MMA reads only the upper 19 bits of an fp32 operand in shared memory, so the tile TMA wrote already is the
 // "hi" operand (x truncated to TF32); the splitting threads write only the "lo" twin, for `n4` float4s.
 __device__ __forceinline__ void split_tile(const float* hi_buf, float* lo_buf, int n4, int t, int n_threads) {
@@ -374,12 +373,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
                     tmem_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
-                        float pv = fast_exp2(__uint_as_float(r[j]) - m_safe);
+                        const float pv = fast_exp2(__uint_as_float(r[j]) - m_safe);
                         psum += pv;
-                        float ph, pl;
-                        split_tf32(pv, ph, pl);
-                        r[j] = __float_as_uint(ph);
-                        lo[j] = __float_as_uint(pl);
+                        // P_hi = pv as it is (the MMA reads only its upper 19 bits), P_lo = the 13 bits it does not see: exact, no conversion
+                        r[j] = __float_as_uint(pv);
+                        lo[j] = __float_as_uint(pv - __uint_as_float(__float_as_uint(pv) & 0xffffe000u));
                     }
                     tmem_st32(tmem + kColPhi + lane_base + col, r);
                     tmem_st32(tmem + kColPlo + lane_base + col, lo);

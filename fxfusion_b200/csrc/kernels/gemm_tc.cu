@@ -12,9 +12,11 @@
 // the kernel while the tensor core works on earlier stages, in one of two ways:
 //   A in shared memory (256-wide tiles): a TF32 MMA ignores the 13 low mantissa bits of an fp32 operand,
 //     so the tile TMA wrote already is x_hi (x truncated); four warps write only x_lo into a twin buffer.
-//   A in tensor memory (192- and 128-wide tiles): one thread per tile row reads its BK floats, splits
-//     them (x_hi rounded to nearest) and stores x_hi / x_lo with tcgen05.st; the MMAs take A from TMEM
-//     and only B (w_hi, w_lo) from shared memory.
+//   A in tensor memory (192- and 128-wide tiles): one thread per tile row reads its BK floats and stores
+//     them (= x_hi) and x_lo with tcgen05.st; the MMAs take A from TMEM and only B (w_hi, w_lo) from
+//     shared memory.
+//   Either way x_lo = x - trunc_tf32(x) exactly (13 bits), passed on without a conversion: the MMA drops
+//   its lowest 3 bits, below 2^-20 of x.
 //
 // Why two ways.  The kernel is bound by the shared-memory data pipe before the tensor pipe: with both
 // operands in shared memory, operand reads and the split pass each took ~46 % of its wavefronts.
@@ -112,11 +114,10 @@ struct TcParams {
     int* status;
 };
 
-// x - (x with its 13 low mantissa bits cleared), rounded to TF32: the part of x a TF32 MMA does not see
-__device__ __forceinline__ float lo_of_truncated(float x) {
-    const float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
-    return __uint_as_float(to_tf32(x - hi));
-}
+// x - (x with its 13 low mantissa bits cleared): the part of x a TF32 MMA does not see.  The difference is exact in fp32 and
+// is handed to the MMA as it is (which again reads its upper 19 bits: what is dropped is below 2^-20 of x), so the
+// activation split needs no conversion instruction.
+__device__ __forceinline__ float lo_of_truncated(float x) { return x - __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
 
 struct Unit {
     int tile, k0, k1, part, nparts, u;
@@ -370,12 +371,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     uint32_t hi[BK], lo[BK];
 #pragma unroll
                     for (int c = 0; c < BK / 4; c++) {
-                        float4 v = src[c ^ sw];
-                        float h, l;
-                        split_tf32(v.x, h, l); hi[4 * c + 0] = __float_as_uint(h); lo[4 * c + 0] = __float_as_uint(l);
-                        split_tf32(v.y, h, l); hi[4 * c + 1] = __float_as_uint(h); lo[4 * c + 1] = __float_as_uint(l);
-                        split_tf32(v.z, h, l); hi[4 * c + 2] = __float_as_uint(h); lo[4 * c + 2] = __float_as_uint(l);
-                        split_tf32(v.w, h, l); hi[4 * c + 3] = __float_as_uint(h); lo[4 * c + 3] = __float_as_uint(l);
+                        float4 v = src[c ^ sw];   // x_hi = x as it is (the MMA truncates), x_lo = what the truncation drops
+                        hi[4 * c + 0] = __float_as_uint(v.x); lo[4 * c + 0] = __float_as_uint(lo_of_truncated(v.x));
+                        hi[4 * c + 1] = __float_as_uint(v.y); lo[4 * c + 1] = __float_as_uint(lo_of_truncated(v.y));
+                        hi[4 * c + 2] = __float_as_uint(v.z); lo[4 * c + 2] = __float_as_uint(lo_of_truncated(v.z));
+                        hi[4 * c + 3] = __float_as_uint(v.w); lo[4 * c + 3] = __float_as_uint(lo_of_truncated(v.w));
                     }
                     const uint32_t a_col = tmem_base + lane_base + kColA + uint32_t(st * kACols);
                     tmem_st(a_col, hi);
