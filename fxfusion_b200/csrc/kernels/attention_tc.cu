@@ -345,13 +345,23 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
                     const uint32_t col = uint32_t(half * 64 + c * 32);
                     tmem_ld32(tmem + kColS + lane_base + col, r);
                     tmem_wait_ld();
+                    if (p.scale_is_pow2) {
+                        // v / 2^k * log2(e) == v * (2^-k * log2(e)) bit for bit: the first factor only shifts the exponent
+                        const float cmul = p.inv_scale * kLog2e;
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        float v = __uint_as_float(r[j]);
-                        v = p.scale_is_pow2 ? v * p.inv_scale : v / p.scale_divisor;   // identical rounding for a power of two
-                        v = ((keep[c] >> j) & 1u) ? v * kLog2e : -INFINITY;
-                        tmax = fmaxf(tmax, v);  // NaN scores do not move the max; they reach the sum below
-                        r[j] = __float_as_uint(v);
+                        for (int j = 0; j < 32; j++) {
+                            float v = ((keep[c] >> j) & 1u) ? __uint_as_float(r[j]) * cmul : -INFINITY;
+                            tmax = fmaxf(tmax, v);  // NaN scores do not move the max; they reach the sum below
+                            r[j] = __float_as_uint(v);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            float v = __uint_as_float(r[j]) / p.scale_divisor;
+                            v = ((keep[c] >> j) & 1u) ? v * kLog2e : -INFINITY;
+                            tmax = fmaxf(tmax, v);
+                            r[j] = __float_as_uint(v);
+                        }
                     }
                     tmem_st32(tmem + kColS + lane_base + col, r);
                 }
@@ -407,11 +417,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
         soft_sync(quarter);
         const float l_tot = s.exch[0][row] + s.exch[1][row];
         if (alive && row_ok) {
-            // 0/0 = NaN for a fully masked row, as the reference softmax gives
+            // one reciprocal per row instead of 32 divisions; a fully masked row has o = 0 and l = 0: 0 * inf = NaN, as the
+            // reference softmax gives
+            const float inv_l = 1.0f / l_tot;
             float* dst = p.ctx + (int64_t(b) * T + qi) * p.ld_ctx + int64_t(h) * HD + half * 32;
 #pragma unroll
             for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(dst + j) = make_float4(o[j] / l_tot, o[j + 1] / l_tot, o[j + 2] / l_tot, o[j + 3] / l_tot);
+                *reinterpret_cast<float4*>(dst + j) = make_float4(o[j] * inv_l, o[j + 1] * inv_l, o[j + 2] * inv_l, o[j + 3] * inv_l);
         }
     }
     tc_fence_before();
