@@ -131,7 +131,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
     extern __shared__ unsigned char smem_raw[];
     AttnTcSmem& s = *reinterpret_cast<AttnTcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H, q0 = blockIdx.x * BQ, T = p.T, Tk = p.Tk;
+    // CTAs are handed out in linear order (x fastest): the last query tile of every (batch, head) goes first.  Under a
+    // causal mask the later query tiles keep more key blocks, so the long CTAs start first and the short ones fill the tail.
+    const int lin = blockIdx.y * gridDim.x + blockIdx.x, n_bh = gridDim.y;
+    const int bh = lin % n_bh, b = bh / p.H, h = bh % p.H, q0 = (int(gridDim.x) - 1 - lin / n_bh) * BQ, T = p.T, Tk = p.Tk;
     const int nblk = (Tk + BKEY - 1) / BKEY;
     volatile int* abort_flag = &s.abort_flag;
     constexpr uint32_t kQBytes = BQ * HD * 4, kKBytes = BKEY * HD * 4, kVBytes = HD * BKEY * 4;
