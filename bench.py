@@ -382,6 +382,15 @@ def run_ours(args):
         kernels = {k: {"launches": v["n"], "ms": round(v["ms"], 4), "share": round(v["ms"] / total_ms, 4),
                        "tflops": round(v["flops"] / (v["ms"] * 1e-3) / 1e12, 3) if v["ms"] > 0 else None,
                        "gbs": round(v["bytes"] / (v["ms"] * 1e-3) / 1e9, 1) if v["ms"] > 0 else None} for k, v in sorted(by.items(), key=lambda kv: -kv[1]["ms"])}
+        # per-kernel fraction of its own roofline: tensor-core kernels against the ceiling of their arithmetic on the measured
+        # scale (three TF32 products per fp32 product = sustained bf16 peak / 6; the bf16 peak itself in bf16 mode), every
+        # other kernel against the measured copy bandwidth with its algorithmic bytes
+        tensor_ceiling = peaks["bf16_tflops_sustained"] / (1.0 if args.precision == "bf16" else 6.0)
+        for k, v in kernels.items():
+            if "tcgen05" in k and v["tflops"] is not None:
+                v["bound"], v["frac"] = "tensor", round(v["tflops"] / tensor_ceiling, 4)
+            elif v["gbs"] is not None:
+                v["bound"], v["frac"] = "hbm", round(v["gbs"] / peaks["hbm_gbs"], 4)
         # ---- CPU baseline on a bounded sample -------------------------------------------------------
         cpu = None
         if not args.no_cpu_baseline:

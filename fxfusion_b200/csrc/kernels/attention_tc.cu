@@ -56,23 +56,28 @@ __device__ __forceinline__ void soft_sync(int quarter) { asm volatile("bar.sync 
 // ---- V transpose -------------------------------------------------------------------------------------
 // Also records, per (batch*head, 32-key slab), whether any V element is NaN or infinite: vflags[bh * n32 + slab].
 __global__ void __launch_bounds__(256) attn_vt_kernel(const float* __restrict__ qkv, int64_t ld, int64_t v_off, int T, int H, float* __restrict__ vt,
-                                                      unsigned char* __restrict__ vflags) {
-    __shared__ float tile[HD][33];
-    const int bh = blockIdx.y, b = bh / H, h = bh % H, t0 = blockIdx.x * 32, tid = threadIdx.x;
-    int bad = 0;
+                                                      unsigned char* __restrict__ vflags, int n32) {
+    // one block moves 64 keys x 64 head columns: rows of 256 bytes on both sides
+    __shared__ float tile[HD][65];
+    const int bh = blockIdx.y, b = bh / H, h = bh % H, t0 = blockIdx.x * 64, tid = threadIdx.x;
+    int bad[2] = {0, 0};
 #pragma unroll
-    for (int i = 0; i < 2; i++) {
-        int f = tid + i * 256, r = f >> 4, c4 = (f & 15) * 4, t = t0 + r;
+    for (int i = 0; i < 4; i++) {
+        int f = tid + i * 256, r = f >> 4, c4 = (f & 15) * 4, t = t0 + r;   // i = 0, 1: keys 0..31 of the block; i = 2, 3: keys 32..63
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (t < T) v = *reinterpret_cast<const float4*>(qkv + (int64_t(b) * T + t) * ld + v_off + int64_t(h) * HD + c4);
         // x - x is 0 for finite x and NaN for NaN / infinity
-        bad |= ((v.x - v.x) != 0.f) | ((v.y - v.y) != 0.f) | ((v.z - v.z) != 0.f) | ((v.w - v.w) != 0.f);
+        bad[i >> 1] |= ((v.x - v.x) != 0.f) | ((v.y - v.y) != 0.f) | ((v.z - v.z) != 0.f) | ((v.w - v.w) != 0.f);
         tile[c4 + 0][r] = v.x; tile[c4 + 1][r] = v.y; tile[c4 + 2][r] = v.z; tile[c4 + 3][r] = v.w;
     }
-    bad = __syncthreads_or(bad);
-    if (tid == 0) vflags[int64_t(bh) * gridDim.x + blockIdx.x] = bad ? 1 : 0;
-    for (int idx = tid; idx < HD * 32; idx += 256) {
-        int d = idx >> 5, tt = idx & 31, t = t0 + tt;
+    const int bad0 = __syncthreads_or(bad[0]), bad1 = __syncthreads_or(bad[1]);
+    if (tid == 0) {
+        const int sl = blockIdx.x * 2;
+        vflags[int64_t(bh) * n32 + sl] = bad0 ? 1 : 0;
+        if (sl + 1 < n32) vflags[int64_t(bh) * n32 + sl + 1] = bad1 ? 1 : 0;
+    }
+    for (int idx = tid; idx < HD * 64; idx += 256) {
+        int d = idx >> 6, tt = idx & 63, t = t0 + tt;
         if (t < T) vt[(int64_t(bh) * HD + d) * T + t] = tile[d][tt];
     }
 }
@@ -487,10 +492,11 @@ int launch_attention_tc(const AttnArgs& a, float* vt_scratch, ExecCtx& ctx) {
     const int Tk = a.kv ? a.Tk : a.T;                     // keys per batch
     const float* kvp = a.kv ? a.kv : a.qkv;               // where K and V live
     const int64_t ldk = a.kv ? a.ld_kv : a.ld_qkv;
-    dim3 pgrid(unsigned((Tk + 31) / 32), unsigned(BH));
+    const int n32 = (Tk + 31) / 32;
+    dim3 pgrid(unsigned((Tk + 63) / 64), unsigned(BH));
     tag_launch(ctx, "attention_v_transpose", 0, 8.0 * double(BH) * Tk * HD);
     unsigned char* vflags = reinterpret_cast<unsigned char*>(vt_scratch + size_t(BH) * size_t(Tk) * HD);
-    attn_vt_kernel<<<pgrid, 256, 0, ctx.stream>>>(kvp, ldk, a.v_off, Tk, a.H, vt_scratch, vflags);
+    attn_vt_kernel<<<pgrid, 256, 0, ctx.stream>>>(kvp, ldk, a.v_off, Tk, a.H, vt_scratch, vflags, n32);
     FXF_LAUNCHED(ctx);
 
     CUtensorMap mq, mk, mv;
