@@ -65,6 +65,11 @@ struct Node {
     int fuse_res = -1, fuse_out = -1;   // tensor ids of the residual operand and of the Add's output
     bool fuse_relu = false;
     bool folded = false;                // ... and this Add / AddRelu node launches nothing
+    // tensor parallelism: the exchange after this sharded contraction also performs the residual Add and the LayerNorm that
+    // follow it (tensor ids; -1 = not part of the fold).  The folded nodes launch nothing.
+    bool xchg = false, xchg_replicate_x = false;
+    int xchg_res = -1, xchg_x = -1, xchg_y = -1, xchg_gamma = -1, xchg_beta = -1;
+    float xchg_eps = 0.f;
 };
 
 }  // namespace
@@ -139,10 +144,26 @@ int run_node(fxf_engine* e, size_t i) {
         e->ctx.fuse.out = static_cast<float*>(e->reg[size_t(n.fuse_out)].ptr);
         e->ctx.fuse.relu = n.fuse_relu;
     }
+    e->ctx.xchg = TpExchange{};
+    if (n.xchg) {
+        auto fp = [&](int id) { return id >= 0 ? static_cast<float*>(e->reg[size_t(id)].ptr) : nullptr; };
+        e->ctx.xchg.enabled = true;
+        e->ctx.xchg.residual = fp(n.xchg_res);
+        e->ctx.xchg.x_out = fp(n.xchg_x);
+        e->ctx.xchg.y_out = fp(n.xchg_y);
+        e->ctx.xchg.gamma = fp(n.xchg_gamma);
+        e->ctx.xchg.beta = fp(n.xchg_beta);
+        e->ctx.xchg.eps = n.xchg_eps;
+        e->ctx.xchg.replicate_x = n.xchg_replicate_x;
+    }
     if (n.fn(e->reg, n.in, n.out, n.params, n.plan.get(), e->ctx)) return 1;
     if (n.fuse_out >= 0) {
         FXF_CHECK(e->ctx.fuse.consumed, "node %zu (%s): the folded residual Add was not performed by the kernel", i, op_entry(n.op).name);
         e->ctx.fuse = EpilogueFusion{};
+    }
+    if (n.xchg) {
+        FXF_CHECK(e->ctx.xchg.consumed, "node %zu (%s): the folded exchange was not performed by the kernel", i, op_entry(n.op).name);
+        e->ctx.xchg = TpExchange{};
     }
     n.launches = e->ctx.launches - before;
     return 0;
@@ -331,82 +352,6 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
             if (cl[id]) set_channels_last(e->reg[id]);
     }
 
-    // ---- epilogue fusion: a residual Add / AddRelu right after a dense contraction is folded into that contraction ------
-    // The contraction writes act(acc + bias + residual) straight into the Add's output (bit-identical to the two nodes run
-    // separately: the same two fp32 additions in the same order).  Conditions: the two nodes are adjacent; the
-    // contraction's result (through aliases) is read by nothing else and is not a graph output; shapes, dtypes and layouts
-    // agree without broadcasting; the residual exists before the contraction runs; and the Add's output does not share
-    // arena bytes with any operand the writing GEMM still reads (the planner may have given it the slot of a tensor that
-    // dies at the contraction).  FXF_FUSE_ADD=0 turns the pass off.
-    {
-        const char* fenv = std::getenv("FXF_FUSE_ADD");
-        const bool enabled = !(fenv && fenv[0] == '0');
-        auto root = [&](uint32_t id) {
-            for (int guard = 0; guard < 64 && meta[id].alias_of >= 0 && uint32_t(meta[id].alias_of) < n_tensors; guard++) id = uint32_t(meta[id].alias_of);
-            return id;
-        };
-        auto same_shape = [&](uint32_t a, uint32_t b) {
-            const FxfTensor &x = e->reg[a], &y = e->reg[b];
-            if (x.rank != y.rank) return false;
-            for (int k = 0; k < x.rank; k++)
-                if (x.shape[k] != y.shape[k]) return false;
-            return true;
-        };
-        std::vector<int> producer(n_tensors, -1), n_readers(n_tensors, 0);
-        std::vector<char> escapes(n_tensors, 0);
-        for (size_t i = 0; i < e->nodes.size(); i++) {
-            for (auto id : e->nodes[i].out) producer[root(id)] = int(i);
-            for (auto id : e->nodes[i].in) n_readers[root(id)]++;
-        }
-        for (uint32_t id = 0; id < n_tensors; id++)
-            if (meta[id].kind == kOutput) escapes[root(id)] = 1;
-        auto arena_range = [&](uint32_t id, int64_t* lo, int64_t* hi) {   // false: not in the arena (constant, input)
-            const uint32_t r = root(id);
-            if (meta[r].kind == kConstant || meta[r].kind == kInput || meta[r].offset < 0) return false;
-            *lo = meta[r].offset;
-            *hi = meta[r].offset + int64_t(e->reg[r].nbytes);
-            return true;
-        };
-        for (size_t bi = 1; enabled && bi < e->nodes.size(); bi++) {
-            Node &A = e->nodes[bi - 1], &B = e->nodes[bi];
-            if ((B.op != FXF_OP_ADD && B.op != FXF_OP_ADD_RELU) || B.in.size() != 2 || B.out.size() != 1) continue;
-            // Convolutions are left alone: their layers are bandwidth-bound with short K loops, and the residual read in the
-            // GEMM epilogue (16 KB in flight per SM) is slower than the separate AddRelu kernel (measured on ResNet-50).
-            if (A.op != FXF_OP_LINEAR && A.op != FXF_OP_FEEDFORWARD && A.op != FXF_OP_MHA && A.op != FXF_OP_CROSS_MHA) continue;
-            if (A.fuse_out >= 0 || A.out.size() != 1) continue;
-            if (B.op == FXF_OP_ADD_RELU && e->opts.tp_size > 1) continue;   // the ReLU would have to follow the all-reduce
-            if (A.op == FXF_OP_LINEAR && e->opts.tp_size > 1 && e->opts.tp_shard_output) continue;
-            const uint32_t t = root(A.out[0]);
-            const int which = root(B.in[0]) == t ? 0 : (root(B.in[1]) == t ? 1 : -1);
-            if (which < 0) continue;
-            const uint32_t r = B.in[1 - which], o = B.out[0];
-            if (root(r) == t || n_readers[t] != 1 || escapes[t]) continue;
-            const FxfTensor &ta = e->reg[A.out[0]], &tr = e->reg[r], &to = e->reg[o];
-            if (ta.dtype != FXF_F32 || tr.dtype != FXF_F32 || to.dtype != FXF_F32) continue;
-            if (!same_shape(A.out[0], r) || !same_shape(A.out[0], o)) continue;
-            if (!same_layout(ta, tr) || !same_layout(ta, to)) continue;
-            const int pr = producer[root(r)];
-            if (pr >= int(bi) - 1) continue;   // the residual must exist before the contraction runs (inputs / constants: -1)
-            int64_t olo = 0, ohi = 0;
-            if (!arena_range(o, &olo, &ohi) || meta[o].alias_of >= 0) continue;
-            bool clash = false;
-            // MHA / CrossMHA / FeedForward read their activation inputs in their first GEMM; the final GEMM, which does the
-            // writing, reads only scratch and weights.  A plain Linear reads its input while it writes.
-            if (A.op == FXF_OP_LINEAR)
-                for (auto id : A.in) {
-                    int64_t lo = 0, hi = 0;
-                    if (arena_range(id, &lo, &hi) && lo < ohi && olo < hi) clash = true;
-                }
-            int64_t rlo = 0, rhi = 0;
-            if (arena_range(r, &rlo, &rhi) && rlo < ohi && olo < rhi) clash = true;
-            if (clash) continue;
-            A.fuse_res = int(r);
-            A.fuse_out = int(o);
-            A.fuse_relu = B.op == FXF_OP_ADD_RELU;
-            B.folded = true;
-        }
-    }
-
     // ---- plans (they see the final layouts) ---------------------------------------------------------
     for (auto& n : e->nodes) {
         const int op = n.op;
@@ -437,14 +382,14 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
     e->status_off = cursor;
     cursor += kAlign;
     if (e->opts.gemm_mode != FXF_GEMM_FP32_SIMT) {
-        // K-split workspace of the tensor-core GEMM: one 128 x 256 partial tile and four flags per SM
+        // K-split workspace of the tensor-core GEMM: one 128 x 256 partial tile and eight flags (one per epilogue warp) per SM
         int sms = 148;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, e->device);
         e->gemm_ws_off = cursor;
         e->gemm_ws_bytes = round_up(size_t(sms) * 128 * 256 * sizeof(float), kAlign);
         cursor += e->gemm_ws_bytes;
         e->gemm_flags_off = cursor;
-        e->gemm_flags_bytes = round_up(size_t(sms) * 4 * sizeof(int), kAlign);
+        e->gemm_flags_bytes = round_up(size_t(sms) * 8 * sizeof(int), kAlign);
         cursor += e->gemm_flags_bytes;
     }
     if (e->head_sharded && !e->input_ids.empty() && e->reg[e->input_ids[0]].rank >= 1) {
@@ -480,6 +425,7 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
     FXF_CHECK(prop.major == 10, "this library is built for sm_100a only (B200); device %d is sm_%d%d", e->device, prop.major, prop.minor);
     e->ctx.sm_count = prop.multiProcessorCount;
     e->ctx.gemm_mode = e->opts.gemm_mode;
+    e->ctx.tc_chunk_k = e->opts.tc_chunk_k;
     e->ctx.tp_rank = e->opts.tp_rank;
     e->ctx.tp_size = e->opts.tp_size;
     e->ctx.comm = e->comm;
@@ -503,10 +449,7 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
                 e->peers.flags_off = e->p2p_off;
                 e->peers.epoch_off = e->p2p_off + 4096;
                 e->peers.grid = 128;  // 8 ranks x 128 blocks x 4 bytes = 4 KB of flags
-                if (const char* g = std::getenv("FXF_P2P_GRID")) {  // debug override, 1..128
-                    int v = std::atoi(g);
-                    if (v >= 1 && v <= 128) e->peers.grid = v;
-                }
+                if (e->opts.p2p_grid >= 1 && e->opts.p2p_grid <= 128) e->peers.grid = e->opts.p2p_grid;
                 e->peers_mapped = true;
                 e->ctx.peers = &e->peers;
             } else {
@@ -520,6 +463,178 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
         e->ctx.gemm_flags = reinterpret_cast<int*>(e->base + e->gemm_flags_off);
         e->ctx.gemm_flag_count = int(e->gemm_flags_bytes / sizeof(int));
         FXF_CUDA(cudaMemset(e->ctx.gemm_flags, 0, e->gemm_flags_bytes));
+    }
+
+    // ---- fusion of the nodes that follow a dense contraction (decided here: whether the peers are mapped is known) ------
+    {
+        auto root = [&](uint32_t id) {
+            for (int guard = 0; guard < 64 && meta[id].alias_of >= 0 && uint32_t(meta[id].alias_of) < n_tensors; guard++) id = uint32_t(meta[id].alias_of);
+            return id;
+        };
+        auto same_shape = [&](uint32_t a, uint32_t b) {
+            const FxfTensor &x = e->reg[a], &y = e->reg[b];
+            if (x.rank != y.rank) return false;
+            for (int k = 0; k < x.rank; k++)
+                if (x.shape[k] != y.shape[k]) return false;
+            return true;
+        };
+        std::vector<int> producer(n_tensors, -1), n_readers(n_tensors, 0);
+        std::vector<char> escapes(n_tensors, 0);
+        for (size_t i = 0; i < e->nodes.size(); i++) {
+            for (auto id : e->nodes[i].out) producer[root(id)] = int(i);
+            for (auto id : e->nodes[i].in) n_readers[root(id)]++;
+        }
+        for (uint32_t id = 0; id < n_tensors; id++)
+            if (meta[id].kind == kOutput) escapes[root(id)] = 1;
+        auto arena_range = [&](uint32_t id, int64_t* lo, int64_t* hi) {   // false: not in the arena (constant, input)
+            const uint32_t r = root(id);
+            if (meta[r].kind == kConstant || meta[r].kind == kInput || meta[r].offset < 0) return false;
+            *lo = meta[r].offset;
+            *hi = meta[r].offset + int64_t(e->reg[r].nbytes);
+            return true;
+        };
+
+        // -- tensor parallelism: [sharded contraction -> Add -> LayerNorm] or [sharded contraction -> AddLayerNorm] becomes the
+        // contraction plus ONE exchange kernel over peer memory that sums the ranks' partial outputs, adds the residual and
+        // normalises (kernels/tp_exchange.cu).  Rank r owns rows [r*R, (r+1)*R): it alone computes them, keeps the new residual
+        // rows for itself and stores the normalised rows on every rank.  Conditions: the peers are mapped; the contraction's
+        // result is read by the Add only; no broadcasting; the LayerNorm normalises the last dimension (<= 1024 floats); every
+        // tensor the kernel writes lies in the arena, apart from or exactly on top of each tensor it reads (rows have one owner,
+        // so exact overlap is harmless) and apart from the other output.
+        if (e->peers_mapped && !e->opts.no_tp_fused_exchange) {
+            auto is_plain_f32 = [&](uint32_t id) { return e->reg[id].dtype == FXF_F32 && is_contiguous(e->reg[id]); };
+            auto compatible = [&](uint32_t w, uint32_t r) {   // written tensor w vs read tensor r: disjoint or identical
+                int64_t wl = 0, wh = 0, rl = 0, rh = 0;
+                if (!arena_range(w, &wl, &wh)) return false;
+                if (!arena_range(r, &rl, &rh)) return true;
+                return wh <= rl || rh <= wl || (wl == rl && wh == rh);
+            };
+            for (size_t ai = 0; ai + 1 < e->nodes.size(); ai++) {
+                Node& A = e->nodes[ai];
+                if ((A.op != FXF_OP_FEEDFORWARD && A.op != FXF_OP_MHA && A.op != FXF_OP_CROSS_MHA) || !A.plan->tp_sharded || A.out.size() != 1) continue;
+                Node& B = e->nodes[ai + 1];
+                const bool add = B.op == FXF_OP_ADD && B.in.size() == 2, addln = B.op == FXF_OP_ADD_LAYER_NORM && B.in.size() == 4;
+                if ((!add && !addln) || B.out.size() != 1) continue;
+                const uint32_t t = root(A.out[0]);
+                const int which = root(B.in[0]) == t ? 0 : (root(B.in[1]) == t ? 1 : -1);
+                if (which < 0) continue;
+                const uint32_t r = B.in[1 - which], o = B.out[0];
+                if (root(r) == t || n_readers[t] != 1 || escapes[t]) continue;
+                if (!is_plain_f32(A.out[0]) || !is_plain_f32(r) || !is_plain_f32(o) || !same_shape(A.out[0], r) || !same_shape(A.out[0], o)) continue;
+                if (producer[root(r)] >= int(ai)) continue;   // the residual exists before the contraction runs
+                const FxfTensor& ta = e->reg[A.out[0]];
+                if (ta.rank < 1) continue;
+                const int64_t D = ta.shape[ta.rank - 1];
+                if (D <= 0 || D % 4 != 0 || D > 1024 || numel(ta) == 0) continue;
+                int64_t lo = 0, hi = 0;
+                if (!arena_range(A.out[0], &lo, &hi) || !arena_range(o, &lo, &hi) || meta[o].alias_of >= 0) continue;
+                auto ln_over_last_dim = [&](const Node& n, size_t w_at) {
+                    return n.params.ints.size() >= 2 && n.params.ints[0] == 1 && n.params.ints[1] == D && !n.params.floats.empty() &&
+                           numel(e->reg[n.in[w_at]]) == D && numel(e->reg[n.in[w_at + 1]]) == D && e->reg[n.in[w_at]].dtype == FXF_F32 &&
+                           e->reg[n.in[w_at + 1]].dtype == FXF_F32;
+                };
+                if (addln) {
+                    if (!ln_over_last_dim(B, 2)) continue;
+                    if (!compatible(o, A.out[0]) || !compatible(o, r)) continue;
+                    A.xchg = true;
+                    A.xchg_res = int(r); A.xchg_y = int(o); A.xchg_gamma = int(B.in[2]); A.xchg_beta = int(B.in[3]); A.xchg_eps = B.params.floats[0];
+                    B.folded = true;
+                    continue;
+                }
+                if (!compatible(o, A.out[0]) || !compatible(o, r)) continue;
+                A.xchg = true;
+                A.xchg_res = int(r); A.xchg_x = int(o);
+                A.xchg_replicate_x = true;   // until the second pass has looked at the readers
+                B.folded = true;
+                if (ai + 2 < e->nodes.size()) {
+                    Node& Cn = e->nodes[ai + 2];
+                    if (Cn.op == FXF_OP_LAYER_NORM && Cn.in.size() == 3 && Cn.out.size() == 1 && root(Cn.in[0]) == root(o) && ln_over_last_dim(Cn, 1) &&
+                        is_plain_f32(Cn.out[0]) && same_shape(Cn.out[0], o) && meta[Cn.out[0]].alias_of < 0 && arena_range(Cn.out[0], &lo, &hi) &&
+                        compatible(Cn.out[0], A.out[0]) && compatible(Cn.out[0], r)) {
+                        int64_t yl = 0, yh = 0, xl = 0, xh = 0;
+                        arena_range(Cn.out[0], &yl, &yh);
+                        arena_range(o, &xl, &xh);
+                        if (yh <= xl || xh <= yl) {
+                            A.xchg_y = int(Cn.out[0]); A.xchg_gamma = int(Cn.in[1]); A.xchg_beta = int(Cn.in[2]); A.xchg_eps = Cn.params.floats[0];
+                            Cn.folded = true;
+                        }
+                    }
+                }
+            }
+            // second pass: the new residual stream may stay row-sharded (each rank holds only the rows it owns) when every reader
+            // of it is inside the scheme: the LayerNorm folded into the same exchange, or the residual operand of a later
+            // exchange with the same row partition.  Anything else (another node, a graph output) needs every row everywhere.
+            for (size_t ai = 0; ai < e->nodes.size(); ai++) {
+                Node& A = e->nodes[ai];
+                if (!A.xchg || A.xchg_x < 0) continue;
+                const uint32_t X = root(uint32_t(A.xchg_x));
+                bool inside = !escapes[X];
+                for (size_t bi = 0; bi < e->nodes.size() && inside; bi++) {
+                    const Node& R = e->nodes[bi];
+                    bool reads = false;
+                    for (auto id : R.in) reads = reads || root(id) == X;
+                    if (!reads) continue;
+                    if (R.folded && bi == ai + 2 && A.xchg_y >= 0) continue;   // the LayerNorm folded into this exchange
+                    bool ok = false;
+                    if (R.folded && bi >= 1) {
+                        const Node& P = e->nodes[bi - 1];   // the contraction this Add / AddLayerNorm was folded into
+                        ok = P.xchg && P.xchg_res >= 0 && root(uint32_t(P.xchg_res)) == X && numel(e->reg[P.out[0]]) == numel(e->reg[A.out[0]]) &&
+                             e->reg[P.out[0]].shape[e->reg[P.out[0]].rank - 1] == e->reg[A.out[0]].shape[e->reg[A.out[0]].rank - 1];
+                        // X must be that Add's residual operand only, not also its other operand
+                        int uses = 0;
+                        for (auto id : R.in) uses += root(id) == X ? 1 : 0;
+                        ok = ok && uses == 1;
+                    }
+                    inside = ok;
+                }
+                A.xchg_replicate_x = !inside;
+            }
+        }
+
+        // -- a residual Add / AddRelu right after a dense contraction is folded into that contraction's epilogue: it writes
+        // act(acc + bias + residual) straight into the Add's output (bit-identical to the two nodes run separately: the same
+        // two fp32 additions in the same order).  Conditions: the two nodes are adjacent; the contraction's result (through
+        // aliases) is read by nothing else and is not a graph output; shapes, dtypes and layouts agree without broadcasting;
+        // the residual exists before the contraction runs; and the Add's output does not share arena bytes with any operand
+        // the writing GEMM still reads (the planner may have given it the slot of a tensor that dies at the contraction).
+        for (size_t bi = 1; !e->opts.no_epilogue_fusion && bi < e->nodes.size(); bi++) {
+            Node &A = e->nodes[bi - 1], &B = e->nodes[bi];
+            if ((B.op != FXF_OP_ADD && B.op != FXF_OP_ADD_RELU) || B.in.size() != 2 || B.out.size() != 1 || B.folded || A.xchg) continue;
+            // Convolutions are left alone: their layers are bandwidth-bound with short K loops, and the residual read in the
+            // GEMM epilogue (16 KB in flight per SM) is slower than the separate AddRelu kernel (measured on ResNet-50).
+            if (A.op != FXF_OP_LINEAR && A.op != FXF_OP_FEEDFORWARD && A.op != FXF_OP_MHA && A.op != FXF_OP_CROSS_MHA) continue;
+            if (A.fuse_out >= 0 || A.out.size() != 1) continue;
+            if (B.op == FXF_OP_ADD_RELU && A.plan->tp_sharded) continue;   // the ReLU would have to follow the all-reduce
+            if (A.op == FXF_OP_LINEAR && e->opts.tp_size > 1 && e->opts.tp_shard_output) continue;
+            const uint32_t t = root(A.out[0]);
+            const int which = root(B.in[0]) == t ? 0 : (root(B.in[1]) == t ? 1 : -1);
+            if (which < 0) continue;
+            const uint32_t r = B.in[1 - which], o = B.out[0];
+            if (root(r) == t || n_readers[t] != 1 || escapes[t]) continue;
+            const FxfTensor &ta = e->reg[A.out[0]], &tr = e->reg[r], &to = e->reg[o];
+            if (ta.dtype != FXF_F32 || tr.dtype != FXF_F32 || to.dtype != FXF_F32) continue;
+            if (!same_shape(A.out[0], r) || !same_shape(A.out[0], o)) continue;
+            if (!same_layout(ta, tr) || !same_layout(ta, to)) continue;
+            const int pr = producer[root(r)];
+            if (pr >= int(bi) - 1) continue;   // the residual must exist before the contraction runs (inputs / constants: -1)
+            int64_t olo = 0, ohi = 0;
+            if (!arena_range(o, &olo, &ohi) || meta[o].alias_of >= 0) continue;
+            bool clash = false;
+            // MHA / CrossMHA / FeedForward read their activation inputs in their first GEMM; the final GEMM, which does the
+            // writing, reads only scratch and weights.  A plain Linear reads its input while it writes.
+            if (A.op == FXF_OP_LINEAR)
+                for (auto id : A.in) {
+                    int64_t lo = 0, hi = 0;
+                    if (arena_range(id, &lo, &hi) && lo < ohi && olo < hi) clash = true;
+                }
+            int64_t rlo = 0, rhi = 0;
+            if (arena_range(r, &rlo, &rhi) && rlo < ohi && olo < rhi) clash = true;
+            if (clash) continue;
+            A.fuse_res = int(r);
+            A.fuse_out = int(o);
+            A.fuse_relu = B.op == FXF_OP_ADD_RELU;
+            B.folded = true;
+        }
     }
 
     // ---- registry binding, in file order (an alias binds to an already-built source) --------
@@ -579,6 +694,12 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
     if (run_nodes(e, e->capture_stream)) return 1;
     e->launches_per_run = e->ctx.launches;
     FXF_CUDA(cudaStreamSynchronize(e->capture_stream));
+    // The warm-up above ran with the default (generous) peer-wait budgets: the ranks reach it with whatever skew their
+    // builds had.  The caller's budgets apply from here on (they are kernel arguments, so they are set before the capture).
+    if (e->peers_mapped) {
+        if (e->opts.p2p_start_budget_ms > 0) e->peers.start_budget_ns = (unsigned long long)e->opts.p2p_start_budget_ms * 1000000ull;
+        if (e->opts.p2p_end_budget_ms > 0) e->peers.end_budget_ns = (unsigned long long)e->opts.p2p_end_budget_ms * 1000000ull;
+    }
     if (e->opts.use_cuda_graph && !e->nodes.empty()) {
         FXF_CUDA(cudaStreamBeginCapture(e->capture_stream, cudaStreamCaptureModeThreadLocal));
         int rc = run_nodes(e, e->capture_stream);
@@ -767,7 +888,10 @@ int fxf_engine_describe(const fxf_engine* e, char* out, size_t out_bytes) {
         for (auto id : n.out) os << id << "@" << (static_cast<uint8_t*>(e->reg[id].ptr) - e->base) << (is_channels_last(e->reg[id]) ? "[nhwc] " : " ");
         os << "] launches " << n.launches << " variant " << n.plan->variant << " scratch " << n.plan->scratch_bytes;
         if (n.fuse_out >= 0) os << " +" << (n.fuse_relu ? "AddRelu" : "Add") << "(residual " << n.fuse_res << ") -> out " << n.fuse_out;
-        if (n.folded) os << " folded into the previous node's epilogue";
+        if (n.xchg)
+            os << " +exchange(residual " << n.xchg_res << ") -> x " << n.xchg_x << (n.xchg_x >= 0 ? (n.xchg_replicate_x ? " [all rows on every rank]" : " [own rows]") : "")
+               << " y " << n.xchg_y;
+        if (n.folded) os << " folded into an earlier node";
         os << "\n";
     }
     std::string s = os.str();
@@ -872,7 +996,7 @@ static int make_call(int op_code, const FxfTensor* reg, int n_reg, const uint32_
 
 // A single kernel call that may reach the tensor-core GEMM (its plan keeps split weights) also carries that kernel's
 // K-split workspace behind its scratch: partial tiles for up to kCallWsSms SMs, then the flags.
-constexpr size_t kCallWsSms = 160, kCallWsTile = size_t(128) * 256 * sizeof(float), kCallFlagBytes = 4096;
+constexpr size_t kCallWsSms = 160, kCallWsTile = size_t(128) * 256 * sizeof(float), kCallFlagBytes = 8192;
 static size_t call_ws_bytes(const NodePlan& plan, int gemm_mode) {
     return (gemm_mode != FXF_GEMM_FP32_SIMT && plan.persist_bytes > 0) ? kCallWsSms * kCallWsTile + kCallFlagBytes : 0;
 }
@@ -925,6 +1049,25 @@ int fxf_kernel_invoke(int op_code, const FxfTensor* reg, int n_reg, const uint32
     ctx.sm_count = sms;
     if (plan->prepare(r, in, out, p, ctx)) return 1;
     return entry.kernel(r, in, out, p, plan.get(), ctx);
+}
+
+int fxf_gemm_variant(int64_t M, int64_t N, int64_t K, int gemm_mode, int sm_count, char* out, size_t out_bytes) {
+    FXF_CHECK(out != nullptr && out_bytes > 0, "fxf_gemm_variant: NULL argument");
+    GemmArgs a;
+    a.M = M; a.N = N; a.K = K;
+    std::string v = gemm_variant_name(a, gemm_mode, sm_count > 0 ? sm_count : 148);
+    size_t k = std::min(out_bytes - 1, v.size());
+    std::memcpy(out, v.data(), k);
+    out[k] = 0;
+    return 0;
+}
+
+int fxf_tp_exchange_emulated(int n_ranks, const float* const* partial, const float* const* residual, float* const* x_out, float* const* y_out,
+                             const float* gamma, const float* beta, float eps, int64_t M, int64_t D, int replicate_x, void* sync_mem, int64_t sync_bytes,
+                             int budget_ms, int skip_rank, void* stream) {
+    FXF_CHECK(n_ranks >= 2 && sync_mem != nullptr && sync_bytes >= int64_t(n_ranks) * 8192, "fxf_tp_exchange_emulated: sync_mem must hold n_ranks * 8192 zeroed bytes");
+    return tp_exchange_emulated(n_ranks, partial, residual, x_out, y_out, gamma, beta, eps, M, D, replicate_x, sync_mem, budget_ms, skip_rank,
+                                static_cast<cudaStream_t>(stream));
 }
 
 // ---- greedy static decode ---------------------------------------------------------------------
@@ -990,6 +1133,7 @@ int fxf_decode_cached(fxf_engine* e, int64_t* tokens_io, int initial_len, void* 
     FXF_CHECK(pos.dtype == FXF_I64 && numel(pos) == 1, "fxf_decode_cached: input 1 must be one int64");
     FXF_CHECK(logits.dtype == FXF_F32 && logits.rank == 3 && logits.shape[0] == B && logits.shape[1] == 1, "fxf_decode_cached: output 0 must be float32 [B,1,V]");
     FXF_CHECK(initial_len >= 1 && initial_len <= T, "fxf_decode_cached: initial_len %d must be in [1, %d]", initial_len, T);
+    FXF_CHECK(!e->head_sharded, "fxf_decode_cached: the step graph's final Linear is sharded over the vocabulary; build the engine without tp_shard_output");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int64_t* slot = static_cast<int64_t*>(tok.ptr);
     if (tokens_io != slot) FXF_CUDA(cudaMemcpyAsync(slot, tokens_io, size_t(tok.nbytes), cudaMemcpyDeviceToDevice, s));
@@ -1015,6 +1159,7 @@ static int last_row_head(fxf_engine* e, int64_t* tokens, int cur, ExecCtx& ctx) 
     const int64_t col0 = e->head_sharded ? e->head_col0 : 0, ncols = e->head_sharded ? e->head_ncols : V;
     float* rows = reinterpret_cast<float*>(e->base + e->lastrow_off);
     ctx.gemm_mode = e->ctx.gemm_mode;
+    ctx.tc_chunk_k = e->ctx.tc_chunk_k;
     ctx.status = e->ctx.status;
     ctx.gemm_ws = e->ctx.gemm_ws; ctx.gemm_ws_bytes = e->ctx.gemm_ws_bytes;
     ctx.gemm_flags = e->ctx.gemm_flags; ctx.gemm_flag_count = e->ctx.gemm_flag_count;

@@ -475,6 +475,7 @@ bool attention_tc_supported(const AttnArgs& a, int gemm_mode) {
     if (gemm_mode == FXF_GEMM_FP32_SIMT) return false;
     const int Tk = a.kv ? a.Tk : a.T;
     if (a.hd != HD || Tk % 4 != 0 || Tk < 16 || a.T < 1) return false;   // V^T rows (Tk floats) must be 16-byte multiples
+    if ((Tk + BKEY - 1) / BKEY > 32) return false;   // the kernel tracks its key blocks in one 32-bit word: at most 4096 keys
     if (a.ld_qkv % 4 != 0 || a.ld_ctx % 4 != 0 || (a.q_off | a.k_off | a.v_off) % 4 != 0) return false;
     if (a.kv && (a.ld_kv % 4 != 0 || !aligned16(a.kv))) return false;
     if (!aligned16(a.qkv) || !aligned16(a.ctx)) return false;

@@ -356,7 +356,7 @@ int run_conv(Registry& reg, const TensorIds& in, const TensorIds& out, const Par
         g.M = n_pix; g.N = d.O; g.K = d.C;
         g.ldx = d.C; g.ldw = d.C; g.ldo = d.O;
         g.relu = relu;
-        apply_fusion(ctx, g);
+        apply_fusion(ctx, g, false);
         return launch_gemm(g, ctx);
     }
     if (cp && cp->s2d_tc && cp->w_hi && is_channels_last(o) && ctx.scratch != nullptr &&
@@ -375,7 +375,7 @@ int run_conv(Registry& reg, const TensorIds& in, const TensorIds& out, const Par
         c.N = d.N; c.C = 16; c.H = cp->Hs; c.W = cp->Ws; c.O = d.O; c.KH = cp->KH2; c.KW = cp->KW2; c.HO = d.HO; c.WO = d.WO;
         c.pad_h = 0; c.pad_w = 0; c.dil_h = 1; c.dil_w = 1; c.str_h = 1; c.str_w = 1;
         c.relu = relu;
-        apply_fusion(ctx, c);
+        apply_fusion(ctx, c, false);
         tag_launch(ctx, "conv2d_s2d_igemm_tf32x3_tcgen05", 2.0 * double(n_pix) * d.O * d.C * d.KH * d.KW, double(x.nbytes) + double(w.nbytes) + double(o.nbytes));
         return launch_conv_tc(c, ctx);
     }
@@ -388,7 +388,7 @@ int run_conv(Registry& reg, const TensorIds& in, const TensorIds& out, const Par
         c.N = d.N; c.C = d.C; c.H = d.H; c.W = d.W; c.O = d.O; c.KH = d.KH; c.KW = d.KW; c.HO = d.HO; c.WO = d.WO;
         c.pad_h = d.ph; c.pad_w = d.pw; c.dil_h = d.dh; c.dil_w = d.dw; c.str_h = d.sh; c.str_w = d.sw;
         c.relu = relu;
-        apply_fusion(ctx, c);
+        apply_fusion(ctx, c, false);
         return launch_conv_tc(c, ctx);
     }
     dim3 grid(unsigned((n_pix + CBM - 1) / CBM), unsigned((d.og + CBN - 1) / CBN), unsigned(d.groups));

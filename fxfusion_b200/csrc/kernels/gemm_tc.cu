@@ -29,18 +29,25 @@
 // bf16-grade (about 3e-3 of the output scale); it exists for throughput, not for the parity contract.
 //
 // Structure: a PERSISTENT kernel, one CTA per SM, each CTA walking a strided list of 128 x BN output
-// tiles.  320 threads in four roles that only meet on mbarriers:
-//   warps 0-3  epilogue: tcgen05.ld of a finished accumulator (each warp its 32 TMEM lanes), staged
-//              through shared memory so that global stores are row-contiguous, bias + ReLU fused.
-//              With ACC = 2 TMEM holds two accumulators, so the epilogue of tile i runs under the
-//              main loop of tile i+1 (BN <= 192); BN = 256 has one accumulator.
-//   warp 4     TMA producer: per K-slab three cp.async.bulk.tensor loads — x tile [128,BK], w_hi and
-//              w_lo tiles [BN,BK] — into a STAGES-deep ring, completion counted on an mbarrier.
-//   warp 5     one thread issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8), 3 products per K-step,
-//              accumulating in TMEM; tcgen05.commit hands the stage back to the producer and, after
-//              the last slab of a tile, the accumulator to the epilogue.
-//   warps 6-9  the activation split of a landed stage (either way above), then arrive.
-// TMEM columns: [0, ACC*BN) accumulators, then STAGES x (BK hi + BK lo) columns of A.
+// tiles.  512 threads = four warpgroups whose roles only meet on mbarriers; each role resizes its register
+// budget (setmaxnreg) so that the epilogue can keep a tile's running sums in registers:
+//   warps 0-7   epilogue.  Warp w owns TMEM lanes 32*(w%4).. and the column half w/4 of the tile.  The
+//               K loop of a tile is cut into chunks (TcParams::chunk_slabs K-slabs); the MMA warp
+//               accumulates each chunk from zero into one of TWO TMEM accumulators, alternating, and the
+//               epilogue warps add every finished chunk to fp32 running sums in registers (round to
+//               nearest) while the tensor core works on the next chunk.  After the last chunk: bias, residual
+//               and ReLU, staged through shared memory so that global stores are row-contiguous.
+//   warps 8-11  the activation split of a landed stage (either way above), then arrive.
+//   warp 12     TMA producer: per K-slab three cp.async.bulk.tensor loads — x tile [128,BK], w_hi and
+//               w_lo tiles [BN,BK] — into a STAGES-deep ring, completion counted on an mbarrier.
+//   warp 13     one thread issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8), 3 products per K-step,
+//               accumulating in TMEM; tcgen05.commit hands the stage back to the producer and, after
+//               the last slab of a chunk, the accumulator to the epilogue.
+//   warps 14-15 idle (they complete the fourth warpgroup, which setmaxnreg needs).
+// Why chunks.  The tensor core adds into its fp32 accumulator with truncation, so the error of one long
+// accumulation chain grows linearly with K (about 4e-8 * K of the result's scale, measured).  Chains of at
+// most `chunk` K-elements summed by CUDA cores keep the result at fp32 FFMA grade for any K.
+// TMEM columns: [0, 2*BN) accumulators, then STAGES x (BK hi + BK lo) columns of A.
 // Every mbarrier wait is bounded by a wall-clock budget; on expiry the CTA records an error in the
 // status word, all roles stop issuing work, the CTA frees its TMEM and returns.
 //
@@ -48,7 +55,6 @@
 #include <cuda.h>
 
 #include <algorithm>
-#include <cstdlib>
 #include <mutex>
 
 #include "../runtime.hpp"
@@ -60,12 +66,32 @@ namespace {
 using namespace sm100;
 
 constexpr int BM = 128;
-constexpr int kThreads = 320;
-constexpr int kEpiWarp0 = 0, kTmaWarp = 4, kMmaWarp = 5, kSplitWarp0 = 6;
+constexpr int kThreads = 512;
+constexpr int kEpiWarps = 8, kSplitWarp0 = 8, kTmaWarp = 12, kMmaWarp = 13;
+constexpr int ACC = 2;   // TMEM accumulators, alternating per K chunk
 
 enum : int { kErrWaitTma = 101, kErrWaitSplit = 102, kErrWaitEmpty = 103, kErrWaitAcc = 104, kErrWaitAccEmpty = 105, kErrWaitPartial = 106 };
 
-constexpr int kStagePad = 36;  // floats per staged epilogue row: 32 + 4 keeps float4 rows conflict-free
+constexpr int kStagePad = 20;  // floats per staged epilogue row: 16 + 4 keeps float4 rows conflict-free
+
+// Register budgets per role (setmaxnreg, multiples of 8; the four warpgroups of a CTA must fit 64 K registers).  The
+// epilogue holds BN / 2 running sums per thread; the split warps hold a row of the A stage when A goes to tensor memory.
+template <int BN, int BK, bool TS, bool BF16>
+struct RegBudget {
+    static constexpr int epi = BN >= 256 ? 208 : (BN >= 224 ? 192 : (BN >= 192 ? 184 : 176));
+    static constexpr int split = !TS ? 48 : (BN >= 224 ? 72 : ((BK == 32 && !BF16) ? 104 : 80));
+    static constexpr int ctrl = BN >= 192 ? 48 : 56;
+    static_assert(2 * 128 * epi + 128 * split + 128 * ctrl <= 65536, "register budgets exceed the register file");
+};
+template <int N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_set() {   // the kernel starts with 128 registers per thread (512 threads, one CTA per SM)
+    if constexpr (N > 128) reg_inc<N>();
+    else if constexpr (N < 128) reg_dec<N>();
+}
 
 template <int BN, int BK, int STAGES, bool TS, bool BF16>
 struct alignas(1024) TcSmem {
@@ -73,7 +99,7 @@ struct alignas(1024) TcSmem {
     float a_lo[TS ? 1 : STAGES][TS ? 256 : BM * BK];  // x_lo twin buffers, only when the MMAs read A from shared memory
     float b_hi[STAGES][BF16 ? BN * BK / 2 : BN * BK];   // w_hi tile (fp32), or the whole bf16 weight tile in bf16 mode
     float b_lo[BF16 ? 1 : STAGES][BF16 ? 256 : BN * BK];
-    float stage_out[4][32 * kStagePad];   // one 32 x 32 block per epilogue warp
+    float stage_out[kEpiWarps][32 * kStagePad];   // one 32 x 16 block per epilogue warp
     uint64_t full_tma[STAGES];
     uint64_t full_split[STAGES];
     uint64_t empty[STAGES];
@@ -109,6 +135,7 @@ struct TcParams {
     // into `tail_split` work units that run on different CTAs.  Parts 1.. write their partial accumulator to `ws`
     // (unit-major, 128 x BN floats each) and raise flags[unit*4 + warp]; part 0 adds them in part order (deterministic).
     int full_tiles, tail_tiles, tail_split;
+    int chunk_slabs;   // K-slabs per accumulation chain (>= 1)
     float* ws;
     int* flags;
     int* status;
@@ -169,7 +196,33 @@ __device__ __forceinline__ int64_t out_row_offset(const TcParams& p, int tm, int
     return ((int64_t(n) * c.HO + oy) * c.WO + ox) * p.ldo;
 }
 
-template <int BN, int BK, int STAGES, int ACC, bool TS, bool BF16, bool HYB>
+// 32 consecutive TMEM columns of this thread's lane (tcgen05.ld 32x32b.x32) or 16 (x16)
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ float relu_keep_nan(float v) { return v > 0.f ? v : (v != v ? v : 0.f); }
+
+// One finished accumulation chunk, this thread's row and HALF columns of it: TMEM -> registers, added to the running sums
+// (16 columns per load keep the temporaries small: the sums themselves take HALF registers).
+template <int HALF>
+__device__ __forceinline__ void drain_chunk(uint32_t tacc, float (&sum)[HALF]) {
+    static_assert(HALF % 16 == 0, "column halves are drained 16 columns at a time");
+#pragma unroll
+    for (int c = 0; c < HALF; c += 16) {
+        uint32_t r[16];
+        tmem_ld16(tacc + uint32_t(c), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 16; j++) sum[c + j] += __uint_as_float(r[j]);
+    }
+}
+
+template <int BN, int BK, int STAGES, bool TS, bool BF16, bool HYB>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_whi,
                    const __grid_constant__ CUtensorMap map_wlo, TcParams p) {
@@ -177,12 +230,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     // dynamic shared memory is only guaranteed 16-byte aligned; swizzled tiles need 1024
     static_assert(!BF16 || (TS && BK == 32), "the bf16 mode takes A from tensor memory with 32-float slabs");
     static_assert(!HYB || (TS && !BF16), "hybrid: x_hi is the raw tile in shared memory, x_lo goes to tensor memory");
+    static_assert(BN % 32 == 0, "tile width must be a multiple of 32 columns (16 per column half and staging step)");
     using Smem = TcSmem<BN, BK, STAGES, TS, BF16>;
+    using Regs = RegBudget<BN, BK, TS, BF16>;
     Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_k = int((p.K + BK - 1) / BK);
     const int num_units = p.full_tiles + p.tail_tiles * p.tail_split;
+    const int chunk = p.chunk_slabs > 0 ? p.chunk_slabs : num_k;
     constexpr uint32_t kBBytes = BF16 ? uint32_t(BN * BK) * 2u : uint32_t(2 * BN * BK) * 4u;   // weight bytes per stage
     constexpr uint32_t kStageBytes = uint32_t(BM * BK) * 4u + kBBytes;
     constexpr uint32_t kIdesc = BF16 ? umma_idesc_bf16(BM, BN) : umma_idesc_tf32(BM, BN);
@@ -201,7 +257,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         }
         for (int i = 0; i < ACC; i++) {
             mbar_init(&s.acc_full[i], 1);
-            mbar_init(&s.acc_empty[i], 4);    // one arrival per epilogue warp
+            mbar_init(&s.acc_empty[i], kEpiWarps);    // one arrival per epilogue warp
         }
         s.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -215,109 +271,116 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = s.tmem_base;
 
-    if (warp == kTmaWarp) {
-        // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            uint32_t it = 0;  // slab counter over all tiles of this CTA
-            for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
-                const Unit un = get_unit(p, unit, num_k);
-                int tm, tn;
-                tile_coords(p, un.tile, tm, tn);
-                for (int k = un.k0; k < un.k1; k++, it++) {
-                    int st = it % STAGES;
-                    if (it >= uint32_t(STAGES) && !mbar_wait(&s.empty[st], ((it / STAGES) - 1) & 1, abort_flag)) {
-                        give_up(abort_flag, p.status, kErrWaitEmpty);
-                        goto producer_done;
+    if (warp >= kTmaWarp) {
+        reg_set<Regs::ctrl>();
+        if (warp == kTmaWarp) {
+            // ---------------- TMA producer ----------------
+            if (lane == 0) {
+                uint32_t it = 0;  // slab counter over all tiles of this CTA
+                for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+                    const Unit un = get_unit(p, unit, num_k);
+                    int tm, tn;
+                    tile_coords(p, un.tile, tm, tn);
+                    for (int k = un.k0; k < un.k1; k++, it++) {
+                        int st = it % STAGES;
+                        if (it >= uint32_t(STAGES) && !mbar_wait(&s.empty[st], ((it / STAGES) - 1) & 1, abort_flag)) {
+                            give_up(abort_flag, p.status, kErrWaitEmpty);
+                            goto producer_done;
+                        }
+                        if (p.cv.enabled) {
+                            int ox0, oy0, n0;
+                            conv_tile_origin(p.cv, tm, ox0, oy0, n0);
+                            const int tap = k / p.cv.c_slabs, cs = k - tap * p.cv.c_slabs, kh = tap / p.cv.KW, kw = tap - kh * p.cv.KW;
+                            mbar_expect_tx(&s.full_tma[st], p.cv.a_bytes + kBBytes);
+                            tma_load_4d(s.a[st], &map_x, cs * BK, ox0 * p.cv.str_w - p.cv.pad_w + kw * p.cv.dil_w,
+                                        oy0 * p.cv.str_h - p.cv.pad_h + kh * p.cv.dil_h, n0, &s.full_tma[st]);
+                        } else {
+                            mbar_expect_tx(&s.full_tma[st], kStageBytes);
+                            tma_load_2d(s.a[st], &map_x, k * BK, tm * BM, &s.full_tma[st]);
+                        }
+                        tma_load_2d(s.b_hi[st], &map_whi, k * BK, tn * BN, &s.full_tma[st]);
+                        if (!BF16) tma_load_2d(s.b_lo[BF16 ? 0 : st], &map_wlo, k * BK, tn * BN, &s.full_tma[st]);
                     }
-                    if (p.cv.enabled) {
-                        int ox0, oy0, n0;
-                        conv_tile_origin(p.cv, tm, ox0, oy0, n0);
-                        const int tap = k / p.cv.c_slabs, cs = k - tap * p.cv.c_slabs, kh = tap / p.cv.KW, kw = tap - kh * p.cv.KW;
-                        mbar_expect_tx(&s.full_tma[st], p.cv.a_bytes + kBBytes);
-                        tma_load_4d(s.a[st], &map_x, cs * BK, ox0 * p.cv.str_w - p.cv.pad_w + kw * p.cv.dil_w,
-                                    oy0 * p.cv.str_h - p.cv.pad_h + kh * p.cv.dil_h, n0, &s.full_tma[st]);
-                    } else {
-                        mbar_expect_tx(&s.full_tma[st], kStageBytes);
-                        tma_load_2d(s.a[st], &map_x, k * BK, tm * BM, &s.full_tma[st]);
-                    }
-                    tma_load_2d(s.b_hi[st], &map_whi, k * BK, tn * BN, &s.full_tma[st]);
-                    if (!BF16) tma_load_2d(s.b_lo[BF16 ? 0 : st], &map_wlo, k * BK, tn * BN, &s.full_tma[st]);
                 }
+            producer_done:;
             }
-        producer_done:;
-        }
-    } else if (warp == kMmaWarp) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            uint32_t it = 0, tcount = 0;
-            for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, tcount++) {
-                const Unit un = get_unit(p, unit, num_k);
-                const uint32_t buf = tcount % ACC;
-                if (tcount >= uint32_t(ACC) && !mbar_wait(&s.acc_empty[buf], ((tcount / ACC) - 1) & 1, abort_flag)) {
-                    give_up(abort_flag, p.status, kErrWaitAccEmpty);
-                    goto mma_done;
+        } else if (warp == kMmaWarp) {
+            // ---------------- MMA issuer ----------------
+            if (lane == 0) {
+                uint32_t it = 0, ccount = 0;   // K-slabs and accumulation chunks issued so far by this CTA
+                for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+                    const Unit un = get_unit(p, unit, num_k);
+                    for (int kc0 = un.k0; kc0 < un.k1; kc0 += chunk, ccount++) {
+                        const int kc1 = min(kc0 + chunk, un.k1);
+                        const uint32_t buf = ccount % ACC;
+                        if (ccount >= uint32_t(ACC) && !mbar_wait(&s.acc_empty[buf], ((ccount / ACC) - 1) & 1, abort_flag)) {
+                            give_up(abort_flag, p.status, kErrWaitAccEmpty);
+                            goto mma_done;
+                        }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t tmem_acc = tmem_base + buf * uint32_t(BN);
+                        for (int k = kc0; k < kc1; k++, it++) {
+                            int st = it % STAGES;
+                            uint32_t par = (it / STAGES) & 1;
+                            if (!mbar_wait(&s.full_tma[st], par, abort_flag)) {
+                                give_up(abort_flag, p.status, kErrWaitTma);
+                                goto mma_done;
+                            }
+                            if (!mbar_wait(&s.full_split[st], par, abort_flag)) {
+                                give_up(abort_flag, p.status, kErrWaitSplit);
+                                goto mma_done;
+                            }
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                            if (BF16) {
+                                const uint32_t a_bf = tmem_base + kColA + uint32_t(st * kACols);   // 8 columns (16 bf16) per K-step
+                                const uint64_t b_bf = umma_desc_k_major_bytes<BK * 2>(smem_u32(s.b_hi[st]));
+#pragma unroll
+                                for (int kk = 0; kk < BK / 16; kk++)
+                                    umma_bf16_ts(tmem_acc, a_bf + uint32_t(kk * 8), b_bf + uint64_t((kk * 32) >> 4), kIdesc, (k > kc0 || kk > 0) ? 1u : 0u);
+                                umma_commit(&s.empty[st]);
+                                continue;
+                            }
+                            uint64_t b_hi = umma_desc_k_major<BK>(smem_u32(s.b_hi[st])), b_lo = umma_desc_k_major<BK>(smem_u32(s.b_lo[BF16 ? 0 : st]));
+                            if (HYB) {
+                                // x_hi = the fp32 tile as it lies in shared memory (the MMA truncates it), x_lo from tensor memory
+                                const uint32_t a_lo = tmem_base + kColA + uint32_t(st * kACols);
+                                const uint64_t a_hi = umma_desc_k_major<BK>(smem_u32(s.a[st]));
+#pragma unroll
+                                for (int kk = 0; kk < BK / 8; kk++) {
+                                    uint64_t adv = uint64_t((kk * 8 * 4) >> 4);
+                                    umma_tf32_ts(tmem_acc, a_lo + uint32_t(kk * 8), b_hi + adv, kIdesc, (k > kc0 || kk > 0) ? 1u : 0u);
+                                    umma_tf32(tmem_acc, a_hi + adv, b_lo + adv, kIdesc, 1u);
+                                    umma_tf32(tmem_acc, a_hi + adv, b_hi + adv, kIdesc, 1u);
+                                }
+                            } else if (TS) {
+                                const uint32_t a_hi = tmem_base + kColA + uint32_t(st * kACols), a_lo = a_hi + uint32_t(BK);  // 8 columns per K-step
+#pragma unroll
+                                for (int kk = 0; kk < BK / 8; kk++) {
+                                    uint64_t adv = uint64_t((kk * 8 * 4) >> 4);  // 32 bytes per K-step inside the swizzle row
+                                    umma_tf32_ts(tmem_acc, a_lo + uint32_t(kk * 8), b_hi + adv, kIdesc, (k > kc0 || kk > 0) ? 1u : 0u);
+                                    umma_tf32_ts(tmem_acc, a_hi + uint32_t(kk * 8), b_lo + adv, kIdesc, 1u);
+                                    umma_tf32_ts(tmem_acc, a_hi + uint32_t(kk * 8), b_hi + adv, kIdesc, 1u);
+                                }
+                            } else {
+                                uint64_t a_hi = umma_desc_k_major<BK>(smem_u32(s.a[st])), a_lo = umma_desc_k_major<BK>(smem_u32(s.a_lo[st]));
+#pragma unroll
+                                for (int kk = 0; kk < BK / 8; kk++) {
+                                    uint64_t adv = uint64_t((kk * 8 * 4) >> 4);
+                                    umma_tf32(tmem_acc, a_lo + adv, b_hi + adv, kIdesc, (k > kc0 || kk > 0) ? 1u : 0u);
+                                    umma_tf32(tmem_acc, a_hi + adv, b_lo + adv, kIdesc, 1u);
+                                    umma_tf32(tmem_acc, a_hi + adv, b_hi + adv, kIdesc, 1u);
+                                }
+                            }
+                            umma_commit(&s.empty[st]);  // arrives once the MMAs above have consumed the stage
+                        }
+                        umma_commit(&s.acc_full[buf]);
+                    }
                 }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t tmem_acc = tmem_base + buf * uint32_t(BN);
-                for (int k = un.k0; k < un.k1; k++, it++) {
-                    int st = it % STAGES;
-                    uint32_t par = (it / STAGES) & 1;
-                    if (!mbar_wait(&s.full_tma[st], par, abort_flag)) {
-                        give_up(abort_flag, p.status, kErrWaitTma);
-                        goto mma_done;
-                    }
-                    if (!mbar_wait(&s.full_split[st], par, abort_flag)) {
-                        give_up(abort_flag, p.status, kErrWaitSplit);
-                        goto mma_done;
-                    }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    if (BF16) {
-                        const uint32_t a_bf = tmem_base + kColA + uint32_t(st * kACols);   // 8 columns (16 bf16) per K-step
-                        const uint64_t b_bf = umma_desc_k_major_bytes<BK * 2>(smem_u32(s.b_hi[st]));
-#pragma unroll
-                        for (int kk = 0; kk < BK / 16; kk++)
-                            umma_bf16_ts(tmem_acc, a_bf + uint32_t(kk * 8), b_bf + uint64_t((kk * 32) >> 4), kIdesc, (k > un.k0 || kk > 0) ? 1u : 0u);
-                        umma_commit(&s.empty[st]);
-                        continue;
-                    }
-                    uint64_t b_hi = umma_desc_k_major<BK>(smem_u32(s.b_hi[st])), b_lo = umma_desc_k_major<BK>(smem_u32(s.b_lo[BF16 ? 0 : st]));
-                    if (HYB) {
-                        // x_hi = the fp32 tile as it lies in shared memory (the MMA truncates it), x_lo from tensor memory
-                        const uint32_t a_lo = tmem_base + kColA + uint32_t(st * kACols);
-                        const uint64_t a_hi = umma_desc_k_major<BK>(smem_u32(s.a[st]));
-#pragma unroll
-                        for (int kk = 0; kk < BK / 8; kk++) {
-                            uint64_t adv = uint64_t((kk * 8 * 4) >> 4);
-                            umma_tf32_ts(tmem_acc, a_lo + uint32_t(kk * 8), b_hi + adv, kIdesc, (k > un.k0 || kk > 0) ? 1u : 0u);
-                            umma_tf32(tmem_acc, a_hi + adv, b_lo + adv, kIdesc, 1u);
-                            umma_tf32(tmem_acc, a_hi + adv, b_hi + adv, kIdesc, 1u);
-                        }
-                    } else if (TS) {
-                        const uint32_t a_hi = tmem_base + kColA + uint32_t(st * kACols), a_lo = a_hi + uint32_t(BK);  // 8 columns per K-step
-#pragma unroll
-                        for (int kk = 0; kk < BK / 8; kk++) {
-                            uint64_t adv = uint64_t((kk * 8 * 4) >> 4);  // 32 bytes per K-step inside the swizzle row
-                            umma_tf32_ts(tmem_acc, a_lo + uint32_t(kk * 8), b_hi + adv, kIdesc, (k > un.k0 || kk > 0) ? 1u : 0u);
-                            umma_tf32_ts(tmem_acc, a_hi + uint32_t(kk * 8), b_lo + adv, kIdesc, 1u);
-                            umma_tf32_ts(tmem_acc, a_hi + uint32_t(kk * 8), b_hi + adv, kIdesc, 1u);
-                        }
-                    } else {
-                        uint64_t a_hi = umma_desc_k_major<BK>(smem_u32(s.a[st])), a_lo = umma_desc_k_major<BK>(smem_u32(s.a_lo[st]));
-#pragma unroll
-                        for (int kk = 0; kk < BK / 8; kk++) {
-                            uint64_t adv = uint64_t((kk * 8 * 4) >> 4);
-                            umma_tf32(tmem_acc, a_lo + adv, b_hi + adv, kIdesc, (k > un.k0 || kk > 0) ? 1u : 0u);
-                            umma_tf32(tmem_acc, a_hi + adv, b_lo + adv, kIdesc, 1u);
-                            umma_tf32(tmem_acc, a_hi + adv, b_hi + adv, kIdesc, 1u);
-                        }
-                    }
-                    umma_commit(&s.empty[st]);  // arrives once the MMAs above have consumed the stage
-                }
-                umma_commit(&s.acc_full[buf]);
+            mma_done:;
             }
-        mma_done:;
         }
     } else if (warp >= kSplitWarp0) {
+        reg_set<Regs::split>();
         uint32_t it = 0;
         if (TS) {
             // ---------------- activation split: shared memory -> registers -> TMEM (hi | lo) ----------------
@@ -368,18 +431,22 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         if (lane == 0) mbar_arrive(&s.full_split[st]);
                         continue;
                     }
-                    uint32_t hi[BK], lo[BK];
-#pragma unroll
-                    for (int c = 0; c < BK / 4; c++) {
-                        float4 v = src[c ^ sw];   // x_hi = x as it is (the MMA truncates), x_lo = what the truncation drops
-                        hi[4 * c + 0] = __float_as_uint(v.x); lo[4 * c + 0] = __float_as_uint(lo_of_truncated(v.x));
-                        hi[4 * c + 1] = __float_as_uint(v.y); lo[4 * c + 1] = __float_as_uint(lo_of_truncated(v.y));
-                        hi[4 * c + 2] = __float_as_uint(v.z); lo[4 * c + 2] = __float_as_uint(lo_of_truncated(v.z));
-                        hi[4 * c + 3] = __float_as_uint(v.w); lo[4 * c + 3] = __float_as_uint(lo_of_truncated(v.w));
-                    }
+                    // x_hi = x as it is (the MMA truncates), x_lo = what the truncation drops; 16 columns at a time
                     const uint32_t a_col = tmem_base + lane_base + kColA + uint32_t(st * kACols);
-                    tmem_st(a_col, hi);
-                    tmem_st(a_col + uint32_t(BK), lo);
+#pragma unroll
+                    for (int h = 0; h < BK / 16; h++) {
+                        uint32_t hi[16], lo[16];
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            float4 v = src[(h * 4 + c) ^ sw];
+                            hi[4 * c + 0] = __float_as_uint(v.x); lo[4 * c + 0] = __float_as_uint(lo_of_truncated(v.x));
+                            hi[4 * c + 1] = __float_as_uint(v.y); lo[4 * c + 1] = __float_as_uint(lo_of_truncated(v.y));
+                            hi[4 * c + 2] = __float_as_uint(v.z); lo[4 * c + 2] = __float_as_uint(lo_of_truncated(v.z));
+                            hi[4 * c + 3] = __float_as_uint(v.w); lo[4 * c + 3] = __float_as_uint(lo_of_truncated(v.w));
+                        }
+                        tmem_st16(a_col + uint32_t(h * 16), hi);
+                        tmem_st16(a_col + uint32_t(BK + h * 16), lo);
+                    }
                     tmem_wait_st();
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
@@ -418,155 +485,136 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         }
     split_done:;
     } else {
-        // ---------------- epilogue (warps 0..3; warp w owns TMEM lanes 32w .. 32w+31) ----------------
-        const int q = warp - kEpiWarp0;
-        float* stage = s.stage_out[q];
-        uint32_t tcount = 0;
-        for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, tcount++) {
+        // ---------------- epilogue (warps 0..7; warp w owns TMEM lanes 32*(w%4).. and column half w/4) ----------------
+        reg_set<Regs::epi>();
+        constexpr int HALF = BN / 2;
+        const int q = warp & 3, chalf = warp >> 2;
+        float* stage = s.stage_out[warp];
+        const uint32_t lane_base = uint32_t(q * 32) << 16;
+        uint32_t ccount = 0;
+        for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
             const Unit un = get_unit(p, unit, num_k);
-            const uint32_t buf = tcount % ACC;
             int tm, tn;
             tile_coords(p, un.tile, tm, tn);
             const bool writes_partial = un.nparts > 1 && un.part > 0;
             const bool adds_partials = un.nparts > 1 && un.part == 0;
             float* ws_mine = p.ws + size_t(un.u) * size_t(BM * BN);
+            // ---- running sums of this thread's row over the K chunks of the unit ----
+            float sum[HALF];   // start from zero and always add: one code path keeps the register allocation tight
+#pragma unroll
+            for (int j = 0; j < HALF; j++) sum[j] = 0.f;
+            bool alive = true;
+            for (int kc0 = un.k0; kc0 < un.k1; kc0 += chunk, ccount++) {
+                const uint32_t buf = ccount % ACC;
+                if (!mbar_wait(&s.acc_full[buf], (ccount / ACC) & 1, abort_flag)) {
+                    give_up(abort_flag, p.status, kErrWaitAcc);
+                    alive = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tacc = tmem_base + buf * uint32_t(BN) + lane_base + uint32_t(chalf * HALF);
+                drain_chunk<HALF>(tacc, sum);
+                // the chunk is in registers: hand the TMEM buffer back
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
+            }
+            if (!alive) break;
             if (adds_partials) {
-                // the other K-parts of this tile run on other CTAs of this launch; wait for this warp's rows of each
+                // the other K-parts of this tile run on other CTAs of this launch; wait for this warp's share of each
                 int ok = 1;
                 if (lane == 0)
-                    for (int pp = 1; pp < un.nparts && ok; pp++) ok = flag_wait(p.flags + (un.u + pp) * 4 + q, abort_flag) ? 1 : 0;
+                    for (int pp = 1; pp < un.nparts && ok; pp++) ok = flag_wait(p.flags + (un.u + pp) * kEpiWarps + warp, abort_flag) ? 1 : 0;
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) {
                     give_up(abort_flag, p.status, kErrWaitPartial);
                     break;
                 }
             }
-            if (!mbar_wait(&s.acc_full[buf], (tcount / ACC) & 1, abort_flag)) {
-                give_up(abort_flag, p.status, kErrWaitAcc);
-                break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // ---- store: 16 columns at a time through shared memory, so that global accesses are row-contiguous ----
             const int row0 = q * 32;  // first row of this warp inside the tile
-            const int64_t col0 = int64_t(tn) * BN;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + buf * uint32_t(BN) + (uint32_t(q * 32) << 16) + uint32_t(c * 32), r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (c == BN / 32 - 1) {
-                    // the accumulator is in registers: hand the TMEM buffer back before storing
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
-                }
-                const int64_t col = col0 + c * 32;
-                if (col >= p.N) continue;  // warp-uniform
-                // thread `lane` holds row (row0 + lane), 32 consecutive columns: stage it row-major
+            const int64_t col_base = int64_t(tn) * BN + chalf * HALF;
+            const int cq = (lane & 3) * 4, rsub = lane >> 2;  // 4 lanes cover one 64-byte row segment, 8 rows per instruction
+            // Per-lane row pointers (rows i*8 + rsub, columns from col_base + cq): a group only adds a compile-time offset.
+            float* orow[4];
+            const float* rrow[4];
+            bool oks[4];
 #pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                    *reinterpret_cast<float4*>(stage + lane * kStagePad + j) =
-                        make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            for (int i = 0; i < 4; i++) {
+                const int64_t off = out_row_offset(p, tm, row0 + i * 8 + rsub, oks[i]) + col_base + cq;
+                orow[i] = p.out + off;
+                rrow[i] = p.residual + off;   // only dereferenced when p.residual is set
+            }
+            const float* brow = p.bias + col_base + cq;              // only dereferenced when p.bias is set
+            float* wrow = ws_mine + (row0 + rsub) * BN + chalf * HALF + cq;   // this lane's first row of the partial tile
+#pragma unroll
+            for (int g = 0; g < HALF / 16; g++) {
+                const int64_t col = col_base + g * 16;
+                if (col >= p.N && !writes_partial) continue;  // warp-uniform
+                // thread `lane` holds row (row0 + lane), 16 consecutive columns: stage them row-major
+#pragma unroll
+                for (int j = 0; j < 16; j += 4)
+                    *reinterpret_cast<float4*>(stage + lane * kStagePad + j) = make_float4(sum[g * 16 + j], sum[g * 16 + j + 1], sum[g * 16 + j + 2], sum[g * 16 + j + 3]);
                 __syncwarp();
-                const int cq = (lane & 7) * 4, rsub = lane >> 3;  // 8 lanes cover one 128-byte row segment, 4 rows per instruction
                 if (writes_partial) {
                     // raw partial sums, 128 x BN row-major; bias and activation belong to part 0
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        int rr = i * 4 + rsub;
-                        *reinterpret_cast<float4*>(ws_mine + (row0 + rr) * BN + c * 32 + cq) = *reinterpret_cast<const float4*>(stage + rr * kStagePad + cq);
-                    }
-                } else if (p.vec_out && col + 31 < p.N) {
-                    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (p.bias) b4 = *reinterpret_cast<const float4*>(p.bias + col + cq);
-                    float4 v[8];
+                    for (int i = 0; i < 4; i++)
+                        *reinterpret_cast<float4*>(wrow + i * 8 * BN + g * 16) = *reinterpret_cast<const float4*>(stage + (i * 8 + rsub) * kStagePad + cq);
+                } else if (p.vec_out && col + 15 < p.N) {
+                    float4 v[4];
 #pragma unroll
-                    for (int i = 0; i < 8; i++) v[i] = *reinterpret_cast<const float4*>(stage + (i * 4 + rsub) * kStagePad + cq);
+                    for (int i = 0; i < 4; i++) v[i] = *reinterpret_cast<const float4*>(stage + (i * 8 + rsub) * kStagePad + cq);
                     if (adds_partials) {
-                        // all eight loads of a part are issued before the first add: one L2 round trip per part and chunk
+                        // the loads of a part are issued before the first add: one L2 round trip per part and group
                         for (int pp = 1; pp < un.nparts; pp++) {
-                            const float* src = ws_mine + size_t(pp) * size_t(BM * BN) + row0 * BN + c * 32 + cq;
-                            float4 w[8];
+                            const float* src = wrow + size_t(pp) * size_t(BM * BN) + g * 16;
+                            float4 w[4];
 #pragma unroll
-                            for (int i = 0; i < 8; i++) w[i] = __ldcg(reinterpret_cast<const float4*>(src + (i * 4 + rsub) * BN));
+                            for (int i = 0; i < 4; i++) w[i] = __ldcg(reinterpret_cast<const float4*>(src + i * 8 * BN));
 #pragma unroll
-                            for (int i = 0; i < 8; i++) { v[i].x += w[i].x; v[i].y += w[i].y; v[i].z += w[i].z; v[i].w += w[i].w; }
+                            for (int i = 0; i < 4; i++) { v[i].x += w[i].x; v[i].y += w[i].y; v[i].z += w[i].z; v[i].w += w[i].w; }
                         }
                     }
-                    if (p.residual == nullptr) {
+                    if (p.bias) {
+                        const float4 b4 = *reinterpret_cast<const float4*>(brow + g * 16);
 #pragma unroll
-                        for (int i = 0; i < 8; i++) {
-                            int rr = i * 4 + rsub;
-                            float4 o = v[i];
-                            o.x += b4.x; o.y += b4.y; o.z += b4.z; o.w += b4.w;
-                            if (p.relu) {
-                                o.x = o.x > 0.f ? o.x : (o.x != o.x ? o.x : 0.f);
-                                o.y = o.y > 0.f ? o.y : (o.y != o.y ? o.y : 0.f);
-                                o.z = o.z > 0.f ? o.z : (o.z != o.z ? o.z : 0.f);
-                                o.w = o.w > 0.f ? o.w : (o.w != o.w ? o.w : 0.f);
-                            }
-                            bool row_ok;
-                            int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
-                            if (row_ok) *reinterpret_cast<float4*>(p.out + off + col + cq) = o;
-                        }
-                    } else {
-                        // a folded residual Add: the eight residual loads are issued before any store, (acc + bias) + residual
-                        // is the order of the two separate nodes
-                        int64_t offs[8];
-                        bool oks[8];
-                        float4 r4[8];
-#pragma unroll
-                        for (int i = 0; i < 8; i++) {
-                            offs[i] = out_row_offset(p, tm, row0 + i * 4 + rsub, oks[i]);
-                            r4[i] = oks[i] ? *reinterpret_cast<const float4*>(p.residual + offs[i] + col + cq) : make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
-#pragma unroll
-                        for (int i = 0; i < 8; i++) {
-                            float4 o = v[i];
-                            o.x = (o.x + b4.x) + r4[i].x; o.y = (o.y + b4.y) + r4[i].y; o.z = (o.z + b4.z) + r4[i].z; o.w = (o.w + b4.w) + r4[i].w;
-                            if (p.relu) {
-                                o.x = o.x > 0.f ? o.x : (o.x != o.x ? o.x : 0.f);
-                                o.y = o.y > 0.f ? o.y : (o.y != o.y ? o.y : 0.f);
-                                o.z = o.z > 0.f ? o.z : (o.z != o.z ? o.z : 0.f);
-                                o.w = o.w > 0.f ? o.w : (o.w != o.w ? o.w : 0.f);
-                            }
-                            if (oks[i]) *reinterpret_cast<float4*>(p.out + offs[i] + col + cq) = o;
-                        }
+                        for (int i = 0; i < 4; i++) { v[i].x += b4.x; v[i].y += b4.y; v[i].z += b4.z; v[i].w += b4.w; }
                     }
-                } else if (!adds_partials) {
-                    // one row per instruction, lanes on consecutive columns
-                    const bool col_ok = col + lane < p.N;
-                    const float b = (p.bias && col_ok) ? __ldg(p.bias + col + lane) : 0.f;
-                    if (p.residual == nullptr) {   // kept free of loads: the stores of consecutive rows pipeline
-#pragma unroll 4
-                        for (int rr = 0; rr < 32; rr++) {
-                            float v = stage[rr * kStagePad + lane] + b;
-                            if (p.relu) v = v > 0.f ? v : (v != v ? v : 0.f);
-                            bool row_ok;
-                            int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
-                            if (col_ok && row_ok) p.out[off + col + lane] = v;
+                    if (p.residual != nullptr) {
+                        // a folded residual Add, (acc + bias) + residual as the two separate nodes do; the loads are issued together
+                        float4 r4[4];
+#pragma unroll
+                        for (int i = 0; i < 4; i++) r4[i] = oks[i] ? *reinterpret_cast<const float4*>(rrow[i] + g * 16) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (int i = 0; i < 4; i++) { v[i].x += r4[i].x; v[i].y += r4[i].y; v[i].z += r4[i].z; v[i].w += r4[i].w; }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        float4 o = v[i];
+                        if (p.relu) {
+                            o.x = relu_keep_nan(o.x); o.y = relu_keep_nan(o.y); o.z = relu_keep_nan(o.z); o.w = relu_keep_nan(o.w);
                         }
-                    } else {
-                        for (int rr = 0; rr < 32; rr++) {
-                            float v = stage[rr * kStagePad + lane] + b;
-                            bool row_ok;
-                            int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
-                            if (col_ok && row_ok) v += p.residual[off + col + lane];
-                            if (p.relu) v = v > 0.f ? v : (v != v ? v : 0.f);
-                            if (col_ok && row_ok) p.out[off + col + lane] = v;
-                        }
+                        if (oks[i]) *reinterpret_cast<float4*>(orow[i] + g * 16) = o;
                     }
                 } else {
-                    const bool col_ok = col + lane < p.N;
-                    const float b = (p.bias && col_ok) ? __ldg(p.bias + col + lane) : 0.f;
-                    for (int rr = 0; rr < 32; rr++) {
-                        float v = stage[rr * kStagePad + lane];
-                        for (int pp = 1; pp < un.nparts; pp++) v += __ldcg(ws_mine + size_t(pp) * size_t(BM * BN) + (row0 + rr) * BN + c * 32 + lane);
+                    // ragged or unaligned output: two rows per instruction, 16 lanes on consecutive columns
+                    const int cl = lane & 15, r2 = lane >> 4;
+                    const bool col_ok = col + cl < p.N;
+                    const float b = (p.bias && col_ok) ? __ldg(p.bias + col + cl) : 0.f;
+#pragma unroll 1
+                    for (int i = 0; i < 16; i++) {
+                        const int rr = i * 2 + r2;
+                        float v = stage[rr * kStagePad + cl];
+                        if (adds_partials)
+                            for (int pp = 1; pp < un.nparts; pp++)
+                                v += __ldcg(ws_mine + size_t(pp) * size_t(BM * BN) + (row0 + rr) * BN + chalf * HALF + g * 16 + cl);
                         v += b;
                         bool row_ok;
-                        int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
-                        if (p.residual && col_ok && row_ok) v += p.residual[off + col + lane];
-                        if (p.relu) v = v > 0.f ? v : (v != v ? v : 0.f);
-                        if (col_ok && row_ok) p.out[off + col + lane] = v;
+                        const int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
+                        if (p.residual && col_ok && row_ok) v += p.residual[off + col + cl];
+                        if (p.relu) v = relu_keep_nan(v);
+                        if (col_ok && row_ok) p.out[off + col + cl] = v;
                     }
                 }
                 __syncwarp();
@@ -574,11 +622,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             if (writes_partial) {
                 __threadfence();
                 __syncwarp();
-                if (lane == 0) flag_set(p.flags + un.u * 4 + q, 1);
+                if (lane == 0) flag_set(p.flags + un.u * kEpiWarps + warp, 1);
             } else if (adds_partials) {
                 __syncwarp();   // every lane has read its partials: lower the flags for the next launch
                 if (lane == 0)
-                    for (int pp = 1; pp < un.nparts; pp++) flag_set(p.flags + (un.u + pp) * 4 + q, 0);
+                    for (int pp = 1; pp < un.nparts; pp++) flag_set(p.flags + (un.u + pp) * kEpiWarps + warp, 0);
             }
         }
     }
@@ -612,11 +660,7 @@ TailSplit plan_tail(int64_t tiles, int64_t K, int bn, int sms, bool allowed) {
     TailSplit t{tiles, 0, 1, 0.0, 0.0};
     t.tile_us = double((K + 15) / 16) * 0.43 * double(bn) / 256.0;
     t.tail_us = tiles % std::max(sms, 1) ? t.tile_us : 0.0;
-    static const bool disabled = [] {  // debug override: FXF_TC_SPLITK=0 computes every tile whole
-        const char* e = std::getenv("FXF_TC_SPLITK");
-        return e && e[0] == '0';
-    }();
-    if (!allowed || disabled || sms <= 1) return t;
+    if (!allowed || sms <= 1) return t;
     const int64_t R = tiles % sms;
     if (R == 0) return t;
     const int64_t smax = std::min<int64_t>(std::min<int64_t>(sms / R, K / 64), 4);
@@ -692,7 +736,11 @@ int make_map_nhwc(CUtensorMap* map, const float* base, int N, int H, int W, int 
     return 0;
 }
 
-template <int BN, int BK, int STAGES, int ACC, bool TS, bool BF16 = false, bool HYB = false>
+// K-elements per accumulation chain: the tensor core's truncating adds cost about 4e-8 of the result's scale per K-element
+// of a chain; 128 keeps a chain's share below 1e-5 while a chunk (at least 12 MMAs) still hides the epilogue warps' drain.
+constexpr int kChunkK = 128;
+
+template <int BN, int BK, int STAGES, bool TS, bool BF16 = false, bool HYB = false>
 int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, const ConvGeom* geom = nullptr) {
     CUtensorMap mx, mhi, mlo;
     if (cv) {
@@ -725,14 +773,15 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
     int dev = 0;
     FXF_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        FXF_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, BK, STAGES, ACC, TS, BF16, HYB>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        FXF_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, BK, STAGES, TS, BF16, HYB>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
     TailSplit ts = plan_tail(tiles, a.K, BN, ctx.sm_count, ctx.gemm_ws != nullptr && ctx.gemm_flags != nullptr);
-    if (ts.parts > 1 && (size_t(ts.tail) * ts.parts * size_t(BM * BN) * sizeof(float) > ctx.gemm_ws_bytes || ts.tail * ts.parts * 4 > ctx.gemm_flag_count))
+    if (ts.parts > 1 && (size_t(ts.tail) * ts.parts * size_t(BM * BN) * sizeof(float) > ctx.gemm_ws_bytes || ts.tail * ts.parts * kEpiWarps > ctx.gemm_flag_count))
         ts = TailSplit{tiles, 0, 1, 0.0, 0.0};
     p.full_tiles = int(ts.full); p.tail_tiles = int(ts.tail); p.tail_split = ts.parts;
+    p.chunk_slabs = std::max(1, (ctx.tc_chunk_k > 0 ? ctx.tc_chunk_k : kChunkK) / BK);
     p.ws = ctx.gemm_ws; p.flags = ctx.gemm_flags;
     const int64_t units = ts.full + ts.tail * ts.parts;
     int grid = int(units < ctx.sm_count ? units : ctx.sm_count);
@@ -744,7 +793,7 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
         tag_launch(ctx, BF16 ? "gemm_bf16_tcgen05" : "gemm_tf32x3_tcgen05", 2.0 * double(a.M) * double(a.N) * double(a.K),
                    4.0 * (double(a.M) * a.K + double(a.N) * a.K + double(a.N) + double(a.M) * a.N));
     }
-    gemm_tf32x3_kernel<BN, BK, STAGES, ACC, TS, BF16, HYB><<<grid, kThreads, smem, ctx.stream>>>(mx, mhi, mlo, p);
+    gemm_tf32x3_kernel<BN, BK, STAGES, TS, BF16, HYB><<<grid, kThreads, smem, ctx.stream>>>(mx, mhi, mlo, p);
     FXF_LAUNCHED(ctx);
     return 0;
 }
@@ -796,58 +845,43 @@ int gemm_tc_pick_bn(int64_t M, int64_t N, int sm_count, int64_t K) {
     return best;
 }
 
-// Where the MMAs take A from.  With A in shared memory the kernel saturates the shared-memory data pipe (192-wide
-// tiles: operand reads 48 % + split loads/stores 48 % of its wavefronts, tensor pipe 62 %); from tensor memory the
-// split writes nothing to shared memory and the MMA reads only B there.  Measured on B200: 128-wide tiles gain 40 %,
-// 192-wide 5-7 %.  256-wide tiles keep A in shared memory: TMEM has no room for two 256-column accumulators plus
-// A stages, and one accumulator (no epilogue overlap) costs more than the shared-memory pressure.
-// Debug override: FXF_TC_A=smem | tmem forces one variant for every width.
-static bool a_from_smem(int bn) {
-    static const int mode = [] {
-        const char* e = std::getenv("FXF_TC_A");
-        return !e ? 0 : (e[0] == 's' ? 1 : (e[0] == 't' ? 2 : 0));
-    }();
-    return mode == 1 || (mode == 0 && bn > 192);
-}
-
-// Debug override: FXF_TC_N64=0 keeps 128-wide tiles for N <= 64.
-static bool narrow_tiles() {
-    static const bool on = [] {
-        const char* e = std::getenv("FXF_TC_N64");
-        return !(e && e[0] == '0');
-    }();
-    return on;
+// Kernel variant per tile width.  Where the MMAs take A from decides it: with both operands in shared memory the kernel
+// saturates the shared-memory data pipe (192-wide tiles: operand reads 48 % + split loads/stores 48 % of its wavefronts,
+// tensor pipe 62 %); from tensor memory the split writes nothing to shared memory and the MMA reads only B there (measured
+// on B200: 128-wide tiles gain 40 %, 192-wide 5-7 %).  256-wide tiles keep A in shared memory: TMEM (512 columns) holds the
+// two 256-column accumulators and nothing else.  224 = the widest tile that leaves TMEM room for x_lo stages (hybrid).
+//   256  A in shared memory (x_hi = the tile as delivered, x_lo twin buffer), BK 16, 4 stages
+//   224  hybrid: x_hi read from shared memory as delivered, x_lo from tensor memory, BK 16, 4 stages
+//   192  A (hi and lo) in tensor memory, BK 16, 4 stages
+//   128  A in tensor memory, BK 32, 4 stages;  64: the same with 64-wide tiles for N <= 64
+const char* gemm_tc_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool k_split, bool few_rows, int* bn_out) {
+    int bn = gemm_tc_pick_bn(M, N, sm_count, k_split ? K : 0);
+    if (N <= 128) bn = N <= 64 ? 64 : 128;
+    if (few_rows && M < 64) bn = N <= 64 ? 64 : 128;   // a weight-streaming problem: more, narrower tiles keep more SMs loading
+    if (bn_out) *bn_out = bn;
+    switch (bn) {
+        case 256: return "tcgen05-tf32x3-128x256-smemA";
+        case 224: return "tcgen05-tf32x3-128x224-hybridA";
+        case 192: return "tcgen05-tf32x3-128x192-tmemA";
+        case 128: return "tcgen05-tf32x3-128x128-tmemA";
+        default: return "tcgen05-tf32x3-128x64-tmemA";
+    }
 }
 
 int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows) {
     FXF_CHECK(gemm_tc_supported(a, allow_few_rows), "tensor-core GEMM called with an unsupported problem");
-    // Debug override: FXF_TC_BN=256|192|128 forces the tile width.
-    static const int forced = [] {
-        const char* e = std::getenv("FXF_TC_BN");
-        return e ? std::atoi(e) : 0;
-    }();
-    int bn = forced ? forced : gemm_tc_pick_bn(a.M, a.N, ctx.sm_count, ctx.gemm_ws ? a.K : 0);
-    if (a.N <= 128) bn = 128;
-    if (allow_few_rows && a.M < 64 && !forced) bn = 128;   // a weight-streaming problem: more, narrower tiles keep more SMs loading
+    int bn = 0;
+    gemm_tc_variant(a.M, a.N, a.K, ctx.sm_count, ctx.gemm_ws != nullptr, allow_few_rows, &bn);
     if (a.w_is_bf16) {  // bf16 mode: one product per logical product, A converted into tensor memory
-        if (bn >= 192 && a.N > 128) return launch_tc<192, 32, 6, 2, true, true>(a, ctx);
-        return launch_tc<128, 32, 8, 2, true, true>(a, ctx);
-    }
-    if (bn == 224) return launch_tc<224, 16, 4, 2, true, false, true>(a, ctx);
-    if (a_from_smem(bn)) {
-        switch (bn) {
-            case 256: return launch_tc<256, 16, 4, 2, false>(a, ctx);
-            case 192: return launch_tc<192, 16, 5, 2, false>(a, ctx);
-            default: return launch_tc<128, 32, 3, 2, false>(a, ctx);
-        }
+        if (bn >= 192 && a.N > 128) return launch_tc<192, 32, 6, true, true>(a, ctx);
+        return launch_tc<128, 32, 8, true, true>(a, ctx);
     }
     switch (bn) {
-        case 256: return launch_tc<256, 16, 5, 1, true>(a, ctx);
-        case 192: return launch_tc<192, 16, 4, 2, true>(a, ctx);
-        default:
-            // N <= 64 (64-channel convolutions as GEMM, narrow heads): a 64-wide tile does not multiply 64 columns of padding
-            if (a.N <= 64 && narrow_tiles()) return launch_tc<64, 32, 4, 2, true>(a, ctx);
-            return launch_tc<128, 32, 4, 2, true>(a, ctx);
+        case 256: return launch_tc<256, 16, 4, false>(a, ctx);
+        case 224: return launch_tc<224, 16, 4, true, false, true>(a, ctx);
+        case 192: return launch_tc<192, 16, 4, true>(a, ctx);
+        case 128: return launch_tc<128, 32, 4, true>(a, ctx);
+        default: return launch_tc<64, 32, 4, true>(a, ctx);
     }
 }
 
@@ -916,27 +950,20 @@ int launch_conv_tc(const ConvTcArgs& c, ExecCtx& ctx) {
     a.K = int64_t(c.KH) * c.KW * c.C;
     a.ldo = c.O;
     a.relu = c.relu;
-    int bn = a.N <= 128 ? 128 : gemm_tc_pick_bn(a.M, a.N, ctx.sm_count, ctx.gemm_ws ? a.K : 0);
+    int bn = 0;
+    gemm_tc_variant(a.M, a.N, a.K, ctx.sm_count, ctx.gemm_ws != nullptr, false, &bn);
     if (c.w_is_bf16) {
         a.w_is_bf16 = true;
         FXF_CHECK(c.C % 32 == 0, "conv (tensor core, bf16): input channels must be a multiple of 32");
-        if (bn >= 192) return launch_tc<192, 32, 6, 2, true, true>(a, ctx, &c, &g);
-        return launch_tc<128, 32, 8, 2, true, true>(a, ctx, &c, &g);
-    }
-    if (bn == 224) return launch_tc<224, 16, 4, 2, true, false, true>(a, ctx, &c, &g);
-    if (a_from_smem(bn)) {
-        switch (bn) {
-            case 256: return launch_tc<256, 16, 4, 2, false>(a, ctx, &c, &g);
-            case 192: return launch_tc<192, 16, 5, 2, false>(a, ctx, &c, &g);
-            default: return launch_tc<128, 16, 6, 2, false>(a, ctx, &c, &g);
-        }
+        if (bn >= 192) return launch_tc<192, 32, 6, true, true>(a, ctx, &c, &g);
+        return launch_tc<128, 32, 8, true, true>(a, ctx, &c, &g);
     }
     switch (bn) {
-        case 256: return launch_tc<256, 16, 5, 1, true>(a, ctx, &c, &g);
-        case 192: return launch_tc<192, 16, 4, 2, true>(a, ctx, &c, &g);
-        default:
-            if (a.N <= 64 && narrow_tiles()) return c.C % 32 == 0 ? launch_tc<64, 32, 4, 2, true>(a, ctx, &c, &g) : launch_tc<64, 16, 8, 2, true>(a, ctx, &c, &g);
-            return c.C % 32 == 0 ? launch_tc<128, 32, 4, 2, true>(a, ctx, &c, &g) : launch_tc<128, 16, 8, 2, true>(a, ctx, &c, &g);
+        case 256: return launch_tc<256, 16, 4, false>(a, ctx, &c, &g);
+        case 224: return launch_tc<224, 16, 4, true, false, true>(a, ctx, &c, &g);
+        case 192: return launch_tc<192, 16, 4, true>(a, ctx, &c, &g);
+        case 128: return c.C % 32 == 0 ? launch_tc<128, 32, 4, true>(a, ctx, &c, &g) : launch_tc<128, 16, 8, true>(a, ctx, &c, &g);
+        default: return c.C % 32 == 0 ? launch_tc<64, 32, 4, true>(a, ctx, &c, &g) : launch_tc<64, 16, 8, true>(a, ctx, &c, &g);
     }
 }
 

@@ -71,7 +71,7 @@ int launch_gemm(const GemmArgs& a, ExecCtx& ctx) {
 
 std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count) {
     if (gemm_mode == FXF_GEMM_BF16 && gemm_tc_shape_ok(a.M, a.N, a.K) && a.K % 8 == 0) return std::string("tcgen05-bf16-128x") + (a.N > 128 ? "192" : "128");
-    if (gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(a.M, a.N, a.K)) return "tcgen05-tf32x3-128x" + std::to_string(gemm_tc_pick_bn(a.M, a.N, sm_count, a.K));
+    if (gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(a.M, a.N, a.K)) return gemm_tc_variant(a.M, a.N, a.K, sm_count, true, false, nullptr);
     static const char* names[] = {"simt128x128", "simt64x64", "simt32x32", "skinny32x8"};
     return names[simt_tile_choice(a.M, a.N, sm_count)];
 }
@@ -197,7 +197,7 @@ int run_linear(Registry& reg, const TensorIds& in, const TensorIds& out, bool re
     FXF_CHECK(pl != nullptr && pl->n == 2 && pl->prepared, "%s: the node was not prepared", who);
     GemmArgs g;
     fill_gemm(g, static_cast<const float*>(x.ptr), pl->s[0], &pl->s[1], static_cast<float*>(o.ptr) + pl->col_off, M, K, N, relu);
-    if (pl->col_off == 0 && pl->s[0].rows() == N) apply_fusion(ctx, g);   // never with a column-sharded output
+    if (pl->col_off == 0 && pl->s[0].rows() == N) apply_fusion(ctx, g, false);   // never with a column-sharded output
     return launch_gemm(g, ctx);
 }
 
@@ -250,6 +250,22 @@ std::unique_ptr<NodePlan> plan_linear(const Registry& reg, const TensorIds& in, 
     return p;
 }
 
+// Last step of a row-parallel product (the second GEMM of MHA / CrossMHA / FeedForward).  Single GPU or a node that is
+// replicated on every rank: the GEMM with a folded residual Add, if any.  Sharded node: the GEMM leaves this rank's
+// partial sums in the node's own output tensor, then either ONE fused exchange (sum over the ranks + residual + LayerNorm,
+// kernels/tp_exchange.cu) when the engine folded the following nodes into it, or the plain all-reduce.
+static int finish_row_parallel(GemmArgs& g2, int64_t M, int64_t N, bool sharded, ExecCtx& ctx) {
+    if (sharded && ctx.tp_size > 1 && ctx.xchg.enabled) {
+        FXF_CHECK(g2.ldo == N && tp_exchange_usable(ctx.xchg, g2.out, M, N, ctx), "tensor-parallel exchange: the folded nodes cannot be served");
+        if (launch_gemm(g2, ctx)) return 1;
+        ctx.xchg.consumed = true;
+        return launch_tp_exchange(ctx.xchg, g2.out, M, N, ctx);
+    }
+    apply_fusion(ctx, g2, sharded);
+    if (launch_gemm(g2, ctx)) return 1;
+    return sharded ? tp_all_reduce_sum(g2.out, M * N, ctx) : 0;
+}
+
 // ---- FeedForward ------------------------------------------------------------------------------
 // slices: s[0] = w1 rows of this rank [Fl, D], s[1] = b1 entries [Fl], s[2] = w2 columns of this rank [P, Fl], s[3] = b2
 int k_feedforward(Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const NodePlan* plan, ExecCtx& ctx) {
@@ -272,9 +288,7 @@ int k_feedforward(Registry& reg, const TensorIds& in, const TensorIds& out, cons
     fill_gemm(g1, static_cast<const float*>(x.ptr), pl->s[0], &pl->s[1], hidden, M, K, Fl, true);
     if (launch_gemm(g1, ctx)) return 1;
     fill_gemm(g2, hidden, pl->s[2], &pl->s[3], static_cast<float*>(o.ptr), M, Fl, P, false);
-    apply_fusion(ctx, g2);
-    if (launch_gemm(g2, ctx)) return 1;
-    return tp_all_reduce_sum(g2.out, M * P, ctx);
+    return finish_row_parallel(g2, M, P, pl->tp_sharded, ctx);
 }
 
 std::unique_ptr<NodePlan> plan_feedforward(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const PlanEnv& env) {
@@ -290,6 +304,7 @@ std::unique_ptr<NodePlan> plan_feedforward(const Registry& reg, const TensorIds&
     Slice& s_b1 = p->add(2, F, 1);
     Slice& s_w2 = p->add(3, P, F);
     Slice& s_b2 = p->add(4, P, 1);
+    p->tp_sharded = n > 1;
     if (n > 1) {
         s_w1.row0[0] = f0; s_w1.nrow[0] = Fl; s_w1.whole = false;
         s_b1.row0[0] = f0; s_b1.nrow[0] = Fl; s_b1.whole = false;
@@ -366,9 +381,7 @@ int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params
 
     GemmArgs g2;
     fill_gemm(g2, cx, pl->s[2], &pl->s[3], static_cast<float*>(o.ptr), M, Dl, D, false);
-    apply_fusion(ctx, g2);
-    if (launch_gemm(g2, ctx)) return 1;
-    return tp_all_reduce_sum(g2.out, M * D, ctx);
+    return finish_row_parallel(g2, M, D, pl->tp_sharded, ctx);
 }
 
 std::unique_ptr<NodePlan> plan_mha(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& env) {
@@ -382,6 +395,7 @@ std::unique_ptr<NodePlan> plan_mha(const Registry& reg, const TensorIds& in, con
     const int64_t Hl = H / n, h0 = (n > 1 ? env.tp_rank : 0) * Hl, Dl = Hl * hd;
     pl->heads_local = Hl;
     pl->head0 = h0;
+    pl->tp_sharded = n > 1;
     Slice& s_wq = pl->add(2, QKV, D);
     Slice& s_bq = pl->add(3, QKV, 1);
     Slice& s_wo = pl->add(4, D, D);
@@ -406,7 +420,7 @@ std::unique_ptr<NodePlan> plan_mha(const Registry& reg, const TensorIds& in, con
     pl->reserve(s_bo, false);
     pl->M = M;
     pl->scratch_bytes = size_t(M) * size_t(3 * Dl + Dl) * sizeof(float);
-    const bool tc_attn = env.gemm_mode != FXF_GEMM_FP32_SIMT && hd == 64 && T % 4 == 0 && T >= 16 && Dl % 4 == 0;
+    const bool tc_attn = env.gemm_mode != FXF_GEMM_FP32_SIMT && hd == 64 && T % 4 == 0 && T >= 16 && T <= 4096 && Dl % 4 == 0;   // the tcgen05 kernel covers at most 32 blocks of 128 keys
     if (tc_attn) pl->scratch_bytes += attention_tc_scratch_bytes(B, T, Hl);
     pl->flops = 2.0 * M * double(3 * Dl) * D + 4.0 * double(B) * Hl * double(T) * T * hd + 2.0 * double(M) * D * Dl;
     pl->bytes = 4.0 * (2.0 * double(M) * D + double(3 * Dl) * D + 3 * Dl + double(D) * Dl + D) + double(reg[in[1]].nbytes);
@@ -488,9 +502,7 @@ int k_cross_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const 
 
     GemmArgs g2;
     fill_gemm(g2, cx, pl->s[4], &pl->s[5], static_cast<float*>(o.ptr), Mq, Dl, D, false);
-    apply_fusion(ctx, g2);
-    if (launch_gemm(g2, ctx)) return 1;
-    return tp_all_reduce_sum(g2.out, Mq * D, ctx);
+    return finish_row_parallel(g2, Mq, D, pl->tp_sharded, ctx);
 }
 
 std::unique_ptr<NodePlan> plan_cross_mha(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& env) {
@@ -505,6 +517,7 @@ std::unique_ptr<NodePlan> plan_cross_mha(const Registry& reg, const TensorIds& i
     const int64_t Hl = H / n, h0 = (n > 1 ? env.tp_rank : 0) * Hl, Dl = Hl * hd;
     pl->heads_local = Hl;
     pl->head0 = h0;
+    pl->tp_sharded = n > 1;
     Slice& s_wq = pl->add(3, D, D);
     Slice& s_bq = pl->add(4, D, 1);
     Slice& s_wkv = pl->add(5, KV, D);
@@ -537,7 +550,7 @@ std::unique_ptr<NodePlan> plan_cross_mha(const Registry& reg, const TensorIds& i
     pl->reserve(s_bo, false);
     pl->M = Mq;
     pl->scratch_bytes = (size_t(Mq) * size_t(2 * Dl) + size_t(Mk) * size_t(2 * Dl)) * sizeof(float);
-    const bool tc_attn = env.gemm_mode != FXF_GEMM_FP32_SIMT && hd == 64 && Tk % 4 == 0 && Tk >= 16 && Dl % 4 == 0;
+    const bool tc_attn = env.gemm_mode != FXF_GEMM_FP32_SIMT && hd == 64 && Tk % 4 == 0 && Tk >= 16 && Tk <= 4096 && Dl % 4 == 0;
     if (tc_attn) pl->scratch_bytes += attention_tc_scratch_bytes(B, Tk, Hl);
     pl->flops = 2.0 * double(Mq) * Dl * D + 2.0 * double(Mk) * 2 * Dl * D + 4.0 * double(B) * Hl * double(Tq) * Tk * hd + 2.0 * double(Mq) * D * Dl;
     pl->bytes = 4.0 * (2.0 * double(Mq) * D + double(Mk) * D + 2.0 * double(Dl) * D + 2.0 * double(Dl) * D + 3 * Dl + D) + double(reg[in[2]].nbytes);

@@ -45,7 +45,25 @@ struct PeerMap {
     size_t shared_bytes = 0;        // offsets below this mean the same tensor on every rank (the planner's arena)
     size_t flags_off = 0;           // barrier flags [peer][block] of the peer all-reduce, same offset on every rank
     size_t epoch_off = 0;           // two ints: epoch, finished-block counter
-    int grid = 0;                   // blocks of the peer all-reduce kernel (fixes the flag layout)
+    int grid = 0;                   // blocks of the peer exchange kernels (fixes the flag layout)
+    // wait budgets of the two peer barriers of an exchange; the first also absorbs the skew between the ranks' host threads
+    unsigned long long start_budget_ns = 20000000000ull, end_budget_ns = 2000000000ull;
+};
+
+// The exchange step of a row-parallel product under tensor parallelism, fused with what follows it in a pre-LN transformer
+// block: the ranks' partial [M,D] outputs are summed, the residual is added and the rows are normalised by ONE kernel over
+// peer memory (kernels/tp_exchange.cu).  Set by the engine around a sharded MHA / CrossMHA / FeedForward node whose
+// following Add (+ LayerNorm) or AddLayerNorm nodes were folded into it.
+struct TpExchange {
+    bool enabled = false;
+    const float* residual = nullptr;   // the other operand of the folded Add (this rank's rows of it are read)
+    float* x_out = nullptr;            // output of the folded Add: the new residual stream (NULL for AddLayerNorm)
+    float* y_out = nullptr;            // output of the folded LayerNorm / AddLayerNorm (NULL: a plain Add was folded)
+    const float* gamma = nullptr;
+    const float* beta = nullptr;
+    float eps = 0.f;
+    bool replicate_x = false;          // x_out is read outside this scheme: every rank gets every row of it
+    bool consumed = false;
 };
 
 // A residual Add / AddRelu node folded into the contraction that precedes it: the owner of that node's final GEMM writes
@@ -69,12 +87,14 @@ struct ExecCtx {
     void* comm = nullptr;          // fxf_comm* (NCCL communicator wrapper), owned by the caller
     const PeerMap* peers = nullptr;  // set when the ranks' allocations are mapped into each other: all-reduce over peer memory
     EpilogueFusion fuse;             // set by the engine around a node whose following Add was folded into it
+    TpExchange xchg;                 // set by the engine around a sharded node whose exchange absorbs the following Add / LayerNorm
     // workspace of the tensor-core GEMM's K-split last round: partial tiles and their ready flags (zero between
     // launches).  Without it every tile is computed whole.
     float* gemm_ws = nullptr;
     size_t gemm_ws_bytes = 0;
     int* gemm_flags = nullptr;
     int gemm_flag_count = 0;
+    int tc_chunk_k = 0;            // K-elements per tensor-core accumulation chain (0 = the kernel's default)
     // profiling: when `trace` is set every launch appends a record carrying the current tag
     std::vector<LaunchRecord>* trace = nullptr;
     int cur_node = -1;
@@ -88,12 +108,13 @@ inline void tag_launch(ExecCtx& c, const char* name, double flops, double bytes)
 }
 int trace_after_launch(ExecCtx& ctx);
 // Called by the op that owns the final GEMM of a node: redirects the output and attaches the residual of a folded Add.
-// Under tensor parallelism the partial outputs are summed afterwards, so only rank 0 adds the residual (like the bias).
+// `partial`: the node is sharded over the tensor-parallel ranks and its outputs are summed afterwards, so only rank 0 adds
+// the residual (like the bias); a node that is replicated on every rank adds it everywhere.
 template <class Args>
-inline void apply_fusion(ExecCtx& ctx, Args& g) {
+inline void apply_fusion(ExecCtx& ctx, Args& g, bool partial) {
     if (ctx.fuse.out == nullptr) return;
     g.out = ctx.fuse.out;
-    g.residual = (ctx.tp_size <= 1 || ctx.tp_rank == 0) ? ctx.fuse.residual : nullptr;
+    g.residual = (!partial || ctx.tp_rank == 0) ? ctx.fuse.residual : nullptr;
     g.relu = g.relu || ctx.fuse.relu;
     ctx.fuse.consumed = true;
 }
@@ -107,6 +128,7 @@ struct NodePlan {
     void* persist = nullptr;    // assigned by the engine before prepare()
     double flops = 0, bytes = 0;  // algorithmic work of the node
     std::string variant;        // which kernel variant was chosen (for describe / profiling)
+    bool tp_sharded = false;    // the node computes a partial result on each tensor-parallel rank (summed by an exchange)
     // Called once after device memory exists (constants uploaded).  May launch kernels.
     virtual int prepare(Registry&, const TensorIds&, const TensorIds&, const Params&, ExecCtx&) { return 0; }
 };
@@ -250,6 +272,8 @@ bool gemm_tc_supported(const GemmArgs& a, bool allow_few_rows = false);
 bool gemm_tc_shape_ok(int64_t M, int64_t N, int64_t K);
 // K > 0: the launch may cut the tiles of its last round along K (needs the context's GEMM workspace)
 int gemm_tc_pick_bn(int64_t M, int64_t N, int sm_count, int64_t K = 0);
+// Name of the tensor-core kernel variant launch_gemm_tc takes for a problem (and its tile width): the one dispatch rule.
+const char* gemm_tc_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool k_split, bool few_rows, int* bn_out);
 int launch_split_tf32(const float* w, float* hi, float* lo, int64_t n, ExecCtx& ctx);
 int simt_tile_choice(int64_t M, int64_t N, int sm_count);
 std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count);
@@ -297,9 +321,15 @@ struct AttnArgs {
 int launch_attention(const AttnArgs& a, ExecCtx& ctx);
 // Sum `n` floats in place over the tensor-parallel ranks (NCCL all-reduce on ctx.stream); no-op for tp_size 1.
 int tp_all_reduce_sum(float* buf, int64_t n, ExecCtx& ctx);
-// Peer-memory all-reduce (kernels/allreduce_p2p.cu) and the IPC exchange that sets it up (tp_comm.cpp).
+// Peer-memory exchanges (kernels/tp_exchange.cu) and the IPC exchange that sets them up (tp_comm.cpp).
 bool p2p_all_reduce_usable(const float* buf, int64_t n, const ExecCtx& ctx);
 int launch_p2p_all_reduce(float* buf, int64_t n, ExecCtx& ctx);
+// sum of the ranks' partial [M,D] + residual -> x_out (own rows or all), LayerNorm of the rows -> y_out on every rank
+bool tp_exchange_usable(const TpExchange& x, const float* partial, int64_t M, int64_t D, const ExecCtx& ctx);
+int launch_tp_exchange(const TpExchange& x, const float* partial, int64_t M, int64_t D, ExecCtx& ctx);
+int tp_exchange_emulated(int n_ranks, const float* const* partial, const float* const* residual, float* const* x_out, float* const* y_out,
+                         const float* gamma, const float* beta, float eps, int64_t M, int64_t D, int replicate_x, void* sync_mem, int budget_ms,
+                         int skip_rank, cudaStream_t stream);
 int tp_map_peers(void* comm, void* base, PeerMap* out);     // collective: every rank passes its own allocation
 void tp_unmap_peers(void* comm, PeerMap* pm);               // collective as well
 // Gather `bytes` from every rank into recv[rank * bytes ...] (NCCL all-gather on ctx.stream).

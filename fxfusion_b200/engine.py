@@ -63,11 +63,12 @@ class ExecutionEngine:
     """Loads a graph file onto one GPU and runs it.  Not re-entrant (one run at a time)."""
 
     def __init__(self, graph_path: str, device: str = "cuda:0", *, use_cuda_graph: bool = True,
-                 precision: str = "auto", comm=None, shard_output: bool = False) -> None:
+                 precision: str = "auto", comm=None, shard_output: bool = False, **options) -> None:
         """`comm`: a fxfusion_b200.tp.Communicator makes this a tensor-parallel engine (heads and FeedForward
         hidden units sharded over its ranks; construction is collective).  `shard_output` additionally shards
         the vocabulary of the final Linear: `outputs()` then holds only this rank's column block and
-        `argmax_scatter` / `decode_static` combine the ranks."""
+        `argmax_scatter` / `decode_static` combine the ranks.  `options`: further integer fields of FxfEngineOptions by
+        name (no_epilogue_fusion, no_tp_fused_exchange, p2p_start_budget_ms, p2p_end_budget_ms, p2p_grid, tc_chunk_k)."""
         self._h = C.c_void_p()
         lib = _lib.lib()
         if precision not in _lib.GEMM_MODES:
@@ -78,6 +79,10 @@ class ExecutionEngine:
         opts.gemm_mode = _lib.GEMM_MODES[precision]
         opts.tp_rank, opts.tp_size = (comm.rank, comm.size) if comm is not None else (0, 1)
         opts.tp_shard_output = 1 if (shard_output and comm is not None) else 0
+        for key, value in options.items():
+            if key not in ("no_epilogue_fusion", "no_tp_fused_exchange", "p2p_start_budget_ms", "p2p_end_budget_ms", "p2p_grid", "tc_chunk_k"):
+                raise TypeError(f"unknown engine option '{key}'")
+            setattr(opts, key, int(value))
         self.comm = comm  # keeps the communicator alive as long as the engine
         self.device_index = _device_index(device)
         self.device = f"cuda:{self.device_index}"

@@ -71,3 +71,31 @@ def feedforward_static(x, w1, b1, w2, b2, out) -> None:
     stream = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
     _lib.check(lib.fxf_feedforward_static(x.data_ptr(), w1.data_ptr(), b1.data_ptr(), w2.data_ptr(), b2.data_ptr(), out.data_ptr(),
                                           M, D, F, P, stream))
+
+
+def tp_exchange_emulated(partials, residuals=None, x_outs=None, y_outs=None, gamma=None, beta=None, eps: float = 1e-5,
+                         replicate_x: bool = False, budget_ms: int = 200, skip_rank: int = -1):
+    """The tensor-parallel exchange (sum of the ranks' partial [M,D] + residual, LayerNorm, rows owned by rank) with all
+    ranks' buffers on the current GPU and one cooperative launch (fxf_tp_exchange_emulated).  Each argument is a list with
+    one float32 CUDA tensor [M,D] per rank (or None).  Returns the ranks' status words after the call has finished."""
+    import torch
+    lib = _lib.lib()
+    n = len(partials)
+    M, D = partials[0].shape
+    arr = lambda ts: (C.c_void_p * n)(*[t.data_ptr() for t in ts]) if ts is not None else None
+    sync = torch.zeros(n * 8192, dtype=torch.uint8, device=partials[0].device)
+    stream = C.c_void_p(torch.cuda.current_stream(partials[0].device).cuda_stream)
+    _lib.check(lib.fxf_tp_exchange_emulated(n, arr(partials), arr(residuals), arr(x_outs), arr(y_outs),
+                                            gamma.data_ptr() if gamma is not None else None, beta.data_ptr() if beta is not None else None,
+                                            float(eps), M, D, 1 if replicate_x else 0, C.c_void_p(sync.data_ptr()), sync.numel(), int(budget_ms),
+                                            int(skip_rank), stream))
+    torch.cuda.synchronize()
+    words = sync.view(torch.int32).view(n, 2048)[:, 4160 // 4].cpu().tolist()
+    return words
+
+
+def gemm_variant(M: int, N: int, K: int, precision: str = "auto", sm_count: int = 148) -> str:
+    """Which GEMM kernel the dispatch rule takes for out[M,N] = x[M,K] @ w[N,K].T (host-only query)."""
+    buf = C.create_string_buffer(96)
+    _lib.check(_lib.lib().fxf_gemm_variant(M, N, K, _lib.GEMM_MODES[precision], sm_count, buf, len(buf)))
+    return buf.value.decode()

@@ -76,7 +76,14 @@ typedef struct FxfEngineOptions {
     int32_t tp_size;         /* number of tensor-parallel ranks (1 = none); both are taken from the communicator */
     int32_t tp_shard_output; /* 1: also shard the rows (vocabulary) of the final Linear over the ranks; each rank then
                                 writes only its column block of the output and fxf_engine_argmax_scatter combines them */
-    int32_t reserved[10];
+    int32_t no_epilogue_fusion;    /* 1: never fold a residual Add into the epilogue of the contraction before it */
+    int32_t no_tp_fused_exchange;  /* 1: tensor parallelism keeps all-reduce + Add + LayerNorm as separate launches */
+    int32_t p2p_start_budget_ms;   /* wait budget of an exchange's first peer barrier (0 = 20000: it absorbs host-side skew) */
+    int32_t p2p_end_budget_ms;     /* wait budget of its second peer barrier (0 = 2000) */
+    int32_t p2p_grid;              /* blocks of the peer exchange kernels, 1..128 (0 = 128); must agree on all ranks */
+    int32_t tc_chunk_k;            /* K-elements per tensor-core accumulation chain before the partial sums are added in fp32
+                                      by CUDA cores (0 = 128); larger = fewer drains, more truncation bias per chain */
+    int32_t reserved[4];
 } FxfEngineOptions;
 
 typedef struct fxf_engine fxf_engine;
@@ -98,10 +105,15 @@ FXF_API int fxf_engine_create(const char* graph_path, int device_ordinal, const 
  * same graph file; MHA nodes keep H/n heads, FeedForward nodes F/n hidden units, their partial outputs are
  * summed with one all-reduce each (on the run's stream, captured into the CUDA Graph); all other nodes
  * are replicated.  `comm` must outlive the engine.  Creation is collective: all ranks call it together.
- * The all-reduce is this library's own kernel over peer memory: at creation the ranks exchange CUDA IPC handles of their
- * engine allocations and map each other's memory (GPUs of one node with peer access); where that is not possible, or with
- * FXF_TP_ALLREDUCE=nccl in the environment, NCCL's all-reduce is used.  Device status 121 / 122 = a peer did not reach the
- * all-reduce within its budget (20 s for the first barrier, which absorbs host-side skew; 2 s for the second). */
+ * The exchange is this library's own kernel over peer memory: at creation the ranks exchange CUDA IPC handles of their
+ * engine allocations and map each other's memory (GPUs of one node with peer access).  Where a residual Add and a LayerNorm
+ * (or an AddLayerNorm) follow the sharded node, one kernel sums the ranks' partial outputs, adds the residual and
+ * normalises: each rank does that for M / n rows and stores the normalised rows on every rank.  Where peer mapping is not
+ * possible, or with FXF_TP_ALLREDUCE=nccl in the environment, NCCL's all-reduce is used and the other nodes stay separate.
+ * Device status 121 / 122 = a peer did not reach an exchange within its budget (p2p_start_budget_ms / p2p_end_budget_ms
+ * of the options: 20 s for the first barrier, which absorbs host-side skew, 2 s for the second); 123 = a peer reported
+ * that it had given up.  After any of them every later exchange of the engine returns at once (on every rank: the rank
+ * that gave up tells its peers), results are undefined and the engine has to be destroyed. */
 typedef struct fxf_comm fxf_comm;
 FXF_API int fxf_comm_unique_id(void* out_128_bytes);           /* rank 0; ship the 128 bytes to the others */
 FXF_API int fxf_comm_create(const void* unique_id_128_bytes, int rank, int size, int device_ordinal, fxf_comm** out);
@@ -110,6 +122,19 @@ FXF_API int fxf_comm_rank(const fxf_comm* c);
 FXF_API int fxf_comm_size(const fxf_comm* c);
 FXF_API int fxf_engine_create_tp(const char* graph_path, int device_ordinal, const FxfEngineOptions* opts, fxf_comm* comm,
                                  fxf_engine** out_engine);
+/* The exchange step of the tensor-parallel layout, emulated on ONE GPU (no counterpart in the reference; meant for tests
+ * where fewer GPUs than ranks are available): the buffers of all n_ranks ranks live on the current device and one
+ * cooperative launch carries the blocks of every rank.  For rank r and its rows [r*R, (r+1)*R), R = ceil(M / n_ranks):
+ *   x = sum_q partial[q][row] (q = 0..n-1 in order) + residual[r][row];   x_out[r][row] = x  (every x_out[q] when replicate_x);
+ *   y_out[q][row] = LayerNorm(x) * gamma + beta over the D columns, for every q.
+ * residual, x_out, y_out may be NULL (then gamma / beta may be NULL too).  sync_mem: n_ranks * 8192 zeroed device bytes;
+ * afterwards the int at byte r * 8192 + 4160 is rank r's status word (0, or 121 / 122 / 123 as for fxf_engine_create_tp).
+ * budget_ms (1..2000) bounds each peer wait; skip_rank >= 0 keeps that rank away from the exchange, so the other ranks'
+ * waits run out and report it — the call still returns and the device stays usable. */
+FXF_API int fxf_tp_exchange_emulated(int n_ranks, const float* const* partial, const float* const* residual,
+                                     float* const* x_out, float* const* y_out, const float* gamma, const float* beta,
+                                     float eps, int64_t M, int64_t D, int replicate_x, void* sync_mem,
+                                     int64_t sync_bytes, int budget_ms, int skip_rank, void* stream);
 /* tokens[b, current_len] = argmax_v output0[b, current_len-1, v] for this engine, whether the vocabulary is
  * sharded (candidates of all ranks are gathered and every rank writes the same token) or not. */
 FXF_API int fxf_engine_argmax_scatter(fxf_engine* e, int64_t* tokens, int current_len, void* stream);
@@ -178,6 +203,12 @@ FXF_API int fxf_kernel_invoke(int op_code, const FxfTensor* reg, int n_reg,
                       const uint32_t* in_ids, int n_in, const uint32_t* out_ids, int n_out,
                       const int64_t* ints, int n_ints, const float* floats, int n_floats,
                       void* scratch, int64_t scratch_bytes, int gemm_mode, void* stream);
+
+/* Name of the GEMM kernel variant the dispatch rule picks for out[M,N] = x[M,K] . w[N,K]^T in an engine with `sm_count`
+ * SMs (0 = 148): "tcgen05-tf32x3-128x<width>-<where A is read from>", "tcgen05-bf16-...", or one of the fp32 FFMA
+ * kernels ("simt128x128", "simt64x64", "simt32x32", "skinny32x8").  Pure host code (no counterpart in the reference, whose
+ * CUDA linear kernel has one 32x32 tile); tests use it to make sure every variant is exercised. */
+FXF_API int fxf_gemm_variant(int64_t M, int64_t N, int64_t K, int gemm_mode, int sm_count, char* out, size_t out_bytes);
 
 /* Greedy static decode on the device — the loop of
  * py/fxfusion/models/transformer/inference.py:28-45 with the mask rule of

@@ -2,6 +2,9 @@
 
     python -m oracle.ref_cpu.build [/path/to/reference]
 
+Without an argument the checkout is looked up in $FXFUSION_REFERENCE, then in a directory named
+`reference` beside this repository.
+
 The reference CPU kernels (csrc/kernels/cpu/*.cpp) and csrc/runtime/cache.cpp include only
 LibTorch and two of the reference's headers, so they compile as they are with g++ against the
 installed torch; the reference's CMake build is not used (it needs flatc-generated headers).
@@ -18,10 +21,15 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 OUT = HERE.parent / "_ref"
 NAME = "fxf_ref_cpu"
-DEFAULT_REFERENCE = "/root/reference"
 
 
-def build(reference: str = DEFAULT_REFERENCE, verbose: bool = False):
+def default_reference() -> str:
+    """Path of the reference checkout: $FXFUSION_REFERENCE, else `<parent of this repository>/reference`."""
+    return os.environ.get("FXFUSION_REFERENCE") or str(HERE.parents[2] / "reference")
+
+
+def build(reference: str | None = None, verbose: bool = False):
+    reference = reference or default_reference()
     ref = Path(reference)
     csrc = ref / "csrc"
     if not (csrc / "kernels" / "cpu").is_dir():
@@ -46,7 +54,8 @@ def load():
     return mod
 
 
-def ensure(reference: str = DEFAULT_REFERENCE):
+def ensure(reference: str | None = None):
+    reference = reference or default_reference()
     mod = load()
     if mod is None and os.path.isdir(reference):
         build(reference)
@@ -55,5 +64,5 @@ def ensure(reference: str = DEFAULT_REFERENCE):
 
 
 if __name__ == "__main__":
-    build(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_REFERENCE, verbose=True)
+    build(sys.argv[1] if len(sys.argv) > 1 else None, verbose=True)
     print(OUT / f"{NAME}.so")

@@ -8,7 +8,7 @@ REPO = Path(__file__).resolve().parents[1]
 if str(REPO) not in sys.path:
     sys.path.insert(0, str(REPO))
 
-REFERENCE = Path(os.environ.get("FXFUSION_REFERENCE", "/root/reference"))
+REFERENCE = Path(os.environ.get("FXFUSION_REFERENCE") or REPO.parent / "reference")
 GOLDEN = REPO / "tests" / "golden"
 
 

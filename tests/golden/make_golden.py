@@ -20,7 +20,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parents[1]
 sys.path.insert(0, str(REPO))
-REFERENCE = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REFERENCE = sys.argv[1] if len(sys.argv) > 1 else (os.environ.get("FXFUSION_REFERENCE") or str(REPO.parent / "reference"))
 os.environ.setdefault("FXFUSION_REFERENCE_PY", str(Path(REFERENCE) / "py"))
 sys.dont_write_bytecode = True
 

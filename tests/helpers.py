@@ -40,3 +40,19 @@ def max_abs_rel(a: torch.Tensor, e: torch.Tensor):
     if d.numel() == 0:
         return 0.0, 0.0
     return d.max().item(), (d / e[ok].abs().clamp_min(1e-6)).max().item()
+
+
+def reference_cpu_kernels():
+    """The reference's own compiled CPU kernels (oracle/_ref) as a kernel table for GraphOracle, or None when that
+    module has not been built (the restated oracle, tested bit-identical to it, is used then)."""
+    from oracle.graph_oracle import KERNELS
+    from oracle.ref_cpu.build import load as load_ref
+    ref = load_ref()
+    if ref is None:
+        return None
+
+    def bind(op):
+        def fn(reg, i, o, ints, floats):
+            ref.call(op, [t if t is not None else torch.empty(0) for t in reg], list(i), list(o), list(ints), list(floats))
+        return fn
+    return {op: bind(op) for op in KERNELS}

@@ -46,6 +46,44 @@ def test_linear(built_lib, M, N, K, relu):
     both("LinearRelu" if relu else "Linear", [x, w, b, torch.zeros(M, N)], [0, 1, 2], [3], precision="fp32_simt")
 
 
+# Shapes chosen so that every arm of the tensor-core dispatch runs (asserted through fxf_gemm_variant): 256-wide tiles with A
+# in shared memory, the 224-wide hybrid, 192- / 128- / 64-wide tiles with A in tensor memory; K-split last rounds (tiles not
+# a multiple of 148 SMs, K >= 128), ragged M / N / K, an output pitch that is not a multiple of 4 (scalar epilogue), and
+# accumulation chains of one to 24 chunks.
+TC_SHAPES = [
+    (8192, 3072, 768, "128x256-smemA"), (8192, 2304, 768, "128x256-smemA"), (8192, 768, 3072, "128x256-smemA"),
+    (2048, 12565, 768, "128x256-smemA"), (8192, 768, 768, "128x192-tmemA"), (4096, 576, 768, "128x192-tmemA"),
+    (5000, 1111, 500, "128x192-tmemA"), (8192, 8288, 768, "128x224-hybridA"), (2048, 50257, 768, "128x224-hybridA"),
+    (1024, 768, 768, "128x128-tmemA"), (300, 700, 260, "128x128-tmemA"), (512, 1001, 256, "128x128-tmemA"),
+    (128, 128, 64, "128x128-tmemA"), (1024, 64, 256, "128x64-tmemA"), (200, 64, 36, "128x64-tmemA"),
+]
+
+
+@pytest.mark.parametrize("M,N,K,arm", TC_SHAPES)
+@pytest.mark.parametrize("relu", [False, True])
+def test_linear_tensor_core(built_lib, M, N, K, arm, relu):
+    """The tcgen05 3xTF32 GEMM itself (precision "auto"), every variant, against the reference CPU kernel."""
+    from fxfusion_b200.kernels import gemm_variant
+    assert gemm_variant(M, N, K) == "tcgen05-tf32x3-" + arm
+    x, w, b = rnd(M, K), rnd(N, K, seed=1, scale=1 / math.sqrt(K)), rnd(N, seed=2)
+    both("LinearRelu" if relu else "Linear", [x, w, b, torch.zeros(M, N)], [0, 1, 2], [3], precision="auto")
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 16384), (384, 192, 6144), (1000, 300, 3072)])
+def test_tensor_core_error_does_not_grow_with_k(built_lib, M, N, K):
+    """The tensor core adds into its accumulator with truncation (about 4e-8 * K of the result's scale for one chain);
+    the kernel cuts the K loop into chains of 128 and sums them with CUDA cores, so a K of 16384 still lands within
+    3e-5 of the scale (one unbroken chain would be off by 6e-4)."""
+    from fxfusion_b200.kernels import invoke
+    x, w, b = rnd(M, K), rnd(N, K, seed=1, scale=1 / math.sqrt(K)), rnd(N, seed=2)
+    want = (x.double() @ w.double().T + b.double())
+    out = torch.zeros(M, N).cuda()
+    invoke("Linear", [x.cuda(), w.cuda(), b.cuda(), out], [0, 1, 2], [3], precision="auto")
+    err = ((out.cpu().double() - want).abs().max() / want.abs().max()).item()
+    assert err < 3e-5, err
+    both("Linear", [x, w, b, torch.zeros(M, N)], [0, 1, 2], [3], precision="auto")
+
+
 def test_linear_keeps_leading_dims(built_lib):
     both("Linear", [rnd(2, 3, 5, 16), rnd(24, 16, seed=1), rnd(24, seed=2), torch.zeros(2, 3, 5, 24)], [0, 1, 2], [3])
 
@@ -69,6 +107,15 @@ def test_mha_causal(built_lib, B, T, H, hd, precision):
     """head_dim 64 with T % 4 == 0 takes the tcgen05 attention kernel in "auto" mode, everything else the fp32 one."""
     mask = torch.tril(torch.ones(T, T, dtype=torch.bool)).view(1, 1, T, T).expand(B, 1, T, T).contiguous()
     both("MHA", _mha_reg(B, T, H, hd, mask), [0, 1, 2, 3, 4, 5], [6], ints=[H, hd, H * hd, 3 * H * hd], floats=[math.sqrt(hd)], precision=precision)
+
+
+def test_mha_beyond_4096_keys(built_lib):
+    """The tcgen05 attention kernel tracks its key blocks in one 32-bit word (32 blocks of 128 keys); longer sequences must
+    take the fp32 kernel instead of silently dropping the keys from position 4096 on."""
+    B, T, H, hd = 1, 4224, 1, 64
+    mask = torch.tril(torch.ones(T, T, dtype=torch.bool)).view(1, 1, T, T)
+    got = both("MHA", _mha_reg(B, T, H, hd, mask), [0, 1, 2, 3, 4, 5], [6], ints=[H, hd, H * hd, 3 * H * hd], floats=[math.sqrt(hd)])
+    assert not torch.isnan(got).any()
 
 
 @pytest.mark.parametrize("hd", [16, 64])

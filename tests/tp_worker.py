@@ -86,8 +86,24 @@ def cpu_checks(rank, size):
     assert torch.equal(idx, logits.argmax(-1)), (idx, logits.argmax(-1))
     covered = sum(r1 - r0 for r0, r1 in (tp.vocab_range(V, r, size) for r in range(size)))
     assert covered == V
-    # --- non-divisible head counts are replicated, not sharded ---
+    # --- non-divisible head counts are replicated, not sharded: every rank computes the whole node, bias and residual
+    # included, and nothing is summed over the ranks afterwards ---
     assert tp.head_range(12, rank, 8) == (0, 12) and tp.head_range(12, 1, 4) == (3, 6)
+    H3, hd3 = 3, 8
+    D3 = H3 * hd3
+    x3 = torch.randn(B, T, D3, generator=g)
+    w3, b3 = torch.randn(3 * D3, D3, generator=g) / math.sqrt(D3), torch.randn(3 * D3, generator=g) * 0.1
+    wo3, bo3 = torch.randn(D3, D3, generator=g) / math.sqrt(D3), torch.randn(D3, generator=g) * 0.1
+    s3 = tp.shard_mha(w3.numpy(), b3.numpy(), wo3.numpy(), bo3.numpy(), H3, rank, size)
+    assert not s3["sharded"] and s3["heads"] == H3 and np.array_equal(s3["bo"], bo3.numpy())
+    qkv = F.linear(x3, torch.from_numpy(s3["wqkv"]), torch.from_numpy(s3["bqkv"]))
+    q, k, v = (qkv[:, :, i * D3:(i + 1) * D3].view(B, T, H3, hd3).transpose(1, 2) for i in range(3))
+    sc3 = ((q @ k.transpose(-2, -1)) / math.sqrt(hd3)).masked_fill(mask == 0, -math.inf)
+    ctx3 = (torch.softmax(sc3, -1) @ v).transpose(1, 2).contiguous().view(B, T, D3)
+    full = F.linear(ctx3, torch.from_numpy(np.ascontiguousarray(s3["wo"])), torch.from_numpy(s3["bo"]))   # no all-reduce
+    want = torch.zeros(B, T, D3)
+    KERNELS[wire.OP["MHA"]]([x3, mask, w3, b3, wo3, bo3, want], [0, 1, 2, 3, 4, 5], [6], [H3, hd3, D3, 3 * D3], [math.sqrt(hd3)])
+    assert torch.allclose(full, want, atol=1e-5, rtol=1e-5)
 
 
 def gpu_checks(rank, size, tmp):
@@ -104,11 +120,35 @@ def gpu_checks(rank, size, tmp):
     mask = static_decoder_mask(buf, L0)
     oracle = GraphOracle(graph)
     want = oracle.run([buf, mask])[0]
-    for precision in ("auto", "fp32_simt"):
-        eng = ExecutionEngine(path, f"cuda:{rank}", comm=comm, precision=precision)
-        got = eng.run([buf.cuda(), mask.cuda()])[0].cpu()
-        err = (got - want).abs().max().item()
-        assert err < 1e-4, f"rank {rank} {precision}: TP forward differs from the oracle by {err}"
+    for precision, options in (("auto", {}), ("fp32_simt", {}), ("auto", {"no_tp_fused_exchange": 1}), ("auto", {"no_epilogue_fusion": 1})):
+        eng = ExecutionEngine(path, f"cuda:{rank}", comm=comm, precision=precision, **options)
+        text = eng.describe()
+        fused = "+exchange(" in text
+        assert fused == (not options.get("no_tp_fused_exchange")), f"rank {rank}: unexpected exchange fusion state with {options}:\n{text}"
+        if fused:   # the residual stream between two exchanges stays row-sharded; Add and LayerNorm nodes launch nothing
+            assert "[own rows]" in text and "folded into an earlier node" in text
+        for _ in range(2):   # twice: the epochs of the peer barriers carry over from run to run
+            got = eng.run([buf.cuda(), mask.cuda()])[0].cpu()
+            err = (got - want).abs().max().item()
+            assert err < 1e-4, f"rank {rank} {precision} {options}: TP forward differs from the oracle by {err}"
+        assert eng.device_status() == 0
+        eng.close()
+    # heads that do not divide over the ranks (3 heads): the MHA nodes are replicated on every rank (no exchange, bias and
+    # residual on every rank), the FeedForward nodes are still sharded
+    cfg3 = lowering.GPTConfig(192, 3, 300, 4, 2)
+    g3 = lowering.gpt_graph(cfg3, lowering.gpt_params(cfg3, 5), batch=2, seq=32, name="tp_gpt3")
+    path3 = os.path.join(tmp, f"tp_gpt3_{rank}.bin")
+    wire.dump(g3, path3)
+    tok3 = torch.from_numpy(lowering.decode_prompt(2, 20, cfg3.vocab))
+    buf3 = make_static_buffer(tok3, 32)
+    mask3 = static_decoder_mask(buf3, 20)
+    want3 = GraphOracle(g3).run([buf3, mask3])[0]
+    for options in ({}, {"no_tp_fused_exchange": 1}):
+        eng = ExecutionEngine(path3, f"cuda:{rank}", comm=comm, **options)
+        assert "replicated" in eng.describe()
+        got3 = eng.run([buf3.cuda(), mask3.cuda()])[0].cpu()
+        err = (got3 - want3).abs().max().item()
+        assert err < 1e-4, f"rank {rank}: TP forward with replicated attention differs from the oracle by {err} ({options})"
         assert eng.device_status() == 0
         eng.close()
     # encoder-decoder graph: CrossMHA nodes are head-sharded like MHA
@@ -139,6 +179,23 @@ def gpu_checks(rank, size, tmp):
     eng.decode_static(dev, L0, last_row_only=True)
     torch.cuda.synchronize()
     assert torch.equal(dev.cpu(), want_tokens), f"rank {rank}: TP greedy tokens (last-row projection) differ from the oracle"
+    eng.close()
+    # failure detection, injected on the host: rank 0 runs a forward that the other ranks never join.  Its first exchange
+    # runs into the 50 ms budget, records 121 and tells the peers; every later exchange of every rank returns at once.  The
+    # late ranks then run their forward: it returns too, with status 123.  Nothing hangs and the engines are destroyed.
+    eng = ExecutionEngine(path, f"cuda:{rank}", comm=comm, p2p_start_budget_ms=50, p2p_end_budget_ms=50)
+    torch.cuda.synchronize()
+    dist.barrier()
+    if rank == 0:
+        eng.run([buf.cuda(), mask.cuda()])
+        st = eng.device_status()
+        assert st == 121, f"rank 0: expected status 121 after a lonely forward, got {st}"
+    dist.barrier()
+    if rank != 0:
+        eng.run([buf.cuda(), mask.cuda()])
+        st = eng.device_status()
+        assert st == 123, f"rank {rank}: expected status 123 (a peer gave up), got {st}"
+    dist.barrier()
     eng.close()
     comm.close()
 
