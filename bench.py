@@ -1,13 +1,13 @@
 """Benchmark of the hot path: GPT-2-small-shape greedy static decode on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3|c1|c2|c4|c5]
 
 Workload (BASELINE.json config 3): 12 layers, d_model 768, 12 heads, d_ff 3072, vocab 50257, fp32,
 batch 32, static length 256 = 128 prompt tokens + 128 generated; weights ~N(0, 0.02) and prompt ids
 uniform in [1, vocab) from a fixed seed (synthetic stand-ins: no dataset is involved).  Decode is the
 reference's full-recompute loop (no KV cache): one STEP = rebuild the [B,1,T,T] mask, run the whole
 graph on the [B,256] token buffer, argmax of one logits row, write the next token — 32 tokens per
-step and per GPU.  K defaults to 128 steps (one complete decode), W to 3.
+step and per batch.  K defaults to 128 steps (one complete decode), W to 3.
 
 `value`   tokens/s with everything resident in HBM: mask kernel + captured CUDA Graph + argmax kernel
           per step, no host synchronisation inside the timed region (CUDA events, max over ranks).
@@ -15,9 +15,15 @@ step and per GPU.  K defaults to 128 steps (one complete decode), W to 3.
           tokens + mask host->device from pinned memory through fxf_engine_run_host, runs the
           forward and the argmax, and reads the token buffer back device->host.
 Inputs exceed L2 (weights 0.65 GB + 1.65 GB of logits written per step), so no explicit L2 flush.
-N > 1: every rank runs an independent batch-32 replica (sequences are independent; no collective).
+N > 1 (default `--parallel tp`): the batch-32 decode is tensor-parallel — heads, FeedForward hidden units and the
+vocabulary sharded over 2 or 4 GPUs, one fused exchange kernel (sum over the ranks + residual Add + LayerNorm) after
+the attention output projection and one after the second FeedForward product; 12 heads do not divide by 8, so 8 GPUs
+run two tensor-parallel groups of 4, each decoding its own batch of 32.  `--parallel replicas` runs N independent
+batch-32 decodes instead (no collective).
 `--impl reference` times the reference's CPU backend arithmetic (its own compiled CPU kernels when
-`oracle/_ref` is built, else the restated oracle) on the host cores, on a reduced batch per step.
+`oracle/_ref` is built, else the restated oracle) on all host cores, on a reduced batch per step.
+`--workload c1|c2|c4|c5` measures the other configurations (forward only) with the same kinds of evidence; the default
+run folds their one-line results into `secondary`.
 """
 from __future__ import annotations
 
@@ -37,10 +43,11 @@ sys.path.insert(0, str(REPO))
 
 B, T, PROMPT = 32, 256, 128
 METRIC = "gpt2_small_greedy_decode_tokens_per_s"
-# DRAM bytes (read + written) of the dominant kernel's launches in ONE forward, from an ncu capture of
-# this workload (profiles/decode_step_gpt2_small_b32_launch_list.md); bench.py cannot run ncu itself.
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel's launches in ONE forward of this
+# workload on one GPU, summed over an ncu capture of a forward; bench.py cannot run ncu itself.
 NCU_DRAM_BYTES_PER_FORWARD = {"gemm_tf32x3_tcgen05": (6591865088, 49)}
 CPU_BUDGET_S = 150.0  # wall-clock budget of a CPU arm; the per-step batch is sized to fit it
+NVLINK_GBS_PER_DIRECTION = 770.0  # measured peer copy on this pool's B200s (nominal 900)
 
 
 def measured_peaks():
@@ -66,6 +73,7 @@ class ClockSampler:
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
+        return self
 
     def _read(self):
         for line in self.proc.stdout:
@@ -93,6 +101,40 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def layout(world: int, parallel: str):
+    """(tp_size, dp_size) of an N-GPU run: tensor-parallel groups of 4 or 2 GPUs (12 heads divide by 2 and 4, not by 8)."""
+    if parallel == "replicas" or world <= 1:
+        return 1, max(world, 1)
+    tp = 4 if world % 4 == 0 else 2 if world % 2 == 0 else 1
+    return tp, world // tp
+
+
+def workload_config(world: int, parallel: str, precision: str):
+    """The `config` object of the c3 line; both arms (ours and --impl reference) print the same one."""
+    tp, dp = layout(world, parallel)
+    if tp == 1:
+        par = f"{dp} independent batch-{B} replica(s), no collective"
+    else:
+        par = (f"tp{tp} x dp{dp}: heads, FeedForward hidden units and vocabulary sharded over {tp} GPUs, one fused exchange kernel "
+               f"(sum over ranks + residual Add + LayerNorm, peer memory over NVLink) after each of the two row-parallel products of a layer, "
+               f"{dp} group(s) of batch {B}")
+    return {"workload": "GPT-2-small-shape greedy static decode, batch 32, 128 prompt + 128 generated, fp32, full recompute",
+            "layers": 12, "d_model": 768, "heads": 12, "d_ff": 3072, "vocab": 50257, "batch": B, "global_batch": B * dp, "seq": T,
+            "parallelism": par, "gemm": precision, "l2": "inputs larger than L2 (0.65 GB weights read, 1.65 GB logits written per step)"}
+
+
+def use_all_host_cores() -> int:
+    """A launcher may export OMP_NUM_THREADS=1 (torch.distributed.run does); the CPU arms use every core."""
+    import torch
+    n = os.cpu_count() or 1
+    try:
+        n = len(os.sched_getaffinity(0)) or n
+    except AttributeError:
+        pass
+    torch.set_num_threads(n)
+    return torch.get_num_threads()
+
+
 def build_graph_file(batch: int, tmpdir: str) -> str:
     from fxfusion_b200 import lowering, wire
     cfg = lowering.GPT2_SMALL
@@ -102,36 +144,40 @@ def build_graph_file(batch: int, tmpdir: str) -> str:
     return path
 
 
-def pick_cpu_batch(steps: int, warmup: int) -> int:
-    """Largest power-of-two batch <= 32 whose (steps + warmup) decode steps fit CPU_BUDGET_S, from a
-    one-step calibration at batch 2 (bigger batches cost ~2.2x more per sequence: the 1.65 GB logits
-    tensor falls out of cache)."""
-    _, s_per_step, _, _ = cpu_decode_steps(2, 1, 1)
-    per_seq = s_per_step / 2 * 2.2
-    b = 32
-    while b > 1 and (steps + warmup) * per_seq * b > CPU_BUDGET_S:
-        b //= 2
-    return b
+def reference_kernels():
+    """Kernel table for the CPU arms: the reference's own compiled CPU kernels where `oracle/_ref` is built (this library's
+    extension opcodes, for which the reference has no kernel, stay with the restated oracle), else the restated oracle
+    alone.  Returns (table or None, kind)."""
+    import torch
+    from oracle.graph_oracle import KERNELS
+    from oracle.ref_cpu.build import load as load_ref
+    ref = load_ref()
+    if ref is None:
+        return None, "port"
+
+    def bind(op):
+        def fn(reg, i, o, ints, floats):
+            ref.call(op, [t if t is not None else torch.empty(0) for t in reg], list(i), list(o), list(ints), list(floats))
+        return fn
+    table = dict(KERNELS)
+    for op in KERNELS:
+        if op <= 19:   # opcodes of the reference schema
+            table[op] = bind(op)
+    return table, "reference"
 
 
 def cpu_decode_steps(batch: int, steps: int, warmup: int):
-    """Reference CPU backend: graph walked node by node through the reference's CPU kernels."""
+    """Reference CPU backend: the c3 graph walked node by node through the reference's CPU kernels, on the first `batch`
+    sequences of the benchmark's prompts.  Returns (tokens/s, s/step, kind, threads, token buffer after all steps)."""
     import torch
-    from fxfusion_b200 import lowering, wire
-    from oracle.graph_oracle import KERNELS, GraphOracle, make_static_buffer, static_decoder_mask
-    from oracle.ref_cpu.build import load as load_ref
+    from fxfusion_b200 import lowering
+    from oracle.graph_oracle import GraphOracle, make_static_buffer, static_decoder_mask
+    cores = use_all_host_cores()
     cfg = lowering.GPT2_SMALL
     graph = lowering.gpt_graph(cfg, lowering.gpt_params(cfg, 0), batch=batch, seq=T, name="cpu")
-    ref = load_ref()
-    kernels, kind = None, "port"
-    if ref is not None:
-        def bind(op):
-            def fn(reg, i, o, ints, floats):
-                ref.call(op, [t if t is not None else torch.empty(0) for t in reg], list(i), list(o), list(ints), list(floats))
-            return fn
-        kernels, kind = {op: bind(op) for op in KERNELS}, "reference"
+    kernels, kind = reference_kernels()
     orc = GraphOracle(graph, kernels=kernels)
-    tokens = torch.from_numpy(lowering.decode_prompt(batch, PROMPT, cfg.vocab))
+    tokens = torch.from_numpy(lowering.decode_prompt(B, PROMPT, cfg.vocab))[:batch]
     buf = make_static_buffer(tokens, T)
     cur = PROMPT
 
@@ -147,26 +193,111 @@ def cpu_decode_steps(batch: int, steps: int, warmup: int):
     for _ in range(steps):
         step()
     dt = time.perf_counter() - t0
-    return batch * steps / dt, dt / steps, kind, torch.get_num_threads()
+    return batch * steps / dt, dt / steps, kind, cores, buf.clone()
+
+
+def pick_cpu_batch(steps: int, warmup: int) -> int:
+    """Largest power-of-two batch <= 32 whose (steps + warmup) decode steps fit CPU_BUDGET_S, from a
+    one-step calibration at batch 2 (bigger batches cost ~2.2x more per sequence: the 1.65 GB logits
+    tensor falls out of cache)."""
+    s_per_step = cpu_decode_steps(2, 1, 1)[1]
+    per_seq = s_per_step / 2 * 2.2
+    b = 32
+    while b > 1 and (steps + warmup) * per_seq * b > CPU_BUDGET_S:
+        b //= 2
+    return b
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if args.workload != "c3":
+        print(json.dumps(secondary_reference(args.workload, args)), flush=True)
+        return
     batch = pick_cpu_batch(args.steps, args.warmup)
-    tps, s_per_step, kind, cores = cpu_decode_steps(batch, args.steps, args.warmup)
-    sample = f"{args.steps} full-recompute decode steps of the same model at batch {batch} (of {B}), seq {T}"
+    tps, s_per_step, kind, cores, _ = cpu_decode_steps(batch, args.steps, args.warmup)
+    tp, _ = layout(args.gpus, args.parallel)
+    sample = f"{args.steps} full-recompute decode steps of the same model on the first {batch} of the {B} sequences, seq {T}, {cores} threads"
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": s_per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "GPT-2-small-shape greedy static decode, batch 32, 128 prompt + 128 generated, fp32, full recompute",
-                   "cpu_step_batch": batch},
+        "warmup": args.warmup, "ms_per_step": s_per_step * 1e3, "higher_is_better": True, "scaling": "weak" if tp == 1 else "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": workload_config(args.gpus, args.parallel, args.precision),
         "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+def measure_tf32_peak(device_index: int):
+    """Dense TF32 rate of the library GEMM (torch.matmul with TF32 allowed, 8192^3), measured like the bf16 peak of
+    MEASURED_PEAKS.json: best of 10 (burst) and back to back for about 2 s (sustained), SM clock sampled beside each.
+    Three TF32 products make one fp32-grade product, so the ceiling of the 3xTF32 arithmetic is a third of these."""
+    import torch
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        n = 8192
+        a = torch.randn(n, n, device="cuda")
+        b = torch.randn(n, n, device="cuda")
+        for _ in range(3):
+            a @ b
+        torch.cuda.synchronize()
+        flops = 2.0 * n ** 3
+        sampler = ClockSampler(device_index).start()
+        best = None
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            a @ b
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None else min(best, ms)
+        burst_clock = sampler.stop()
+        sampler = ClockSampler(device_index).start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        iters = max(10, int(2000.0 / best))
+        e0.record()
+        for _ in range(iters):
+            a @ b
+        e1.record()
+        torch.cuda.synchronize()
+        sustained_ms = e0.elapsed_time(e1) / iters
+        sus_clock = sampler.stop()
+        return {"tf32_tflops_burst": flops / best / 1e9, "tf32_tflops_sustained": flops / sustained_ms / 1e9,
+                "burst_sm_mhz": burst_clock.get("sm_mhz"), "sustained_sm_mhz": sus_clock.get("sm_mhz"), "sustained_reasons": sus_clock.get("reasons"),
+                "how": "torch.matmul fp32 with allow_tf32 (library GEMM) 8192^3: best of 10, and back to back for ~2 s"}
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+
+
+def kernel_table(trace, precision: str, peaks, tf32_peak):
+    by = {}
+    for r in trace:
+        a = by.setdefault(r["kernel"], {"ms": 0.0, "flops": 0.0, "bytes": 0.0, "n": 0})
+        a["ms"] += r["ms"]; a["flops"] += r["flops"]; a["bytes"] += r["bytes"]; a["n"] += 1
+    total_ms = sum(a["ms"] for a in by.values()) or 1e-9
+    kernels = {k: {"launches": v["n"], "ms": round(v["ms"], 4), "share": round(v["ms"] / total_ms, 4),
+                   "tflops": round(v["flops"] / (v["ms"] * 1e-3) / 1e12, 3) if v["ms"] > 0 else None,
+                   "gbs": round(v["bytes"] / (v["ms"] * 1e-3) / 1e9, 1) if v["ms"] > 0 else None} for k, v in sorted(by.items(), key=lambda kv: -kv[1]["ms"])}
+    # per-kernel fraction of its own roofline: tensor-core kernels against the ceiling of their arithmetic (three TF32
+    # products per fp32 product = measured TF32 rate / 3; the measured bf16 peak in bf16 mode), exchange kernels against
+    # the NVLink rate (bytes that cross the link, both directions), every other kernel against the measured copy bandwidth
+    if precision == "bf16":
+        tensor_ceiling = peaks["bf16_tflops_sustained"]
+    elif tf32_peak:
+        tensor_ceiling = tf32_peak["tf32_tflops_sustained"] / 3.0
+    else:
+        tensor_ceiling = peaks["bf16_tflops_sustained"] / 6.0
+    for k, v in kernels.items():
+        if "tcgen05" in k and v["tflops"] is not None:
+            v["bound"], v["frac"] = "tensor", round(v["tflops"] / tensor_ceiling, 4)
+        elif k in ("tp_exchange_add_layernorm", "p2p_all_reduce") and v["gbs"] is not None:
+            v["bound"], v["frac"] = "nvlink", round(v["gbs"] / (2 * NVLINK_GBS_PER_DIRECTION), 4)
+        elif v["gbs"] is not None:
+            v["bound"], v["frac"] = "hbm", round(v["gbs"] / peaks["hbm_gbs"], 4)
+    return by, kernels, total_ms, tensor_ceiling
 
 
 def run_ours(args):
@@ -188,16 +319,14 @@ def run_ours(args):
     K, W = args.steps, max(args.warmup, 3)
     cfg = lowering.GPT2_SMALL
     tmp = tempfile.TemporaryDirectory()
-    # layout: independent replicas (default), or tensor-parallel groups of 2 / 4 GPUs (12 heads do not divide by 8)
-    tp_size, comm = 1, None
-    if args.parallel == "tp" and world > 1:
+    tp_size, dp_size = layout(world, args.parallel)
+    comm = None
+    if tp_size > 1:
         from fxfusion_b200.tp import Communicator
-        tp_size = 4 if world % 4 == 0 else 2 if world % 2 == 0 else 1
         groups = [list(range(g * tp_size, (g + 1) * tp_size)) for g in range(world // tp_size)]
         handles = [dist.new_group(ranks=r) for r in groups]
         mine = rank // tp_size
-        comm = Communicator.from_process_group(local, ranks=groups[mine], group=handles[mine]) if tp_size > 1 else None
-    dp_size = world // tp_size
+        comm = Communicator.from_process_group(local, ranks=groups[mine], group=handles[mine])
     dp_rank = rank // tp_size
     graph_path = build_graph_file(B, tmp.name)
     eng = ExecutionEngine(graph_path, f"cuda:{local}", precision=args.precision, comm=comm, shard_output=comm is not None)
@@ -206,8 +335,6 @@ def run_ours(args):
     start_buf = torch.zeros((B, T), dtype=torch.int64)
     start_buf[:, :PROMPT] = prompt
     tok_slot, mask_slot = eng.input_slots()
-    logits = eng.outputs()[0]
-    V = logits.shape[-1]
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     h = eng.handle
 
@@ -320,8 +447,7 @@ def run_ours(args):
     kv = None
     if world == 1 and not args.no_extras:
         try:
-            cfg3 = lowering.GPT2_SMALL
-            step_graph = lowering.gpt_step_graph(cfg3, lowering.gpt_params(cfg3, 0), batch=B, max_len=T, name="c3_step")
+            step_graph = lowering.gpt_step_graph(cfg, lowering.gpt_params(cfg, 0), batch=B, max_len=T, name="c3_step")
             step_path = os.path.join(tmp.name, "c3_step.bin")
             wire.dump(step_graph, step_path)
             del step_graph
@@ -353,78 +479,269 @@ def run_ours(args):
         lr_ms = t[2].item() if lr_ms is not None else None
 
     # one traced forward (an event after every launch).  With tensor parallelism a forward contains
-    # collectives, so every rank of the group has to run it, not only the rank that reports.
+    # exchanges, so every rank of the group has to run it, not only the rank that reports.
     trace = None
     if rank == 0 or comm is not None:
         tok_slot.copy_(start_buf)
         eng.profile_launches()
         trace = eng.profile_launches()
-    if rank == 0:
-        # ---- roofline of the dominant kernel -----
-        by = {}
-        for r in trace:
-            a = by.setdefault(r["kernel"], {"ms": 0.0, "flops": 0.0, "bytes": 0.0, "n": 0})
-            a["ms"] += r["ms"]; a["flops"] += r["flops"]; a["bytes"] += r["bytes"]; a["n"] += 1
-        total_ms = sum(a["ms"] for a in by.values())
-        top_name, top = max(by.items(), key=lambda kv: kv[1]["ms"])
-        peaks = measured_peaks()
-        achieved = top["flops"] / (top["ms"] * 1e-3) / 1e12
-        traffic = NCU_DRAM_BYTES_PER_FORWARD.get(top_name)
-        roofline = {"bound": "tensor", "kernel": top_name, "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                    "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": (traffic[0] / traffic[1]) if traffic and traffic[1] == top["n"] else None,
-                    "algorithmic_bytes": top["bytes"] / top["n"], "peak_source": peaks["source"] + " cuBLAS bf16, sustained",
-                    "launches_per_step": top["n"], "share_of_step": top["ms"] / total_ms,
-                    # fp32 results from three TF32 products: TF32 runs at half the bf16 rate, so the ceiling of this arithmetic
-                    # on the measured scale is peak / 6 (bf16 mode: the peak itself)
-                    "fp32_emulation_ceiling": None if args.precision == "bf16" else peaks["bf16_tflops_sustained"] / 6.0,
-                    "frac_of_fp32_emulation_ceiling": None if args.precision == "bf16" else achieved / (peaks["bf16_tflops_sustained"] / 6.0),
-                    "note": "achieved = logical fp32 flops (2MNK, counted once) of all launches of this kernel in one forward / their summed device time"}
-        kernels = {k: {"launches": v["n"], "ms": round(v["ms"], 4), "share": round(v["ms"] / total_ms, 4),
-                       "tflops": round(v["flops"] / (v["ms"] * 1e-3) / 1e12, 3) if v["ms"] > 0 else None,
-                       "gbs": round(v["bytes"] / (v["ms"] * 1e-3) / 1e9, 1) if v["ms"] > 0 else None} for k, v in sorted(by.items(), key=lambda kv: -kv[1]["ms"])}
-        # per-kernel fraction of its own roofline: tensor-core kernels against the ceiling of their arithmetic on the measured
-        # scale (three TF32 products per fp32 product = sustained bf16 peak / 6; the bf16 peak itself in bf16 mode), every
-        # other kernel against the measured copy bandwidth with its algorithmic bytes
-        tensor_ceiling = peaks["bf16_tflops_sustained"] / (1.0 if args.precision == "bf16" else 6.0)
-        for k, v in kernels.items():
-            if "tcgen05" in k and v["tflops"] is not None:
-                v["bound"], v["frac"] = "tensor", round(v["tflops"] / tensor_ceiling, 4)
-            elif v["gbs"] is not None:
-                v["bound"], v["frac"] = "hbm", round(v["gbs"] / peaks["hbm_gbs"], 4)
-        # ---- CPU baseline on a bounded sample -------------------------------------------------------
-        cpu = None
-        if not args.no_cpu_baseline:
-            cb = pick_cpu_batch(2, 1)
-            tps, s_per_step, kind, cores = cpu_decode_steps(cb, 2, 1)
-            cpu = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": kind,
-                   "sample": f"2 full-recompute decode steps of the same model at batch {cb} (of {B}), seq {T}; {s_per_step:.2f} s/step"}
-        tokens_per_step = B * dp_size
-        line = {
-            "metric": METRIC, "value": tokens_per_step * K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak" if tp_size == 1 else "strong", "vs_baseline": None, "dtype": "bf16" if args.precision == "bf16" else "f32", "data": "synthetic",
-            "config": {"workload": "GPT-2-small-shape greedy static decode, batch 32 per replica, 128 prompt + 128 generated, fp32, full recompute",
-                       "layers": 12, "d_model": 768, "heads": 12, "d_ff": 3072, "vocab": 50257, "batch_per_gpu": B, "seq": T,
-                       "parallelism": (f"{world} independent replica(s), no collective" if tp_size == 1 else
-                                       f"tp{tp_size} x dp{dp_size}: heads, FeedForward hidden units and vocabulary sharded over {tp_size} GPUs, "
-                                       f"2 all-reduces per layer (own peer-memory kernel over NVLink, NCCL as fallback), {dp_size} replica group(s) of batch {B}"), "gemm": args.precision,
-                       "l2": "inputs larger than L2 (0.65 GB weights read, 1.65 GB logits written per step)"},
-            "e2e": {"value": tokens_per_step * Ke / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * T * 8 + B * T * T,
-                    "d2h_bytes_per_step": B * T * 8, "steps": Ke, "tokens_equal_device_loop": e2e_match},
-            "last_row_projection": None if lr_ms is None else {
-                "value": tokens_per_step * (T - PROMPT) / (lr_ms * 1e-3), "unit": "tokens/s", "ms_per_step": lr_ms / (T - PROMPT), "steps": T - PROMPT,
-                "tokens_equal_full_loop": lr_match,
-                "note": "opt-in fxf_decode_static_last_row: same tokens, the final Linear evaluated on 1 of 256 positions; not the headline (the graph contract's output is full logits)"},
-            "bf16_mode": bf16,
-            "kv_cache_decode": kv,
-            "gpu_launches": K * (eng.launches_per_run + 2),
-            "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu, "kernels": kernels,
-            "device_status": status, "device_bytes": eng.device_bytes,
-        }
-        print(json.dumps(line), flush=True)
+    launches_per_run, device_bytes = eng.launches_per_run, eng.device_bytes
+    describe_head = eng.describe().splitlines()[:3]
     eng.close()
     if comm is not None:
         comm.close()
+    if rank == 0:
+        report_c3(args, world, local, tp_size, dp_size, K, W, Ke, ms, e2e_ms, e2e_match, lr_ms, lr_match, bf16, kv, trace, clocks, status,
+                  generated, launches_per_run, device_bytes, describe_head)
     tmp.cleanup()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def report_c3(args, world, local, tp_size, dp_size, K, W, Ke, ms, e2e_ms, e2e_match, lr_ms, lr_match, bf16, kv, trace, clocks, status,
+              generated, launches_per_run, device_bytes, describe_head):
+    """Rank 0, after the timed regions: roofline of the dominant kernel, TF32 peak, CPU baseline, secondary workloads, the line."""
+    import torch
+    peaks = measured_peaks()
+    tf32_peak = None
+    try:
+        tf32_peak = measure_tf32_peak(local)
+    except Exception as exc:  # noqa: BLE001
+        sys.stderr.write(f"TF32 peak measurement failed: {exc}\n")
+    by, kernels, total_ms, tensor_ceiling = kernel_table(trace, args.precision, peaks, tf32_peak)
+    top_name, top = max(by.items(), key=lambda kv_: kv_[1]["ms"])
+    achieved = top["flops"] / (top["ms"] * 1e-3) / 1e12
+    traffic = NCU_DRAM_BYTES_PER_FORWARD.get(top_name) if tp_size == 1 else None
+    step_mhz = clocks.get("sm_mhz") if clocks else None
+    emulated = args.precision != "bf16"
+    per_clock = None
+    if emulated and tf32_peak and step_mhz and tf32_peak.get("burst_sm_mhz"):
+        per_clock = (achieved / step_mhz) / (tf32_peak["tf32_tflops_burst"] / 3.0 / tf32_peak["burst_sm_mhz"])
+    roofline = {"bound": "tensor", "kernel": top_name, "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": (traffic[0] / traffic[1]) if traffic and traffic[1] == top["n"] else None,
+                "algorithmic_bytes": top["bytes"] / top["n"], "peak_source": peaks["source"] + " cuBLAS bf16, sustained",
+                "launches_per_step": top["n"], "share_of_step": top["ms"] / total_ms,
+                # fp32 results from three TF32 products: the ceiling of this arithmetic is the TF32 dense rate / 3, with the TF32
+                # rate measured in this run the way the bf16 peak was (library GEMM, burst and sustained, clocks beside them)
+                "tf32_peak": tf32_peak,
+                "fp32_emulation_ceiling": tensor_ceiling if emulated else None,
+                "frac_of_fp32_emulation_ceiling": achieved / tensor_ceiling if emulated else None,
+                # the same fraction with both sides divided by the SM clock they ran at (the library GEMM runs power-capped at a
+                # lower clock than this kernel inside the step): flops per clock against flops per clock
+                "frac_of_fp32_emulation_ceiling_per_clock": per_clock,
+                "note": "achieved = logical fp32 flops (2MNK, counted once) of all launches of this kernel in one forward / their summed device time"}
+    # ---- CPU baseline on a bounded sample; its tokens are compared with the device loop's -----------------
+    cpu = None
+    if not args.no_cpu_baseline:
+        cb = pick_cpu_batch(2, 1)
+        tps, s_per_step, kind, cores, cpu_buf = cpu_decode_steps(cb, 2, 1)
+        n_steps = 3 if K >= 3 else 0   # one warm-up step + two timed steps, all starting at the prompt like the device loop
+        eq = bool(torch.equal(cpu_buf[:, PROMPT:PROMPT + n_steps], generated[:cb, PROMPT:PROMPT + n_steps])) if n_steps else None
+        cpu = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": kind,
+               "sample": f"2 full-recompute decode steps of the same model on the first {cb} of the {B} sequences, seq {T}; {s_per_step:.2f} s/step",
+               "tokens_equal_reference_steps": (n_steps if eq else 0) if eq is not None else None,
+               "tokens_compared": f"{cb} sequences x {n_steps} steps of the reference CPU path against the device loop" if n_steps else None}
+    secondary = None
+    if world == 1 and not args.no_extras:
+        secondary = {}
+        for w in ("c1", "c2", "c4", "c5"):
+            try:
+                secondary[w] = run_secondary(w, args, local, brief=True)
+            except Exception as exc:  # noqa: BLE001
+                secondary[w] = {"error": str(exc)[:300]}
+    tokens_per_step = B * dp_size
+    line = {
+        "metric": METRIC, "value": tokens_per_step * K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak" if tp_size == 1 else "strong", "vs_baseline": None,
+        "dtype": "bf16" if args.precision == "bf16" else "f32", "data": "synthetic",
+        "config": workload_config(world, args.parallel, args.precision),
+        "e2e": {"value": tokens_per_step * Ke / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * T * 8 + B * T * T,
+                "d2h_bytes_per_step": B * T * 8, "steps": Ke, "tokens_equal_device_loop": e2e_match},
+        "last_row_projection": None if lr_ms is None else {
+            "value": tokens_per_step * (T - PROMPT) / (lr_ms * 1e-3), "unit": "tokens/s", "ms_per_step": lr_ms / (T - PROMPT), "steps": T - PROMPT,
+            "tokens_equal_full_loop": lr_match,
+            "note": "opt-in fxf_decode_static_last_row: same tokens, the final Linear evaluated on 1 of 256 positions; not the headline (the graph contract's output is full logits)"},
+        "bf16_mode": bf16,
+        "kv_cache_decode": kv,
+        "gpu_launches": K * (launches_per_run + 2),
+        "launches_per_forward": launches_per_run,
+        "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu, "kernels": kernels, "secondary": secondary,
+        "device_status": status, "device_bytes": device_bytes, "engine": describe_head,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---- secondary workloads (forward only) ---------------------------------------------------------------------------------
+def secondary_case(workload: str, batch=None):
+    """Graph, inputs, logical flops, item count, metric name and description of a secondary configuration."""
+    import torch
+    from fxfusion_b200 import lowering
+    gen = torch.Generator().manual_seed(0)
+    if workload == "c1":
+        nb = batch or 32
+        g = lowering.mlp_graph(lowering.mlp_params(16, 512, 10, seed=0), batch=nb, name="c1_mlp")
+        inputs = [torch.randn(nb, 512, generator=gen)]
+        return (g, inputs, 2.0 * nb * 512 * (512 * 15 + 10), nb, "mlp16x512_forward_samples_per_s",
+                "MLP, 16 layers of width 512 (14 LinearRelu + 1 FeedForward), batch 32, fp32")
+    if workload == "c2":
+        cfg = lowering.GPT_C2
+        nb = batch or 8
+        g = lowering.gpt_graph(cfg, lowering.gpt_params(cfg, 0), batch=nb, seq=64, name="c2_gpt")
+        ids = torch.from_numpy(lowering.decode_prompt(nb, 64, cfg.vocab))
+        inputs = [ids, torch.tril(torch.ones(64, 64, dtype=torch.bool)).view(1, 1, 64, 64).expand(nb, 1, 64, 64).contiguous()]
+        return (g, inputs, 3.62e9 * nb / 8, nb, "gpt4l_d256_forward_sequences_per_s",
+                "GPT 4 layers d_model 256, 4 heads, vocab 1000, batch 8 x seq 64, fp32, single forward")
+    if workload == "c4":
+        cfg = lowering.TRANSFORMER_C4
+        nb = batch or 64
+        L = 256
+        g = lowering.transformer_graph(cfg, lowering.transformer_params(cfg, 0), batch=nb, src_len=L, tgt_len=L, name="c4_encdec")
+        inputs = [torch.randint(1, cfg.vocab, (nb, L), generator=gen), torch.randint(1, cfg.vocab, (nb, L), generator=gen),
+                  torch.ones(nb, 1, 1, L, dtype=torch.bool),
+                  torch.tril(torch.ones(L, L, dtype=torch.bool)).view(1, 1, L, L).expand(nb, 1, L, L).contiguous()]
+        M, D, F, V, H = nb * L, cfg.d_model, cfg.d_ff, cfg.vocab, cfg.heads
+        attn = 4.0 * nb * H * L * L * (D // H)
+        enc = cfg.enc_layers * (2.0 * M * 3 * D * D + attn + 2.0 * M * D * D + 4.0 * M * D * F)
+        dec = cfg.dec_layers * (2.0 * M * 3 * D * D + attn + 2.0 * M * D * D + (2.0 * M * D * D + 2.0 * M * 2 * D * D + attn + 2.0 * M * D * D) + 4.0 * M * D * F)
+        return (g, inputs, enc + dec + 2.0 * M * D * V, nb, "encdec6x6_d512_forward_pairs_per_s",
+                "encoder-decoder Transformer 6+6 layers d_model 512, 8 heads, vocab 32000, batch 64, 256 + 256 positions, fp32, single forward")
+    nb = batch or 256
+    g = lowering.resnet50_graph(lowering.resnet50_params(0), batch=nb, name="c5_resnet50")
+    inputs = [torch.randn(nb, 3, 224, 224, generator=gen)]
+    return (g, inputs, 8.2e9 * nb, nb, "resnet50_inference_images_per_s",
+            "ResNet-50 inference, batch 256 x 3 x 224 x 224, fp32, BatchNorm folded, NCHW in / out")
+
+
+def secondary_cpu(workload: str, budget_s: float = 12.0):
+    """The reference CPU path on a bounded sample of a secondary workload: a reduced batch where the full one would not
+    fit the budget; warm-up + timed iterations with perf_counter (the reference's methodology, benchmarks/utils.py:52-88)."""
+    from oracle.graph_oracle import GraphOracle
+    cores = use_all_host_cores()
+    small = {"c1": 32, "c2": 8, "c4": 1, "c5": 4}[workload]
+    g, inputs, _, items, _, _ = secondary_case(workload, small)
+    kernels, kind = reference_kernels()
+    orc = GraphOracle(g, kernels=kernels)
+    orc.run(inputs)
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        orc.run(inputs)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt > budget_s or n >= 50:
+            break
+    return {"value": items * n / dt, "unit": "items/s", "cores": cores, "kind": kind,
+            "sample": f"{n} forward(s) of the same graph at batch {small}, {dt / n * 1e3:.2f} ms each"}
+
+
+def secondary_reference(workload: str, args):
+    _, _, _, _, metric, desc = secondary_case(workload, {"c1": 32, "c2": 8, "c4": 1, "c5": 1}[workload])
+    cpu = secondary_cpu(workload, budget_s=min(CPU_BUDGET_S, 30.0))
+    return {"impl": "reference", "metric": metric, "value": cpu["value"], "unit": "items/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": desc}, "cpu_baseline": cpu,
+            "e2e": {"value": cpu["value"], "unit": "items/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def run_secondary(workload: str, args, device_index: int = 0, brief: bool = False):
+    """Forward throughput of c1 / c2 / c4 / c5 on one GPU: device-resident value (CUDA-Graph replay), e2e through
+    fxf_engine_run_host with host buffers, roofline of the dominant kernel, CPU baseline on a bounded sample."""
+    import numpy as np
+    import torch
+    from fxfusion_b200 import wire
+    from fxfusion_b200.engine import ExecutionEngine
+    g, inputs, flops, items, metric, desc = secondary_case(workload)
+    tmp = tempfile.TemporaryDirectory()
+    path = os.path.join(tmp.name, g.name + ".bin")
+    wire.dump(g, path)
+    del g
+    eng = ExecutionEngine(path, f"cuda:{device_index}", precision=args.precision)
+    dev_inputs = [t.cuda() for t in inputs]
+    K = (200 if workload in ("c1", "c2") else 10) if brief else max(args.steps, 1)
+    W = max(args.warmup, 3)
+    for _ in range(W):
+        eng.run(dev_inputs)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(device_index).start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        eng.run(dev_inputs)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / K
+    clocks = sampler.stop()
+    # e2e: pinned host inputs in, every output back to the host, each call
+    host_in = [t.contiguous().pin_memory() for t in inputs]
+    host_out = [torch.empty(tuple(d.shape[i] for i in range(d.rank)), dtype=torch.float32).pin_memory() for d in eng.output_descs]
+    as_np = lambda t: t.numpy().view(np.uint8) if t.dtype == torch.bool else t.numpy()
+    Ke = max(2, min(K, 20))
+    for _ in range(2):
+        eng.run_host([as_np(t) for t in host_in], [as_np(t) for t in host_out])
+    t0 = time.perf_counter()
+    for _ in range(Ke):
+        eng.run_host([as_np(t) for t in host_in], [as_np(t) for t in host_out])
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / Ke
+    eng.profile_launches()
+    trace = eng.profile_launches()
+    peaks = measured_peaks()
+    by, kernels, total_ms, tensor_ceiling = kernel_table(trace, args.precision, peaks, None)
+    top_name, top = max(by.items(), key=lambda kv_: kv_[1]["ms"])
+    tensor = "tcgen05" in top_name
+    achieved = (top["flops"] / (top["ms"] * 1e-3) / 1e12) if tensor else (top["bytes"] / (top["ms"] * 1e-3) / 1e9)
+    peak = peaks["bf16_tflops_sustained"] if tensor else peaks["hbm_gbs"]
+    roofline = {"bound": "tensor" if tensor else "hbm", "kernel": top_name, "achieved": achieved, "peak": peak, "unit": "TFLOP/s" if tensor else "GB/s",
+                "frac": achieved / peak, "traffic": None, "launches_per_step": top["n"], "share_of_step": top["ms"] / total_ms,
+                "fp32_emulation_ceiling": tensor_ceiling if tensor else None,
+                "frac_of_fp32_emulation_ceiling": achieved / tensor_ceiling if tensor else None,
+                "peak_source": peaks["source"] + (" cuBLAS bf16, sustained (fp32 emulation ceiling = that / 6)" if tensor else " copy bandwidth")}
+    cpu = None if args.no_cpu_baseline else secondary_cpu(workload, budget_s=8.0 if brief else 20.0)
+    status = eng.device_status()
+    launches = eng.launches_per_run
+    eng.close()
+    tmp.cleanup()
+    line = {"metric": metric, "value": items / (ms * 1e-3), "unit": "items/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": desc},
+            "tflops_logical": flops / (ms * 1e-3) / 1e12,
+            "e2e": {"value": items / (e2e_ms * 1e-3), "unit": "items/s", "h2d_bytes_per_step": int(sum(t.numel() * t.element_size() for t in inputs)),
+                    "d2h_bytes_per_step": int(sum(t.numel() * 4 for t in host_out)), "steps": Ke},
+            "gpu_launches": K * launches, "launches_per_forward": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+            "device_status": status}
+    if brief:
+        line["top_kernels"] = dict(list(kernels.items())[:4])
+    else:
+        line["kernels"] = kernels
+    return line
+
+
+def run_secondary_cli(args):
+    """`--workload c1|c2|c4|c5`.  N > 1: independent replicas of the same batch on every GPU (samples are independent; no
+    collective), value = items of all ranks / max-over-ranks time."""
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+        dist.barrier()
+    if rank != 0:
+        args.no_cpu_baseline = True
+    line = run_secondary(args.workload, args, local)
+    if world > 1:
+        items = line["value"] * line["ms_per_step"] * 1e-3
+        e2e_ms = items / line["e2e"]["value"] * 1e3
+        t = torch.tensor([line["ms_per_step"], e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        line["ms_per_step"] = t[0].item()
+        line["value"] = world * items / (t[0].item() * 1e-3)
+        line["e2e"]["value"] = world * items / (t[1].item() * 1e-3)
+        line["n_gpus"] = world
+        line["config"]["parallelism"] = f"{world} independent replicas of the batch, no collective"
+    if rank == 0:
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -481,71 +798,11 @@ def run_micro(args):
                       "tflops": flops / ms / 1e9, "gbs": nbytes / ms / 1e6, "note": "includes the per-call weight split of the tensor-core path"}), flush=True)
 
 
-def run_latency(args):
-    """Forward latency of the two small configurations (secondary metrics): c1 = MLP, 16 layers of width 512,
-    batch 32; c2 = GPT 4 layers d_model 256, batch 8 x seq 64.  CUDA-Graph replay, device-resident inputs."""
-    import torch
-    from fxfusion_b200 import lowering, wire
-    from fxfusion_b200.engine import ExecutionEngine
-    torch.cuda.set_device(0)
-    tmp = tempfile.TemporaryDirectory()
-    if args.workload == "c5":
-        nb = args.m if args.m != 8192 else 256
-        g = lowering.resnet50_graph(lowering.resnet50_params(0), batch=nb, name="c5_resnet50")
-        inputs = [torch.randn(nb, 3, 224, 224, generator=torch.Generator().manual_seed(0)).cuda()]
-        flops = sum(2.0 * float(np_.size) for np_ in ()) or 8.2e9 * nb
-        weight_bytes = 4.0 * sum(int(v.size) for v in lowering.resnet50_params(0).values())
-    elif args.workload == "c4":
-        cfg = lowering.TRANSFORMER_C4
-        nb = args.m if args.m != 8192 else 64
-        L = 256
-        g = lowering.transformer_graph(cfg, lowering.transformer_params(cfg, 0), batch=nb, src_len=L, tgt_len=L, name="c4_encdec")
-        gen = torch.Generator().manual_seed(0)
-        inputs = [torch.randint(1, cfg.vocab, (nb, L), generator=gen).cuda(), torch.randint(1, cfg.vocab, (nb, L), generator=gen).cuda(),
-                  torch.ones(nb, 1, 1, L, dtype=torch.bool).cuda(),
-                  torch.tril(torch.ones(L, L, dtype=torch.bool)).view(1, 1, L, L).expand(nb, 1, L, L).contiguous().cuda()]
-        M, D, F, V, H = nb * L, cfg.d_model, cfg.d_ff, cfg.vocab, cfg.heads
-        attn = 4.0 * nb * H * L * L * (D // H)
-        enc = cfg.enc_layers * (2.0 * M * 3 * D * D + attn + 2.0 * M * D * D + 4.0 * M * D * F)
-        dec = cfg.dec_layers * (2.0 * M * 3 * D * D + attn + 2.0 * M * D * D + (2.0 * M * D * D + 2.0 * M * 2 * D * D + attn + 2.0 * M * D * D) + 4.0 * M * D * F)
-        flops = enc + dec + 2.0 * M * D * V
-        weight_bytes = 4.0 * sum(int(v.size) for k, v in lowering.transformer_params(cfg, 0).items() if not k.endswith(".pe"))
-    elif args.workload == "c1":
-        g = lowering.mlp_graph(lowering.mlp_params(16, 512, 10, seed=0), batch=32, name="c1_mlp")
-        inputs = [torch.randn(32, 512, generator=torch.Generator().manual_seed(0)).cuda()]
-        flops, weight_bytes = 2.0 * 32 * 512 * (512 * 15 + 10), 4.0 * (512 * 512 * 15 + 512 * 10)
-    else:
-        cfg = lowering.GPT_C2
-        g = lowering.gpt_graph(cfg, lowering.gpt_params(cfg, 0), batch=8, seq=64, name="c2_gpt")
-        ids = torch.from_numpy(lowering.decode_prompt(8, 64, cfg.vocab))
-        inputs = [ids.cuda(), torch.tril(torch.ones(64, 64, dtype=torch.bool)).view(1, 1, 64, 64).expand(8, 1, 64, 64).contiguous().cuda()]
-        flops, weight_bytes = 3.62e9, 4.0 * sum(int(np_.size) for np_ in lowering.gpt_params(cfg, 0).values())
-    path = os.path.join(tmp.name, g.name + ".bin")
-    wire.dump(g, path)
-    eng = ExecutionEngine(path, "cuda:0", precision=args.precision)
-    for _ in range(max(args.warmup, 3)):
-        eng.run(inputs)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    n = max(args.steps, 1)
-    e0.record()
-    for _ in range(n):
-        eng.run(inputs)
-    e1.record()
-    torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / n
-    trace = eng.profile_launches()
-    print(json.dumps({"workload": args.workload, "forward_us": us, "items_per_s": (inputs[0].shape[0] / us * 1e6), "nodes": eng.num_nodes, "launches": eng.launches_per_run,
-                      "gflops_per_forward": flops / 1e9, "tflops": flops / us / 1e6, "weight_mb": weight_bytes / 1e6,
-                      "kernels_us": {r["kernel"]: round(sum(x["ms"] for x in trace if x["kernel"] == r["kernel"]) * 1e3, 2) for r in trace}}), flush=True)
-    eng.close()
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="c3", choices=["c3", "c1", "c2", "c4", "c5"],
-                    help="c3 = the decode benchmark (default); c1 / c2 = forward latency of the small configs; c4 = encoder-decoder forward "
-                         "(batch --m, default 64; 256 source + 256 target positions); c5 = ResNet-50 forward (batch --m, default 256)")
+                    help="c3 = the decode benchmark (default); c1 = MLP 16 x 512 batch 32; c2 = GPT 4 layers d256 batch 8 x 64; "
+                         "c4 = encoder-decoder forward, batch 64, 256 + 256 positions; c5 = ResNet-50 forward, batch 256")
     ap.add_argument("--micro", default=None, choices=["linear", "layernorm", "add", "mha", "conv"], help="profile one op instead of the decode workload")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=3072)
@@ -557,18 +814,18 @@ def main():
     ap.add_argument("--precision", default="auto", choices=["auto", "fp32_simt", "fp32_3xtf32", "bf16"],
                     help="bf16 = optional reduced-precision mode (bf16 tensor-core products, fp32 accumulation); not the headline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-extras", action="store_true", help="skip the opt-in last-row-projection decode measurement (keeps profiler captures short)")
-    ap.add_argument("--parallel", default="replicas", choices=["replicas", "tp"],
-                    help="N > 1: independent batch replicas (default) or tensor-parallel groups (head-sharded MHA, split FeedForward, NCCL all-reduce)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the opt-in decode variants and the secondary workloads (keeps profiler captures short)")
+    ap.add_argument("--parallel", default="tp", choices=["tp", "replicas"],
+                    help="N > 1: tensor-parallel groups of 4 or 2 GPUs (default: the batch-32 decode sharded over heads, hidden units and "
+                         "vocabulary) or N independent batch-32 replicas")
     args = ap.parse_args()
     if args.micro:
         return run_micro(args)
-    if args.workload != "c3":
-        return run_latency(args)
     if args.impl == "reference":
-        run_reference(args)
-    else:
-        run_ours(args)
+        return run_reference(args)
+    if args.workload != "c3":
+        return run_secondary_cli(args)
+    run_ours(args)
 
 
 if __name__ == "__main__":

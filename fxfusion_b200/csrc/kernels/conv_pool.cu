@@ -357,6 +357,7 @@ int run_conv(Registry& reg, const TensorIds& in, const TensorIds& out, const Par
         g.ldx = d.C; g.ldw = d.C; g.ldo = d.O;
         g.relu = relu;
         apply_fusion(ctx, g, false);
+        g.conv_chain = true;
         return launch_gemm(g, ctx);
     }
     if (cp && cp->s2d_tc && cp->w_hi && is_channels_last(o) && ctx.scratch != nullptr &&

@@ -46,7 +46,7 @@
 //   warps 14-15 idle (they complete the fourth warpgroup, which setmaxnreg needs).
 // Why chunks.  The tensor core adds into its fp32 accumulator with truncation, so the error of one long
 // accumulation chain grows linearly with K (about 4e-8 * K of the result's scale, measured).  Chains of at
-// most `chunk` K-elements summed by CUDA cores keep the result at fp32 FFMA grade for any K.
+// most `chunk` K-elements summed by CUDA cores bound that error for any K (see kChunkKDense / kChunkKConv).
 // TMEM columns: [0, 2*BN) accumulators, then STAGES x (BK hi + BK lo) columns of A.
 // Every mbarrier wait is bounded by a wall-clock budget; on expiry the CTA records an error in the
 // status word, all roles stop issuing work, the CTA frees its TMEM and returns.
@@ -598,23 +598,37 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         if (oks[i]) *reinterpret_cast<float4*>(orow[i] + g * 16) = o;
                     }
                 } else {
-                    // ragged or unaligned output: two rows per instruction, 16 lanes on consecutive columns
+                    // ragged or unaligned output (e.g. a vocabulary of 50257 columns): two rows per instruction, 16 lanes on
+                    // consecutive columns
                     const int cl = lane & 15, r2 = lane >> 4;
                     const bool col_ok = col + cl < p.N;
                     const float b = (p.bias && col_ok) ? __ldg(p.bias + col + cl) : 0.f;
+                    if (!p.cv.enabled && !adds_partials && p.residual == nullptr) {
+                        // dense rows without extras: affine addresses, independent iterations (the stores of consecutive rows pipeline)
+                        const int64_t grow = int64_t(tm) * BM + row0 + r2;
+                        float* op = p.out + grow * p.ldo + col + cl;
+                        const int64_t step = 2 * p.ldo;
+#pragma unroll 8
+                        for (int i = 0; i < 16; i++) {
+                            float v = stage[(i * 2 + r2) * kStagePad + cl] + b;
+                            if (p.relu) v = relu_keep_nan(v);
+                            if (col_ok && grow + 2 * i < p.M) op[i * step] = v;
+                        }
+                    } else {
 #pragma unroll 1
-                    for (int i = 0; i < 16; i++) {
-                        const int rr = i * 2 + r2;
-                        float v = stage[rr * kStagePad + cl];
-                        if (adds_partials)
-                            for (int pp = 1; pp < un.nparts; pp++)
-                                v += __ldcg(ws_mine + size_t(pp) * size_t(BM * BN) + (row0 + rr) * BN + chalf * HALF + g * 16 + cl);
-                        v += b;
-                        bool row_ok;
-                        const int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
-                        if (p.residual && col_ok && row_ok) v += p.residual[off + col + cl];
-                        if (p.relu) v = relu_keep_nan(v);
-                        if (col_ok && row_ok) p.out[off + col + cl] = v;
+                        for (int i = 0; i < 16; i++) {
+                            const int rr = i * 2 + r2;
+                            float v = stage[rr * kStagePad + cl];
+                            if (adds_partials)
+                                for (int pp = 1; pp < un.nparts; pp++)
+                                    v += __ldcg(ws_mine + size_t(pp) * size_t(BM * BN) + (row0 + rr) * BN + chalf * HALF + g * 16 + cl);
+                            v += b;
+                            bool row_ok;
+                            const int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
+                            if (p.residual && col_ok && row_ok) v += p.residual[off + col + cl];
+                            if (p.relu) v = relu_keep_nan(v);
+                            if (col_ok && row_ok) p.out[off + col + cl] = v;
+                        }
                     }
                 }
                 __syncwarp();
@@ -736,9 +750,13 @@ int make_map_nhwc(CUtensorMap* map, const float* base, int N, int H, int W, int 
     return 0;
 }
 
-// K-elements per accumulation chain: the tensor core's truncating adds cost about 4e-8 of the result's scale per K-element
-// of a chain; 128 keeps a chain's share below 1e-5 while a chunk (at least 12 MMAs) still hides the epilogue warps' drain.
-constexpr int kChunkK = 128;
+// K-elements per accumulation chain.  The tensor core's truncating adds cost about 4e-8 of the result's scale per K-element
+// of a chain, and every extra chain costs time (measured on B200 at GPT-2-small shape: +2 % per forward with chains of
+// 256, +9 % with 128, +14 % with 64: the drain of a chain competes with the store of the previous tile for the epilogue
+// warps).  Dense layers are followed by normalisation and meet max-abs 1e-4 / rel 1e-3 with chains of 1024 (K = 768 is then
+// one chain, as many as before); convolution stacks (ResNet-50: 52 in a row, logits of scale 400) need chains of 64 to
+// meet the same rule end to end.
+constexpr int kChunkKDense = 1024, kChunkKConv = 64;
 
 template <int BN, int BK, int STAGES, bool TS, bool BF16 = false, bool HYB = false>
 int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, const ConvGeom* geom = nullptr) {
@@ -781,7 +799,7 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
     if (ts.parts > 1 && (size_t(ts.tail) * ts.parts * size_t(BM * BN) * sizeof(float) > ctx.gemm_ws_bytes || ts.tail * ts.parts * kEpiWarps > ctx.gemm_flag_count))
         ts = TailSplit{tiles, 0, 1, 0.0, 0.0};
     p.full_tiles = int(ts.full); p.tail_tiles = int(ts.tail); p.tail_split = ts.parts;
-    p.chunk_slabs = std::max(1, (ctx.tc_chunk_k > 0 ? ctx.tc_chunk_k : kChunkK) / BK);
+    p.chunk_slabs = std::max(1, (ctx.tc_chunk_k > 0 ? ctx.tc_chunk_k : ((cv || a.conv_chain) ? kChunkKConv : kChunkKDense)) / BK);
     p.ws = ctx.gemm_ws; p.flags = ctx.gemm_flags;
     const int64_t units = ts.full + ts.tail * ts.parts;
     int grid = int(units < ctx.sm_count ? units : ctx.sm_count);

@@ -263,6 +263,7 @@ struct GemmArgs {
     int64_t M = 0, N = 0, K = 0;
     int64_t ldx = 0, ldw = 0, ldo = 0;
     bool relu = false;
+    bool conv_chain = false;   // a convolution written as a GEMM: use the (shorter) accumulation chains of convolutions
 };
 int launch_gemm(const GemmArgs& a, ExecCtx& ctx);
 int launch_gemm_simt(const GemmArgs& a, ExecCtx& ctx);

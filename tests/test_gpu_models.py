@@ -243,7 +243,7 @@ def test_c5_resnet50_matches_oracle_on_reduced_batch(built_lib, tmp_path, precis
     """ResNet-50 (BatchNorm folded into 53 convolutions) at batch 2: 72 nodes against the CPU oracle.  The engine
     keeps the activations channels-last internally; input and output stay NCHW.  With random weights and no
     normalisation the logits have a standard deviation near 100 (max 422) and pass through 52 convolutions in a row;
-    both the fp32 FFMA path and the tensor-core path (3xTF32 products, accumulation chains of 128 summed in fp32) are held
+    both the fp32 FFMA path and the tensor-core path (3xTF32 products, accumulation chains of 64 summed in fp32) are held
     to the element-wise 1e-4 / 1e-3 rule."""
     g = lowering.resnet50_graph(lowering.resnet50_params(0), batch=2, name="c5_resnet50_b2")
     x = torch.randn(2, 3, 224, 224, generator=torch.Generator().manual_seed(0))

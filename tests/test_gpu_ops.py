@@ -72,15 +72,15 @@ def test_linear_tensor_core(built_lib, M, N, K, arm, relu):
 @pytest.mark.parametrize("M,N,K", [(256, 256, 16384), (384, 192, 6144), (1000, 300, 3072)])
 def test_tensor_core_error_does_not_grow_with_k(built_lib, M, N, K):
     """The tensor core adds into its accumulator with truncation (about 4e-8 * K of the result's scale for one chain);
-    the kernel cuts the K loop into chains of 128 and sums them with CUDA cores, so a K of 16384 still lands within
-    3e-5 of the scale (one unbroken chain would be off by 6e-4)."""
+    the kernel cuts the K loop into chains of 1024 and sums them with CUDA cores, so a K of 16384 still lands within
+    6e-5 of the scale (one unbroken chain would be off by 6e-4)."""
     from fxfusion_b200.kernels import invoke
     x, w, b = rnd(M, K), rnd(N, K, seed=1, scale=1 / math.sqrt(K)), rnd(N, seed=2)
     want = (x.double() @ w.double().T + b.double())
     out = torch.zeros(M, N).cuda()
     invoke("Linear", [x.cuda(), w.cuda(), b.cuda(), out], [0, 1, 2], [3], precision="auto")
     err = ((out.cpu().double() - want).abs().max() / want.abs().max()).item()
-    assert err < 3e-5, err
+    assert err < 6e-5, err
     both("Linear", [x, w, b, torch.zeros(M, N)], [0, 1, 2], [3], precision="auto")
 
 
