@@ -21,7 +21,7 @@ class FxfEngineOptions(C.Structure):
     _fields_ = [("struct_size", C.c_int32), ("use_cuda_graph", C.c_int32), ("gemm_mode", C.c_int32),
                 ("tp_rank", C.c_int32), ("tp_size", C.c_int32), ("tp_shard_output", C.c_int32),
                 ("no_epilogue_fusion", C.c_int32), ("no_tp_fused_exchange", C.c_int32), ("p2p_start_budget_ms", C.c_int32),
-                ("p2p_end_budget_ms", C.c_int32), ("p2p_grid", C.c_int32), ("tc_chunk_k", C.c_int32), ("reserved", C.c_int32 * 4)]
+                ("p2p_end_budget_ms", C.c_int32), ("p2p_grid", C.c_int32), ("tc_chunk_k", C.c_int32), ("tc_pair", C.c_int32), ("reserved", C.c_int32 * 3)]
 
 
 class FxfLaunchInfo(C.Structure):

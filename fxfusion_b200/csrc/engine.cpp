@@ -426,6 +426,7 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
     e->ctx.sm_count = prop.multiProcessorCount;
     e->ctx.gemm_mode = e->opts.gemm_mode;
     e->ctx.tc_chunk_k = e->opts.tc_chunk_k;
+    e->ctx.tc_pair = e->opts.tc_pair;
     e->ctx.tp_rank = e->opts.tp_rank;
     e->ctx.tp_size = e->opts.tp_size;
     e->ctx.comm = e->comm;
@@ -1160,6 +1161,7 @@ static int last_row_head(fxf_engine* e, int64_t* tokens, int cur, ExecCtx& ctx) 
     float* rows = reinterpret_cast<float*>(e->base + e->lastrow_off);
     ctx.gemm_mode = e->ctx.gemm_mode;
     ctx.tc_chunk_k = e->ctx.tc_chunk_k;
+    ctx.tc_pair = e->ctx.tc_pair;
     ctx.status = e->ctx.status;
     ctx.gemm_ws = e->ctx.gemm_ws; ctx.gemm_ws_bytes = e->ctx.gemm_ws_bytes;
     ctx.gemm_flags = e->ctx.gemm_flags; ctx.gemm_flag_count = e->ctx.gemm_flag_count;

@@ -61,8 +61,10 @@ extern "C" FXF_API int64_t fxf_feedforward_static_max_bytes(void) { return int64
 
 extern "C" FXF_API int fxf_feedforward_static(const float* x, const float* w1, const float* b1, const float* w2, const float* b2, float* out,
                                       int64_t M, int64_t D, int64_t F, int64_t P, void* stream) {
-    FXF_CHECK(x && w1 && b1 && w2 && b2 && out, "fxf_feedforward_static: NULL argument");
     FXF_CHECK(M >= 0 && D >= 0 && F >= 0 && P >= 0, "fxf_feedforward_static: negative dimension");
+    // an operand without elements (a zero extent) may be passed as NULL
+    FXF_CHECK((x || M * D == 0) && (w1 || F * D == 0) && (b1 || F == 0) && (w2 || P * F == 0) && (b2 || P == 0) && (out || M * P == 0),
+              "fxf_feedforward_static: NULL argument");
     // F <= max / (4 M) written without overflow
     FXF_CHECK(M == 0 || F == 0 || uint64_t(F) <= kStaticScratchBytes / sizeof(float) / uint64_t(M),
               "fxf_feedforward_static: the hidden activation needs M*F*4 = %lld x %lld x 4 bytes, more than the %zu-byte static scratch; "

@@ -93,14 +93,16 @@ __device__ __forceinline__ void reg_set() {   // the kernel starts with 128 regi
     else if constexpr (N < 128) reg_dec<N>();
 }
 
-template <int BN, int BK, int STAGES, bool TS, bool BF16>
+// BNB = weight rows held by this CTA: BN, or BN / 2 when two CTAs share a 256-row tile (each stages half of the weight tile)
+template <int BNB, int BK, int STAGES, bool TS, bool BF16>
 struct alignas(1024) TcSmem {
     float a[STAGES][BM * BK];             // x tile as TMA wrote it (fp32, swizzled rows of BK floats); x_hi in place when !TS
     float a_lo[TS ? 1 : STAGES][TS ? 256 : BM * BK];  // x_lo twin buffers, only when the MMAs read A from shared memory
-    float b_hi[STAGES][BF16 ? BN * BK / 2 : BN * BK];   // w_hi tile (fp32), or the whole bf16 weight tile in bf16 mode
-    float b_lo[BF16 ? 1 : STAGES][BF16 ? 256 : BN * BK];
+    float b_hi[STAGES][BF16 ? BNB * BK / 2 : BNB * BK];   // w_hi tile (fp32), or the whole bf16 weight tile in bf16 mode
+    float b_lo[BF16 ? 1 : STAGES][BF16 ? 256 : BNB * BK];
     float stage_out[kEpiWarps][32 * kStagePad];   // one 32 x 16 block per epilogue warp
     uint64_t full_tma[STAGES];
+    uint64_t full_b[STAGES];      // CTA pairs only: the weight halves of both CTAs have landed (the leader's copy counts)
     uint64_t full_split[STAGES];
     uint64_t empty[STAGES];
     uint64_t acc_full[2];
@@ -222,7 +224,12 @@ __device__ __forceinline__ void drain_chunk(uint32_t tacc, float (&sum)[HALF]) {
     }
 }
 
-template <int BN, int BK, int STAGES, bool TS, bool BF16, bool HYB>
+// PAIR: two CTAs of a cluster compute one 256 x BN tile with tcgen05.mma.cta_group::2 — each CTA stages its own 128 rows
+// of x and HALF of the weight tile, which cuts the shared-memory traffic per flop (the limiter of this kernel) by a third
+// to a half.  The leader (even rank) issues the MMAs for both; every CTA splits its own x rows and drains / stores its own
+// 128 accumulator rows.  Barriers that gate the MMA (weight halves landed, x split, accumulator drained) live in the leader
+// and are reached by the other CTA through the shared::cluster window; MMA completion is committed to both CTAs.
+template <int BN, int BK, int STAGES, bool TS, bool BF16, bool HYB, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_whi,
                    const __grid_constant__ CUtensorMap map_wlo, TcParams p) {
@@ -231,7 +238,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     static_assert(!BF16 || (TS && BK == 32), "the bf16 mode takes A from tensor memory with 32-float slabs");
     static_assert(!HYB || (TS && !BF16), "hybrid: x_hi is the raw tile in shared memory, x_lo goes to tensor memory");
     static_assert(BN % 32 == 0, "tile width must be a multiple of 32 columns (16 per column half and staging step)");
-    using Smem = TcSmem<BN, BK, STAGES, TS, BF16>;
+    static_assert(!PAIR || (!BF16 && !HYB), "CTA pairs exist for the plain 3xTF32 variants");
+    constexpr int BNB = PAIR ? BN / 2 : BN;   // weight rows staged by this CTA
+    using Smem = TcSmem<BNB, BK, STAGES, TS, BF16>;
     using Regs = RegBudget<BN, BK, TS, BF16>;
     Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -239,9 +248,12 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     const int num_k = int((p.K + BK - 1) / BK);
     const int num_units = p.full_tiles + p.tail_tiles * p.tail_split;
     const int chunk = p.chunk_slabs > 0 ? p.chunk_slabs : num_k;
-    constexpr uint32_t kBBytes = BF16 ? uint32_t(BN * BK) * 2u : uint32_t(2 * BN * BK) * 4u;   // weight bytes per stage
-    constexpr uint32_t kStageBytes = uint32_t(BM * BK) * 4u + kBBytes;
-    constexpr uint32_t kIdesc = BF16 ? umma_idesc_bf16(BM, BN) : umma_idesc_tf32(BM, BN);
+    const int rank = PAIR ? int(cluster_ctarank()) : 0;     // position inside the CTA pair; rank 0 issues the MMAs
+    const int sched_id = PAIR ? int(blockIdx.x >> 1) : int(blockIdx.x), sched_n = PAIR ? int(gridDim.x >> 1) : int(gridDim.x);
+    constexpr uint32_t kBBytes = BF16 ? uint32_t(BNB * BK) * 2u : uint32_t(2 * BNB * BK) * 4u;   // weight bytes per stage and CTA
+    constexpr uint32_t kABytes = uint32_t(BM * BK) * 4u;
+    constexpr uint32_t kStageBytes = kABytes + kBBytes;
+    constexpr uint32_t kIdesc = BF16 ? umma_idesc_bf16(BM, BN) : umma_idesc_tf32(PAIR ? 2 * BM : BM, BN);
     constexpr int kACols = BF16 ? BK / 2 : (HYB ? BK : 2 * BK);   // TMEM columns of one A stage
     constexpr uint32_t kColA = uint32_t(ACC * BN);             // first TMEM column of the A stages
     constexpr uint32_t kColsUsed = kColA + (TS ? uint32_t(STAGES * kACols) : 0u);
@@ -252,22 +264,29 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; i++) {
             mbar_init(&s.full_tma[i], 1);
-            mbar_init(&s.full_split[i], 4);   // one arrival per split warp
+            mbar_init(&s.full_b[i], 1);
+            mbar_init(&s.full_split[i], PAIR ? 8 : 4);   // one arrival per split warp (of both CTAs of a pair)
             mbar_init(&s.empty[i], 1);
         }
         for (int i = 0; i < ACC; i++) {
             mbar_init(&s.acc_full[i], 1);
-            mbar_init(&s.acc_empty[i], kEpiWarps);    // one arrival per epilogue warp
+            mbar_init(&s.acc_empty[i], PAIR ? 2 * kEpiWarps : kEpiWarps);    // one arrival per epilogue warp
         }
         s.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == kMmaWarp) {  // TMEM allocation is a warp-wide operation
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s.tmem_base)), "r"(kTmemCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (warp == kMmaWarp) {  // TMEM allocation is a warp-wide operation; a pair allocates in both CTAs together
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s.tmem_base)), "r"(kTmemCols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s.tmem_base)), "r"(kTmemCols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (PAIR) cluster_sync_all();   // the other CTA's barriers exist before anything of this CTA signals them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = s.tmem_base;
 
@@ -277,15 +296,26 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             // ---------------- TMA producer ----------------
             if (lane == 0) {
                 uint32_t it = 0;  // slab counter over all tiles of this CTA
-                for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+                for (int unit = sched_id; unit < num_units; unit += sched_n) {
                     const Unit un = get_unit(p, unit, num_k);
                     int tm, tn;
                     tile_coords(p, un.tile, tm, tn);
+                    if (PAIR) tm = tm * 2 + rank;   // this CTA's 128 rows of the pair's 256-row tile
                     for (int k = un.k0; k < un.k1; k++, it++) {
                         int st = it % STAGES;
                         if (it >= uint32_t(STAGES) && !mbar_wait(&s.empty[st], ((it / STAGES) - 1) & 1, abort_flag)) {
                             give_up(abort_flag, p.status, kErrWaitEmpty);
                             goto producer_done;
+                        }
+                        if (PAIR) {
+                            // x rows: this CTA's own barrier (its split warps wait for it); weight halves: the leader's barrier,
+                            // which expects the bytes of both CTAs
+                            mbar_expect_tx(&s.full_tma[st], kABytes);
+                            tma_load_2d(s.a[st], &map_x, k * BK, tm * BM, &s.full_tma[st]);
+                            if (rank == 0) mbar_expect_tx(&s.full_b[st], 2 * kBBytes);
+                            tma_load_2d_pair(s.b_hi[st], &map_whi, k * BK, tn * BN + rank * BNB, &s.full_b[st]);
+                            tma_load_2d_pair(s.b_lo[BF16 ? 0 : st], &map_wlo, k * BK, tn * BN + rank * BNB, &s.full_b[st]);
+                            continue;
                         }
                         if (p.cv.enabled) {
                             int ox0, oy0, n0;
@@ -306,14 +336,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             }
         } else if (warp == kMmaWarp) {
             // ---------------- MMA issuer ----------------
-            if (lane == 0) {
+            if (lane == 0 && rank == 0) {   // in a pair only the leader issues MMAs (for both CTAs)
                 uint32_t it = 0, ccount = 0;   // K-slabs and accumulation chunks issued so far by this CTA
-                for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+                for (int unit = sched_id; unit < num_units; unit += sched_n) {
                     const Unit un = get_unit(p, unit, num_k);
                     for (int kc0 = un.k0; kc0 < un.k1; kc0 += chunk, ccount++) {
                         const int kc1 = min(kc0 + chunk, un.k1);
                         const uint32_t buf = ccount % ACC;
-                        if (ccount >= uint32_t(ACC) && !mbar_wait(&s.acc_empty[buf], ((ccount / ACC) - 1) & 1, abort_flag)) {
+                        if (ccount >= uint32_t(ACC) &&
+                            !(PAIR ? mbar_wait_cluster(&s.acc_empty[buf], ((ccount / ACC) - 1) & 1, abort_flag) : mbar_wait(&s.acc_empty[buf], ((ccount / ACC) - 1) & 1, abort_flag))) {
                             give_up(abort_flag, p.status, kErrWaitAccEmpty);
                             goto mma_done;
                         }
@@ -322,15 +353,41 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         for (int k = kc0; k < kc1; k++, it++) {
                             int st = it % STAGES;
                             uint32_t par = (it / STAGES) & 1;
-                            if (!mbar_wait(&s.full_tma[st], par, abort_flag)) {
+                            if (!mbar_wait(PAIR ? &s.full_b[st] : &s.full_tma[st], par, abort_flag)) {
                                 give_up(abort_flag, p.status, kErrWaitTma);
                                 goto mma_done;
                             }
-                            if (!mbar_wait(&s.full_split[st], par, abort_flag)) {
+                            if (!(PAIR ? mbar_wait_cluster(&s.full_split[st], par, abort_flag) : mbar_wait(&s.full_split[st], par, abort_flag))) {
                                 give_up(abort_flag, p.status, kErrWaitSplit);
                                 goto mma_done;
                             }
                             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                            if (PAIR) {
+                                // 256 x BN over the pair: A (hi / lo) at the same shared- or tensor-memory offsets in both CTAs, the
+                                // weight half of each CTA at the same shared-memory offset
+                                const uint64_t pb_hi = umma_desc_k_major<BK>(smem_u32(s.b_hi[st])), pb_lo = umma_desc_k_major<BK>(smem_u32(s.b_lo[BF16 ? 0 : st]));
+                                if (TS) {
+                                    const uint32_t a_hi = tmem_base + kColA + uint32_t(st * kACols), a_lo = a_hi + uint32_t(BK);
+#pragma unroll
+                                    for (int kk = 0; kk < BK / 8; kk++) {
+                                        const uint64_t adv = uint64_t((kk * 8 * 4) >> 4);
+                                        umma_tf32_ts_pair(tmem_acc, a_lo + uint32_t(kk * 8), pb_hi + adv, kIdesc, (k > kc0 || kk > 0) ? 1u : 0u);
+                                        umma_tf32_ts_pair(tmem_acc, a_hi + uint32_t(kk * 8), pb_lo + adv, kIdesc, 1u);
+                                        umma_tf32_ts_pair(tmem_acc, a_hi + uint32_t(kk * 8), pb_hi + adv, kIdesc, 1u);
+                                    }
+                                } else {
+                                    const uint64_t a_hi = umma_desc_k_major<BK>(smem_u32(s.a[st])), a_lo = umma_desc_k_major<BK>(smem_u32(s.a_lo[st]));
+#pragma unroll
+                                    for (int kk = 0; kk < BK / 8; kk++) {
+                                        const uint64_t adv = uint64_t((kk * 8 * 4) >> 4);
+                                        umma_tf32_pair(tmem_acc, a_lo + adv, pb_hi + adv, kIdesc, (k > kc0 || kk > 0) ? 1u : 0u);
+                                        umma_tf32_pair(tmem_acc, a_hi + adv, pb_lo + adv, kIdesc, 1u);
+                                        umma_tf32_pair(tmem_acc, a_hi + adv, pb_hi + adv, kIdesc, 1u);
+                                    }
+                                }
+                                umma_commit_pair(&s.empty[st]);   // frees the stage in both CTAs
+                                continue;
+                            }
                             if (BF16) {
                                 const uint32_t a_bf = tmem_base + kColA + uint32_t(st * kACols);   // 8 columns (16 bf16) per K-step
                                 const uint64_t b_bf = umma_desc_k_major_bytes<BK * 2>(smem_u32(s.b_hi[st]));
@@ -373,7 +430,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                             }
                             umma_commit(&s.empty[st]);  // arrives once the MMAs above have consumed the stage
                         }
-                        umma_commit(&s.acc_full[buf]);
+                        if (PAIR) umma_commit_pair(&s.acc_full[buf]);
+                        else umma_commit(&s.acc_full[buf]);
                     }
                 }
             mma_done:;
@@ -389,7 +447,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             const uint32_t lane_base = uint32_t(quarter * 32) << 16;
             // TMA swizzle: the 16-byte chunks of a row are permuted by the row index (64-byte rows: bits 1-2, 128-byte rows: bits 0-2)
             const int sw = BK == 16 ? ((row >> 1) & 3) : (row & 7);
-            for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+            for (int unit = sched_id; unit < num_units; unit += sched_n) {
                 const Unit un = get_unit(p, unit, num_k);
                 for (int k = un.k0; k < un.k1; k++, it++) {
                     int st = it % STAGES;
@@ -450,13 +508,16 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     tmem_wait_st();
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&s.full_split[st]);
+                    if (lane == 0) {
+                        if (PAIR) mbar_arrive_leader(&s.full_split[st]);
+                        else mbar_arrive(&s.full_split[st]);
+                    }
                 }
             }
         } else {
             // ---------------- activation split in shared memory (hi in place, lo into the twin buffer) ----------------
             const int t = threadIdx.x - kSplitWarp0 * 32;  // 0..127
-            for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+            for (int unit = sched_id; unit < num_units; unit += sched_n) {
                 const Unit un = get_unit(p, unit, num_k);
                 for (int k = un.k0; k < un.k1; k++, it++) {
                     int st = it % STAGES;
@@ -479,7 +540,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA (async proxy)
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&s.full_split[st]);
+                    if (lane == 0) {
+                        if (PAIR) mbar_arrive_leader(&s.full_split[st]);
+                        else mbar_arrive(&s.full_split[st]);
+                    }
                 }
             }
         }
@@ -492,13 +556,16 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         float* stage = s.stage_out[warp];
         const uint32_t lane_base = uint32_t(q * 32) << 16;
         uint32_t ccount = 0;
-        for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+        for (int unit = sched_id; unit < num_units; unit += sched_n) {
             const Unit un = get_unit(p, unit, num_k);
             int tm, tn;
             tile_coords(p, un.tile, tm, tn);
+            if (PAIR) tm = tm * 2 + rank;   // this CTA's 128 rows of the pair's 256-row tile
             const bool writes_partial = un.nparts > 1 && un.part > 0;
             const bool adds_partials = un.nparts > 1 && un.part == 0;
-            float* ws_mine = p.ws + size_t(un.u) * size_t(BM * BN);
+            // partial-tile slot of (unit, CTA of the pair); the parts of one tile are `pstep` slots apart
+            const int slot = PAIR ? un.u * 2 + rank : un.u, pstep = PAIR ? 2 : 1;
+            float* ws_mine = p.ws + size_t(slot) * size_t(BM * BN);
             // ---- running sums of this thread's row over the K chunks of the unit ----
             float sum[HALF];   // start from zero and always add: one code path keeps the register allocation tight
 #pragma unroll
@@ -517,14 +584,17 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                 // the chunk is in registers: hand the TMEM buffer back
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_leader(&s.acc_empty[buf]);
+                    else mbar_arrive(&s.acc_empty[buf]);
+                }
             }
             if (!alive) break;
             if (adds_partials) {
                 // the other K-parts of this tile run on other CTAs of this launch; wait for this warp's share of each
                 int ok = 1;
                 if (lane == 0)
-                    for (int pp = 1; pp < un.nparts && ok; pp++) ok = flag_wait(p.flags + (un.u + pp) * kEpiWarps + warp, abort_flag) ? 1 : 0;
+                    for (int pp = 1; pp < un.nparts && ok; pp++) ok = flag_wait(p.flags + (slot + pp * pstep) * kEpiWarps + warp, abort_flag) ? 1 : 0;
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) {
                     give_up(abort_flag, p.status, kErrWaitPartial);
@@ -568,7 +638,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     if (adds_partials) {
                         // the loads of a part are issued before the first add: one L2 round trip per part and group
                         for (int pp = 1; pp < un.nparts; pp++) {
-                            const float* src = wrow + size_t(pp) * size_t(BM * BN) + g * 16;
+                            const float* src = wrow + size_t(pp * pstep) * size_t(BM * BN) + g * 16;
                             float4 w[4];
 #pragma unroll
                             for (int i = 0; i < 4; i++) w[i] = __ldcg(reinterpret_cast<const float4*>(src + i * 8 * BN));
@@ -621,7 +691,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                             float v = stage[rr * kStagePad + cl];
                             if (adds_partials)
                                 for (int pp = 1; pp < un.nparts; pp++)
-                                    v += __ldcg(ws_mine + size_t(pp) * size_t(BM * BN) + (row0 + rr) * BN + chalf * HALF + g * 16 + cl);
+                                    v += __ldcg(ws_mine + size_t(pp * pstep) * size_t(BM * BN) + (row0 + rr) * BN + chalf * HALF + g * 16 + cl);
                             v += b;
                             bool row_ok;
                             const int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
@@ -636,20 +706,22 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             if (writes_partial) {
                 __threadfence();
                 __syncwarp();
-                if (lane == 0) flag_set(p.flags + un.u * kEpiWarps + warp, 1);
+                if (lane == 0) flag_set(p.flags + slot * kEpiWarps + warp, 1);
             } else if (adds_partials) {
                 __syncwarp();   // every lane has read its partials: lower the flags for the next launch
                 if (lane == 0)
-                    for (int pp = 1; pp < un.nparts; pp++) flag_set(p.flags + (un.u + pp) * kEpiWarps + warp, 0);
+                    for (int pp = 1; pp < un.nparts; pp++) flag_set(p.flags + (slot + pp * pstep) * kEpiWarps + warp, 0);
             }
         }
     }
     // ---------------- teardown (every thread arrives here, whatever happened above) ----------------
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (PAIR) cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while the other may still touch its memory
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
 }
 
@@ -758,8 +830,11 @@ int make_map_nhwc(CUtensorMap* map, const float* base, int N, int H, int W, int 
 // meet the same rule end to end.
 constexpr int kChunkKDense = 1024, kChunkKConv = 64;
 
-template <int BN, int BK, int STAGES, bool TS, bool BF16 = false, bool HYB = false>
+template <int BN, int BK, int STAGES, bool TS, bool BF16 = false, bool HYB = false, bool PAIR = false>
 int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, const ConvGeom* geom = nullptr) {
+    constexpr int BNB = PAIR ? BN / 2 : BN;      // weight rows one CTA stages
+    constexpr int TM = PAIR ? 2 * BM : BM;       // rows of a scheduled tile (a CTA pair works on 256)
+    FXF_CHECK(!PAIR || cv == nullptr, "CTA pairs are not used for convolutions");
     CUtensorMap mx, mhi, mlo;
     if (cv) {
         if (make_map_nhwc(&mx, cv->x, cv->N, cv->H, cv->W, cv->C, geom->BNI, geom->BH, geom->BW, BK, geom->str_h, geom->str_w)) return 1;
@@ -768,8 +843,8 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
         if (make_map_bf16(&mhi, a.w_hi, a.N, a.K, a.K, BN, BK)) return 1;
         mlo = mhi;
     } else {
-        if (make_map(&mhi, a.w_hi, a.N, a.K, a.K, BN, BK)) return 1;
-        if (make_map(&mlo, a.w_lo, a.N, a.K, a.K, BN, BK)) return 1;
+        if (make_map(&mhi, a.w_hi, a.N, a.K, a.K, BNB, BK)) return 1;
+        if (make_map(&mlo, a.w_lo, a.N, a.K, a.K, BNB, BK)) return 1;
     }
     TcParams p{};
     if (geom) {
@@ -781,28 +856,31 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
     p.bias = a.bias; p.residual = cv ? cv->residual : a.residual; p.out = a.out; p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo;
     p.relu = a.relu ? 1 : 0;
     p.vec_out = (a.ldo % 4 == 0 && aligned16(a.out) && (a.bias == nullptr || aligned16(a.bias)) && (p.residual == nullptr || aligned16(p.residual))) ? 1 : 0;
-    p.tiles_m = int((a.M + BM - 1) / BM);
+    p.tiles_m = int((a.M + TM - 1) / TM);
     p.tiles_n = int((a.N + BN - 1) / BN);
     // walk tiles so that the operand that does not fit in L2 is the one reused by concurrent CTAs
     p.m_fastest = a.N > a.M ? 1 : 0;
     p.status = ctx.status;
-    size_t smem = sizeof(TcSmem<BN, BK, STAGES, TS, BF16>) + 1024;
+    size_t smem = sizeof(TcSmem<BNB, BK, STAGES, TS, BF16>) + 1024;
     static bool configured[64] = {};
     int dev = 0;
     FXF_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        FXF_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, BK, STAGES, TS, BF16, HYB>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        FXF_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, BK, STAGES, TS, BF16, HYB, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
-    TailSplit ts = plan_tail(tiles, a.K, BN, ctx.sm_count, ctx.gemm_ws != nullptr && ctx.gemm_flags != nullptr);
-    if (ts.parts > 1 && (size_t(ts.tail) * ts.parts * size_t(BM * BN) * sizeof(float) > ctx.gemm_ws_bytes || ts.tail * ts.parts * kEpiWarps > ctx.gemm_flag_count))
+    // work units are scheduled over CTAs, or over CTA pairs (each CTA of a pair needs its own partial-tile slot and flags)
+    const int workers = PAIR ? ctx.sm_count / 2 : ctx.sm_count, slots_per_unit = PAIR ? 2 : 1;
+    TailSplit ts = plan_tail(tiles, a.K, BN, workers, ctx.gemm_ws != nullptr && ctx.gemm_flags != nullptr);
+    if (ts.parts > 1 && (size_t(ts.tail) * ts.parts * slots_per_unit * size_t(BM * BN) * sizeof(float) > ctx.gemm_ws_bytes ||
+                         ts.tail * ts.parts * slots_per_unit * kEpiWarps > ctx.gemm_flag_count))
         ts = TailSplit{tiles, 0, 1, 0.0, 0.0};
     p.full_tiles = int(ts.full); p.tail_tiles = int(ts.tail); p.tail_split = ts.parts;
     p.chunk_slabs = std::max(1, (ctx.tc_chunk_k > 0 ? ctx.tc_chunk_k : ((cv || a.conv_chain) ? kChunkKConv : kChunkKDense)) / BK);
     p.ws = ctx.gemm_ws; p.flags = ctx.gemm_flags;
     const int64_t units = ts.full + ts.tail * ts.parts;
-    int grid = int(units < ctx.sm_count ? units : ctx.sm_count);
+    int grid = int(units < workers ? units : workers) * slots_per_unit;
     if (cv) {
         const double pix = double(cv->N) * cv->HO * cv->WO;
         tag_launch(ctx, BF16 ? "conv2d_igemm_bf16_tcgen05" : "conv2d_igemm_tf32x3_tcgen05", 2.0 * pix * double(a.N) * double(a.K),
@@ -811,7 +889,23 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
         tag_launch(ctx, BF16 ? "gemm_bf16_tcgen05" : "gemm_tf32x3_tcgen05", 2.0 * double(a.M) * double(a.N) * double(a.K),
                    4.0 * (double(a.M) * a.K + double(a.N) * a.K + double(a.N) + double(a.M) * a.N));
     }
-    gemm_tf32x3_kernel<BN, BK, STAGES, TS, BF16, HYB><<<grid, kThreads, smem, ctx.stream>>>(mx, mhi, mlo, p);
+    if (PAIR) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(unsigned(grid));
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = ctx.stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        FXF_CUDA(cudaLaunchKernelEx(&cfg, gemm_tf32x3_kernel<BN, BK, STAGES, TS, BF16, HYB, PAIR>, mx, mhi, mlo, p));
+    } else {
+        gemm_tf32x3_kernel<BN, BK, STAGES, TS, BF16, HYB, PAIR><<<grid, kThreads, smem, ctx.stream>>>(mx, mhi, mlo, p);
+    }
     FXF_LAUNCHED(ctx);
     return 0;
 }
@@ -893,6 +987,10 @@ int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows) {
     if (a.w_is_bf16) {  // bf16 mode: one product per logical product, A converted into tensor memory
         if (bn >= 192 && a.N > 128) return launch_tc<192, 32, 6, true, true>(a, ctx);
         return launch_tc<128, 32, 8, true, true>(a, ctx);
+    }
+    if (ctx.tc_pair && a.M > BM && ctx.sm_count >= 2) {   // two CTAs per 256-row tile, each staging half of the weight tile
+        if (bn >= 224) return launch_tc<256, 16, 6, false, false, false, true>(a, ctx);
+        if (bn == 192) return launch_tc<192, 16, 4, true, false, false, true>(a, ctx);
     }
     switch (bn) {
         case 256: return launch_tc<256, 16, 4, false>(a, ctx);

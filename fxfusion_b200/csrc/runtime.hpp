@@ -95,6 +95,7 @@ struct ExecCtx {
     int* gemm_flags = nullptr;
     int gemm_flag_count = 0;
     int tc_chunk_k = 0;            // K-elements per tensor-core accumulation chain (0 = the kernel's default)
+    int tc_pair = 0;               // 1: wide tensor-core GEMM tiles are computed by CTA pairs (tcgen05 cta_group::2)
     // profiling: when `trace` is set every launch appends a record carrying the current tag
     std::vector<LaunchRecord>* trace = nullptr;
     int cur_node = -1;

@@ -66,8 +66,8 @@ def feedforward_static(x, w1, b1, w2, b2, out) -> None:
     import torch
     lib = _lib.lib()
     D = x.shape[-1]
-    M = x.numel() // D if D else 0
     F, P = w1.shape[0], w2.shape[0]
+    M = out.numel() // P if P else (x.numel() // D if D else 0)   # rows come from the output: x has no elements when D == 0
     stream = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
     _lib.check(lib.fxf_feedforward_static(x.data_ptr(), w1.data_ptr(), b1.data_ptr(), w2.data_ptr(), b2.data_ptr(), out.data_ptr(),
                                           M, D, F, P, stream))

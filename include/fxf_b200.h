@@ -84,7 +84,9 @@ typedef struct FxfEngineOptions {
     int32_t tc_chunk_k;            /* K-elements per tensor-core accumulation chain before the partial sums are added in fp32
                                       by CUDA cores (0 = 1024 for dense layers, 64 for convolutions); larger = fewer
                                       drains, more truncation bias per chain (about 4e-8 of the result's scale per element) */
-    int32_t reserved[4];
+    int32_t tc_pair;               /* 1: wide tensor-core GEMM tiles (192 / 256 columns) are computed by pairs of CTAs
+                                      (tcgen05 cta_group::2: 256-row tiles, each CTA stages half of the weight tile) */
+    int32_t reserved[3];
 } FxfEngineOptions;
 
 typedef struct fxf_engine fxf_engine;

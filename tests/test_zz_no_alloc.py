@@ -26,7 +26,9 @@ def _problem(M, D, F, P, seed):
 def test_static_feedforward_matches_existing_entry_point_twice(built_lib):
     from fxfusion_b200.kernels import feedforward_static, invoke
     assert built_lib.fxf_feedforward_static_max_bytes() == 8 << 20
-    for M, D, F, P, seed in [(300, 96, 1000, 64, 1), (130, 96, 200, 50, 2)]:
+    # the last case has at most 64 rows against a weight of a megabyte: the few-rows kernels, which must not cut K into parts
+    # here because this entry point hands them no workspace
+    for M, D, F, P, seed in [(300, 96, 1000, 64, 1), (130, 96, 200, 50, 2), (8, 1024, 1024, 64, 3)]:
         x, w1, b1, w2, b2 = _problem(M, D, F, P, seed)
         want = torch.zeros(M, P, device="cuda")
         invoke("FeedForward", [x, w1, b1, w2, b2, want], [0, 1, 2, 3, 4], [5], precision="fp32_simt")
@@ -37,6 +39,18 @@ def test_static_feedforward_matches_existing_entry_point_twice(built_lib):
         assert torch.allclose(got, want, atol=ATOL, rtol=RTOL), (got - want).abs().max().item()
         ref = torch.relu(x.cpu() @ w1.cpu().T + b1.cpu()) @ w2.cpu().T + b2.cpu()
         assert torch.allclose(got.cpu(), ref, atol=ATOL, rtol=RTOL)
+
+
+def test_static_feedforward_with_empty_extents(built_lib):
+    """No hidden units (F = 0): the output is the second bias; no input columns (D = 0): the hidden layer is relu(b1)."""
+    from fxfusion_b200.kernels import feedforward_static
+    for M, D, F, P, seed in [(40, 64, 0, 16, 4), (5, 0, 32, 7, 5)]:
+        x, w1, b1, w2, b2 = _problem(M, D, F, P, seed)
+        got = torch.full((M, P), float("nan"), device="cuda")
+        feedforward_static(x, w1, b1, w2, b2, got)
+        torch.cuda.synchronize()
+        ref = torch.relu(x.cpu() @ w1.cpu().T + b1.cpu()) @ w2.cpu().T + b2.cpu()
+        assert torch.allclose(got.cpu(), ref, atol=ATOL, rtol=RTOL), (M, D, F, P)
 
 
 def test_static_feedforward_refuses_oversized_problems(built_lib):
