@@ -300,6 +300,15 @@ def kernel_table(trace, precision: str, peaks, tf32_peak):
     return by, kernels, total_ms, tensor_ceiling
 
 
+def engine_options(args):
+    """`--engine-option name=value` pairs (integer fields of FxfEngineOptions, e.g. tc_pair=1) for experiments."""
+    out = {}
+    for item in args.engine_option or []:
+        k, _, v = item.partition("=")
+        out[k] = int(v)
+    return out
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -329,7 +338,7 @@ def run_ours(args):
         comm = Communicator.from_process_group(local, ranks=groups[mine], group=handles[mine])
     dp_rank = rank // tp_size
     graph_path = build_graph_file(B, tmp.name)
-    eng = ExecutionEngine(graph_path, f"cuda:{local}", precision=args.precision, comm=comm, shard_output=comm is not None)
+    eng = ExecutionEngine(graph_path, f"cuda:{local}", precision=args.precision, comm=comm, shard_output=comm is not None, **engine_options(args))
     lib = _lib.lib()
     prompt = torch.from_numpy(lowering.decode_prompt(B, PROMPT, cfg.vocab, seed=dp_rank))
     start_buf = torch.zeros((B, T), dtype=torch.int64)
@@ -815,6 +824,8 @@ def main():
                     help="bf16 = optional reduced-precision mode (bf16 tensor-core products, fp32 accumulation); not the headline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the opt-in decode variants and the secondary workloads (keeps profiler captures short)")
+    ap.add_argument("--engine-option", action="append", default=[], metavar="NAME=VALUE",
+                    help="integer field of FxfEngineOptions for the benchmark engine (tc_pair, tc_chunk_k, no_tp_fused_exchange, ...); repeatable")
     ap.add_argument("--parallel", default="tp", choices=["tp", "replicas"],
                     help="N > 1: tensor-parallel groups of 4 or 2 GPUs (default: the batch-32 decode sharded over heads, hidden units and "
                          "vocabulary) or N independent batch-32 replicas")

@@ -138,6 +138,7 @@ struct TcParams {
     // (unit-major, 128 x BN floats each) and raise flags[unit*4 + warp]; part 0 adds them in part order (deterministic).
     int full_tiles, tail_tiles, tail_split;
     int chunk_slabs;   // K-slabs per accumulation chain (>= 1)
+    int pair_sync;     // CTA pairs, experiment switch: bit 0 = CTA-scope waits in the MMA thread, bit 1 = CTA-scope remote arrives
     float* ws;
     int* flags;
     int* status;
@@ -198,6 +199,9 @@ __device__ __forceinline__ int64_t out_row_offset(const TcParams& p, int tm, int
     return ((int64_t(n) * c.HO + oy) * c.WO + ox) * p.ldo;
 }
 
+#ifdef FXF_TC_PROFILE
+__device__ long long g_tc_prof[148 * 8];
+#endif
 // 32 consecutive TMEM columns of this thread's lane (tcgen05.ld 32x32b.x32) or 16 (x16)
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
@@ -338,29 +342,48 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             // ---------------- MMA issuer ----------------
             if (lane == 0 && rank == 0) {   // in a pair only the leader issues MMAs (for both CTAs)
                 uint32_t it = 0, ccount = 0;   // K-slabs and accumulation chunks issued so far by this CTA
+#ifdef FXF_TC_PROFILE
+                long long t_tma = 0, t_split = 0, t_acc = 0, t_begin = clock64(), tq;
+#endif
                 for (int unit = sched_id; unit < num_units; unit += sched_n) {
                     const Unit un = get_unit(p, unit, num_k);
                     for (int kc0 = un.k0; kc0 < un.k1; kc0 += chunk, ccount++) {
                         const int kc1 = min(kc0 + chunk, un.k1);
                         const uint32_t buf = ccount % ACC;
+#ifdef FXF_TC_PROFILE
+                        tq = clock64();
+#endif
                         if (ccount >= uint32_t(ACC) &&
-                            !(PAIR ? mbar_wait_cluster(&s.acc_empty[buf], ((ccount / ACC) - 1) & 1, abort_flag) : mbar_wait(&s.acc_empty[buf], ((ccount / ACC) - 1) & 1, abort_flag))) {
+                            !((PAIR && !(p.pair_sync & 1)) ? mbar_wait_cluster(&s.acc_empty[buf], ((ccount / ACC) - 1) & 1, abort_flag) : mbar_wait(&s.acc_empty[buf], ((ccount / ACC) - 1) & 1, abort_flag))) {
                             give_up(abort_flag, p.status, kErrWaitAccEmpty);
                             goto mma_done;
                         }
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#ifdef FXF_TC_PROFILE
+                        t_acc += clock64() - tq;
+#endif
                         const uint32_t tmem_acc = tmem_base + buf * uint32_t(BN);
                         for (int k = kc0; k < kc1; k++, it++) {
                             int st = it % STAGES;
                             uint32_t par = (it / STAGES) & 1;
+#ifdef FXF_TC_PROFILE
+                            tq = clock64();
+#endif
                             if (!mbar_wait(PAIR ? &s.full_b[st] : &s.full_tma[st], par, abort_flag)) {
                                 give_up(abort_flag, p.status, kErrWaitTma);
                                 goto mma_done;
                             }
-                            if (!(PAIR ? mbar_wait_cluster(&s.full_split[st], par, abort_flag) : mbar_wait(&s.full_split[st], par, abort_flag))) {
+#ifdef FXF_TC_PROFILE
+                            t_tma += clock64() - tq;
+                            tq = clock64();
+#endif
+                            if (!((PAIR && !(p.pair_sync & 1)) ? mbar_wait_cluster(&s.full_split[st], par, abort_flag) : mbar_wait(&s.full_split[st], par, abort_flag))) {
                                 give_up(abort_flag, p.status, kErrWaitSplit);
                                 goto mma_done;
                             }
+#ifdef FXF_TC_PROFILE
+                            t_split += clock64() - tq;
+#endif
                             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                             if (PAIR) {
                                 // 256 x BN over the pair: A (hi / lo) at the same shared- or tensor-memory offsets in both CTAs, the
@@ -435,6 +458,12 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     }
                 }
             mma_done:;
+#ifdef FXF_TC_PROFILE
+                if (blockIdx.x < 148) {   // the MMA thread's cycles: total, waiting for tiles, for the split, for an accumulator; slabs issued
+                    long long* prof = g_tc_prof + blockIdx.x * 8;
+                    prof[0] = clock64() - t_begin; prof[1] = t_tma; prof[2] = t_split; prof[3] = t_acc; prof[4] = it;
+                }
+#endif
             }
         }
     } else if (warp >= kSplitWarp0) {
@@ -509,7 +538,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
-                        if (PAIR) mbar_arrive_leader(&s.full_split[st]);
+                        if (PAIR && (p.pair_sync & 2)) mbar_arrive_leader_relaxed_scope(&s.full_split[st]);
+                        else if (PAIR) mbar_arrive_leader(&s.full_split[st]);
                         else mbar_arrive(&s.full_split[st]);
                     }
                 }
@@ -541,7 +571,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA (async proxy)
                     __syncwarp();
                     if (lane == 0) {
-                        if (PAIR) mbar_arrive_leader(&s.full_split[st]);
+                        if (PAIR && (p.pair_sync & 2)) mbar_arrive_leader_relaxed_scope(&s.full_split[st]);
+                        else if (PAIR) mbar_arrive_leader(&s.full_split[st]);
                         else mbar_arrive(&s.full_split[st]);
                     }
                 }
@@ -585,7 +616,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) {
-                    if (PAIR) mbar_arrive_leader(&s.acc_empty[buf]);
+                    if (PAIR && (p.pair_sync & 2)) mbar_arrive_leader_relaxed_scope(&s.acc_empty[buf]);
+                    else if (PAIR) mbar_arrive_leader(&s.acc_empty[buf]);
                     else mbar_arrive(&s.acc_empty[buf]);
                 }
             }
@@ -879,6 +911,7 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
     p.full_tiles = int(ts.full); p.tail_tiles = int(ts.tail); p.tail_split = ts.parts;
     p.chunk_slabs = std::max(1, (ctx.tc_chunk_k > 0 ? ctx.tc_chunk_k : ((cv || a.conv_chain) ? kChunkKConv : kChunkKDense)) / BK);
     p.ws = ctx.gemm_ws; p.flags = ctx.gemm_flags;
+    p.pair_sync = ctx.tc_pair > 0 ? ctx.tc_pair - 1 : 0;
     const int64_t units = ts.full + ts.tail * ts.parts;
     int grid = int(units < workers ? units : workers) * slots_per_unit;
     if (cv) {
@@ -1120,6 +1153,12 @@ int launch_conv_weight_bf16(const float* w_oihw, void* out, int O, int C, int KH
     FXF_LAUNCHED(ctx);
     return 0;
 }
+
+#ifdef FXF_TC_PROFILE
+extern "C" __attribute__((visibility("default"))) int fxf_tc_prof_read(long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, g_tc_prof, sizeof(long long) * 148 * 8) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 int launch_split_tf32(const float* w, float* hi, float* lo, int64_t n, ExecCtx& ctx) {
     if (n == 0) return 0;

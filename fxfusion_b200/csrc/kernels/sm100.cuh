@@ -183,6 +183,11 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
         }
     }
 }
+// the same arrival with the default (CTA-scope) release: enough when what the arrival publishes was already made visible to
+// the consuming proxy by its own fence (fence.proxy.async / tcgen05.fence)
+__device__ __forceinline__ void mbar_arrive_leader_relaxed_scope(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & kPeerBitMask) : "memory");
+}
 // Tile load issued by either CTA of a pair into its own shared memory, completion counted on the LEADER's barrier.
 __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
