@@ -268,6 +268,7 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
     env.gemm_mode = e->opts.gemm_mode;
     env.tp_rank = e->opts.tp_rank;
     env.tp_size = e->opts.tp_size;
+    env.tc_pairs = e->opts.tc_pair != 1;
     for (uint32_t i = 0; i < n_nodes; i++) {
         fbs::Table nt = g.table_at(fbs::GraphF::nodes, i);
         int op = nt.scalar<int8_t>(fbs::NodeF::op_code, 0);

@@ -94,12 +94,12 @@ __device__ __forceinline__ void reg_set() {   // the kernel starts with 128 regi
 }
 
 // BNB = weight rows held by this CTA: BN, or BN / 2 when two CTAs share a 256-row tile (each stages half of the weight tile)
-template <int BNB, int BK, int STAGES, bool TS, bool BF16>
+template <int BNB, int BK, int STAGES, bool TS, bool BF16, bool MIX = false>
 struct alignas(1024) TcSmem {
     float a[STAGES][BM * BK];             // x tile as TMA wrote it (fp32, swizzled rows of BK floats); x_hi in place when !TS
     float a_lo[TS ? 1 : STAGES][TS ? 256 : BM * BK];  // x_lo twin buffers, only when the MMAs read A from shared memory
     float b_hi[STAGES][BF16 ? BNB * BK / 2 : BNB * BK];   // w_hi tile (fp32), or the whole bf16 weight tile in bf16 mode
-    float b_lo[BF16 ? 1 : STAGES][BF16 ? 256 : BNB * BK];
+    float b_lo[BF16 ? 1 : STAGES][BF16 ? 256 : (MIX ? BNB * BK / 2 : BNB * BK)];   // w_lo tile: fp32, or bf16 in the mixed variant
     float stage_out[kEpiWarps][32 * kStagePad];   // one 32 x 16 block per epilogue warp
     uint64_t full_tma[STAGES];
     uint64_t full_b[STAGES];      // CTA pairs only: the weight halves of both CTAs have landed (the leader's copy counts)
@@ -138,7 +138,6 @@ struct TcParams {
     // (unit-major, 128 x BN floats each) and raise flags[unit*4 + warp]; part 0 adds them in part order (deterministic).
     int full_tiles, tail_tiles, tail_split;
     int chunk_slabs;   // K-slabs per accumulation chain (>= 1)
-    int pair_sync;     // CTA pairs, experiment switch: bit 0 = CTA-scope waits in the MMA thread, bit 1 = CTA-scope remote arrives
     float* ws;
     int* flags;
     int* status;
@@ -233,18 +232,29 @@ __device__ __forceinline__ void drain_chunk(uint32_t tacc, float (&sum)[HALF]) {
 // to a half.  The leader (even rank) issues the MMAs for both; every CTA splits its own x rows and drains / stores its own
 // 128 accumulator rows.  Barriers that gate the MMA (weight halves landed, x split, accumulator drained) live in the leader
 // and are reached by the other CTA through the shared::cluster window; MMA completion is committed to both CTAs.
-template <int BN, int BK, int STAGES, bool TS, bool BF16, bool HYB, bool PAIR>
+// VAR selects how the three products of a logical product are formed:
+//   0  three TF32 products, A (hi and lo) from shared memory or from tensor memory (TS)
+//   1  hybrid: x_hi read from shared memory as delivered, x_lo from tensor memory
+//   2  mixed: x_hi * w_hi and x_lo * w_hi as TF32 products against the one fp32 w_hi tile (x_hi read from shared memory as
+//      delivered, x_lo from tensor memory), and the third product x_hi * w_lo as ONE bf16 MMA (kind::f16, K = 16 per
+//      instruction): bf16(x) packed into tensor memory by the split warps, w_lo kept and fetched as bf16.  w_lo is 2^-11
+//      of w, so its bf16 rounding (and that of x beside it) costs about 2^-20 of a product, below the tensor core's own
+//      accumulation error.  What it buys: 6 instead of 8 bytes per weight element through L2 and shared memory — these
+//      kernels run at the L2 -> SM fill rate (about 42 bytes per clock and SM, measured) — and a sixth less tensor time.
+template <int BN, int BK, int STAGES, bool TS, bool BF16, int VAR, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_whi,
                    const __grid_constant__ CUtensorMap map_wlo, TcParams p) {
     extern __shared__ unsigned char smem_raw[];
     // dynamic shared memory is only guaranteed 16-byte aligned; swizzled tiles need 1024
     static_assert(!BF16 || (TS && BK == 32), "the bf16 mode takes A from tensor memory with 32-float slabs");
+    constexpr bool HYB = VAR == 1, MIX = VAR == 2;
     static_assert(!HYB || (TS && !BF16), "hybrid: x_hi is the raw tile in shared memory, x_lo goes to tensor memory");
+    static_assert(!MIX || (TS && !BF16 && BK == 16), "mixed: x_lo and bf16(x) go to tensor memory, 16-deep slabs (one bf16 MMA each)");
     static_assert(BN % 32 == 0, "tile width must be a multiple of 32 columns (16 per column half and staging step)");
-    static_assert(!PAIR || (!BF16 && !HYB), "CTA pairs exist for the plain 3xTF32 variants");
+    static_assert(!PAIR || (!BF16 && VAR != 1), "CTA pairs exist for the plain 3xTF32 and the mixed variants");
     constexpr int BNB = PAIR ? BN / 2 : BN;   // weight rows staged by this CTA
-    using Smem = TcSmem<BNB, BK, STAGES, TS, BF16>;
+    using Smem = TcSmem<BNB, BK, STAGES, TS, BF16, VAR == 2>;
     using Regs = RegBudget<BN, BK, TS, BF16>;
     Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -254,11 +264,12 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     const int chunk = p.chunk_slabs > 0 ? p.chunk_slabs : num_k;
     const int rank = PAIR ? int(cluster_ctarank()) : 0;     // position inside the CTA pair; rank 0 issues the MMAs
     const int sched_id = PAIR ? int(blockIdx.x >> 1) : int(blockIdx.x), sched_n = PAIR ? int(gridDim.x >> 1) : int(gridDim.x);
-    constexpr uint32_t kBBytes = BF16 ? uint32_t(BNB * BK) * 2u : uint32_t(2 * BNB * BK) * 4u;   // weight bytes per stage and CTA
+    constexpr uint32_t kBBytes = BF16 ? uint32_t(BNB * BK) * 2u : (VAR == 2 ? uint32_t(BNB * BK) * 6u : uint32_t(2 * BNB * BK) * 4u);   // weight bytes per stage and CTA
     constexpr uint32_t kABytes = uint32_t(BM * BK) * 4u;
     constexpr uint32_t kStageBytes = kABytes + kBBytes;
     constexpr uint32_t kIdesc = BF16 ? umma_idesc_bf16(BM, BN) : umma_idesc_tf32(PAIR ? 2 * BM : BM, BN);
-    constexpr int kACols = BF16 ? BK / 2 : (HYB ? BK : 2 * BK);   // TMEM columns of one A stage
+    constexpr int kACols = BF16 ? BK / 2 : (MIX ? BK + BK / 2 : (HYB ? BK : 2 * BK));   // TMEM columns of one A stage (mixed: x_lo | bf16(x))
+    constexpr uint32_t kIdescBf = umma_idesc_bf16(PAIR ? 2 * BM : BM, BN);   // the bf16 product of the mixed variant
     constexpr uint32_t kColA = uint32_t(ACC * BN);             // first TMEM column of the A stages
     constexpr uint32_t kColsUsed = kColA + (TS ? uint32_t(STAGES * kACols) : 0u);
     static_assert(kColsUsed <= 512, "accumulators and A stages exceed the 512 TMEM columns");
@@ -333,7 +344,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                             tma_load_2d(s.a[st], &map_x, k * BK, tm * BM, &s.full_tma[st]);
                         }
                         tma_load_2d(s.b_hi[st], &map_whi, k * BK, tn * BN, &s.full_tma[st]);
-                        if (!BF16) tma_load_2d(s.b_lo[BF16 ? 0 : st], &map_wlo, k * BK, tn * BN, &s.full_tma[st]);
+                        if (!BF16) tma_load_2d(s.b_lo[BF16 ? 0 : st], &map_wlo, k * BK, tn * BN, &s.full_tma[st]);   // fp32 w_lo, or bf16 w_lo (mixed)
                     }
                 }
             producer_done:;
@@ -354,7 +365,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         tq = clock64();
 #endif
                         if (ccount >= uint32_t(ACC) &&
-                            !((PAIR && !(p.pair_sync & 1)) ? mbar_wait_cluster(&s.acc_empty[buf], ((ccount / ACC) - 1) & 1, abort_flag) : mbar_wait(&s.acc_empty[buf], ((ccount / ACC) - 1) & 1, abort_flag))) {
+                            !(PAIR ? mbar_wait_cluster(&s.acc_empty[buf], ((ccount / ACC) - 1) & 1, abort_flag) : mbar_wait(&s.acc_empty[buf], ((ccount / ACC) - 1) & 1, abort_flag))) {
                             give_up(abort_flag, p.status, kErrWaitAccEmpty);
                             goto mma_done;
                         }
@@ -377,7 +388,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                             t_tma += clock64() - tq;
                             tq = clock64();
 #endif
-                            if (!((PAIR && !(p.pair_sync & 1)) ? mbar_wait_cluster(&s.full_split[st], par, abort_flag) : mbar_wait(&s.full_split[st], par, abort_flag))) {
+                            if (!(PAIR ? mbar_wait_cluster(&s.full_split[st], par, abort_flag) : mbar_wait(&s.full_split[st], par, abort_flag))) {
                                 give_up(abort_flag, p.status, kErrWaitSplit);
                                 goto mma_done;
                             }
@@ -389,7 +400,18 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                                 // 256 x BN over the pair: A (hi / lo) at the same shared- or tensor-memory offsets in both CTAs, the
                                 // weight half of each CTA at the same shared-memory offset
                                 const uint64_t pb_hi = umma_desc_k_major<BK>(smem_u32(s.b_hi[st])), pb_lo = umma_desc_k_major<BK>(smem_u32(s.b_lo[BF16 ? 0 : st]));
-                                if (TS) {
+                                if (MIX) {
+                                    const uint64_t a_raw = umma_desc_k_major<BK>(smem_u32(s.a[st]));
+                                    const uint32_t a_lo = tmem_base + kColA + uint32_t(st * kACols), a_bf = a_lo + uint32_t(BK);
+                                    const uint64_t wlb = umma_desc_k_major_bytes<BK * 2>(smem_u32(s.b_lo[BF16 ? 0 : st]));
+                                    umma_bf16_ts_pair(tmem_acc, a_bf, wlb, kIdescBf, k > kc0 ? 1u : 0u);
+#pragma unroll
+                                    for (int kk = 0; kk < BK / 8; kk++) {
+                                        const uint64_t adv = uint64_t((kk * 8 * 4) >> 4);
+                                        umma_tf32_ts_pair(tmem_acc, a_lo + uint32_t(kk * 8), pb_hi + adv, kIdesc, 1u);
+                                        umma_tf32_pair(tmem_acc, a_raw + adv, pb_hi + adv, kIdesc, 1u);
+                                    }
+                                } else if (TS) {
                                     const uint32_t a_hi = tmem_base + kColA + uint32_t(st * kACols), a_lo = a_hi + uint32_t(BK);
 #pragma unroll
                                     for (int kk = 0; kk < BK / 8; kk++) {
@@ -421,7 +443,20 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                                 continue;
                             }
                             uint64_t b_hi = umma_desc_k_major<BK>(smem_u32(s.b_hi[st])), b_lo = umma_desc_k_major<BK>(smem_u32(s.b_lo[BF16 ? 0 : st]));
-                            if (HYB) {
+                            if (MIX) {
+                                // x_hi * w_lo: bf16(x) * bf16(w_lo), one 16-deep bf16 MMA; then per 8-deep step x_lo * w_hi (A from tensor
+                                // memory) and x_hi * w_hi (x as delivered in shared memory: the MMA truncates it to TF32)
+                                const uint64_t a_raw = umma_desc_k_major<BK>(smem_u32(s.a[st]));
+                                const uint32_t a_lo = tmem_base + kColA + uint32_t(st * kACols), a_bf = a_lo + uint32_t(BK);   // [x_lo fp32: 16 columns | bf16(x): 8 columns]
+                                const uint64_t wlb = umma_desc_k_major_bytes<BK * 2>(smem_u32(s.b_lo[BF16 ? 0 : st]));
+                                umma_bf16_ts(tmem_acc, a_bf, wlb, kIdescBf, k > kc0 ? 1u : 0u);
+#pragma unroll
+                                for (int kk = 0; kk < BK / 8; kk++) {
+                                    const uint64_t adv = uint64_t((kk * 8 * 4) >> 4);
+                                    umma_tf32_ts(tmem_acc, a_lo + uint32_t(kk * 8), b_hi + adv, kIdesc, 1u);
+                                    umma_tf32(tmem_acc, a_raw + adv, b_hi + adv, kIdesc, 1u);
+                                }
+                            } else if (HYB) {
                                 // x_hi = the fp32 tile as it lies in shared memory (the MMA truncates it), x_lo from tensor memory
                                 const uint32_t a_lo = tmem_base + kColA + uint32_t(st * kACols);
                                 const uint64_t a_hi = umma_desc_k_major<BK>(smem_u32(s.a[st]));
@@ -476,14 +511,27 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             const uint32_t lane_base = uint32_t(quarter * 32) << 16;
             // TMA swizzle: the 16-byte chunks of a row are permuted by the row index (64-byte rows: bits 1-2, 128-byte rows: bits 0-2)
             const int sw = BK == 16 ? ((row >> 1) & 3) : (row & 7);
+#ifdef FXF_TC_PROFILE
+            long long sp_wait = 0, sp_begin = clock64(), sq;
+#endif
             for (int unit = sched_id; unit < num_units; unit += sched_n) {
                 const Unit un = get_unit(p, unit, num_k);
                 for (int k = un.k0; k < un.k1; k++, it++) {
                     int st = it % STAGES;
+#ifdef FXF_TC_PROFILE
+                    sq = clock64();
+#endif
                     if (!mbar_wait(&s.full_tma[st], (it / STAGES) & 1, abort_flag)) {
                         give_up(abort_flag, p.status, kErrWaitTma);
                         goto split_done;
                     }
+#ifdef FXF_TC_PROFILE
+                    sp_wait += clock64() - sq;
+                    if (k + 1 == un.k1 && unit + sched_n >= num_units && warp == kSplitWarp0 && lane == 0 && blockIdx.x < 148) {
+                        g_tc_prof[blockIdx.x * 8 + 5] = clock64() - sp_begin;   // split warp 0: total cycles, cycles waiting for tiles
+                        g_tc_prof[blockIdx.x * 8 + 6] = sp_wait;
+                    }
+#endif
                     const float4* src = reinterpret_cast<const float4*>(s.a[st]) + row * (BK / 4);
                     if (BF16) {
                         // bf16 mode: the row's BK floats become BK/2 packed words (element k in the low half of word k/2)
@@ -499,6 +547,32 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&s.full_split[st]);
+                        continue;
+                    }
+                    if (MIX) {
+                        // what the TF32 truncation of x drops (fp32, 16 columns) and the row's 16 floats as 8 packed bf16 pairs
+                        // (element k in the low half of word k/2)
+                        uint32_t lo16[16], packed[8];
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            const float4 v = src[c ^ sw];
+                            lo16[4 * c + 0] = __float_as_uint(lo_of_truncated(v.x));
+                            lo16[4 * c + 1] = __float_as_uint(lo_of_truncated(v.y));
+                            lo16[4 * c + 2] = __float_as_uint(lo_of_truncated(v.z));
+                            lo16[4 * c + 3] = __float_as_uint(lo_of_truncated(v.w));
+                            packed[2 * c + 0] = pack_bf16x2(v.x, v.y);
+                            packed[2 * c + 1] = pack_bf16x2(v.z, v.w);
+                        }
+                        const uint32_t a_col = tmem_base + lane_base + kColA + uint32_t(st * kACols);
+                        tmem_st16(a_col, lo16);
+                        tmem_st8(a_col + uint32_t(BK), packed);
+                        tmem_wait_st();
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (PAIR) mbar_arrive_leader(&s.full_split[st]);
+                            else mbar_arrive(&s.full_split[st]);
+                        }
                         continue;
                     }
                     if (HYB) {
@@ -538,8 +612,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
-                        if (PAIR && (p.pair_sync & 2)) mbar_arrive_leader_relaxed_scope(&s.full_split[st]);
-                        else if (PAIR) mbar_arrive_leader(&s.full_split[st]);
+                        if (PAIR) mbar_arrive_leader(&s.full_split[st]);
                         else mbar_arrive(&s.full_split[st]);
                     }
                 }
@@ -571,8 +644,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA (async proxy)
                     __syncwarp();
                     if (lane == 0) {
-                        if (PAIR && (p.pair_sync & 2)) mbar_arrive_leader_relaxed_scope(&s.full_split[st]);
-                        else if (PAIR) mbar_arrive_leader(&s.full_split[st]);
+                        if (PAIR) mbar_arrive_leader(&s.full_split[st]);
                         else mbar_arrive(&s.full_split[st]);
                     }
                 }
@@ -616,8 +688,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) {
-                    if (PAIR && (p.pair_sync & 2)) mbar_arrive_leader_relaxed_scope(&s.acc_empty[buf]);
-                    else if (PAIR) mbar_arrive_leader(&s.acc_empty[buf]);
+                    if (PAIR) mbar_arrive_leader(&s.acc_empty[buf]);
                     else mbar_arrive(&s.acc_empty[buf]);
                 }
             }
@@ -832,7 +903,7 @@ int make_map_bf16(CUtensorMap* map, const void* base, int64_t rows, int64_t cols
     cuuint32_t box[2] = {cuuint32_t(bk), cuuint32_t(box_rows)};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    bk == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    bk == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B), CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     FXF_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (bf16) failed with code %d (rows %lld cols %lld ld %lld)", int(r), (long long)rows, (long long)cols, (long long)ld);
     return 0;
@@ -862,7 +933,7 @@ int make_map_nhwc(CUtensorMap* map, const float* base, int N, int H, int W, int 
 // meet the same rule end to end.
 constexpr int kChunkKDense = 1024, kChunkKConv = 64;
 
-template <int BN, int BK, int STAGES, bool TS, bool BF16 = false, bool HYB = false, bool PAIR = false>
+template <int BN, int BK, int STAGES, bool TS, bool BF16 = false, int VAR = 0, bool PAIR = false>
 int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, const ConvGeom* geom = nullptr) {
     constexpr int BNB = PAIR ? BN / 2 : BN;      // weight rows one CTA stages
     constexpr int TM = PAIR ? 2 * BM : BM;       // rows of a scheduled tile (a CTA pair works on 256)
@@ -874,7 +945,13 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
     if (BF16) {
         if (make_map_bf16(&mhi, a.w_hi, a.N, a.K, a.K, BN, BK)) return 1;
         mlo = mhi;
+    } else if (VAR == 2) {
+        // mixed: w_lo points to bf16(w - w_hi), an [N, K] bf16 matrix
+        FXF_CHECK(a.w_mixed, "the mixed GEMM variant needs weights prepared for it");
+        if (make_map(&mhi, a.w_hi, a.N, a.K, a.K, BNB, BK)) return 1;
+        if (make_map_bf16(&mlo, a.w_lo, a.N, a.K, a.K, BNB, BK)) return 1;
     } else {
+        FXF_CHECK(!a.w_mixed, "weights prepared for the mixed GEMM variant cannot feed the 3xTF32 kernels");
         if (make_map(&mhi, a.w_hi, a.N, a.K, a.K, BNB, BK)) return 1;
         if (make_map(&mlo, a.w_lo, a.N, a.K, a.K, BNB, BK)) return 1;
     }
@@ -893,12 +970,12 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
     // walk tiles so that the operand that does not fit in L2 is the one reused by concurrent CTAs
     p.m_fastest = a.N > a.M ? 1 : 0;
     p.status = ctx.status;
-    size_t smem = sizeof(TcSmem<BNB, BK, STAGES, TS, BF16>) + 1024;
+    size_t smem = sizeof(TcSmem<BNB, BK, STAGES, TS, BF16, VAR == 2>) + 1024;
     static bool configured[64] = {};
     int dev = 0;
     FXF_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        FXF_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, BK, STAGES, TS, BF16, HYB, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        FXF_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, BK, STAGES, TS, BF16, VAR, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
@@ -911,7 +988,6 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
     p.full_tiles = int(ts.full); p.tail_tiles = int(ts.tail); p.tail_split = ts.parts;
     p.chunk_slabs = std::max(1, (ctx.tc_chunk_k > 0 ? ctx.tc_chunk_k : ((cv || a.conv_chain) ? kChunkKConv : kChunkKDense)) / BK);
     p.ws = ctx.gemm_ws; p.flags = ctx.gemm_flags;
-    p.pair_sync = ctx.tc_pair > 0 ? ctx.tc_pair - 1 : 0;
     const int64_t units = ts.full + ts.tail * ts.parts;
     int grid = int(units < workers ? units : workers) * slots_per_unit;
     if (cv) {
@@ -935,9 +1011,9 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        FXF_CUDA(cudaLaunchKernelEx(&cfg, gemm_tf32x3_kernel<BN, BK, STAGES, TS, BF16, HYB, PAIR>, mx, mhi, mlo, p));
+        FXF_CUDA(cudaLaunchKernelEx(&cfg, gemm_tf32x3_kernel<BN, BK, STAGES, TS, BF16, VAR, PAIR>, mx, mhi, mlo, p));
     } else {
-        gemm_tf32x3_kernel<BN, BK, STAGES, TS, BF16, HYB, PAIR><<<grid, kThreads, smem, ctx.stream>>>(mx, mhi, mlo, p);
+        gemm_tf32x3_kernel<BN, BK, STAGES, TS, BF16, VAR, PAIR><<<grid, kThreads, smem, ctx.stream>>>(mx, mhi, mlo, p);
     }
     FXF_LAUNCHED(ctx);
     return 0;
@@ -995,15 +1071,18 @@ int gemm_tc_pick_bn(int64_t M, int64_t N, int sm_count, int64_t K) {
 // tensor pipe 62 %); from tensor memory the split writes nothing to shared memory and the MMA reads only B there (measured
 // on B200: 128-wide tiles gain 40 %, 192-wide 5-7 %).  256-wide tiles keep A in shared memory: TMEM (512 columns) holds the
 // two 256-column accumulators and nothing else.  224 = the widest tile that leaves TMEM room for x_lo stages (hybrid).
-//   256  A in shared memory (x_hi = the tile as delivered, x_lo twin buffer), BK 16, 4 stages
+//   256x256 pair  two CTAs of a cluster per 256-row tile (cta_group::2), A in shared memory, each CTA stages half of the
+//        weight tile, BK 16, 6 stages: the default for the widest tiles of plain GEMMs
+//   256  A in shared memory (x_hi = the tile as delivered, x_lo twin buffer), BK 16, 4 stages (convolutions; GEMMs with pairs off)
 //   224  hybrid: x_hi read from shared memory as delivered, x_lo from tensor memory, BK 16, 4 stages
 //   192  A (hi and lo) in tensor memory, BK 16, 4 stages
 //   128  A in tensor memory, BK 32, 4 stages;  64: the same with 64-wide tiles for N <= 64
-const char* gemm_tc_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool k_split, bool few_rows, int* bn_out) {
+const char* gemm_tc_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool k_split, bool few_rows, int* bn_out, bool pairs) {
     int bn = gemm_tc_pick_bn(M, N, sm_count, k_split ? K : 0);
     if (N <= 128) bn = N <= 64 ? 64 : 128;
     if (few_rows && M < 64) bn = N <= 64 ? 64 : 128;   // a weight-streaming problem: more, narrower tiles keep more SMs loading
     if (bn_out) *bn_out = bn;
+    if (pairs && M > BM && sm_count >= 2 && bn >= 224) return "tcgen05-tf32x3-256x256-pair-smemA";
     switch (bn) {
         case 256: return "tcgen05-tf32x3-128x256-smemA";
         case 224: return "tcgen05-tf32x3-128x224-hybridA";
@@ -1013,18 +1092,55 @@ const char* gemm_tc_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool 
     }
 }
 
+// Tile width of the mixed variant (two TF32 products + one bf16 product): 192, 128 or 64 — x_lo and bf16(x) live in tensor
+// memory (24 columns per stage), which two 256-column accumulators would fill.  Same time model as gemm_tc_pick_bn.
+const char* gemm_tc_mixed_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool k_split, bool few_rows, int* bn_out) {
+    int bn = 128;
+    if (N <= 64) bn = 64;
+    else if (N <= 128 || (few_rows && M < 64)) bn = 128;
+    else {
+        const int64_t tiles_m = (M + BM - 1) / BM;
+        const int cand[2] = {192, 128};
+        const double penalty[2] = {1.0, 1.12};   // time per flop relative to the widest tile
+        double best_cost = 0;
+        for (int i = 0; i < 2; i++) {
+            const int64_t tiles = tiles_m * ((N + cand[i] - 1) / cand[i]);
+            const TailSplit t = plan_tail(tiles, K, cand[i], sm_count, k_split);
+            const double cost = (double(t.full / sm_count) * t.tile_us + t.tail_us) * penalty[i];
+            if (i == 0 || cost < best_cost * 0.97) {
+                bn = cand[i];
+                best_cost = cost;
+            }
+        }
+    }
+    if (bn_out) *bn_out = bn;
+    switch (bn) {
+        case 192: return "tcgen05-tf32x2+bf16-128x192";
+        case 128: return "tcgen05-tf32x2+bf16-128x128";
+        default: return "tcgen05-tf32x2+bf16-128x64";
+    }
+}
+
 int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows) {
     FXF_CHECK(gemm_tc_supported(a, allow_few_rows), "tensor-core GEMM called with an unsupported problem");
     int bn = 0;
-    gemm_tc_variant(a.M, a.N, a.K, ctx.sm_count, ctx.gemm_ws != nullptr, allow_few_rows, &bn);
+    if (a.w_mixed) {
+        gemm_tc_mixed_variant(a.M, a.N, a.K, ctx.sm_count, ctx.gemm_ws != nullptr, allow_few_rows, &bn);
+        switch (bn) {
+            case 192: return launch_tc<192, 16, 5, true, false, 2>(a, ctx);
+            case 128: return launch_tc<128, 16, 8, true, false, 2>(a, ctx);
+            default: return launch_tc<64, 16, 8, true, false, 2>(a, ctx);
+        }
+    }
+    gemm_tc_variant(a.M, a.N, a.K, ctx.sm_count, ctx.gemm_ws != nullptr, allow_few_rows, &bn, false);
     if (a.w_is_bf16) {  // bf16 mode: one product per logical product, A converted into tensor memory
         if (bn >= 192 && a.N > 128) return launch_tc<192, 32, 6, true, true>(a, ctx);
         return launch_tc<128, 32, 8, true, true>(a, ctx);
     }
-    if (ctx.tc_pair && a.M > BM && ctx.sm_count >= 2) {   // two CTAs per 256-row tile, each staging half of the weight tile
-        if (bn >= 224) return launch_tc<256, 16, 6, false, false, false, true>(a, ctx);
-        if (bn == 192) return launch_tc<192, 16, 4, true, false, false, true>(a, ctx);
-    }
+    // Wide tiles go to CTA pairs (256-row tiles, each CTA stages half of the weight tile: 40 % fewer bytes from L2 and six
+    // stages instead of four): measured +4 % on the GPT-2-small GEMMs, also against the 224-wide hybrid.  192-wide tiles lose
+    // with pairs (tensor memory leaves them four stages, too few for the cross-CTA latency).
+    if (ctx.tc_pair != 1 && a.M > BM && ctx.sm_count >= 2 && bn >= 224) return launch_tc<256, 16, 6, false, false, 0, true>(a, ctx);
     switch (bn) {
         case 256: return launch_tc<256, 16, 4, false>(a, ctx);
         case 224: return launch_tc<224, 16, 4, true, false, true>(a, ctx);
@@ -1100,7 +1216,7 @@ int launch_conv_tc(const ConvTcArgs& c, ExecCtx& ctx) {
     a.ldo = c.O;
     a.relu = c.relu;
     int bn = 0;
-    gemm_tc_variant(a.M, a.N, a.K, ctx.sm_count, ctx.gemm_ws != nullptr, false, &bn);
+    gemm_tc_variant(a.M, a.N, a.K, ctx.sm_count, ctx.gemm_ws != nullptr, false, &bn, false);
     if (c.w_is_bf16) {
         a.w_is_bf16 = true;
         FXF_CHECK(c.C % 32 == 0, "conv (tensor core, bf16): input channels must be a multiple of 32");
@@ -1159,6 +1275,28 @@ extern "C" __attribute__((visibility("default"))) int fxf_tc_prof_read(long long
     return cudaMemcpyFromSymbol(host_out, g_tc_prof, sizeof(long long) * 148 * 8) == cudaSuccess ? 0 : 1;
 }
 #endif
+
+namespace {
+__global__ void __launch_bounds__(256) split_mixed_kernel(const float* __restrict__ w, float* __restrict__ hi, uint16_t* __restrict__ lo_bf, int64_t n) {
+    int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float h, l;
+        split_tf32(w[i], h, l);   // h = tf32(w) rounded to nearest; the low part is taken exactly below
+        hi[i] = h;
+        lo_bf[i] = uint16_t(pack_bf16x2(w[i] - h, 0.f) & 0xffffu);
+        (void)l;
+    }
+}
+}  // namespace
+
+int launch_split_mixed(const float* w, float* hi, void* bf_pair, int64_t n, ExecCtx& ctx) {
+    if (n == 0) return 0;
+    int64_t blocks = (n + 255) / 256, cap = int64_t(ctx.sm_count) * 8;
+    tag_launch(ctx, "split_tf32_bf16", 0, 12.0 * double(n));
+    split_mixed_kernel<<<int(blocks < cap ? blocks : cap), 256, 0, ctx.stream>>>(w, hi, static_cast<uint16_t*>(bf_pair), n);
+    FXF_LAUNCHED(ctx);
+    return 0;
+}
 
 int launch_split_tf32(const float* w, float* hi, float* lo, int64_t n, ExecCtx& ctx) {
     if (n == 0) return 0;

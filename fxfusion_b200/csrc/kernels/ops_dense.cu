@@ -69,9 +69,10 @@ int launch_gemm(const GemmArgs& a, ExecCtx& ctx) {
     return launch_gemm_simt(a, ctx);
 }
 
-std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count) {
+std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count, bool pairs) {
     if (gemm_mode == FXF_GEMM_BF16 && gemm_tc_shape_ok(a.M, a.N, a.K) && a.K % 8 == 0) return std::string("tcgen05-bf16-128x") + (a.N > 128 ? "192" : "128");
-    if (gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(a.M, a.N, a.K)) return gemm_tc_variant(a.M, a.N, a.K, sm_count, true, false, nullptr);
+    if (gemm_mode == FXF_GEMM_TF32X2_BF16 && gemm_tc_shape_ok(a.M, a.N, a.K) && a.K % 8 == 0) return gemm_tc_mixed_variant(a.M, a.N, a.K, sm_count, true, false, nullptr);
+    if (gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(a.M, a.N, a.K)) return gemm_tc_variant(a.M, a.N, a.K, sm_count, true, false, nullptr, pairs);
     static const char* names[] = {"simt128x128", "simt64x64", "simt32x32", "skinny32x8"};
     return names[simt_tile_choice(a.M, a.N, sm_count)];
 }
@@ -89,6 +90,7 @@ struct Slice {
     bool whole = true;              // the slice is the entire tensor: no copy
     bool split = false;             // TF32 hi/lo copies wanted (tensor-core GEMM operand)
     bool bf16 = false;              // bf16 mode: one bf16 copy instead (hi points to it, lo stays NULL)
+    bool mixed = false;             // mixed mode: hi = TF32 high part (fp32), lo -> bf16(w - hi)
     bool drop = false;              // replaced by "no bias" (rank != 0 of a row-parallel product)
     size_t off_copy = 0, off_split = 0;  // byte offsets inside the plan's persistent memory
     const float *ptr = nullptr, *hi = nullptr, *lo = nullptr;  // resolved by prepare()
@@ -104,6 +106,7 @@ struct DensePlan : NodePlan {
     size_t cache_off = 0;   // CachedMHA: byte offset of the K/V cache inside the persistent memory
     bool prepared = false;
     bool bf16_mode = false;   // set by the plan builders from the engine's GEMM mode
+    bool mixed_mode = false;  // likewise: FXF_GEMM_TF32X2_BF16
 
     Slice& add(int input, int64_t rows, int64_t cols) {
         Slice& x = s[n++];
@@ -122,6 +125,7 @@ struct DensePlan : NodePlan {
         if (want_split) {
             x.split = true;
             x.bf16 = bf16_mode && x.ncol % 8 == 0;
+            x.mixed = mixed_mode && x.ncol % 8 == 0;   // bf16 rows must be 16-byte multiples for TMA; same bytes as a hi/lo pair
             x.off_split = persist_bytes;
             persist_bytes += round_up(x.bf16 ? size_t(x.elems()) * 2 : size_t(2) * size_t(x.elems()) * sizeof(float), 256);
         }
@@ -152,6 +156,10 @@ struct DensePlan : NodePlan {
                     if (launch_convert_bf16(x.ptr, h, x.elems(), ctx)) return 1;
                     x.hi = h;
                     x.lo = nullptr;
+                } else if (x.mixed) {
+                    if (launch_split_mixed(x.ptr, h, h + x.elems(), x.elems(), ctx)) return 1;
+                    x.hi = h;
+                    x.lo = h + x.elems();
                 } else {
                     if (launch_split_tf32(x.ptr, h, h + x.elems(), x.elems(), ctx)) return 1;
                     x.hi = h;
@@ -170,7 +178,7 @@ inline const DensePlan* dense(const NodePlan* p) { return static_cast<const Dens
 bool want_tc(const PlanEnv& env, int64_t M, int64_t N, int64_t K) { return env.gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(M, N, K); }
 
 void fill_gemm(GemmArgs& g, const float* x, const Slice& w, const Slice* bias, float* out, int64_t M, int64_t ldx, int64_t ldo, bool relu) {
-    g.x = x; g.w = w.ptr; g.w_hi = w.hi; g.w_lo = w.lo; g.w_is_bf16 = w.bf16;
+    g.x = x; g.w = w.ptr; g.w_hi = w.hi; g.w_lo = w.lo; g.w_is_bf16 = w.bf16; g.w_mixed = w.mixed;
     g.bias = (bias && !bias->drop) ? bias->ptr : nullptr;
     g.out = out; g.M = M; g.N = w.rows(); g.K = w.ncol;
     g.ldx = ldx; g.ldw = w.ncol; g.ldo = ldo; g.relu = relu;
@@ -224,6 +232,7 @@ int k_linear_relu(Registry& reg, const TensorIds& in, const TensorIds& out, cons
 std::unique_ptr<NodePlan> plan_linear(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const PlanEnv& env) {
     auto p = std::make_unique<DensePlan>();
     p->bf16_mode = env.gemm_mode == FXF_GEMM_BF16;
+    p->mixed_mode = env.gemm_mode == FXF_GEMM_TF32X2_BF16;
     if (in.size() < 3 || out.size() < 1) return p;
     const FxfTensor &x = reg[in[0]], &w = reg[in[1]];
     if (w.rank != 2 || x.rank < 1) return p;
@@ -246,7 +255,7 @@ std::unique_ptr<NodePlan> plan_linear(const Registry& reg, const TensorIds& in, 
     p->bytes = 4.0 * (double(M) * K + double(p->n_local) * K + double(p->n_local) + double(M) * p->n_local);
     GemmArgs g;
     g.M = M; g.N = p->n_local; g.K = K;
-    p->variant = gemm_variant_name(g, env.gemm_mode, 148);
+    p->variant = gemm_variant_name(g, env.gemm_mode, 148, env.tc_pairs);
     return p;
 }
 
@@ -294,6 +303,7 @@ int k_feedforward(Registry& reg, const TensorIds& in, const TensorIds& out, cons
 std::unique_ptr<NodePlan> plan_feedforward(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const PlanEnv& env) {
     auto p = std::make_unique<DensePlan>();
     p->bf16_mode = env.gemm_mode == FXF_GEMM_BF16;
+    p->mixed_mode = env.gemm_mode == FXF_GEMM_TF32X2_BF16;
     if (in.size() < 5 || out.size() < 1) return p;
     const FxfTensor &x = reg[in[0]], &w1 = reg[in[1]], &w2 = reg[in[3]];
     if (w1.rank != 2 || w2.rank != 2 || x.rank < 1) return p;
@@ -324,7 +334,7 @@ std::unique_ptr<NodePlan> plan_feedforward(const Registry& reg, const TensorIds&
     GemmArgs g1, g2;
     g1.M = M; g1.N = Fl; g1.K = K;
     g2.M = M; g2.N = P; g2.K = Fl;
-    p->variant += gemm_variant_name(g1, env.gemm_mode, 148) + "+" + gemm_variant_name(g2, env.gemm_mode, 148);
+    p->variant += gemm_variant_name(g1, env.gemm_mode, 148, env.tc_pairs) + "+" + gemm_variant_name(g2, env.gemm_mode, 148, env.tc_pairs);
     return p;
 }
 
@@ -387,6 +397,7 @@ int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params
 std::unique_ptr<NodePlan> plan_mha(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& env) {
     auto pl = std::make_unique<DensePlan>();
     pl->bf16_mode = env.gemm_mode == FXF_GEMM_BF16;
+    pl->mixed_mode = env.gemm_mode == FXF_GEMM_TF32X2_BF16;
     if (in.size() < 6 || out.size() < 1 || p.ints.size() < 4 || reg[in[0]].rank != 3) return pl;
     const FxfTensor& x = reg[in[0]];
     const int64_t B = x.shape[0], T = x.shape[1], H = p.ints[0], hd = p.ints[1], D = p.ints[2], QKV = p.ints[3], M = B * T;
@@ -427,7 +438,7 @@ std::unique_ptr<NodePlan> plan_mha(const Registry& reg, const TensorIds& in, con
     GemmArgs g1, g2;
     g1.M = M; g1.N = 3 * Dl; g1.K = D;
     g2.M = M; g2.N = D; g2.K = Dl;
-    pl->variant += gemm_variant_name(g1, env.gemm_mode, 148) + (tc_attn ? "+attn-tcgen05-tf32x3+" : "+flash-fp32+") + gemm_variant_name(g2, env.gemm_mode, 148);
+    pl->variant += gemm_variant_name(g1, env.gemm_mode, 148, env.tc_pairs) + (tc_attn ? "+attn-tcgen05-tf32x3+" : "+flash-fp32+") + gemm_variant_name(g2, env.gemm_mode, 148, env.tc_pairs);
     return pl;
 }
 
@@ -508,6 +519,7 @@ int k_cross_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const 
 std::unique_ptr<NodePlan> plan_cross_mha(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& env) {
     auto pl = std::make_unique<DensePlan>();
     pl->bf16_mode = env.gemm_mode == FXF_GEMM_BF16;
+    pl->mixed_mode = env.gemm_mode == FXF_GEMM_TF32X2_BF16;
     if (in.size() < 9 || out.size() < 1 || p.ints.size() < 4 || reg[in[0]].rank != 3 || reg[in[1]].rank != 3) return pl;
     const FxfTensor &x = reg[in[0]], &mem = reg[in[1]];
     const int64_t B = x.shape[0], Tq = x.shape[1], Tk = mem.shape[1], H = p.ints[0], hd = p.ints[1], D = p.ints[2], KV = p.ints[3];
@@ -558,8 +570,8 @@ std::unique_ptr<NodePlan> plan_cross_mha(const Registry& reg, const TensorIds& i
     g1.M = Mq; g1.N = Dl; g1.K = D;
     g2.M = Mk; g2.N = 2 * Dl; g2.K = D;
     g3.M = Mq; g3.N = D; g3.K = Dl;
-    pl->variant += gemm_variant_name(g1, env.gemm_mode, 148) + "+" + gemm_variant_name(g2, env.gemm_mode, 148) +
-                   (tc_attn ? "+attn-tcgen05-tf32x3+" : "+flash-fp32+") + gemm_variant_name(g3, env.gemm_mode, 148);
+    pl->variant += gemm_variant_name(g1, env.gemm_mode, 148, env.tc_pairs) + "+" + gemm_variant_name(g2, env.gemm_mode, 148, env.tc_pairs) +
+                   (tc_attn ? "+attn-tcgen05-tf32x3+" : "+flash-fp32+") + gemm_variant_name(g3, env.gemm_mode, 148, env.tc_pairs);
     return pl;
 }
 
@@ -710,6 +722,7 @@ int k_cached_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const
 std::unique_ptr<NodePlan> plan_cached_mha(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& env) {
     auto pl = std::make_unique<DensePlan>();
     pl->bf16_mode = env.gemm_mode == FXF_GEMM_BF16;
+    pl->mixed_mode = env.gemm_mode == FXF_GEMM_TF32X2_BF16;
     if (in.size() < 7 || out.size() < 1 || p.ints.size() < 5 || reg[in[0]].rank != 3 || reg[in[1]].rank != 2) return pl;
     const int64_t B = reg[in[0]].shape[0], T = reg[in[1]].shape[1], H = p.ints[0], hd = p.ints[1], D = p.ints[2], QKV = p.ints[3];
     if (H <= 0 || hd <= 0) return pl;
@@ -730,7 +743,7 @@ std::unique_ptr<NodePlan> plan_cached_mha(const Registry& reg, const TensorIds& 
     pl->bytes = 4.0 * (double(QKV) * D + double(D) * D + 2.0 * double(B) * T * D);
     GemmArgs g1;
     g1.M = B; g1.N = QKV; g1.K = D;
-    pl->variant = std::string(env.tp_size > 1 ? "replicated " : "") + gemm_variant_name(g1, env.gemm_mode, 148) + "+cached-attn-fp32";
+    pl->variant = std::string(env.tp_size > 1 ? "replicated " : "") + gemm_variant_name(g1, env.gemm_mode, 148, env.tc_pairs) + "+cached-attn-fp32";
     return pl;
 }
 

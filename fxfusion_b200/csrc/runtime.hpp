@@ -95,7 +95,7 @@ struct ExecCtx {
     int* gemm_flags = nullptr;
     int gemm_flag_count = 0;
     int tc_chunk_k = 0;            // K-elements per tensor-core accumulation chain (0 = the kernel's default)
-    int tc_pair = 0;               // 1: wide tensor-core GEMM tiles are computed by CTA pairs (tcgen05 cta_group::2)
+    int tc_pair = 0;               // 0: 256-wide tensor-core GEMM tiles are computed by CTA pairs (tcgen05 cta_group::2); 1: never
     // profiling: when `trace` is set every launch appends a record carrying the current tag
     std::vector<LaunchRecord>* trace = nullptr;
     int cur_node = -1;
@@ -139,6 +139,7 @@ struct PlanEnv {
     int gemm_mode = FXF_GEMM_AUTO;
     int tp_rank = 0, tp_size = 1;     // tensor-parallel position of this engine
     bool shard_output_cols = false;   // this node is the graph's final Linear and its columns are sharded over the ranks
+    bool tc_pairs = true;             // the engine lets CTA pairs compute the widest GEMM tiles (reported in variant names)
 };
 
 using KernelFn = int (*)(Registry&, const TensorIds&, const TensorIds&, const Params&, const NodePlan*, ExecCtx&);
@@ -258,6 +259,7 @@ struct GemmArgs {
     const float* w_hi = nullptr;
     const float* w_lo = nullptr;
     bool w_is_bf16 = false;   // bf16 mode: w_hi points to the weight as bf16 [N,K] (w_lo unused)
+    bool w_mixed = false;     // mixed mode: w_hi is the TF32 high part (fp32), w_lo points to bf16(w - w_hi) [N,K]
     const float* bias = nullptr;
     const float* residual = nullptr;   // optional [M,N] with the pitch of `out`, added after the bias and before the ReLU
     float* out = nullptr;
@@ -275,10 +277,13 @@ bool gemm_tc_shape_ok(int64_t M, int64_t N, int64_t K);
 // K > 0: the launch may cut the tiles of its last round along K (needs the context's GEMM workspace)
 int gemm_tc_pick_bn(int64_t M, int64_t N, int sm_count, int64_t K = 0);
 // Name of the tensor-core kernel variant launch_gemm_tc takes for a problem (and its tile width): the one dispatch rule.
-const char* gemm_tc_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool k_split, bool few_rows, int* bn_out);
+const char* gemm_tc_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool k_split, bool few_rows, int* bn_out, bool pairs = true);
+const char* gemm_tc_mixed_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool k_split, bool few_rows, int* bn_out);
 int launch_split_tf32(const float* w, float* hi, float* lo, int64_t n, ExecCtx& ctx);
+// mixed mode: hi = tf32(w) as fp32 [n], lo_bf16 = bf16(w - hi) [n]
+int launch_split_mixed(const float* w, float* hi, void* lo_bf16, int64_t n, ExecCtx& ctx);
 int simt_tile_choice(int64_t M, int64_t N, int sm_count);
-std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count);
+std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count, bool pairs = true);
 
 // Convolution (stride 1 or 2) as an implicit GEMM on the tensor cores: channels-last activation x [N,H,W,C], weights
 // repacked to [O, KH*KW*C] (tap-major, channel-minor) and split into TF32 hi/lo, channels-last output [N,HO,WO,O].

@@ -63,9 +63,14 @@ enum {
     FXF_GEMM_AUTO = 0,      /* tensor-core 3xTF32 where the shape allows it, else fp32 SIMT */
     FXF_GEMM_FP32_SIMT = 1, /* fp32 FFMA tiles only */
     FXF_GEMM_TF32X3 = 2,    /* tcgen05 kind::tf32 with hi/lo operand split (fp32-grade result) */
-    FXF_GEMM_BF16 = 3       /* optional reduced-precision mode: weights and activations rounded to bf16 for the tensor-core
+    FXF_GEMM_BF16 = 3,      /* optional reduced-precision mode: weights and activations rounded to bf16 for the tensor-core
                                products (one product per logical product), fp32 accumulation and fp32 tensors everywhere
                                else; results within about 1e-2 relative of the fp32 path, decode tokens may differ */
+    FXF_GEMM_TF32X2_BF16 = 4 /* fp32-grade like FXF_GEMM_TF32X3, with the split's third product computed as a bf16 tensor-core
+                               product (x = x_hi + x_lo, w = w_hi + w_lo: x_hi*w_hi and x_lo*w_hi in TF32, x_hi*w_lo in
+                               bf16): w_lo is 2^-11 of w, so its bf16 rounding costs about 2^-20 of a product, and it is
+                               stored and fetched in 2 bytes instead of 4 — a quarter less operand traffic, which is what
+                               bounds these kernels */
 };
 
 typedef struct FxfEngineOptions {
@@ -84,8 +89,9 @@ typedef struct FxfEngineOptions {
     int32_t tc_chunk_k;            /* K-elements per tensor-core accumulation chain before the partial sums are added in fp32
                                       by CUDA cores (0 = 1024 for dense layers, 64 for convolutions); larger = fewer
                                       drains, more truncation bias per chain (about 4e-8 of the result's scale per element) */
-    int32_t tc_pair;               /* 1: wide tensor-core GEMM tiles (192 / 256 columns) are computed by pairs of CTAs
-                                      (tcgen05 cta_group::2: 256-row tiles, each CTA stages half of the weight tile) */
+    int32_t tc_pair;               /* 0: the widest tensor-core GEMM tiles (256 columns) are computed by pairs of CTAs
+                                      (tcgen05 cta_group::2: 256-row tiles, each CTA stages half of the weight tile);
+                                      1: never */
     int32_t reserved[3];
 } FxfEngineOptions;
 

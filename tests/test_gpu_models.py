@@ -205,7 +205,7 @@ def test_c3_greedy_tokens_equal_reference_cpu_path(built_lib, c3):
     assert eng.device_status() == 0
 
 
-@pytest.mark.parametrize("M,N,K,arm", [(1024, 768, 768, "128x128-tmemA"), (4096, 768, 768, "128x192-tmemA"), (8192, 1536, 768, "128x256-smemA"),
+@pytest.mark.parametrize("M,N,K,arm", [(1024, 768, 768, "128x128-tmemA"), (4096, 768, 768, "128x192-tmemA"), (8192, 1536, 768, "256x256-pair-smemA"),
                                        (300, 700, 260, "128x128-tmemA")])
 def test_linear_add_graph_folds_the_residual_into_the_gemm_epilogue(built_lib, tmp_path, M, N, K, arm):
     """Linear -> Add: the engine folds the Add into the tensor-core GEMM's epilogue ((acc + bias) + residual, the order of

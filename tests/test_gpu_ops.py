@@ -46,14 +46,16 @@ def test_linear(built_lib, M, N, K, relu):
     both("LinearRelu" if relu else "Linear", [x, w, b, torch.zeros(M, N)], [0, 1, 2], [3], precision="fp32_simt")
 
 
-# Shapes chosen so that every arm of the tensor-core dispatch runs (asserted through fxf_gemm_variant): 256-wide tiles with A
-# in shared memory, the 224-wide hybrid, 192- / 128- / 64-wide tiles with A in tensor memory; K-split last rounds (tiles not
-# a multiple of 148 SMs, K >= 128), ragged M / N / K, an output pitch that is not a multiple of 4 (scalar epilogue), and
-# accumulation chains of one to 24 chunks.
+# Shapes chosen so that every arm of the default tensor-core dispatch runs (asserted through fxf_gemm_variant): 256-wide
+# tiles computed by CTA pairs (cta_group::2), 192- / 128- / 64-wide tiles with A in tensor memory; K-split last rounds (tiles
+# not a multiple of the worker count, K >= 128), ragged M / N / K, an output pitch that is not a multiple of 4 (scalar
+# epilogue, the 50257-column vocabulary among them), and accumulation chains of one to three chunks.  The single-CTA 256-wide
+# and 224-wide hybrid variants are reached with CTA pairs switched off (test_linear_variants_without_cta_pairs).
 TC_SHAPES = [
-    (8192, 3072, 768, "128x256-smemA"), (8192, 2304, 768, "128x256-smemA"), (8192, 768, 3072, "128x256-smemA"),
-    (2048, 12565, 768, "128x256-smemA"), (8192, 768, 768, "128x192-tmemA"), (4096, 576, 768, "128x192-tmemA"),
-    (5000, 1111, 500, "128x192-tmemA"), (8192, 8288, 768, "128x224-hybridA"), (2048, 50257, 768, "128x224-hybridA"),
+    (8192, 3072, 768, "256x256-pair-smemA"), (8192, 2304, 768, "256x256-pair-smemA"), (8192, 768, 3072, "256x256-pair-smemA"),
+    (2048, 12565, 768, "256x256-pair-smemA"), (8192, 768, 768, "128x192-tmemA"), (4096, 576, 768, "128x192-tmemA"),
+    (5000, 1111, 500, "128x192-tmemA"), (8192, 8288, 768, "256x256-pair-smemA"), (2048, 50257, 768, "256x256-pair-smemA"),
+    (3000, 3000, 516, "256x256-pair-smemA"), (1000, 4096, 520, "256x256-pair-smemA"),
     (1024, 768, 768, "128x128-tmemA"), (300, 700, 260, "128x128-tmemA"), (512, 1001, 256, "128x128-tmemA"),
     (128, 128, 64, "128x128-tmemA"), (1024, 64, 256, "128x64-tmemA"), (200, 64, 36, "128x64-tmemA"),
 ]
@@ -67,6 +69,56 @@ def test_linear_tensor_core(built_lib, M, N, K, arm, relu):
     assert gemm_variant(M, N, K) == "tcgen05-tf32x3-" + arm
     x, w, b = rnd(M, K), rnd(N, K, seed=1, scale=1 / math.sqrt(K)), rnd(N, seed=2)
     both("LinearRelu" if relu else "Linear", [x, w, b, torch.zeros(M, N)], [0, 1, 2], [3], precision="auto")
+
+
+def _linear_engine(M, N, K, tmp_path, relu=False, **options):
+    """One Linear node as an engine (engine options reach the dispatch; fxf_kernel_invoke always uses the defaults)."""
+    import numpy as np
+    from fxfusion_b200 import lowering
+    from fxfusion_b200.engine import ExecutionEngine
+    b = lowering.GraphBuilder(f"lin_{M}_{N}_{K}")
+    g = np.random.default_rng(M + N + K)
+    w = (g.standard_normal((N, K), dtype=np.float32) / math.sqrt(K)).astype(np.float32)
+    bias = g.standard_normal((N,), dtype=np.float32)
+    x = b.input((M, K), wire.DT_F32)
+    b.output(b.op("LinearRelu" if relu else "Linear", [x, b.const(w), b.const(bias)], (M, N)))
+    path = tmp_path / f"lin_{M}_{N}_{K}.bin"
+    wire.dump(b.finish(), path)
+    return ExecutionEngine(str(path), "cuda:0", **options), torch.from_numpy(w), torch.from_numpy(bias)
+
+
+@pytest.mark.parametrize("M,N,K,arm", [(8192, 3072, 768, "128x256-smemA"), (2048, 50257, 768, "128x224-hybridA"), (8192, 8288, 768, "128x224-hybridA"),
+                                       (3000, 3000, 516, "128x256-smemA")])
+def test_linear_variants_without_cta_pairs(built_lib, tmp_path, M, N, K, arm):
+    """Engine option tc_pair = 1: the widest tiles are computed by single CTAs (256-wide with A in shared memory, and the
+    224-wide hybrid the time model picks for very wide outputs) — the variants convolutions and pair-less engines use."""
+    eng, w, bias = _linear_engine(M, N, K, tmp_path, relu=True, tc_pair=1)
+    assert "tcgen05-tf32x3-" + arm in eng.describe()
+    x = rnd(M, K)
+    got = eng.run([x.cuda()])[0].cpu()
+    want = torch.zeros(M, N)
+    KERNELS[wire.OP["LinearRelu"]]([x, w, bias, want], [0, 1, 2], [3], [], [])
+    ok, info = compare_outputs(got, want, atol=ATOL, rtol=RTOL)
+    assert ok, info
+    assert eng.device_status() == 0
+    eng.close()
+
+
+@pytest.mark.parametrize("M,N,K,arm", [(8192, 3072, 768, "128x192"), (1024, 768, 768, "128x128"), (300, 700, 264, "128x128"), (1024, 64, 256, "128x64"),
+                                       (2048, 50257, 768, "128x192"), (512, 200, 4096, "128x128")])
+def test_linear_mixed_tf32_bf16_mode(built_lib, tmp_path, M, N, K, arm):
+    """Optional mode fp32_tf32x2_bf16: x_hi*w_hi and x_lo*w_hi as TF32 products, x_hi*w_lo as one bf16 product (w_lo kept in
+    bf16).  It is held to the same 1e-4 / 1e-3 rule as the 3xTF32 mode."""
+    eng, w, bias = _linear_engine(M, N, K, tmp_path, precision="fp32_tf32x2_bf16")
+    assert "tcgen05-tf32x2+bf16-" + arm in eng.describe()
+    x = rnd(M, K)
+    got = eng.run([x.cuda()])[0].cpu()
+    want = torch.zeros(M, N)
+    KERNELS[wire.OP["Linear"]]([x, w, bias, want], [0, 1, 2], [3], [], [])
+    ok, info = compare_outputs(got, want, atol=ATOL, rtol=RTOL)
+    assert ok, info
+    assert eng.device_status() == 0
+    eng.close()
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 256, 16384), (384, 192, 6144), (1000, 300, 3072)])
