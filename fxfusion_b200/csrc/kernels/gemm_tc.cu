@@ -198,9 +198,6 @@ __device__ __forceinline__ int64_t out_row_offset(const TcParams& p, int tm, int
     return ((int64_t(n) * c.HO + oy) * c.WO + ox) * p.ldo;
 }
 
-#ifdef FXF_TC_PROFILE
-__device__ long long g_tc_prof[148 * 8];
-#endif
 // 32 consecutive TMEM columns of this thread's lane (tcgen05.ld 32x32b.x32) or 16 (x16)
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
@@ -353,48 +350,29 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             // ---------------- MMA issuer ----------------
             if (lane == 0 && rank == 0) {   // in a pair only the leader issues MMAs (for both CTAs)
                 uint32_t it = 0, ccount = 0;   // K-slabs and accumulation chunks issued so far by this CTA
-#ifdef FXF_TC_PROFILE
-                long long t_tma = 0, t_split = 0, t_acc = 0, t_begin = clock64(), tq;
-#endif
                 for (int unit = sched_id; unit < num_units; unit += sched_n) {
                     const Unit un = get_unit(p, unit, num_k);
                     for (int kc0 = un.k0; kc0 < un.k1; kc0 += chunk, ccount++) {
                         const int kc1 = min(kc0 + chunk, un.k1);
                         const uint32_t buf = ccount % ACC;
-#ifdef FXF_TC_PROFILE
-                        tq = clock64();
-#endif
                         if (ccount >= uint32_t(ACC) &&
                             !(PAIR ? mbar_wait_cluster(&s.acc_empty[buf], ((ccount / ACC) - 1) & 1, abort_flag) : mbar_wait(&s.acc_empty[buf], ((ccount / ACC) - 1) & 1, abort_flag))) {
                             give_up(abort_flag, p.status, kErrWaitAccEmpty);
                             goto mma_done;
                         }
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#ifdef FXF_TC_PROFILE
-                        t_acc += clock64() - tq;
-#endif
                         const uint32_t tmem_acc = tmem_base + buf * uint32_t(BN);
                         for (int k = kc0; k < kc1; k++, it++) {
                             int st = it % STAGES;
                             uint32_t par = (it / STAGES) & 1;
-#ifdef FXF_TC_PROFILE
-                            tq = clock64();
-#endif
                             if (!mbar_wait(PAIR ? &s.full_b[st] : &s.full_tma[st], par, abort_flag)) {
                                 give_up(abort_flag, p.status, kErrWaitTma);
                                 goto mma_done;
                             }
-#ifdef FXF_TC_PROFILE
-                            t_tma += clock64() - tq;
-                            tq = clock64();
-#endif
                             if (!(PAIR ? mbar_wait_cluster(&s.full_split[st], par, abort_flag) : mbar_wait(&s.full_split[st], par, abort_flag))) {
                                 give_up(abort_flag, p.status, kErrWaitSplit);
                                 goto mma_done;
                             }
-#ifdef FXF_TC_PROFILE
-                            t_split += clock64() - tq;
-#endif
                             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                             if (PAIR) {
                                 // 256 x BN over the pair: A (hi / lo) at the same shared- or tensor-memory offsets in both CTAs, the
@@ -493,12 +471,6 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     }
                 }
             mma_done:;
-#ifdef FXF_TC_PROFILE
-                if (blockIdx.x < 148) {   // the MMA thread's cycles: total, waiting for tiles, for the split, for an accumulator; slabs issued
-                    long long* prof = g_tc_prof + blockIdx.x * 8;
-                    prof[0] = clock64() - t_begin; prof[1] = t_tma; prof[2] = t_split; prof[3] = t_acc; prof[4] = it;
-                }
-#endif
             }
         }
     } else if (warp >= kSplitWarp0) {
@@ -511,27 +483,14 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             const uint32_t lane_base = uint32_t(quarter * 32) << 16;
             // TMA swizzle: the 16-byte chunks of a row are permuted by the row index (64-byte rows: bits 1-2, 128-byte rows: bits 0-2)
             const int sw = BK == 16 ? ((row >> 1) & 3) : (row & 7);
-#ifdef FXF_TC_PROFILE
-            long long sp_wait = 0, sp_begin = clock64(), sq;
-#endif
             for (int unit = sched_id; unit < num_units; unit += sched_n) {
                 const Unit un = get_unit(p, unit, num_k);
                 for (int k = un.k0; k < un.k1; k++, it++) {
                     int st = it % STAGES;
-#ifdef FXF_TC_PROFILE
-                    sq = clock64();
-#endif
                     if (!mbar_wait(&s.full_tma[st], (it / STAGES) & 1, abort_flag)) {
                         give_up(abort_flag, p.status, kErrWaitTma);
                         goto split_done;
                     }
-#ifdef FXF_TC_PROFILE
-                    sp_wait += clock64() - sq;
-                    if (k + 1 == un.k1 && unit + sched_n >= num_units && warp == kSplitWarp0 && lane == 0 && blockIdx.x < 148) {
-                        g_tc_prof[blockIdx.x * 8 + 5] = clock64() - sp_begin;   // split warp 0: total cycles, cycles waiting for tiles
-                        g_tc_prof[blockIdx.x * 8 + 6] = sp_wait;
-                    }
-#endif
                     const float4* src = reinterpret_cast<const float4*>(s.a[st]) + row * (BK / 4);
                     if (BF16) {
                         // bf16 mode: the row's BK floats become BK/2 packed words (element k in the low half of word k/2)
@@ -1270,11 +1229,6 @@ int launch_conv_weight_bf16(const float* w_oihw, void* out, int O, int C, int KH
     return 0;
 }
 
-#ifdef FXF_TC_PROFILE
-extern "C" __attribute__((visibility("default"))) int fxf_tc_prof_read(long long* host_out) {
-    return cudaMemcpyFromSymbol(host_out, g_tc_prof, sizeof(long long) * 148 * 8) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 namespace {
 __global__ void __launch_bounds__(256) split_mixed_kernel(const float* __restrict__ w, float* __restrict__ hi, uint16_t* __restrict__ lo_bf, int64_t n) {
