@@ -283,7 +283,9 @@ def kernel_table(trace, precision: str, peaks, tf32_peak):
                    "gbs": round(v["bytes"] / (v["ms"] * 1e-3) / 1e9, 1) if v["ms"] > 0 else None} for k, v in sorted(by.items(), key=lambda kv: -kv[1]["ms"])}
     # per-kernel fraction of its own roofline: tensor-core kernels against the ceiling of their arithmetic (three TF32
     # products per fp32 product = measured TF32 rate / 3; the measured bf16 peak in bf16 mode), exchange kernels against
-    # the NVLink rate (bytes that cross the link, both directions), every other kernel against the measured copy bandwidth
+    # the NVLink rate per direction (the kernel reports the bytes that ARRIVE at a rank during the exchange: the peers' partial
+    # rows it fetches plus the normalised rows the peers store into it, 2 * (n-1)/n of the activation; as many leave it),
+    # every other kernel against the measured copy bandwidth
     if precision == "bf16":
         tensor_ceiling = peaks["bf16_tflops_sustained"]
     elif tf32_peak:
@@ -294,7 +296,7 @@ def kernel_table(trace, precision: str, peaks, tf32_peak):
         if "tcgen05" in k and v["tflops"] is not None:
             v["bound"], v["frac"] = "tensor", round(v["tflops"] / tensor_ceiling, 4)
         elif k in ("tp_exchange_add_layernorm", "p2p_all_reduce") and v["gbs"] is not None:
-            v["bound"], v["frac"] = "nvlink", round(v["gbs"] / (2 * NVLINK_GBS_PER_DIRECTION), 4)
+            v["bound"], v["frac"] = "nvlink", round(v["gbs"] / NVLINK_GBS_PER_DIRECTION, 4)
         elif v["gbs"] is not None:
             v["bound"], v["frac"] = "hbm", round(v["gbs"] / peaks["hbm_gbs"], 4)
     return by, kernels, total_ms, tensor_ceiling
@@ -542,7 +544,7 @@ def report_c3(args, world, local, tp_size, dp_size, K, W, Ke, ms, e2e_ms, e2e_ma
                 "note": "achieved = logical fp32 flops (2MNK, counted once) of all launches of this kernel in one forward / their summed device time"}
     # ---- CPU baseline on a bounded sample; its tokens are compared with the device loop's -----------------
     cpu = None
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:   # the CPU baseline is a single-GPU figure (rank 0, N = 1)
         cb = pick_cpu_batch(2, 1)
         tps, s_per_step, kind, cores, cpu_buf = cpu_decode_steps(cb, 2, 1)
         n_steps = 3 if K >= 3 else 0   # one warm-up step + two timed steps, all starting at the prompt like the device loop

@@ -21,7 +21,7 @@ class FxfEngineOptions(C.Structure):
     _fields_ = [("struct_size", C.c_int32), ("use_cuda_graph", C.c_int32), ("gemm_mode", C.c_int32),
                 ("tp_rank", C.c_int32), ("tp_size", C.c_int32), ("tp_shard_output", C.c_int32),
                 ("no_epilogue_fusion", C.c_int32), ("no_tp_fused_exchange", C.c_int32), ("p2p_start_budget_ms", C.c_int32),
-                ("p2p_end_budget_ms", C.c_int32), ("p2p_grid", C.c_int32), ("tc_chunk_k", C.c_int32), ("tc_pair", C.c_int32), ("reserved", C.c_int32 * 3)]
+                ("p2p_end_budget_ms", C.c_int32), ("p2p_grid", C.c_int32), ("tc_chunk_k", C.c_int32), ("tc_pair", C.c_int32), ("tp_push", C.c_int32), ("reserved", C.c_int32 * 2)]
 
 
 class FxfLaunchInfo(C.Structure):
@@ -49,6 +49,9 @@ SIGNATURES = {
     "fxf_gemm_variant": (C.c_int, [C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_char_p, C.c_size_t]),
     "fxf_tp_exchange_emulated": (C.c_int, [C.c_int] + [C.POINTER(C.c_void_p)] * 4 + [C.c_void_p, C.c_void_p, C.c_float, C.c_int64, C.c_int64, C.c_int,
                                             C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
+    "fxf_linear_pushed_scratch_bytes": (C.c_int64, [C.c_int64, C.c_int64]),
+    "fxf_linear_pushed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int64,
+                                    C.c_void_p, C.c_int64, C.c_void_p]),
     "fxf_engine_argmax_scatter": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "fxf_engine_create_from_memory": (C.c_int, [C.c_void_p, C.c_size_t, C.c_int, C.POINTER(FxfEngineOptions), C.POINTER(C.c_void_p)]),
     "fxf_engine_destroy": (None, [C.c_void_p]),

@@ -93,6 +93,7 @@ struct fxf_engine {
     size_t total_bytes = 0, arena_bytes = 0, const_bytes = 0, input_bytes = 0, persist_bytes = 0, scratch_bytes = 0;
     size_t scratch_off = 0, status_off = 0;
     size_t gemm_ws_off = 0, gemm_ws_bytes = 0, gemm_flags_off = 0, gemm_flags_bytes = 0;
+    size_t push_off = 0, push_bytes = 0;   // exchange window of the row-parallel products (tensor parallelism)
     ExecCtx ctx;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
@@ -375,6 +376,14 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
         // placed before everything whose size may differ between ranks, so that its offset is the same everywhere
         e->p2p_off = cursor;
         cursor += kP2pRegion;
+        // exchange window of the row-parallel products (their largest output): same size and offset on every rank
+        if (e->opts.tp_push) {
+            for (auto& n : e->nodes)
+                if (n.plan && n.plan->tp_sharded && (n.op == FXF_OP_MHA || n.op == FXF_OP_CROSS_MHA || n.op == FXF_OP_FEEDFORWARD) && !n.out.empty())
+                    e->push_bytes = std::max(e->push_bytes, round_up(size_t(e->reg[n.out[0]].nbytes), kAlign));
+            e->push_off = cursor;
+            cursor += e->push_bytes;
+        }
     }
     size_t persist_off = cursor;
     cursor += e->persist_bytes;
@@ -450,6 +459,8 @@ int build(fxf_engine* e, const uint8_t* bytes, size_t nbytes) {
                 e->peers.shared_bytes = e->arena_bytes;
                 e->peers.flags_off = e->p2p_off;
                 e->peers.epoch_off = e->p2p_off + 4096;
+                e->peers.push_off = e->push_off;
+                e->peers.push_bytes = e->push_bytes;
                 e->peers.grid = 128;  // 8 ranks x 128 blocks x 4 bytes = 4 KB of flags
                 if (e->opts.p2p_grid >= 1 && e->opts.p2p_grid <= 128) e->peers.grid = e->opts.p2p_grid;
                 e->peers_mapped = true;
@@ -880,7 +891,9 @@ int fxf_engine_describe(const fxf_engine* e, char* out, size_t out_bytes) {
     std::ostringstream os;
     os << "graph '" << e->name << "' device " << e->device << " nodes " << e->nodes.size() << " tensors " << e->reg.size() << "\n";
     os << "device allocation " << e->total_bytes << " B = arena " << e->arena_bytes << " + constants " << e->const_bytes << " + input slots " << e->input_bytes
-       << " + persistent " << e->persist_bytes << " + scratch " << e->scratch_bytes << " + status 256\n";
+       << " + persistent " << e->persist_bytes << " + scratch " << e->scratch_bytes << " + status 256";
+    if (e->push_bytes) os << " + exchange window " << e->push_bytes;
+    os << "\n";
     os << "cuda_graph " << (e->graph_exec ? "yes" : "no") << " launches/run " << e->launches_per_run << "\n";
     for (size_t i = 0; i < e->nodes.size(); i++) {
         const Node& n = e->nodes[i];
@@ -1065,11 +1078,47 @@ int fxf_gemm_variant(int64_t M, int64_t N, int64_t K, int gemm_mode, int sm_coun
 }
 
 int fxf_tp_exchange_emulated(int n_ranks, const float* const* partial, const float* const* residual, float* const* x_out, float* const* y_out,
-                             const float* gamma, const float* beta, float eps, int64_t M, int64_t D, int replicate_x, void* sync_mem, int64_t sync_bytes,
+                             const float* gamma, const float* beta, float eps, int64_t M, int64_t D, int layout, void* sync_mem, int64_t sync_bytes,
                              int budget_ms, int skip_rank, void* stream) {
     FXF_CHECK(n_ranks >= 2 && sync_mem != nullptr && sync_bytes >= int64_t(n_ranks) * 8192, "fxf_tp_exchange_emulated: sync_mem must hold n_ranks * 8192 zeroed bytes");
-    return tp_exchange_emulated(n_ranks, partial, residual, x_out, y_out, gamma, beta, eps, M, D, replicate_x, sync_mem, budget_ms, skip_rank,
+    return tp_exchange_emulated(n_ranks, partial, residual, x_out, y_out, gamma, beta, eps, M, D, layout, sync_mem, budget_ms, skip_rank,
                                 static_cast<cudaStream_t>(stream));
+}
+
+// The row-pushed product of the tensor-parallel layout outside an engine (one GPU can play every producer in turn).
+int64_t fxf_linear_pushed_scratch_bytes(int64_t N, int64_t K) {
+    if (N <= 0 || K <= 0) return -1;
+    return int64_t(2 * round_up(size_t(N) * size_t(K) * sizeof(float), 256) + kCallWsSms * kCallWsTile + kCallFlagBytes);
+}
+
+int fxf_linear_pushed(const float* x, const float* w, const float* bias, float* const* windows, int n_ranks, int rank, int64_t M, int64_t N, int64_t K,
+                      void* scratch, int64_t scratch_bytes, void* stream) {
+    FXF_CHECK(x && w && windows && scratch, "fxf_linear_pushed: NULL argument");
+    FXF_CHECK(n_ranks >= 1 && n_ranks <= kMaxTpRanks && rank >= 0 && rank < n_ranks, "fxf_linear_pushed: 1..%d ranks", kMaxTpRanks);
+    FXF_CHECK(M > 0 && M % n_ranks == 0 && (M / n_ranks) % 128 == 0, "fxf_linear_pushed: every rank must own a whole number of 128-row tiles");
+    FXF_CHECK(scratch_bytes >= fxf_linear_pushed_scratch_bytes(N, K) && (reinterpret_cast<uintptr_t>(scratch) & 255) == 0,
+              "fxf_linear_pushed: scratch too small or not 256-byte aligned");
+    ExecCtx ctx;
+    ctx.stream = static_cast<cudaStream_t>(stream);
+    int dev = 0, sms = 0;
+    FXF_CUDA(cudaGetDevice(&dev));
+    FXF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    ctx.sm_count = sms;
+    const size_t wb = round_up(size_t(N) * size_t(K) * sizeof(float), 256);
+    char* s = static_cast<char*>(scratch);
+    float *hi = reinterpret_cast<float*>(s), *lo = reinterpret_cast<float*>(s + wb);
+    ctx.gemm_ws = reinterpret_cast<float*>(s + 2 * wb);
+    ctx.gemm_ws_bytes = kCallWsSms * kCallWsTile;
+    ctx.gemm_flags = reinterpret_cast<int*>(s + 2 * wb + kCallWsSms * kCallWsTile);
+    ctx.gemm_flag_count = int(kCallFlagBytes / sizeof(int));
+    FXF_CUDA(cudaMemsetAsync(ctx.gemm_flags, 0, kCallFlagBytes, ctx.stream));
+    if (launch_split_tf32(w, hi, lo, N * K, ctx)) return 1;
+    GemmArgs a;
+    a.x = x; a.w = w; a.w_hi = hi; a.w_lo = lo; a.bias = bias; a.out = windows[rank];
+    a.M = M; a.N = N; a.K = K; a.ldx = K; a.ldw = K; a.ldo = N;
+    a.push_out = windows; a.push_rows = M / n_ranks; a.push_rank = rank;
+    FXF_CHECK(gemm_tc_supported(a), "fxf_linear_pushed: the shape M=%lld N=%lld K=%lld is not served by the tensor-core kernels", (long long)M, (long long)N, (long long)K);
+    return launch_gemm_tc(a, ctx);
 }
 
 // ---- greedy static decode ---------------------------------------------------------------------

@@ -141,6 +141,14 @@ struct TcParams {
     float* ws;
     int* flags;
     int* status;
+    // Row-pushed output (tensor parallelism, row-parallel product): push_rows > 0 sends the rows [q*push_rows, (q+1)*push_rows)
+    // of the result to push_out[q] (rank q's exchange window, possibly peer memory), at row push_rank*push_rows + (row -
+    // q*push_rows) of it: after all ranks' launches rank q holds every rank's partial sums of the rows it owns, rank-major.
+    // push_rows is a multiple of the 128 rows a CTA stores, so a tile has one destination.
+    float* push_out[kMaxTpRanks];
+    int64_t push_rows;
+    int push_rank;
+    int push_owners;   // > 1: row tiles are walked owner-interleaved (tiles_m is a multiple of it)
 };
 
 // x - (x with its 13 low mantissa bits cleared): the part of x a TF32 MMA does not see.  The difference is exact in fp32 and
@@ -174,6 +182,9 @@ __device__ __forceinline__ void tile_coords(const TcParams& p, int tile, int& tm
         tn = tile % p.tiles_n;
         tm = tile / p.tiles_n;
     }
+    // Row-pushed output: consecutive row tiles go to different owners, so that the stores that cross NVLink are spread over
+    // the whole launch instead of arriving in one burst (owner-major order would send a rank's remote rows last).
+    if (p.push_owners > 1) tm = (tm % p.push_owners) * (p.tiles_m / p.push_owners) + tm / p.push_owners;
 }
 
 // origin (ox0, oy0, n0) of the pixel box of M-tile `tm`
@@ -671,10 +682,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             float* orow[4];
             const float* rrow[4];
             bool oks[4];
+            float* out_base = p.out;
+            if (p.push_rows > 0) {
+                const int64_t owner = (int64_t(tm) * BM) / p.push_rows;
+                out_base = p.push_out[owner] + (int64_t(p.push_rank) - owner) * p.push_rows * p.ldo;
+            }
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int64_t off = out_row_offset(p, tm, row0 + i * 8 + rsub, oks[i]) + col_base + cq;
-                orow[i] = p.out + off;
+                orow[i] = out_base + off;
                 rrow[i] = p.residual + off;   // only dereferenced when p.residual is set
             }
             const float* brow = p.bias + col_base + cq;              // only dereferenced when p.bias is set
@@ -738,7 +754,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     if (!p.cv.enabled && !adds_partials && p.residual == nullptr) {
                         // dense rows without extras: affine addresses, independent iterations (the stores of consecutive rows pipeline)
                         const int64_t grow = int64_t(tm) * BM + row0 + r2;
-                        float* op = p.out + grow * p.ldo + col + cl;
+                        float* op = out_base + grow * p.ldo + col + cl;
                         const int64_t step = 2 * p.ldo;
 #pragma unroll 8
                         for (int i = 0; i < 16; i++) {
@@ -759,7 +775,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                             const int64_t off = out_row_offset(p, tm, row0 + rr, row_ok);
                             if (p.residual && col_ok && row_ok) v += p.residual[off + col + cl];
                             if (p.relu) v = relu_keep_nan(v);
-                            if (col_ok && row_ok) p.out[off + col + cl] = v;
+                            if (col_ok && row_ok) out_base[off + col + cl] = v;
                         }
                     }
                 }
@@ -924,7 +940,21 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
     p.bias = a.bias; p.residual = cv ? cv->residual : a.residual; p.out = a.out; p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo;
     p.relu = a.relu ? 1 : 0;
     p.vec_out = (a.ldo % 4 == 0 && aligned16(a.out) && (a.bias == nullptr || aligned16(a.bias)) && (p.residual == nullptr || aligned16(p.residual))) ? 1 : 0;
+    if (a.push_rows > 0) {
+        const int64_t owners = a.M / a.push_rows;
+        FXF_CHECK(!cv && a.residual == nullptr && a.push_out != nullptr && a.push_rows % BM == 0 && a.M % a.push_rows == 0 && owners >= 1 &&
+                      owners <= kMaxTpRanks && a.push_rank >= 0 && a.push_rank < owners,
+                  "gemm: a row-pushed output needs whole 128-row tiles per owner, no residual and at most %d owners", kMaxTpRanks);
+        for (int64_t r = 0; r < owners; r++) {
+            FXF_CHECK(a.push_out[r] != nullptr, "gemm: row-pushed output with a NULL window");
+            p.push_out[r] = a.push_out[r];
+            if (!aligned16(a.push_out[r])) p.vec_out = 0;
+        }
+        p.push_rows = a.push_rows;
+        p.push_rank = a.push_rank;
+    }
     p.tiles_m = int((a.M + TM - 1) / TM);
+    if (a.push_rows > 0 && a.push_rows % TM == 0) p.push_owners = int(a.M / a.push_rows);
     p.tiles_n = int((a.N + BN - 1) / BN);
     // walk tiles so that the operand that does not fit in L2 is the one reused by concurrent CTAs
     p.m_fastest = a.N > a.M ? 1 : 0;

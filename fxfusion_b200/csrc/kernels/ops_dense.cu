@@ -55,6 +55,7 @@ int launch_residual_epilogue(float* out, const float* residual, int64_t n, bool 
 int launch_gemm(const GemmArgs& a, ExecCtx& ctx) {
     if (a.M == 0 || a.N == 0) return 0;
     if (use_tc(a, ctx.gemm_mode)) return launch_gemm_tc(a, ctx);
+    FXF_CHECK(a.push_rows == 0, "gemm: a row-pushed output needs the tensor-core kernels");
     if (a.residual != nullptr) {
         // the FFMA kernels have no residual epilogue: plain GEMM, then act(out + residual) in place (dense rows only)
         FXF_CHECK(a.ldo == a.N, "gemm: a fused residual needs a dense output on the fp32 FFMA path");
@@ -266,9 +267,19 @@ std::unique_ptr<NodePlan> plan_linear(const Registry& reg, const TensorIds& in, 
 static int finish_row_parallel(GemmArgs& g2, int64_t M, int64_t N, bool sharded, ExecCtx& ctx) {
     if (sharded && ctx.tp_size > 1 && ctx.xchg.enabled) {
         FXF_CHECK(g2.ldo == N && tp_exchange_usable(ctx.xchg, g2.out, M, N, ctx), "tensor-parallel exchange: the folded nodes cannot be served");
+        // On the tensor-core kernels the product stores each row straight into its owner's exchange window (peer stores from
+        // the epilogue, behind the product's own time): the exchange then reads local memory only.
+        float* windows[kMaxTpRanks] = {};
+        const bool pushed = g2.residual == nullptr && use_tc(g2, ctx.gemm_mode) && tp_push_usable(M, N, ctx);
+        if (pushed) {
+            for (int r = 0; r < ctx.tp_size; r++) windows[r] = tp_push_window(r, ctx);
+            g2.push_out = windows;
+            g2.push_rows = M / ctx.tp_size;
+            g2.push_rank = ctx.tp_rank;
+        }
         if (launch_gemm(g2, ctx)) return 1;
         ctx.xchg.consumed = true;
-        return launch_tp_exchange(ctx.xchg, g2.out, M, N, ctx);
+        return launch_tp_exchange(ctx.xchg, g2.out, M, N, ctx, pushed);
     }
     apply_fusion(ctx, g2, sharded);
     if (launch_gemm(g2, ctx)) return 1;

@@ -14,8 +14,15 @@
 //       new residual row (to its own memory only — the residual stream stays row-sharded between exchanges — unless
 //       someone outside this scheme reads it), normalises the row in registers and stores the normalised row into
 //       EVERY rank's LayerNorm output (plain peer stores) -> end barrier.
-//       NVLink traffic per rank is that of an all-reduce ((n-1)/n of the buffer in and out); the separate residual Add,
-//       the LayerNorm launch and their HBM round trips disappear, and each rank normalises only M/n rows.
+//       NVLink traffic per rank is that of an all-reduce: (n-1)/n of the buffer arrives as fetched partial rows and
+//       another (n-1)/n as the normalised rows the peers store, and as much leaves.  The separate residual Add, the
+//       LayerNorm launch and their HBM round trips disappear, and each rank normalises only M/n rows.
+//       Pushed variant: the row-parallel product that precedes the exchange has already stored its partial sums of the
+//       rows rank q owns into rank q's exchange window (GemmArgs::push_out: peer stores from the GEMM epilogue, hidden
+//       behind the product), at row p*R + (row - q*R) for producer p.  The kernel then finds all n partial rows in its own
+//       memory, and only the normalised rows cross NVLink inside the exchange.  The window is a buffer of its own: a
+//       producer writes it only after it has left the end barrier of the previous exchange, i.e. after every rank has
+//       finished reading it.
 //
 // Only plain ld / st to peer memory: no multimem, no TMA.  Barriers: block b of rank r tells block b of every peer and
 // waits for theirs; flag values are a per-engine epoch that only grows (kept in device memory so that a captured CUDA
@@ -60,7 +67,8 @@ struct XchgParams {
     P2pSync sync;
     int rank;                             // < 0: single-GPU emulation, rank = blockIdx.y
     int skip_rank;                        // emulation only: this rank never arrives (exercises the bounded waits); -1 = none
-    const float* part[kMaxTpRanks];       // every rank's partial sums [M, D]
+    const float* part[kMaxTpRanks];       // every rank's partial sums [M, D]; pushed: every rank's exchange window
+    int pushed;                           // the products stored their rows into the owners' windows (see below)
     float* y[kMaxTpRanks];                // LayerNorm output of every rank (y[0] == NULL: no LayerNorm)
     float* x[kMaxTpRanks];                // new residual stream; NULL entries are not written
     const float* residual[kMaxTpRanks];   // residual[r] is read by rank r only; NULL = none
@@ -200,6 +208,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 __device__ __forceinline__ void add4(float4& a, const float4& b) { a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
 
+
 // NV = float4 per lane per row (rows of up to 128 * NV floats).
 template <int NV>
 __global__ void __launch_bounds__(kXchgThreads, 1) tp_exchange_ln_kernel(XchgParams p) {
@@ -235,7 +244,8 @@ __global__ void __launch_bounds__(kXchgThreads, 1) tp_exchange_ln_kernel(XchgPar
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
                         if (g0 + q < n) {
-                            const float4* src = reinterpret_cast<const float4*>(p.part[g0 + q]) + off;
+                            const float4* src = p.pushed ? reinterpret_cast<const float4*>(p.part[rank]) + (int64_t(g0 + q) * p.rows_per_rank + (row - r0)) * n4
+                                                         : reinterpret_cast<const float4*>(p.part[g0 + q]) + off;
 #pragma unroll
                             for (int i = 0; i < NV; i++) {
                                 const int c = lane + 32 * i;
@@ -380,15 +390,24 @@ bool tp_exchange_usable(const TpExchange& x, const float* partial, int64_t M, in
     if (ctx.peers == nullptr || ctx.tp_size < 2 || ctx.tp_size > kMaxTpRanks) return false;
     if (D % 4 != 0 || D > 1024 || M <= 0) return false;
     const int64_t bytes = M * D * 4;
-    if (!aligned16(partial) || !in_shared_region(partial, bytes, ctx)) return false;
+    if (partial != nullptr && (!aligned16(partial) || !in_shared_region(partial, bytes, ctx))) return false;   // NULL: pushed rows
     if (x.y_out && (!aligned16(x.y_out) || !in_shared_region(x.y_out, bytes, ctx) || !aligned16(x.gamma) || !aligned16(x.beta))) return false;
     if (x.x_out && (!aligned16(x.x_out) || !in_shared_region(x.x_out, bytes, ctx))) return false;
     if (x.residual && !aligned16(x.residual)) return false;
     return x.y_out != nullptr || x.x_out != nullptr;
 }
 
-int launch_tp_exchange(const TpExchange& x, const float* partial, int64_t M, int64_t D, ExecCtx& ctx) {
-    FXF_CHECK(tp_exchange_usable(x, partial, M, D, ctx), "tensor-parallel exchange called with operands it cannot serve");
+bool tp_push_usable(int64_t M, int64_t D, const ExecCtx& ctx) {
+    const PeerMap* pm = ctx.peers;
+    if (pm == nullptr || ctx.tp_size < 2 || pm->push_bytes == 0 || M <= 0 || M % ctx.tp_size != 0) return false;
+    return (M / ctx.tp_size) % 128 == 0 && size_t(M) * size_t(D) * 4 <= pm->push_bytes;
+}
+
+float* tp_push_window(int rank, const ExecCtx& ctx) { return reinterpret_cast<float*>(ctx.peers->base[rank] + ctx.peers->push_off); }
+
+int launch_tp_exchange(const TpExchange& x, const float* partial, int64_t M, int64_t D, ExecCtx& ctx, bool pushed) {
+    FXF_CHECK(tp_exchange_usable(x, pushed ? nullptr : partial, M, D, ctx), "tensor-parallel exchange called with operands it cannot serve");
+    FXF_CHECK(!pushed || tp_push_usable(M, D, ctx), "tensor-parallel exchange: no exchange window for pushed rows");
     const PeerMap* pm = ctx.peers;
     XchgParams p{};
     fill_sync(&p.sync, pm, ctx);
@@ -396,7 +415,7 @@ int launch_tp_exchange(const TpExchange& x, const float* partial, int64_t M, int
     p.skip_rank = -1;
     const char* mine = pm->base[ctx.tp_rank];
     for (int r = 0; r < ctx.tp_size; r++) {
-        p.part[r] = reinterpret_cast<const float*>(pm->base[r] + (reinterpret_cast<const char*>(partial) - mine));
+        p.part[r] = pushed ? tp_push_window(r, ctx) : reinterpret_cast<const float*>(pm->base[r] + (reinterpret_cast<const char*>(partial) - mine));
         p.y[r] = x.y_out ? reinterpret_cast<float*>(pm->base[r] + (reinterpret_cast<char*>(x.y_out) - mine)) : nullptr;
         p.x[r] = (x.x_out && (x.replicate_x || r == ctx.tp_rank)) ? reinterpret_cast<float*>(pm->base[r] + (reinterpret_cast<char*>(x.x_out) - mine)) : nullptr;
         p.residual[r] = nullptr;
@@ -406,10 +425,13 @@ int launch_tp_exchange(const TpExchange& x, const float* partial, int64_t M, int
     p.M = M; p.n4 = int(D / 4);
     p.rows_per_rank = (M + ctx.tp_size - 1) / ctx.tp_size;
     p.x_own_only = x.replicate_x ? 0 : 1;
+    p.pushed = pushed ? 1 : 0;
     const double frac = double(ctx.tp_size - 1) / ctx.tp_size;
-    // bytes = what crosses NVLink for this rank, both directions (partial rows in, normalised / residual rows out)
+    // bytes = what ARRIVES at this rank over NVLink during the kernel: the peers' partial rows it fetches (unless pushed) and
+    // the normalised / residual rows the peers store into it; the same amount leaves it.  That makes an exchange an
+    // NVLink-bound step: 2 * (n-1)/n of the activation per direction, whatever the kernel does with it.
     tag_launch(ctx, "tp_exchange_add_layernorm", double(M) * D + 8.0 * double(M) * D / ctx.tp_size,
-               4.0 * double(M) * D * frac * (1.0 + (x.y_out ? 1.0 : 0.0) + ((x.x_out && x.replicate_x) ? 1.0 : 0.0)));
+               4.0 * double(M) * D * frac * ((pushed ? 0.0 : 1.0) + (x.y_out ? 1.0 : 0.0) + ((x.x_out && x.replicate_x) ? 1.0 : 0.0)));
     cudaError_t e = launch_xchg_nv((p.n4 + 31) / 32, p, dim3(unsigned(pm->grid)), ctx.stream, false);
     FXF_CHECK(e == cudaSuccess, "tensor-parallel exchange: launch failed: %s", cudaGetErrorString(e));
     FXF_LAUNCHED(ctx);
@@ -420,9 +442,13 @@ int launch_tp_exchange(const TpExchange& x, const float* partial, int64_t M, int
 // carries the blocks of every rank (blockIdx.y = rank), so that blocks that wait for one another are resident together.
 // `sync_mem`: n_ranks * 8192 zeroed bytes ([0,4096) flags, then three control ints, status word at byte 4160 of each
 // rank's region).  skip_rank >= 0 keeps that rank away from the exchange: the others run into their wait budget.
+// layout: bit 0 = every rank receives every row of x_out; bit 1 = partial[q] is rank q's exchange window as the pushing
+// products leave it (row p*R + l = producer p's partial sums of row q*R + l, R = M / n_ranks).
 int tp_exchange_emulated(int n_ranks, const float* const* partial, const float* const* residual, float* const* x_out, float* const* y_out,
-                         const float* gamma, const float* beta, float eps, int64_t M, int64_t D, int replicate_x, void* sync_mem, int budget_ms,
+                         const float* gamma, const float* beta, float eps, int64_t M, int64_t D, int layout, void* sync_mem, int budget_ms,
                          int skip_rank, cudaStream_t stream) {
+    const int replicate_x = layout & 1, pushed = (layout >> 1) & 1;
+    FXF_CHECK(!pushed || M % n_ranks == 0, "emulated exchange: pushed rows need M to be a multiple of the rank count");
     FXF_CHECK(n_ranks >= 2 && n_ranks <= kMaxTpRanks, "emulated exchange: 2..%d ranks", kMaxTpRanks);
     FXF_CHECK(partial && sync_mem && D % 4 == 0 && D > 0 && D <= 1024 && M > 0, "emulated exchange: bad arguments");
     FXF_CHECK(budget_ms > 0 && budget_ms <= 2000, "emulated exchange: the wait budget must be 1..2000 ms");
@@ -448,6 +474,7 @@ int tp_exchange_emulated(int n_ranks, const float* const* partial, const float* 
     p.M = M; p.n4 = int(D / 4);
     p.rows_per_rank = (M + n_ranks - 1) / n_ranks;
     p.x_own_only = replicate_x ? 0 : 1;
+    p.pushed = pushed;
     cudaError_t e = launch_xchg_nv((p.n4 + 31) / 32, p, dim3(kGridX, unsigned(n_ranks)), stream, true);
     FXF_CHECK(e == cudaSuccess, "emulated exchange: cooperative launch failed: %s", cudaGetErrorString(e));
     return 0;

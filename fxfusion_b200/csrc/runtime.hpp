@@ -46,6 +46,9 @@ struct PeerMap {
     size_t flags_off = 0;           // barrier flags [peer][block] of the peer all-reduce, same offset on every rank
     size_t epoch_off = 0;           // two ints: epoch, finished-block counter
     int grid = 0;                   // blocks of the peer exchange kernels (fixes the flag layout)
+    // Exchange window: a buffer outside the planner's arena (same offset on every rank, never reused for anything else) into
+    // which the peers' row-parallel products store their partial sums of this rank's rows.  0 bytes: no window.
+    size_t push_off = 0, push_bytes = 0;
     // wait budgets of the two peer barriers of an exchange; the first also absorbs the skew between the ranks' host threads
     unsigned long long start_budget_ns = 20000000000ull, end_budget_ns = 2000000000ull;
 };
@@ -267,6 +270,12 @@ struct GemmArgs {
     int64_t ldx = 0, ldw = 0, ldo = 0;
     bool relu = false;
     bool conv_chain = false;   // a convolution written as a GEMM: use the (shorter) accumulation chains of convolutions
+    // Row-pushed output of a row-parallel product under tensor parallelism (tensor-core kernels only): rows
+    // [q*push_rows, (q+1)*push_rows) of the result go to push_out[q] (rank q's exchange window, peer memory for q != rank) at
+    // row push_rank*push_rows + (row - q*push_rows); `out` is not written.  push_rows == 0: the plain output.
+    float* const* push_out = nullptr;
+    int64_t push_rows = 0;
+    int push_rank = 0;
 };
 int launch_gemm(const GemmArgs& a, ExecCtx& ctx);
 int launch_gemm_simt(const GemmArgs& a, ExecCtx& ctx);
@@ -333,7 +342,11 @@ bool p2p_all_reduce_usable(const float* buf, int64_t n, const ExecCtx& ctx);
 int launch_p2p_all_reduce(float* buf, int64_t n, ExecCtx& ctx);
 // sum of the ranks' partial [M,D] + residual -> x_out (own rows or all), LayerNorm of the rows -> y_out on every rank
 bool tp_exchange_usable(const TpExchange& x, const float* partial, int64_t M, int64_t D, const ExecCtx& ctx);
-int launch_tp_exchange(const TpExchange& x, const float* partial, int64_t M, int64_t D, ExecCtx& ctx);
+int launch_tp_exchange(const TpExchange& x, const float* partial, int64_t M, int64_t D, ExecCtx& ctx, bool pushed = false);
+// Pushed exchange: the product stores its rows straight into the owners' exchange windows (GemmArgs::push_out); `partial`
+// is then unused.  Usable when the engine has a window of M*D floats and every rank owns a whole number of 128-row tiles.
+bool tp_push_usable(int64_t M, int64_t D, const ExecCtx& ctx);
+float* tp_push_window(int rank, const ExecCtx& ctx);
 int tp_exchange_emulated(int n_ranks, const float* const* partial, const float* const* residual, float* const* x_out, float* const* y_out,
                          const float* gamma, const float* beta, float eps, int64_t M, int64_t D, int replicate_x, void* sync_mem, int budget_ms,
                          int skip_rank, cudaStream_t stream);

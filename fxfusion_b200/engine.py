@@ -68,7 +68,7 @@ class ExecutionEngine:
         hidden units sharded over its ranks; construction is collective).  `shard_output` additionally shards
         the vocabulary of the final Linear: `outputs()` then holds only this rank's column block and
         `argmax_scatter` / `decode_static` combine the ranks.  `options`: further integer fields of FxfEngineOptions by
-        name (no_epilogue_fusion, no_tp_fused_exchange, p2p_start_budget_ms, p2p_end_budget_ms, p2p_grid, tc_chunk_k, tc_pair)."""
+        name (no_epilogue_fusion, no_tp_fused_exchange, p2p_start_budget_ms, p2p_end_budget_ms, p2p_grid, tc_chunk_k, tc_pair, tp_push)."""
         self._h = C.c_void_p()
         lib = _lib.lib()
         if precision not in _lib.GEMM_MODES:
@@ -80,7 +80,7 @@ class ExecutionEngine:
         opts.tp_rank, opts.tp_size = (comm.rank, comm.size) if comm is not None else (0, 1)
         opts.tp_shard_output = 1 if (shard_output and comm is not None) else 0
         for key, value in options.items():
-            if key not in ("no_epilogue_fusion", "no_tp_fused_exchange", "p2p_start_budget_ms", "p2p_end_budget_ms", "p2p_grid", "tc_chunk_k", "tc_pair"):
+            if key not in ("no_epilogue_fusion", "no_tp_fused_exchange", "p2p_start_budget_ms", "p2p_end_budget_ms", "p2p_grid", "tc_chunk_k", "tc_pair", "tp_push"):
                 raise TypeError(f"unknown engine option '{key}'")
             setattr(opts, key, int(value))
         self.comm = comm  # keeps the communicator alive as long as the engine

@@ -74,10 +74,11 @@ def feedforward_static(x, w1, b1, w2, b2, out) -> None:
 
 
 def tp_exchange_emulated(partials, residuals=None, x_outs=None, y_outs=None, gamma=None, beta=None, eps: float = 1e-5,
-                         replicate_x: bool = False, budget_ms: int = 200, skip_rank: int = -1):
+                         replicate_x: bool = False, budget_ms: int = 200, skip_rank: int = -1, pushed: bool = False):
     """The tensor-parallel exchange (sum of the ranks' partial [M,D] + residual, LayerNorm, rows owned by rank) with all
     ranks' buffers on the current GPU and one cooperative launch (fxf_tp_exchange_emulated).  Each argument is a list with
-    one float32 CUDA tensor [M,D] per rank (or None).  Returns the ranks' status words after the call has finished."""
+    one float32 CUDA tensor [M,D] per rank (or None).  pushed: partials[q] is rank q's exchange window as the row-pushed
+    products leave it (see linear_pushed).  Returns the ranks' status words after the call has finished."""
     import torch
     lib = _lib.lib()
     n = len(partials)
@@ -87,11 +88,30 @@ def tp_exchange_emulated(partials, residuals=None, x_outs=None, y_outs=None, gam
     stream = C.c_void_p(torch.cuda.current_stream(partials[0].device).cuda_stream)
     _lib.check(lib.fxf_tp_exchange_emulated(n, arr(partials), arr(residuals), arr(x_outs), arr(y_outs),
                                             gamma.data_ptr() if gamma is not None else None, beta.data_ptr() if beta is not None else None,
-                                            float(eps), M, D, 1 if replicate_x else 0, C.c_void_p(sync.data_ptr()), sync.numel(), int(budget_ms),
+                                            float(eps), M, D, (1 if replicate_x else 0) | (2 if pushed else 0), C.c_void_p(sync.data_ptr()), sync.numel(), int(budget_ms),
                                             int(skip_rank), stream))
     torch.cuda.synchronize()
     words = sync.view(torch.int32).view(n, 2048)[:, 4160 // 4].cpu().tolist()
     return words
+
+
+def linear_pushed(x, w, bias, windows, rank: int):
+    """Producer `rank`'s row-parallel product x[M,K] @ w[N,K].T (+ bias) on the tensor cores with a row-pushed output
+    (fxf_linear_pushed): row g of the result, owned by rank q = g // R with R = M // len(windows), lands in windows[q] at
+    row rank*R + (g - q*R).  windows: one float32 CUDA tensor [M,N] per rank, all on the current GPU."""
+    import torch
+    lib = _lib.lib()
+    n = len(windows)
+    M, K = x.shape
+    N = w.shape[0]
+    need = lib.fxf_linear_pushed_scratch_bytes(N, K)
+    scratch = torch.empty(need + 256, dtype=torch.uint8, device=x.device)
+    base = (scratch.data_ptr() + 255) // 256 * 256
+    arr = (C.c_void_p * n)(*[t.data_ptr() for t in windows])
+    stream = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(lib.fxf_linear_pushed(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None, arr, n, int(rank), M, N, K,
+                                     C.c_void_p(base), need, stream))
+    torch.cuda.synchronize()
 
 
 def gemm_variant(M: int, N: int, K: int, precision: str = "auto", sm_count: int = 148) -> str:

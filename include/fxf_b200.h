@@ -92,7 +92,11 @@ typedef struct FxfEngineOptions {
     int32_t tc_pair;               /* 0: the widest tensor-core GEMM tiles (256 columns) are computed by pairs of CTAs
                                       (tcgen05 cta_group::2: 256-row tiles, each CTA stages half of the weight tile);
                                       1: never */
-    int32_t reserved[3];
+    int32_t tp_push;               /* 0: under tensor parallelism the row-parallel products keep their partial sums local and
+                                      the exchange kernel fetches them from the peers; 1: the products store each row
+                                      into its owner's exchange window (peer stores from the GEMM epilogue), the exchange
+                                      kernel then reads local memory only */
+    int32_t reserved[2];
 } FxfEngineOptions;
 
 typedef struct fxf_engine fxf_engine;
@@ -134,16 +138,27 @@ FXF_API int fxf_engine_create_tp(const char* graph_path, int device_ordinal, con
 /* The exchange step of the tensor-parallel layout, emulated on ONE GPU (no counterpart in the reference; meant for tests
  * where fewer GPUs than ranks are available): the buffers of all n_ranks ranks live on the current device and one
  * cooperative launch carries the blocks of every rank.  For rank r and its rows [r*R, (r+1)*R), R = ceil(M / n_ranks):
- *   x = sum_q partial[q][row] (q = 0..n-1 in order) + residual[r][row];   x_out[r][row] = x  (every x_out[q] when replicate_x);
+ *   x = sum_q partial[q][row] (q = 0..n-1 in order) + residual[r][row];   x_out[r][row] = x  (every x_out[q] when layout & 1);
  *   y_out[q][row] = LayerNorm(x) * gamma + beta over the D columns, for every q.
  * residual, x_out, y_out may be NULL (then gamma / beta may be NULL too).  sync_mem: n_ranks * 8192 zeroed device bytes;
  * afterwards the int at byte r * 8192 + 4160 is rank r's status word (0, or 121 / 122 / 123 as for fxf_engine_create_tp).
  * budget_ms (1..2000) bounds each peer wait; skip_rank >= 0 keeps that rank away from the exchange, so the other ranks'
- * waits run out and report it — the call still returns and the device stays usable. */
+ * waits run out and report it — the call still returns and the device stays usable.
+ * layout bit 1 (value 2): partial[q] is rank q's exchange window as the row-pushed products leave it (M a multiple of
+ * n_ranks): row p*R + l of it holds producer p's partial sums of row q*R + l, so rank q reads only its own buffer. */
 FXF_API int fxf_tp_exchange_emulated(int n_ranks, const float* const* partial, const float* const* residual,
                                      float* const* x_out, float* const* y_out, const float* gamma, const float* beta,
-                                     float eps, int64_t M, int64_t D, int replicate_x, void* sync_mem,
+                                     float eps, int64_t M, int64_t D, int layout, void* sync_mem,
                                      int64_t sync_bytes, int budget_ms, int skip_rank, void* stream);
+/* The row-parallel product of the tensor-parallel layout with a row-pushed output, outside an engine (no counterpart in
+ * the reference; one GPU can play every producer in turn): producer `rank` of n_ranks computes x[M,K] @ w[N,K]^T (+ bias
+ * [N], may be NULL) on the tensor cores and stores row g of the result, owned by rank q = g / R (R = M / n_ranks, a
+ * multiple of 128), into windows[q] at row rank*R + (g - q*R); each window holds M*N floats.  scratch: 256-byte aligned,
+ * fxf_linear_pushed_scratch_bytes(N, K) bytes (split weights + the kernel's K-split workspace). */
+FXF_API int64_t fxf_linear_pushed_scratch_bytes(int64_t N, int64_t K);
+FXF_API int fxf_linear_pushed(const float* x, const float* w, const float* bias, float* const* windows, int n_ranks,
+                              int rank, int64_t M, int64_t N, int64_t K, void* scratch, int64_t scratch_bytes,
+                              void* stream);
 /* tokens[b, current_len] = argmax_v output0[b, current_len-1, v] for this engine, whether the vocabulary is
  * sharded (candidates of all ranks are gathered and every rank writes the same token) or not. */
 FXF_API int fxf_engine_argmax_scatter(fxf_engine* e, int64_t* tokens, int current_len, void* stream);

@@ -89,3 +89,44 @@ def test_exchange_wait_runs_out_when_a_rank_never_arrives(built_lib):
     status = tp_exchange_emulated(dp, None, None, dy, gamma.cuda(), beta.cuda(), 1e-5, budget_ms=200)
     assert status == [0] * n
     assert torch.allclose(dy[0].cpu(), torch.nn.functional.layer_norm(x, (D,), gamma, beta, 1e-5), atol=1e-4, rtol=1e-3)
+
+
+@pytest.mark.parametrize("n,M,N,K", [(2, 512, 256, 128), (4, 1024, 768, 192), (2, 2048, 768, 384), (4, 512, 200, 64)])
+def test_row_pushed_product_feeds_the_exchange(built_lib, n, M, N, K):
+    """The row-parallel product with a row-pushed output (every producer played in turn on this GPU) followed by the exchange
+    in its pushed layout: each owner finds all producers' partial rows in its own window, and the result equals the
+    unsharded Linear + residual Add + LayerNorm."""
+    from fxfusion_b200.kernels import linear_pushed, tp_exchange_emulated
+    g = torch.Generator().manual_seed(n * 100 + K)
+    xs = [torch.randn(M, K, generator=g) for _ in range(n)]            # producer p's slice of the activation columns
+    ws = [torch.randn(N, K, generator=g) / K ** 0.5 for _ in range(n)]  # and of the weight columns
+    bias = torch.randn(N, generator=g)
+    res = torch.randn(M, N, generator=g)
+    gamma, beta = torch.randn(N, generator=g), torch.randn(N, generator=g)
+    R = M // n
+    windows = [torch.full((M, N), float("nan"), device="cuda") for _ in range(n)]
+    for p in range(n):
+        linear_pushed(xs[p].cuda(), ws[p].cuda(), bias.cuda() if p == 0 else None, windows, p)
+    parts = [xs[p].double() @ ws[p].double().T + (bias.double() if p == 0 else 0.0) for p in range(n)]
+    for q in range(n):
+        got = windows[q].cpu()
+        for p in range(n):
+            want = parts[p][q * R:(q + 1) * R]
+            err = (got[p * R:(p + 1) * R].double() - want).abs().max().item()
+            assert err < 2e-5 * max(1.0, want.abs().max().item()), (q, p, err)
+    want_x = (sum(parts) + res.double()).float()
+    want_y = torch.nn.functional.layer_norm(want_x, (N,), gamma, beta, 1e-5)
+    dx = [torch.full((M, N), float("nan"), device="cuda") for _ in range(n)]
+    dy = [torch.full((M, N), float("nan"), device="cuda") for _ in range(n)]
+    status = tp_exchange_emulated(windows, [res.cuda() for _ in range(n)], dx, dy, gamma.cuda(), beta.cuda(), 1e-5, pushed=True)
+    assert status == [0] * n
+    for r in range(n):
+        assert torch.allclose(dx[r].cpu()[r * R:(r + 1) * R], want_x[r * R:(r + 1) * R], atol=1e-4, rtol=1e-4)
+        assert torch.allclose(dy[r].cpu(), want_y, atol=1e-4, rtol=1e-3), (dy[r].cpu() - want_y).abs().max().item()
+
+
+def test_row_pushed_product_rejects_ragged_ownership(built_lib):
+    from fxfusion_b200.kernels import linear_pushed
+    windows = [torch.zeros(384, 256, device="cuda") for _ in range(2)]
+    with pytest.raises(RuntimeError, match="128-row"):
+        linear_pushed(torch.zeros(384, 128, device="cuda"), torch.zeros(256, 128, device="cuda"), None, windows, 0)

@@ -133,6 +133,24 @@ def gpu_checks(rank, size, tmp):
             assert err < 1e-4, f"rank {rank} {precision} {options}: TP forward differs from the oracle by {err}"
         assert eng.device_status() == 0
         eng.close()
+    # row-pushed products: every rank owns whole 128-row tiles (8 x 64 = 512 rows over 2 or 4 ranks), so the products store
+    # their rows into the owners' exchange windows and the exchange reads local memory
+    B8 = 8
+    graph8 = lowering.gpt_graph(cfg, lowering.gpt_params(cfg, 0), batch=B8, seq=T, name="tp_gpt8")
+    path8 = os.path.join(tmp, f"tp_gpt8_{rank}.bin")
+    wire.dump(graph8, path8)
+    buf8 = make_static_buffer(torch.from_numpy(lowering.decode_prompt(B8, L0, cfg.vocab)), T)
+    mask8 = static_decoder_mask(buf8, L0)
+    want8 = GraphOracle(graph8).run([buf8, mask8])[0]
+    for options in ({"tp_push": 1}, {}):
+        eng = ExecutionEngine(path8, f"cuda:{rank}", comm=comm, **options)
+        assert ("exchange window" in eng.describe()) == bool(options), eng.describe()
+        for _ in range(3):   # the window is reused by every exchange of every run
+            got8 = eng.run([buf8.cuda(), mask8.cuda()])[0].cpu()
+            err = (got8 - want8).abs().max().item()
+            assert err < 1e-4, f"rank {rank} {options}: TP forward with row-pushed products differs from the oracle by {err}"
+        assert eng.device_status() == 0
+        eng.close()
     # heads that do not divide over the ranks (3 heads): the MHA nodes are replicated on every rank (no exchange, bias and
     # residual on every rank), the FeedForward nodes are still sharded
     cfg3 = lowering.GPTConfig(192, 3, 300, 4, 2)
