@@ -3,7 +3,7 @@
 // with both contractions on tcgen05 (kind::tf32, three products per logical product, fp32-grade).
 // Same semantics as attention.cu (reference csrc/kernels/cpu/mha.cpp:38-49): division by the scale,
 // -inf where mask == 0, fully masked rows give NaN, masked keys still enter P·V with weight 0 (so a
-// non-finite V row poisons the output as 0 * inf does in the reference).  A block of 128 keys is skipped
+// non-finite V row poisons the output as 0 * inf does in the reference).  A block of 64 keys is skipped
 // only when that cannot change a bit of the result: every mask byte of the block is 0 for all 128 query
 // rows of the CTA (its probabilities are exactly 0) and the block's V rows are all finite (0 * V = 0).
 // With a causal mask that drops the upper-triangle blocks.
@@ -11,19 +11,25 @@
 // Two kernels:
 //   attn_vt_kernel   transposes the V third of the packed projection qkv[B*T, 3D] into V^T [B*H, 64, T]
 //                    (keys contiguous) so that the B operand of P·V is K-major.
-//   attn_tc_kernel   one CTA per (128 queries, b, h), 384 threads.  TMEM columns:
-//                    S [128x128] | P_hi [128x128] | P_lo [128x128] | O [128x64].
+//   attn_tc_kernel   one CTA per (128 queries, b, h), 384 threads, key blocks of 64, TWO CTAs per SM: a CTA walks
+//                    TMA -> split -> S-MMA -> softmax -> P·V-MMA of a block as one dependent chain, so a second resident
+//                    CTA is what keeps the tensor pipe and the softmax threads of an SM busy at the same time.  Per CTA
+//                    106 KB of shared memory and 256 of the 512 tensor-memory columns:
+//                        S [128x64] (P_hi overwrites it in place) | P_lo [128x64] | O [128x64] | Q_lo [128x64].
 //       warp 0, lane 0  TMA loads (Q and K tiles straight out of qkv through a 3-D tensor map, V^T
 //                       tiles from the transposed copy; zero fill beyond T) and all MMAs:
-//                       S = Q·K_blk^T with both operands in shared memory, O_blk = P·V_blk with P read
-//                       from TMEM.
-//       warps 1-3       write the TF32 "lo" twin of every landed Q / K / V tile (the tile itself serves as "hi": the MMA
+//                       S = Q·K_blk^T (q_lo from tensor memory, q_hi / k_hi / k_lo from shared memory),
+//                       O_blk = P·V_blk with P read from tensor memory.
+//       warps 1-3       write the TF32 "lo" twin of every landed K / V tile (the tile itself serves as "hi": the MMA
 //                       ignores the 13 low mantissa bits), so the softmax threads never wait for operands;
-//       warps 4-11      softmax, two threads per query row, each owning 64 of the block's 128 keys
-//                       and 32 of the 64 output columns: tcgen05.ld of S, scale, mask (staged through
-//                       shared memory so the global reads are coalesced), online softmax in the log2
-//                       domain (running max m, running sum l), P split into hi/lo and stored to TMEM;
-//                       after the P·V MMA the block's O is folded into registers (o = o*alpha + O_blk).
+//       warps 4-11      softmax, two threads per query row, each owning 32 of the block's 64 keys and 32 of the 64
+//                       output columns: first the "lo" twin of their half row of Q into tensor memory; per block
+//                       tcgen05.ld of S, scale, mask (staged through shared memory so the global reads are
+//                       coalesced), online softmax in the log2 domain (running max m, running sum l), P split
+//                       into hi/lo and stored to TMEM; after the P·V MMA the block's O is folded into registers
+//                       (o = o*alpha + O_blk).
+//       Registers: the kernel starts with 80 per thread (384 threads x 2 CTAs); setmaxnreg moves warps 0-3 to 48 and
+//       the softmax warps to 96.
 // Waits are bounded; on expiry the CTA records an error code in the status word and leaves.
 #include <cmath>
 
@@ -35,11 +41,14 @@ namespace {
 
 using namespace sm100;
 
-constexpr int HD = 64, BQ = 128, BKEY = 128;
+constexpr int HD = 64, BQ = 128, BKEY = 64;
 constexpr int kAttnThreads = 384;
+constexpr uint32_t kTmemCols = 256;      // S / P_hi | P_lo | O | Q_lo, 64 columns each: two CTAs share an SM's 512 columns
+constexpr int kRegsCtrl = 48, kRegsSoft = 96;   // setmaxnreg budgets: warps 0-3 (TMA / MMA / splits) and warps 4-11 (softmax);
+                                                // 128 * 48 + 256 * 96 = the 384 * 80 registers a CTA starts with
 constexpr int kSoftWarp0 = 4;            // warps 4..11: TMEM lane quarter = warp % 4, key half = (warp - 4) / 4
 constexpr int kSplitWarp0 = 1, kSplitWarps = 3;   // warps 1..3 split the landed Q / K / V tiles (off the softmax threads' path)
-constexpr int kMaskPitch = 144;          // bytes per staged mask row (128 + 16): 16-byte reads stay conflict-free
+constexpr int kMaskPitch = 80;           // bytes per staged mask row (64 + 16): 16-byte reads stay conflict-free
 constexpr float kLog2e = 1.4426950408889634f;
 enum : int { kErrAttnQ = 111, kErrAttnK = 112, kErrAttnV = 113, kErrAttnS = 114, kErrAttnP = 115, kErrAttnO = 116, kErrAttnSplit = 117 };
 
@@ -84,16 +93,17 @@ __global__ void __launch_bounds__(256) attn_vt_kernel(const float* __restrict__ 
 
 // ---- main kernel -------------------------------------------------------------------------------------
 struct alignas(1024) AttnTcSmem {
-    float q_hi[2][BQ * 32], q_lo[2][BQ * 32];      // two 32-wide slabs of head_dim
+    float q_hi[2][BQ * 32];                        // two 32-wide slabs of head_dim (the "lo" twin of Q lives in tensor memory)
     float k_hi[2][BKEY * 32], k_lo[2][BKEY * 32];
-    float v_hi[4][HD * 32], v_lo[4][HD * 32];      // four 32-key slabs of V^T [64 x 32]
+    float v_hi[2][HD * 32], v_lo[2][HD * 32];      // two 32-key slabs of V^T [64 x 32]
     unsigned char mask_rows[BQ * kMaskPitch];      // this block's mask bytes, one padded row per query
     float exch[2][BQ];                             // row statistics exchanged between the two threads of a row
     uint64_t bar_q, bar_k, bar_v, bar_qs, bar_ks, bar_vs, bar_s, bar_p, bar_o;
+    unsigned long long need_blocks;                // bit blk set: key block blk has to be processed
     uint32_t tmem_base;
     int abort_flag;
-    unsigned int need_blocks;   // bit blk set: key block blk has to be processed
 };
+static_assert(2 * (sizeof(AttnTcSmem) + 2048) <= 228 * 1024, "two CTAs of the attention kernel must fit one SM");
 
 struct AttnTcParams {
     const unsigned char* vflags;   // per (batch*head, 32-key slab): V has a non-finite element
@@ -129,8 +139,12 @@ __device__ __forceinline__ void split_tile(const float* hi_buf, float* lo_buf, i
         lo[i] = l;
     }
 }
+template <int N>
+__device__ __forceinline__ void attn_reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void attn_reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kAttnThreads, 2)
 attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_vt,
                AttnTcParams p) {
     extern __shared__ unsigned char smem_raw[];
@@ -143,25 +157,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
     const int nblk = (Tk + BKEY - 1) / BKEY;
     volatile int* abort_flag = &s.abort_flag;
     constexpr uint32_t kQBytes = BQ * HD * 4, kKBytes = BKEY * HD * 4, kVBytes = HD * BKEY * 4;
-    constexpr uint32_t kColS = 0, kColPhi = 128, kColPlo = 256, kColO = 384;
-    constexpr uint32_t kIdescS = umma_idesc_tf32(BQ, BKEY), kIdescO = umma_idesc_tf32(BQ, HD);
+    constexpr uint32_t kColS = 0, kColPhi = 0, kColPlo = 64, kColO = 128, kColQlo = 192;   // P_hi replaces S in place
+    constexpr uint32_t kIdesc = umma_idesc_tf32(BQ, 64);   // both contractions produce 128 x 64 tiles (64 keys / 64 head columns)
 
     if (threadIdx.x == 0) {
         mbar_init(&s.bar_q, 1);
         mbar_init(&s.bar_k, 1);
         mbar_init(&s.bar_v, 1);
-        mbar_init(&s.bar_qs, kSplitWarps);    // one arrival per split warp
-        mbar_init(&s.bar_ks, kSplitWarps);
+        mbar_init(&s.bar_qs, 8);              // one arrival per softmax warp (they write Q_lo into tensor memory)
+        mbar_init(&s.bar_ks, kSplitWarps);    // one arrival per split warp
         mbar_init(&s.bar_vs, kSplitWarps);
         mbar_init(&s.bar_s, 1);
         mbar_init(&s.bar_p, 8);
         mbar_init(&s.bar_o, 1);
         s.abort_flag = 0;
-        s.need_blocks = 0;
+        s.need_blocks = 0ull;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s.tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s.tmem_base)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -170,209 +184,223 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
     const uint32_t tmem = s.tmem_base;
 
     // ---- which key blocks matter to this CTA's 128 query rows ----
-    const unsigned int all_blocks = nblk >= 32 ? 0xffffffffu : ((1u << nblk) - 1u);
-    if (p.mask_vec16 && nblk <= 32) {
-        unsigned int mine = 0;
+    const unsigned long long all_blocks = nblk >= 64 ? ~0ull : ((1ull << nblk) - 1ull);
+    if (p.mask_vec16 && nblk <= 64) {
+        unsigned long long mine = 0;
         const uint8_t* mh = p.mask + int64_t(b) * p.mask_sb + int64_t(h) * p.mask_sh;
         const int vec_per_row = Tk / 16, rows = min(BQ, T - q0);
         for (int idx = threadIdx.x; idx < rows * vec_per_row; idx += kAttnThreads) {
             const int rr = idx / vec_per_row, vv = idx - rr * vec_per_row;
             const uint4 m16 = *reinterpret_cast<const uint4*>(mh + int64_t(q0 + rr) * p.mask_sq + vv * 16);
-            if (m16.x | m16.y | m16.z | m16.w) mine |= 1u << (vv / (BKEY / 16));
+            if (m16.x | m16.y | m16.z | m16.w) mine |= 1ull << (vv / (BKEY / 16));
         }
         // a block whose V rows hold NaN or infinity is kept: 0 * inf has to reach the output
         for (int sl = threadIdx.x; sl < p.n32; sl += kAttnThreads)
-            if (p.vflags[int64_t(bh) * p.n32 + sl]) mine |= 1u << (sl / (BKEY / 32));
-        mine = __reduce_or_sync(0xffffffffu, mine);
+            if (p.vflags[int64_t(bh) * p.n32 + sl]) mine |= 1ull << (sl / (BKEY / 32));
+        const unsigned int lo32 = __reduce_or_sync(0xffffffffu, (unsigned int)(mine & 0xffffffffull));
+        const unsigned int hi32 = __reduce_or_sync(0xffffffffu, (unsigned int)(mine >> 32));
+        mine = (unsigned long long)lo32 | ((unsigned long long)hi32 << 32);
         if (lane == 0 && mine) atomicOr(&s.need_blocks, mine);
         __syncthreads();
     } else {
         if (threadIdx.x == 0) s.need_blocks = all_blocks;
         __syncthreads();
     }
-    const unsigned int need = s.need_blocks & all_blocks;
-    const int n_act = __popc(need);
+    const unsigned long long need = s.need_blocks & all_blocks;
+    const int n_act = __popcll(need);
 
-    if (warp == 0) {
-        if (lane == 0) {
-            auto load_k = [&](int blk) {
-                mbar_expect_tx(&s.bar_k, kKBytes);
-                for (int sl = 0; sl < 2; sl++) tma_load_3d(s.k_hi[sl], &map_k, p.k_col + h * HD + sl * 32, blk * BKEY, b, &s.bar_k);
-            };
-            auto load_v = [&](int blk) {
-                mbar_expect_tx(&s.bar_v, kVBytes);
-                for (int ks = 0; ks < 4; ks++) tma_load_3d(s.v_hi[ks], &map_vt, blk * BKEY + ks * 32, 0, bh, &s.bar_v);
-            };
-            unsigned int rem = need;
-            if (n_act > 0) {
-                mbar_expect_tx(&s.bar_q, kQBytes);
-                for (int sl = 0; sl < 2; sl++) tma_load_3d(s.q_hi[sl], &map_qkv, p.q_col + h * HD + sl * 32, q0, b, &s.bar_q);
-                load_k(__ffs(rem) - 1);
-                load_v(__ffs(rem) - 1);
-            }
-            if (n_act > 0 && !mbar_wait(&s.bar_qs, 0, abort_flag)) {
-                give_up(abort_flag, p.status, kErrAttnQ);
-            } else {
-                for (int i = 0; i < n_act; i++) {
-                    rem &= rem - 1;                                   // `rem` now holds the blocks after this one
-                    const int next_blk = rem ? __ffs(rem) - 1 : -1;
-                    const uint32_t par = i & 1;
-                    if (!mbar_wait(&s.bar_ks, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnK); break; }
-                    tc_fence_after();
-                    // S = Q · K_blk^T
+    if (warp < 4) {
+        attn_reg_dec<kRegsCtrl>();
+        if (warp == 0) {
+            if (lane == 0) {
+                auto load_k = [&](int blk) {
+                    mbar_expect_tx(&s.bar_k, kKBytes);
+                    for (int sl = 0; sl < 2; sl++) tma_load_3d(s.k_hi[sl], &map_k, p.k_col + h * HD + sl * 32, blk * BKEY, b, &s.bar_k);
+                };
+                auto load_v = [&](int blk) {
+                    mbar_expect_tx(&s.bar_v, kVBytes);
+                    for (int ks = 0; ks < 2; ks++) tma_load_3d(s.v_hi[ks], &map_vt, blk * BKEY + ks * 32, 0, bh, &s.bar_v);
+                };
+                unsigned long long rem = need;
+                if (n_act > 0) {
+                    mbar_expect_tx(&s.bar_q, kQBytes);
+                    for (int sl = 0; sl < 2; sl++) tma_load_3d(s.q_hi[sl], &map_qkv, p.q_col + h * HD + sl * 32, q0, b, &s.bar_q);
+                    load_k(__ffsll(rem) - 1);
+                    load_v(__ffsll(rem) - 1);
+                }
+                if (n_act > 0 && !mbar_wait(&s.bar_qs, 0, abort_flag)) {
+                    give_up(abort_flag, p.status, kErrAttnQ);
+                } else {
+                    for (int i = 0; i < n_act; i++) {
+                        rem &= rem - 1;                                   // `rem` now holds the blocks after this one
+                        const int next_blk = rem ? __ffsll(rem) - 1 : -1;
+                        const uint32_t par = i & 1;
+                        if (!mbar_wait(&s.bar_ks, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnK); break; }
+                        tc_fence_after();
+                        // S = Q · K_blk^T: q_lo·k_hi (A from tensor memory), q_hi·k_lo, q_hi·k_hi (A from shared memory)
 #pragma unroll
-                    for (int sl = 0; sl < 2; sl++) {
-                        uint64_t qh = umma_desc_k_major<32>(smem_u32(s.q_hi[sl])), ql = umma_desc_k_major<32>(smem_u32(s.q_lo[sl]));
-                        uint64_t kh = umma_desc_k_major<32>(smem_u32(s.k_hi[sl])), kl = umma_desc_k_major<32>(smem_u32(s.k_lo[sl]));
+                        for (int sl = 0; sl < 2; sl++) {
+                            const uint64_t qh = umma_desc_k_major<32>(smem_u32(s.q_hi[sl]));
+                            const uint64_t kh = umma_desc_k_major<32>(smem_u32(s.k_hi[sl])), kl = umma_desc_k_major<32>(smem_u32(s.k_lo[sl]));
 #pragma unroll
-                        for (int kk = 0; kk < 4; kk++) {
-                            uint64_t adv = uint64_t((kk * 32) >> 4);
-                            umma_tf32(tmem + kColS, ql + adv, kh + adv, kIdescS, (sl > 0 || kk > 0) ? 1u : 0u);
-                            umma_tf32(tmem + kColS, qh + adv, kl + adv, kIdescS, 1u);
-                            umma_tf32(tmem + kColS, qh + adv, kh + adv, kIdescS, 1u);
+                            for (int kk = 0; kk < 4; kk++) {
+                                const uint64_t adv = uint64_t((kk * 32) >> 4);
+                                umma_tf32_ts(tmem + kColS, tmem + kColQlo + uint32_t(sl * 32 + kk * 8), kh + adv, kIdesc, (sl > 0 || kk > 0) ? 1u : 0u);
+                                umma_tf32(tmem + kColS, qh + adv, kl + adv, kIdesc, 1u);
+                                umma_tf32(tmem + kColS, qh + adv, kh + adv, kIdesc, 1u);
+                            }
                         }
-                    }
-                    umma_commit(&s.bar_s);
-                    if (next_blk >= 0) {  // K buffer is free once the S MMAs have completed
-                        if (!mbar_wait(&s.bar_s, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnS); break; }
-                        load_k(next_blk);
-                    }
-                    if (!mbar_wait(&s.bar_vs, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnV); break; }
-                    if (!mbar_wait(&s.bar_p, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnP); break; }
-                    tc_fence_after();
-                    // O_blk = P · V_blk   (A = P from TMEM, B = V^T slabs, K-major over keys)
-#pragma unroll
-                    for (int ks = 0; ks < 4; ks++) {
-                        uint64_t vh = umma_desc_k_major<32>(smem_u32(s.v_hi[ks])), vl = umma_desc_k_major<32>(smem_u32(s.v_lo[ks]));
-#pragma unroll
-                        for (int kk = 0; kk < 4; kk++) {
-                            uint64_t adv = uint64_t((kk * 32) >> 4);
-                            uint32_t pc = uint32_t(ks * 32 + kk * 8);
-                            umma_tf32_ts(tmem + kColO, tmem + kColPlo + pc, vh + adv, kIdescO, (ks > 0 || kk > 0) ? 1u : 0u);
-                            umma_tf32_ts(tmem + kColO, tmem + kColPhi + pc, vl + adv, kIdescO, 1u);
-                            umma_tf32_ts(tmem + kColO, tmem + kColPhi + pc, vh + adv, kIdescO, 1u);
+                        umma_commit(&s.bar_s);
+                        if (next_blk >= 0) {  // K buffer is free once the S MMAs have completed
+                            if (!mbar_wait(&s.bar_s, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnS); break; }
+                            load_k(next_blk);
                         }
-                    }
-                    umma_commit(&s.bar_o);
-                    if (next_blk >= 0) {  // V buffer is free once the P·V MMAs have completed
-                        if (!mbar_wait(&s.bar_o, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnO); break; }
-                        load_v(next_blk);
+                        if (!mbar_wait(&s.bar_vs, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnV); break; }
+                        if (!mbar_wait(&s.bar_p, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnP); break; }
+                        tc_fence_after();
+                        // O_blk = P · V_blk   (A = P from tensor memory, B = V^T slabs, K-major over keys)
+#pragma unroll
+                        for (int ks = 0; ks < 2; ks++) {
+                            const uint64_t vh = umma_desc_k_major<32>(smem_u32(s.v_hi[ks])), vl = umma_desc_k_major<32>(smem_u32(s.v_lo[ks]));
+#pragma unroll
+                            for (int kk = 0; kk < 4; kk++) {
+                                const uint64_t adv = uint64_t((kk * 32) >> 4);
+                                const uint32_t pc = uint32_t(ks * 32 + kk * 8);
+                                umma_tf32_ts(tmem + kColO, tmem + kColPlo + pc, vh + adv, kIdesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                                umma_tf32_ts(tmem + kColO, tmem + kColPhi + pc, vl + adv, kIdesc, 1u);
+                                umma_tf32_ts(tmem + kColO, tmem + kColPhi + pc, vh + adv, kIdesc, 1u);
+                            }
+                        }
+                        umma_commit(&s.bar_o);
+                        if (next_blk >= 0) {  // V buffer is free once the P·V MMAs have completed
+                            if (!mbar_wait(&s.bar_o, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnO); break; }
+                            load_v(next_blk);
+                        }
                     }
                 }
             }
+        } else {
+            // ---------------- operand split: the "lo" twins of every landed K / V block ----------------
+            const int t = threadIdx.x - kSplitWarp0 * 32, nt = kSplitWarps * 32;
+            for (int i = 0; i < n_act; i++) {
+                const uint32_t par = i & 1;
+                if (!mbar_wait(&s.bar_k, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnK); break; }
+                split_tile(s.k_hi[0], s.k_lo[0], 2 * BKEY * 32 / 4, t, nt);
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.bar_ks);
+                if (!mbar_wait(&s.bar_v, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnV); break; }
+                split_tile(s.v_hi[0], s.v_lo[0], 2 * HD * 32 / 4, t, nt);
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.bar_vs);
+            }
         }
-    } else if (warp >= kSplitWarp0 && warp < kSplitWarp0 + kSplitWarps) {
-        // ---------------- operand split: the "lo" twins of Q (once) and of every landed K / V block ----------------
-        const int t = threadIdx.x - kSplitWarp0 * 32, nt = kSplitWarps * 32;
-        bool ok = n_act > 0;
-        if (ok && !mbar_wait(&s.bar_q, 0, abort_flag)) { give_up(abort_flag, p.status, kErrAttnQ); ok = false; }
-        if (ok) {
-            split_tile(s.q_hi[0], s.q_lo[0], 2 * BQ * 32 / 4, t, nt);
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s.bar_qs);
-        }
-        for (int i = 0; ok && i < n_act; i++) {
-            const uint32_t par = i & 1;
-            if (!mbar_wait(&s.bar_k, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnK); break; }
-            split_tile(s.k_hi[0], s.k_lo[0], 2 * BKEY * 32 / 4, t, nt);
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s.bar_ks);
-            if (!mbar_wait(&s.bar_v, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnV); break; }
-            split_tile(s.v_hi[0], s.v_lo[0], 4 * HD * 32 / 4, t, nt);
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s.bar_vs);
-        }
-    } else if (warp >= kSoftWarp0) {
+    } else {
         // ---------------- softmax: two threads per query row ----------------
+        attn_reg_inc<kRegsSoft>();
         const int sw = warp - kSoftWarp0;          // 0..7
         const int quarter = sw & 3, half = sw >> 2;
         const int row = quarter * 32 + lane, qi = q0 + row;
         const uint32_t lane_base = uint32_t(quarter * 32) << 16;
         const bool row_ok = qi < T;
         const uint8_t* mhead = p.mask + int64_t(b) * p.mask_sb + int64_t(h) * p.mask_sh;
+        bool alive = true;   // a thread that gave up keeps walking the loop so that soft_sync() stays matched
+        if (n_act > 0) {
+            // ---- the "lo" twin of this thread's row of Q (head columns [32*half, 32*half + 32)) goes into tensor memory ----
+            if (!mbar_wait(&s.bar_q, 0, abort_flag)) { give_up(abort_flag, p.status, kErrAttnQ); alive = false; }
+            if (alive) {
+                const float4* src = reinterpret_cast<const float4*>(s.q_hi[half]) + row * 8;   // 128-byte rows, 16-byte chunks XOR-swizzled by row % 8
+                const int swz = row & 7;
+                uint32_t lo[32];
+#pragma unroll
+                for (int c = 0; c < 8; c++) {
+                    const float4 v = src[c ^ swz];
+                    lo[4 * c + 0] = __float_as_uint(lo_of_truncated(v.x));
+                    lo[4 * c + 1] = __float_as_uint(lo_of_truncated(v.y));
+                    lo[4 * c + 2] = __float_as_uint(lo_of_truncated(v.z));
+                    lo[4 * c + 3] = __float_as_uint(lo_of_truncated(v.w));
+                }
+                tmem_st32(tmem + kColQlo + lane_base + uint32_t(half * 32), lo);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.bar_qs);
+            }
+        }
         float o[32];
 #pragma unroll
         for (int j = 0; j < 32; j++) o[j] = 0.f;
         float m_run = -INFINITY, l_run = 0.f;
-        bool alive = true;   // a thread that gave up keeps walking the loop so that soft_sync() stays matched
 
-        unsigned int rem = need;
+        unsigned long long rem = need;
         for (int i = 0; i < n_act; i++) {
-            const int blk = __ffs(rem) - 1;
+            const int blk = __ffsll(rem) - 1;
             rem &= rem - 1;
             const uint32_t par = i & 1;
-            // ---- stage this warp's share of the mask: rows of its quarter, the 64 keys of its half ----
-            const int key0 = blk * BKEY + half * 64;
+            // ---- stage this warp's share of the mask: rows of its quarter, the 32 keys of its half ----
+            const int key0 = blk * BKEY + half * 32;
             if (p.mask_vec16) {
 #pragma unroll
-                for (int it = 0; it < 4; it++) {
-                    int rr = quarter * 32 + it * 8 + (lane >> 2), kq = key0 + (lane & 3) * 16, qq = q0 + rr;
+                for (int it = 0; it < 2; it++) {
+                    const int rr = quarter * 32 + it * 16 + (lane >> 1), kq = key0 + (lane & 1) * 16, qq = q0 + rr;
                     uint4 v = make_uint4(0u, 0u, 0u, 0u);
                     if (qq < T && kq < Tk) v = *reinterpret_cast<const uint4*>(mhead + int64_t(qq) * p.mask_sq + kq);
-                    *reinterpret_cast<uint4*>(s.mask_rows + rr * kMaskPitch + half * 64 + (lane & 3) * 16) = v;
+                    *reinterpret_cast<uint4*>(s.mask_rows + rr * kMaskPitch + half * 32 + (lane & 1) * 16) = v;
                 }
             } else {
-                for (int idx = lane; idx < 32 * 64; idx += 32) {
-                    int rr = quarter * 32 + (idx >> 6), kc = key0 + (idx & 63), qq = q0 + rr;
+                for (int idx = lane; idx < 32 * 32; idx += 32) {
+                    const int rr = quarter * 32 + (idx >> 5), kc = key0 + (idx & 31), qq = q0 + rr;
                     unsigned char v = 0;
                     if (qq < T && kc < Tk) v = mhead[int64_t(qq) * p.mask_sq + int64_t(kc) * p.mask_sk];
-                    s.mask_rows[rr * kMaskPitch + half * 64 + (idx & 63)] = v;
+                    s.mask_rows[rr * kMaskPitch + half * 32 + (idx & 31)] = v;
                 }
             }
             __syncwarp();
-            uint32_t keep[2];
-#pragma unroll
-            for (int c = 0; c < 2; c++) {
-                uint32_t bits = 0;
-                const uint4* mp = reinterpret_cast<const uint4*>(s.mask_rows + row * kMaskPitch + half * 64 + c * 32);
+            uint32_t keep = 0;
+            {
+                const uint4* mp = reinterpret_cast<const uint4*>(s.mask_rows + row * kMaskPitch + half * 32);
 #pragma unroll
                 for (int w = 0; w < 2; w++) {
-                    uint4 m16 = mp[w];
-                    uint32_t words[4] = {m16.x, m16.y, m16.z, m16.w};
+                    const uint4 m16 = mp[w];
+                    const uint32_t words[4] = {m16.x, m16.y, m16.z, m16.w};
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
                         // 0x01 per non-zero byte, gathered into 4 bits by one multiply
-                        uint32_t nz = __vcmpne4(words[k], 0u) & 0x01010101u;
-                        bits |= ((nz * 0x01020408u) >> 24 & 0xFu) << (16 * w + 4 * k);
+                        const uint32_t nz = __vcmpne4(words[k], 0u) & 0x01010101u;
+                        keep |= ((nz * 0x01020408u) >> 24 & 0xFu) << (16 * w + 4 * k);
                     }
                 }
-                keep[c] = bits;
             }
             __syncwarp();
             // ---- pass 1: scale, mask, log2 domain, partial row maximum; processed scores go back to TMEM ----
             if (alive && !mbar_wait(&s.bar_s, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnS); alive = false; }
             float tmax = -INFINITY;
+            const uint32_t scol = tmem + kColS + lane_base + uint32_t(half * 32);
             if (alive) {
                 tc_fence_after();
+                uint32_t r[32];
+                tmem_ld32(scol, r);
+                tmem_wait_ld();
+                if (p.scale_is_pow2) {
+                    // v / 2^k * log2(e) == v * (2^-k * log2(e)) bit for bit: the first factor only shifts the exponent
+                    const float cmul = p.inv_scale * kLog2e;
 #pragma unroll
-                for (int c = 0; c < 2; c++) {
-                    uint32_t r[32];
-                    const uint32_t col = uint32_t(half * 64 + c * 32);
-                    tmem_ld32(tmem + kColS + lane_base + col, r);
-                    tmem_wait_ld();
-                    if (p.scale_is_pow2) {
-                        // v / 2^k * log2(e) == v * (2^-k * log2(e)) bit for bit: the first factor only shifts the exponent
-                        const float cmul = p.inv_scale * kLog2e;
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            float v = ((keep[c] >> j) & 1u) ? __uint_as_float(r[j]) * cmul : -INFINITY;
-                            tmax = fmaxf(tmax, v);  // NaN scores do not move the max; they reach the sum below
-                            r[j] = __float_as_uint(v);
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            float v = __uint_as_float(r[j]) / p.scale_divisor;
-                            v = ((keep[c] >> j) & 1u) ? v * kLog2e : -INFINITY;
-                            tmax = fmaxf(tmax, v);
-                            r[j] = __float_as_uint(v);
-                        }
+                    for (int j = 0; j < 32; j++) {
+                        const float v = ((keep >> j) & 1u) ? __uint_as_float(r[j]) * cmul : -INFINITY;
+                        tmax = fmaxf(tmax, v);  // NaN scores do not move the max; they reach the sum below
+                        r[j] = __float_as_uint(v);
                     }
-                    tmem_st32(tmem + kColS + lane_base + col, r);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        float v = __uint_as_float(r[j]) / p.scale_divisor;
+                        v = ((keep >> j) & 1u) ? v * kLog2e : -INFINITY;
+                        tmax = fmaxf(tmax, v);
+                        r[j] = __float_as_uint(v);
+                    }
                 }
+                tmem_st32(scol, r);
                 tmem_wait_st();
             }
             s.exch[half][row] = tmax;
@@ -380,25 +408,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
             const float m_new = fmaxf(m_run, fmaxf(tmax, s.exch[half ^ 1][row]));
             const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
             const float alpha = fast_exp2(m_run - m_safe);
-            // ---- pass 2: probabilities, their partial sum, hi/lo halves into TMEM ----
+            // ---- pass 2: probabilities, their partial sum, hi/lo halves into TMEM (P_hi over the scores), 16 keys at a time ----
             float psum = 0.f;
             if (alive) {
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
-                    uint32_t r[32], lo[32];
-                    const uint32_t col = uint32_t(half * 64 + c * 32);
-                    tmem_ld32(tmem + kColS + lane_base + col, r);
+                    uint32_t r[16], lo[16];
+                    tmem_ld16(scol + uint32_t(c * 16), r);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
+                    for (int j = 0; j < 16; j++) {
                         const float pv = fast_exp2(__uint_as_float(r[j]) - m_safe);
                         psum += pv;
                         // P_hi = pv as it is (the MMA reads only its upper 19 bits), P_lo = the 13 bits it does not see: exact, no conversion
                         r[j] = __float_as_uint(pv);
                         lo[j] = __float_as_uint(pv - __uint_as_float(__float_as_uint(pv) & 0xffffe000u));
                     }
-                    tmem_st32(tmem + kColPhi + lane_base + col, r);
-                    tmem_st32(tmem + kColPlo + lane_base + col, lo);
+                    tmem_st16(scol + uint32_t(c * 16), r);
+                    tmem_st16(tmem + kColPlo + lane_base + uint32_t(half * 32 + c * 16), lo);
                 }
                 tmem_wait_st();
                 tc_fence_before();
@@ -412,11 +439,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
             if (alive && !mbar_wait(&s.bar_o, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnO); alive = false; }
             if (alive) {
                 tc_fence_after();
-                uint32_t r[32];
-                tmem_ld32(tmem + kColO + lane_base + uint32_t(half * 32), r);
-                tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 32; j++) o[j] += __uint_as_float(r[j]);
+                for (int c = 0; c < 2; c++) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem + kColO + lane_base + uint32_t(half * 32 + c * 16), r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 16; j++) o[c * 16 + j] += __uint_as_float(r[j]);
+                }
                 tc_fence_before();
             }
             soft_sync(quarter);   // exch[] is reused by the next block (and by the final sum exchange)
@@ -438,7 +468,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
     __syncthreads();
     if (warp == 0) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
 }
 
@@ -475,7 +505,7 @@ bool attention_tc_supported(const AttnArgs& a, int gemm_mode) {
     if (gemm_mode == FXF_GEMM_FP32_SIMT) return false;
     const int Tk = a.kv ? a.Tk : a.T;
     if (a.hd != HD || Tk % 4 != 0 || Tk < 16 || a.T < 1) return false;   // V^T rows (Tk floats) must be 16-byte multiples
-    if ((Tk + BKEY - 1) / BKEY > 32) return false;   // the kernel tracks its key blocks in one 32-bit word: at most 4096 keys
+    if ((Tk + BKEY - 1) / BKEY > 64) return false;   // the kernel tracks its key blocks in one 64-bit word: at most 4096 keys
     if (a.ld_qkv % 4 != 0 || a.ld_ctx % 4 != 0 || (a.q_off | a.k_off | a.v_off) % 4 != 0) return false;
     if (a.kv && (a.ld_kv % 4 != 0 || !aligned16(a.kv))) return false;
     if (!aligned16(a.qkv) || !aligned16(a.ctx)) return false;
@@ -525,6 +555,7 @@ int launch_attention_tc(const AttnArgs& a, float* vt_scratch, ExecCtx& ctx) {
     FXF_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
         FXF_CUDA(cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        FXF_CUDA(cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, int(cudaSharedmemCarveoutMaxShared)));   // room for two CTAs
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     dim3 grid(unsigned((a.T + BQ - 1) / BQ), unsigned(BH));
