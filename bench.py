@@ -822,7 +822,7 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--precision", default="auto", choices=["auto", "fp32_simt", "fp32_3xtf32", "fp32_tf32x2_bf16", "bf16"],
+    ap.add_argument("--precision", default="auto", choices=["auto", "fp32_simt", "fp32_3xtf32", "fp32_tf32_bf16x2", "bf16"],
                     help="bf16 = optional reduced-precision mode (bf16 tensor-core products, fp32 accumulation); not the headline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the opt-in decode variants and the secondary workloads (keeps profiler captures short)")

@@ -30,8 +30,8 @@ class FxfLaunchInfo(C.Structure):
 
 GEMM_AUTO, GEMM_FP32_SIMT, GEMM_TF32X3 = 0, 1, 2
 GEMM_BF16 = 3
-GEMM_TF32X2_BF16 = 4
-GEMM_MODES = {"auto": GEMM_AUTO, "fp32_simt": GEMM_FP32_SIMT, "fp32_3xtf32": GEMM_TF32X3, "bf16": GEMM_BF16, "fp32_tf32x2_bf16": GEMM_TF32X2_BF16}
+GEMM_TF32_BF16X2 = 4
+GEMM_MODES = {"auto": GEMM_AUTO, "fp32_simt": GEMM_FP32_SIMT, "fp32_3xtf32": GEMM_TF32X3, "bf16": GEMM_BF16, "fp32_tf32_bf16x2": GEMM_TF32_BF16X2}
 
 # name -> (restype, argtypes); mirrors include/fxf_b200.h one to one
 _u32p, _i64p, _f32p = C.POINTER(C.c_uint32), C.POINTER(C.c_int64), C.POINTER(C.c_float)

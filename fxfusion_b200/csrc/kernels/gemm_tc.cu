@@ -94,12 +94,12 @@ __device__ __forceinline__ void reg_set() {   // the kernel starts with 128 regi
 }
 
 // BNB = weight rows held by this CTA: BN, or BN / 2 when two CTAs share a 256-row tile (each stages half of the weight tile)
-template <int BNB, int BK, int STAGES, bool TS, bool BF16, bool MIX = false>
+template <int BNB, int BK, int STAGES, bool TS, bool BF16>
 struct alignas(1024) TcSmem {
     float a[STAGES][BM * BK];             // x tile as TMA wrote it (fp32, swizzled rows of BK floats); x_hi in place when !TS
-    float a_lo[TS ? 1 : STAGES][TS ? 256 : BM * BK];  // x_lo twin buffers, only when the MMAs read A from shared memory
+    float a_lo[TS ? 1 : STAGES][TS ? 256 : BM * BK];  // x_lo twin buffers (mixed: bf16(x_lo) | bf16(x)), only when the MMAs read A from shared memory
     float b_hi[STAGES][BF16 ? BNB * BK / 2 : BNB * BK];   // w_hi tile (fp32), or the whole bf16 weight tile in bf16 mode
-    float b_lo[BF16 ? 1 : STAGES][BF16 ? 256 : (MIX ? BNB * BK / 2 : BNB * BK)];   // w_lo tile: fp32, or bf16 in the mixed variant
+    float b_lo[BF16 ? 1 : STAGES][BF16 ? 256 : BNB * BK];   // w_lo tile (fp32); mixed variant: bf16(w_hi) tile | bf16(w_lo) tile
     float stage_out[kEpiWarps][32 * kStagePad];   // one 32 x 16 block per epilogue warp
     uint64_t full_tma[STAGES];
     uint64_t full_b[STAGES];      // CTA pairs only: the weight halves of both CTAs have landed (the leader's copy counts)
@@ -234,12 +234,15 @@ __device__ __forceinline__ void drain_chunk(uint32_t tacc, float (&sum)[HALF]) {
 // VAR selects how the three products of a logical product are formed:
 //   0  three TF32 products, A (hi and lo) from shared memory or from tensor memory (TS)
 //   1  hybrid: x_hi read from shared memory as delivered, x_lo from tensor memory
-//   2  mixed: x_hi * w_hi and x_lo * w_hi as TF32 products against the one fp32 w_hi tile (x_hi read from shared memory as
-//      delivered, x_lo from tensor memory), and the third product x_hi * w_lo as ONE bf16 MMA (kind::f16, K = 16 per
-//      instruction): bf16(x) packed into tensor memory by the split warps, w_lo kept and fetched as bf16.  w_lo is 2^-11
-//      of w, so its bf16 rounding (and that of x beside it) costs about 2^-20 of a product, below the tensor core's own
-//      accumulation error.  What it buys: 6 instead of 8 bytes per weight element through L2 and shared memory — these
-//      kernels run at the L2 -> SM fill rate (about 42 bytes per clock and SM, measured) — and a sixth less tensor time.
+//   2  mixed: the main product x_hi * w_hi as TF32 MMAs (x as delivered in shared memory: the MMA truncates it; w_hi the
+//      fp32 tile), and BOTH correction products as bf16 MMAs (kind::f16, K = 16 per instruction): bf16(x_lo) * bf16(w_hi)
+//      and bf16(x) * bf16(w_lo).  The correction operands are 2^-11 of their products, so their bf16 rounding (2^-9) costs
+//      about 2^-20 of a product — the grade of the three-TF32 scheme, whose own accumulation truncates at that level.
+//      What it buys: a tcgen05.mma occupies the tensor pipe for the same time whatever its kind (measured: 137 cycles at
+//      N = 256, 97 at N <= 128), so 4 instead of 6 instructions per 16-deep K-slab is a third less tensor time.  Bytes
+//      through L2 and shared memory are unchanged: per weight element 4 (w_hi) + 2 (bf16 w_hi) + 2 (bf16 w_lo).
+//      With CTA pairs the bf16 copies of x_lo and x are written into shared memory by the split warps (rows of 32 bytes,
+//      32-byte swizzle, beside each other in the stage's x_lo buffer); narrower tiles pack them into tensor memory.
 template <int BN, int BK, int STAGES, bool TS, bool BF16, int VAR, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_whi,
@@ -249,11 +252,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     static_assert(!BF16 || (TS && BK == 32), "the bf16 mode takes A from tensor memory with 32-float slabs");
     constexpr bool HYB = VAR == 1, MIX = VAR == 2;
     static_assert(!HYB || (TS && !BF16), "hybrid: x_hi is the raw tile in shared memory, x_lo goes to tensor memory");
-    static_assert(!MIX || (TS && !BF16 && BK == 16), "mixed: x_lo and bf16(x) go to tensor memory, 16-deep slabs (one bf16 MMA each)");
+    static_assert(!MIX || (!BF16 && BK == 16 && (TS != PAIR)), "mixed: 16-deep slabs (one bf16 MMA per correction); A in shared memory for CTA pairs, in tensor memory otherwise");
     static_assert(BN % 32 == 0, "tile width must be a multiple of 32 columns (16 per column half and staging step)");
     static_assert(!PAIR || (!BF16 && VAR != 1), "CTA pairs exist for the plain 3xTF32 and the mixed variants");
     constexpr int BNB = PAIR ? BN / 2 : BN;   // weight rows staged by this CTA
-    using Smem = TcSmem<BNB, BK, STAGES, TS, BF16, VAR == 2>;
+    using Smem = TcSmem<BNB, BK, STAGES, TS, BF16>;
     using Regs = RegBudget<BN, BK, TS, BF16>;
     Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -263,11 +266,12 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     const int chunk = p.chunk_slabs > 0 ? p.chunk_slabs : num_k;
     const int rank = PAIR ? int(cluster_ctarank()) : 0;     // position inside the CTA pair; rank 0 issues the MMAs
     const int sched_id = PAIR ? int(blockIdx.x >> 1) : int(blockIdx.x), sched_n = PAIR ? int(gridDim.x >> 1) : int(gridDim.x);
-    constexpr uint32_t kBBytes = BF16 ? uint32_t(BNB * BK) * 2u : (VAR == 2 ? uint32_t(BNB * BK) * 6u : uint32_t(2 * BNB * BK) * 4u);   // weight bytes per stage and CTA
+    constexpr uint32_t kBBytes = BF16 ? uint32_t(BNB * BK) * 2u : uint32_t(2 * BNB * BK) * 4u;   // weight bytes per stage and CTA (mixed: fp32 w_hi + two bf16 tiles)
     constexpr uint32_t kABytes = uint32_t(BM * BK) * 4u;
     constexpr uint32_t kStageBytes = kABytes + kBBytes;
     constexpr uint32_t kIdesc = BF16 ? umma_idesc_bf16(BM, BN) : umma_idesc_tf32(PAIR ? 2 * BM : BM, BN);
-    constexpr int kACols = BF16 ? BK / 2 : (MIX ? BK + BK / 2 : (HYB ? BK : 2 * BK));   // TMEM columns of one A stage (mixed: x_lo | bf16(x))
+    constexpr int kACols = BF16 ? BK / 2 : (MIX ? BK : (HYB ? BK : 2 * BK));   // TMEM columns of one A stage (mixed: bf16(x_lo) | bf16(x), 8 columns each)
+    constexpr int kBfTileBytes = BNB * BK * 2;   // one bf16 weight tile of the mixed variant
     constexpr uint32_t kIdescBf = umma_idesc_bf16(PAIR ? 2 * BM : BM, BN);   // the bf16 product of the mixed variant
     constexpr uint32_t kColA = uint32_t(ACC * BN);             // first TMEM column of the A stages
     constexpr uint32_t kColsUsed = kColA + (TS ? uint32_t(STAGES * kACols) : 0u);
@@ -328,7 +332,13 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                             tma_load_2d(s.a[st], &map_x, k * BK, tm * BM, &s.full_tma[st]);
                             if (rank == 0) mbar_expect_tx(&s.full_b[st], 2 * kBBytes);
                             tma_load_2d_pair(s.b_hi[st], &map_whi, k * BK, tn * BN + rank * BNB, &s.full_b[st]);
-                            tma_load_2d_pair(s.b_lo[BF16 ? 0 : st], &map_wlo, k * BK, tn * BN + rank * BNB, &s.full_b[st]);
+                            if (MIX) {   // rows [0, N) of the bf16 matrix are bf16(w_hi), rows [N, 2N) bf16(w_lo)
+                                char* bl = reinterpret_cast<char*>(s.b_lo[BF16 ? 0 : st]);
+                                tma_load_2d_pair(bl, &map_wlo, k * BK, tn * BN + rank * BNB, &s.full_b[st]);
+                                tma_load_2d_pair(bl + kBfTileBytes, &map_wlo, k * BK, int(p.N) + tn * BN + rank * BNB, &s.full_b[st]);
+                            } else {
+                                tma_load_2d_pair(s.b_lo[BF16 ? 0 : st], &map_wlo, k * BK, tn * BN + rank * BNB, &s.full_b[st]);
+                            }
                             continue;
                         }
                         if (p.cv.enabled) {
@@ -343,7 +353,13 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                             tma_load_2d(s.a[st], &map_x, k * BK, tm * BM, &s.full_tma[st]);
                         }
                         tma_load_2d(s.b_hi[st], &map_whi, k * BK, tn * BN, &s.full_tma[st]);
-                        if (!BF16) tma_load_2d(s.b_lo[BF16 ? 0 : st], &map_wlo, k * BK, tn * BN, &s.full_tma[st]);   // fp32 w_lo, or bf16 w_lo (mixed)
+                        if (MIX) {
+                            char* bl = reinterpret_cast<char*>(s.b_lo[BF16 ? 0 : st]);
+                            tma_load_2d(bl, &map_wlo, k * BK, tn * BN, &s.full_tma[st]);                              // bf16(w_hi)
+                            tma_load_2d(bl + kBfTileBytes, &map_wlo, k * BK, int(p.N) + tn * BN, &s.full_tma[st]);    // bf16(w_lo)
+                        } else if (!BF16) {
+                            tma_load_2d(s.b_lo[BF16 ? 0 : st], &map_wlo, k * BK, tn * BN, &s.full_tma[st]);   // fp32 w_lo
+                        }
                     }
                 }
             producer_done:;
@@ -381,14 +397,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                                 // weight half of each CTA at the same shared-memory offset
                                 const uint64_t pb_hi = umma_desc_k_major<BK>(smem_u32(s.b_hi[st])), pb_lo = umma_desc_k_major<BK>(smem_u32(s.b_lo[BF16 ? 0 : st]));
                                 if (MIX) {
+                                    // bf16(x_lo) * bf16(w_hi) and bf16(x) * bf16(w_lo): one 16-deep bf16 MMA each, all operands in shared
+                                    // memory; then x_hi * w_hi as two 8-deep TF32 MMAs on the raw tiles
                                     const uint64_t a_raw = umma_desc_k_major<BK>(smem_u32(s.a[st]));
-                                    const uint32_t a_lo = tmem_base + kColA + uint32_t(st * kACols), a_bf = a_lo + uint32_t(BK);
-                                    const uint64_t wlb = umma_desc_k_major_bytes<BK * 2>(smem_u32(s.b_lo[BF16 ? 0 : st]));
-                                    umma_bf16_ts_pair(tmem_acc, a_bf, wlb, kIdescBf, k > kc0 ? 1u : 0u);
+                                    const uint32_t al = smem_u32(s.a_lo[TS ? 0 : st]), bl = smem_u32(s.b_lo[BF16 ? 0 : st]);
+                                    umma_bf16_pair(tmem_acc, umma_desc_k_major_bytes<BK * 2>(al), umma_desc_k_major_bytes<BK * 2>(bl), kIdescBf, k > kc0 ? 1u : 0u);
+                                    umma_bf16_pair(tmem_acc, umma_desc_k_major_bytes<BK * 2>(al + uint32_t(BM * BK * 2)), umma_desc_k_major_bytes<BK * 2>(bl + uint32_t(kBfTileBytes)), kIdescBf, 1u);
 #pragma unroll
                                     for (int kk = 0; kk < BK / 8; kk++) {
                                         const uint64_t adv = uint64_t((kk * 8 * 4) >> 4);
-                                        umma_tf32_ts_pair(tmem_acc, a_lo + uint32_t(kk * 8), pb_hi + adv, kIdesc, 1u);
                                         umma_tf32_pair(tmem_acc, a_raw + adv, pb_hi + adv, kIdesc, 1u);
                                     }
                                 } else if (TS) {
@@ -424,16 +441,16 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                             }
                             uint64_t b_hi = umma_desc_k_major<BK>(smem_u32(s.b_hi[st])), b_lo = umma_desc_k_major<BK>(smem_u32(s.b_lo[BF16 ? 0 : st]));
                             if (MIX) {
-                                // x_hi * w_lo: bf16(x) * bf16(w_lo), one 16-deep bf16 MMA; then per 8-deep step x_lo * w_hi (A from tensor
-                                // memory) and x_hi * w_hi (x as delivered in shared memory: the MMA truncates it to TF32)
+                                // bf16(x_lo) * bf16(w_hi) and bf16(x) * bf16(w_lo), one 16-deep bf16 MMA each (A from tensor memory); then
+                                // x_hi * w_hi per 8-deep step (x as delivered in shared memory: the MMA truncates it to TF32)
                                 const uint64_t a_raw = umma_desc_k_major<BK>(smem_u32(s.a[st]));
-                                const uint32_t a_lo = tmem_base + kColA + uint32_t(st * kACols), a_bf = a_lo + uint32_t(BK);   // [x_lo fp32: 16 columns | bf16(x): 8 columns]
-                                const uint64_t wlb = umma_desc_k_major_bytes<BK * 2>(smem_u32(s.b_lo[BF16 ? 0 : st]));
-                                umma_bf16_ts(tmem_acc, a_bf, wlb, kIdescBf, k > kc0 ? 1u : 0u);
+                                const uint32_t a_lb = tmem_base + kColA + uint32_t(st * kACols), a_bf = a_lb + uint32_t(BK / 2);   // [bf16(x_lo): 8 columns | bf16(x): 8 columns]
+                                const uint32_t bl = smem_u32(s.b_lo[BF16 ? 0 : st]);
+                                umma_bf16_ts(tmem_acc, a_lb, umma_desc_k_major_bytes<BK * 2>(bl), kIdescBf, k > kc0 ? 1u : 0u);
+                                umma_bf16_ts(tmem_acc, a_bf, umma_desc_k_major_bytes<BK * 2>(bl + uint32_t(kBfTileBytes)), kIdescBf, 1u);
 #pragma unroll
                                 for (int kk = 0; kk < BK / 8; kk++) {
                                     const uint64_t adv = uint64_t((kk * 8 * 4) >> 4);
-                                    umma_tf32_ts(tmem_acc, a_lo + uint32_t(kk * 8), b_hi + adv, kIdesc, 1u);
                                     umma_tf32(tmem_acc, a_raw + adv, b_hi + adv, kIdesc, 1u);
                                 }
                             } else if (HYB) {
@@ -511,22 +528,19 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         continue;
                     }
                     if (MIX) {
-                        // what the TF32 truncation of x drops (fp32, 16 columns) and the row's 16 floats as 8 packed bf16 pairs
-                        // (element k in the low half of word k/2)
-                        uint32_t lo16[16], packed[8];
+                        // what the TF32 truncation of x drops, and x itself, each as 8 packed bf16 pairs (element k in the low half
+                        // of word k/2): columns [0, 8) and [8, 16) of the stage
+                        uint32_t packed[16];
 #pragma unroll
                         for (int c = 0; c < 4; c++) {
                             const float4 v = src[c ^ sw];
-                            lo16[4 * c + 0] = __float_as_uint(lo_of_truncated(v.x));
-                            lo16[4 * c + 1] = __float_as_uint(lo_of_truncated(v.y));
-                            lo16[4 * c + 2] = __float_as_uint(lo_of_truncated(v.z));
-                            lo16[4 * c + 3] = __float_as_uint(lo_of_truncated(v.w));
-                            packed[2 * c + 0] = pack_bf16x2(v.x, v.y);
-                            packed[2 * c + 1] = pack_bf16x2(v.z, v.w);
+                            packed[2 * c + 0] = pack_bf16x2(lo_of_truncated(v.x), lo_of_truncated(v.y));
+                            packed[2 * c + 1] = pack_bf16x2(lo_of_truncated(v.z), lo_of_truncated(v.w));
+                            packed[8 + 2 * c + 0] = pack_bf16x2(v.x, v.y);
+                            packed[8 + 2 * c + 1] = pack_bf16x2(v.z, v.w);
                         }
                         const uint32_t a_col = tmem_base + lane_base + kColA + uint32_t(st * kACols);
-                        tmem_st16(a_col, lo16);
-                        tmem_st8(a_col + uint32_t(BK), packed);
+                        tmem_st16(a_col, packed);
                         tmem_wait_st();
                         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                         __syncwarp();
@@ -593,14 +607,33 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     // (x truncated to TF32); only x_lo = tf32(x - trunc(x)) has to be written.
                     const float4* hi = reinterpret_cast<const float4*>(s.a[st]);
                     float4* lo = reinterpret_cast<float4*>(s.a_lo[st]);
+                    if (MIX) {
+                        // bf16(x_lo) and bf16(x) tiles, [128 rows x 16] bf16 = rows of 32 bytes with the 32-byte swizzle the MMA
+                        // descriptor names (16-byte chunk j of row r lies at chunk j ^ ((r >> 2) & 1)), one behind the other
+                        char* lob = reinterpret_cast<char*>(s.a_lo[st]);
 #pragma unroll
-                    for (int i = 0; i < (BM * BK / 4) / 128; i++) {
-                        float4 v = hi[t + i * 128], l;
-                        l.x = lo_of_truncated(v.x);
-                        l.y = lo_of_truncated(v.y);
-                        l.z = lo_of_truncated(v.z);
-                        l.w = lo_of_truncated(v.w);
-                        lo[t + i * 128] = l;
+                        for (int i = 0; i < (BM * BK / 4) / 128; i++) {
+                            const int f = t + i * 128, row = f >> 2, c_log = (f & 3) ^ ((row >> 1) & 3);   // 64-byte rows of x: chunk ^ bits 1-2 of the row
+                            const float4 v = hi[f];
+                            uint2 pl, px;
+                            pl.x = pack_bf16x2(lo_of_truncated(v.x), lo_of_truncated(v.y));
+                            pl.y = pack_bf16x2(lo_of_truncated(v.z), lo_of_truncated(v.w));
+                            px.x = pack_bf16x2(v.x, v.y);
+                            px.y = pack_bf16x2(v.z, v.w);
+                            const int dst = row * 32 + (((c_log >> 1) ^ ((row >> 2) & 1)) << 4) + ((c_log & 1) << 3);
+                            *reinterpret_cast<uint2*>(lob + dst) = pl;
+                            *reinterpret_cast<uint2*>(lob + BM * BK * 2 + dst) = px;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < (BM * BK / 4) / 128; i++) {
+                            float4 v = hi[t + i * 128], l;
+                            l.x = lo_of_truncated(v.x);
+                            l.y = lo_of_truncated(v.y);
+                            l.z = lo_of_truncated(v.z);
+                            l.w = lo_of_truncated(v.w);
+                            lo[t + i * 128] = l;
+                        }
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA (async proxy)
                     __syncwarp();
@@ -912,10 +945,10 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
         if (make_map_bf16(&mhi, a.w_hi, a.N, a.K, a.K, BN, BK)) return 1;
         mlo = mhi;
     } else if (VAR == 2) {
-        // mixed: w_lo points to bf16(w - w_hi), an [N, K] bf16 matrix
+        // mixed: w_lo points to a [2N, K] bf16 matrix, rows [0, N) = bf16(w_hi), rows [N, 2N) = bf16(w - w_hi)
         FXF_CHECK(a.w_mixed, "the mixed GEMM variant needs weights prepared for it");
         if (make_map(&mhi, a.w_hi, a.N, a.K, a.K, BNB, BK)) return 1;
-        if (make_map_bf16(&mlo, a.w_lo, a.N, a.K, a.K, BNB, BK)) return 1;
+        if (make_map_bf16(&mlo, a.w_lo, 2 * a.N, a.K, a.K, BNB, BK)) return 1;
     } else {
         FXF_CHECK(!a.w_mixed, "weights prepared for the mixed GEMM variant cannot feed the 3xTF32 kernels");
         if (make_map(&mhi, a.w_hi, a.N, a.K, a.K, BNB, BK)) return 1;
@@ -950,7 +983,7 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
     // walk tiles so that the operand that does not fit in L2 is the one reused by concurrent CTAs
     p.m_fastest = a.N > a.M ? 1 : 0;
     p.status = ctx.status;
-    size_t smem = sizeof(TcSmem<BNB, BK, STAGES, TS, BF16, VAR == 2>) + 1024;
+    size_t smem = sizeof(TcSmem<BNB, BK, STAGES, TS, BF16>) + 1024;
     static bool configured[64] = {};
     int dev = 0;
     FXF_CUDA(cudaGetDevice(&dev));
@@ -1072,32 +1105,20 @@ const char* gemm_tc_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool 
     }
 }
 
-// Tile width of the mixed variant (two TF32 products + one bf16 product): 192, 128 or 64 — x_lo and bf16(x) live in tensor
-// memory (24 columns per stage), which two 256-column accumulators would fill.  Same time model as gemm_tc_pick_bn.
-const char* gemm_tc_mixed_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool k_split, bool few_rows, int* bn_out) {
-    int bn = 128;
-    if (N <= 64) bn = 64;
-    else if (N <= 128 || (few_rows && M < 64)) bn = 128;
-    else {
-        const int64_t tiles_m = (M + BM - 1) / BM;
-        const int cand[2] = {192, 128};
-        const double penalty[2] = {1.0, 1.12};   // time per flop relative to the widest tile
-        double best_cost = 0;
-        for (int i = 0; i < 2; i++) {
-            const int64_t tiles = tiles_m * ((N + cand[i] - 1) / cand[i]);
-            const TailSplit t = plan_tail(tiles, K, cand[i], sm_count, k_split);
-            const double cost = (double(t.full / sm_count) * t.tile_us + t.tail_us) * penalty[i];
-            if (i == 0 || cost < best_cost * 0.97) {
-                bn = cand[i];
-                best_cost = cost;
-            }
-        }
-    }
-    if (bn_out) *bn_out = bn;
+// Variant of the mixed arithmetic (one TF32 product + two bf16 corrections): the dispatch rule of the 3xTF32 kernels, with
+// the 256- and 224-wide single-CTA tiles (whose A operand would not fit beside two accumulators in tensor memory) mapped to
+// 192-wide ones.
+const char* gemm_tc_mixed_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool k_split, bool few_rows, int* bn_out, bool pairs) {
+    int bn = 0;
+    gemm_tc_variant(M, N, K, sm_count, k_split, few_rows, &bn, false);
+    const bool pair = pairs && M > BM && sm_count >= 2 && bn >= 224;
+    if (!pair && bn > 192) bn = 192;
+    if (bn_out) *bn_out = pair ? 256 : bn;
+    if (pair) return "tcgen05-tf32+2bf16-256x256-pair-smemA";
     switch (bn) {
-        case 192: return "tcgen05-tf32x2+bf16-128x192";
-        case 128: return "tcgen05-tf32x2+bf16-128x128";
-        default: return "tcgen05-tf32x2+bf16-128x64";
+        case 192: return "tcgen05-tf32+2bf16-128x192-tmemA";
+        case 128: return "tcgen05-tf32+2bf16-128x128-tmemA";
+        default: return "tcgen05-tf32+2bf16-128x64-tmemA";
     }
 }
 
@@ -1105,8 +1126,9 @@ int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows) {
     FXF_CHECK(gemm_tc_supported(a, allow_few_rows), "tensor-core GEMM called with an unsupported problem");
     int bn = 0;
     if (a.w_mixed) {
-        gemm_tc_mixed_variant(a.M, a.N, a.K, ctx.sm_count, ctx.gemm_ws != nullptr, allow_few_rows, &bn);
+        gemm_tc_mixed_variant(a.M, a.N, a.K, ctx.sm_count, ctx.gemm_ws != nullptr, allow_few_rows, &bn, ctx.tc_pair != 1);
         switch (bn) {
+            case 256: return launch_tc<256, 16, 6, false, false, 2, true>(a, ctx);
             case 192: return launch_tc<192, 16, 5, true, false, 2>(a, ctx);
             case 128: return launch_tc<128, 16, 8, true, false, 2>(a, ctx);
             default: return launch_tc<64, 16, 8, true, false, 2>(a, ctx);
@@ -1258,7 +1280,8 @@ __global__ void __launch_bounds__(256) split_mixed_kernel(const float* __restric
         float h, l;
         split_tf32(w[i], h, l);   // h = tf32(w) rounded to nearest; the low part is taken exactly below
         hi[i] = h;
-        lo_bf[i] = uint16_t(pack_bf16x2(w[i] - h, 0.f) & 0xffffu);
+        lo_bf[i] = uint16_t(pack_bf16x2(h, 0.f) & 0xffffu);              // rows [0, N): bf16(w_hi)
+        lo_bf[n + i] = uint16_t(pack_bf16x2(w[i] - h, 0.f) & 0xffffu);   // rows [N, 2N): bf16(w - w_hi)
         (void)l;
     }
 }

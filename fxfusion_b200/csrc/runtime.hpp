@@ -262,7 +262,7 @@ struct GemmArgs {
     const float* w_hi = nullptr;
     const float* w_lo = nullptr;
     bool w_is_bf16 = false;   // bf16 mode: w_hi points to the weight as bf16 [N,K] (w_lo unused)
-    bool w_mixed = false;     // mixed mode: w_hi is the TF32 high part (fp32), w_lo points to bf16(w - w_hi) [N,K]
+    bool w_mixed = false;     // mixed mode: w_hi is the TF32 high part (fp32), w_lo points to a bf16 matrix [2N,K]: bf16(w_hi) rows, then bf16(w - w_hi) rows
     const float* bias = nullptr;
     const float* residual = nullptr;   // optional [M,N] with the pitch of `out`, added after the bias and before the ReLU
     float* out = nullptr;
@@ -287,9 +287,9 @@ bool gemm_tc_shape_ok(int64_t M, int64_t N, int64_t K);
 int gemm_tc_pick_bn(int64_t M, int64_t N, int sm_count, int64_t K = 0);
 // Name of the tensor-core kernel variant launch_gemm_tc takes for a problem (and its tile width): the one dispatch rule.
 const char* gemm_tc_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool k_split, bool few_rows, int* bn_out, bool pairs = true);
-const char* gemm_tc_mixed_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool k_split, bool few_rows, int* bn_out);
+const char* gemm_tc_mixed_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool k_split, bool few_rows, int* bn_out, bool pairs = true);
 int launch_split_tf32(const float* w, float* hi, float* lo, int64_t n, ExecCtx& ctx);
-// mixed mode: hi = tf32(w) as fp32 [n], lo_bf16 = bf16(w - hi) [n]
+// mixed mode: hi = tf32(w) as fp32 [n], lo_bf16 = bf16(hi) [n] followed by bf16(w - hi) [n]
 int launch_split_mixed(const float* w, float* hi, void* lo_bf16, int64_t n, ExecCtx& ctx);
 int simt_tile_choice(int64_t M, int64_t N, int sm_count);
 std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count, bool pairs = true);

@@ -66,11 +66,11 @@ enum {
     FXF_GEMM_BF16 = 3,      /* optional reduced-precision mode: weights and activations rounded to bf16 for the tensor-core
                                products (one product per logical product), fp32 accumulation and fp32 tensors everywhere
                                else; results within about 1e-2 relative of the fp32 path, decode tokens may differ */
-    FXF_GEMM_TF32X2_BF16 = 4 /* fp32-grade like FXF_GEMM_TF32X3, with the split's third product computed as a bf16 tensor-core
-                               product (x = x_hi + x_lo, w = w_hi + w_lo: x_hi*w_hi and x_lo*w_hi in TF32, x_hi*w_lo in
-                               bf16): w_lo is 2^-11 of w, so its bf16 rounding costs about 2^-20 of a product, and it is
-                               stored and fetched in 2 bytes instead of 4 — a quarter less operand traffic, which is what
-                               bounds these kernels */
+    FXF_GEMM_TF32_BF16X2 = 4 /* fp32-grade like FXF_GEMM_TF32X3 (x = x_hi + x_lo, w = w_hi + w_lo): the main product
+                               x_hi*w_hi in TF32, both correction products bf16(x_lo)*bf16(w_hi) and bf16(x)*bf16(w_lo) as
+                               bf16 tensor-core products with fp32 accumulation.  The corrections are 2^-11 of a product, so
+                               their bf16 rounding costs about 2^-20 of it.  Four tensor-core instructions per 16 K-elements
+                               instead of six (an instruction takes the same time whatever its kind) */
 };
 
 typedef struct FxfEngineOptions {

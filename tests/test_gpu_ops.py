@@ -104,13 +104,16 @@ def test_linear_variants_without_cta_pairs(built_lib, tmp_path, M, N, K, arm):
     eng.close()
 
 
-@pytest.mark.parametrize("M,N,K,arm", [(8192, 3072, 768, "128x192"), (1024, 768, 768, "128x128"), (300, 700, 264, "128x128"), (1024, 64, 256, "128x64"),
-                                       (2048, 50257, 768, "128x192"), (512, 200, 4096, "128x128")])
-def test_linear_mixed_tf32_bf16_mode(built_lib, tmp_path, M, N, K, arm):
-    """Optional mode fp32_tf32x2_bf16: x_hi*w_hi and x_lo*w_hi as TF32 products, x_hi*w_lo as one bf16 product (w_lo kept in
-    bf16).  It is held to the same 1e-4 / 1e-3 rule as the 3xTF32 mode."""
-    eng, w, bias = _linear_engine(M, N, K, tmp_path, precision="fp32_tf32x2_bf16")
-    assert "tcgen05-tf32x2+bf16-" + arm in eng.describe()
+@pytest.mark.parametrize("M,N,K,arm,options", [
+    (8192, 3072, 768, "256x256-pair", {}), (8192, 768, 3072, "256x256-pair", {}), (2048, 50257, 768, "256x256-pair", {}),
+    (8192, 3072, 768, "128x192", {"tc_pair": 1}), (1024, 768, 768, "128x128", {}), (300, 700, 264, "128x128", {}), (1024, 64, 256, "128x64", {}),
+    (2048, 50257, 768, "128x192", {"tc_pair": 1}), (512, 200, 4096, "128x128", {}), (8192, 768, 768, "128x192", {})])
+def test_linear_mixed_tf32_bf16_mode(built_lib, tmp_path, M, N, K, arm, options):
+    """Mode fp32_tf32_bf16x2: x_hi*w_hi as TF32 products, the corrections bf16(x_lo)*bf16(w_hi) and bf16(x)*bf16(w_lo) as one
+    bf16 product each per 16 K-elements — with CTA pairs (operands in shared memory) and without (A in tensor memory).  It
+    is held to the same 1e-4 / 1e-3 rule as the 3xTF32 mode."""
+    eng, w, bias = _linear_engine(M, N, K, tmp_path, precision="fp32_tf32_bf16x2", **options)
+    assert "tcgen05-tf32+2bf16-" + arm in eng.describe(), eng.describe()
     x = rnd(M, K)
     got = eng.run([x.cuda()])[0].cpu()
     want = torch.zeros(M, N)
