@@ -45,7 +45,8 @@ B, T, PROMPT = 32, 256, 128
 METRIC = "gpt2_small_greedy_decode_tokens_per_s"
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel's launches in ONE forward of this
 # workload on one GPU, summed over an ncu capture of a forward; bench.py cannot run ncu itself.
-NCU_DRAM_BYTES_PER_FORWARD = {"gemm_tf32x3_tcgen05": (7035996416, 49)}
+NCU_DRAM_BYTES_PER_FORWARD = {"gemm_tf32x3_tcgen05": (7035996416, 49)}   # fp32_3xtf32; the default arithmetic moves the same bytes
+NCU_DRAM_BYTES_PER_FORWARD["gemm_tf32_bf16x2_tcgen05"] = NCU_DRAM_BYTES_PER_FORWARD["gemm_tf32x3_tcgen05"]
 CPU_BUDGET_S = 150.0  # wall-clock budget of a CPU arm; the per-step batch is sized to fit it
 NVLINK_GBS_PER_DIRECTION = 770.0  # measured peer copy on this pool's B200s (nominal 900)
 
@@ -272,6 +273,11 @@ def measure_tf32_peak(device_index: int):
         torch.backends.cuda.matmul.allow_tf32 = old
 
 
+def tf32_slots(kernel_name: str) -> float:
+    """TF32-instruction-equivalents of tensor-core time per fp32 product of a kernel's arithmetic."""
+    return 2.0 if "tf32_bf16x2" in kernel_name else 3.0
+
+
 def kernel_table(trace, precision: str, peaks, tf32_peak):
     by = {}
     for r in trace:
@@ -281,20 +287,21 @@ def kernel_table(trace, precision: str, peaks, tf32_peak):
     kernels = {k: {"launches": v["n"], "ms": round(v["ms"], 4), "share": round(v["ms"] / total_ms, 4),
                    "tflops": round(v["flops"] / (v["ms"] * 1e-3) / 1e12, 3) if v["ms"] > 0 else None,
                    "gbs": round(v["bytes"] / (v["ms"] * 1e-3) / 1e9, 1) if v["ms"] > 0 else None} for k, v in sorted(by.items(), key=lambda kv: -kv[1]["ms"])}
-    # per-kernel fraction of its own roofline: tensor-core kernels against the ceiling of their arithmetic (three TF32
-    # products per fp32 product = measured TF32 rate / 3; the measured bf16 peak in bf16 mode), exchange kernels against
+    # per-kernel fraction of its own roofline: tensor-core kernels against the ceiling of their arithmetic (the measured TF32
+    # rate / the TF32-instruction-equivalents one fp32 product costs: 3 for three TF32 products, 2 for one TF32 product + two
+    # bf16 corrections, a bf16 instruction covering twice the K of a TF32 one in the same time; the measured bf16 peak in
+    # bf16 mode), exchange kernels against
     # the NVLink rate per direction (the kernel reports the bytes that ARRIVE at a rank during the exchange: the peers' partial
     # rows it fetches plus the normalised rows the peers store into it, 2 * (n-1)/n of the activation; as many leave it),
     # every other kernel against the measured copy bandwidth
-    if precision == "bf16":
-        tensor_ceiling = peaks["bf16_tflops_sustained"]
-    elif tf32_peak:
-        tensor_ceiling = tf32_peak["tf32_tflops_sustained"] / 3.0
-    else:
-        tensor_ceiling = peaks["bf16_tflops_sustained"] / 6.0
+    def tensor_ceiling(name):
+        if "_bf16_tcgen05" in name:
+            return peaks["bf16_tflops_sustained"]
+        slots = tf32_slots(name)
+        return tf32_peak["tf32_tflops_sustained"] / slots if tf32_peak else peaks["bf16_tflops_sustained"] / (2.0 * slots)
     for k, v in kernels.items():
         if "tcgen05" in k and v["tflops"] is not None:
-            v["bound"], v["frac"] = "tensor", round(v["tflops"] / tensor_ceiling, 4)
+            v["bound"], v["frac"] = "tensor", round(v["tflops"] / tensor_ceiling(k), 4)
         elif k in ("tp_exchange_add_layernorm", "p2p_all_reduce") and v["gbs"] is not None:
             v["bound"], v["frac"] = "nvlink", round(v["gbs"] / NVLINK_GBS_PER_DIRECTION, 4)
         elif v["gbs"] is not None:
@@ -520,22 +527,25 @@ def report_c3(args, world, local, tp_size, dp_size, K, W, Ke, ms, e2e_ms, e2e_ma
         tf32_peak = measure_tf32_peak(local)
     except Exception as exc:  # noqa: BLE001
         sys.stderr.write(f"TF32 peak measurement failed: {exc}\n")
-    by, kernels, total_ms, tensor_ceiling = kernel_table(trace, args.precision, peaks, tf32_peak)
+    by, kernels, total_ms, ceiling_of = kernel_table(trace, args.precision, peaks, tf32_peak)
     top_name, top = max(by.items(), key=lambda kv_: kv_[1]["ms"])
+    tensor_ceiling = ceiling_of(top_name)
     achieved = top["flops"] / (top["ms"] * 1e-3) / 1e12
     traffic = NCU_DRAM_BYTES_PER_FORWARD.get(top_name) if tp_size == 1 else None
     step_mhz = clocks.get("sm_mhz") if clocks else None
     emulated = args.precision != "bf16"
     per_clock = None
     if emulated and tf32_peak and step_mhz and tf32_peak.get("burst_sm_mhz"):
-        per_clock = (achieved / step_mhz) / (tf32_peak["tf32_tflops_burst"] / 3.0 / tf32_peak["burst_sm_mhz"])
+        per_clock = (achieved / step_mhz) / (tf32_peak["tf32_tflops_burst"] / tf32_slots(top_name) / tf32_peak["burst_sm_mhz"])
     roofline = {"bound": "tensor", "kernel": top_name, "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": (traffic[0] / traffic[1]) if traffic and traffic[1] == top["n"] else None,
                 "algorithmic_bytes": top["bytes"] / top["n"], "peak_source": peaks["source"] + " cuBLAS bf16, sustained",
                 "launches_per_step": top["n"], "share_of_step": top["ms"] / total_ms,
-                # fp32 results from three TF32 products: the ceiling of this arithmetic is the TF32 dense rate / 3, with the TF32
-                # rate measured in this run the way the bf16 peak was (library GEMM, burst and sustained, clocks beside them)
+                # fp32 results from one TF32 product + two bf16 corrections (or three TF32 products): the ceiling of this arithmetic
+                # is the TF32 dense rate / 2 (/ 3), with the TF32 rate measured in this run the way the bf16 peak was (library
+                # GEMM, burst and sustained, clocks beside them)
                 "tf32_peak": tf32_peak,
+                "tf32_instruction_equivalents_per_fp32_product": tf32_slots(top_name) if emulated else None,
                 "fp32_emulation_ceiling": tensor_ceiling if emulated else None,
                 "frac_of_fp32_emulation_ceiling": achieved / tensor_ceiling if emulated else None,
                 # the same fraction with both sides divided by the SM clock they ran at (the library GEMM runs power-capped at a
@@ -697,16 +707,17 @@ def run_secondary(workload: str, args, device_index: int = 0, brief: bool = Fals
     eng.profile_launches()
     trace = eng.profile_launches()
     peaks = measured_peaks()
-    by, kernels, total_ms, tensor_ceiling = kernel_table(trace, args.precision, peaks, None)
+    by, kernels, total_ms, ceiling_of = kernel_table(trace, args.precision, peaks, None)
     top_name, top = max(by.items(), key=lambda kv_: kv_[1]["ms"])
     tensor = "tcgen05" in top_name
+    tensor_ceiling = ceiling_of(top_name) if tensor else None
     achieved = (top["flops"] / (top["ms"] * 1e-3) / 1e12) if tensor else (top["bytes"] / (top["ms"] * 1e-3) / 1e9)
     peak = peaks["bf16_tflops_sustained"] if tensor else peaks["hbm_gbs"]
     roofline = {"bound": "tensor" if tensor else "hbm", "kernel": top_name, "achieved": achieved, "peak": peak, "unit": "TFLOP/s" if tensor else "GB/s",
                 "frac": achieved / peak, "traffic": None, "launches_per_step": top["n"], "share_of_step": top["ms"] / total_ms,
                 "fp32_emulation_ceiling": tensor_ceiling if tensor else None,
                 "frac_of_fp32_emulation_ceiling": achieved / tensor_ceiling if tensor else None,
-                "peak_source": peaks["source"] + (" cuBLAS bf16, sustained (fp32 emulation ceiling = that / 6)" if tensor else " copy bandwidth")}
+                "peak_source": peaks["source"] + (" cuBLAS bf16, sustained (fp32 emulation ceiling = that / 6 for three TF32 products, / 4 for TF32 + two bf16 corrections)" if tensor else " copy bandwidth")}
     cpu = None if args.no_cpu_baseline else secondary_cpu(workload, budget_s=8.0 if brief else 20.0)
     status = eng.device_status()
     launches = eng.launches_per_run

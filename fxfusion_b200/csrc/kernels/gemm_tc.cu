@@ -1008,7 +1008,7 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
         tag_launch(ctx, BF16 ? "conv2d_igemm_bf16_tcgen05" : "conv2d_igemm_tf32x3_tcgen05", 2.0 * pix * double(a.N) * double(a.K),
                    4.0 * (double(cv->N) * cv->H * cv->W * cv->C + double(a.N) * a.K + double(a.N) + pix * a.N));
     } else {
-        tag_launch(ctx, BF16 ? "gemm_bf16_tcgen05" : "gemm_tf32x3_tcgen05", 2.0 * double(a.M) * double(a.N) * double(a.K),
+        tag_launch(ctx, BF16 ? "gemm_bf16_tcgen05" : (VAR == 2 ? "gemm_tf32_bf16x2_tcgen05" : "gemm_tf32x3_tcgen05"), 2.0 * double(a.M) * double(a.N) * double(a.K),
                    4.0 * (double(a.M) * a.K + double(a.N) * a.K + double(a.N) + double(a.M) * a.N));
     }
     if (PAIR) {

@@ -27,6 +27,10 @@
 
 namespace fxf {
 
+// FXF_GEMM_AUTO takes the cheapest fp32-grade arithmetic the tensor cores offer: one TF32 product plus two bf16 corrections
+// (weights whose rows are not multiples of 8 elements, and convolutions, stay with three TF32 products).
+static bool mixed_arithmetic(int gemm_mode) { return gemm_mode == FXF_GEMM_TF32_BF16X2 || gemm_mode == FXF_GEMM_AUTO; }
+
 static bool use_tc(const GemmArgs& a, int gemm_mode) {
     if (gemm_mode == FXF_GEMM_FP32_SIMT) return false;
     return gemm_tc_supported(a);
@@ -72,7 +76,7 @@ int launch_gemm(const GemmArgs& a, ExecCtx& ctx) {
 
 std::string gemm_variant_name(const GemmArgs& a, int gemm_mode, int sm_count, bool pairs) {
     if (gemm_mode == FXF_GEMM_BF16 && gemm_tc_shape_ok(a.M, a.N, a.K) && a.K % 8 == 0) return std::string("tcgen05-bf16-128x") + (a.N > 128 ? "192" : "128");
-    if (gemm_mode == FXF_GEMM_TF32_BF16X2 && gemm_tc_shape_ok(a.M, a.N, a.K) && a.K % 8 == 0) return gemm_tc_mixed_variant(a.M, a.N, a.K, sm_count, true, false, nullptr, pairs);
+    if (mixed_arithmetic(gemm_mode) && gemm_tc_shape_ok(a.M, a.N, a.K) && a.K % 8 == 0) return gemm_tc_mixed_variant(a.M, a.N, a.K, sm_count, true, false, nullptr, pairs);
     if (gemm_mode != FXF_GEMM_FP32_SIMT && gemm_tc_shape_ok(a.M, a.N, a.K)) return gemm_tc_variant(a.M, a.N, a.K, sm_count, true, false, nullptr, pairs);
     static const char* names[] = {"simt128x128", "simt64x64", "simt32x32", "skinny32x8"};
     return names[simt_tile_choice(a.M, a.N, sm_count)];
@@ -233,7 +237,7 @@ int k_linear_relu(Registry& reg, const TensorIds& in, const TensorIds& out, cons
 std::unique_ptr<NodePlan> plan_linear(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const PlanEnv& env) {
     auto p = std::make_unique<DensePlan>();
     p->bf16_mode = env.gemm_mode == FXF_GEMM_BF16;
-    p->mixed_mode = env.gemm_mode == FXF_GEMM_TF32_BF16X2;
+    p->mixed_mode = mixed_arithmetic(env.gemm_mode);
     if (in.size() < 3 || out.size() < 1) return p;
     const FxfTensor &x = reg[in[0]], &w = reg[in[1]];
     if (w.rank != 2 || x.rank < 1) return p;
@@ -314,7 +318,7 @@ int k_feedforward(Registry& reg, const TensorIds& in, const TensorIds& out, cons
 std::unique_ptr<NodePlan> plan_feedforward(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params&, const PlanEnv& env) {
     auto p = std::make_unique<DensePlan>();
     p->bf16_mode = env.gemm_mode == FXF_GEMM_BF16;
-    p->mixed_mode = env.gemm_mode == FXF_GEMM_TF32_BF16X2;
+    p->mixed_mode = mixed_arithmetic(env.gemm_mode);
     if (in.size() < 5 || out.size() < 1) return p;
     const FxfTensor &x = reg[in[0]], &w1 = reg[in[1]], &w2 = reg[in[3]];
     if (w1.rank != 2 || w2.rank != 2 || x.rank < 1) return p;
@@ -408,7 +412,7 @@ int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params
 std::unique_ptr<NodePlan> plan_mha(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& env) {
     auto pl = std::make_unique<DensePlan>();
     pl->bf16_mode = env.gemm_mode == FXF_GEMM_BF16;
-    pl->mixed_mode = env.gemm_mode == FXF_GEMM_TF32_BF16X2;
+    pl->mixed_mode = mixed_arithmetic(env.gemm_mode);
     if (in.size() < 6 || out.size() < 1 || p.ints.size() < 4 || reg[in[0]].rank != 3) return pl;
     const FxfTensor& x = reg[in[0]];
     const int64_t B = x.shape[0], T = x.shape[1], H = p.ints[0], hd = p.ints[1], D = p.ints[2], QKV = p.ints[3], M = B * T;
@@ -530,7 +534,7 @@ int k_cross_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const 
 std::unique_ptr<NodePlan> plan_cross_mha(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& env) {
     auto pl = std::make_unique<DensePlan>();
     pl->bf16_mode = env.gemm_mode == FXF_GEMM_BF16;
-    pl->mixed_mode = env.gemm_mode == FXF_GEMM_TF32_BF16X2;
+    pl->mixed_mode = mixed_arithmetic(env.gemm_mode);
     if (in.size() < 9 || out.size() < 1 || p.ints.size() < 4 || reg[in[0]].rank != 3 || reg[in[1]].rank != 3) return pl;
     const FxfTensor &x = reg[in[0]], &mem = reg[in[1]];
     const int64_t B = x.shape[0], Tq = x.shape[1], Tk = mem.shape[1], H = p.ints[0], hd = p.ints[1], D = p.ints[2], KV = p.ints[3];
@@ -733,7 +737,7 @@ int k_cached_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const
 std::unique_ptr<NodePlan> plan_cached_mha(const Registry& reg, const TensorIds& in, const TensorIds& out, const Params& p, const PlanEnv& env) {
     auto pl = std::make_unique<DensePlan>();
     pl->bf16_mode = env.gemm_mode == FXF_GEMM_BF16;
-    pl->mixed_mode = env.gemm_mode == FXF_GEMM_TF32_BF16X2;
+    pl->mixed_mode = mixed_arithmetic(env.gemm_mode);
     if (in.size() < 7 || out.size() < 1 || p.ints.size() < 5 || reg[in[0]].rank != 3 || reg[in[1]].rank != 2) return pl;
     const int64_t B = reg[in[0]].shape[0], T = reg[in[1]].shape[1], H = p.ints[0], hd = p.ints[1], D = p.ints[2], QKV = p.ints[3];
     if (H <= 0 || hd <= 0) return pl;

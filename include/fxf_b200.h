@@ -60,7 +60,8 @@ typedef struct FxfTensor {
 
 /* GEMM arithmetic used by Linear / LinearRelu / FeedForward / MHA projections. */
 enum {
-    FXF_GEMM_AUTO = 0,      /* tensor-core 3xTF32 where the shape allows it, else fp32 SIMT */
+    FXF_GEMM_AUTO = 0,      /* fp32-grade on the tensor cores where the shape allows it (FXF_GEMM_TF32_BF16X2 for dense layers
+                               whose K is a multiple of 8, FXF_GEMM_TF32X3 otherwise and for convolutions), else fp32 SIMT */
     FXF_GEMM_FP32_SIMT = 1, /* fp32 FFMA tiles only */
     FXF_GEMM_TF32X3 = 2,    /* tcgen05 kind::tf32 with hi/lo operand split (fp32-grade result) */
     FXF_GEMM_BF16 = 3,      /* optional reduced-precision mode: weights and activations rounded to bf16 for the tensor-core

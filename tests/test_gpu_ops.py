@@ -63,12 +63,15 @@ TC_SHAPES = [
 
 @pytest.mark.parametrize("M,N,K,arm", TC_SHAPES)
 @pytest.mark.parametrize("relu", [False, True])
-def test_linear_tensor_core(built_lib, M, N, K, arm, relu):
-    """The tcgen05 3xTF32 GEMM itself (precision "auto"), every variant, against the reference CPU kernel."""
+@pytest.mark.parametrize("precision", ["auto", "fp32_3xtf32"])
+def test_linear_tensor_core(built_lib, M, N, K, arm, relu, precision):
+    """The tcgen05 GEMM itself, every variant, against the reference CPU kernel, in both fp32-grade arithmetics: three TF32
+    products ("fp32_3xtf32") and one TF32 product + two bf16 corrections, which "auto" takes whenever K is a multiple of 8."""
     from fxfusion_b200.kernels import gemm_variant
-    assert gemm_variant(M, N, K) == "tcgen05-tf32x3-" + arm
+    mixed = precision == "auto" and K % 8 == 0
+    assert gemm_variant(M, N, K, precision) == ("tcgen05-tf32+2bf16-" if mixed else "tcgen05-tf32x3-") + arm
     x, w, b = rnd(M, K), rnd(N, K, seed=1, scale=1 / math.sqrt(K)), rnd(N, seed=2)
-    both("LinearRelu" if relu else "Linear", [x, w, b, torch.zeros(M, N)], [0, 1, 2], [3], precision="auto")
+    both("LinearRelu" if relu else "Linear", [x, w, b, torch.zeros(M, N)], [0, 1, 2], [3], precision=precision)
 
 
 def _linear_engine(M, N, K, tmp_path, relu=False, **options):
@@ -92,7 +95,7 @@ def _linear_engine(M, N, K, tmp_path, relu=False, **options):
 def test_linear_variants_without_cta_pairs(built_lib, tmp_path, M, N, K, arm):
     """Engine option tc_pair = 1: the widest tiles are computed by single CTAs (256-wide with A in shared memory, and the
     224-wide hybrid the time model picks for very wide outputs) — the variants convolutions and pair-less engines use."""
-    eng, w, bias = _linear_engine(M, N, K, tmp_path, relu=True, tc_pair=1)
+    eng, w, bias = _linear_engine(M, N, K, tmp_path, relu=True, tc_pair=1, precision="fp32_3xtf32")
     assert "tcgen05-tf32x3-" + arm in eng.describe()
     x = rnd(M, K)
     got = eng.run([x.cuda()])[0].cpu()
