@@ -1,6 +1,8 @@
 // Tensor-core attention core for head_dim 64 on sm_100a:
 //     ctx = softmax(mask_fill(Q·K^T / scale_divisor)) · V        per (batch, head)
-// with both contractions on tcgen05 (kind::tf32, three products per logical product, fp32-grade).
+// with both contractions on tcgen05, fp32-grade: per fp32 product one TF32 product of the high parts plus two bf16
+// correction products (bf16(a_lo)·bf16(b) and bf16(a)·bf16(b_lo), fp32 accumulation) — 32 tensor-core instructions per
+// block of 64 keys where three TF32 products would take 48; an instruction costs the same whatever its kind.
 // Same semantics as attention.cu (reference csrc/kernels/cpu/mha.cpp:38-49): division by the scale,
 // -inf where mask == 0, fully masked rows give NaN, masked keys still enter P·V with weight 0 (so a
 // non-finite V row poisons the output as 0 * inf does in the reference).  A block of 64 keys is skipped
@@ -15,19 +17,19 @@
 //                    TMA -> split -> S-MMA -> softmax -> P·V-MMA of a block as one dependent chain, so a second resident
 //                    CTA is what keeps the tensor pipe and the softmax threads of an SM busy at the same time.  Per CTA
 //                    106 KB of shared memory and 256 of the 512 tensor-memory columns:
-//                        S [128x64] (P_hi overwrites it in place) | P_lo [128x64] | O [128x64] | Q_lo [128x64].
+//                        S [128x64] (P_hi overwrites it in place) | bf16(P_lo), bf16(P) | O [128x64] | bf16(Q_lo), bf16(Q).
 //       warp 0, lane 0  TMA loads (Q and K tiles straight out of qkv through a 3-D tensor map, V^T
 //                       tiles from the transposed copy; zero fill beyond T) and all MMAs:
-//                       S = Q·K_blk^T (q_lo from tensor memory, q_hi / k_hi / k_lo from shared memory),
+//                       S = Q·K_blk^T (main product on the fp32 tiles as delivered, corrections with A from tensor memory),
 //                       O_blk = P·V_blk with P read from tensor memory.
-//       warps 1-3       write the TF32 "lo" twin of every landed K / V tile (the tile itself serves as "hi": the MMA
-//                       ignores the 13 low mantissa bits), so the softmax threads never wait for operands;
+//       warps 1-3       write the bf16 copies (x and x_lo) of every landed K / V tile, so the softmax threads never wait
+//                       for operands;
 //       warps 4-11      softmax, two threads per query row, each owning 32 of the block's 64 keys and 32 of the 64
-//                       output columns: first the "lo" twin of their half row of Q into tensor memory; per block
+//                       output columns: first the bf16 copies of their half row of Q into tensor memory; per block
 //                       tcgen05.ld of S, scale, mask (staged through shared memory so the global reads are
-//                       coalesced), online softmax in the log2 domain (running max m, running sum l), P split
-//                       into hi/lo and stored to TMEM; after the P·V MMA the block's O is folded into registers
-//                       (o = o*alpha + O_blk).
+//                       coalesced), online softmax in the log2 domain (running max m, running sum l), P as fp32
+//                       (over S) and as two bf16 copies into TMEM; after the P·V MMA the block's O is folded into
+//                       registers (o = o*alpha + O_blk).
 //       Registers: the kernel starts with 80 per thread (384 threads x 2 CTAs); setmaxnreg moves warps 0-3 to 48 and
 //       the softmax warps to 96.
 // Waits are bounded; on expiry the CTA records an error code in the status word and leaves.
@@ -93,9 +95,11 @@ __global__ void __launch_bounds__(256) attn_vt_kernel(const float* __restrict__ 
 
 // ---- main kernel -------------------------------------------------------------------------------------
 struct alignas(1024) AttnTcSmem {
-    float q_hi[2][BQ * 32];                        // two 32-wide slabs of head_dim (the "lo" twin of Q lives in tensor memory)
-    float k_hi[2][BKEY * 32], k_lo[2][BKEY * 32];
-    float v_hi[2][HD * 32], v_lo[2][HD * 32];      // two 32-key slabs of V^T [64 x 32]
+    float q_hi[2][BQ * 32];                        // two 32-wide slabs of head_dim (the bf16 copies of Q live in tensor memory)
+    float k_hi[2][BKEY * 32];                      // K block as delivered: two 32-wide slabs of head_dim
+    uint16_t k_bf[BKEY * HD], k_lo_bf[BKEY * HD];  // bf16(k) and bf16(k - tf32(k)): [64 keys x 64] rows of 128 bytes, 128-byte swizzle
+    float v_hi[2][HD * 32];                        // V^T block as delivered: two 32-key slabs [64 x 32]
+    uint16_t v_bf[HD * BKEY], v_lo_bf[HD * BKEY];  // the same two bf16 copies of V^T [64 head columns x 64 keys]
     unsigned char mask_rows[BQ * kMaskPitch];      // this block's mask bytes, one padded row per query
     float exch[2][BQ];                             // row statistics exchanged between the two threads of a row
     uint64_t bar_q, bar_k, bar_v, bar_qs, bar_ks, bar_vs, bar_s, bar_p, bar_o;
@@ -125,18 +129,26 @@ struct AttnTcParams {
 // is handed to the MMA as it is (which again reads its upper 19 bits: what is dropped is below 2^-20 of x), so the split
 // needs no conversion instruction.
 __device__ __forceinline__ float lo_of_truncated(float x) { return x - __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
-// The MMA reads only the upper 19 bits of an fp32 operand in shared memory, so the tile TMA wrote already is the
-// "hi" operand (x truncated to TF32); the splitting threads write only the "lo" twin, for `n4` float4s.
-__device__ __forceinline__ void split_tile(const float* hi_buf, float* lo_buf, int n4, int t, int n_threads) {
-    const float4* hi = reinterpret_cast<const float4*>(hi_buf);
-    float4* lo = reinterpret_cast<float4*>(lo_buf);
-    for (int i = t; i < n4; i += n_threads) {
-        float4 v = hi[i], l;
-        l.x = lo_of_truncated(v.x);
-        l.y = lo_of_truncated(v.y);
-        l.z = lo_of_truncated(v.z);
-        l.w = lo_of_truncated(v.w);
-        lo[i] = l;
+// The MMA reads only the upper 19 bits of an fp32 operand in shared memory, so the tile TMA wrote already is the "hi"
+// operand of the main TF32 product.  The two correction products run as bf16 MMAs: this writes their B operands, bf16(x)
+// and bf16(x_lo), for a tile of 64 rows x 64 elements delivered as two 32-float slabs (128-byte rows, 16-byte chunk j of row
+// r at chunk j ^ (r & 7)); the bf16 tiles have 128-byte rows of 64 elements under the same swizzle.
+__device__ __forceinline__ void split_tile_bf16(const float* slabs, uint16_t* x_bf, uint16_t* lo_bf, int t, int n_threads) {
+    const float4* src = reinterpret_cast<const float4*>(slabs);
+    char* db = reinterpret_cast<char*>(x_bf);
+    char* dl = reinterpret_cast<char*>(lo_bf);
+    for (int i = t; i < 2 * 64 * 8; i += n_threads) {
+        const int sl = i >> 9, r = (i >> 3) & 63, j = (i & 7) ^ (r & 7);   // slab, row, logical 16-byte chunk of the slab row
+        const float4 v = src[i];
+        uint2 px, pl;
+        px.x = pack_bf16x2(v.x, v.y);
+        px.y = pack_bf16x2(v.z, v.w);
+        pl.x = pack_bf16x2(lo_of_truncated(v.x), lo_of_truncated(v.y));
+        pl.y = pack_bf16x2(lo_of_truncated(v.z), lo_of_truncated(v.w));
+        const int J = sl * 4 + (j >> 1);                                     // 16-byte chunk of the bf16 row (8 elements)
+        const int dst = r * 128 + ((J ^ (r & 7)) << 4) + ((j & 1) << 3);
+        *reinterpret_cast<uint2*>(db + dst) = px;
+        *reinterpret_cast<uint2*>(dl + dst) = pl;
     }
 }
 template <int N>
@@ -157,8 +169,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
     const int nblk = (Tk + BKEY - 1) / BKEY;
     volatile int* abort_flag = &s.abort_flag;
     constexpr uint32_t kQBytes = BQ * HD * 4, kKBytes = BKEY * HD * 4, kVBytes = HD * BKEY * 4;
-    constexpr uint32_t kColS = 0, kColPhi = 0, kColPlo = 64, kColO = 128, kColQlo = 192;   // P_hi replaces S in place
-    constexpr uint32_t kIdesc = umma_idesc_tf32(BQ, 64);   // both contractions produce 128 x 64 tiles (64 keys / 64 head columns)
+    // tensor-memory columns: S (P_hi replaces it in place) | bf16(P_lo) 32 + bf16(P) 32 | O | bf16(Q_lo) 32 + bf16(Q) 32
+    constexpr uint32_t kColS = 0, kColPhi = 0, kColPloB = 64, kColPB = 96, kColO = 128, kColQloB = 192, kColQB = 224;
+    constexpr uint32_t kIdesc = umma_idesc_tf32(BQ, 64);     // both contractions produce 128 x 64 tiles (64 keys / 64 head columns)
+    constexpr uint32_t kIdescBf = umma_idesc_bf16(BQ, 64);   // the correction products (bf16, K = 16 per instruction)
 
     if (threadIdx.x == 0) {
         mbar_init(&s.bar_q, 1);
@@ -237,17 +251,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
                         const uint32_t par = i & 1;
                         if (!mbar_wait(&s.bar_ks, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnK); break; }
                         tc_fence_after();
-                        // S = Q · K_blk^T: q_lo·k_hi (A from tensor memory), q_hi·k_lo, q_hi·k_hi (A from shared memory)
+                        // S = Q · K_blk^T: q_hi·k_hi as TF32 products (both operands as delivered in shared memory), then the
+                        // corrections bf16(q_lo)·bf16(k) and bf16(q)·bf16(k_lo) as bf16 products (A from tensor memory), 16 deep each
 #pragma unroll
                         for (int sl = 0; sl < 2; sl++) {
-                            const uint64_t qh = umma_desc_k_major<32>(smem_u32(s.q_hi[sl]));
-                            const uint64_t kh = umma_desc_k_major<32>(smem_u32(s.k_hi[sl])), kl = umma_desc_k_major<32>(smem_u32(s.k_lo[sl]));
+                            const uint64_t qh = umma_desc_k_major<32>(smem_u32(s.q_hi[sl])), kh = umma_desc_k_major<32>(smem_u32(s.k_hi[sl]));
 #pragma unroll
                             for (int kk = 0; kk < 4; kk++) {
                                 const uint64_t adv = uint64_t((kk * 32) >> 4);
-                                umma_tf32_ts(tmem + kColS, tmem + kColQlo + uint32_t(sl * 32 + kk * 8), kh + adv, kIdesc, (sl > 0 || kk > 0) ? 1u : 0u);
-                                umma_tf32(tmem + kColS, qh + adv, kl + adv, kIdesc, 1u);
-                                umma_tf32(tmem + kColS, qh + adv, kh + adv, kIdesc, 1u);
+                                umma_tf32(tmem + kColS, qh + adv, kh + adv, kIdesc, (sl > 0 || kk > 0) ? 1u : 0u);
+                            }
+                        }
+                        {
+                            const uint64_t kb = umma_desc_k_major_bytes<128>(smem_u32(s.k_bf)), klb = umma_desc_k_major_bytes<128>(smem_u32(s.k_lo_bf));
+#pragma unroll
+                            for (int kk = 0; kk < 4; kk++) {
+                                const uint64_t adv = uint64_t((kk * 32) >> 4);
+                                umma_bf16_ts(tmem + kColS, tmem + kColQloB + uint32_t(kk * 8), kb + adv, kIdescBf, 1u);
+                                umma_bf16_ts(tmem + kColS, tmem + kColQB + uint32_t(kk * 8), klb + adv, kIdescBf, 1u);
                             }
                         }
                         umma_commit(&s.bar_s);
@@ -258,17 +279,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
                         if (!mbar_wait(&s.bar_vs, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnV); break; }
                         if (!mbar_wait(&s.bar_p, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnP); break; }
                         tc_fence_after();
-                        // O_blk = P · V_blk   (A = P from tensor memory, B = V^T slabs, K-major over keys)
+                        // O_blk = P · V_blk   (A = P from tensor memory, B = V^T, K-major over keys): p_hi·v_hi as TF32 products, the
+                        // corrections bf16(p_lo)·bf16(v) and bf16(p)·bf16(v_lo) as bf16 products
 #pragma unroll
                         for (int ks = 0; ks < 2; ks++) {
-                            const uint64_t vh = umma_desc_k_major<32>(smem_u32(s.v_hi[ks])), vl = umma_desc_k_major<32>(smem_u32(s.v_lo[ks]));
+                            const uint64_t vh = umma_desc_k_major<32>(smem_u32(s.v_hi[ks]));
 #pragma unroll
                             for (int kk = 0; kk < 4; kk++) {
                                 const uint64_t adv = uint64_t((kk * 32) >> 4);
-                                const uint32_t pc = uint32_t(ks * 32 + kk * 8);
-                                umma_tf32_ts(tmem + kColO, tmem + kColPlo + pc, vh + adv, kIdesc, (ks > 0 || kk > 0) ? 1u : 0u);
-                                umma_tf32_ts(tmem + kColO, tmem + kColPhi + pc, vl + adv, kIdesc, 1u);
-                                umma_tf32_ts(tmem + kColO, tmem + kColPhi + pc, vh + adv, kIdesc, 1u);
+                                umma_tf32_ts(tmem + kColO, tmem + kColPhi + uint32_t(ks * 32 + kk * 8), vh + adv, kIdesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                            }
+                        }
+                        {
+                            const uint64_t vb = umma_desc_k_major_bytes<128>(smem_u32(s.v_bf)), vlb = umma_desc_k_major_bytes<128>(smem_u32(s.v_lo_bf));
+#pragma unroll
+                            for (int kk = 0; kk < 4; kk++) {
+                                const uint64_t adv = uint64_t((kk * 32) >> 4);
+                                umma_bf16_ts(tmem + kColO, tmem + kColPloB + uint32_t(kk * 8), vb + adv, kIdescBf, 1u);
+                                umma_bf16_ts(tmem + kColO, tmem + kColPB + uint32_t(kk * 8), vlb + adv, kIdescBf, 1u);
                             }
                         }
                         umma_commit(&s.bar_o);
@@ -285,12 +313,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
             for (int i = 0; i < n_act; i++) {
                 const uint32_t par = i & 1;
                 if (!mbar_wait(&s.bar_k, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnK); break; }
-                split_tile(s.k_hi[0], s.k_lo[0], 2 * BKEY * 32 / 4, t, nt);
+                split_tile_bf16(s.k_hi[0], s.k_bf, s.k_lo_bf, t, nt);
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s.bar_ks);
                 if (!mbar_wait(&s.bar_v, par, abort_flag)) { give_up(abort_flag, p.status, kErrAttnV); break; }
-                split_tile(s.v_hi[0], s.v_lo[0], 2 * HD * 32 / 4, t, nt);
+                split_tile_bf16(s.v_hi[0], s.v_bf, s.v_lo_bf, t, nt);
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s.bar_vs);
@@ -307,21 +335,23 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
         const uint8_t* mhead = p.mask + int64_t(b) * p.mask_sb + int64_t(h) * p.mask_sh;
         bool alive = true;   // a thread that gave up keeps walking the loop so that soft_sync() stays matched
         if (n_act > 0) {
-            // ---- the "lo" twin of this thread's row of Q (head columns [32*half, 32*half + 32)) goes into tensor memory ----
+            // ---- bf16(q_lo) and bf16(q) of this thread's row of Q (head columns [32*half, 32*half + 32)) go into tensor memory,
+            //      two elements per column (element k in the low half of word k/2) ----
             if (!mbar_wait(&s.bar_q, 0, abort_flag)) { give_up(abort_flag, p.status, kErrAttnQ); alive = false; }
             if (alive) {
                 const float4* src = reinterpret_cast<const float4*>(s.q_hi[half]) + row * 8;   // 128-byte rows, 16-byte chunks XOR-swizzled by row % 8
                 const int swz = row & 7;
-                uint32_t lo[32];
+                uint32_t ql[16], qx[16];
 #pragma unroll
                 for (int c = 0; c < 8; c++) {
                     const float4 v = src[c ^ swz];
-                    lo[4 * c + 0] = __float_as_uint(lo_of_truncated(v.x));
-                    lo[4 * c + 1] = __float_as_uint(lo_of_truncated(v.y));
-                    lo[4 * c + 2] = __float_as_uint(lo_of_truncated(v.z));
-                    lo[4 * c + 3] = __float_as_uint(lo_of_truncated(v.w));
+                    ql[2 * c + 0] = pack_bf16x2(lo_of_truncated(v.x), lo_of_truncated(v.y));
+                    ql[2 * c + 1] = pack_bf16x2(lo_of_truncated(v.z), lo_of_truncated(v.w));
+                    qx[2 * c + 0] = pack_bf16x2(v.x, v.y);
+                    qx[2 * c + 1] = pack_bf16x2(v.z, v.w);
                 }
-                tmem_st32(tmem + kColQlo + lane_base + uint32_t(half * 32), lo);
+                tmem_st16(tmem + kColQloB + lane_base + uint32_t(half * 16), ql);
+                tmem_st16(tmem + kColQB + lane_base + uint32_t(half * 16), qx);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
@@ -413,19 +443,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
             if (alive) {
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
-                    uint32_t r[16], lo[16];
+                    uint32_t r[16], pl[8], px[8];
                     tmem_ld16(scol + uint32_t(c * 16), r);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const float pv = fast_exp2(__uint_as_float(r[j]) - m_safe);
-                        psum += pv;
-                        // P_hi = pv as it is (the MMA reads only its upper 19 bits), P_lo = the 13 bits it does not see: exact, no conversion
-                        r[j] = __float_as_uint(pv);
-                        lo[j] = __float_as_uint(pv - __uint_as_float(__float_as_uint(pv) & 0xffffe000u));
+                    for (int j = 0; j < 16; j += 2) {
+                        const float p0 = fast_exp2(__uint_as_float(r[j]) - m_safe), p1 = fast_exp2(__uint_as_float(r[j + 1]) - m_safe);
+                        psum += p0;
+                        psum += p1;
+                        // P_hi = p as it is (the TF32 MMA reads only its upper 19 bits); the corrections take bf16(p_lo), the 13
+                        // bits it does not see, and bf16(p)
+                        r[j] = __float_as_uint(p0);
+                        r[j + 1] = __float_as_uint(p1);
+                        pl[j >> 1] = pack_bf16x2(lo_of_truncated(p0), lo_of_truncated(p1));
+                        px[j >> 1] = pack_bf16x2(p0, p1);
                     }
                     tmem_st16(scol + uint32_t(c * 16), r);
-                    tmem_st16(tmem + kColPlo + lane_base + uint32_t(half * 32 + c * 16), lo);
+                    tmem_st8(tmem + kColPloB + lane_base + uint32_t(half * 16 + c * 8), pl);
+                    tmem_st8(tmem + kColPB + lane_base + uint32_t(half * 16 + c * 8), px);
                 }
                 tmem_wait_st();
                 tc_fence_before();
@@ -559,7 +594,7 @@ int launch_attention_tc(const AttnArgs& a, float* vt_scratch, ExecCtx& ctx) {
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     dim3 grid(unsigned((a.T + BQ - 1) / BQ), unsigned(BH));
-    tag_launch(ctx, "attention_tf32x3_tcgen05", 4.0 * double(a.B) * a.H * double(a.T) * Tk * a.hd,
+    tag_launch(ctx, "attention_tf32_bf16x2_tcgen05", 4.0 * double(a.B) * a.H * double(a.T) * Tk * a.hd,
                4.0 * 2.0 * double(a.B) * (double(a.T) + Tk) * double(a.H) * a.hd + double(a.B) * a.T * Tk);
     attn_tc_kernel<<<grid, kAttnThreads, smem, ctx.stream>>>(mq, mk, mv, p);
     FXF_LAUNCHED(ctx);

@@ -453,7 +453,7 @@ std::unique_ptr<NodePlan> plan_mha(const Registry& reg, const TensorIds& in, con
     GemmArgs g1, g2;
     g1.M = M; g1.N = 3 * Dl; g1.K = D;
     g2.M = M; g2.N = D; g2.K = Dl;
-    pl->variant += gemm_variant_name(g1, env.gemm_mode, 148, env.tc_pairs) + (tc_attn ? "+attn-tcgen05-tf32x3+" : "+flash-fp32+") + gemm_variant_name(g2, env.gemm_mode, 148, env.tc_pairs);
+    pl->variant += gemm_variant_name(g1, env.gemm_mode, 148, env.tc_pairs) + (tc_attn ? "+attn-tcgen05-tf32+2bf16+" : "+flash-fp32+") + gemm_variant_name(g2, env.gemm_mode, 148, env.tc_pairs);
     return pl;
 }
 
@@ -586,7 +586,7 @@ std::unique_ptr<NodePlan> plan_cross_mha(const Registry& reg, const TensorIds& i
     g2.M = Mk; g2.N = 2 * Dl; g2.K = D;
     g3.M = Mq; g3.N = D; g3.K = Dl;
     pl->variant += gemm_variant_name(g1, env.gemm_mode, 148, env.tc_pairs) + "+" + gemm_variant_name(g2, env.gemm_mode, 148, env.tc_pairs) +
-                   (tc_attn ? "+attn-tcgen05-tf32x3+" : "+flash-fp32+") + gemm_variant_name(g3, env.gemm_mode, 148, env.tc_pairs);
+                   (tc_attn ? "+attn-tcgen05-tf32+2bf16+" : "+flash-fp32+") + gemm_variant_name(g3, env.gemm_mode, 148, env.tc_pairs);
     return pl;
 }
 
