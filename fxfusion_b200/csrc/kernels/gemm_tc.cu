@@ -252,7 +252,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     static_assert(!BF16 || (TS && BK == 32), "the bf16 mode takes A from tensor memory with 32-float slabs");
     constexpr bool HYB = VAR == 1, MIX = VAR == 2;
     static_assert(!HYB || (TS && !BF16), "hybrid: x_hi is the raw tile in shared memory, x_lo goes to tensor memory");
-    static_assert(!MIX || (!BF16 && BK == 16 && (TS != PAIR)), "mixed: 16-deep slabs (one bf16 MMA per correction); A in shared memory for CTA pairs, in tensor memory otherwise");
+    static_assert(!MIX || (!BF16 && (TS != PAIR) && (BK == 16 || (BK == 32 && PAIR))), "mixed: A in shared memory for CTA pairs (16- or 32-deep slabs), in tensor memory otherwise (16-deep)");
     static_assert(BN % 32 == 0, "tile width must be a multiple of 32 columns (16 per column half and staging step)");
     static_assert(!PAIR || (!BF16 && VAR != 1), "CTA pairs exist for the plain 3xTF32 and the mixed variants");
     constexpr int BNB = PAIR ? BN / 2 : BN;   // weight rows staged by this CTA
@@ -401,8 +401,14 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                                     // memory; then x_hi * w_hi as two 8-deep TF32 MMAs on the raw tiles
                                     const uint64_t a_raw = umma_desc_k_major<BK>(smem_u32(s.a[st]));
                                     const uint32_t al = smem_u32(s.a_lo[TS ? 0 : st]), bl = smem_u32(s.b_lo[BF16 ? 0 : st]);
-                                    umma_bf16_pair(tmem_acc, umma_desc_k_major_bytes<BK * 2>(al), umma_desc_k_major_bytes<BK * 2>(bl), kIdescBf, k > kc0 ? 1u : 0u);
-                                    umma_bf16_pair(tmem_acc, umma_desc_k_major_bytes<BK * 2>(al + uint32_t(BM * BK * 2)), umma_desc_k_major_bytes<BK * 2>(bl + uint32_t(kBfTileBytes)), kIdescBf, 1u);
+                                    const uint64_t d_xl = umma_desc_k_major_bytes<BK * 2>(al), d_wh = umma_desc_k_major_bytes<BK * 2>(bl);
+                                    const uint64_t d_xb = umma_desc_k_major_bytes<BK * 2>(al + uint32_t(BM * BK * 2)), d_wl = umma_desc_k_major_bytes<BK * 2>(bl + uint32_t(kBfTileBytes));
+#pragma unroll
+                                    for (int kk = 0; kk < BK / 16; kk++) {   // 16 bf16 = 32 bytes per instruction inside the swizzle row
+                                        const uint64_t adv = uint64_t((kk * 32) >> 4);
+                                        umma_bf16_pair(tmem_acc, d_xl + adv, d_wh + adv, kIdescBf, (k > kc0 || kk > 0) ? 1u : 0u);
+                                        umma_bf16_pair(tmem_acc, d_xb + adv, d_wl + adv, kIdescBf, 1u);
+                                    }
 #pragma unroll
                                     for (int kk = 0; kk < BK / 8; kk++) {
                                         const uint64_t adv = uint64_t((kk * 8 * 4) >> 4);
@@ -608,19 +614,24 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     const float4* hi = reinterpret_cast<const float4*>(s.a[st]);
                     float4* lo = reinterpret_cast<float4*>(s.a_lo[st]);
                     if (MIX) {
-                        // bf16(x_lo) and bf16(x) tiles, [128 rows x 16] bf16 = rows of 32 bytes with the 32-byte swizzle the MMA
-                        // descriptor names (16-byte chunk j of row r lies at chunk j ^ ((r >> 2) & 1)), one behind the other
+                        // bf16(x_lo) and bf16(x) tiles, [128 rows x BK] bf16 = rows of 2*BK bytes under the swizzle the MMA descriptor
+                        // names (32-byte rows: 16-byte chunk j of row r at j ^ ((r >> 2) & 1); 64-byte rows: at j ^ ((r >> 1) & 3)),
+                        // one tile behind the other.  The fp32 source rows are swizzled too (64-byte rows: chunk ^ ((r >> 1) & 3),
+                        // 128-byte rows: chunk ^ (r & 7)).
                         char* lob = reinterpret_cast<char*>(s.a_lo[st]);
+                        constexpr int CH = BK / 4;   // 16-byte chunks per fp32 row
 #pragma unroll
                         for (int i = 0; i < (BM * BK / 4) / 128; i++) {
-                            const int f = t + i * 128, row = f >> 2, c_log = (f & 3) ^ ((row >> 1) & 3);   // 64-byte rows of x: chunk ^ bits 1-2 of the row
+                            const int f = t + i * 128, row = f / CH;
+                            const int c_log = (f % CH) ^ (BK == 16 ? ((row >> 1) & 3) : (row & 7));
                             const float4 v = hi[f];
                             uint2 pl, px;
                             pl.x = pack_bf16x2(lo_of_truncated(v.x), lo_of_truncated(v.y));
                             pl.y = pack_bf16x2(lo_of_truncated(v.z), lo_of_truncated(v.w));
                             px.x = pack_bf16x2(v.x, v.y);
                             px.y = pack_bf16x2(v.z, v.w);
-                            const int dst = row * 32 + (((c_log >> 1) ^ ((row >> 2) & 1)) << 4) + ((c_log & 1) << 3);
+                            const int dsw = BK == 16 ? ((row >> 2) & 1) : ((row >> 1) & 3);
+                            const int dst = row * (2 * BK) + (((c_log >> 1) ^ dsw) << 4) + ((c_log & 1) << 3);
                             *reinterpret_cast<uint2*>(lob + dst) = pl;
                             *reinterpret_cast<uint2*>(lob + BM * BK * 2 + dst) = px;
                         }
@@ -1130,7 +1141,9 @@ int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows) {
     if (a.w_mixed) {
         gemm_tc_mixed_variant(a.M, a.N, a.K, ctx.sm_count, ctx.gemm_ws != nullptr, allow_few_rows, &bn, ctx.tc_pair != 1);
         switch (bn) {
-            case 256: return launch_tc<256, 16, 6, false, false, 2, true>(a, ctx);
+            // 32-deep slabs, three stages: the MMA-issuing thread pays its two barrier waits and its commit (about 90 cycles each)
+            // per slab, which at 16-deep slabs and four instructions left the tensor pipe waiting for the thread (+9 % measured)
+            case 256: return launch_tc<256, 32, 3, false, false, 2, true>(a, ctx);
             case 192: return launch_tc<192, 16, 5, true, false, 2>(a, ctx);
             case 128: return launch_tc<128, 16, 8, true, false, 2>(a, ctx);
             default: return launch_tc<64, 16, 8, true, false, 2>(a, ctx);
