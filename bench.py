@@ -535,8 +535,17 @@ def report_c3(args, world, local, tp_size, dp_size, K, W, Ke, ms, e2e_ms, e2e_ma
     step_mhz = clocks.get("sm_mhz") if clocks else None
     emulated = args.precision != "bf16"
     per_clock = None
-    if emulated and tf32_peak and step_mhz and tf32_peak.get("burst_sm_mhz"):
-        per_clock = (achieved / step_mhz) / (tf32_peak["tf32_tflops_burst"] / tf32_slots(top_name) / tf32_peak["burst_sm_mhz"])
+    if emulated and tf32_peak and step_mhz:
+        # flops per clock of the library GEMM: from its ~2 s loop (clock always sampled); the 15 ms burst only when a clock
+        # sample fell inside it
+        if tf32_peak.get("sustained_sm_mhz"):
+            lib_per_mhz = tf32_peak["tf32_tflops_sustained"] / tf32_peak["sustained_sm_mhz"]
+        elif tf32_peak.get("burst_sm_mhz"):
+            lib_per_mhz = tf32_peak["tf32_tflops_burst"] / tf32_peak["burst_sm_mhz"]
+        else:
+            lib_per_mhz = None
+        if lib_per_mhz:
+            per_clock = (achieved / step_mhz) / (lib_per_mhz / tf32_slots(top_name))
     roofline = {"bound": "tensor", "kernel": top_name, "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": (traffic[0] / traffic[1]) if traffic and traffic[1] == top["n"] else None,
                 "algorithmic_bytes": top["bytes"] / top["n"], "peak_source": peaks["source"] + " cuBLAS bf16, sustained",
