@@ -730,6 +730,73 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             }
             const float* brow = p.bias + col_base + cq;              // only dereferenced when p.bias is set
             float* wrow = ws_mine + (row0 + rsub) * BN + chalf * HALF + cq;   // this lane's first row of the partial tile
+            if (!p.vec_out && !p.cv.enabled && un.nparts == 1 && p.residual == nullptr) {
+                // ---- rows that do not start on 16-byte boundaries (a pitch like the 50257-column vocabulary) ----
+                // Row r of this warp's 32 x HALF block starts `a` floats past a 16-byte boundary (a depends on the row).  The
+                // block is stored as aligned 16-byte pieces shifted by a: the staging rows carry the last four columns of the
+                // previous group in front of the current sixteen, so that the four pieces of a group, columns
+                // [16g - a + 4q, +4), lie inside one staging row; the 4 - a leading and a trailing columns of the row segment
+                // are stored by the row's owner straight from its registers.  Bias and activation are applied in place first.
+                if (p.bias) {
+#pragma unroll
+                    for (int j = 0; j < HALF; j++) {
+                        const int64_t c = col_base + j;
+                        sum[j] += c < p.N ? __ldg(p.bias + c) : 0.f;   // the same address in every lane: one broadcast load
+                    }
+                }
+                if (p.relu) {
+#pragma unroll
+                    for (int j = 0; j < HALF; j++) sum[j] = relu_keep_nan(sum[j]);
+                }
+                const int qq = lane & 3;
+                float* rp[4];
+                int ra[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int64_t grow = int64_t(tm) * BM + row0 + i * 8 + rsub;
+                    rp[i] = out_base + grow * p.ldo + col_base;
+                    ra[i] = grow < p.M ? int((reinterpret_cast<uintptr_t>(rp[i]) >> 2) & 3) : -1;   // -1: no such row
+                }
+#pragma unroll
+                for (int g = 0; g < HALF / 16; g++) {
+                    if (col_base + g * 16 - 3 >= p.N) continue;   // warp-uniform: nothing of this group (or its carry) is inside
+                    if (g > 0) *reinterpret_cast<float4*>(stage + lane * kStagePad) = make_float4(sum[g * 16 - 4], sum[g * 16 - 3], sum[g * 16 - 2], sum[g * 16 - 1]);
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4)
+                        *reinterpret_cast<float4*>(stage + lane * kStagePad + 4 + j) = make_float4(sum[g * 16 + j], sum[g * 16 + j + 1], sum[g * 16 + j + 2], sum[g * 16 + j + 3]);
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int a = ra[i];
+                        if (a < 0 || (g == 0 && qq == 0 && a > 0)) continue;   // the piece left of the block belongs to the neighbour
+                        const int c = g * 16 - a + 4 * qq;                      // first column of the piece, relative to col_base
+                        const float* sp = stage + (i * 8 + rsub) * kStagePad + 4 - a + 4 * qq;
+                        const float4 v = make_float4(sp[0], sp[1], sp[2], sp[3]);
+                        const int64_t cabs = col_base + c;
+                        if (cabs + 3 < p.N) {
+                            *reinterpret_cast<float4*>(rp[i] + c) = v;
+                        } else {
+                            if (cabs < p.N) rp[i][c] = v.x;
+                            if (cabs + 1 < p.N) rp[i][c + 1] = v.y;
+                            if (cabs + 2 < p.N) rp[i][c + 2] = v.z;
+                        }
+                    }
+                    __syncwarp();
+                }
+                {   // the row owner's leading 4 - a and trailing a columns
+                    const int64_t grow = int64_t(tm) * BM + row0 + lane;
+                    float* op = out_base + grow * p.ldo + col_base;
+                    const int a = int((reinterpret_cast<uintptr_t>(op) >> 2) & 3);
+                    if (grow < p.M && a > 0) {
+#pragma unroll
+                        for (int j = 0; j < 3; j++) {
+                            if (j < 4 - a && col_base + j < p.N) op[j] = sum[j];
+                            if (j < a && col_base + HALF - 1 - j < p.N) op[HALF - 1 - j] = sum[HALF - 1 - j];
+                        }
+                    }
+                }
+                continue;
+            }
 #pragma unroll
             for (int g = 0; g < HALF / 16; g++) {
                 const int64_t col = col_base + g * 16;
