@@ -552,7 +552,7 @@ size_t attention_tc_scratch_bytes(int64_t B, int64_t T, int64_t H) {
     return size_t(B) * size_t(T) * size_t(H) * HD * sizeof(float) + round_up(size_t(B) * size_t(H) * size_t((T + 31) / 32), 256);
 }
 
-int launch_attention_tc(const AttnArgs& a, float* vt_scratch, ExecCtx& ctx) {
+int launch_attention_tc(const AttnArgs& a, float* vt_scratch, ExecCtx& ctx, bool v_transposed) {
     FXF_CHECK(vt_scratch != nullptr && aligned16(vt_scratch), "attention: tensor-core path needs its V^T buffer");
     const int64_t BH = int64_t(a.B) * a.H;
     const int Tk = a.kv ? a.Tk : a.T;                     // keys per batch
@@ -560,10 +560,12 @@ int launch_attention_tc(const AttnArgs& a, float* vt_scratch, ExecCtx& ctx) {
     const int64_t ldk = a.kv ? a.ld_kv : a.ld_qkv;
     const int n32 = (Tk + 31) / 32;
     dim3 pgrid(unsigned((Tk + 63) / 64), unsigned(BH));
-    tag_launch(ctx, "attention_v_transpose", 0, 8.0 * double(BH) * Tk * HD);
     unsigned char* vflags = reinterpret_cast<unsigned char*>(vt_scratch + size_t(BH) * size_t(Tk) * HD);
-    attn_vt_kernel<<<pgrid, 256, 0, ctx.stream>>>(kvp, ldk, a.v_off, Tk, a.H, vt_scratch, vflags, n32);
-    FXF_LAUNCHED(ctx);
+    if (!v_transposed) {   // otherwise the projection's epilogue has written V^T and the flags already
+        tag_launch(ctx, "attention_v_transpose", 0, 8.0 * double(BH) * Tk * HD);
+        attn_vt_kernel<<<pgrid, 256, 0, ctx.stream>>>(kvp, ldk, a.v_off, Tk, a.H, vt_scratch, vflags, n32);
+        FXF_LAUNCHED(ctx);
+    }
 
     CUtensorMap mq, mk, mv;
     // Q and K tiles come straight out of the packed projection: [B, T, ld] with the row pitch of qkv

@@ -149,6 +149,12 @@ struct TcParams {
     int64_t push_rows;
     int push_rank;
     int push_owners;   // > 1: row tiles are walked owner-interleaved (tiles_m is a multiple of it)
+    // Transposed column range (GemmArgs::vt_*): vt_out != NULL switches it on; vt_col0 is a multiple of the column half of
+    // the tile, the half a multiple of 64, vt_T a multiple of 32 and no tile is cut along K.
+    float* vt_out;
+    unsigned char* vt_flags;
+    int64_t vt_col0;
+    int vt_T, vt_heads, vt_n32;
 };
 
 // x - (x with its 13 low mantissa bits cleared): the part of x a TF32 MMA does not see.  The difference is exact in fp32 and
@@ -730,6 +736,31 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             }
             const float* brow = p.bias + col_base + cq;              // only dereferenced when p.bias is set
             float* wrow = ws_mine + (row0 + rsub) * BN + chalf * HALF + cq;   // this lane's first row of the partial tile
+            if (p.vt_out != nullptr && col_base >= p.vt_col0) {
+                // ---- the V third of a packed QKV projection: transposed per head, straight from the registers ----
+                // lane = row (token t of batch b), register j = column: for a fixed column the 32 lanes write 32 consecutive
+                // keys of one V^T row (128 bytes).  A 32-row group never straddles two sequences (vt_T % 32 == 0).
+                const int64_t grow = int64_t(tm) * BM + row0 + lane;
+                const bool ok = grow < p.M;
+                const int64_t b = grow / p.vt_T, t = grow - b * p.vt_T;
+#pragma unroll
+                for (int hh = 0; hh < HALF / 64; hh++) {
+                    const int64_t c0 = col_base + hh * 64;             // first column of this head inside the result
+                    if (c0 >= p.N) continue;
+                    const int64_t h = (c0 - p.vt_col0) >> 6;
+                    float* dst = p.vt_out + ((b * p.vt_heads + h) * 64) * int64_t(p.vt_T) + t;
+                    bool bad = false;
+#pragma unroll
+                    for (int d = 0; d < 64; d++) {
+                        const float v = sum[hh * 64 + d] + (p.bias ? __ldg(p.bias + c0 + d) : 0.f);
+                        bad = bad || (v - v != 0.f);   // NaN or infinity
+                        if (ok) dst[int64_t(d) * p.vt_T] = v;
+                    }
+                    const unsigned any_bad = __ballot_sync(0xffffffffu, ok && bad);
+                    if (lane == 0 && ok) p.vt_flags[(b * p.vt_heads + h) * p.vt_n32 + (t >> 5)] = any_bad ? 1 : 0;
+                }
+                continue;
+            }
             if (!p.vec_out && !p.cv.enabled && un.nparts == 1 && p.residual == nullptr) {
                 // ---- rows that do not start on 16-byte boundaries (a pitch like the 50257-column vocabulary) ----
                 // Row r of this warp's 32 x HALF block starts `a` floats past a 16-byte boundary (a depends on the row).  The
@@ -1042,6 +1073,12 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
     p.bias = a.bias; p.residual = cv ? cv->residual : a.residual; p.out = a.out; p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo;
     p.relu = a.relu ? 1 : 0;
     p.vec_out = (a.ldo % 4 == 0 && aligned16(a.out) && (a.bias == nullptr || aligned16(a.bias)) && (p.residual == nullptr || aligned16(p.residual))) ? 1 : 0;
+    if (a.vt_out != nullptr) {
+        FXF_CHECK(!cv && a.residual == nullptr && !a.relu && a.push_rows == 0 && (BN / 2) % 64 == 0 && a.vt_col0 % (BN / 2) == 0 && (a.N - a.vt_col0) % 64 == 0 &&
+                      a.vt_T > 0 && a.vt_T % 32 == 0 && a.M % a.vt_T == 0 && a.vt_flags != nullptr && a.vt_heads * 64 == a.N - a.vt_col0,
+                  "gemm: the transposed column range does not fit this kernel variant");
+        p.vt_out = a.vt_out; p.vt_flags = a.vt_flags; p.vt_col0 = a.vt_col0; p.vt_T = a.vt_T; p.vt_heads = a.vt_heads; p.vt_n32 = a.vt_n32;
+    }
     if (a.push_rows > 0) {
         const int64_t owners = a.M / a.push_rows;
         FXF_CHECK(!cv && a.residual == nullptr && a.push_out != nullptr && a.push_rows % BM == 0 && a.M % a.push_rows == 0 && owners >= 1 &&
@@ -1072,7 +1109,7 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
     const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
     // work units are scheduled over CTAs, or over CTA pairs (each CTA of a pair needs its own partial-tile slot and flags)
     const int workers = PAIR ? ctx.sm_count / 2 : ctx.sm_count, slots_per_unit = PAIR ? 2 : 1;
-    TailSplit ts = plan_tail(tiles, a.K, BN, workers, ctx.gemm_ws != nullptr && ctx.gemm_flags != nullptr);
+    TailSplit ts = plan_tail(tiles, a.K, BN, workers, ctx.gemm_ws != nullptr && ctx.gemm_flags != nullptr && a.vt_out == nullptr);
     if (ts.parts > 1 && (size_t(ts.tail) * ts.parts * slots_per_unit * size_t(BM * BN) * sizeof(float) > ctx.gemm_ws_bytes ||
                          ts.tail * ts.parts * slots_per_unit * kEpiWarps > ctx.gemm_flag_count))
         ts = TailSplit{tiles, 0, 1, 0.0, 0.0};
@@ -1202,11 +1239,25 @@ const char* gemm_tc_mixed_variant(int64_t M, int64_t N, int64_t K, int sm_count,
     }
 }
 
+bool gemm_tc_vt_ok(const GemmArgs& a, const ExecCtx& ctx) {
+    if (a.vt_out == nullptr || a.vt_flags == nullptr || a.residual != nullptr || a.relu || a.push_rows != 0 || a.w_is_bf16) return false;
+    if (!gemm_tc_supported(a) || a.vt_T <= 0 || a.vt_T % 32 != 0 || a.M % a.vt_T != 0 || (a.N - a.vt_col0) != int64_t(a.vt_heads) * 64) return false;
+    int bn = 0;
+    if (a.w_mixed) gemm_tc_mixed_variant(a.M, a.N, a.K, ctx.sm_count, false, false, &bn, ctx.tc_pair != 1);
+    else {
+        gemm_tc_variant(a.M, a.N, a.K, ctx.sm_count, false, false, &bn, false);
+        if (ctx.tc_pair != 1 && a.M > BM && ctx.sm_count >= 2 && bn >= 224) bn = 256;
+    }
+    if (bn != 256 && bn != 128) return false;          // column halves of whole heads (64 columns)
+    return a.vt_col0 % (bn / 2) == 0;
+}
+
 int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows) {
     FXF_CHECK(gemm_tc_supported(a, allow_few_rows), "tensor-core GEMM called with an unsupported problem");
     int bn = 0;
+    const bool ks = ctx.gemm_ws != nullptr && a.vt_out == nullptr;   // a transposed column range rules out tiles cut along K
     if (a.w_mixed) {
-        gemm_tc_mixed_variant(a.M, a.N, a.K, ctx.sm_count, ctx.gemm_ws != nullptr, allow_few_rows, &bn, ctx.tc_pair != 1);
+        gemm_tc_mixed_variant(a.M, a.N, a.K, ctx.sm_count, ks, allow_few_rows, &bn, ctx.tc_pair != 1);
         switch (bn) {
             // 32-deep slabs, three stages: the MMA-issuing thread pays its two barrier waits and its commit (about 90 cycles each)
             // per slab, which at 16-deep slabs and four instructions left the tensor pipe waiting for the thread (+9 % measured)
@@ -1216,7 +1267,7 @@ int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows) {
             default: return launch_tc<64, 16, 8, true, false, 2>(a, ctx);
         }
     }
-    gemm_tc_variant(a.M, a.N, a.K, ctx.sm_count, ctx.gemm_ws != nullptr, allow_few_rows, &bn, false);
+    gemm_tc_variant(a.M, a.N, a.K, ctx.sm_count, ks, allow_few_rows, &bn, false);
     if (a.w_is_bf16) {  // bf16 mode: one product per logical product, A converted into tensor memory
         if (bn >= 192 && a.N > 128) return launch_tc<192, 32, 6, true, true>(a, ctx);
         return launch_tc<128, 32, 8, true, true>(a, ctx);

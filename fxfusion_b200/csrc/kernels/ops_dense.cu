@@ -389,6 +389,17 @@ int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params
 
     GemmArgs g;
     fill_gemm(g, static_cast<const float*>(x.ptr), pl->s[0], &pl->s[1], qkv, M, D, QKVl, false);
+    // Where the projection runs on a tensor-core variant whose column halves are whole heads, its epilogue writes the V third
+    // transposed (and the finite flags of V) straight into the attention kernel's V^T buffer: no transpose launch.
+    bool v_transposed = false;
+    if (have_vt && hd == 64 && ctx.gemm_mode != FXF_GEMM_FP32_SIMT && use_tc(g, ctx.gemm_mode)) {
+        g.vt_out = vt;
+        g.vt_flags = reinterpret_cast<unsigned char*>(vt + size_t(B) * size_t(Hl) * size_t(T) * 64);
+        g.vt_col0 = 2 * Dl;
+        g.vt_T = int(T); g.vt_heads = int(Hl); g.vt_n32 = int((T + 31) / 32);
+        v_transposed = gemm_tc_vt_ok(g, ctx);
+        if (!v_transposed) { g.vt_out = nullptr; g.vt_flags = nullptr; }
+    }
     if (launch_gemm(g, ctx)) return 1;
 
     AttnArgs a;
@@ -399,8 +410,9 @@ int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params
     a.mask_sb = ms[0]; a.mask_sh = ms[1]; a.mask_sq = ms[2]; a.mask_sk = ms[3];
     a.scale_divisor = p.floats[0];
     if (have_vt && attention_tc_supported(a, ctx.gemm_mode)) {
-        if (launch_attention_tc(a, vt, ctx)) return 1;
+        if (launch_attention_tc(a, vt, ctx, v_transposed)) return 1;
     } else {
+        FXF_CHECK(!v_transposed, "mha: the projection wrote V transposed but the tensor-core attention kernel cannot run");
         if (launch_attention(a, ctx)) return 1;
     }
 

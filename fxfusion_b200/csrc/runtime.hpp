@@ -276,7 +276,18 @@ struct GemmArgs {
     float* const* push_out = nullptr;
     int64_t push_rows = 0;
     int push_rank = 0;
+    // Transposed column range (the V third of a packed QKV projection, tensor-core kernels only): columns [vt_col0, N) of
+    // the result are not written to `out`; column vt_col0 + 64*h + d of row b*vt_T + t goes to vt_out[((b*vt_heads + h)*64 + d)
+    // * vt_T + t] (V^T per batch and head, keys contiguous: the B operand of the attention's second product), and
+    // vt_flags[(b*vt_heads + h)*vt_n32 + t/32] tells whether any of those values of a 32-row group is NaN or infinite.
+    // Ask gemm_tc_vt_ok() first.
+    float* vt_out = nullptr;
+    unsigned char* vt_flags = nullptr;
+    int64_t vt_col0 = 0;
+    int vt_T = 0, vt_heads = 0, vt_n32 = 0;
 };
+// Whether launch_gemm would serve the transposed column range of `a` (fields vt_* filled in) on this context.
+bool gemm_tc_vt_ok(const GemmArgs& a, const ExecCtx& ctx);
 int launch_gemm(const GemmArgs& a, ExecCtx& ctx);
 int launch_gemm_simt(const GemmArgs& a, ExecCtx& ctx);
 int launch_gemm_tc(const GemmArgs& a, ExecCtx& ctx, bool allow_few_rows = false);
@@ -357,6 +368,7 @@ int tp_all_gather(const void* send, void* recv, int64_t bytes, ExecCtx& ctx);
 // tcgen05 path (head_dim 64): needs 6*B*T*H*64 floats of scratch for the split, per-head operand copies
 bool attention_tc_supported(const AttnArgs& a, int gemm_mode);
 size_t attention_tc_scratch_bytes(int64_t B, int64_t T, int64_t H);
-int launch_attention_tc(const AttnArgs& a, float* split_scratch, ExecCtx& ctx);
+// v_transposed: V^T and its finite flags are already in the scratch (written by the projection's epilogue)
+int launch_attention_tc(const AttnArgs& a, float* split_scratch, ExecCtx& ctx, bool v_transposed = false);
 
 }  // namespace fxf

@@ -39,6 +39,26 @@ def test_c1_mlp_matches_oracle(built_lib, tmp_path, precision):
     eng.close()
 
 
+@pytest.mark.parametrize("T,fused", [(128, True), (100, False)])
+def test_qkv_projection_writes_v_transposed(built_lib, tmp_path, T, fused):
+    """GPT block at d_model 768: where the sequence length is a multiple of 32 the QKV projection's epilogue writes the V
+    third transposed for the attention kernel, and the separate transpose kernel is not launched; otherwise it is.  Same
+    result as the oracle either way."""
+    cfg = lowering.GPTConfig(768, 12, 500, 4, 1)
+    g = lowering.gpt_graph(cfg, lowering.gpt_params(cfg, 0), batch=4, seq=T, name=f"gpt_vt_{T}")
+    _, buf, mask = _gpt_inputs(cfg, 4, T, T - 8)
+    eng = _engine(g, tmp_path)
+    got = eng.run([buf.cuda(), mask.cuda()])[0].cpu()
+    kernels = [r["kernel"] for r in eng.profile_launches()]
+    assert any("attention_tf32" in k for k in kernels), kernels
+    assert ("attention_v_transpose" not in kernels) == fused, kernels
+    want = GraphOracle(g).run([buf, mask])[0]
+    ok, info = compare_outputs(got, want, atol=ATOL, rtol=RTOL)
+    assert ok, info
+    assert eng.device_status() == 0
+    eng.close()
+
+
 def _gpt_inputs(cfg, B, T, prompt_len, seed=0):
     tokens = torch.from_numpy(lowering.decode_prompt(B, prompt_len, cfg.vocab, seed))
     buf = make_static_buffer(tokens, T)
