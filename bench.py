@@ -45,7 +45,7 @@ B, T, PROMPT = 32, 256, 128
 METRIC = "gpt2_small_greedy_decode_tokens_per_s"
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel's launches in ONE forward of this
 # workload on one GPU, summed over an ncu capture of a forward; bench.py cannot run ncu itself.
-NCU_DRAM_BYTES_PER_FORWARD = {"gemm_tf32_bf16x2_tcgen05": (6991554048, 49),   # default arithmetic
+NCU_DRAM_BYTES_PER_FORWARD = {"gemm_tf32_bf16x2_tcgen05": (7092533248, 49),   # default arithmetic
                               "gemm_tf32x3_tcgen05": (7035996416, 49)}        # --precision fp32_3xtf32
 CPU_BUDGET_S = 150.0  # wall-clock budget of a CPU arm; the per-step batch is sized to fit it
 NVLINK_GBS_PER_DIRECTION = 770.0  # measured peer copy on this pool's B200s (nominal 900)
