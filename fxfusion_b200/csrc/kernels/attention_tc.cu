@@ -65,7 +65,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __device__ __forceinline__ void soft_sync(int quarter) { asm volatile("bar.sync %0, 64;" ::"r"(quarter + 1) : "memory"); }
 
 // ---- V transpose -------------------------------------------------------------------------------------
-// Also records, per (batch*head, 32-key slab), whether any V element is NaN or infinite: vflags[bh * n32 + slab].
+// Also records, per (batch*head, half of the head's 64 columns, 32-key slab), whether any V element is NaN or infinite:
+// vflags[(bh * 2 + half) * n32 + slab] (this kernel reports a slab under half 0 and clears half 1).
 __global__ void __launch_bounds__(256) attn_vt_kernel(const float* __restrict__ qkv, int64_t ld, int64_t v_off, int T, int H, float* __restrict__ vt,
                                                       unsigned char* __restrict__ vflags, int n32) {
     // one block moves 64 keys x 64 head columns: rows of 256 bytes on both sides
@@ -84,8 +85,12 @@ __global__ void __launch_bounds__(256) attn_vt_kernel(const float* __restrict__ 
     const int bad0 = __syncthreads_or(bad[0]), bad1 = __syncthreads_or(bad[1]);
     if (tid == 0) {
         const int sl = blockIdx.x * 2;
-        vflags[int64_t(bh) * n32 + sl] = bad0 ? 1 : 0;
-        if (sl + 1 < n32) vflags[int64_t(bh) * n32 + sl + 1] = bad1 ? 1 : 0;
+        vflags[int64_t(bh) * 2 * n32 + sl] = bad0 ? 1 : 0;
+        vflags[(int64_t(bh) * 2 + 1) * n32 + sl] = 0;
+        if (sl + 1 < n32) {
+            vflags[int64_t(bh) * 2 * n32 + sl + 1] = bad1 ? 1 : 0;
+            vflags[(int64_t(bh) * 2 + 1) * n32 + sl + 1] = 0;
+        }
     }
     for (int idx = tid; idx < HD * 64; idx += 256) {
         int d = idx >> 6, tt = idx & 63, t = t0 + tt;
@@ -110,7 +115,7 @@ struct alignas(1024) AttnTcSmem {
 static_assert(2 * (sizeof(AttnTcSmem) + 2048) <= 228 * 1024, "two CTAs of the attention kernel must fit one SM");
 
 struct AttnTcParams {
-    const unsigned char* vflags;   // per (batch*head, 32-key slab): V has a non-finite element
+    const unsigned char* vflags;   // per (batch*head, column half of the head, 32-key slab): V has a non-finite element
     int n32;                       // slabs per (batch*head)
     const uint8_t* mask;
     float* ctx;
@@ -210,7 +215,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constan
         }
         // a block whose V rows hold NaN or infinity is kept: 0 * inf has to reach the output
         for (int sl = threadIdx.x; sl < p.n32; sl += kAttnThreads)
-            if (p.vflags[int64_t(bh) * p.n32 + sl]) mine |= 1ull << (sl / (BKEY / 32));
+            if (p.vflags[int64_t(bh) * 2 * p.n32 + sl] | p.vflags[(int64_t(bh) * 2 + 1) * p.n32 + sl]) mine |= 1ull << (sl / (BKEY / 32));
         const unsigned int lo32 = __reduce_or_sync(0xffffffffu, (unsigned int)(mine & 0xffffffffull));
         const unsigned int hi32 = __reduce_or_sync(0xffffffffu, (unsigned int)(mine >> 32));
         mine = (unsigned long long)lo32 | ((unsigned long long)hi32 << 32);
@@ -547,9 +552,9 @@ bool attention_tc_supported(const AttnArgs& a, int gemm_mode) {
     return true;
 }
 
-// V^T [B*H, 64, T] followed by one "non-finite" byte per (batch*head, 32-key slab)
+// V^T [B*H, 64, T] followed by one "non-finite" byte per (batch*head, column half of the head, 32-key slab)
 size_t attention_tc_scratch_bytes(int64_t B, int64_t T, int64_t H) {
-    return size_t(B) * size_t(T) * size_t(H) * HD * sizeof(float) + round_up(size_t(B) * size_t(H) * size_t((T + 31) / 32), 256);
+    return size_t(B) * size_t(T) * size_t(H) * HD * sizeof(float) + round_up(size_t(2) * size_t(B) * size_t(H) * size_t((T + 31) / 32), 256);
 }
 
 int launch_attention_tc(const AttnArgs& a, float* vt_scratch, ExecCtx& ctx, bool v_transposed) {

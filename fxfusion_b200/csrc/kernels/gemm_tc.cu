@@ -150,7 +150,7 @@ struct TcParams {
     int push_rank;
     int push_owners;   // > 1: row tiles are walked owner-interleaved (tiles_m is a multiple of it)
     // Transposed column range (GemmArgs::vt_*): vt_out != NULL switches it on; vt_col0 is a multiple of the column half of
-    // the tile, the half a multiple of 64, vt_T a multiple of 32 and no tile is cut along K.
+    // the tile, the half a multiple of 32 (half a head), vt_T a multiple of 32 and no tile is cut along K.
     float* vt_out;
     unsigned char* vt_flags;
     int64_t vt_col0;
@@ -744,20 +744,21 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                 const bool ok = grow < p.M;
                 const int64_t b = grow / p.vt_T, t = grow - b * p.vt_T;
 #pragma unroll
-                for (int hh = 0; hh < HALF / 64; hh++) {
-                    const int64_t c0 = col_base + hh * 64;             // first column of this head inside the result
+                for (int hh = 0; hh < HALF / 32; hh++) {               // 32 columns = half a head at a time
+                    const int64_t c0 = col_base + hh * 32;             // first column of this piece inside the result
                     if (c0 >= p.N) continue;
-                    const int64_t h = (c0 - p.vt_col0) >> 6;
-                    float* dst = p.vt_out + ((b * p.vt_heads + h) * 64) * int64_t(p.vt_T) + t;
+                    const int64_t v0 = c0 - p.vt_col0, h = v0 >> 6;
+                    const int d0 = int(v0 & 32);                       // 0 or 32: which half of the head
+                    float* dst = p.vt_out + ((b * p.vt_heads + h) * 64 + d0) * int64_t(p.vt_T) + t;
                     bool bad = false;
 #pragma unroll
-                    for (int d = 0; d < 64; d++) {
-                        const float v = sum[hh * 64 + d] + (p.bias ? __ldg(p.bias + c0 + d) : 0.f);
+                    for (int d = 0; d < 32; d++) {
+                        const float v = sum[hh * 32 + d] + (p.bias ? __ldg(p.bias + c0 + d) : 0.f);
                         bad = bad || (v - v != 0.f);   // NaN or infinity
                         if (ok) dst[int64_t(d) * p.vt_T] = v;
                     }
                     const unsigned any_bad = __ballot_sync(0xffffffffu, ok && bad);
-                    if (lane == 0 && ok) p.vt_flags[(b * p.vt_heads + h) * p.vt_n32 + (t >> 5)] = any_bad ? 1 : 0;
+                    if (lane == 0 && ok) p.vt_flags[((b * p.vt_heads + h) * 2 + (d0 >> 5)) * p.vt_n32 + (t >> 5)] = any_bad ? 1 : 0;
                 }
                 continue;
             }
@@ -1074,7 +1075,7 @@ int launch_tc(const GemmArgs& a, ExecCtx& ctx, const ConvTcArgs* cv = nullptr, c
     p.relu = a.relu ? 1 : 0;
     p.vec_out = (a.ldo % 4 == 0 && aligned16(a.out) && (a.bias == nullptr || aligned16(a.bias)) && (p.residual == nullptr || aligned16(p.residual))) ? 1 : 0;
     if (a.vt_out != nullptr) {
-        FXF_CHECK(!cv && a.residual == nullptr && !a.relu && a.push_rows == 0 && (BN / 2) % 64 == 0 && a.vt_col0 % (BN / 2) == 0 && (a.N - a.vt_col0) % 64 == 0 &&
+        FXF_CHECK(!cv && a.residual == nullptr && !a.relu && a.push_rows == 0 && (BN / 2) % 32 == 0 && a.vt_col0 % (BN / 2) == 0 && (a.N - a.vt_col0) % 64 == 0 &&
                       a.vt_T > 0 && a.vt_T % 32 == 0 && a.M % a.vt_T == 0 && a.vt_flags != nullptr && a.vt_heads * 64 == a.N - a.vt_col0,
                   "gemm: the transposed column range does not fit this kernel variant");
         p.vt_out = a.vt_out; p.vt_flags = a.vt_flags; p.vt_col0 = a.vt_col0; p.vt_T = a.vt_T; p.vt_heads = a.vt_heads; p.vt_n32 = a.vt_n32;
@@ -1248,7 +1249,7 @@ bool gemm_tc_vt_ok(const GemmArgs& a, const ExecCtx& ctx) {
         gemm_tc_variant(a.M, a.N, a.K, ctx.sm_count, false, false, &bn, false);
         if (ctx.tc_pair != 1 && a.M > BM && ctx.sm_count >= 2 && bn >= 224) bn = 256;
     }
-    if (bn != 256 && bn != 128) return false;          // column halves of whole heads (64 columns)
+    if (bn == 224) return false;                       // column halves must be multiples of half a head (32 columns)
     return a.vt_col0 % (bn / 2) == 0;
 }
 

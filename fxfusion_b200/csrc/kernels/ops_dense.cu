@@ -389,7 +389,7 @@ int k_mha(Registry& reg, const TensorIds& in, const TensorIds& out, const Params
 
     GemmArgs g;
     fill_gemm(g, static_cast<const float*>(x.ptr), pl->s[0], &pl->s[1], qkv, M, D, QKVl, false);
-    // Where the projection runs on a tensor-core variant whose column halves are whole heads, its epilogue writes the V third
+    // Where the projection runs on a tensor-core variant whose column halves are multiples of half a head, its epilogue writes the V third
     // transposed (and the finite flags of V) straight into the attention kernel's V^T buffer: no transpose launch.
     bool v_transposed = false;
     if (have_vt && hd == 64 && ctx.gemm_mode != FXF_GEMM_FP32_SIMT && use_tc(g, ctx.gemm_mode)) {

@@ -279,7 +279,8 @@ struct GemmArgs {
     // Transposed column range (the V third of a packed QKV projection, tensor-core kernels only): columns [vt_col0, N) of
     // the result are not written to `out`; column vt_col0 + 64*h + d of row b*vt_T + t goes to vt_out[((b*vt_heads + h)*64 + d)
     // * vt_T + t] (V^T per batch and head, keys contiguous: the B operand of the attention's second product), and
-    // vt_flags[(b*vt_heads + h)*vt_n32 + t/32] tells whether any of those values of a 32-row group is NaN or infinite.
+    // vt_flags[((b*vt_heads + h)*2 + d/32)*vt_n32 + t/32] tells whether any of those values of a 32-row group and half a
+    // head is NaN or infinite.
     // Ask gemm_tc_vt_ok() first.
     float* vt_out = nullptr;
     unsigned char* vt_flags = nullptr;
