@@ -54,3 +54,20 @@ def test_product_never_imports_the_oracle():
             text = path.read_text(errors="ignore")
             assert not re.search(r"^\s*(from|import)\s+oracle\b", text, re.M), path
             assert "oracle/" not in text, path
+
+
+def test_gemm_dispatch_rule_is_a_host_side_query(built_lib):
+    """fxf_gemm_variant answers without a GPU which kernel a dense layer of a given shape takes: the benchmark's layer
+    shapes go to CTA pairs with the default arithmetic (one TF32 product + two bf16 corrections), a K that is not a multiple
+    of 8 keeps three TF32 products, batch-sized layers stay on the fp32 weight-streaming kernel."""
+    from fxfusion_b200.kernels import gemm_variant
+    pair = "tcgen05-tf32+2bf16-256x256-pair-smemA"
+    for shape in [(8192, 3072, 768), (8192, 2304, 768), (8192, 768, 3072), (8192, 50257, 768), (8192, 768, 1536)]:
+        assert gemm_variant(*shape) == pair, shape
+    assert gemm_variant(8192, 768, 768) == "tcgen05-tf32+2bf16-128x192-tmemA"
+    assert gemm_variant(1024, 64, 256) == "tcgen05-tf32+2bf16-128x64-tmemA"
+    assert gemm_variant(5000, 1111, 500) == "tcgen05-tf32x3-128x192-tmemA"          # K % 8 != 0
+    assert gemm_variant(8192, 3072, 768, precision="fp32_3xtf32") == "tcgen05-tf32x3-256x256-pair-smemA"
+    assert gemm_variant(8192, 3072, 768, precision="bf16") == "tcgen05-bf16-128x192"
+    assert gemm_variant(8192, 3072, 768, precision="fp32_simt") == "simt128x128"
+    assert gemm_variant(32, 512, 512) == "skinny32x8"                                # the MLP of the first benchmark configuration
